@@ -1,0 +1,277 @@
+"""Bank-parameterised GPT: parameters, initialisation and the autograd (oracle) forward.
+
+Parameter layout (``parameter-golf-rs/crates/pg-model/src/model.rs:18-67``; Python record
+``records/track_10min_16mb/2026-03-23_LeakyReLU_LegalTTT_ParallelMuon/train_gpt.py:812-870``):
+``tok_emb[V,d]`` (tied output), banks ``qo_bank[2n,d,d]`` (Q then O), ``kv_bank[2n,kv,d]`` (K then V),
+``mlp_up_bank[n,mlp,d]``, ``mlp_down_bank[n,d,mlp]``; per-block controls are stored stacked over layers:
+``attn_scale[n,d]``, ``mlp_scale[n,d]``, ``resid_mix[n,2,d]``, ``q_gain[n,H]``; ``skip_weights[min(n/2,n-n/2),d]``,
+``smear_gate[d]``, BigramHash ``bigram_embed[B,bd]``/``bigram_proj[d,bd]``/``bigram_scale``, value embedding
+``ve_embed[V,ve]``/``ve_proj[kv,ve]``/``ve_scale``/``ve_layer_scales``, optional attention gates.
+
+`gpt_forward` is the single definition of the model function (forward math of
+``model.rs:681-827`` / block ``:448-663``); the CUDA engine is tested against it.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import reference as R
+from ..spec import ModelSpec
+
+BANKS = ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank")
+EMBEDS = ("tok_emb", "bigram_embed", "ve_embed", "lm_head")
+
+
+def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
+    n, d, kv, mlp, H = m.num_layers, m.model_dim, m.kv_dim, m.mlp_dim, m.num_heads
+    enc = n // 2
+    sh = {
+        "tok_emb": (m.vocab_size, d),
+        "qo_bank": (2 * n, d, d),
+        "kv_bank": (2 * n, kv, d),
+        "mlp_up_bank": (n, mlp, d),
+        "mlp_down_bank": (n, d, mlp),
+        "attn_scale": (n, d),
+        "mlp_scale": (n, d),
+        "resid_mix": (n, 2, d),
+        "q_gain": (n, H),
+    }
+    if m.skip_topology == "unet" and min(enc, n - enc) > 0:
+        sh["skip_weights"] = (min(enc, n - enc), d)
+    if m.smear_gate:
+        sh["smear_gate"] = (d,)
+    if m.bigram.enabled:
+        sh["bigram_embed"] = (m.bigram.vocab_size, m.bigram.dim)
+        if m.bigram.dim != d:
+            sh["bigram_proj"] = (d, m.bigram.dim)
+        sh["bigram_scale"] = (1,)
+    if m.value_embedding.enabled:
+        sh["ve_embed"] = (m.vocab_size, m.value_embedding.dim)
+        sh["ve_proj"] = (kv, m.value_embedding.dim)
+        sh["ve_scale"] = (1,)
+        sh["ve_layer_scales"] = (len(m.value_embedding.layers),)
+    if m.attn_out_gate.enabled:
+        sh["attn_gate_weight"] = (n, H, m.attn_out_gate.width)
+        sh["attn_gate_bias"] = (n, H)
+    if m.sparse_attn_gate.enabled:
+        sh["sparse_attn_gate_weight"] = (n, H, m.sparse_attn_gate.width)
+    if not m.tie_embeddings:
+        sh["lm_head"] = (m.vocab_size, d)
+    return sh
+
+
+def count_params(m: ModelSpec) -> int:
+    return sum(math.prod(s) for s in param_shapes(m).values())
+
+
+def _orthogonal(rows: int, cols: int, gen: torch.Generator) -> torch.Tensor:
+    a = torch.randn(max(rows, cols), min(rows, cols), generator=gen, dtype=torch.float32)
+    q, r = torch.linalg.qr(a)
+    q = q * torch.sign(torch.diagonal(r))[None, :]
+    return q if rows >= cols else q.t().contiguous()
+
+
+def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    """Random initialisation of the Python records (``…03-23…/train_gpt.py:875-897``): tied embedding
+    N(0, std), orthogonal Q/K/V/up, zero O/down, zero bigram tables, scale 0.05; controls at identity."""
+    g = torch.Generator().manual_seed(seed)
+    n, d = m.num_layers, m.model_dim
+    p: Dict[str, torch.Tensor] = {}
+    for name, shape in param_shapes(m).items():
+        p[name] = torch.zeros(shape, dtype=torch.float32)
+    p["tok_emb"].normal_(0.0, m.tied_embed_init_std if m.tie_embeddings else 1.0, generator=g)
+    for i in range(n):
+        p["qo_bank"][i] = _orthogonal(d, d, g)
+        p["kv_bank"][i] = _orthogonal(m.kv_dim, d, g)
+        p["kv_bank"][n + i] = _orthogonal(m.kv_dim, d, g)
+        p["mlp_up_bank"][i] = _orthogonal(m.mlp_dim, d, g)
+    p["attn_scale"].fill_(1.0)
+    p["mlp_scale"].fill_(1.0)
+    p["resid_mix"][:, 0].fill_(1.0)
+    p["q_gain"].fill_(m.qk_gain_init)
+    if "skip_weights" in p:
+        p["skip_weights"].fill_(1.0)
+    if "bigram_scale" in p:
+        p["bigram_scale"].fill_(0.05)
+    if "ve_embed" in p:
+        p["ve_embed"].normal_(0.0, 0.01, generator=g)
+        p["ve_scale"].fill_(0.1)
+        p["ve_layer_scales"].fill_(1.0)
+    if "attn_gate_bias" in p:
+        p["attn_gate_bias"].fill_(4.0)
+    return {k: v.to(device=device, dtype=dtype) for k, v in p.items()}
+
+
+def fill_deterministic(m: ModelSpec, device="cpu", dtype=torch.float32) -> Dict[str, torch.Tensor]:
+    """Seed-free, dense, non-degenerate weights for parity tests: element ``i`` of tensor number ``t``
+    is ``amp * sin(0.37*i + 1.3*t + 0.11*(i mod 97))`` with a per-tensor amplitude, so every code
+    path (O/down projections, bigram, gates) carries signal. Same role as the reference's
+    ``fill_deterministic`` (``pg-model/src/model.rs:281-331``); the pattern itself is this project's."""
+    p: Dict[str, torch.Tensor] = {}
+    for t, (name, shape) in enumerate(sorted(param_shapes(m).items())):
+        numel = math.prod(shape)
+        i = torch.arange(numel, dtype=torch.float64)
+        fan_in = shape[-1] if len(shape) >= 2 else 1
+        amp = {"tok_emb": 0.3, "bigram_embed": 0.3, "ve_embed": 0.3}.get(name, 1.0 / math.sqrt(fan_in) if len(shape) >= 2 else 0.2)
+        v = amp * torch.sin(0.37 * i + 1.3 * t + 0.11 * (i % 97))
+        if name in ("attn_scale", "mlp_scale", "skip_weights", "q_gain"):
+            v = 1.0 + 0.25 * v / amp * 0.2
+        if name == "resid_mix":
+            v = v.reshape(shape)
+            v[:, 0] = 0.9 + 0.1 * v[:, 0]
+            v[:, 1] = 0.2 * v[:, 1]
+        if name in ("bigram_scale", "ve_scale"):
+            v = torch.full(shape, 0.3, dtype=torch.float64)
+        if name == "ve_layer_scales":
+            v = torch.full(shape, 0.8, dtype=torch.float64)
+        p[name] = v.reshape(shape).to(device=device, dtype=dtype)
+    return p
+
+
+def layer_ln_scale(m: ModelSpec, layer: int) -> float:
+    return 1.0 / math.sqrt(layer + 1) if m.ln_scale else 1.0
+
+
+def layer_schedule(m: ModelSpec):
+    """Execution order as (layer index, pass index): recurrent layers run the block twice in a row
+    (``pg-model/src/model.rs:666-671``)."""
+    order = []
+    for i in range(m.num_layers):
+        reps = 2 if (m.recurrence.enabled and m.recurrence.start_layer <= i < m.recurrence.start_layer + m.recurrence.repeat_layers) else 1
+        order.extend((i, r) for r in range(reps))
+    return order
+
+
+def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = False, lora=None, return_kv: bool = False, taps=None):
+    n, H, Hkv, D = m.num_layers, m.num_heads, m.num_kv_heads, m.head_dim
+    B, T, d = x.shape
+    dt = x.dtype
+    wq = p["qo_bank"][i]
+    wo = p["qo_bank"][n + i]
+    wk, wv = p["kv_bank"][i], p["kv_bank"][n + i]
+    wu, wd = p["mlp_up_bank"][i], p["mlp_down_bank"][i]
+    if qat:
+        wq, wo, wk, wv, wu, wd = (R.fake_quant_int6_ste(w) for w in (wq, wo, wk, wv, wu, wd))
+    s_l = layer_ln_scale(m, i)
+    mix = p["resid_mix"][i].to(dt)
+    x_in = mix[0][None, None, :] * x + mix[1][None, None, :] * x0
+    h = R.rms_norm(x_in, s_l)
+    if taps is not None:
+        taps.add(i, "qkv", h)
+    q = F.linear(h, wq.to(dt))
+    if lora is not None:
+        a, b, alpha = lora["a"][i], lora["b"][i], lora["alpha"]
+        q = q + (alpha / a.shape[0]) * F.linear(F.linear(h, a.to(dt)), b.to(dt))
+    k = F.linear(h, wk.to(dt))
+    v = F.linear(h, wv.to(dt))
+    if m.value_embedding.enabled and i in m.value_embedding.layers:
+        li = m.value_embedding.layers.index(i)
+        ve = F.linear(p["ve_embed"][ids].to(dt), p["ve_proj"].to(dt))
+        v = v + (p["ve_layer_scales"][li] * p["ve_scale"][0]).to(dt) * ve
+    q = q.reshape(B, T, H, D)
+    k = k.reshape(B, T, Hkv, D)
+    v = v.reshape(B, T, Hkv, D)
+    q, k = R.qk_norm_rope_gain(q, k, cos, sin, m.rope_dims, p["q_gain"][i])
+    y = R.causal_gqa_attention(q, k, v)
+    if i in m.xsa_layers():
+        y = R.xsa(y, v)
+    if m.attn_out_gate.enabled:
+        y = R.attn_out_gate(y, h, p["attn_gate_weight"][i], p["attn_gate_bias"][i])
+    if m.sparse_attn_gate.enabled:
+        y = R.sparse_attn_gate(y, h, p["sparse_attn_gate_weight"][i], m.sparse_attn_gate.scale)
+    if taps is not None:
+        taps.add(i, "o", y.reshape(B, T, d))
+    attn = F.linear(y.reshape(B, T, d), wo.to(dt))
+    x_mid = x_in + p["attn_scale"][i].to(dt)[None, None, :] * attn
+    mlp_in = R.rms_norm(x_in if m.parallel_residual.enabled else x_mid, s_l)
+    if taps is not None:
+        taps.add(i, "up", mlp_in)
+    hid = R.act_sq(F.linear(mlp_in, wu.to(dt)), m.leaky_slope if m.activation == "leaky_relu_sq" else 0.0)
+    if taps is not None:
+        taps.add(i, "down", hid)
+    out = x_mid + p["mlp_scale"][i].to(dt)[None, None, :] * F.linear(hid, wd.to(dt))
+    if return_kv:
+        return out, (k, v)
+    return out
+
+
+def gpt_hidden(m: ModelSpec, p, ids: torch.Tensor, qat: bool = False, lora=None, dtype=None, taps=None):
+    """Final-norm hidden states [B,T,d]."""
+    dt = dtype or p["tok_emb"].dtype
+    B, T = ids.shape
+    x = p["tok_emb"][ids].to(dt)
+    if m.bigram.enabled:
+        bg = p["bigram_embed"][R.bigram_hash(ids, m.bigram.vocab_size)].to(dt)
+        if "bigram_proj" in p:
+            bg = F.linear(bg, p["bigram_proj"].to(dt))
+        x = x + p["bigram_scale"][0].to(dt) * bg
+    x = R.rms_norm(x)
+    if m.smear_gate:
+        x = R.smear_gate(x, p["smear_gate"], ids, m.smear_gate_boundary_token_id)
+    x0 = x
+    rd = m.rope_dims
+    cos, sin = R.rope_tables(T, rd, m.rope.base, train_seq_len=1024, device=ids.device) if rd > 0 else (None, None)
+    enc = m.num_layers // 2
+    unet = m.skip_topology == "unet" and "skip_weights" in p
+    skips = []
+    sched = layer_schedule(m)
+    for j, (i, rep) in enumerate(sched):
+        last_pass = j + 1 == len(sched) or sched[j + 1][0] != i
+        if unet and i >= enc and rep == 0 and skips:
+            x = x + p["skip_weights"][i - enc].to(dt)[None, None, :] * skips.pop()
+        x = block_forward(m, p, i, x, x0, ids, cos, sin, qat=qat, lora=lora, taps=taps)
+        if unet and i < enc and last_pass:
+            skips.append(x)
+    return R.rms_norm(x)
+
+
+def gpt_logits(m: ModelSpec, p, ids, qat: bool = False, lora=None, dtype=None):
+    """Soft-capped logits [B,T,V]."""
+    h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
+    w = p["tok_emb"] if m.tie_embeddings else p["lm_head"]
+    z = F.linear(h, w.to(h.dtype))
+    return m.logit_softcap * torch.tanh(z.float() / m.logit_softcap)
+
+
+def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dtype=None, reduction: str = "mean"):
+    """Training loss: mean soft-capped cross-entropy over all tokens (``reduction='none'`` gives the
+    per-token losses [B,T])."""
+    h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
+    w = p["tok_emb"] if m.tie_embeddings else p["lm_head"]
+    z = F.linear(h, w.to(h.dtype))
+    loss = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction=reduction)
+    return loss.reshape(ids.shape) if reduction == "none" else loss
+
+
+def bank_views(m: ModelSpec, p) -> Dict[str, torch.Tensor]:
+    """Zero-copy per-group 2-D views used by export and quantisation: ``qo_bank.q`` [n*d, d] etc.
+    (``parameter-golf-rs/crates/pg-quant/src/export.rs:48-126``)."""
+    n, d, kv, mlp = m.num_layers, m.model_dim, m.kv_dim, m.mlp_dim
+    return {
+        "qo_bank.q": p["qo_bank"][:n].reshape(n * d, d),
+        "qo_bank.o": p["qo_bank"][n:].reshape(n * d, d),
+        "kv_bank.k": p["kv_bank"][:n].reshape(n * kv, d),
+        "kv_bank.v": p["kv_bank"][n:].reshape(n * kv, d),
+        "mlp_up_bank": p["mlp_up_bank"].reshape(n * mlp, d),
+        "mlp_down_bank": p["mlp_down_bank"].reshape(n * d, mlp),
+        "tok_emb": p["tok_emb"],
+    }
+
+
+def overlaps_storage(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Alias guard: do two tensors share any byte of the same storage?
+    (``parameter-golf-rs/crates/pg-core/src/tensor.rs:349-367``)."""
+    if a.untyped_storage().data_ptr() != b.untyped_storage().data_ptr():
+        return False
+
+    def span(t):
+        lo = t.storage_offset() * t.element_size()
+        ext = sum((s - 1) * st for s, st in zip(t.shape, t.stride()) if s > 0) + 1 if t.numel() else 0
+        return lo, lo + ext * t.element_size()
+
+    (a0, a1), (b0, b1) = span(a), span(b)
+    return a0 < b1 and b0 < a1

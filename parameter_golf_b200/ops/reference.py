@@ -1,0 +1,146 @@
+"""Plain PyTorch fp32 statements of every model op (the CPU oracle).
+
+Each function is the mathematical definition that the sm_100a kernels are tested against, and the
+implementation used on CPU. Backward passes come from autograd and are checked against central
+finite differences in the tests, as the reference does for its own CPU oracles
+(``parameter-golf-rs/crates/pg-kernels/src/{rms_norm,rope,attention,xsa,smear_gate,bigram_hash,
+cross_entropy,activations}.rs``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+RMS_EPS = 1e-6
+
+
+def _f(x: torch.Tensor) -> torch.Tensor:
+    """Promote to fp32 for the arithmetic; float64 inputs (finite-difference tests) stay float64."""
+    return x if x.dtype == torch.float64 else x.float()
+
+
+def rms_norm(x: torch.Tensor, scale: float = 1.0, eps: float = RMS_EPS) -> torch.Tensor:
+    """``y = x * scale / sqrt(mean(x^2) + eps)`` over the last dim (``rms_norm.rs``; eps 1e-6 as in
+    ``pg-model/src/model.rs:470``)."""
+    xf = _f(x)
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * scale).to(x.dtype)
+
+
+def rope_tables(seq_len: int, rope_dims: int, base: float = 10000.0, train_seq_len: int = 0, device=None):
+    """cos/sin tables of shape [seq_len, rope_dims/2], ``theta = pos / base^(2i/rope_dims)``
+    (``pg-kernels/src/rope.rs:13-28``). When ``seq_len > train_seq_len > 0`` the base is rescaled
+    NTK-style (``records/.../2026-03-23_.../train_gpt.py:578-584``)."""
+    rd = rope_dims
+    if train_seq_len and seq_len > train_seq_len and rd > 2:
+        base = base * ((seq_len / train_seq_len) ** (rd / (rd - 2)))
+    inv = 1.0 / (base ** (torch.arange(0, rd, 2, dtype=torch.float32, device=device) / rd))
+    fr = torch.outer(torch.arange(seq_len, dtype=torch.float32, device=device), inv)
+    return fr.cos(), fr.sin()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rope_dims: int) -> torch.Tensor:
+    """Half-split rotary on the first ``rope_dims`` of the last dim. ``x``: [B, T, H, D]."""
+    if rope_dims <= 0:
+        return x
+    half = rope_dims // 2
+    c = cos[None, : x.shape[1], None, :].to(x.dtype)
+    s = sin[None, : x.shape[1], None, :].to(x.dtype)
+    x1, x2, rest = x[..., :half], x[..., half:rope_dims], x[..., rope_dims:]
+    return torch.cat((x1 * c + x2 * s, -x1 * s + x2 * c, rest), dim=-1)
+
+
+def qk_norm_rope_gain(q, k, cos, sin, rope_dims, q_gain, eps: float = RMS_EPS):
+    """Per-head RMSNorm of q and k, partial RoPE, then ``q *= gain[h]``. q: [B,T,H,D], k: [B,T,Hkv,D]."""
+    q = apply_rope(rms_norm(q, eps=eps), cos, sin, rope_dims)
+    k = apply_rope(rms_norm(k, eps=eps), cos, sin, rope_dims)
+    return q * q_gain.to(q.dtype)[None, None, :, None], k
+
+
+def causal_gqa_attention(q, k, v):
+    """Causal softmax attention with grouped KV heads, scale 1/sqrt(D), batched (each batch row is
+    one sequence). q: [B,T,H,D]; k, v: [B,T,Hkv,D] -> [B,T,H,D]. Written out explicitly in fp32."""
+    B, T, H, D = q.shape
+    Hkv = k.shape[2]
+    g = H // Hkv
+    qf = _f(q).permute(0, 2, 1, 3).reshape(B, Hkv, g, T, D)
+    kf = _f(k).permute(0, 2, 1, 3)[:, :, None]
+    vf = _f(v).permute(0, 2, 1, 3)[:, :, None]
+    s = (qf @ kf.transpose(-1, -2)) / math.sqrt(D)
+    mask = torch.ones(T, T, dtype=torch.bool, device=q.device).tril()
+    s = s.masked_fill(~mask, float("-inf"))
+    y = torch.softmax(s, dim=-1) @ vf
+    return y.reshape(B, H, T, D).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def xsa(y, v, eps: float = 1e-8):
+    """Exclusive self attention: remove from each head output its component along that token's own
+    value vector, ``z = y - (<y,v>/(|v|^2+eps)) v`` (``pg-kernels/src/xsa.rs:35``). y: [B,T,H,D], v: [B,T,Hkv,D]."""
+    B, T, H, D = y.shape
+    Hkv = v.shape[2]
+    yg = _f(y).reshape(B, T, Hkv, H // Hkv, D)
+    vf = _f(v)[:, :, :, None, :]
+    coef = (yg * vf).sum(-1, keepdim=True) / (vf.pow(2).sum(-1, keepdim=True) + eps)
+    return (yg - coef * vf).reshape(B, T, H, D).to(y.dtype)
+
+
+def attn_out_gate(y, h, weight, bias):
+    """``y *= 2*sigmoid(bias_h + W_h . h[:w])`` per (token, head). y: [B,T,H,D], h: [B,T,d], weight: [H,w]."""
+    w = weight.shape[1]
+    g = 2.0 * torch.sigmoid(_f(h[..., :w]) @ _f(weight).t() + _f(bias))
+    return (_f(y) * g[..., None]).to(y.dtype)
+
+
+def sparse_attn_gate(y, h, weight, scale: float):
+    """``y *= sigmoid(scale * W_h . h[:w])`` per (token, head)."""
+    w = weight.shape[1]
+    g = torch.sigmoid(scale * (_f(h[..., :w]) @ _f(weight).t()))
+    return (_f(y) * g[..., None]).to(y.dtype)
+
+
+def smear_gate(x, gate, ids=None, boundary_id=None):
+    """``out = (1-s)*x + s*x_prev`` with ``s = sigmoid(gate)`` per feature; ``x_prev`` is zero at the
+    first position of a sequence and, when ``boundary_id`` is given, where the current token equals
+    it (``pg-kernels/src/smear_gate.rs:33-51``). x: [B,T,d]."""
+    s = torch.sigmoid(_f(gate)).to(x.dtype)[None, None, :]
+    x_prev = torch.cat([torch.zeros_like(x[:, :1]), x[:, :-1]], dim=1)
+    if boundary_id is not None and ids is not None:
+        x_prev = x_prev * (ids != boundary_id).to(x.dtype)[..., None]
+    return (1 - s) * x + s * x_prev
+
+
+def bigram_hash(ids: torch.Tensor, buckets: int) -> torch.Tensor:
+    """``((36313*cur) xor (27191*prev)) mod (buckets-1)`` in wrapping 32-bit arithmetic; the first
+    position of each sequence maps to the sentinel bucket ``buckets-1``
+    (``pg-kernels/src/bigram_hash.rs``; ``records/.../2026-03-23_.../train_gpt.py:700-706``). ids: [B,T]."""
+    t = ids.to(torch.int64)
+    mod = buckets - 1
+    cur = (36313 * t[..., 1:]) & 0xFFFFFFFF
+    prev = (27191 * t[..., :-1]) & 0xFFFFFFFF
+    out = torch.empty_like(t)
+    out[..., 0] = mod
+    out[..., 1:] = torch.bitwise_xor(cur, prev) % mod
+    return out
+
+
+def act_sq(x, slope: float):
+    """``leaky_relu(x, slope)^2``; slope 0 is relu^2."""
+    return F.leaky_relu(x, negative_slope=slope).square()
+
+
+def softcap_cross_entropy(logits, targets, cap: float, reduction: str = "mean"):
+    """``CE(cap * tanh(z / cap))`` in fp32 (``pg-kernels/src/cross_entropy.rs``)."""
+    c = cap * torch.tanh(_f(logits) / cap)
+    return F.cross_entropy(c.reshape(-1, c.shape[-1]), targets.reshape(-1), reduction=reduction)
+
+
+def fake_quant_int6_ste(w: torch.Tensor) -> torch.Tensor:
+    """Late-QAT straight-through estimator: per-row ``s = max(|w|)/31`` (floored at 1/31),
+    ``w_q = clamp(round(w/s), -32, 31) * s``; forward uses ``w_q`` and the gradient passes to ``w``
+    (``records/.../2026-03-23_.../train_gpt.py:541-553``)."""
+    with torch.no_grad():
+        w32 = _f(w)
+        scale = (w32.abs().amax(dim=-1, keepdim=True) / 31.0).clamp_min(1.0 / 31.0)
+        wq = (torch.clamp(torch.round(w32 / scale), -32, 31) * scale).to(w.dtype)
+    return w + (wq - w).detach()

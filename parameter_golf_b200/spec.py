@@ -1,0 +1,603 @@
+"""Run specification: TOML ``RunSpec`` + CLI overrides + ``train_gpt.py`` environment names.
+
+Three configuration surfaces are accepted and merged into one validated, fingerprinted object:
+
+* a TOML file with the same section/key names as the reference's ``RunSpec``
+  (``parameter-golf-rs/crates/pg-model/src/spec.rs:137-718``): ``name``, ``mode``,
+  ``[model]``, ``[train]``, ``[quant]``, ``[eval]``; every key is optional;
+* ``key=value`` overrides (``train.matrix_lr=0.02``) from the command line
+  (``parameter-golf-rs/crates/pg-train/src/main.rs:132-208``);
+* the environment variables of the Python entrypoint (``train_gpt.py:39-87`` and the record
+  scripts' extensions), e.g. ``NUM_LAYERS``, ``TRAIN_BATCH_TOKENS``, ``XSA_LAST_N``.
+
+``RunSpec.validate`` holds the fail-closed rules (``pg-model/src/plan.rs:369-485``) and
+``RunSpec.fingerprint`` the 64-bit variant fingerprint stamped into artifacts
+(``pg-model/src/plan.rs:487-529``).
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+import tomllib
+from dataclasses import dataclass, field, fields, is_dataclass
+from typing import Any, Optional
+
+RUN_MODES = ("smoke", "proxy", "record_shaped_proxy", "record")
+TRAIN_BACKENDS = ("cpu", "cuda_single", "cuda_single_parity", "cuda_distributed")
+DIST_OPT_BACKENDS = ("all_reduce_replicated_muon", "sharded_parallel_muon")
+QUANT_SCHEMES = ("none", "gptq_lite_int6", "mixed_int5_int6", "aggressive", "tight_int7_int4", "full_gptq_int6")
+COMPRESSION_MODES = ("none", "zstd22", "lzma9", "pergroup")
+CALIBRATION_MODES = ("disabled", "self_generated")
+ADAPTATION_BACKENDS = ("none", "cpu_q_only", "gpu_lora_phased", "full_sgd", "lact", "slot")
+NS_PROFILES = ("simple", "quintic", "polar_express")
+FAMILIES = (
+    "baseline_sp8192", "xsa_all_sp8192", "recurrence_mid_sp8192", "parallel_resid_sp8192",
+    "hybrid_competitive_sp8192", "frontier_1855_like",
+    # families of this framework, named after the benchmark configurations
+    "tiny_cpu", "baseline_9l", "record_11l",
+)
+
+
+@dataclass
+class BigramSpec:
+    enabled: bool = False
+    vocab_size: int = 2048
+    dim: int = 128
+
+
+@dataclass
+class RopeSpec:
+    mode: str = "partial"          # none | partial | yarn (yarn is declared and rejected)
+    dims: int = 16                 # 0 or head_dim => full rotary
+    base: float = 10000.0
+
+
+@dataclass
+class ValueEmbeddingSpec:
+    enabled: bool = False
+    dim: int = 128
+    layers: list = field(default_factory=lambda: [9, 10])
+
+
+@dataclass
+class RecurrenceSpec:
+    enabled: bool = False
+    start_layer: int = 0
+    repeat_layers: int = 0
+
+
+@dataclass
+class ParallelResidualSpec:
+    enabled: bool = False
+    split_attention_mlp: bool = False
+
+
+@dataclass
+class AttnOutGateSpec:
+    enabled: bool = False
+    width: int = 12
+
+
+@dataclass
+class SparseAttnGateSpec:
+    enabled: bool = False
+    width: int = 12
+    scale: float = 1.0
+
+
+@dataclass
+class ModelSpec:
+    family: str = "record_11l"
+    vocab_size: int = 1024
+    num_layers: int = 11
+    model_dim: int = 512
+    num_heads: int = 8
+    num_kv_heads: int = 4
+    mlp_mult: float = 3.0
+    activation: str = "leaky_relu_sq"     # relu_sq | leaky_relu_sq
+    leaky_slope: float = 0.5
+    train_seq_len: int = 2048
+    eval_seq_len: int = 2048
+    bigram: BigramSpec = field(default_factory=BigramSpec)
+    xsa_last_n: int = 0
+    value_embedding: ValueEmbeddingSpec = field(default_factory=ValueEmbeddingSpec)
+    skip_topology: str = "unet"           # none | unet
+    recurrence: RecurrenceSpec = field(default_factory=RecurrenceSpec)
+    parallel_residual: ParallelResidualSpec = field(default_factory=ParallelResidualSpec)
+    attn_out_gate: AttnOutGateSpec = field(default_factory=AttnOutGateSpec)
+    sparse_attn_gate: SparseAttnGateSpec = field(default_factory=SparseAttnGateSpec)
+    rope: RopeSpec = field(default_factory=RopeSpec)
+    smear_gate: bool = False
+    smear_gate_boundary_token_id: Optional[int] = None
+    logit_softcap: float = 30.0
+    qk_gain_init: float = 1.5
+    ln_scale: bool = False
+    tie_embeddings: bool = True
+    tied_embed_init_std: float = 0.005
+    compute_precision: str = "bf16_tensor_core"  # f32 (CPU oracle) | bf16_tensor_core
+
+    @property
+    def head_dim(self) -> int:
+        return self.model_dim // self.num_heads
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def mlp_dim(self) -> int:
+        return int(self.mlp_mult * self.model_dim)
+
+    @property
+    def rope_dims(self) -> int:
+        if self.rope.mode == "none":
+            return 0
+        d = self.rope.dims
+        return self.head_dim if d <= 0 or d >= self.head_dim else d
+
+    def xsa_layers(self) -> list:
+        return list(range(max(0, self.num_layers - self.xsa_last_n), self.num_layers))
+
+
+@dataclass
+class TrainSpec:
+    backend: str = "cpu"
+    distributed_optimizer_backend: str = "all_reduce_replicated_muon"
+    batch_tokens: int = 524_288
+    seq_len: int = 2048
+    grad_accum_steps: int = 0           # 0 = automatic: 8 // world_size on CUDA backends, 1 on cpu
+    train_data_pattern: Optional[str] = None
+    validation_data_pattern: Optional[str] = None
+    rank: int = 0
+    world_size: int = 1
+    artifact_path: str = "artifact.pgrs"
+    warmup_steps: int = 0
+    total_iterations: int = 9000
+    warmdown_iters: int = 3500
+    warmdown_frac: float = 0.0
+    min_lr_scale: float = 0.0
+    wallclock_warmdown: bool = True
+    max_wallclock_seconds: float = 600.0
+    matrix_lr: float = 0.025
+    scalar_lr: float = 0.025
+    embed_lr: float = 0.6
+    tied_embed_lr: float = 0.035
+    head_lr: float = 0.008
+    muon_momentum: float = 0.99
+    muon_momentum_warmup_start: float = 0.92
+    muon_momentum_warmup_steps: int = 1500
+    muon_wd: float = 0.04
+    muon_ns_profile: str = "quintic"
+    muon_ns_steps: int = 5
+    adam_wd: float = 0.04
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.95
+    adam_eps: float = 1e-8
+    grad_clip_norm: float = 0.3
+    ema_decay: float = 0.997
+    swa_enabled: bool = True
+    swa_every: int = 50
+    swa_threshold: float = 0.2
+    late_qat_threshold: float = 0.15
+    qat_enabled: bool = False
+    seed: int = 1337
+    val_loss_every: int = 0
+    train_log_every: int = 200
+    val_batch_size: int = 524_288
+    grad_wire_dtype: str = "bf16"       # wire dtype of bank-gradient reduce-scatter
+    checkpoint_every: int = 0
+    checkpoint_path: Optional[str] = None
+    resume_from: Optional[str] = None
+
+
+@dataclass
+class LqerSpec:
+    enabled: bool = False
+    rank: int = 4
+    top_k: int = 0
+    a_bits: int = 8
+    b_bits: int = 8
+    group_size: int = 0
+    asymmetric: bool = False
+
+
+@dataclass
+class QuantSpec:
+    scheme: str = "gptq_lite_int6"
+    calibration: str = "disabled"
+    prune_keep_ratio: Optional[float] = None
+    lqer: LqerSpec = field(default_factory=LqerSpec)
+    compression: str = "zstd22"
+    matrix_bits: int = 6
+    embed_bits: int = 8
+    attn_gate_bits: int = 8
+    mlp_clip_sigmas: float = 0.0
+    attn_clip_sigmas: float = 0.0
+    embed_clip_sigmas: float = 0.0
+    gptq_calibration_batches: int = 64
+    gptq_block_size: int = 128
+    gptq_damping: float = 0.01
+    gptq_temperature: float = 0.8
+    target_artifact_bytes: int = 16_000_000
+
+
+@dataclass
+class EvalSpec:
+    stride: int = 64
+    legal_score_first: bool = False
+    qttt: bool = False
+    adaptation_backend: str = "none"
+    lora_rank: int = 16
+    lora_alpha: float = 16.0
+    phased_ttt_prefix_docs: int = 0
+    phased_ttt_phases: int = 1
+    phased_ttt_weight_decay: float = 0.0
+    chunk_tokens: int = 32768
+    tokenizer_vocab_path: Optional[str] = None
+    caseops_byte_sidecar_pattern: Optional[str] = None
+    max_tokens: Optional[int] = None
+    batch_windows: int = 32
+    ttt_lr: float = 0.002
+    ttt_epochs: int = 1
+    ttt_momentum: float = 0.9
+    ttt_batch_seqs: int = 32
+    ttt_grad_clip: float = 1.0
+    ttt_freeze_blocks: int = 0
+    max_eval_seconds: float = 600.0
+    byte_table_seed: int = 20240520
+
+
+@dataclass
+class RunSpec:
+    name: str = "run"
+    model: ModelSpec = field(default_factory=ModelSpec)
+    train: TrainSpec = field(default_factory=TrainSpec)
+    quant: QuantSpec = field(default_factory=QuantSpec)
+    eval: EvalSpec = field(default_factory=EvalSpec)
+    mode: str = "smoke"
+    allow_unsupported_variants: bool = False
+
+    # ---- construction -------------------------------------------------------------------
+    @staticmethod
+    def from_dict(d: dict) -> "RunSpec":
+        return _from_dict(RunSpec, d)
+
+    @staticmethod
+    def load(path: str) -> "RunSpec":
+        with open(path, "rb") as f:
+            return RunSpec.from_dict(tomllib.load(f))
+
+    @staticmethod
+    def for_family(family: str) -> "RunSpec":
+        return family_preset(family)
+
+    def to_dict(self) -> dict:
+        return dataclasses.asdict(self)
+
+    def to_toml(self) -> str:
+        return _to_toml(self.to_dict())
+
+    def apply_overrides(self, overrides: list) -> "RunSpec":
+        """Apply ``section.key=value`` strings (dots descend into sub-tables)."""
+        for ov in overrides:
+            if "=" not in ov:
+                raise ValueError(f"override must be key=value: {ov!r}")
+            key, val = ov.split("=", 1)
+            obj: Any = self
+            parts = key.strip().split(".")
+            for p in parts[:-1]:
+                if not hasattr(obj, p):
+                    raise KeyError(f"unknown spec section {p!r} in {key!r}")
+                obj = getattr(obj, p)
+            leaf = parts[-1]
+            if not hasattr(obj, leaf):
+                raise KeyError(f"unknown spec key {key!r}")
+            setattr(obj, leaf, _coerce(val.strip(), getattr(obj, leaf), _field_type(obj, leaf)))
+        return self
+
+    def apply_env(self, env: Optional[dict] = None) -> "RunSpec":
+        """Overlay the ``train_gpt.py`` environment names (only the ones that are set)."""
+        env = os.environ if env is None else env
+        m, t, q, e = self.model, self.train, self.quant, self.eval
+
+        def has(k):
+            return k in env and env[k] != ""
+
+        def I(k):
+            return int(env[k])
+
+        def F(k):
+            return float(env[k])
+
+        def B(k):
+            return bool(int(env[k]))
+
+        if has("RUN_ID"): self.name = env["RUN_ID"]
+        if has("DATA_PATH"):
+            t.train_data_pattern = os.path.join(env["DATA_PATH"], "fineweb_train_*.bin")
+            t.validation_data_pattern = os.path.join(env["DATA_PATH"], "fineweb_val_*.bin")
+        if has("TOKENIZER_PATH"): e.tokenizer_vocab_path = env["TOKENIZER_PATH"]
+        if has("SEED"): t.seed = I("SEED")
+        if has("VAL_BATCH_SIZE"): t.val_batch_size = I("VAL_BATCH_SIZE")
+        if has("VAL_LOSS_EVERY"): t.val_loss_every = I("VAL_LOSS_EVERY")
+        if has("TRAIN_LOG_EVERY"): t.train_log_every = I("TRAIN_LOG_EVERY")
+        if has("ITERATIONS"): t.total_iterations = I("ITERATIONS")
+        if has("WARMDOWN_ITERS"): t.warmdown_iters = I("WARMDOWN_ITERS")
+        if has("WARMUP_STEPS"): t.warmup_steps = I("WARMUP_STEPS")
+        if has("TRAIN_BATCH_TOKENS"): t.batch_tokens = I("TRAIN_BATCH_TOKENS")
+        if has("TRAIN_SEQ_LEN"): t.seq_len = m.train_seq_len = I("TRAIN_SEQ_LEN")
+        if has("EVAL_SEQ_LEN"): m.eval_seq_len = I("EVAL_SEQ_LEN")
+        if has("EVAL_STRIDE"): e.stride = I("EVAL_STRIDE")
+        if has("MAX_WALLCLOCK_SECONDS"): t.max_wallclock_seconds = F("MAX_WALLCLOCK_SECONDS")
+        if has("QK_GAIN_INIT"): m.qk_gain_init = F("QK_GAIN_INIT")
+        if has("VOCAB_SIZE"): m.vocab_size = I("VOCAB_SIZE")
+        if has("NUM_LAYERS"): m.num_layers = I("NUM_LAYERS")
+        if has("NUM_KV_HEADS"): m.num_kv_heads = I("NUM_KV_HEADS")
+        if has("MODEL_DIM"): m.model_dim = I("MODEL_DIM")
+        if has("NUM_HEADS"): m.num_heads = I("NUM_HEADS")
+        if has("MLP_MULT"): m.mlp_mult = F("MLP_MULT")
+        if has("TIE_EMBEDDINGS"): m.tie_embeddings = B("TIE_EMBEDDINGS")
+        if has("ROPE_BASE"): m.rope.base = F("ROPE_BASE")
+        if has("ROPE_DIMS"): m.rope.dims = I("ROPE_DIMS")
+        if has("LOGIT_SOFTCAP"): m.logit_softcap = F("LOGIT_SOFTCAP")
+        if has("EMBED_LR"): t.embed_lr = F("EMBED_LR")
+        if has("HEAD_LR"): t.head_lr = F("HEAD_LR")
+        if has("TIED_EMBED_LR"): t.tied_embed_lr = F("TIED_EMBED_LR")
+        if has("TIED_EMBED_INIT_STD"): m.tied_embed_init_std = F("TIED_EMBED_INIT_STD")
+        if has("MATRIX_LR"): t.matrix_lr = F("MATRIX_LR")
+        if has("SCALAR_LR"): t.scalar_lr = F("SCALAR_LR")
+        if has("MUON_MOMENTUM"): t.muon_momentum = F("MUON_MOMENTUM")
+        if has("MUON_BACKEND_STEPS"): t.muon_ns_steps = I("MUON_BACKEND_STEPS")
+        if has("MUON_MOMENTUM_WARMUP_START"): t.muon_momentum_warmup_start = F("MUON_MOMENTUM_WARMUP_START")
+        if has("MUON_MOMENTUM_WARMUP_STEPS"): t.muon_momentum_warmup_steps = I("MUON_MOMENTUM_WARMUP_STEPS")
+        if has("BETA1"): t.adam_beta1 = F("BETA1")
+        if has("BETA2"): t.adam_beta2 = F("BETA2")
+        if has("ADAM_EPS"): t.adam_eps = F("ADAM_EPS")
+        if has("GRAD_CLIP_NORM"): t.grad_clip_norm = F("GRAD_CLIP_NORM")
+        if has("MUON_WD"): t.muon_wd = F("MUON_WD")
+        if has("ADAM_WD"): t.adam_wd = F("ADAM_WD")
+        if has("SWA_ENABLED"): t.swa_enabled = B("SWA_ENABLED")
+        if has("SWA_EVERY"): t.swa_every = I("SWA_EVERY")
+        if has("QAT_ENABLED"): t.qat_enabled = B("QAT_ENABLED")
+        if has("LATE_QAT_THRESHOLD"): t.late_qat_threshold = F("LATE_QAT_THRESHOLD")
+        if has("BIGRAM_VOCAB_SIZE"):
+            m.bigram.vocab_size = I("BIGRAM_VOCAB_SIZE")
+            m.bigram.enabled = m.bigram.vocab_size > 0
+        if has("BIGRAM_DIM"): m.bigram.dim = I("BIGRAM_DIM")
+        if has("XSA_LAST_N"): m.xsa_last_n = I("XSA_LAST_N")
+        if has("LN_SCALE"): m.ln_scale = B("LN_SCALE")
+        if has("VE_ENABLED"): m.value_embedding.enabled = B("VE_ENABLED")
+        if has("VE_DIM"): m.value_embedding.dim = I("VE_DIM")
+        if has("VE_LAYERS"):
+            m.value_embedding.layers = [int(x) for x in env["VE_LAYERS"].split(",") if x.strip()]
+        if has("TTT_ENABLED") and B("TTT_ENABLED"):
+            e.legal_score_first = True
+            e.adaptation_backend = "full_sgd"
+        if has("TTT_LR"): e.ttt_lr = F("TTT_LR")
+        if has("TTT_EPOCHS"): e.ttt_epochs = I("TTT_EPOCHS")
+        if has("TTT_CHUNK_TOKENS"): e.chunk_tokens = I("TTT_CHUNK_TOKENS")
+        if has("TTT_FREEZE_BLOCKS"): e.ttt_freeze_blocks = I("TTT_FREEZE_BLOCKS")
+        if has("TTT_MOMENTUM"): e.ttt_momentum = F("TTT_MOMENTUM")
+        if has("TTT_BATCH_SEQS"): e.ttt_batch_seqs = I("TTT_BATCH_SEQS")
+        if has("TTT_GRAD_CLIP"): e.ttt_grad_clip = F("TTT_GRAD_CLIP")
+        if has("GPTQ_CALIB_BATCHES"): q.gptq_calibration_batches = I("GPTQ_CALIB_BATCHES")
+        if has("GPTQ_BLOCK_SIZE"): q.gptq_block_size = I("GPTQ_BLOCK_SIZE")
+        if has("TARGET_MB"): q.target_artifact_bytes = int(F("TARGET_MB") * 1024 * 1024)
+        return self
+
+    # ---- validation / fingerprint ----------------------------------------------------------
+    def validate(self) -> "RunSpec":
+        m, t, q, e = self.model, self.train, self.quant, self.eval
+        errs = []
+
+        def chk(c, msg):
+            if not c:
+                errs.append(msg)
+
+        chk(self.mode in RUN_MODES, f"mode must be one of {RUN_MODES}")
+        chk(t.backend in TRAIN_BACKENDS, f"train.backend must be one of {TRAIN_BACKENDS}")
+        chk(t.distributed_optimizer_backend in DIST_OPT_BACKENDS, "unknown distributed_optimizer_backend")
+        chk(q.scheme in QUANT_SCHEMES, f"quant.scheme must be one of {QUANT_SCHEMES}")
+        chk(q.compression in COMPRESSION_MODES, "unknown quant.compression")
+        chk(q.compression != "lzma9", "compression lzma9 is declared but not supported by the artifact writer")
+        chk(q.calibration in CALIBRATION_MODES, "unknown quant.calibration")
+        chk(e.adaptation_backend in ADAPTATION_BACKENDS, "unknown eval.adaptation_backend")
+        chk(t.muon_ns_profile in NS_PROFILES, f"train.muon_ns_profile must be one of {NS_PROFILES}")
+        chk(m.activation in ("relu_sq", "leaky_relu_sq"), "model.activation must be relu_sq or leaky_relu_sq")
+        chk(m.rope.mode in ("none", "partial", "yarn"), "unknown rope.mode")
+        chk(m.rope.mode != "yarn", "rope.mode=yarn is declared but not implemented")
+        chk(m.skip_topology in ("none", "unet"), "unknown skip_topology")
+        chk(m.num_layers >= 1, "num_layers must be >= 1")
+        chk(m.model_dim % m.num_heads == 0, "model_dim must be divisible by num_heads")
+        chk(m.num_heads % max(m.num_kv_heads, 1) == 0, "num_heads must be divisible by num_kv_heads")
+        chk(m.head_dim % 2 == 0, "head_dim must be even for RoPE")
+        chk(m.rope_dims % 2 == 0 and m.rope_dims <= m.head_dim, "rope.dims must be even and <= head_dim")
+        chk(m.logit_softcap > 0, "logit_softcap must be positive")
+        chk(m.xsa_last_n <= m.num_layers, "xsa_last_n exceeds num_layers")
+        chk(m.vocab_size <= 65536, "token ids are uint16: vocab_size must be <= 65536")
+        chk(not (m.attn_out_gate.enabled and m.sparse_attn_gate.enabled),
+            "attn_out_gate and sparse_attn_gate are mutually exclusive")
+        if m.bigram.enabled:
+            chk(m.bigram.vocab_size >= 2, "bigram.vocab_size must be >= 2")
+        if m.value_embedding.enabled:
+            chk(all(0 <= l < m.num_layers for l in m.value_embedding.layers), "value_embedding.layers out of range")
+        if m.recurrence.enabled:
+            chk(m.recurrence.start_layer + m.recurrence.repeat_layers <= m.num_layers, "recurrence range out of bounds")
+        chk(t.seq_len > 0 and t.batch_tokens % t.seq_len == 0, "batch_tokens must be a multiple of seq_len")
+        chk(t.world_size >= 1 and 0 <= t.rank < t.world_size, "rank must be in [0, world_size)")
+        if t.backend in ("cpu", "cuda_single", "cuda_single_parity"):
+            chk(t.world_size == 1, f"backend {t.backend} requires world_size == 1")
+        chk(4 <= q.matrix_bits <= 8 and 4 <= q.embed_bits <= 8, "quant bits must be in [4, 8]")
+        chk(e.stride >= 1, "eval.stride must be >= 1")
+        chk(t.grad_wire_dtype in ("bf16", "f32"), "grad_wire_dtype must be bf16 or f32")
+        if self.mode == "record" and not self.allow_unsupported_variants:
+            chk(t.backend == "cuda_distributed", "record mode requires the cuda_distributed backend")
+            chk(t.train_data_pattern is not None, "record mode requires train.train_data_pattern")
+            chk(t.validation_data_pattern is not None, "record mode requires train.validation_data_pattern")
+            chk(e.max_tokens is None, "record mode requires the full validation set (eval.max_tokens unset)")
+        if errs:
+            raise ValueError("invalid run spec: " + "; ".join(errs))
+        return self
+
+    def fingerprint(self) -> int:
+        """64-bit FNV-1a over the canonical JSON of model/quant/eval and the training knobs that
+        change the trained function (optimizer hyper-parameters, batch shape)."""
+        t = self.train
+        crit = {
+            "model": dataclasses.asdict(self.model),
+            "quant": dataclasses.asdict(self.quant),
+            "eval": {k: v for k, v in dataclasses.asdict(self.eval).items()
+                     if k not in ("tokenizer_vocab_path", "caseops_byte_sidecar_pattern", "max_eval_seconds")},
+            "train": {k: getattr(t, k) for k in (
+                "batch_tokens", "seq_len", "matrix_lr", "scalar_lr", "embed_lr", "tied_embed_lr", "muon_momentum",
+                "muon_wd", "adam_wd", "muon_ns_profile", "muon_ns_steps", "ema_decay", "late_qat_threshold",
+                "grad_clip_norm", "distributed_optimizer_backend")},
+        }
+        h = 0xCBF29CE484222325
+        for b in json.dumps(crit, sort_keys=True, separators=(",", ":")).encode():
+            h ^= b
+            h = (h * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
+        return h
+
+
+# ---- presets ------------------------------------------------------------------------------------
+
+def family_preset(family: str) -> RunSpec:
+    """Built-in variants. ``tiny_cpu``, ``baseline_9l`` and ``record_11l`` are the three model shapes of
+    the benchmark configurations; the ``*_sp8192`` names mirror the reference's sweep families
+    (``pg-model/src/spec.rs:313-399``) at vocabulary 8192."""
+    if family not in FAMILIES:
+        raise ValueError(f"unknown family {family!r}; known: {FAMILIES}")
+    s = RunSpec(name=family)
+    m, t = s.model, s.train
+    m.family = family
+    if family == "tiny_cpu":
+        m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads = 1024, 2, 128, 4, 2
+        m.mlp_mult, m.activation, m.train_seq_len, m.eval_seq_len = 2.0, "relu_sq", 256, 256
+        m.rope.dims = 0
+        m.compute_precision = "f32"
+        t.backend, t.batch_tokens, t.seq_len, t.total_iterations = "cpu", 8 * 256, 256, 20
+        t.matrix_lr, t.muon_momentum, t.muon_momentum_warmup_steps = 0.02, 0.95, 0
+        t.tied_embed_lr = t.scalar_lr = 0.05
+        t.muon_wd = t.adam_wd = 0.0
+        t.warmdown_iters, t.grad_clip_norm, t.max_wallclock_seconds = 0, 0.0, 0.0
+        t.swa_enabled, t.late_qat_threshold, t.ema_decay = False, 0.0, 0.0
+        s.eval.stride = 64
+    elif family == "baseline_9l":
+        m.num_layers, m.mlp_mult, m.activation = 9, 2.0, "relu_sq"
+        m.train_seq_len = m.eval_seq_len = 1024
+        m.rope.dims = 0
+        t.backend, t.batch_tokens, t.seq_len = "cuda_distributed", 524_288, 1024
+        t.total_iterations, t.warmdown_iters = 20000, 1200
+        t.matrix_lr, t.scalar_lr, t.tied_embed_lr = 0.04, 0.04, 0.05
+        t.muon_momentum, t.muon_momentum_warmup_start, t.muon_momentum_warmup_steps = 0.95, 0.85, 500
+        t.muon_wd = t.adam_wd = 0.0
+        t.muon_ns_profile = "simple"
+        t.grad_clip_norm, t.swa_enabled, t.late_qat_threshold, t.ema_decay = 0.0, False, 0.0, 0.0
+    elif family == "record_11l":
+        m.num_layers, m.mlp_mult, m.activation = 11, 3.0, "leaky_relu_sq"
+        m.xsa_last_n, m.ln_scale, m.smear_gate = 4, True, True
+        m.rope.dims = 16
+        m.bigram = BigramSpec(True, 3072, 128)
+        t.backend, t.distributed_optimizer_backend = "cuda_distributed", "sharded_parallel_muon"
+        t.batch_tokens, t.seq_len = 786_432, 2048
+        s.quant.scheme = "full_gptq_int6"
+        s.quant.calibration = "self_generated"
+        s.eval.legal_score_first = True
+        s.eval.adaptation_backend = "full_sgd"
+    else:
+        m.vocab_size = 8192
+        m.num_layers, m.mlp_mult, m.activation = 11, 3.0, "leaky_relu_sq"
+        m.ln_scale, m.smear_gate = True, True
+        m.bigram = BigramSpec(True, 2048, 128)
+        t.batch_tokens, t.seq_len = 524_288, 2048
+        if family == "xsa_all_sp8192":
+            m.xsa_last_n = m.num_layers
+        elif family == "recurrence_mid_sp8192":
+            m.xsa_last_n = 4
+            m.recurrence = RecurrenceSpec(True, 4, 2)
+        elif family == "parallel_resid_sp8192":
+            m.xsa_last_n = 4
+            m.parallel_residual = ParallelResidualSpec(True, False)
+        elif family == "hybrid_competitive_sp8192":
+            m.xsa_last_n = m.num_layers
+            m.recurrence = RecurrenceSpec(True, 4, 2)
+            m.value_embedding = ValueEmbeddingSpec(True, 128, [9, 10])
+        elif family == "frontier_1855_like":
+            m.xsa_last_n = m.num_layers
+            m.sparse_attn_gate = SparseAttnGateSpec(True, 12, 1.0)
+            m.value_embedding = ValueEmbeddingSpec(True, 128, [9, 10])
+        else:  # baseline_sp8192
+            m.xsa_last_n = 4
+    return s
+
+
+# ---- helpers --------------------------------------------------------------------------------------
+
+def _field_type(obj, name):
+    for f in fields(obj):
+        if f.name == name:
+            return f.type
+    return None
+
+
+def _coerce(text: str, current, ftype=None):
+    if isinstance(current, bool):
+        return text.lower() in ("1", "true", "yes", "on")
+    if isinstance(current, int):
+        return int(text)
+    if isinstance(current, float):
+        return float(text)
+    if isinstance(current, list):
+        return [int(x) for x in text.strip("[]").split(",") if x.strip()]
+    if current is None:
+        if text.lower() in ("none", "null", ""):
+            return None
+        t = str(ftype)
+        if "int" in t:
+            return int(text)
+        if "float" in t:
+            return float(text)
+        return text
+    return text
+
+
+def _from_dict(cls, d: dict):
+    obj = cls()
+    known = {f.name: f for f in fields(cls)}
+    for k, v in d.items():
+        if k not in known:
+            raise KeyError(f"unknown key {k!r} in [{cls.__name__}]")
+        cur = getattr(obj, k)
+        if is_dataclass(cur):
+            if not isinstance(v, dict):
+                raise TypeError(f"{k} must be a table")
+            setattr(obj, k, _from_dict(type(cur), v))
+        else:
+            if isinstance(cur, float) and isinstance(v, int) and not isinstance(v, bool):
+                v = float(v)
+            setattr(obj, k, v)
+    return obj
+
+
+def _to_toml(d: dict, prefix: str = "") -> str:
+    scalars, tables = [], []
+    for k, v in d.items():
+        if isinstance(v, dict):
+            tables.append((k, v))
+        elif v is None:
+            continue
+        elif isinstance(v, bool):
+            scalars.append(f"{k} = {'true' if v else 'false'}")
+        elif isinstance(v, (int, float)):
+            scalars.append(f"{k} = {v!r}")
+        elif isinstance(v, list):
+            scalars.append(f"{k} = [{', '.join(repr(x) for x in v)}]")
+        else:
+            scalars.append(f"{k} = {json.dumps(v)}")
+    out = "\n".join(scalars)
+    for k, v in tables:
+        name = f"{prefix}{k}"
+        out += f"\n\n[{name}]\n" + _to_toml(v, name + ".")
+    return out.strip() + "\n" if not prefix else out

@@ -1,0 +1,407 @@
+"""Run orchestration: validation gates, batch plan, step loop with wallclock cap, export, evaluation.
+
+The flow mirrors ``VariantRunner::run`` (``parameter-golf-rs/crates/pg-train/src/lib.rs:864-1781``) and the
+Python trainer's loop (``train_gpt.py:966-1060``): gates → model → loader → for each step
+{wallclock check, LR scale, momentum warm-up, micro-batches, optimizer} → EMA/SWA application → export →
+artifact budget check → evaluation → ``key=value`` result lines and one ``record_audit_json=`` line.
+
+Backends: ``cpu`` runs the autograd oracle (one process, or gloo ranks for control-plane tests);
+``cuda_single`` / ``cuda_distributed`` run the sm_100a engine (`parameter_golf_b200.models.engine`), one process
+per GPU.
+
+Command line: ``python -m parameter_golf_b200.train run [--spec file.toml | --family name] [--mode smoke|proxy|
+record_shaped_proxy|record] [--env] [key=value …]`` and ``… train sweep --families a,b``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .data.bpb import BpbLuts
+from .data.shards import DistributedTokenLoader, load_validation_tokens, write_synthetic_dataset
+from .eval.sliding import eval_contiguous, eval_sliding
+from .eval.ttt import eval_lora_phased_ttt, eval_score_first_ttt
+from .models import gpt
+from .models.runner import OracleRunner
+from .optim.muon import AdamW, Ema, Muon, Swa, clip_grads_, lr_scale_with_floor, muon_momentum_at, wallclock_lr_scale
+from .quant.export import check_budget, code_bytes, export_model, load_artifact
+from .spec import RunSpec, family_preset
+from .utils.checkpoint import load_checkpoint, save_checkpoint
+from .utils.logging import RunLog, StageTimers
+
+
+def split_param_groups(spec: RunSpec, params: Dict[str, torch.Tensor]):
+    """Optimizer grouping of the Python records (``…03-23…/train_gpt.py:1517-1529``): banks → Muon;
+    embedding tables → Adam at the (tied) embedding LR; everything else → Adam at the scalar LR."""
+    t = spec.train
+    banks = [k for k in gpt.BANKS if k in params]
+    emb = [k for k in ("tok_emb", "bigram_embed", "ve_embed") if k in params]
+    head = [k for k in ("lm_head",) if k in params]
+    scalars = [k for k in params if k not in banks and k not in emb and k not in head]
+    emb_lr = t.tied_embed_lr if spec.model.tie_embeddings else t.embed_lr
+    groups = [{"names": emb, "lr": emb_lr}, {"names": scalars, "lr": t.scalar_lr}]
+    if head:
+        groups.append({"names": head, "lr": t.head_lr})
+    return banks, groups
+
+
+def step_batch_plan(spec: RunSpec, mode: str):
+    """(global tokens per step, micro-batches per rank). Smoke and proxy modes shrink the batch
+    (``pg-train/src/lib.rs:5932-5971``); the record modes keep the real arithmetic."""
+    t = spec.train
+    seq = t.seq_len
+    world = t.world_size
+    tokens = t.batch_tokens
+    if mode == "smoke":
+        tokens = min(tokens, world * seq * 2)
+    elif mode == "proxy":
+        tokens = min(tokens, world * seq * 8)
+    if t.grad_accum_steps > 0:
+        accum = t.grad_accum_steps
+    elif t.backend == "cpu" or world > 8 or 8 % world or tokens % (8 * seq):
+        accum = 1
+    else:
+        accum = 8 // world          # the reference's rule: the micro-batch is always 1/8 of the global batch
+    return tokens, accum
+
+
+def mode_max_steps(spec: RunSpec, mode: str) -> int:
+    return {"smoke": min(4, spec.train.total_iterations), "proxy": min(32, spec.train.total_iterations),
+            "record_shaped_proxy": min(8, spec.train.total_iterations)}.get(mode, spec.train.total_iterations)
+
+
+class OracleBackend:
+    """CPU / reference training backend on the autograd model with the torch optimizers."""
+
+    def __init__(self, spec: RunSpec, params: Dict[str, torch.Tensor]):
+        self.spec = spec
+        self.params = params
+        self.runner = OracleRunner(spec.model, params)
+        t = spec.train
+        self.bank_names, self.adam_groups = split_param_groups(spec, params)
+        self.muon = Muon([params[k] for k in self.bank_names], t.matrix_lr, t.muon_momentum, t.muon_ns_steps,
+                         t.muon_ns_profile, t.muon_wd)
+        self.adam = AdamW([{"params": [params[k] for k in g["names"]], "lr": g["lr"]} for g in self.adam_groups],
+                          (t.adam_beta1, t.adam_beta2), t.adam_eps, t.adam_wd)
+
+    def train_step(self, batches, lr_scale: float, momentum: float, qat: bool) -> float:
+        import torch.distributed as dist
+        total: Optional[Dict[str, torch.Tensor]] = None
+        loss_sum = 0.0
+        for ids, tgt in batches:
+            loss, g = self.runner.loss_and_grads(ids, tgt, qat=qat)
+            loss_sum += float(loss)
+            total = g if total is None else {k: total[k] + g[k] for k in g}
+        inv = 1.0 / len(batches)
+        grads = {k: v * inv for k, v in total.items()}
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            flat = torch.cat([grads[k].reshape(-1) for k in sorted(grads)])
+            dist.all_reduce(flat)
+            flat /= dist.get_world_size()
+            off = 0
+            for k in sorted(grads):
+                n = grads[k].numel()
+                grads[k] = flat[off:off + n].reshape(grads[k].shape)
+                off += n
+        if self.spec.train.grad_clip_norm > 0:
+            clip_grads_(list(grads.values()), self.spec.train.grad_clip_norm)
+        self.adam.step([[grads[k] for k in g["names"]] for g in self.adam_groups], lr_scale)
+        self.muon.step([grads[k] for k in self.bank_names], lr=self.spec.train.matrix_lr * lr_scale, momentum=momentum)
+        return loss_sum * inv
+
+    def state_dict(self):
+        return {"muon": self.muon.state_dict(), "adam": self.adam.state_dict()}
+
+    def load_state_dict(self, st):
+        self.muon.load_state_dict(st["muon"])
+        self.adam.load_state_dict(st["adam"])
+
+    def sync_params(self) -> Dict[str, torch.Tensor]:
+        return self.params
+
+
+@dataclass
+class VariantResult:
+    name: str = ""
+    mode: str = ""
+    backend: str = ""
+    fingerprint: str = ""
+    steps: int = 0
+    train_loss_first: float = float("nan")
+    train_loss_last: float = float("nan")
+    train_ms: float = 0.0
+    step_avg_ms: float = 0.0
+    tokens_per_step: int = 0
+    tokens_per_s: float = 0.0
+    stopped_early: bool = False
+    artifact_bytes: int = 0
+    code_bytes: int = 0
+    budget_ok: bool = True
+    val_loss: float = float("nan")
+    val_bpb: float = float("nan")
+    eval_ms: float = 0.0
+    eval_kind: str = "none"
+    peak_mem_mib: int = 0
+    timers: dict = field(default_factory=dict)
+
+    def key_value_lines(self) -> List[str]:
+        out = []
+        for k, v in self.__dict__.items():
+            if isinstance(v, dict):
+                out.extend(f"{k}.{kk}={vv}" for kk, vv in v.items())
+            else:
+                out.append(f"{k}={v}")
+        if self.steps:
+            out.append(f"train_ms_per_step={self.train_ms / self.steps:.3f}")
+        return out
+
+
+def record_gaps(spec: RunSpec, mode: str) -> List[str]:
+    """Fail-closed checklist for a record attempt (``pg-train/src/lib.rs:5533-5635``)."""
+    gaps = []
+    t = spec.train
+    if mode == "record":
+        if t.backend != "cuda_distributed":
+            gaps.append("record needs the cuda_distributed backend")
+        if not t.train_data_pattern or not t.validation_data_pattern:
+            gaps.append("record needs real train/validation shards")
+        if spec.eval.max_tokens is not None:
+            gaps.append("record needs the full validation set")
+        if t.world_size != 8:
+            gaps.append("record is defined on 8 GPUs")
+    return gaps
+
+
+class VariantRunner:
+    def __init__(self, spec: RunSpec, log: Optional[RunLog] = None, backend_factory: Optional[Callable] = None):
+        self.spec = spec.validate()
+        self.log = log or RunLog(spec.name)
+        self.backend_factory = backend_factory
+
+    def _make_backend(self, params):
+        if self.backend_factory is not None:
+            return self.backend_factory(self.spec, params)
+        if self.spec.train.backend == "cpu":
+            return OracleBackend(self.spec, params)
+        from .models.engine import EngineBackend       # needs the CUDA extension
+        return EngineBackend(self.spec, params)
+
+    def run(self, mode: Optional[str] = None) -> VariantResult:
+        spec = self.spec
+        mode = mode or spec.mode
+        t, m = spec.train, spec.model
+        log = self.log
+        gaps = record_gaps(spec, mode)
+        if gaps and not spec.allow_unsupported_variants:
+            raise RuntimeError("record gate failed: " + "; ".join(gaps))
+        res = VariantResult(name=spec.name, mode=mode, backend=t.backend, fingerprint=f"{spec.fingerprint():016x}")
+        timers = StageTimers()
+        torch.manual_seed(t.seed)
+        np.random.seed(t.seed)
+        device = "cpu" if t.backend == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}"
+
+        # ---- data ----------------------------------------------------------------------------------
+        if not t.train_data_pattern:
+            root = os.path.join(os.environ.get("PGB_DATA_ROOT", "/tmp/pgb200_synth"), f"v{m.vocab_size}_s{t.seed}")
+            if t.rank == 0 or not os.path.exists(os.path.join(root, "fineweb_val_000000.bin")):
+                write_synthetic_dataset(root, m.vocab_size, train_tokens=max(4 * t.batch_tokens, 1 << 20),
+                                        val_tokens=max(4 * m.eval_seq_len * 8 + 1, 1 << 16), seed=t.seed)
+            t.train_data_pattern = os.path.join(root, "fineweb_train_*.bin")
+            t.validation_data_pattern = os.path.join(root, "fineweb_val_*.bin")
+        loader = DistributedTokenLoader(t.train_data_pattern, t.rank, t.world_size)
+        tokens_per_step, accum = step_batch_plan(spec, mode)
+        res.tokens_per_step = tokens_per_step
+
+        # ---- model + backend ------------------------------------------------------------------------
+        params = gpt.init_params(m, t.seed, device="cpu")
+        backend = self._make_backend(params)
+        ema = Ema(t.ema_decay) if t.ema_decay > 0 else None
+        swa = Swa(t.swa_every, t.swa_threshold) if t.swa_enabled else None
+        step0 = 0
+        if t.resume_from:
+            ck = load_checkpoint(t.resume_from)
+            if ck["fingerprint"] != res.fingerprint:
+                raise RuntimeError("checkpoint fingerprint does not match this run spec")
+            for k, v in ck["params"].items():
+                backend.sync_params()[k].copy_(v)
+            backend.load_state_dict(ck["optim"])
+            loader.restore(ck["loader"])
+            step0 = int(ck["step"])
+            if ema is not None and ck.get("ema") is not None:
+                ema.shadow = ck["ema"]
+            torch.set_rng_state(ck["rng"])
+            if hasattr(backend, "params_changed"):
+                backend.params_changed()
+            log.info(f"resumed from {t.resume_from} at step {step0}")
+
+        max_steps = mode_max_steps(spec, mode)
+        max_ms = 1000.0 * t.max_wallclock_seconds if t.max_wallclock_seconds > 0 else None
+        qat = t.qat_enabled
+        log.info(f"model_params:{gpt.count_params(m)} world_size:{t.world_size} grad_accum_steps:{accum} "
+                 f"train_batch_tokens:{tokens_per_step} train_seq_len:{t.seq_len} iterations:{max_steps}")
+        train_ms = 0.0
+        step = step0
+        t_start = time.perf_counter()
+        while step < max_steps:
+            elapsed = train_ms + 1000.0 * (time.perf_counter() - t_start)
+            if max_ms is not None and elapsed >= max_ms:
+                res.stopped_early = True
+                log.info(f"stopping_early: wallclock_cap train_time:{elapsed:.0f}ms step:{step}/{max_steps}")
+                break
+            if t.wallclock_warmdown and max_ms is not None:
+                scale = wallclock_lr_scale(step, elapsed, max_steps, t.warmdown_iters, max_ms)
+            else:
+                wd = int(round(max_steps * t.warmdown_frac)) if t.warmdown_frac > 0 else min(t.warmdown_iters, max_steps)
+                scale = lr_scale_with_floor(step, t.warmup_steps, max_steps, wd, t.min_lr_scale) if (wd or t.warmup_steps) else 1.0
+            if t.late_qat_threshold > 0 and scale < t.late_qat_threshold and not qat:
+                qat = True
+                log.info(f"late_qat:enabled step:{step} scale:{scale:.4f}")
+            mom = muon_momentum_at(step, t.muon_momentum_warmup_start, t.muon_momentum, t.muon_momentum_warmup_steps)
+            with timers.time("data"):
+                batches = []
+                for _ in range(accum):
+                    x, y = loader.next_batch(tokens_per_step, t.seq_len, accum)
+                    batches.append((torch.from_numpy(x), torch.from_numpy(y)))
+            with timers.time("train_step"):
+                loss = backend.train_step(batches, scale, mom, qat)
+            step += 1
+            if step == step0 + 1:
+                res.train_loss_first = loss
+            res.train_loss_last = loss
+            if ema is not None:
+                with timers.time("ema"):
+                    ema.update(backend.sync_params())
+            if swa is not None and swa.should_collect(step, scale):
+                swa.collect(backend.sync_params())
+            now_ms = train_ms + 1000.0 * (time.perf_counter() - t_start)
+            if t.train_log_every > 0 and (step <= 10 or step % t.train_log_every == 0 or step == max_steps):
+                log.info(f"step:{step}/{max_steps} train_loss:{loss:.4f} train_time:{now_ms:.0f}ms step_avg:{now_ms / (step - step0):.2f}ms")
+            if t.checkpoint_every > 0 and t.checkpoint_path and step % t.checkpoint_every == 0 and t.rank == 0:
+                save_checkpoint(t.checkpoint_path, res.fingerprint, step, backend.sync_params(), backend.state_dict(),
+                                loader.state(), ema.shadow if ema else None)
+        train_ms += 1000.0 * (time.perf_counter() - t_start)
+        res.steps = step - step0
+        res.train_ms = train_ms
+        res.step_avg_ms = train_ms / max(res.steps, 1)
+        res.tokens_per_s = tokens_per_step * res.steps / max(train_ms / 1000.0, 1e-9)
+        if torch.cuda.is_available() and t.backend != "cpu":
+            res.peak_mem_mib = torch.cuda.max_memory_allocated() // (1 << 20)
+            log.info(f"peak memory allocated: {res.peak_mem_mib} MiB")
+
+        # ---- weight averaging, export, budget ---------------------------------------------------------
+        final = {k: v.detach().cpu().float().clone() for k, v in backend.sync_params().items()}
+        if swa is not None and swa.count > 1:
+            log.info(f"swa:applying {swa.count} snapshots")
+            final = {k: v.cpu() for k, v in swa.average().items()}
+        elif ema is not None and ema.shadow is not None:
+            log.info("ema:applying EMA weights")
+            final = {k: v.cpu().clone() for k, v in ema.shadow.items()}
+        with timers.time("export"):
+            precomputed = None
+            if spec.quant.scheme == "full_gptq_int6" and spec.quant.calibration == "self_generated":
+                from .quant.calibrate import self_generated_hessians
+                from .quant.gptq import gptq_quantize_model
+                hess = self_generated_hessians(spec, final, device=device if t.backend != "cpu" else "cpu",
+                                               num_seqs=spec.quant.gptq_calibration_batches if mode == "record" else 2,
+                                               seq_len=m.train_seq_len if mode == "record" else min(m.train_seq_len, 64))
+                precomputed = gptq_quantize_model(spec, final, hess)
+            blob = export_model(spec, final, t.artifact_path if t.rank == 0 else None, precomputed) if spec.quant.scheme != "none" else b""
+        res.artifact_bytes = len(blob)
+        res.code_bytes = code_bytes()
+        res.budget_ok = check_budget(res.artifact_bytes, res.code_bytes, spec.quant.target_artifact_bytes)
+        log.info(f"artifact_bytes:{res.artifact_bytes} code_bytes:{res.code_bytes} budget_ok:{res.budget_ok}")
+        if mode == "record" and not res.budget_ok:
+            raise RuntimeError("artifact + code exceed the byte budget")
+
+        # ---- evaluation on the round-tripped artifact ---------------------------------------------------
+        with timers.time("eval"):
+            t_eval = time.perf_counter()
+            eval_params = load_artifact(blob, spec) if blob else final
+            val = load_validation_tokens(t.validation_data_pattern, m.eval_seq_len, spec.eval.max_tokens if mode == "record" else
+                                         min(spec.eval.max_tokens or (1 << 62), 8 * m.eval_seq_len))
+            luts = (BpbLuts.from_sentencepiece(spec.eval.tokenizer_vocab_path, m.vocab_size) if spec.eval.tokenizer_vocab_path
+                    else BpbLuts.seeded(m.vocab_size, spec.eval.byte_table_seed))
+            if t.backend == "cpu":
+                runner = OracleRunner(m, eval_params)
+                edev = "cpu"
+            else:
+                from .models.engine import EngineRunner
+                runner = EngineRunner(spec, eval_params, device)
+                edev = device
+            ab = spec.eval.adaptation_backend
+            if spec.eval.legal_score_first and ab in ("full_sgd", "cpu_q_only", "lact"):
+                emode = {"full_sgd": "full_sgd", "cpu_q_only": "q_only", "lact": "lact"}[ab]
+                res.val_loss, res.val_bpb = eval_score_first_ttt(runner, val, m, spec.eval, luts, t.rank, t.world_size, emode, edev, log.info)
+                res.eval_kind = f"score_first_{emode}"
+            elif spec.eval.legal_score_first and ab == "gpu_lora_phased":
+                res.val_loss, res.val_bpb = eval_lora_phased_ttt(runner, val, m, spec.eval, luts, t.rank, t.world_size, edev, log.info)
+                res.eval_kind = "lora_phased"
+            else:
+                res.val_loss, res.val_bpb = eval_sliding(runner.nll, val, m.eval_seq_len, spec.eval.stride, luts, t.rank, t.world_size,
+                                                         spec.eval.batch_windows, edev)
+                res.eval_kind = "sliding"
+            res.eval_ms = 1000.0 * (time.perf_counter() - t_eval)
+        log.info(f"final_{res.eval_kind}_roundtrip val_loss:{res.val_loss:.4f} val_bpb:{res.val_bpb:.4f} eval_time:{res.eval_ms:.0f}ms")
+        res.timers = timers.summary()
+        if t.rank == 0:
+            log.raw("record_audit_json=" + json.dumps({
+                "name": spec.name, "mode": mode, "fingerprint": res.fingerprint, "backend": t.backend,
+                "distributed_optimizer_backend": t.distributed_optimizer_backend, "world_size": t.world_size,
+                "tokens_per_step": tokens_per_step, "grad_accum": accum, "seq_len": t.seq_len, "steps": res.steps,
+                "step_avg_ms": round(res.step_avg_ms, 3), "ns_profile": t.muon_ns_profile, "grad_wire_dtype": t.grad_wire_dtype,
+                "quant_scheme": spec.quant.scheme, "compression": spec.quant.compression, "artifact_bytes": res.artifact_bytes,
+                "eval_kind": res.eval_kind, "gaps": gaps, "timing_backend": "host_perf_counter" if t.backend == "cpu" else "cuda_events_max_over_ranks"}))
+        return res
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="parameter_golf_b200.train")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    for name in ("run", "sweep"):
+        sp = sub.add_parser(name)
+        sp.add_argument("--spec")
+        sp.add_argument("--family", default=None)
+        sp.add_argument("--families", default="tiny_cpu")
+        sp.add_argument("--mode", default=None)
+        sp.add_argument("--env", action="store_true", help="overlay train_gpt.py environment variable names")
+        sp.add_argument("--backend", default=None)
+        sp.add_argument("--artifact", default=None)
+        sp.add_argument("overrides", nargs="*")
+    a = ap.parse_args(argv)
+    fams = [a.family] if (a.cmd == "run" and a.family) else ([None] if a.cmd == "run" else a.families.split(","))
+    rc = 0
+    for fam in fams:
+        spec = RunSpec.load(a.spec) if a.spec else family_preset(fam or "tiny_cpu")
+        if a.env:
+            spec.apply_env()
+        if "RANK" in os.environ:
+            spec.train.rank, spec.train.world_size = int(os.environ["RANK"]), int(os.environ.get("WORLD_SIZE", 1))
+        if a.backend:
+            spec.train.backend = a.backend
+        if a.artifact:
+            spec.train.artifact_path = a.artifact
+        spec.apply_overrides(a.overrides)
+        if a.mode:
+            spec.mode = a.mode
+        if spec.train.world_size > 1:
+            import torch.distributed as dist
+            if not dist.is_initialized():
+                dist.init_process_group("gloo" if spec.train.backend == "cpu" else "nccl")
+        res = VariantRunner(spec).run()
+        if spec.train.rank == 0:
+            print("\n".join(res.key_value_lines()))
+        rc |= 0 if (res.budget_ok or spec.mode != "record") else 1
+    return rc
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,107 @@
+import numpy as np
+import pytest
+
+from parameter_golf_b200.data import shards as S
+from parameter_golf_b200.data.bpb import BpbLuts, compute_bpb
+
+
+def _mk(tmp_path, n_files=2, n=1000, vocab=64):
+    for i in range(n_files):
+        S.write_shard(str(tmp_path / f"t_train_{i:06d}.bin"), (np.arange(n) + 1000 * i) % vocab)
+    return str(tmp_path / "t_train_*.bin")
+
+
+def test_shard_roundtrip_and_header(tmp_path):
+    p = str(tmp_path / "a.bin")
+    toks = np.arange(777, dtype=np.uint16)
+    S.write_shard(p, toks)
+    assert (tmp_path / "a.bin").stat().st_size == 1024 + 2 * 777
+    hdr = np.fromfile(p, dtype="<i4", count=3)
+    assert list(hdr) == [20240520, 1, 777]
+    assert np.array_equal(np.asarray(S.open_shard(p)), toks)
+
+
+def test_shard_rejects_bad_files(tmp_path):
+    p = tmp_path / "a.bin"
+    S.write_shard(str(p), np.arange(10))
+    raw = bytearray(p.read_bytes())
+    (tmp_path / "short.bin").write_bytes(raw[:-2])
+    with pytest.raises(S.ShardError):
+        S.open_shard(str(tmp_path / "short.bin"))
+    raw[0] ^= 0xFF
+    (tmp_path / "magic.bin").write_bytes(raw)
+    with pytest.raises(S.ShardError):
+        S.open_shard(str(tmp_path / "magic.bin"))
+    with pytest.raises(FileNotFoundError):
+        S.TokenStream(str(tmp_path / "none_*.bin"))
+
+
+def test_stream_wraps_and_skips(tmp_path):
+    pat = _mk(tmp_path, 2, 100, 1 << 16)
+    st = S.TokenStream(pat)
+    a = st.take(150)
+    assert a[99] == 99 and a[100] == 1000
+    st.skip(50)
+    assert st.take(3).tolist() == [0, 1, 2]      # wrapped to the first shard
+
+
+@pytest.mark.parametrize("world,accum", [(1, 1), (2, 1), (4, 2), (8, 1)])
+def test_loader_spans_are_the_reference_slicing(tmp_path, world, accum):
+    pat = _mk(tmp_path, 3, 5000, 1 << 16)
+    global_tokens, seq = 64 * world * accum, 16
+    ref = S.TokenStream(pat)
+    loaders = [S.DistributedTokenLoader(pat, r, world) for r in range(world)]
+    for _ in range(5):
+        L = global_tokens // (world * accum)
+        chunk = ref.take((L + 1) * world)
+        for r, ld in enumerate(loaders):
+            x, y = ld.next_batch(global_tokens, seq, accum)
+            span = chunk[r * (L + 1):(r + 1) * (L + 1)].astype(np.int64)
+            assert np.array_equal(x.reshape(-1), span[:-1]) and np.array_equal(y.reshape(-1), span[1:])
+            assert x.shape == (L // seq, seq)
+
+
+def test_loader_state_restore(tmp_path):
+    pat = _mk(tmp_path, 2, 3000, 1 << 16)
+    a = S.DistributedTokenLoader(pat, 1, 2)
+    a.next_batch(256, 16)
+    st = a.state()
+    x1, _ = a.next_batch(256, 16)
+    b = S.DistributedTokenLoader(pat, 1, 2)
+    b.restore(st)
+    x2, _ = b.next_batch(256, 16)
+    assert np.array_equal(x1, x2)
+
+
+def test_markov_generator_is_seeded_and_zipfian():
+    a = S.generate_markov_tokens(50000, 1024, seed=3)
+    assert np.array_equal(a, S.generate_markov_tokens(50000, 1024, seed=3))
+    assert not np.array_equal(a, S.generate_markov_tokens(50000, 1024, seed=4))
+    assert a.dtype == np.uint16 and a.max() < 1024
+    # order-1 structure: the conditional entropy is far below the marginal entropy
+    pair = np.bincount(a[:-1].astype(np.int64) * 1024 + a[1:], minlength=1024 * 1024).reshape(1024, 1024).astype(np.float64)
+    rowp = pair / np.clip(pair.sum(1, keepdims=True), 1, None)
+    h_cond = -(pair / pair.sum() * np.log(np.clip(rowp, 1e-12, None))).sum()
+    marg = np.bincount(a, minlength=1024) / a.size
+    h_marg = -(marg * np.log(np.clip(marg, 1e-12, None))).sum()
+    assert h_cond < 0.8 * h_marg
+
+
+def test_validation_loader_truncates(tmp_path):
+    S.write_shard(str(tmp_path / "v_val_000000.bin"), np.arange(1000) % 50)
+    v = S.load_validation_tokens(str(tmp_path / "v_val_*.bin"), 64)
+    assert v.shape[0] == 15 * 64 + 1
+    assert S.load_validation_tokens(str(tmp_path / "v_val_*.bin"), 64, max_tokens=200).shape[0] == 3 * 64 + 1
+
+
+def test_bpb_formula_and_luts():
+    luts = BpbLuts.from_pieces(["<s>", "▁the", "cat", "<0x41>", "▁"], 5, control={0})
+    assert luts.base_bytes.tolist() == [0, 3, 3, 1, 0]
+    prev, tgt = np.array([0, 1, 2]), np.array([1, 2, 1])
+    # "▁the" after a boundary token: no space byte; after "cat": +1
+    assert luts.token_bytes(prev, tgt).tolist() == [3, 3, 4]
+    loss, bpb = compute_bpb(loss_sum_nats=np.log(2.0) * 10, token_count=10, byte_count=40)
+    assert abs(loss - np.log(2.0)) < 1e-12 and abs(bpb - 0.25) < 1e-12
+    s = BpbLuts.seeded(1024)
+    assert s.base_bytes.min() >= 1 and s.base_bytes.max() <= 6 and np.array_equal(s.base_bytes, BpbLuts.seeded(1024).base_bytes)
+    assert BpbLuts.placeholder(8).base_bytes.tolist() == [4] * 8

@@ -1,0 +1,162 @@
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from parameter_golf_b200.data.bpb import BpbLuts
+from parameter_golf_b200.eval import sliding as S
+from parameter_golf_b200.eval import ttt as T
+from parameter_golf_b200.models import gpt
+from parameter_golf_b200.models.runner import OracleRunner
+from parameter_golf_b200.spec import family_preset
+
+
+def spec(**ov):
+    s = family_preset("tiny_cpu")
+    m = s.model
+    m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads, m.eval_seq_len = 32, 2, 16, 4, 2, 16
+    s.eval.stride, s.eval.chunk_tokens, s.eval.ttt_batch_seqs, s.eval.batch_windows = 4, 32, 2, 8
+    s.apply_overrides([f"{k}={v}" for k, v in ov.items()])
+    return s.validate()
+
+
+def test_window_rule():
+    starts = S.window_starts(100, 16, 4)
+    assert starts[:3] == [0, 4, 8] and starts[-1] == 96
+    assert S.scored_range(0, 100, 16, 4) == (0, 16) and S.scored_range(8, 100, 16, 4) == (12, 16)
+    assert S.scored_range(96, 100, 16, 4) == (0, 4) and S.scored_range(90, 100, 16, 4) == (6, 10)
+    covered = np.zeros(100, int)
+    for ws in starts:
+        s, w = S.scored_range(ws, 100, 16, 4)
+        covered[ws + s: ws + w] += 1
+    assert covered.min() >= 1 and (covered[:84] == 1).all()      # every token scored; exactly once away from the tail
+
+
+def test_chunk_assignment_by_first_scored_token():
+    chunks = S.build_ttt_chunks(100, 16, 4, 32)
+    assert len(chunks) == 4 and chunks[0][0] == 0
+    for ci, ws_list in enumerate(chunks):
+        for ws in ws_list:
+            s, _ = S.scored_range(ws, 100, 16, 4)
+            assert min((ws + s) // 32, 3) == ci
+    assert sum(len(c) for c in chunks) == len(S.window_starts(100, 16, 4, min_len=4))
+
+
+def test_sliding_equals_contiguous_when_stride_is_window_and_rank_split():
+    s = spec()
+    p = gpt.fill_deterministic(s.model)
+    r = OracleRunner(s.model, p)
+    toks = np.random.default_rng(0).integers(0, 32, 16 * 6 + 1).astype(np.uint16)
+    luts = BpbLuts.seeded(32)
+    a = S.eval_sliding(r.nll, toks, 16, 16, luts)
+    b = S.eval_contiguous(r.nll, toks, 16, luts)
+    assert abs(a[0] - b[0]) < 1e-6 and abs(a[1] - b[1]) < 1e-6
+    starts = S.window_starts(96, 16, 4)
+    parts = S.ScoreSums()
+    for rank in range(3):
+        lo, hi = S.rank_slice(len(starts), rank, 3)
+        parts.add(S.score_windows(r.nll, toks, starts[lo:hi], 16, 4, luts, 4))
+    whole = S.score_windows(r.nll, toks, starts, 16, 4, luts, 8)
+    assert abs(parts.loss - whole.loss) < 1e-6 and parts.tokens == whole.tokens and parts.bytes == whole.bytes
+
+
+def test_more_context_scores_better_on_markov_data():
+    from parameter_golf_b200.data.shards import generate_markov_tokens
+    s = spec()
+    p = gpt.fill_deterministic(s.model)
+    toks = generate_markov_tokens(200, 32, seed=1)
+    luts = BpbLuts.placeholder(32)
+    loss, bpb = S.eval_sliding(OracleRunner(s.model, p).nll, toks, 16, 4, luts)
+    assert math.isfinite(loss) and abs(bpb - loss / math.log(2) / 4) < 1e-9
+
+
+@pytest.mark.parametrize("mode", ["full_sgd", "q_only", "lact"])
+def test_score_first_ttt_runs_and_masks(mode):
+    s = spec()
+    s.eval.ttt_lr, s.eval.ttt_epochs = 0.05, 1
+    p = gpt.fill_deterministic(s.model)
+    before = {k: v.clone() for k, v in p.items()}
+    toks = np.random.default_rng(1).integers(0, 32, 16 * 8 + 1).astype(np.uint16)
+    loss, bpb = T.eval_score_first_ttt(OracleRunner(s.model, p), toks, s.model, s.eval, BpbLuts.seeded(32), mode=mode)
+    assert math.isfinite(loss) and math.isfinite(bpb)
+    n = s.model.num_layers
+    assert not torch.equal(p["qo_bank"][:n], before["qo_bank"][:n])
+    if mode == "q_only":
+        assert torch.equal(p["qo_bank"][n:], before["qo_bank"][n:]) and torch.equal(p["kv_bank"], before["kv_bank"])
+        assert torch.equal(p["tok_emb"], before["tok_emb"])
+    else:
+        assert not torch.equal(p["kv_bank"], before["kv_bank"])
+
+
+def test_first_chunk_score_is_unadapted_and_last_chunk_not_trained():
+    s = spec()
+    s.eval.ttt_lr = 0.05
+    toks = np.random.default_rng(2).integers(0, 32, 32 + 1).astype(np.uint16)       # exactly one chunk
+    p = gpt.fill_deterministic(s.model)
+    ref = S.eval_sliding(OracleRunner(s.model, {k: v.clone() for k, v in p.items()}).nll, toks, 16, 4, BpbLuts.seeded(32))
+    before = {k: v.clone() for k, v in p.items()}
+    got = T.eval_score_first_ttt(OracleRunner(s.model, p), toks, s.model, s.eval, BpbLuts.seeded(32))
+    assert all(torch.equal(p[k], before[k]) for k in p)                                  # a single (= last) chunk is never trained on
+    chunks = S.build_ttt_chunks(32, 16, 4, 32)
+    assert sum(len(c) for c in chunks) == len(S.window_starts(32, 16, 4, min_len=4)) and math.isfinite(got[0]) and math.isfinite(ref[0])
+
+
+def test_mutation_guard_trips():
+    s = spec()
+    p = gpt.fill_deterministic(s.model)
+    r = OracleRunner(s.model, p)
+    orig = r.nll
+
+    def evil(ids, tg):
+        p["qo_bank"].add_(1e-3)
+        return orig(ids, tg)
+    r.nll = evil
+    toks = np.random.default_rng(3).integers(0, 32, 16 * 4 + 1).astype(np.uint16)
+    with pytest.raises(RuntimeError, match="mutation"):
+        T.eval_score_first_ttt(r, toks, s.model, s.eval, BpbLuts.seeded(32))
+
+
+def test_freeze_blocks_and_cosine():
+    s = spec()
+    g = {k: torch.ones_like(v) for k, v in gpt.fill_deterministic(s.model).items()}
+    T.mask_grads(s.model, g, "full_sgd", freeze_blocks=1)
+    assert g["qo_bank"][0].abs().max() == 0 and g["qo_bank"][2].abs().max() == 0 and g["qo_bank"][1].abs().max() == 1
+    assert g["mlp_up_bank"][0].abs().max() == 0 and g["tok_emb"].abs().max() == 1
+    assert S.cosine_over_chunks(1.0, 0, 11) == 1.0 and abs(S.cosine_over_chunks(1.0, 10, 11)) < 1e-12
+
+
+def test_lora_phased_ttt_and_deadline():
+    s = spec()
+    s.eval.lora_rank, s.eval.phased_ttt_phases, s.eval.ttt_lr = 4, 2, 0.05
+    p = gpt.fill_deterministic(s.model)
+    before = {k: v.clone() for k, v in p.items()}
+    toks = np.random.default_rng(4).integers(0, 32, 16 * 8 + 1).astype(np.uint16)
+    logs = []
+    loss, bpb = T.eval_lora_phased_ttt(OracleRunner(s.model, p), toks, s.model, s.eval, BpbLuts.seeded(32), log=logs.append)
+    assert math.isfinite(loss) and all(torch.equal(p[k], before[k]) for k in p)          # base weights untouched
+    assert any(l.startswith("ttt_audit_json=") for l in logs)
+    s.eval.max_eval_seconds = 1e-9
+    logs.clear()
+    T.eval_lora_phased_ttt(OracleRunner(s.model, p), toks, s.model, s.eval, BpbLuts.seeded(32), log=logs.append)
+    assert any("deadline" in l for l in logs)
+
+
+def test_prefix_doc_schedule():
+    toks = np.array([5, 1, 7, 7, 1, 9, 9, 9, 1, 3] * 10, dtype=np.uint16)
+    assert T.schedule_prefix_docs(toks, 1, 2, 8) == 8 and T.schedule_prefix_docs(toks, 1, 0, 8) == 0
+    assert T.schedule_prefix_docs(toks, None, 2, 8) == 0
+
+
+def test_slot_limits():
+    tab = T.BigramCounts(8)
+    prev, cur = np.array([1, 1, 1, 2]), np.array([3, 3, 4, 5])
+    tab.update(prev, cur)
+    logits = torch.randn(4, 8)
+    neural = -torch.log_softmax(logits.double(), -1)[torch.arange(4), torch.from_numpy(cur)].numpy()
+    assert np.allclose(T.slot_nll(logits, prev, cur, tab, alpha=1.0), neural)
+    bg = -np.log(tab.row_probs(prev)[np.arange(4), cur])
+    assert np.allclose(T.slot_nll(logits, prev, cur, tab, alpha=0.0), bg)
+    assert abs(tab.row_probs(np.array([1]))[0, 3] - 3 / 11) < 1e-12                     # add-one smoothing
+    mid = T.slot_nll(logits, prev, cur, tab, alpha=0.5, adaptive=True)
+    assert np.isfinite(mid).all()

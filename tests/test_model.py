@@ -1,0 +1,126 @@
+import copy
+
+import pytest
+import torch
+
+from parameter_golf_b200.models import gpt
+from parameter_golf_b200.spec import family_preset
+
+
+def tiny(**ov):
+    s = family_preset("tiny_cpu")
+    m = s.model
+    m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads, m.mlp_mult = 32, 3, 16, 4, 2, 2.0
+    s.apply_overrides([f"model.{k}={v}" for k, v in ov.items()])
+    return s.validate().model
+
+
+FULL = dict(xsa_last_n=2, ln_scale="true", smear_gate="true", activation="leaky_relu_sq")
+
+
+def full_model():
+    m = tiny(**FULL)
+    m.bigram.enabled, m.bigram.vocab_size, m.bigram.dim = True, 24, 8
+    m.value_embedding.enabled, m.value_embedding.dim, m.value_embedding.layers = True, 8, [1, 2]
+    m.rope.dims = 2
+    return m
+
+
+def test_shapes_and_count():
+    m = full_model()
+    sh = gpt.param_shapes(m)
+    assert sh["qo_bank"] == (6, 16, 16) and sh["kv_bank"] == (6, 8, 16) and sh["mlp_up_bank"] == (3, 32, 16)
+    assert sh["skip_weights"] == (1, 16) and sh["bigram_proj"] == (16, 8) and sh["ve_proj"] == (8, 8)
+    p = gpt.init_params(m)
+    assert sum(v.numel() for v in p.values()) == gpt.count_params(m)
+    assert p["qo_bank"][3:].abs().max() == 0 and p["mlp_down_bank"].abs().max() == 0          # zero-init projections
+    q = p["qo_bank"][0]
+    assert torch.allclose(q @ q.t(), torch.eye(16), atol=1e-5)                                  # orthogonal init
+
+
+def test_bank_slices_are_zero_copy_and_overlap_guard():
+    m = tiny()
+    p = gpt.init_params(m)
+    v = gpt.bank_views(m, p)
+    assert v["qo_bank.o"].data_ptr() == p["qo_bank"][3].data_ptr()
+    assert gpt.overlaps_storage(p["qo_bank"][1], p["qo_bank"])
+    assert not gpt.overlaps_storage(p["qo_bank"][0], p["qo_bank"][1])
+    assert not gpt.overlaps_storage(p["qo_bank"], p["kv_bank"])
+
+
+def test_finite_loss_near_uniform_at_init():
+    m = full_model()
+    p = gpt.init_params(m)
+    ids = torch.randint(0, 32, (2, 12))
+    loss = gpt.gpt_forward(m, p, ids, ids)
+    assert torch.isfinite(loss) and abs(float(loss) - torch.log(torch.tensor(32.0))) < 0.1
+
+
+def test_model_is_causal_and_batch_rows_independent():
+    m = full_model()
+    p = gpt.fill_deterministic(m)
+    ids = torch.randint(0, 32, (2, 10))
+    a = gpt.gpt_logits(m, p, ids)
+    ids2 = ids.clone()
+    ids2[0, 7:] = (ids2[0, 7:] + 5) % 32
+    b = gpt.gpt_logits(m, p, ids2)
+    assert torch.allclose(a[0, :7], b[0, :7], atol=1e-5) and not torch.allclose(a[0, 7:], b[0, 7:])
+    assert torch.allclose(a[1], b[1], atol=1e-6)
+
+
+def test_identity_gates_are_no_ops():
+    base = tiny()
+    p = gpt.fill_deterministic(base)
+    ids = torch.randint(0, 32, (1, 8))
+    ref = gpt.gpt_logits(base, p, ids)
+    g = tiny()
+    g.attn_out_gate.enabled = True
+    pg = dict(p, attn_gate_weight=torch.zeros(3, 4, g.attn_out_gate.width), attn_gate_bias=torch.zeros(3, 4))
+    assert torch.allclose(gpt.gpt_logits(g, pg, ids), ref, atol=1e-6)
+    s = tiny(smear_gate="true")
+    ps = dict(p, smear_gate=torch.full((16,), -40.0))
+    assert torch.allclose(gpt.gpt_logits(s, ps, ids), ref, atol=1e-5)
+
+
+def test_recurrence_runs_block_twice():
+    m = tiny()
+    m.recurrence.enabled, m.recurrence.start_layer, m.recurrence.repeat_layers = True, 1, 1
+    assert gpt.layer_schedule(m) == [(0, 0), (1, 0), (1, 1), (2, 0)]
+    p = gpt.fill_deterministic(m)
+    ids = torch.randint(0, 32, (1, 8))
+    assert not torch.allclose(gpt.gpt_logits(m, p, ids), gpt.gpt_logits(tiny(), p, ids))
+
+
+def test_numerical_gradient_of_tok_emb_and_bank():
+    m = full_model()
+    p = {k: v.double() for k, v in gpt.fill_deterministic(m).items()}
+    ids = torch.randint(0, 32, (2, 6))
+    tgt = torch.randint(0, 32, (2, 6))
+    for name, idx in (("tok_emb", (int(ids[0, 0]), 3)), ("qo_bank", (4, 2, 5)), ("resid_mix", (1, 1, 3)), ("bigram_scale", (0,))):
+        leaf = p[name].clone().requires_grad_(True)
+        loss = gpt.gpt_forward(m, dict(p, **{name: leaf}), ids, tgt)
+        (g,) = torch.autograd.grad(loss, leaf)
+        eps = 1e-5
+        pp, pm = p[name].clone(), p[name].clone()
+        pp[idx] += eps
+        pm[idx] -= eps
+        fd = (gpt.gpt_forward(m, dict(p, **{name: pp}), ids, tgt) - gpt.gpt_forward(m, dict(p, **{name: pm}), ids, tgt)) / (2 * eps)
+        assert abs(float(fd) - float(g[idx])) < 1e-3 * max(1.0, abs(float(fd))), name
+
+
+def test_qat_forward_differs_but_trains():
+    m = tiny()
+    p = gpt.fill_deterministic(m)
+    ids = torch.randint(0, 32, (1, 8))
+    a = gpt.gpt_forward(m, p, ids, ids)
+    b = gpt.gpt_forward(m, p, ids, ids, qat=True)
+    assert torch.isfinite(b) and abs(float(a) - float(b)) < 0.2 and float(a) != float(b)
+
+
+def test_lora_with_zero_b_is_identity():
+    from parameter_golf_b200.eval.ttt import init_q_lora
+    m = tiny()
+    p = gpt.fill_deterministic(m)
+    ids = torch.randint(0, 32, (1, 8))
+    lora = init_q_lora(m, 4, 4.0)
+    assert torch.allclose(gpt.gpt_logits(m, p, ids, lora=lora), gpt.gpt_logits(m, p, ids), atol=1e-6)

@@ -1,0 +1,191 @@
+import json
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from parameter_golf_b200.models import gpt
+from parameter_golf_b200.quant import container as C
+from parameter_golf_b200.quant import quantize as Q
+from parameter_golf_b200.quant.export import build_artifact, check_budget, export_model, load_artifact
+from parameter_golf_b200.quant.gptq import gptq_quantize
+from parameter_golf_b200.spec import family_preset
+
+torch.manual_seed(0)
+
+
+def small_spec(**ov):
+    s = family_preset("tiny_cpu")
+    m = s.model
+    m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads = 64, 2, 32, 4, 2
+    m.bigram.enabled, m.bigram.vocab_size, m.bigram.dim = True, 16, 8
+    m.smear_gate = True
+    s.apply_overrides([f"{k}={v}" for k, v in ov.items()])
+    return s.validate()
+
+
+def test_pgrs_roundtrip_and_layout():
+    recs = [C.TensorRecord("a.weight", (2, 3), "i8", b"\x01\x02\x03"), C.TensorRecord("b", (2,), "f16", np.array([1, 2], "<f2").tobytes())]
+    blob = C.write_pgrs(recs, '{"k":1}')
+    assert blob[:4] == b"PGRS" and struct.unpack_from("<II", blob, 4) == (1, 2)
+    # first record: name_len, name, ndim, dims, dtype code, data_len
+    assert struct.unpack_from("<I", blob, 12)[0] == 8 and blob[16:24] == b"a.weight"
+    assert struct.unpack_from("<III", blob, 24) == (2, 2, 3) and blob[36] == 3
+    out, md = C.read_pgrs(blob)
+    assert md == '{"k":1}' and [(r.name, r.dims, r.dtype, r.data) for r in out] == [(r.name, r.dims, r.dtype, r.data) for r in recs]
+
+
+def test_pgrs_crc_detects_corruption():
+    blob = bytearray(C.write_pgrs([C.TensorRecord("w", (4,), "i8", b"abcd")], "{}"))
+    blob[blob.index(b"abcd") + 1] ^= 0x40
+    with pytest.raises(C.ArtifactError, match="CRC"):
+        C.read_pgrs(bytes(blob))
+    with pytest.raises(C.ArtifactError):
+        C.read_pgrs(bytes(blob[:20]))
+
+
+def test_zstd_and_pergroup_roundtrip_and_sniffing():
+    raw = C.write_pgrs([C.TensorRecord("w", (1000,), "i8", bytes(1000))], "{}")
+    z = C.compress_payload(raw, "zstd22")
+    assert z[:4] == b"\x28\xb5\x2f\xfd" and len(z) < len(raw) and C.decompress_payload(z) == raw
+    g = C.compress_pergroup(raw, chunk_bytes=300)
+    assert g[:4] == b"PGPG" and struct.unpack_from("<IQII", g, 4) == (1, len(raw), 300, 4)
+    assert C.decompress_payload(g) == raw and C.decompress_payload(raw) == raw
+    with pytest.raises(C.ArtifactError):
+        C.compress_payload(raw, "lzma9")
+
+
+@pytest.mark.parametrize("bits", [4, 5, 6, 7, 8])
+def test_bitpack_lsb_first(bits):
+    qmin, qmax = Q.qrange(bits)
+    q = np.random.default_rng(bits).integers(qmin, qmax + 1, size=37)
+    data = C.pack_bits(q, bits)
+    assert len(data) == (37 * bits + 7) // 8
+    assert np.array_equal(C.unpack_bits(data, 37, bits), q)
+    one = C.pack_bits(np.array([qmin + 1, qmin]), bits)       # encoded values 1, 0 => only bit 0 set
+    assert one[0] == 1
+
+
+def test_quantizer_rule():
+    assert Q.qrange(6) == (-32, 31) and Q.qrange(5) == (-16, 15)
+    assert Q.round_half_away(torch.tensor([0.5, -0.5, 1.5, 2.5, -2.5])).tolist() == [1, -1, 2, 3, -3]
+    w = torch.randn(8, 4096)
+    w[0, 0] = 5.0                                             # an outlier makes a clipped percentile win
+    q, s = Q.quantize_rows(w, 6)
+    assert q.dtype == torch.int8 and q.min() >= -32 and q.max() <= 31
+    srt = w[0].abs().sort().values
+    assert any(abs(float(s[0]) - float(srt[min(int(4096 * p), 4095)] / 31)) < 1e-7 for p in Q.CLIP_PERCENTILES)
+    assert float(s[0]) < 5.0 / 31
+    for r in range(8):                                         # the chosen clip has the smallest error of the five
+        errs = []
+        for p in Q.CLIP_PERCENTILES:
+            sc = max(float(w[r].abs().sort().values[min(int(4096 * p), 4095)]), 1e-8) / 31
+            qq = Q.round_half_away(w[r] / sc).clamp(-32, 31)
+            errs.append(float((w[r] - qq * sc).pow(2).sum()))
+        got = float((w[r] - q[r].float() * s[r]).pow(2).sum())
+        assert got <= min(errs) * (1 + 1e-5)
+
+
+@pytest.mark.parametrize("scheme,compression", [("gptq_lite_int6", "zstd22"), ("mixed_int5_int6", "pergroup"), ("aggressive", "none"),
+                                                ("tight_int7_int4", "zstd22")])
+def test_export_load_roundtrip(scheme, compression, tmp_path):
+    s = small_spec(**{"quant.scheme": scheme, "quant.compression": compression})
+    p = gpt.fill_deterministic(s.model)
+    blob = export_model(s, p, str(tmp_path / "a.pgrs"))
+    assert (tmp_path / "a.pgrs").read_bytes() == blob
+    back = load_artifact(blob, s)
+    assert set(back) == set(p)
+    bits = Q.scheme_bits(scheme)
+    for k in p:
+        tol = 0.6 * float(p[k].abs().max()) / (2 ** (min(bits.values()) - 1) - 1) if k in gpt.BANKS or k == "tok_emb" else 2e-3 * max(1.0, float(p[k].abs().max()))
+        assert (back[k] - p[k]).abs().max() <= tol + 1e-6, k
+    recs, md = C.read_pgrs(C.decompress_payload(blob))
+    names = [r.name for r in recs]
+    assert names[:4] == ["qo_bank.q.weight", "qo_bank.q.scale", "qo_bank.o.weight", "qo_bank.o.scale"]
+    assert names[14:17] == ["bigram_embed", "bigram_proj", "bigram_scale"] and "blocks.1.q_gain" in names
+    meta = json.loads(md)
+    assert meta["format"] == "pgrs_quant" and meta["groups"] == bits and '"qo_bank.q":' in md and " " not in md
+    w = next(r for r in recs if r.name == "mlp_up_bank.weight")
+    assert w.dtype == "i8" and w.dims == (2 * 64, 32) and len(w.data) == (2 * 64 * 32 * bits["mlp_up_bank"] + 7) // 8
+
+
+def test_load_rejects_mismatched_shape_and_corruption():
+    s = small_spec()
+    blob = export_model(s, gpt.fill_deterministic(s.model))
+    other = small_spec(**{"model.num_layers": 3})
+    with pytest.raises(C.ArtifactError, match="num_layers"):
+        load_artifact(blob, other)
+    raw = bytearray(C.decompress_payload(blob))
+    raw[200] ^= 1
+    with pytest.raises(C.ArtifactError):
+        load_artifact(bytes(raw), s)
+
+
+def test_lqer_reduces_error():
+    s0, s1 = small_spec(**{"quant.matrix_bits": 4}), small_spec(**{"quant.matrix_bits": 4, "quant.lqer.enabled": "true", "quant.lqer.rank": 8})
+    p = gpt.init_params(s0.model, seed=1)
+    p["mlp_down_bank"].normal_()
+    e0 = (load_artifact(export_model(s0, p), s0)["mlp_down_bank"] - p["mlp_down_bank"]).pow(2).mean()
+    e1 = (load_artifact(export_model(s1, p), s1)["mlp_down_bank"] - p["mlp_down_bank"]).pow(2).mean()
+    assert e1 < 0.9 * e0
+
+
+def test_legacy_unsplit_names_load():
+    s = small_spec()
+    p = gpt.fill_deterministic(s.model)
+    recs, md = C.read_pgrs(build_artifact(s, p))
+    by = {r.name: r for r in recs}
+    meta = json.loads(md)
+    meta["groups"]["qo_bank"] = 6
+    meta["groups"]["kv_bank"] = 6
+    merged = []
+    for bank, (a, b) in (("qo_bank", ("qo_bank.q", "qo_bank.o")), ("kv_bank", ("kv_bank.k", "kv_bank.v"))):
+        qa = C.unpack_bits(by[f"{a}.weight"].data, int(np.prod(by[f"{a}.weight"].dims)), 6)
+        qb = C.unpack_bits(by[f"{b}.weight"].data, int(np.prod(by[f"{b}.weight"].dims)), 6)
+        rows = by[f"{a}.weight"].dims[0] + by[f"{b}.weight"].dims[0]
+        merged.append(C.TensorRecord(f"{bank}.weight", (rows, by[f"{a}.weight"].dims[1]), "i8", C.pack_bits(np.concatenate([qa, qb]), 6)))
+        merged.append(C.TensorRecord(f"{bank}.scale", (rows,), "f16", by[f"{a}.scale"].data + by[f"{b}.scale"].data))
+    rest = [r for r in recs if not r.name.startswith(("qo_bank.", "kv_bank."))]
+    back = load_artifact(C.write_pgrs(merged + rest, json.dumps(meta, separators=(",", ":"))), s)
+    ref = load_artifact(build_artifact(s, p), s)
+    assert torch.equal(back["qo_bank"], ref["qo_bank"]) and torch.equal(back["kv_bank"], ref["kv_bank"])
+
+
+def test_prune_masks_and_ordering():
+    w = torch.randn(6, 16)
+    assert (Q.prune_topk_per_row(w, 0.25).sum(1) == 4).all()
+    assert Q.prune_global_magnitude(w, 0.5).sum() == 48
+    m24 = Q.prune_2_of_4(w).reshape(6, 4, 4)
+    assert (m24.sum(-1) == 2).all()
+    ab = Q.ordering_ab_test(w, 0.5, 6)
+    assert set(ab) == {"prune_then_quantize_mse", "quantize_then_prune_mse"} and all(v > 0 for v in ab.values())
+
+
+def test_budget_is_strict():
+    assert check_budget(15_000_000, 999_999) and not check_budget(15_000_000, 1_000_000)
+
+
+def test_gptq_beats_round_to_nearest_on_hessian_error():
+    rows, cols = 24, 48
+    W = torch.randn(rows, cols)
+    X = torch.randn(400, cols) @ (torch.eye(cols) + 0.6 * torch.randn(cols, cols))      # correlated inputs
+    H = X.t() @ X / 400
+    q, s = gptq_quantize(W, H, bits=4, block=16)
+    assert q.min() >= -8 and q.max() <= 7
+    q0, s0 = Q.quantize_rows(W, 4)
+
+    def out_err(qq, ss):
+        return float(((W - qq.float() * ss.half().float()[:, None]) @ X.t()).pow(2).mean())
+    assert out_err(q, s) < 0.85 * out_err(q0, s0)
+
+
+def test_selective_prune_hits_target():
+    q = {"a": torch.randint(-3, 4, (64, 64), dtype=torch.int8)}
+    sc = {"a": torch.rand(64) + 0.1}
+    size = lambda d: len(C.zstd_compress(C.pack_bits(d["a"].numpy(), 6), 3))
+    full = size(q)
+    out, n = Q.selective_prune_to_target(q, sc, size, int(full * 0.93))
+    assert size(out) <= int(full * 0.93) and n > 0
+    changed = out["a"] != q["a"]
+    assert (q["a"][changed].abs() == 1).all() and (out["a"][changed] == 0).all()

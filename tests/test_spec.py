@@ -1,0 +1,82 @@
+import os
+
+import pytest
+
+from parameter_golf_b200.spec import RunSpec, family_preset
+
+
+def test_partial_toml_loads(tmp_path):
+    f = tmp_path / "s.toml"
+    f.write_text('name = "x"\nmode = "smoke"\n[model]\nnum_layers = 3\n[model.bigram]\nenabled = true\nvocab_size = 64\n[eval]\nstride = 32\n')
+    s = RunSpec.load(str(f)).validate()
+    assert s.model.num_layers == 3 and s.model.bigram.enabled and s.eval.stride == 32 and s.train.seq_len == 2048
+
+
+def test_unknown_key_rejected(tmp_path):
+    f = tmp_path / "s.toml"
+    f.write_text("[model]\nnot_a_key = 1\n")
+    with pytest.raises(KeyError):
+        RunSpec.load(str(f))
+
+
+def test_toml_roundtrip():
+    s = family_preset("record_11l")
+    import tomllib
+    s2 = RunSpec.from_dict(tomllib.loads(s.to_toml()))
+    assert s2.to_dict() == s.to_dict()
+
+
+def test_env_overlay_uses_train_gpt_names():
+    s = family_preset("baseline_9l").apply_env({"NUM_LAYERS": "5", "TRAIN_SEQ_LEN": "512", "BIGRAM_VOCAB_SIZE": "3072",
+                                                "XSA_LAST_N": "2", "MATRIX_LR": "0.01", "VE_LAYERS": "3,4", "TTT_ENABLED": "1"})
+    assert s.model.num_layers == 5 and s.train.seq_len == 512 and s.model.train_seq_len == 512
+    assert s.model.bigram.enabled and s.model.bigram.vocab_size == 3072 and s.model.xsa_last_n == 2
+    assert s.train.matrix_lr == 0.01 and s.model.value_embedding.layers == [3, 4] and s.eval.legal_score_first
+
+
+def test_overrides():
+    s = family_preset("tiny_cpu").apply_overrides(["train.matrix_lr=0.5", "model.bigram.enabled=true", "eval.max_tokens=100"])
+    assert s.train.matrix_lr == 0.5 and s.model.bigram.enabled is True and s.eval.max_tokens == 100
+    with pytest.raises(KeyError):
+        s.apply_overrides(["train.nope=1"])
+
+
+@pytest.mark.parametrize("ov", ["model.num_heads=7", "model.rope.mode=yarn", "quant.compression=lzma9", "train.world_size=2",
+                                "model.vocab_size=70000", "quant.matrix_bits=3", "train.batch_tokens=1000"])
+def test_validation_rejects(ov):
+    with pytest.raises(ValueError):
+        family_preset("tiny_cpu").apply_overrides([ov]).validate()
+
+
+def test_gates_mutually_exclusive():
+    s = family_preset("tiny_cpu").apply_overrides(["model.attn_out_gate.enabled=true", "model.sparse_attn_gate.enabled=true"])
+    with pytest.raises(ValueError):
+        s.validate()
+
+
+def test_record_mode_is_fail_closed():
+    s = family_preset("record_11l")
+    s.mode = "record"
+    s.train.world_size = 8
+    with pytest.raises(ValueError):
+        s.validate()     # no data patterns
+    s.allow_unsupported_variants = True
+    s.validate()
+
+
+def test_fingerprint_sensitivity():
+    a = family_preset("record_11l").fingerprint()
+    assert a == family_preset("record_11l").fingerprint()
+    assert a != family_preset("record_11l").apply_overrides(["model.xsa_last_n=3"]).fingerprint()
+    assert a != family_preset("record_11l").apply_overrides(["train.matrix_lr=0.03"]).fingerprint()
+    assert a == family_preset("record_11l").apply_overrides(["train.train_log_every=7"]).fingerprint()
+
+
+def test_presets_match_benchmark_configs():
+    t = family_preset("tiny_cpu").validate().model
+    assert (t.num_layers, t.model_dim, t.num_heads, t.num_kv_heads, t.head_dim, t.mlp_dim) == (2, 128, 4, 2, 32, 256)
+    b = family_preset("baseline_9l").validate()
+    assert (b.model.num_layers, b.model.rope_dims, b.train.batch_tokens, b.train.seq_len) == (9, 64, 524288, 1024)
+    r = family_preset("record_11l").validate()
+    assert (r.model.mlp_dim, r.model.rope_dims, r.model.xsa_layers(), r.model.bigram.vocab_size) == (1536, 16, [7, 8, 9, 10], 3072)
+    assert r.train.distributed_optimizer_backend == "sharded_parallel_muon" and r.train.batch_tokens == 786432

@@ -1,0 +1,167 @@
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from parameter_golf_b200.models import gpt
+from parameter_golf_b200.quant.export import load_artifact
+from parameter_golf_b200.spec import family_preset
+from parameter_golf_b200.train import VariantRunner, mode_max_steps, record_gaps, split_param_groups, step_batch_plan
+from parameter_golf_b200.utils.checkpoint import load_checkpoint, save_checkpoint
+from parameter_golf_b200.utils.logging import RunLog
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def quiet(spec):
+    return VariantRunner(spec, RunLog(spec.name, console=False))
+
+
+def test_tiny_config_end_to_end(tmp_path, monkeypatch):
+    """2 layers, d128, 4/2 heads, vocab 1024, seq 256, 8x256 tokens, 20 Muon+Adam steps, int6 + zstd round trip."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "record_shaped_proxy"
+    s.train.total_iterations = 20
+    s.train.artifact_path = str(tmp_path / "tiny.pgrs")
+    s.eval.max_tokens = 1024
+    r = quiet(s)
+    import parameter_golf_b200.train as tr
+    monkeypatch.setattr(tr, "mode_max_steps", lambda spec, mode: 20)
+    res = r.run()
+    assert res.steps == 20 and res.tokens_per_step == 8 * 256
+    assert res.train_loss_last < res.train_loss_first < 7.0
+    assert os.path.getsize(s.train.artifact_path) == res.artifact_bytes and res.budget_ok
+    assert np.isfinite(res.val_loss) and np.isfinite(res.val_bpb) and res.eval_kind == "sliding"
+    back = load_artifact(open(s.train.artifact_path, "rb").read(), s)
+    assert back["qo_bank"].shape == (4, 128, 128)
+    lines = res.key_value_lines()
+    assert any(l.startswith("step_avg_ms=") for l in lines) and any(l.startswith("fingerprint=") for l in lines)
+    assert any(l.startswith("record_audit_json=") for l in r.log.lines)
+    assert any(l.startswith("step:20/20 train_loss:") for l in r.log.lines)
+
+
+def test_batch_plan_and_modes():
+    s = family_preset("record_11l")
+    s.train.world_size = 8
+    assert step_batch_plan(s, "record") == (786432, 1)
+    s.train.world_size = 2
+    assert step_batch_plan(s, "record_shaped_proxy") == (786432, 4)
+    assert step_batch_plan(s, "smoke") == (2 * 2048 * 2, 1)
+    assert mode_max_steps(s, "smoke") == 4 and mode_max_steps(s, "proxy") == 32 and mode_max_steps(s, "record") == 9000
+    assert step_batch_plan(family_preset("tiny_cpu"), "record") == (2048, 1)
+
+
+def test_param_groups_follow_python_grouping():
+    s = family_preset("record_11l")
+    s.model.value_embedding.enabled = True
+    shapes = gpt.param_shapes(s.model)
+    banks, groups = split_param_groups(s, shapes)
+    assert banks == ["qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank"]
+    assert groups[0]["names"] == ["tok_emb", "bigram_embed", "ve_embed"] and groups[0]["lr"] == s.train.tied_embed_lr
+    assert "bigram_proj" in groups[1]["names"] and "ve_proj" in groups[1]["names"] and "resid_mix" in groups[1]["names"]
+
+
+def test_record_gate_fails_closed():
+    s = family_preset("record_11l")
+    gaps = record_gaps(s, "record")
+    assert any("shards" in g for g in gaps) and any("8 GPUs" in g for g in gaps)
+    assert record_gaps(s, "proxy") == []
+
+
+def test_wallclock_cap_stops_cleanly(tmp_path, monkeypatch):
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "proxy"
+    s.train.max_wallclock_seconds = 0.2
+    s.train.total_iterations = 32
+    s.train.artifact_path = str(tmp_path / "a.pgrs")
+    res = quiet(s).run()
+    assert res.stopped_early and 0 < res.steps < 32 and np.isfinite(res.val_bpb)
+
+
+def test_checkpoint_resume_continues_the_trajectory(tmp_path, monkeypatch):
+    """3 steps + checkpoint + resume for 3 more reproduces the loss trajectory of 6 straight steps
+    (multi-threaded CPU reductions make bit equality of the weights too strict)."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+
+    def run(iters, **kw):
+        s = family_preset("tiny_cpu")
+        s.mode = "proxy"
+        s.train.total_iterations = iters
+        s.train.train_log_every = 1
+        s.train.artifact_path = str(tmp_path / f"a{iters}{len(kw)}.pgrs")
+        for k, v in kw.items():
+            setattr(s.train, k, v)
+        r = quiet(s)
+        res = r.run()
+        losses = [float(l.split("train_loss:")[1].split()[0]) for l in r.log.lines if l.startswith("step:")]
+        return losses, res
+
+    ck = str(tmp_path / "ck.bin")
+    full, res_full = run(6)
+    run(3, checkpoint_every=3, checkpoint_path=ck)
+    st = load_checkpoint(ck)
+    assert st["step"] == 3 and "muon" in st["optim"] and st["loader"]["pos"] > 0
+    resumed, res_resumed = run(6, resume_from=ck)
+    assert len(resumed) == 3 and np.allclose(resumed, full[3:], atol=2e-3)
+    assert abs(res_resumed.val_loss - res_full.val_loss) < 5e-3
+
+
+def test_checkpoint_detects_corruption_and_fingerprint(tmp_path, monkeypatch):
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    ck = str(tmp_path / "c.bin")
+    save_checkpoint(ck, "abc", 1, {"w": torch.ones(3)}, {}, {"file_idx": 0, "pos": 0})
+    raw = bytearray(open(ck, "rb").read())
+    raw[-1] ^= 1
+    open(ck, "wb").write(raw)
+    with pytest.raises(ValueError, match="corrupted"):
+        load_checkpoint(ck)
+    save_checkpoint(ck, "abc", 1, {"w": torch.ones(3)}, {}, {"file_idx": 0, "pos": 0})
+    s = family_preset("tiny_cpu")
+    s.mode, s.train.resume_from = "smoke", ck
+    with pytest.raises(RuntimeError, match="fingerprint"):
+        quiet(s).run()
+
+
+def test_cli_prints_key_value_protocol(tmp_path):
+    env = dict(os.environ, PGB_DATA_ROOT=str(tmp_path / "d"), PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-m", "parameter_golf_b200.train", "run", "--family", "tiny_cpu", "--mode", "smoke",
+                          "--artifact", str(tmp_path / "x.pgrs"), "train.seed=7"], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    kv = dict(l.split("=", 1) for l in out.stdout.splitlines() if "=" in l and not l.startswith("record_audit_json"))
+    assert kv["steps"] == "4" and kv["mode"] == "smoke" and float(kv["val_bpb"]) > 0
+
+
+def test_two_cpu_ranks_stay_in_sync(tmp_path):
+    """gloo ranks: each reads its own span, gradients are averaged, and both end with identical weights."""
+    script = tmp_path / "w.py"
+    script.write_text(f"""
+import os, sys, hashlib, torch
+sys.path.insert(0, {ROOT!r})
+import torch.distributed as dist
+from parameter_golf_b200.spec import family_preset
+from parameter_golf_b200.train import VariantRunner
+from parameter_golf_b200.utils.logging import RunLog
+dist.init_process_group('gloo')
+s = family_preset('tiny_cpu'); s.mode = 'smoke'
+s.train.backend = 'cpu'; s.train.rank = dist.get_rank(); s.train.world_size = 2
+s.allow_unsupported_variants = True
+s.train.artifact_path = {str(tmp_path)!r} + f'/a{{dist.get_rank()}}.pgrs'
+s.quant.compression = 'none'
+import parameter_golf_b200.spec as sp
+orig = sp.RunSpec.validate
+sp.RunSpec.validate = lambda self: self
+res = VariantRunner(s, RunLog('r', rank=dist.get_rank(), console=False)).run()
+blob = open(s.train.artifact_path, 'rb').read() if dist.get_rank() == 0 else b''
+print('OK', dist.get_rank(), res.steps, res.val_bpb)
+""")
+    env = dict(os.environ, PGB_DATA_ROOT=str(tmp_path / "d"), PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                          "--master-port", "29611", str(script)], capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    oks = [l.split() for l in out.stdout.splitlines() if l.startswith("OK")]
+    assert len(oks) == 2 and oks[0][3] == oks[1][3]          # identical reduced val_bpb on both ranks

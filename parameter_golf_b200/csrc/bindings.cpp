@@ -1,0 +1,89 @@
+// pybind11 bindings: torch tensors in, raw pointers + the current CUDA stream out to the kernel library.
+#include <ATen/cuda/CUDAContext.h>
+#include <torch/extension.h>
+
+#include "pgb.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_bf16(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == torch::kBFloat16, name, " must be bfloat16");
+}
+
+int* status_ptr(const c10::optional<torch::Tensor>& status) {
+  if (!status.has_value()) return nullptr;
+  TORCH_CHECK(status->is_cuda() && status->scalar_type() == torch::kInt32 && status->numel() >= 4, "status must be int32[4] on CUDA");
+  return status->data_ptr<int>();
+}
+
+// Operands are 2-D ([rows, cols]) or 3-D ([batch, rows, cols]) with a contiguous last dim.
+// a_kmajor: A is [.., M, K]; otherwise A is [.., K, M]. Same for B with N.
+void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor D, bool a_kmajor, bool b_kmajor, int64_t epi, double alpha, double beta,
+          double slope, c10::optional<torch::Tensor> aux, c10::optional<torch::Tensor> colscale, c10::optional<torch::Tensor> D2,
+          int64_t splits, c10::optional<torch::Tensor> status) {
+  check_bf16(A, "A");
+  check_bf16(B, "B");
+  TORCH_CHECK(A.dim() == B.dim() && A.dim() == D.dim() && (A.dim() == 2 || A.dim() == 3), "gemm: operands must all be 2-D or all 3-D");
+  TORCH_CHECK(A.stride(-1) == 1 && B.stride(-1) == 1 && D.stride(-1) == 1, "gemm: last dim must be contiguous");
+  const int nd = A.dim();
+  pgb::GemmArgs g;
+  g.batch = nd == 3 ? (int)A.size(0) : 1;
+  g.a_kmajor = a_kmajor;
+  g.b_kmajor = b_kmajor;
+  g.M = (int)(a_kmajor ? A.size(-2) : A.size(-1));
+  g.K = (int)(a_kmajor ? A.size(-1) : A.size(-2));
+  g.N = (int)(b_kmajor ? B.size(-2) : B.size(-1));
+  const int kb = (int)(b_kmajor ? B.size(-1) : B.size(-2));
+  TORCH_CHECK(kb == g.K, "gemm: reduction dims differ: ", g.K, " vs ", kb);
+  TORCH_CHECK(D.size(-2) == g.M && D.size(-1) == g.N, "gemm: D must be [M, N]");
+  if (nd == 3) TORCH_CHECK(B.size(0) == g.batch && D.size(0) == g.batch, "gemm: batch sizes differ");
+  g.A = A.data_ptr();
+  g.B = B.data_ptr();
+  g.D = D.data_ptr();
+  g.lda = A.stride(-2);
+  g.ldb = B.stride(-2);
+  g.ldd = D.stride(-2);
+  g.stride_a = nd == 3 ? A.stride(0) : 0;
+  g.stride_b = nd == 3 ? B.stride(0) : 0;
+  g.stride_d = nd == 3 ? D.stride(0) : 0;
+  g.epi = (int)epi;
+  const bool f32_out = (epi == pgb::EPI_F32 || epi == pgb::EPI_F32_ATOMIC);
+  TORCH_CHECK(D.scalar_type() == (f32_out ? torch::kFloat32 : torch::kBFloat16), "gemm: D dtype does not match the epilogue");
+  if (aux.has_value()) {
+    check_bf16(*aux, "aux");
+    TORCH_CHECK(aux->dim() == nd && aux->size(-2) == g.M && aux->size(-1) == g.N && aux->stride(-1) == 1, "gemm: aux must be [M, N]");
+    g.aux = aux->data_ptr();
+    g.ld_aux = aux->stride(-2);
+    g.stride_aux = nd == 3 ? aux->stride(0) : 0;
+  }
+  if (epi == pgb::EPI_AXPBY_BF16 || epi == pgb::EPI_RESID_BF16 || epi == pgb::EPI_MUL_ACTGRAD)
+    TORCH_CHECK(g.aux != nullptr, "gemm: this epilogue needs aux");
+  if (colscale.has_value()) {
+    TORCH_CHECK(colscale->is_cuda() && colscale->scalar_type() == torch::kFloat32 && colscale->numel() == g.N && colscale->is_contiguous(),
+                "gemm: colscale must be fp32[N]");
+    g.colscale = colscale->data_ptr<float>();
+  }
+  if (epi == pgb::EPI_RESID_BF16) TORCH_CHECK(g.colscale != nullptr, "gemm: residual epilogue needs colscale");
+  if (D2.has_value()) {
+    check_bf16(*D2, "D2");
+    TORCH_CHECK(D2->sizes() == D.sizes() && D2->strides() == D.strides(), "gemm: D2 must match D");
+    g.D2 = D2->data_ptr();
+  }
+  if (epi == pgb::EPI_ACT_SQ) TORCH_CHECK(g.D2 != nullptr, "gemm: activation epilogue needs D2");
+  g.alpha = (float)alpha;
+  g.beta = (float)beta;
+  g.slope = (float)slope;
+  g.splits = (int)splits;
+  g.status = status_ptr(status);
+  pgb::gemm_bf16(g, cur_stream());
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogue");
+#include "bindings_more.inc"
+}

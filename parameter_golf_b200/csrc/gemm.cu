@@ -1,0 +1,401 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM -> epilogue.
+//
+//   D[b][m][n] = epilogue( sum_k A[b][m][k] * B[b][n][k] )
+//
+// Both operands may be stored K-contiguous ("K-major", [rows][K]) or row-contiguous along M/N
+// ("MN-major", [K][rows]); the tensor core reads either through the shared-memory descriptor, so the
+// three GEMMs of a linear layer need no transposes:
+//   forward  Y = X W^T         A = X  [T][K]  K-major     B = W  [N][K]  K-major
+//   dX = dY W                  A = dY [T][N]  K-major     B = W  [N][K]  MN-major (reduction over N)
+//   dW = dY^T X                A = dY [T][N]  MN-major    B = X  [T][K]  MN-major (reduction over T, split-K)
+// It replaces the cuBLAS calls of the reference's GEMM engine
+// (parameter-golf-rs/crates/pg-kernels/src/gemm.rs:158-179,501-698) and the elementwise kernels that
+// follow them, which become epilogues here.
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs (one elected lane),
+// warps 2..5 read the accumulator back (tcgen05.ld, one row per thread) and run the epilogue. Two
+// accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
+// Tile 128 x BN x 64, BN in {128, 256}; grid = min(#tiles, #SMs); tile index = n fastest so CTAs
+// working at the same time share the rows of the large operand in L2.
+#include "common.cuh"
+#include "pgb.h"
+#include "tma_host.h"
+
+namespace pgb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmKernelParams {
+  int M, N, K, batch;
+  int tiles_m, tiles_n, splits, kb_per_split, kb_total;
+  long long ldd, stride_d;
+  long long ld_aux, stride_aux;
+  void* D;
+  void* D2;
+  const void* aux;
+  const float* colscale;
+  float alpha, beta, slope;
+  int* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float act_fn(float x, float slope) { return x >= 0.f ? x : slope * x; }
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b, int m, int n0, const uint32_t (&r)[32]) {
+  // One thread: row m, columns n0 .. n0+31 of batch b. Caller guarantees m < M.
+  const bool full = (n0 + 32 <= p.N);
+  const long long off = (long long)b * p.stride_d + (long long)m * p.ldd + n0;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+
+  if constexpr (EPI == EPI_F32 || EPI == EPI_F32_ATOMIC) {
+    float* d = reinterpret_cast<float*>(p.D) + off;
+    if (full && ((reinterpret_cast<uintptr_t>(d) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float4 q = make_float4(v[i] * p.alpha, v[i + 1] * p.alpha, v[i + 2] * p.alpha, v[i + 3] * p.alpha);
+        if constexpr (EPI == EPI_F32) *reinterpret_cast<float4*>(d + i) = q;
+        else atomicAdd(reinterpret_cast<float4*>(d + i), q);
+      }
+    } else {
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < p.N) {
+          if constexpr (EPI == EPI_F32) d[i] = v[i] * p.alpha;
+          else atomicAdd(d + i, v[i] * p.alpha);
+        }
+    }
+    return;
+  } else {
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + off;
+    const long long aoff = (long long)b * p.stride_aux + (long long)m * p.ld_aux + n0;
+    const bool vec = full && ((reinterpret_cast<uintptr_t>(d) & 15) == 0);
+    float a[32];
+    if constexpr (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD) {
+      const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + aoff;
+      if (vec && ((reinterpret_cast<uintptr_t>(ap) & 15) == 0)) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 q = *reinterpret_cast<const uint4*>(ap + i);
+          float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+          a[i] = f0.x; a[i + 1] = f0.y; a[i + 2] = f1.x; a[i + 3] = f1.y;
+          a[i + 4] = f2.x; a[i + 5] = f2.y; a[i + 6] = f3.x; a[i + 7] = f3.y;
+        }
+      } else {
+        for (int i = 0; i < 32; ++i) a[i] = (n0 + i < p.N) ? __bfloat162float(ap[i]) : 0.f;
+      }
+    }
+    float o[32];
+    float o2[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if constexpr (EPI == EPI_BF16) o[i] = v[i] * p.alpha;
+      if constexpr (EPI == EPI_AXPBY_BF16) o[i] = p.alpha * v[i] + p.beta * a[i];
+      if constexpr (EPI == EPI_RESID_BF16) o[i] = a[i] + ((n0 + i < p.N) ? p.colscale[n0 + i] : 0.f) * v[i];
+      if constexpr (EPI == EPI_ACT_SQ) {
+        // the pre-activation is stored in bf16 and the activation is computed from that stored value,
+        // so the backward pass (which reads it back) sees exactly the same argument
+        float h = __bfloat162float(__float2bfloat16(v[i]));
+        float t = act_fn(h, p.slope);
+        o[i] = h;
+        o2[i] = t * t;
+      }
+      if constexpr (EPI == EPI_MUL_ACTGRAD) {
+        float h = a[i];
+        o[i] = v[i] * 2.f * act_fn(h, p.slope) * (h >= 0.f ? 1.f : p.slope);
+      }
+    }
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8)
+        *reinterpret_cast<uint4*>(d + i) = make_uint4(pack_bf16x2(o[i], o[i + 1]), pack_bf16x2(o[i + 2], o[i + 3]),
+                                                      pack_bf16x2(o[i + 4], o[i + 5]), pack_bf16x2(o[i + 6], o[i + 7]));
+      if constexpr (EPI == EPI_ACT_SQ) {
+        __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(p.D2) + off;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8)
+          *reinterpret_cast<uint4*>(d2 + i) = make_uint4(pack_bf16x2(o2[i], o2[i + 1]), pack_bf16x2(o2[i + 2], o2[i + 3]),
+                                                         pack_bf16x2(o2[i + 4], o2[i + 5]), pack_bf16x2(o2[i + 6], o2[i + 7]));
+      }
+    } else {
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < p.N) {
+          d[i] = __float2bfloat16(o[i]);
+          if constexpr (EPI == EPI_ACT_SQ) (reinterpret_cast<__nv_bfloat16*>(p.D2) + off)[i] = __float2bfloat16(o2[i]);
+        }
+    }
+  }
+}
+
+template <int BN, bool A_KMAJOR, bool B_KMAJOR, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;            // 256 or 512: two accumulators
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::TILE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 128);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_batch = p.tiles_m * p.tiles_n * p.splits;
+  const int total_tiles = tiles_per_batch * p.batch;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int b = tile / tiles_per_batch;
+        int r = tile - b * tiles_per_batch;
+        const int split = r / (p.tiles_m * p.tiles_n);
+        r -= split * p.tiles_m * p.tiles_n;
+        const int tm = r / p.tiles_n, tn = r - tm * p.tiles_n;
+        const int m0 = tm * BM, n0 = tn * BN;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, kb)) { ok = false; break; }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          if constexpr (A_KMAJOR) {
+            tma_load_3d(sa, &map_a, &full_bar[stage], kb * BK, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * 8192, &map_a, &full_bar[stage], m0 + 64 * j, kb * BK, b);
+          }
+          if constexpr (B_KMAJOR) {
+            tma_load_3d(sb, &map_b, &full_bar[stage], kb * BK, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * 8192, &map_b, &full_bar[stage], n0 + 64 * j, kb * BK, b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // drain: every stage whose load may still be in flight
+        for (int s = 0; s < STAGES; ++s) mbar_drain(&full_bar[s], (s < stage) ? phase : (phase ^ 1));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC = make_idesc_bf16(BM, BN, A_KMAJOR ? 0 : 1, B_KMAJOR ? 0 : 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int r = tile % tiles_per_batch;
+        const int split = r / (p.tiles_m * p.tiles_n);
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, tile)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, ST_WAIT_FULL, kb)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_KMAJOR ? make_smem_desc(sa + k * 32, 16, 1024) : make_smem_desc(sa + k * 2048, 8192, 1024);
+            const uint64_t db = B_KMAJOR ? make_smem_desc(sb + k * 32, 16, 1024) : make_smem_desc(sb + k * 2048, 8192, 1024);
+            umma_ss(tmem_d, da, db, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;                 // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int b = tile / tiles_per_batch;
+      int r = tile - b * tiles_per_batch;
+      const int split = r / (p.tiles_m * p.tiles_n);
+      r -= split * p.tiles_m * p.tiles_n;
+      const int tm = r / p.tiles_n, tn = r - tm * p.tiles_n;
+      const int m = tm * BM + quarter * 32 + lane;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, ST_WAIT_TMEM_FULL, tile)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int n0 = tn * BN + c * 32;
+        if (n0 >= p.N) break;                     // warp-uniform
+        uint32_t rr[32];
+        PGB_TMEM_LD32(taddr + c * 32, rr);
+        tmem_wait_ld();
+        if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr);
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------------------------
+static int g_num_sms = 0;
+
+static int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+static CUtensorMap operand_map(const void* ptr, bool kmajor, int rows, int K, long long ld, long long batch_stride, int batch,
+                               int tile_rows) {
+  uint64_t dims[3];
+  uint64_t strides[2];
+  uint32_t box[3];
+  if (kmajor) {         // memory [batch][rows][K]
+    dims[0] = (uint64_t)K; dims[1] = (uint64_t)rows; dims[2] = (uint64_t)batch;
+    box[0] = BK; box[1] = (uint32_t)tile_rows; box[2] = 1;
+  } else {              // memory [batch][K][rows]
+    dims[0] = (uint64_t)rows; dims[1] = (uint64_t)K; dims[2] = (uint64_t)batch;
+    box[0] = 64; box[1] = BK; box[2] = 1;
+  }
+  strides[0] = (uint64_t)ld * 2;
+  strides[1] = (uint64_t)(batch > 1 ? batch_stride : (long long)dims[1] * ld) * 2;
+  return make_tmap_bf16(ptr, 3, dims, strides, box);
+}
+
+template <int BN, bool AK, bool BKM, int EPI>
+static void launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const GemmKernelParams& p, int grid, cudaStream_t stream) {
+  auto kern = gemm_tcgen05_kernel<BN, AK, BKM, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL);
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(ma, mb, p);
+}
+
+template <int BN, int EPI>
+static void launch_major(const GemmArgs& a, const CUtensorMap& ma, const CUtensorMap& mb, const GemmKernelParams& p, int grid,
+                         cudaStream_t stream) {
+  if (a.a_kmajor && a.b_kmajor) launch_variant<BN, true, true, EPI>(ma, mb, p, grid, stream);
+  else if (a.a_kmajor && !a.b_kmajor) launch_variant<BN, true, false, EPI>(ma, mb, p, grid, stream);
+  else if (!a.a_kmajor && a.b_kmajor) launch_variant<BN, false, true, EPI>(ma, mb, p, grid, stream);
+  else launch_variant<BN, false, false, EPI>(ma, mb, p, grid, stream);
+}
+
+template <int BN>
+static void launch_epi(const GemmArgs& a, const CUtensorMap& ma, const CUtensorMap& mb, const GemmKernelParams& p, int grid,
+                       cudaStream_t stream) {
+  switch (a.epi) {
+    case EPI_BF16: launch_major<BN, EPI_BF16>(a, ma, mb, p, grid, stream); break;
+    case EPI_F32: launch_major<BN, EPI_F32>(a, ma, mb, p, grid, stream); break;
+    case EPI_F32_ATOMIC: launch_major<BN, EPI_F32_ATOMIC>(a, ma, mb, p, grid, stream); break;
+    case EPI_AXPBY_BF16: launch_major<BN, EPI_AXPBY_BF16>(a, ma, mb, p, grid, stream); break;
+    case EPI_RESID_BF16: launch_major<BN, EPI_RESID_BF16>(a, ma, mb, p, grid, stream); break;
+    case EPI_ACT_SQ: launch_major<BN, EPI_ACT_SQ>(a, ma, mb, p, grid, stream); break;
+    case EPI_MUL_ACTGRAD: launch_major<BN, EPI_MUL_ACTGRAD>(a, ma, mb, p, grid, stream); break;
+    default: throw std::runtime_error("gemm: unknown epilogue");
+  }
+}
+
+void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) throw std::runtime_error("gemm: empty problem");
+  if ((a.lda % 8) || (a.ldb % 8)) throw std::runtime_error("gemm: leading dimensions must be multiples of 8 elements");
+  const int bn = (a.N > 128) ? 256 : 128;
+  GemmKernelParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
+  p.tiles_m = (a.M + BM - 1) / BM;
+  p.tiles_n = (a.N + bn - 1) / bn;
+  p.kb_total = (a.K + BK - 1) / BK;
+  int splits = a.splits;
+  if (splits <= 0) {
+    splits = 1;
+    if (a.epi == EPI_F32_ATOMIC) {        // fill the machine when the output is small and K is long
+      const int base = p.tiles_m * p.tiles_n * a.batch;
+      splits = std::max(1, std::min(p.kb_total / 8, (2 * num_sms() + base - 1) / base));
+    }
+  }
+  if (splits > 1 && a.epi != EPI_F32_ATOMIC) throw std::runtime_error("gemm: split-K needs the atomic fp32 epilogue");
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+  p.ldd = a.ldd; p.stride_d = a.stride_d;
+  p.ld_aux = a.ld_aux; p.stride_aux = a.stride_aux;
+  p.D = a.D; p.D2 = a.D2; p.aux = a.aux; p.colscale = a.colscale;
+  p.alpha = a.alpha; p.beta = a.beta; p.slope = a.slope;
+  p.status = a.status;
+  const CUtensorMap ma = operand_map(a.A, a.a_kmajor, a.M, a.K, a.lda, a.stride_a, a.batch, BM);
+  const CUtensorMap mb = operand_map(a.B, a.b_kmajor, a.N, a.K, a.ldb, a.stride_b, a.batch, bn);
+  const int total = p.tiles_m * p.tiles_n * p.splits * a.batch;
+  const int grid = std::min(total, num_sms());
+  if (bn == 256) launch_epi<256>(a, ma, mb, p, grid, stream);
+  else launch_epi<128>(a, ma, mb, p, grid, stream);
+}
+
+}  // namespace pgb

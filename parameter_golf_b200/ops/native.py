@@ -1,0 +1,64 @@
+"""Loader of the native extension and thin Python entry points over it.
+
+The extension is built in-tree (`parameter_golf_b200.ops.build`). On a machine with a GPU a missing or stale
+library is an error after one rebuild attempt: there is no fallback implementation of the CUDA ops.
+"""
+from __future__ import annotations
+
+import importlib
+import importlib.util
+import os
+
+import torch
+
+from . import build as _build
+
+_C = None
+
+EPI_BF16, EPI_F32, EPI_F32_ATOMIC, EPI_AXPBY_BF16, EPI_RESID_BF16, EPI_ACT_SQ, EPI_MUL_ACTGRAD = range(7)
+
+STATUS_NAMES = {0: "ok", 1: "wait_full", 2: "wait_empty", 3: "wait_tmem_full", 4: "wait_tmem_empty", 5: "wait_flag", 6: "bad_arg", 7: "wait_misc"}
+
+
+def load():
+    """Import (building if needed) and return the extension module."""
+    global _C
+    if _C is not None:
+        return _C
+    if not _build.is_current():
+        _build.build()
+    spec = importlib.util.spec_from_file_location("parameter_golf_b200._C", _build.LIB)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    _C = mod
+    return mod
+
+
+def available() -> bool:
+    return os.path.exists(_build.LIB)
+
+
+_status = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32[4] status word that bounded waits write to: [code, block, detail, count]."""
+    dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    if dev not in _status:
+        _status[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
+    return _status[dev]
+
+
+def check_status(device=None, reset: bool = True):
+    """Raise if any kernel recorded a timed-out wait since the last check (synchronises the device)."""
+    st = status_word(device)
+    code, block, detail, count = st.tolist()
+    if reset and code:
+        st.zero_()
+    if code:
+        raise RuntimeError(f"kernel wait timed out: {STATUS_NAMES.get(code, code)} (block {block}, detail {detail}, {count} reports)")
+
+
+def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.0, slope=0.0, aux=None, colscale=None, D2=None, splits=0):
+    load().gemm(A, B, D, a_kmajor, b_kmajor, epi, alpha, beta, slope, aux, colscale, D2, splits, status_word(A.device))
+    return D

@@ -1,0 +1,106 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference: operand majors, batch, split-K, every epilogue, ragged edges."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _n():
+    from parameter_golf_b200.ops import native
+    return native
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+def _ref(A, B, a_k, b_k):
+    Af = A.float() if a_k else A.float().transpose(-1, -2)
+    Bf = B.float() if b_k else B.float().transpose(-1, -2)
+    return Af @ Bf.transpose(-1, -2)
+
+
+def _close(got, ref, rel=1e-2):
+    err = (got.float() - ref).abs().max().item()
+    assert err <= rel * max(ref.abs().max().item(), 1e-3), f"max abs err {err} vs ref max {ref.abs().max().item()}"
+
+
+@pytest.mark.parametrize("a_k,b_k", [(True, True), (True, False), (False, True), (False, False)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (384, 512, 192), (200, 136, 72), (128, 1024, 512), (1000, 64, 64)])
+def test_gemm_majors_and_ragged_shapes(a_k, b_k, M, N, K):
+    n = _n()
+    torch.manual_seed(M + N + K)
+    A = _rand(M, K) if a_k else _rand(K, M)
+    B = _rand(N, K) if b_k else _rand(K, N)
+    D = torch.full((M, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    n.gemm(A, B, D, a_k, b_k)
+    torch.cuda.synchronize()
+    n.check_status()
+    _close(D, _ref(A, B, a_k, b_k))
+
+
+def test_gemm_batched_strided_and_fp32_out():
+    n = _n()
+    A, B = _rand(5, 256, 320), _rand(5, 384, 320)
+    D = torch.empty(5, 256, 384, device="cuda", dtype=torch.float32)
+    n.gemm(A, B, D, True, True, n.EPI_F32, alpha=0.5)
+    torch.cuda.synchronize()
+    n.check_status()
+    _close(D, 0.5 * _ref(A, B, True, True), 3e-3)
+    big = _rand(4, 256, 640)                      # batch stride larger than rows*cols, row stride larger than K
+    Av = big[:, :, :320]
+    D2 = torch.empty(4, 256, 384, device="cuda", dtype=torch.bfloat16)
+    n.gemm(Av, B[:4], D2, True, True)
+    torch.cuda.synchronize()
+    _close(D2, _ref(Av, B[:4], True, True))
+
+
+@pytest.mark.parametrize("splits", [0, 1, 3, 8])
+def test_split_k_weight_gradient_accumulates(splits):
+    """dW[N,K] += dY^T X: both operands row-contiguous along the output dims, reduction over tokens."""
+    n = _n()
+    T, N, K = 4096, 256, 192
+    dY, X = _rand(T, N, scale=0.1), _rand(T, K)
+    dW = torch.ones(N, K, device="cuda", dtype=torch.float32)
+    n.gemm(dY, X, dW, False, False, n.EPI_F32_ATOMIC, splits=splits)
+    n.gemm(dY, X, dW, False, False, n.EPI_F32_ATOMIC, splits=splits)
+    torch.cuda.synchronize()
+    n.check_status()
+    _close(dW, 1.0 + 2.0 * (dY.float().t() @ X.float()), 3e-3)
+
+
+def test_epilogue_axpby_residual_activation():
+    n = _n()
+    M, N, K = 384, 512, 256
+    A, B, aux = _rand(M, K), _rand(N, K, scale=0.1), _rand(M, N)
+    ref = _ref(A, B, True, True)
+    D = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    n.gemm(A, B, D, epi=n.EPI_AXPBY_BF16, alpha=0.7, beta=-1.3, aux=aux)
+    _close(D, 0.7 * ref - 1.3 * aux.float())
+    cs = torch.randn(N, device="cuda")
+    n.gemm(A, B, D, epi=n.EPI_RESID_BF16, aux=aux, colscale=cs)
+    _close(D, aux.float() + cs[None, :] * ref)
+    H, Act = torch.empty_like(D), torch.empty_like(D)
+    n.gemm(A, B, H, epi=n.EPI_ACT_SQ, slope=0.5, D2=Act)
+    _close(H, ref)
+    _close(Act, torch.nn.functional.leaky_relu(H.float(), 0.5) ** 2, 1e-2)
+    G = torch.empty_like(D)
+    n.gemm(A, B, G, epi=n.EPI_MUL_ACTGRAD, slope=0.5, aux=aux)
+    h = aux.float()
+    _close(G, ref * 2 * torch.nn.functional.leaky_relu(h, 0.5) * torch.where(h >= 0, 1.0, 0.5))
+    n.gemm(A, B, Act, epi=n.EPI_ACT_SQ, slope=0.0, D2=G)           # relu^2
+    _close(G, torch.relu(Act.float()) ** 2)
+    torch.cuda.synchronize()
+    n.check_status()
+
+
+def test_many_tiles_persistent_schedule_matches():
+    """More tiles than SMs so every CTA loops over several tiles and both accumulators are used."""
+    n = _n()
+    M, N, K = 128 * 40, 1024, 512
+    A, B = _rand(M, K), _rand(N, K, scale=0.05)
+    D = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    n.gemm(A, B, D)
+    torch.cuda.synchronize()
+    n.check_status()
+    _close(D, _ref(A, B, True, True))

@@ -39,4 +39,43 @@ struct GemmArgs {
 
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
 
+// ---- row kernels (rowops.cu); activations bf16, parameters fp32 ------------------------------------------------
+void mix_norm_fwd(const void* x, const void* x0, const void* skip, const float* sw, const float* mix, void* x_in, void* h, int rows, int d, float s,
+                  float eps, cudaStream_t st);
+void mix_norm_bwd(const void* d_h, const void* d_res, const void* x_in, const void* x, const void* x0, const void* skip, const float* sw,
+                  const float* mix, const void* add_grad, void* d_x, void* d_x0, void* d_skip, float* d_mix, float* d_sw, int skip_to_dx, int rows,
+                  int d, float s, float eps, cudaStream_t st);
+void norm_smear_fwd(const void* xe, const float* gate, const int* ids, void* out, int rows, int d, int seq_len, int boundary, float eps,
+                    cudaStream_t st);
+void norm_smear_bwd(const void* g_out, const void* xe, const float* gate, const int* ids, void* d_xe, float* d_gate, int rows, int d, int seq_len,
+                    int boundary, float eps, cudaStream_t st);
+void qk_norm_rope_fwd(const void* src, void* dst, const float* cosT, const float* sinT, const float* gain, int rows, int ld, int H, int Hkv, int hd,
+                      int rope_dims, int seq_len, float eps, cudaStream_t st);
+void qk_norm_rope_bwd(const void* d_post, const void* pre, void* d_pre, const float* cosT, const float* sinT, const float* gain, float* d_gain,
+                      int rows, int ld, int H, int Hkv, int hd, int rope_dims, int seq_len, float eps, cudaStream_t st);
+void xsa_fwd(const void* y, const void* v, void* z, int rows, int Hkv, int group, int hd, int ld_y, int ld_v, float eps, cudaStream_t st);
+void xsa_bwd(const void* dz, const void* y, const void* v, void* dy, void* dv, int accumulate_dv, int rows, int Hkv, int group, int hd, int ld_y,
+             int ld_v, int ld_dv, float eps, cudaStream_t st);
+void softcap_ce(const void* logits, const int* targets, float* nll, void* dlogits, float* loss_sum, int rows, int V, float cap, float gscale,
+                cudaStream_t st);
+void embed_gather(const int* ids, const void* table, void* out, int rows, int d, int bigram_buckets, int seq_len, cudaStream_t st);
+void embed_scatter_add(const int* ids, const void* g, float* dtable, int rows, int d, int table_rows, int bigram_buckets, int seq_len,
+                       cudaStream_t st);
+
+// ---- optimizer / weight preparation (optim.cu) --------------------------------------------------------------------------
+// hp: device fp32[8] = {lr_scale, muon_momentum, adam_bias_corr1, adam_bias_corr2, grad_scale, ...}
+void cast_rows(const float* src, void* dst, const float* rowscale, int scale_stride, int scale_mod, int rows, int cols, long long ld_dst, int qat,
+               cudaStream_t st);
+void fold_scaled_grad(const float* G, const float* W, const float* rowscale, int scale_stride, int scale_mod, float* dW, float* dscale, int rows,
+                      int cols, int qat, cudaStream_t st);
+void sumsq(const float* x, long long n, float scale, float* out, cudaStream_t st);
+void clip_factor(float* stats, float* hp, float base_scale, float max_norm, cudaStream_t st);
+void muon_momentum(const float* g, float* buf, void* U, float* sumsq_out, const float* hp, int matrices, long long per_matrix, int nesterov,
+                   cudaStream_t st);
+void muon_normalize(const void* U, void* X, const float* sumsq_in, int matrices, long long per_matrix, float eps, cudaStream_t st);
+void muon_apply(float* p, const void* X, float* ema, const float* hp, long long n, float base_lr, float wd, float scale, float decay, cudaStream_t st);
+void adamw(float* p, const float* g, float* m, float* v, float* ema, const float* hp, long long n, float base_lr, float b1, float b2, float eps,
+           float wd, float decay, cudaStream_t st);
+void sgd_momentum(float* p, const float* g, float* mom, const float* hp, long long n, float lr, float mu, cudaStream_t st);
+
 }  // namespace pgb

@@ -1,0 +1,604 @@
+"""CUDA engine: explicit forward, backward and optimizer step on the sm_100a kernels.
+
+One engine instance owns, on one GPU: fp32 master parameters (banks + flat Adam groups), their
+gradients, bf16 compute copies of the weights, and every saved activation of one micro-batch. The
+forward/backward is written out kernel by kernel (no autograd), following the block structure of
+``parameter-golf-rs/crates/pg-model/src/gpu.rs:6041-6908`` (forward) and ``:4558-5918`` (backward), but with
+one execution path per op and the element-wise work folded into GEMM epilogues and fused row kernels:
+
+* residual-mix + RMSNorm, RMSNorm-backward + mix/skip backward: one row kernel each;
+* O and MLP-down projections carry the residual add in their epilogue; their per-feature output
+  scales (``attn_scale``, ``mlp_scale``) are folded into the bf16 weight copies at cast time, and the
+  scale gradients are recovered from the un-scaled weight gradient (``d_scale[n] = sum_k W[n,k] G[n,k]``);
+* MLP-up stores the pre-activation and ``leaky_relu(.)^2`` from one accumulator read; the
+  down-projection's dX GEMM multiplies by the activation derivative in its epilogue;
+* tied-embedding logits are produced in bf16 and overwritten in place by their gradient in the
+  soft-capped cross-entropy kernel.
+
+Gradients of bf16 activations are bf16; weight gradients accumulate in fp32 across micro-batches.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..ops import native as N
+from ..ops import reference as R
+from ..optim.muon import ns_coeff
+from ..spec import ModelSpec, RunSpec
+from . import gpt
+
+BF = torch.bfloat16
+EMB_NAMES = ("tok_emb", "bigram_embed", "ve_embed")
+
+
+def _unsupported(m: ModelSpec) -> Optional[str]:
+    if m.recurrence.enabled:
+        return "recurrence"
+    if m.parallel_residual.enabled:
+        return "parallel_residual"
+    if m.attn_out_gate.enabled or m.sparse_attn_gate.enabled:
+        return "attention gates"
+    if not m.tie_embeddings:
+        return "untied lm_head"
+    if m.model_dim % 64 or m.kv_dim % 64 or m.mlp_dim % 64 or m.head_dim % 8 or m.vocab_size % 64:
+        return "dims that are not multiples of 64"
+    if m.bigram.enabled and (m.bigram.dim % 64 or m.bigram.dim == m.model_dim):
+        return "bigram dim not a multiple of 64 (or equal to model_dim)"
+    return None
+
+
+class CudaEngine:
+    def __init__(self, spec: RunSpec, params: Dict[str, torch.Tensor], device, micro_batch: int, seq_len: int, train: bool = True,
+                 attention: str = "sdpa"):
+        bad = _unsupported(spec.model)
+        if bad:
+            raise NotImplementedError(f"the CUDA engine does not cover {bad}; use the cpu backend for this variant")
+        self.C = N.load()
+        self.spec, self.m, self.t = spec, spec.model, spec.train
+        self.dev = torch.device(device)
+        self.B, self.S = micro_batch, seq_len
+        self.T = micro_batch * seq_len
+        self.train = train
+        self.attention = attention
+        self.qat = False
+        m = self.m
+        self.n, self.d, self.kv, self.mlp, self.H, self.Hkv, self.hd = m.num_layers, m.model_dim, m.kv_dim, m.mlp_dim, m.num_heads, m.num_kv_heads, m.head_dim
+        self.qkvw = self.d + 2 * self.kv
+        self.slope = m.leaky_slope if m.activation == "leaky_relu_sq" else 0.0
+        self.enc = self.n // 2
+        self.unet = m.skip_topology == "unet" and "skip_weights" in params
+        self.eps = R.RMS_EPS
+        self._alloc_params(params)
+        self._alloc_acts()
+        self.hp_host = torch.zeros(8, dtype=torch.float32).pin_memory()
+        self.hp = torch.zeros(8, dtype=torch.float32, device=self.dev)
+        self.hp_host[0], self.hp_host[4] = 1.0, 1.0
+        self.hp.copy_(self.hp_host)
+        self.stats = torch.zeros(4, dtype=torch.float32, device=self.dev)
+        self.loss_sum = torch.zeros(1, dtype=torch.float32, device=self.dev)
+        self.adam_t = 0
+        self.launches = 0
+        self.cast_weights()
+
+    # ---- storage -----------------------------------------------------------------------------------------------
+    def _alloc_params(self, params):
+        dev, m = self.dev, self.m
+        shapes = gpt.param_shapes(m)
+        self.p: Dict[str, torch.Tensor] = {}
+        self.g: Dict[str, torch.Tensor] = {}
+        for k in gpt.BANKS:
+            self.p[k] = params[k].detach().to(dev, torch.float32).contiguous()
+            if self.train:
+                self.g[k] = torch.zeros_like(self.p[k])
+        emb = [k for k in EMB_NAMES if k in shapes]
+        sca = [k for k in shapes if k not in gpt.BANKS and k not in emb]
+        self.groups = []
+        for names, lr in ((emb, self.t.tied_embed_lr if m.tie_embeddings else self.t.embed_lr), (sca, self.t.scalar_lr)):
+            total = sum(-(-math.prod(shapes[k]) // 4) * 4 for k in names)
+            flat_p = torch.zeros(total, dtype=torch.float32, device=dev)
+            flat_g = torch.zeros(total, dtype=torch.float32, device=dev) if self.train else None
+            off = 0
+            for k in names:
+                nel = math.prod(shapes[k])
+                self.p[k] = flat_p[off:off + nel].view(shapes[k])
+                self.p[k].copy_(params[k].detach().to(dev, torch.float32))
+                if self.train:
+                    self.g[k] = flat_g[off:off + nel].view(shapes[k])
+                off += -(-nel // 4) * 4
+            grp = {"names": names, "lr": lr, "p": flat_p, "g": flat_g}
+            if self.train:
+                grp["m"], grp["v"] = torch.zeros_like(flat_p), torch.zeros_like(flat_p)
+            self.groups.append(grp)
+        n, d, kv, mlp = self.n, self.d, self.kv, self.mlp
+        self.Wqkv = torch.empty(n, self.qkvw, d, dtype=BF, device=dev)
+        self.Wo = torch.empty(n, d, d, dtype=BF, device=dev)
+        self.Wup = torch.empty(n, mlp, d, dtype=BF, device=dev)
+        self.Wd = torch.empty(n, d, mlp, dtype=BF, device=dev)
+        self.E = torch.empty(m.vocab_size, d, dtype=BF, device=dev)
+        if m.bigram.enabled:
+            self.BE = torch.empty(m.bigram.vocab_size, m.bigram.dim, dtype=BF, device=dev)
+            self.BP = torch.empty(d, m.bigram.dim, dtype=BF, device=dev)
+        if m.value_embedding.enabled:
+            ve = m.value_embedding
+            self.VE = torch.empty(m.vocab_size, ve.dim, dtype=BF, device=dev)
+            self.VP = torch.empty(len(ve.layers), kv, ve.dim, dtype=BF, device=dev)
+            self.ve_eff = torch.zeros(len(ve.layers), dtype=torch.float32, device=dev)
+        if self.train:
+            self.ema: Optional[Dict[str, torch.Tensor]] = None
+            self.mom = {k: torch.zeros_like(self.p[k]) for k in gpt.BANKS}
+            self.ns = {}
+            for k in gpt.BANKS:
+                Bk, Mk, Nk = self.p[k].shape
+                r = min(Mk, Nk)
+                self.ns[k] = {"U": torch.empty(Bk, Mk, Nk, dtype=BF, device=dev), "X0": torch.empty(Bk, Mk, Nk, dtype=BF, device=dev),
+                              "X1": torch.empty(Bk, Mk, Nk, dtype=BF, device=dev), "A": torch.empty(Bk, r, r, dtype=BF, device=dev),
+                              "Bm": torch.empty(Bk, r, r, dtype=BF, device=dev), "sq": torch.zeros(Bk, dtype=torch.float32, device=dev)}
+            self.Gd = torch.zeros(d, mlp, dtype=torch.float32, device=dev)
+            self.Go = torch.zeros(d, d, dtype=torch.float32, device=dev)
+            if m.bigram.enabled:
+                self.Gbp = torch.zeros(d, m.bigram.dim, dtype=torch.float32, device=dev)
+            if m.value_embedding.enabled:
+                self.Gvp = torch.zeros(kv, m.value_embedding.dim, dtype=torch.float32, device=dev)
+
+    def _alloc_acts(self):
+        dev, T, d, n = self.dev, self.T, self.d, self.n
+
+        def buf(*shape, dtype=BF):
+            return torch.empty(*shape, dtype=dtype, device=dev)
+
+        m = self.m
+        self.ids = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.tgt = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.e = buf(T, d)
+        self.xe = buf(T, d) if m.bigram.enabled else self.e
+        if m.bigram.enabled:
+            self.bg = buf(T, m.bigram.dim)
+        if m.value_embedding.enabled:
+            self.ve_e = buf(T, m.value_embedding.dim)
+        self.x0 = buf(T, d)
+        L = n if self.train else 1           # inference reuses one layer's worth of buffers
+
+        def per_layer(*shape):
+            return [buf(*shape) for _ in range(L)]
+
+        self.x_in, self.h = per_layer(T, d), per_layer(T, d)
+        self.qkv_pre, self.qk_post = per_layer(T, self.qkvw), per_layer(T, self.qkvw)
+        self.y, self.x_mid, self.mm = per_layer(T, d), per_layer(T, d), per_layer(T, d)
+        self.z = [buf(T, d) if (self.train and i in m.xsa_layers()) or (not self.train and i == 0 and m.xsa_last_n > 0) else None for i in range(L)]
+        self.hu, self.a = per_layer(T, self.mlp), per_layer(T, self.mlp)
+        self.x_out = [buf(T, d) for _ in range(n)]
+        self.lse = [None] * L
+        self.hf = buf(T, d)
+        self.logits = buf(T, m.vocab_size)
+        self.nll = buf(T, dtype=torch.float32)
+        rd = m.rope_dims
+        if rd > 0:
+            cos, sin = R.rope_tables(self.S, rd, m.rope.base, train_seq_len=1024)
+            self.cos, self.sin = cos.contiguous().to(dev), sin.contiguous().to(dev)
+        else:
+            self.cos = self.sin = None
+        if self.train:
+            self.dx, self.dx_mid, self.d_m, self.d_z, self.d_y, self.d_h = (buf(T, d) for _ in range(6))
+            self.d_hu = buf(T, self.mlp)
+            self.d_qk_post, self.d_qkv_pre = buf(T, self.qkvw), buf(T, self.qkvw)
+            self.d_x0 = buf(T, d)
+            self.d_skip = [buf(T, d) for _ in range(max(self.enc - 1, 0))] if self.unet else []
+            self.d_xe = buf(T, d)
+            if m.bigram.enabled:
+                self.d_bg = buf(T, m.bigram.dim)
+
+    # ---- weights --------------------------------------------------------------------------------------------------
+    def cast_weights(self):
+        """fp32 master -> bf16 compute copies (packed QKV, output scales folded in, optional int6 fake-quant)."""
+        C, p, n, d, kv = self.C, self.p, self.n, self.d, self.kv
+        q = self.qat
+        for i in range(n):       # packed [q; k; v] rows per layer
+            C.cast_rows(p["qo_bank"][i], self.Wqkv[i, :d], None, 0, 1, q)
+            C.cast_rows(p["kv_bank"][i], self.Wqkv[i, d:d + kv], None, 0, 1, q)
+            C.cast_rows(p["kv_bank"][n + i], self.Wqkv[i, d + kv:], None, 0, 1, q)
+        self.launches += 3 * n
+        C.cast_rows(p["qo_bank"][n:], self.Wo, p["attn_scale"], 1, n * d, q)
+        C.cast_rows(p["mlp_up_bank"], self.Wup, None, 0, 1, q)
+        C.cast_rows(p["mlp_down_bank"], self.Wd, p["mlp_scale"], 1, n * d, q)
+        C.cast_rows(p["tok_emb"], self.E, None, 0, 1, False)
+        self.launches += 4
+        if self.m.bigram.enabled:
+            C.cast_rows(p["bigram_embed"], self.BE, None, 0, 1, False)
+            C.cast_rows(p["bigram_proj"], self.BP, p["bigram_scale"], 0, 1, False)
+            self.launches += 2
+        if self.m.value_embedding.enabled:
+            C.cast_rows(p["ve_embed"], self.VE, None, 0, 1, False)
+            torch.mul(p["ve_layer_scales"], p["ve_scale"], out=self.ve_eff)
+            for li in range(self.VP.shape[0]):
+                C.cast_rows(p["ve_proj"], self.VP[li], self.ve_eff[li:li + 1], 0, 1, False)
+
+    def params_changed(self):
+        self.cast_weights()
+
+    # ---- attention -----------------------------------------------------------------------------------------------------
+    def _attn_fwd(self, l, li):
+        d, kv, B, S, H, Hkv, hd = self.d, self.kv, self.B, self.S, self.H, self.Hkv, self.hd
+        q = self.qk_post[li][:, :d]
+        k = self.qk_post[li][:, d:d + kv]
+        v = self.qkv_pre[li][:, d + kv:]
+        if self.attention == "native":
+            self.lse[li] = N.attn_fwd(q, k, v, self.y[li], B, S, H, Hkv, hd, self.lse[li])
+            return
+        q4 = q.reshape(B, S, H, hd).transpose(1, 2)
+        k4 = k.reshape(B, S, Hkv, hd).transpose(1, 2)
+        v4 = v.reshape(B, S, Hkv, hd).transpose(1, 2)
+        out = torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=(H != Hkv))
+        self.y[li].copy_(out.transpose(1, 2).reshape(self.T, d))
+
+    def _attn_bwd(self, l):
+        d, kv, B, S, H, Hkv, hd = self.d, self.kv, self.B, self.S, self.H, self.Hkv, self.hd
+        q = self.qk_post[l][:, :d]
+        k = self.qk_post[l][:, d:d + kv]
+        v = self.qkv_pre[l][:, d + kv:]
+        dq, dk = self.d_qk_post[:, :d], self.d_qk_post[:, d:d + kv]
+        dv = self.d_qkv_pre[:, d + kv:]
+        xsa = l in self.m.xsa_layers()
+        if self.attention == "native":
+            N.attn_bwd(q, k, v, self.y[l], self.d_y, self.lse[l], dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=xsa)
+            return
+        with torch.enable_grad():
+            q4 = q.reshape(B, S, H, hd).transpose(1, 2).detach().requires_grad_(True)
+            k4 = k.reshape(B, S, Hkv, hd).transpose(1, 2).detach().requires_grad_(True)
+            v4 = v.reshape(B, S, Hkv, hd).transpose(1, 2).detach().requires_grad_(True)
+            out = torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=(H != Hkv))
+            gq, gk, gv = torch.autograd.grad(out, (q4, k4, v4), self.d_y.reshape(B, S, H, hd).transpose(1, 2))
+        dq.copy_(gq.transpose(1, 2).reshape(self.T, d))
+        dk.copy_(gk.transpose(1, 2).reshape(self.T, kv))
+        if xsa:
+            dv.add_(gv.transpose(1, 2).reshape(self.T, kv))
+        else:
+            dv.copy_(gv.transpose(1, 2).reshape(self.T, kv))
+
+    # ---- forward -------------------------------------------------------------------------------------------------------------
+    def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor], gscale: float = 0.0, want_grad: bool = False):
+        """Runs the model on one micro-batch. With ``want_grad`` the logits buffer ends up holding
+        ``gscale * dL/dlogits``. Per-token NLL lands in ``self.nll``; the sum is added to ``self.loss_sum``."""
+        C, m, p = self.C, self.m, self.p
+        d, kv, S = self.d, self.kv, self.S
+        self.ids.copy_(ids.reshape(-1))
+        if targets is not None:
+            self.tgt.copy_(targets.reshape(-1))
+        C.embed_gather(self.ids, self.E, self.e, 0, S)
+        if m.bigram.enabled:
+            C.embed_gather(self.ids, self.BE, self.bg, m.bigram.vocab_size, S)
+            N.gemm(self.bg, self.BP, self.xe, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.e)
+        if m.value_embedding.enabled:
+            C.embed_gather(self.ids, self.VE, self.ve_e, 0, S)
+        bid = m.smear_gate_boundary_token_id
+        C.norm_smear_fwd(self.xe, p["smear_gate"] if m.smear_gate else None, self.ids if (m.smear_gate and bid is not None) else None, self.x0,
+                         S, -1 if bid is None else bid, self.eps)
+        x = self.x0
+        skips: List[torch.Tensor] = []
+        xsa_layers = m.xsa_layers()
+        for l in range(self.n):
+            li = l if self.train else 0
+            s_l = gpt.layer_ln_scale(m, l)
+            skip = sw = None
+            if self.unet and l >= self.enc and skips:
+                skip, sw = skips.pop(), p["skip_weights"][l - self.enc]
+            C.mix_norm_fwd(x, self.x0, skip, sw, p["resid_mix"][l], self.x_in[li], self.h[li], s_l, self.eps)
+            N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li])
+            if m.value_embedding.enabled and l in m.value_embedding.layers:
+                vi = m.value_embedding.layers.index(l)
+                vview = self.qkv_pre[li][:, d + kv:]
+                N.gemm(self.ve_e, self.VP[vi], vview, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=vview)
+            C.qk_norm_rope_fwd(self.qkv_pre[li], self.qk_post[li], self.cos, self.sin, p["q_gain"][l], self.H, self.Hkv, self.hd, m.rope_dims, S, self.eps)
+            self._attn_fwd(l, li)
+            zz = self.y[li]
+            if l in xsa_layers:
+                zz = self.z[li]
+                C.xsa_fwd(self.y[li], self.qkv_pre[li][:, d + kv:], zz, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+            N.gemm(zz, self.Wo[l], self.x_mid[li], epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.x_in[li])
+            C.mix_norm_fwd(self.x_mid[li], None, None, None, None, None, self.mm[li], s_l, self.eps)
+            N.gemm(self.mm[li], self.Wup[l], self.hu[li], epi=N.EPI_ACT_SQ, slope=self.slope, D2=self.a[li])
+            xo = self.x_out[l]
+            N.gemm(self.a[li], self.Wd[l], xo, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.x_mid[li])
+            x = xo
+            if self.unet and l < self.enc:
+                skips.append(x)
+        self.x_last = x
+        C.mix_norm_fwd(x, None, None, None, None, None, self.hf, 1.0, self.eps)
+        N.gemm(self.hf, self.E, self.logits)
+        if targets is not None:
+            C.softcap_ce(self.logits, self.tgt, self.nll, self.logits if want_grad else None, self.loss_sum, m.logit_softcap, gscale)
+
+    # ---- backward ---------------------------------------------------------------------------------------------------------------
+    def backward(self):
+        """Consumes the logits gradient left by `forward(..., want_grad=True)`; accumulates into ``self.g``."""
+        C, m, p, g = self.C, self.m, self.p, self.g
+        n, d, kv, S = self.n, self.d, self.kv, self.S
+        A = N.EPI_F32_ATOMIC
+        N.gemm(self.logits, self.E, self.d_h, True, False)                               # d_hf
+        N.gemm(self.logits, self.hf, g["tok_emb"], False, False, A)
+        C.mix_norm_bwd(self.d_h, None, self.x_last, None, None, None, None, None, None, self.dx, None, None, None, None, False, 1.0, self.eps)
+        self.d_x0.zero_()
+        xsa_layers = m.xsa_layers()
+        for l in range(n - 1, -1, -1):
+            s_l = gpt.layer_ln_scale(m, l)
+            # ---- MLP
+            self.Gd.zero_()
+            N.gemm(self.dx, self.a[l], self.Gd, False, False, A)
+            C.fold_scaled_grad(self.Gd, p["mlp_down_bank"][l], p["mlp_scale"][l], 1, d, g["mlp_down_bank"][l], g["mlp_scale"][l], self.qat)
+            N.gemm(self.dx, self.Wd[l], self.d_hu, True, False, N.EPI_MUL_ACTGRAD, slope=self.slope, aux=self.hu[l])
+            N.gemm(self.d_hu, self.mm[l], g["mlp_up_bank"][l], False, False, A)
+            N.gemm(self.d_hu, self.Wup[l], self.d_m, True, False)
+            C.mix_norm_bwd(self.d_m, self.dx, self.x_mid[l], None, None, None, None, None, None, self.dx_mid, None, None, None, None, False, s_l, self.eps)
+            # ---- attention output projection
+            zz = self.z[l] if l in xsa_layers else self.y[l]
+            self.Go.zero_()
+            N.gemm(self.dx_mid, zz, self.Go, False, False, A)
+            C.fold_scaled_grad(self.Go, p["qo_bank"][n + l], p["attn_scale"][l], 1, d, g["qo_bank"][n + l], g["attn_scale"][l], self.qat)
+            vview = self.qkv_pre[l][:, d + kv:]
+            dv = self.d_qkv_pre[:, d + kv:]
+            if l in xsa_layers:
+                N.gemm(self.dx_mid, self.Wo[l], self.d_z, True, False)
+                C.xsa_bwd(self.d_z, self.y[l], vview, self.d_y, dv, False, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+            else:
+                N.gemm(self.dx_mid, self.Wo[l], self.d_y, True, False)
+            self._attn_bwd(l)
+            C.qk_norm_rope_bwd(self.d_qk_post, self.qkv_pre[l], self.d_qkv_pre, self.cos, self.sin, p["q_gain"][l], g["q_gain"][l], self.H, self.Hkv,
+                               self.hd, m.rope_dims, S, self.eps)
+            if m.value_embedding.enabled and l in m.value_embedding.layers:
+                vi = m.value_embedding.layers.index(l)
+                self.Gvp.zero_()
+                N.gemm(dv, self.ve_e, self.Gvp, False, False, A)                         # d(ve_eff * ve_proj)
+                ds = (self.Gvp * p["ve_proj"]).sum()
+                g["ve_proj"].add_(self.Gvp * self.ve_eff[vi])
+                g["ve_layer_scales"][vi] += ds * p["ve_scale"][0]
+                g["ve_scale"][0] += ds * p["ve_layer_scales"][vi]
+                if not hasattr(self, "d_ve_e"):
+                    self.d_ve_e = torch.empty_like(self.ve_e)
+                    self.d_ve_acc = torch.zeros_like(self.ve_e, dtype=torch.float32)
+                N.gemm(dv, self.VP[vi], self.d_ve_e, True, False)
+                self.d_ve_acc.add_(self.d_ve_e)
+            N.gemm(self.d_qkv_pre[:, :d], self.h[l], g["qo_bank"][l], False, False, A)
+            N.gemm(self.d_qkv_pre[:, d:d + kv], self.h[l], g["kv_bank"][l], False, False, A)
+            N.gemm(dv, self.h[l], g["kv_bank"][n + l], False, False, A)
+            N.gemm(self.d_qkv_pre, self.Wqkv[l], self.d_h, True, False)
+            # ---- block input: RMSNorm backward, residual mix, U-Net skip
+            x_prev = self.x_out[l - 1] if l > 0 else self.x0
+            skip = sw = d_skip = d_sw = add_grad = None
+            self_pair = False
+            if self.unet and l >= self.enc and (2 * self.enc - 1 - l) >= 0:
+                e_idx = 2 * self.enc - 1 - l                     # encoder layer whose output this decoder layer consumed
+                skip, sw, d_sw = self.x_out[e_idx], p["skip_weights"][l - self.enc], g["skip_weights"][l - self.enc]
+                self_pair = e_idx == l - 1
+                if not self_pair:
+                    d_skip = self.d_skip[e_idx]
+            if self.unet and 1 <= l <= self.enc - 1:
+                add_grad = self.d_skip[l - 1]                     # the layer below is an encoder layer with a (non-adjacent) skip consumer
+            C.mix_norm_bwd(self.d_h, self.dx_mid, self.x_in[l], x_prev, self.x0, skip, sw, p["resid_mix"][l], add_grad, self.dx, self.d_x0, d_skip,
+                           g["resid_mix"][l], d_sw, self_pair, s_l, self.eps)
+        self.dx.add_(self.d_x0)
+        bid = m.smear_gate_boundary_token_id
+        C.norm_smear_bwd(self.dx, self.xe, p["smear_gate"] if m.smear_gate else None, self.ids if (m.smear_gate and bid is not None) else None,
+                         self.d_xe, g["smear_gate"] if m.smear_gate else None, S, -1 if bid is None else bid, self.eps)
+        C.embed_scatter_add(self.ids, self.d_xe, g["tok_emb"], 0, S)
+        if m.bigram.enabled:
+            self.Gbp.zero_()
+            N.gemm(self.d_xe, self.bg, self.Gbp, False, False, A)
+            C.fold_scaled_grad(self.Gbp, p["bigram_proj"], p["bigram_scale"], 0, 1, g["bigram_proj"], g["bigram_scale"], False)
+            N.gemm(self.d_xe, self.BP, self.d_bg, True, False)
+            C.embed_scatter_add(self.ids, self.d_bg, g["bigram_embed"], m.bigram.vocab_size, S)
+        if m.value_embedding.enabled and hasattr(self, "d_ve_acc"):
+            self.d_ve_e.copy_(self.d_ve_acc)
+            self.d_ve_acc.zero_()
+            C.embed_scatter_add(self.ids, self.d_ve_e, g["ve_embed"], 0, S)
+
+    # ---- public pieces -----------------------------------------------------------------------------------------------------------
+    def zero_grads(self):
+        for k in gpt.BANKS:
+            self.g[k].zero_()
+        for grp in self.groups:
+            grp["g"].zero_()
+        self.loss_sum.zero_()
+
+    def micro_step(self, ids, targets, accum: int):
+        """One micro-batch forward+backward; gradients are scaled so that `accum` of them sum to the mean."""
+        self.forward(ids, targets, gscale=1.0 / (self.T * accum), want_grad=True)
+        self.backward()
+
+    def set_hp(self, lr_scale: float, momentum: float):
+        self.adam_t += 1
+        h = self.hp_host
+        h[0], h[1] = lr_scale, momentum
+        h[2] = 1.0 - self.t.adam_beta1 ** self.adam_t
+        h[3] = 1.0 - self.t.adam_beta2 ** self.adam_t
+        h[4] = 1.0
+        self.hp.copy_(h, non_blocking=True)
+
+    def clip(self, extra_sumsq: Optional[torch.Tensor] = None):
+        """Global-norm clip factor into hp[4] (all gradient buffers of this engine)."""
+        if self.t.grad_clip_norm <= 0:
+            return
+        C = self.C
+        for k in gpt.BANKS:
+            C.sumsq(self.g[k].view(-1), 1.0, self.stats)
+        for grp in self.groups:
+            C.sumsq(grp["g"], 1.0, self.stats)
+        C.clip_factor(self.stats, self.hp, 1.0, self.t.grad_clip_norm)
+
+    def enable_ema(self):
+        self.ema = {k: v.clone() for k, v in self.p.items() if k in gpt.BANKS}
+        for gi, grp in enumerate(self.groups):
+            grp["ema"] = grp["p"].clone()
+
+    def newton_schulz(self, key: str, Bcount: Optional[int] = None) -> torch.Tensor:
+        """Orthogonalise ns[key]["X0"] (already normalised) in place of the ping-pong buffers; returns the result buffer."""
+        st = self.ns[key]
+        X, Xn, Am, Bm = st["X0"], st["X1"], st["A"], st["Bm"]
+        if Bcount is not None:
+            X, Xn, Am, Bm = X[:Bcount], Xn[:Bcount], Am[:Bcount], Bm[:Bcount]
+        tall = X.shape[1] > X.shape[2]
+        for s in range(self.t.muon_ns_steps):
+            a, b, c = ns_coeff(self.t.muon_ns_profile, s)
+            if tall:
+                N.gemm(X, X, Am, False, False)                                           # A = X^T X
+            else:
+                N.gemm(X, X, Am, True, True)                                             # A = X X^T
+            N.gemm(Am, Am, Bm, True, True, N.EPI_AXPBY_BF16, alpha=c, beta=b, aux=Am)    # B = b A + c A A   (A symmetric)
+            if tall:
+                N.gemm(X, Bm, Xn, True, True, N.EPI_AXPBY_BF16, alpha=1.0, beta=a, aux=X)    # X = a X + X B
+            else:
+                N.gemm(Bm, X, Xn, True, False, N.EPI_AXPBY_BF16, alpha=1.0, beta=a, aux=X)   # X = a X + B X
+            X, Xn = Xn, X
+        return X
+
+    def optimizer_step(self):
+        """Replicated step: AdamW on the flat groups, Muon on the banks, then refresh the bf16 weights."""
+        C, t = self.C, self.t
+        decay = t.ema_decay
+        for grp in self.groups:
+            if grp["p"].numel():
+                C.adamw(grp["p"], grp["g"], grp["m"], grp["v"], grp.get("ema"), self.hp, grp["lr"], t.adam_beta1, t.adam_beta2, t.adam_eps, t.adam_wd, decay)
+        for k in gpt.BANKS:
+            st = self.ns[k]
+            st["sq"].zero_()
+            C.muon_momentum(self.g[k], self.mom[k], st["U"], st["sq"], self.hp, True)
+            C.muon_normalize(st["U"], st["X0"], st["sq"], 1e-7)
+            X = self.newton_schulz(k)
+            scale = max(1.0, self.p[k].shape[-2] / self.p[k].shape[-1]) ** 0.5
+            C.muon_apply(self.p[k].view(-1), X.view(-1), self.ema[k].view(-1) if self.ema else None, self.hp, t.matrix_lr, t.muon_wd, scale, decay)
+        self.cast_weights()
+
+    def export_params(self, ema: bool = False) -> Dict[str, torch.Tensor]:
+        out = {}
+        for k, v in self.p.items():
+            out[k] = v.detach().float().cpu().clone()
+        if ema and self.train and self.ema is not None:
+            for k in gpt.BANKS:
+                out[k] = self.ema[k].detach().cpu().clone()
+            for grp in self.groups:
+                off = 0
+                for k in grp["names"]:
+                    nel = self.p[k].numel()
+                    out[k] = grp["ema"][off:off + nel].view(self.p[k].shape).detach().cpu().clone()
+                    off += -(-nel // 4) * 4
+        return out
+
+    def load_params(self, params: Dict[str, torch.Tensor]):
+        for k, v in params.items():
+            self.p[k].copy_(v.to(self.dev, torch.float32))
+        self.cast_weights()
+
+
+class EngineRunner:
+    """Runner interface (see `parameter_golf_b200.models.runner`) on the CUDA engine, for evaluation and TTT."""
+
+    def __init__(self, spec: RunSpec, params: Dict[str, torch.Tensor], device, batch: Optional[int] = None, train: bool = True):
+        self.spec, self.model = spec, spec.model
+        self.device = torch.device(device)
+        self.batch = batch or spec.eval.batch_windows
+        self.engines: Dict[Tuple[int, int], CudaEngine] = {}
+        self._params = {k: v.detach().float() for k, v in params.items()}
+        self.train = train
+        self.lora = None
+
+    def _engine(self, B: int, S: int) -> CudaEngine:
+        key = (B, S)
+        if key not in self.engines:
+            src = next(iter(self.engines.values())).export_params() if self.engines else self._params
+            self.engines.clear()                       # one live shape at a time keeps memory bounded
+            self.engines[key] = CudaEngine(self.spec, src, self.device, B, S, train=self.train)
+        return self.engines[key]
+
+    @property
+    def params(self):
+        if self.engines:
+            return next(iter(self.engines.values())).p
+        return self._params
+
+    def params_changed(self):
+        for e in self.engines.values():
+            e.cast_weights()
+
+    @torch.no_grad()
+    def nll(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        e = self._engine(ids.shape[0], ids.shape[1])
+        e.forward(ids.to(self.device, torch.int32), targets.to(self.device, torch.int32))
+        return e.nll.view(ids.shape).clone()
+
+    @torch.no_grad()
+    def logits(self, ids: torch.Tensor) -> torch.Tensor:
+        e = self._engine(ids.shape[0], ids.shape[1])
+        e.forward(ids.to(self.device, torch.int32), None)
+        z = e.logits.view(*ids.shape, -1).float()
+        return self.model.logit_softcap * torch.tanh(z / self.model.logit_softcap)
+
+    @torch.no_grad()
+    def loss_and_grads(self, ids, targets, qat: bool = False, names=None):
+        e = self._engine(ids.shape[0], ids.shape[1])
+        if e.qat != qat:
+            e.qat = qat
+            e.cast_weights()
+        e.zero_grads()
+        e.micro_step(ids.to(self.device, torch.int32), targets.to(self.device, torch.int32), 1)
+        loss = e.loss_sum[0] / e.T
+        names = list(e.g) if names is None else list(names)
+        return loss.clone(), {k: e.g[k] for k in names}
+
+
+class EngineBackend:
+    """Training backend used by `parameter_golf_b200.train.VariantRunner` for the CUDA backends."""
+
+    def __init__(self, spec: RunSpec, params: Dict[str, torch.Tensor]):
+        import os
+        from ..train import step_batch_plan
+        self.spec = spec
+        t = spec.train
+        self.device = torch.device(f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}")
+        torch.cuda.set_device(self.device)
+        tokens, accum = step_batch_plan(spec, spec.mode)
+        micro_tokens = tokens // (t.world_size * accum)
+        self.accum = accum
+        self.engine = CudaEngine(spec, params, self.device, micro_tokens // t.seq_len, t.seq_len, train=True)
+        if t.ema_decay > 0:
+            self.engine.enable_ema()
+        self.dist = None
+        if t.world_size > 1:
+            from ..parallel.dist_engine import DistributedStep
+            self.dist = DistributedStep(self.engine, spec)
+
+    def train_step(self, batches, lr_scale: float, momentum: float, qat: bool) -> float:
+        e = self.engine
+        if qat != e.qat:
+            e.qat = qat
+            e.cast_weights()
+        e.zero_grads()
+        e.set_hp(lr_scale, momentum)
+        for ids, tgt in batches:
+            e.micro_step(ids.to(self.device, torch.int32, non_blocking=True), tgt.to(self.device, torch.int32, non_blocking=True), len(batches))
+        if self.dist is not None:
+            self.dist.step()
+        else:
+            e.clip()
+            e.optimizer_step()
+        return float(e.loss_sum[0]) / (e.T * len(batches))
+
+    def sync_params(self):
+        return self.engine.p
+
+    def params_changed(self):
+        self.engine.cast_weights()
+
+    def state_dict(self):
+        e = self.engine
+        return {"mom": {k: v.cpu() for k, v in e.mom.items()}, "adam_t": e.adam_t,
+                "m": [g["m"].cpu() for g in e.groups], "v": [g["v"].cpu() for g in e.groups]}
+
+    def load_state_dict(self, st):
+        e = self.engine
+        for k, v in st["mom"].items():
+            e.mom[k].copy_(v)
+        e.adam_t = int(st["adam_t"])
+        for g, mm, vv in zip(e.groups, st["m"], st["v"]):
+            g["m"].copy_(mm)
+            g["v"].copy_(vv)

@@ -1,0 +1,129 @@
+"""CUDA engine against the fp32 autograd oracle: row kernels, one-step loss/gradients, optimizer, short trajectory."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def small_spec(**ov):
+    from parameter_golf_b200.spec import family_preset
+    s = family_preset("record_11l")
+    m = s.model
+    m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads, m.mlp_mult, m.vocab_size = 4, 128, 2, 1, 2.0, 256
+    m.xsa_last_n, m.rope.dims = 2, 16
+    m.bigram.vocab_size, m.bigram.dim = 96, 64
+    m.train_seq_len = m.eval_seq_len = 128
+    s.train.seq_len, s.train.batch_tokens, s.train.backend, s.train.world_size = 128, 4 * 128, "cuda_single", 1
+    s.train.distributed_optimizer_backend = "all_reduce_replicated_muon"
+    s.apply_overrides([f"{k}={v}" for k, v in ov.items()])
+    return s.validate()
+
+
+def oracle_grads(spec, params, ids, tgt):
+    from parameter_golf_b200.models.runner import OracleRunner
+    p = {k: v.double() for k, v in params.items()}
+    return OracleRunner(spec.model, p).loss_and_grads(ids.long().cpu(), tgt.long().cpu())
+
+
+def rel_err(a, b):
+    return float((a.double().cpu() - b.double().cpu()).norm() / (b.double().cpu().norm() + 1e-12))
+
+
+@pytest.mark.parametrize("variant", ["record", "baseline", "ve"])
+def test_one_step_loss_and_gradients_match_oracle(variant):
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine
+    from parameter_golf_b200.ops import native
+    ov = {}
+    if variant == "baseline":
+        ov = {"model.xsa_last_n": 0, "model.rope.dims": 0, "model.bigram.enabled": "false", "model.smear_gate": "false",
+              "model.ln_scale": "false", "model.activation": "relu_sq"}
+    if variant == "ve":
+        ov = {"model.value_embedding.enabled": "true", "model.value_embedding.dim": 64, "model.value_embedding.layers": "[2,3]"}
+    spec = small_spec(**ov)
+    params = gpt.fill_deterministic(spec.model)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 256, (4, 128))
+    tgt = torch.randint(0, 256, (4, 128))
+    eng = CudaEngine(spec, params, "cuda", 4, 128)
+    eng.zero_grads()
+    eng.micro_step(ids.cuda().int(), tgt.cuda().int(), 1)
+    torch.cuda.synchronize()
+    native.check_status()
+    loss = float(eng.loss_sum[0]) / eng.T
+    ref_loss, ref = oracle_grads(spec, params, ids, tgt)
+    assert abs(loss - float(ref_loss)) < 2e-2, (loss, float(ref_loss))
+    worst = {}
+    for k, g in ref.items():
+        worst[k] = rel_err(eng.g[k], g)
+    bad = {k: v for k, v in worst.items() if v > 0.06}          # bf16 activations/gradients vs an fp64 oracle
+    assert not bad, worst
+
+
+def test_forward_logits_and_nll_match_oracle():
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import EngineRunner
+    from parameter_golf_b200.models.runner import OracleRunner
+    spec = small_spec()
+    params = gpt.fill_deterministic(spec.model)
+    ids = torch.randint(0, 256, (3, 128))
+    tgt = torch.randint(0, 256, (3, 128))
+    r = EngineRunner(spec, params, "cuda", train=False)
+    o = OracleRunner(spec.model, params)
+    assert (r.logits(ids).cpu() - o.logits(ids)).abs().max() < 0.35
+    assert (r.nll(ids, tgt).cpu() - o.nll(ids, tgt)).abs().mean() < 2e-2
+
+
+def test_optimizer_step_matches_torch_optimizers():
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine
+    from parameter_golf_b200.train import OracleBackend
+    spec = small_spec(**{"train.grad_clip_norm": 0.3, "train.ema_decay": 0.9})
+    params = gpt.fill_deterministic(spec.model)
+    eng = CudaEngine(spec, params, "cuda", 4, 128)
+    eng.enable_ema()
+    cpu = OracleBackend(spec, {k: v.clone() for k, v in params.items()})
+    torch.manual_seed(1)
+    grads = {k: torch.randn_like(v) * 0.05 for k, v in params.items()}
+    for k in grads:
+        eng.g[k].copy_(grads[k])
+    eng.set_hp(0.7, 0.93)
+    eng.clip()
+    eng.optimizer_step()
+    torch.cuda.synchronize()
+    from parameter_golf_b200.optim.muon import clip_grads_
+    gl = {k: v.clone() for k, v in grads.items()}
+    clip_grads_(list(gl.values()), 0.3)
+    cpu.adam.step([[gl[k] for k in g["names"]] for g in cpu.adam_groups], 0.7)
+    cpu.muon.step([gl[k] for k in cpu.bank_names], lr=spec.train.matrix_lr * 0.7, momentum=0.93)
+    for k in params:
+        upd_ref = cpu.params[k] - params[k]
+        upd = eng.p[k].cpu() - params[k]
+        tol = 0.08 if k in gpt.BANKS else 1e-3                  # bf16 Newton-Schulz vs fp32 Newton-Schulz
+        assert rel_err(upd, upd_ref) < tol, (k, rel_err(upd, upd_ref))
+    ema = eng.export_params(ema=True)
+    for k in ("tok_emb", "qo_bank"):
+        exp = 0.9 * params[k] + 0.1 * eng.p[k].cpu()
+        assert (ema[k] - exp).abs().max() < 1e-5
+
+
+def test_short_training_trajectory_tracks_oracle():
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import EngineBackend
+    from parameter_golf_b200.train import OracleBackend
+    spec = small_spec(**{"train.tied_embed_lr": 0.01, "train.ema_decay": 0.0})
+    spec.mode = "record"
+    spec.allow_unsupported_variants = True
+    params = gpt.init_params(spec.model, 3)
+    gpu = EngineBackend(spec, {k: v.clone() for k, v in params.items()})
+    cpu = OracleBackend(spec, {k: v.clone() for k, v in params.items()})
+    torch.manual_seed(2)
+    lg, lc = [], []
+    for step in range(6):
+        ids = torch.randint(0, 256, (4, 128))
+        tgt = (ids * 7 + 3) % 256                                # learnable mapping
+        lg.append(gpu.train_step([(ids, tgt)], 1.0, 0.95, False))
+        lc.append(cpu.train_step([(ids, tgt)], 1.0, 0.95, False))
+    assert lg[-1] < lg[0] and all(abs(a - b) < 0.02 * max(1.0, abs(b)) for a, b in zip(lg, lc)), (lg, lc)

@@ -1,0 +1,514 @@
+// Causal GQA flash-attention backward for sm_100a (head_dim 64), two kernels, no atomics:
+//
+//   attn_bwd_dq_kernel    query-stationary: for a 128-row query tile of two heads sharing a KV head, streams
+//                         the K/V tiles, recomputes P from the saved log-sum-exp, forms dS and accumulates
+//                         dQ += dS K in tensor memory. Also produces D = rowsum(dO * O).
+//   attn_bwd_dkdv_kernel  key-stationary: for a 128-key tile of one KV head, streams 64-row Q/dO sub-tiles of
+//                         every query head of the group, computes the TRANSPOSED scores S^T = K Q^T and
+//                         dP^T = V dO^T (one thread per key row), and accumulates dV += P^T dO, dK += dS^T Q.
+//
+// In both kernels the bf16 P / dS operands are written over their own fp32 scores in TMEM and consumed by
+// tcgen05.mma straight from there, so probabilities never touch shared or global memory. Accumulating dQ in
+// a second pass costs two extra small GEMMs per tile but removes the fp32 atomics a single-pass design
+// needs (tens of GB of L2 atomic traffic per layer at this problem size).
+// Same role as the cuDNN SDPA backward graph of the reference
+// (parameter-golf-rs/crates/pg-kernels/cpp/cudnn_sdpa.cu:364-435).
+#include "common.cuh"
+#include "pgb.h"
+#include "tma_host.h"
+
+namespace pgb {
+
+constexpr int AB_THREADS = 320;
+constexpr int AB_HD = 64;
+constexpr int AB_TILE = 128 * AB_HD * 2;     // 16 KB
+constexpr int AB_SUB = 64 * AB_HD * 2;       // 8 KB
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void tma2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)), "l"(gsrc),
+               "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct AttnBwdParams {
+  int B, S, H, Hkv, n_qt, pairs, group;
+  float scale, scale_log2;
+  const __nv_bfloat16* O;      // [T, H*hd]
+  const __nv_bfloat16* dO;
+  long long ldo, lddo;
+  const float* lse;            // [B, H, S]
+  float* Dsum;                 // [B, H, S]
+  __nv_bfloat16* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  long long lddq, lddk, lddv;
+  int accumulate_dv;
+  int* status;
+};
+
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int DQ_STAGES = 3;
+constexpr int DQ_SMEM = (4 + 2 * DQ_STAGES) * AB_TILE + 1024 + 256;
+
+__global__ void __launch_bounds__(AB_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const __grid_constant__ CUtensorMap map_do, const AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                       // 2 tiles
+  uint8_t* sdO = smem + 2 * AB_TILE;        // 2 tiles
+  uint8_t* sKV = smem + 4 * AB_TILE;        // stages {K, V}
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (4 + 2 * DQ_STAGES) * AB_TILE);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = kv_full + DQ_STAGES;
+  uint64_t* s_full = kv_empty + DQ_STAGES;   // 2
+  uint64_t* p_full = s_full + 2;             // 2
+  uint64_t* dq_full = p_full + 2;            // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_qt = p.B * p.Hkv * p.pairs;
+  const int qt = p.n_qt - 1 - (int)(blockIdx.x / per_qt);
+  int rem = (int)(blockIdx.x % per_qt);
+  const int b = rem / (p.Hkv * p.pairs);
+  rem -= b * p.Hkv * p.pairs;
+  const int kvh = rem / p.pairs, pair = rem % p.pairs;
+  const int head0 = kvh * p.group + pair * 2;
+  const int n_active = min(2, p.group - pair * 2);
+  const int n_kv = qt + 1;
+  const int nsteps = 2 * n_kv;
+  const int row0 = b * p.S + qt * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < DQ_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(&s_full[w], 1);
+      mbar_init(&p_full[w], 128);
+      mbar_init(&dq_full[w], 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // per head w: S at w*192, dP at w*192+64, dQ at w*192+128 (64 columns each); bf16 dS overwrites S[0,32)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, n_active * 2 * AB_TILE);
+      for (int w = 0; w < n_active; ++w) {
+        tma2d(sQ + w * AB_TILE, &map_q, q_full, (head0 + w) * AB_HD, row0);
+        tma2d(sdO + w * AB_TILE, &map_do, q_full, (head0 + w) * AB_HD, row0);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
+        uint8_t* sk = sKV + stage * 2 * AB_TILE;
+        mbar_expect_tx(&kv_full[stage], 2 * AB_TILE);
+        tma2d(sk, &map_k, &kv_full[stage], kvh * AB_HD, b * p.S + j * 128);
+        tma2d(sk + AB_TILE, &map_v, &kv_full[stage], kvh * AB_HD, b * p.S + j * 128);
+        if (++stage == DQ_STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        mbar_drain(q_full, 0);
+        for (int s = 0; s < DQ_STAGES; ++s) mbar_drain(&kv_full[s], (s < stage) ? phase : (phase ^ 1));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc_bf16(128, 64, 0, 0);     // Q K^T, dO V^T (64-key sub-tiles)
+      constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, 64, 0, 1);    // dS (TMEM) x K, K read N(=hd)-contiguous
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_WAIT_FULL, -1);
+      auto issue_sdp = [&](int w, int t) {
+        const int stage = (t >> 1) % DQ_STAGES, hh = t & 1;
+        const uint32_t sq = smem_u32(sQ + w * AB_TILE), sdo = smem_u32(sdO + w * AB_TILE);
+        const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE) + hh * AB_SUB, sv = sk + AB_TILE;
+        const uint32_t tS = tmem_base + w * 192, tP = tS + 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_ss(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_ss(tP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), IDESC_S, k > 0);
+        umma_commit(&s_full[w]);
+      };
+      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, ST_WAIT_FULL, 0);
+      if (ok) {
+        tc_fence_after();
+        for (int w = 0; w < n_active; ++w) issue_sdp(w, 0);
+      }
+      for (int t = 0; t < nsteps && ok; ++t) {
+        const int tile = t >> 1, hh = t & 1, stage = tile % DQ_STAGES;
+        if (t + 1 < nsteps && ((t + 1) >> 1) != tile) {
+          const int nt = (t + 1) >> 1;
+          if (!mbar_wait(&kv_full[nt % DQ_STAGES], (nt / DQ_STAGES) & 1, abort_flag, p.status, ST_WAIT_FULL, nt)) { ok = false; break; }
+        }
+        const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE) + hh * AB_SUB;
+        for (int w = 0; w < n_active && ok; ++w) {
+          if (!mbar_wait(&p_full[w], t & 1, abort_flag, p.status, ST_WAIT_MISC, t)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_ts(tmem_base + w * 192 + 128, tmem_base + w * 192 + k * 8, make_smem_desc(sk + k * 2048, 8192, 1024), IDESC_DQ,
+                    (t > 0 || k > 0) ? 1u : 0u);
+          if (t + 1 < nsteps) issue_sdp(w, t + 1);
+          else umma_commit(&dq_full[w]);
+        }
+        if (!ok) break;
+        if (hh == 1) umma_commit(&kv_empty[stage]);
+      }
+    }
+  } else {
+    const int w = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    if (w < n_active) {
+      const int head = head0 + w;
+      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+      const uint32_t tS = tmem_base + w * 192 + lane_off, tP = tS + 64, tDQ = tS + 128;
+      // D = rowsum(dO * O) for this query row; also published for the dK/dV kernel
+      float Dr = 0.f;
+      {
+        const __nv_bfloat16* op = p.O + (size_t)(row0 + r) * p.ldo + head * AB_HD;
+        const __nv_bfloat16* dop = p.dO + (size_t)(row0 + r) * p.lddo + head * AB_HD;
+#pragma unroll
+        for (int c = 0; c < AB_HD; c += 8) {
+          uint4 a = *reinterpret_cast<const uint4*>(op + c), g = *reinterpret_cast<const uint4*>(dop + c);
+          float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+          float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
+          Dr += a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y + a2.x * g2.x + a2.y * g2.y + a3.x * g3.x + a3.y * g3.y;
+        }
+      }
+      const size_t sidx = ((size_t)b * p.H + head) * p.S + qt * 128 + r;
+      p.Dsum[sidx] = Dr;
+      const float lse2 = p.lse[sidx] * LOG2E;
+      bool ok = true;
+      for (int t = 0; t < nsteps; ++t) {
+        if (!mbar_wait(&s_full[w], t & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t s[64], dp[64];
+        PGB_TMEM_LD32(tS, (s));
+        PGB_TMEM_LD32(tS + 32, (s + 32));
+        PGB_TMEM_LD32(tP, (dp));
+        PGB_TMEM_LD32(tP + 32, (dp + 32));
+        tmem_wait_ld();
+        const bool diag = (t >> 1) == qt;
+        const int kbase = (t & 1) * 64;                     // key offset of this sub-tile inside the 128-key tile
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          float p0 = ex2f(fmaf(__uint_as_float(s[c]), p.scale_log2, -lse2));
+          float p1 = ex2f(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -lse2));
+          if (diag) {
+            if (kbase + c > r) p0 = 0.f;
+            if (kbase + c + 1 > r) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dp[c]) - Dr) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dp[c + 1]) - Dr) * p.scale;
+          pk[c >> 1] = pack_bf16x2(d0, d1);
+        }
+        PGB_TMEM_ST16(tS, (pk));
+        PGB_TMEM_ST16(tS + 16, (pk + 16));
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_full[w]);
+      }
+      if (ok && mbar_wait(&dq_full[w], 0, abort_flag, p.status, ST_WAIT_MISC, nsteps)) {
+        tc_fence_after();
+        __nv_bfloat16* out = p.dq + (size_t)(row0 + r) * p.lddq + head * AB_HD;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t o[32];
+          PGB_TMEM_LD32(tDQ + h * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 8)
+            *reinterpret_cast<uint4*>(out + h * 32 + c) =
+                make_uint4(pack_bf16x2(__uint_as_float(o[c]), __uint_as_float(o[c + 1])), pack_bf16x2(__uint_as_float(o[c + 2]), __uint_as_float(o[c + 3])),
+                           pack_bf16x2(__uint_as_float(o[c + 4]), __uint_as_float(o[c + 5])), pack_bf16x2(__uint_as_float(o[c + 6]), __uint_as_float(o[c + 7])));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int KV_STAGES = 6;
+// one stage holds a Q sub-tile, a dO sub-tile, lse[64] and D[64]
+constexpr int KV_SMEM = 2 * AB_TILE + KV_STAGES * (2 * AB_SUB) + KV_STAGES * 512 + 1024 + 256;
+
+__global__ void __launch_bounds__(AB_THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                     const __grid_constant__ CUtensorMap map_do64, const AttnBwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + AB_TILE;
+  uint8_t* sQD = smem + 2 * AB_TILE;                                   // stages of {Q64, dO64}
+  float* sVec = reinterpret_cast<float*>(smem + 2 * AB_TILE + KV_STAGES * 2 * AB_SUB);   // stages of {lse[64], D[64]}
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sVec) + KV_STAGES * 512);
+  uint64_t* kv_full = bars;
+  uint64_t* st_full = bars + 1;
+  uint64_t* st_empty = st_full + KV_STAGES;
+  uint64_t* s_full = st_empty + KV_STAGES;    // 2
+  uint64_t* p_full = s_full + 2;              // 2
+  uint64_t* acc_full = p_full + 2;            // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_kt = p.B * p.Hkv;
+  const int j = (int)(blockIdx.x / per_kt);                 // key tile; low j = long query range = scheduled first
+  const int rem = (int)(blockIdx.x % per_kt);
+  const int b = rem / p.Hkv, kvh = rem % p.Hkv;
+  const int nu = (p.n_qt - j) * p.group * 2;                // units: (query tile, head, 64-row half)
+  const int key0 = b * p.S + j * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&st_full[s], 1);
+      mbar_init(&st_empty[s], 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(&s_full[w], 1);
+      mbar_init(&p_full[w], 128);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // buffer u&1: S^T at buf*128, dP^T at buf*128+64; dK at 256, dV at 320
+
+  auto unit_coords = [&](int u, int& qi, int& head, int& hh) {
+    hh = u & 1;
+    const int v = u >> 1;
+    head = kvh * p.group + (v % p.group);
+    qi = j + v / p.group;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * AB_TILE);
+      tma2d(sK, &map_k, kv_full, kvh * AB_HD, key0);
+      tma2d(sV, &map_v, kv_full, kvh * AB_HD, key0);
+      bool ok = true;
+      for (int u = 0; u < nu && ok; ++u) {
+        const int stage = u % KV_STAGES;
+        const uint32_t phase = (u / KV_STAGES) & 1;
+        if (!mbar_wait(&st_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, u)) { ok = false; break; }
+        int qi, head, hh;
+        unit_coords(u, qi, head, hh);
+        const int qrow = b * p.S + qi * 128 + hh * 64;
+        const size_t vidx = ((size_t)b * p.H + head) * p.S + qi * 128 + hh * 64;
+        mbar_expect_tx(&st_full[stage], 2 * AB_SUB + 512);
+        tma2d(sQD + stage * 2 * AB_SUB, &map_q64, &st_full[stage], head * AB_HD, qrow);
+        tma2d(sQD + stage * 2 * AB_SUB + AB_SUB, &map_do64, &st_full[stage], head * AB_HD, qrow);
+        bulk_g2s(sVec + stage * 128, p.lse + vidx, 256, &st_full[stage]);
+        bulk_g2s(sVec + stage * 128 + 64, p.Dsum + vidx, 256, &st_full[stage]);
+      }
+      if (!ok) {
+        mbar_drain(kv_full, 0);
+        for (int s = 0; s < KV_STAGES; ++s) mbar_drain(&st_full[s], 0), mbar_drain(&st_full[s], 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_T = make_idesc_bf16(128, 64, 0, 0);     // K Q^T and V dO^T
+      constexpr uint32_t IDESC_A = make_idesc_bf16(128, 64, 0, 1);     // P^T (TMEM) x dO, dS^T (TMEM) x Q; B read N(=hd)-contiguous
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, ST_WAIT_FULL, -1);
+      const uint32_t sk = smem_u32(sK), sv = smem_u32(sV);
+      auto issue_sdp = [&](int u) -> bool {
+        const int stage = u % KV_STAGES, buf = u & 1;
+        if (!mbar_wait(&st_full[stage], (u / KV_STAGES) & 1, abort_flag, p.status, ST_WAIT_FULL, u)) return false;
+        tc_fence_after();
+        const uint32_t sq = smem_u32(sQD + stage * 2 * AB_SUB), sdo = sq + AB_SUB;
+        const uint32_t tS = tmem_base + buf * 128, tP = tS + 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_ss(tS, make_smem_desc(sk + k * 32, 16, 1024), make_smem_desc(sq + k * 32, 16, 1024), IDESC_T, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_ss(tP, make_smem_desc(sv + k * 32, 16, 1024), make_smem_desc(sdo + k * 32, 16, 1024), IDESC_T, k > 0);
+        umma_commit(&s_full[buf]);
+        return true;
+      };
+      for (int u = 0; u < 2 && u < nu && ok; ++u) ok = issue_sdp(u);
+      for (int u = 0; u < nu && ok; ++u) {
+        const int stage = u % KV_STAGES, buf = u & 1;
+        if (!mbar_wait(&p_full[buf], (u >> 1) & 1, abort_flag, p.status, ST_WAIT_MISC, u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sq = smem_u32(sQD + stage * 2 * AB_SUB), sdo = sq + AB_SUB;
+        const uint32_t tPt = tmem_base + buf * 128, tdSt = tPt + 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // dV += P^T dO
+          umma_ts(tmem_base + 320, tPt + k * 8, make_smem_desc(sdo + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // dK += dS^T Q
+          umma_ts(tmem_base + 256, tdSt + k * 8, make_smem_desc(sq + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&st_empty[stage]);
+        if (u + 2 < nu) ok = issue_sdp(u + 2);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    const int w = (warp - 2) >> 2;                 // this group handles units with (u & 1) == w
+    const int quarter = warp & 3;
+    const int kk = quarter * 32 + lane;            // key row within the tile
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    bool ok = true;
+    for (int u = w; u < nu; u += 2) {
+      const int stage = u % KV_STAGES;
+      if (!mbar_wait(&st_full[stage], (u / KV_STAGES) & 1, abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
+      if (!mbar_wait(&s_full[w], (u >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL, u)) { ok = false; break; }
+      tc_fence_after();
+      int qi, head, hh;
+      unit_coords(u, qi, head, hh);
+      const uint32_t tS = tmem_base + w * 128 + lane_off, tP = tS + 64;
+      uint32_t s[64], dp[64];
+      PGB_TMEM_LD32(tS, (s));
+      PGB_TMEM_LD32(tS + 32, (s + 32));
+      PGB_TMEM_LD32(tP, (dp));
+      PGB_TMEM_LD32(tP + 32, (dp + 32));
+      tmem_wait_ld();
+      const float* vl = sVec + stage * 128;
+      const float* vd = vl + 64;
+      const bool diag = qi == j;
+      const int qbase = hh * 64;
+      uint32_t pp[32], pd[32];
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        float p0 = ex2f(fmaf(__uint_as_float(s[c]), p.scale_log2, -vl[c] * LOG2E));
+        float p1 = ex2f(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -vl[c + 1] * LOG2E));
+        if (diag) {
+          if (qbase + c < kk) p0 = 0.f;              // query position before the key: masked
+          if (qbase + c + 1 < kk) p1 = 0.f;
+        }
+        pp[c >> 1] = pack_bf16x2(p0, p1);
+        pd[c >> 1] = pack_bf16x2(p0 * (__uint_as_float(dp[c]) - vd[c]) * p.scale, p1 * (__uint_as_float(dp[c + 1]) - vd[c + 1]) * p.scale);
+      }
+      PGB_TMEM_ST16(tS, (pp));
+      PGB_TMEM_ST16(tS + 16, (pp + 16));
+      PGB_TMEM_ST16(tP, (pd));
+      PGB_TMEM_ST16(tP + 16, (pd + 16));
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full[w]);
+    }
+    if (ok && mbar_wait(acc_full, 0, abort_flag, p.status, ST_WAIT_MISC, nu)) {
+      tc_fence_after();
+      // group 0 writes dK, group 1 writes dV
+      const uint32_t tA = tmem_base + (w == 0 ? 256 : 320) + lane_off;
+      __nv_bfloat16* out = (w == 0 ? p.dk + (size_t)(key0 + kk) * p.lddk : p.dv + (size_t)(key0 + kk) * p.lddv) + kvh * AB_HD;
+      const bool acc = (w == 1) && p.accumulate_dv;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t o[32];
+        PGB_TMEM_LD32(tA + h * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]);
+          if (acc) {
+            uint4 q = *reinterpret_cast<const uint4*>(out + h * 32 + c);
+            float2 a0 = unpack_bf16x2(q.x), a1 = unpack_bf16x2(q.y), a2 = unpack_bf16x2(q.z), a3 = unpack_bf16x2(q.w);
+            f[0] += a0.x; f[1] += a0.y; f[2] += a1.x; f[3] += a1.y; f[4] += a2.x; f[5] += a2.y; f[6] += a3.x; f[7] += a3.y;
+          }
+          *reinterpret_cast<uint4*>(out + h * 32 + c) =
+              make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+static CUtensorMap bwd_map(const void* ptr, long long ld, int cols, long long rows, int box_rows) {
+  uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows};
+  uint64_t strides[1] = {(uint64_t)ld * 2};
+  uint32_t box[2] = {AB_HD, (uint32_t)box_rows};
+  return make_tmap_bf16(ptr, 2, dims, strides, box);
+}
+
+void attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, float* dsum, void* dq, void* dk, void* dv,
+              long long ldq, long long ldk, long long ldv, long long ldo, long long lddo, long long lddq, long long lddk, long long lddv, int B, int S,
+              int H, int Hkv, int hd, int accumulate_dv, int* status, cudaStream_t st) {
+  if (hd != AB_HD) throw std::runtime_error("attention kernel is specialised for head_dim 64");
+  if (S % 128) throw std::runtime_error("attention kernel needs seq_len to be a multiple of 128");
+  const long long T = (long long)B * S;
+  AttnBwdParams p;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
+  p.n_qt = S / 128;
+  p.group = H / Hkv;
+  p.pairs = (p.group + 1) / 2;
+  p.scale = 1.f / sqrtf((float)hd);
+  p.scale_log2 = p.scale * LOG2E;
+  p.O = (const __nv_bfloat16*)o; p.dO = (const __nv_bfloat16*)d_o;
+  p.ldo = ldo; p.lddo = lddo;
+  p.lse = lse; p.Dsum = dsum;
+  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.lddq = lddq; p.lddk = lddk; p.lddv = lddv;
+  p.accumulate_dv = accumulate_dv;
+  p.status = status;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
+    cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM);
+    configured = true;
+  }
+  {
+    const CUtensorMap mq = bwd_map(q, ldq, H * hd, T, 128), mk = bwd_map(k, ldk, Hkv * hd, T, 128), mv = bwd_map(v, ldv, Hkv * hd, T, 128),
+                      mdo = bwd_map(d_o, lddo, H * hd, T, 128);
+    attn_bwd_dq_kernel<<<p.n_qt * B * Hkv * p.pairs, AB_THREADS, DQ_SMEM, st>>>(mq, mk, mv, mdo, p);
+  }
+  {
+    const CUtensorMap mq = bwd_map(q, ldq, H * hd, T, 64), mk = bwd_map(k, ldk, Hkv * hd, T, 128), mv = bwd_map(v, ldv, Hkv * hd, T, 128),
+                      mdo = bwd_map(d_o, lddo, H * hd, T, 64);
+    attn_bwd_dkdv_kernel<<<p.n_qt * B * Hkv, AB_THREADS, KV_SMEM, st>>>(mq, mk, mv, mdo, p);
+  }
+}
+
+}  // namespace pgb

@@ -1,0 +1,306 @@
+// Causal GQA flash-attention forward for sm_100a (head_dim 64): TMA -> smem, QK^T and PV on tcgen05 with
+// S/P/O in tensor memory, online softmax by one thread per query row.
+//
+// One CTA handles one 128-row query tile of TWO query heads that share a KV head, so every K/V tile is
+// loaded once and used by both. Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer,
+// warps 2-5 softmax for head 0, warps 6-9 softmax for head 1. The two softmax groups ping-pong on the
+// tensor core: while one exponentiates its tile the other's QK^T / PV are in flight.
+//   TMEM: S0 [0,128) S1 [128,256) (fp32 scores; the bf16 probabilities P overwrite the first 64 columns
+//         of their own S and feed the PV MMA straight from tensor memory), O0 [256,320) O1 [320,384).
+// The running maximum is updated lazily: probabilities are taken relative to a stale maximum and O is
+// rescaled in TMEM only when a row's maximum grows by more than 2^8, so the common iteration has no
+// accumulator traffic. Replaces the cuDNN SDPA graph of the reference
+// (parameter-golf-rs/crates/pg-kernels/cpp/cudnn_sdpa.cu:312-362) and its SIMT fallback
+// (pg-kernels/src/gpu_kernels.rs:4751-4843).
+#include "common.cuh"
+#include "pgb.h"
+#include "tma_host.h"
+
+namespace pgb {
+
+constexpr int AT_THREADS = 320;
+constexpr int AT_BM = 128;   // query rows per tile
+constexpr int AT_BN = 128;   // keys per tile
+constexpr int AT_HD = 64;
+constexpr int AT_STAGES = 4;
+constexpr int AT_TILE_BYTES = 128 * AT_HD * 2;   // 16 KB: one Q, K or V tile
+constexpr int AT_SMEM = (2 + 2 * AT_STAGES) * AT_TILE_BYTES + 1024 + 256;
+
+struct AttnFwdParams {
+  int B, S, H, Hkv, n_qt, pairs;     // pairs = ceil(group / 2)
+  float scale_log2;
+  __nv_bfloat16* Y;
+  long long ldy;
+  float* lse;
+  int* status;
+};
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                const AttnFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                                   // 2 tiles
+  uint8_t* sKV = smem + 2 * AT_TILE_BYTES;              // stages of {K, V}
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * AT_STAGES) * AT_TILE_BYTES);
+  uint64_t* q_full = bars;                 // 1
+  uint64_t* kv_full = bars + 1;            // STAGES
+  uint64_t* kv_empty = kv_full + AT_STAGES;
+  uint64_t* s_full = kv_empty + AT_STAGES; // 2
+  uint64_t* p_full = s_full + 2;           // 2
+  uint64_t* o_full = p_full + 2;           // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work item: heavy (long KV range) tiles first
+  const int per_qt = p.B * p.Hkv * p.pairs;
+  const int qt = p.n_qt - 1 - (int)(blockIdx.x / per_qt);
+  int rem = (int)(blockIdx.x % per_qt);
+  const int b = rem / (p.Hkv * p.pairs);
+  rem -= b * p.Hkv * p.pairs;
+  const int kvh = rem / p.pairs, pair = rem % p.pairs;
+  const int group = p.H / p.Hkv;
+  const int head0 = kvh * group + pair * 2;
+  const int n_active = min(2, group - pair * 2);
+  const int n_kv = qt + 1;
+  const int row0 = b * p.S + qt * AT_BM;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < AT_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(&s_full[w], 1);
+      mbar_init(&p_full[w], 128);
+      mbar_init(&o_full[w], 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, n_active * AT_TILE_BYTES);
+      for (int w = 0; w < n_active; ++w) tma_load_2d(sQ + w * AT_TILE_BYTES, &map_q, q_full, (head0 + w) * AT_HD, row0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
+        uint8_t* sk = sKV + stage * 2 * AT_TILE_BYTES;
+        mbar_expect_tx(&kv_full[stage], 2 * AT_TILE_BYTES);
+        tma_load_2d(sk, &map_k, &kv_full[stage], kvh * AT_HD, b * p.S + j * AT_BN);
+        tma_load_2d(sk + AT_TILE_BYTES, &map_v, &kv_full[stage], kvh * AT_HD, b * p.S + j * AT_BN);
+        if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) {
+        mbar_drain(q_full, 0);
+        for (int s = 0; s < AT_STAGES; ++s) mbar_drain(&kv_full[s], (s < stage) ? phase : (phase ^ 1));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);    // Q K^T : both K-major
+      constexpr uint32_t IDESC_O = make_idesc_bf16(128, AT_HD, 0, 1);  // P V   : A from TMEM, V is N-contiguous
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_WAIT_FULL, -1);
+      auto issue_s = [&](int w, int stage) {
+        const uint32_t sq = smem_u32(sQ + w * AT_TILE_BYTES);
+        const uint32_t sk = smem_u32(sKV + stage * 2 * AT_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < AT_HD / 16; ++k)
+          umma_ss(tmem_base + w * 128, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
+        umma_commit(&s_full[w]);
+      };
+      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, ST_WAIT_FULL, 0);
+      if (ok) {
+        tc_fence_after();
+        for (int w = 0; w < n_active; ++w) issue_s(w, 0);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        int nstage = stage + 1;
+        uint32_t nphase = phase;
+        if (nstage == AT_STAGES) { nstage = 0; nphase ^= 1; }
+        if (j + 1 < n_kv) {
+          if (!mbar_wait(&kv_full[nstage], nphase, abort_flag, p.status, ST_WAIT_FULL, j + 1)) { ok = false; break; }
+        }
+        const uint32_t sv = smem_u32(sKV + stage * 2 * AT_TILE_BYTES + AT_TILE_BYTES);
+        for (int w = 0; w < n_active && ok; ++w) {
+          if (!mbar_wait(&p_full[w], j & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < AT_BN / 16; ++k)
+            umma_ts(tmem_base + 256 + w * AT_HD, tmem_base + w * 128 + k * 8, make_smem_desc(sv + k * 2048, 8192, 1024), IDESC_O,
+                    (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&o_full[w]);
+          if (j + 1 < n_kv) issue_s(w, nstage);
+        }
+        if (!ok) break;
+        umma_commit(&kv_empty[stage]);
+        stage = nstage;
+        phase = nphase;
+      }
+    }
+  } else {
+    const int w = (warp - 2) >> 2;                 // softmax group / head within the pair
+    const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
+    const int r = quarter * 32 + lane;             // query row within the tile
+    if (w < n_active) {
+      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+      const uint32_t tS = tmem_base + w * 128 + lane_off;
+      const uint32_t tO = tmem_base + 256 + w * AT_HD + lane_off;
+      float m_used = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int j = 0; j < n_kv; ++j) {
+        if (!mbar_wait(&s_full[w], j & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL, j)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t s[128];
+        PGB_TMEM_LD32(tS, (s));
+        PGB_TMEM_LD32(tS + 32, (s + 32));
+        PGB_TMEM_LD32(tS + 64, (s + 64));
+        PGB_TMEM_LD32(tS + 96, (s + 96));
+        tmem_wait_ld();
+        if (j == qt) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c)
+            if (c > r) s[c] = 0xff800000u;          // -inf
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(s[c]));
+        mx *= p.scale_log2;
+        if (j > 0) {
+          if (!mbar_wait(&o_full[w], (j - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
+        }
+        const bool need = mx > m_used + 8.0f;
+        if (__any_sync(0xffffffffu, need)) {
+          const float m_new = need ? mx : m_used;
+          const float alpha = (m_used == -INFINITY) ? 0.f : ex2(m_used - m_new);
+          if (j > 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t o[32];
+              PGB_TMEM_LD32(tO + h * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+              PGB_TMEM_ST16(tO + h * 32, (o));
+              PGB_TMEM_ST16(tO + h * 32 + 16, (o + 16));
+            }
+          }
+          l *= alpha;
+          m_used = m_new;
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float p0 = ex2(fmaf(__uint_as_float(s[q * 32 + 2 * c]), p.scale_log2, -m_used));
+            const float p1 = ex2(fmaf(__uint_as_float(s[q * 32 + 2 * c + 1]), p.scale_log2, -m_used));
+            sum += p0 + p1;
+            pk[c] = pack_bf16x2(p0, p1);
+          }
+          PGB_TMEM_ST16(tS + q * 16, pk);
+        }
+        l += sum;
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_full[w]);
+      }
+      if (ok && mbar_wait(&o_full[w], (n_kv - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, n_kv)) {
+        tc_fence_after();
+        const float inv = 1.f / l;
+        const int head = head0 + w;
+        __nv_bfloat16* yrow = p.Y + (size_t)(row0 + r) * p.ldy + head * AT_HD;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t o[32];
+          PGB_TMEM_LD32(tO + h * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 8)
+            *reinterpret_cast<uint4*>(yrow + h * 32 + c) =
+                make_uint4(pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv),
+                           pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv),
+                           pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv),
+                           pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv));
+        }
+        p.lse[((size_t)b * p.H + head) * p.S + qt * AT_BM + r] = (m_used + log2f(l)) * 0.6931471805599453f;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+static CUtensorMap attn_map(const void* ptr, long long ld, int cols, long long rows) {
+  uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows};
+  uint64_t strides[1] = {(uint64_t)ld * 2};
+  uint32_t box[2] = {AT_HD, 128};
+  return make_tmap_bf16(ptr, 2, dims, strides, box);
+}
+
+void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, long long ldq, long long ldk, long long ldv, long long ldy, int B,
+              int S, int H, int Hkv, int hd, int* status, cudaStream_t st) {
+  if (hd != AT_HD) throw std::runtime_error("attention kernel is specialised for head_dim 64");
+  if (S % 128) throw std::runtime_error("attention kernel needs seq_len to be a multiple of 128");
+  if (H % Hkv) throw std::runtime_error("num_heads must be divisible by num_kv_heads");
+  const long long T = (long long)B * S;
+  const CUtensorMap mq = attn_map(q, ldq, H * hd, T), mk = attn_map(k, ldk, Hkv * hd, T), mv = attn_map(v, ldv, Hkv * hd, T);
+  AttnFwdParams p;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
+  p.n_qt = S / AT_BM;
+  p.pairs = (H / Hkv + 1) / 2;
+  p.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  p.Y = (__nv_bfloat16*)y;
+  p.ldy = ldy;
+  p.lse = lse;
+  p.status = status;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
+    configured = true;
+  }
+  const int grid = p.n_qt * B * Hkv * p.pairs;
+  attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(mq, mk, mv, p);
+}
+
+}  // namespace pgb

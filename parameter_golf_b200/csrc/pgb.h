@@ -78,4 +78,13 @@ void adamw(float* p, const float* g, float* m, float* v, float* ema, const float
            float wd, float decay, cudaStream_t st);
 void sgd_momentum(float* p, const float* g, float* mom, const float* hp, long long n, float lr, float mu, cudaStream_t st);
 
+// ---- attention (attn_fwd.cu, attn_bwd.cu): causal, grouped KV heads, head_dim 64, bf16 ----------------------------------
+// q/k/v/y are [B*S, heads*hd] views with row strides ld* (elements); lse is fp32 [B, H, S] (natural log).
+void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, long long ldq, long long ldk, long long ldv, long long ldy, int B,
+              int S, int H, int Hkv, int hd, int* status, cudaStream_t st);
+// dsum: fp32 [B, H, S] scratch-free side output (rowsum(dO * O)), written by the dQ kernel and read by the dK/dV kernel.
+void attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, float* dsum, void* dq, void* dk, void* dv,
+              long long ldq, long long ldk, long long ldv, long long ldo, long long lddo, long long lddq, long long lddk, long long lddv, int B, int S,
+              int H, int Hkv, int hd, int accumulate_dv, int* status, cudaStream_t st);
+
 }  // namespace pgb

@@ -52,7 +52,7 @@ def _unsupported(m: ModelSpec) -> Optional[str]:
 
 class CudaEngine:
     def __init__(self, spec: RunSpec, params: Dict[str, torch.Tensor], device, micro_batch: int, seq_len: int, train: bool = True,
-                 attention: str = "sdpa"):
+                 attention: str = "native"):
         bad = _unsupported(spec.model)
         if bad:
             raise NotImplementedError(f"the CUDA engine does not cover {bad}; use the cpu backend for this variant")
@@ -185,6 +185,7 @@ class CudaEngine:
             self.d_hu = buf(T, self.mlp)
             self.d_qk_post, self.d_qkv_pre = buf(T, self.qkvw), buf(T, self.qkvw)
             self.d_x0 = buf(T, d)
+            self.dsum = torch.empty(self.B, self.H, self.S, dtype=torch.float32, device=dev)
             self.d_skip = [buf(T, d) for _ in range(max(self.enc - 1, 0))] if self.unet else []
             self.d_xe = buf(T, d)
             if m.bigram.enabled:
@@ -242,7 +243,7 @@ class CudaEngine:
         dv = self.d_qkv_pre[:, d + kv:]
         xsa = l in self.m.xsa_layers()
         if self.attention == "native":
-            N.attn_bwd(q, k, v, self.y[l], self.d_y, self.lse[l], dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=xsa)
+            N.attn_bwd(q, k, v, self.y[l], self.d_y, self.lse[l], dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=xsa, dsum=self.dsum)
             return
         with torch.enable_grad():
             q4 = q.reshape(B, S, H, hd).transpose(1, 2).detach().requires_grad_(True)

@@ -62,3 +62,19 @@ def check_status(device=None, reset: bool = True):
 def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.0, slope=0.0, aux=None, colscale=None, D2=None, splits=0):
     load().gemm(A, B, D, a_kmajor, b_kmajor, epi, alpha, beta, slope, aux, colscale, D2, splits, status_word(A.device))
     return D
+
+
+def attn_fwd(q, k, v, y, B, S, H, Hkv, hd, lse=None):
+    """Causal GQA attention forward; q/k/v are [B*S, heads*hd] (row-strided views allowed). Returns lse [B, H, S]."""
+    if lse is None:
+        lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
+    load().attn_fwd(q, k, v, y, lse, B, S, H, Hkv, hd, status_word(q.device))
+    return lse
+
+
+def attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=False, dsum=None):
+    """Causal GQA attention backward. Writes dq, dk and dv (dv is added to when ``accumulate_dv``)."""
+    if dsum is None:
+        dsum = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
+    load().attn_bwd(q, k, v, o, d_o, lse, dsum, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv, status_word(q.device))
+    return dsum

@@ -78,6 +78,9 @@ void adamw(float* p, const float* g, float* m, float* v, float* ema, const float
            float wd, float decay, cudaStream_t st);
 void sgd_momentum(float* p, const float* g, float* mom, const float* hp, long long n, float lr, float mu, cudaStream_t st);
 
+// ---- misc (misc.cu) ------------------------------------------------------------------------------------------------------
+void expand_span_u16(const void* span, int* ids, int* targets, int n, cudaStream_t st);
+
 // ---- attention (attn_fwd.cu, attn_bwd.cu): causal, grouped KV heads, head_dim 64, bf16 ----------------------------------
 // q/k/v/y are [B*S, heads*hd] views with row strides ld* (elements); lse is fp32 [B, H, S] (natural log).
 void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, long long ldq, long long ldk, long long ldv, long long ldy, int B,

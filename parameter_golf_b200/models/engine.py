@@ -264,9 +264,10 @@ class CudaEngine:
         ``gscale * dL/dlogits``. Per-token NLL lands in ``self.nll``; the sum is added to ``self.loss_sum``."""
         C, m, p = self.C, self.m, self.p
         d, kv, S = self.d, self.kv, self.S
-        self.ids.copy_(ids.reshape(-1))
-        if targets is not None:
-            self.tgt.copy_(targets.reshape(-1))
+        if ids is not None:                       # otherwise self.ids / self.tgt were filled by `load_span`
+            self.ids.copy_(ids.reshape(-1))
+            if targets is not None and targets is not True:
+                self.tgt.copy_(targets.reshape(-1))
         C.embed_gather(self.ids, self.E, self.e, 0, S)
         if m.bigram.enabled:
             C.embed_gather(self.ids, self.BE, self.bg, m.bigram.vocab_size, S)
@@ -401,6 +402,15 @@ class CudaEngine:
         for grp in self.groups:
             grp["g"].zero_()
         self.loss_sum.zero_()
+
+    def load_span(self, span_u16: torch.Tensor):
+        """Upload path: a uint16 span of T+1 tokens (device tensor) is expanded into inputs and shifted targets."""
+        self.C.expand_span_u16(span_u16, self.ids, self.tgt)
+
+    def micro_step_span(self, span_u16: torch.Tensor, accum: int):
+        self.load_span(span_u16)
+        self.forward(None, True, gscale=1.0 / (self.T * accum), want_grad=True)
+        self.backward()
 
     def micro_step(self, ids, targets, accum: int):
         """One micro-batch forward+backward; gradients are scaled so that `accum` of them sum to the mean."""
@@ -583,6 +593,36 @@ class EngineBackend:
             e.clip()
             e.optimizer_step()
         return float(e.loss_sum[0]) / (e.T * len(batches))
+
+    def stage_spans(self, spans):
+        """Copy uint16 spans (pinned host or device tensors of T+1 tokens, viewed as int16) into device staging buffers."""
+        e = self.engine
+        if not hasattr(self, "_span_dev") or len(self._span_dev) < len(spans):
+            self._span_dev = [torch.empty(e.T + 1, dtype=torch.int16, device=self.device) for _ in range(len(spans))]
+        for dst, src in zip(self._span_dev, spans):
+            dst.copy_(src, non_blocking=True)
+        return self._span_dev[:len(spans)]
+
+    def train_step_spans(self, spans, lr_scale: float, momentum: float, qat: bool = False, read_loss: bool = True, staged: bool = False):
+        """One optimizer step from `len(spans)` micro-batches given as uint16 token spans of T+1 tokens each.
+        ``staged`` means the spans already live on this device. Returns the mean loss (host float) when ``read_loss``."""
+        e = self.engine
+        if qat != e.qat:
+            e.qat = qat
+            e.cast_weights()
+        e.zero_grads()
+        e.set_hp(lr_scale, momentum)
+        dev_spans = spans if staged else self.stage_spans(spans)
+        for sp in dev_spans:
+            e.micro_step_span(sp, len(dev_spans))
+        if self.dist is not None:
+            self.dist.step()
+        else:
+            e.clip()
+            e.optimizer_step()
+        if read_loss:
+            return float(e.loss_sum[0]) / (e.T * len(dev_spans))
+        return None
 
     def sync_params(self):
         return self.engine.p

@@ -30,8 +30,33 @@ def load():
     spec = importlib.util.spec_from_file_location("parameter_golf_b200._C", _build.LIB)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
-    _C = mod
-    return mod
+    _C = _Counting(mod)
+    return _C
+
+
+class _Counting:
+    """Forwards to the extension and counts kernel launches issued through it (`launch_count`)."""
+
+    _PER_CALL = {"attn_bwd": 2}
+
+    def __init__(self, mod):
+        self._mod = mod
+        self.launches = 0
+
+    def __getattr__(self, name):
+        fn = getattr(self._mod, name)
+        n = self._PER_CALL.get(name, 1)
+
+        def call(*a, **k):
+            self.launches += n
+            return fn(*a, **k)
+
+        self.__dict__[name] = call
+        return call
+
+
+def launch_count() -> int:
+    return 0 if _C is None else _C.launches
 
 
 def available() -> bool:

@@ -23,7 +23,7 @@ int* status_ptr(const c10::optional<torch::Tensor>& status) {
 // a_kmajor: A is [.., M, K]; otherwise A is [.., K, M]. Same for B with N.
 void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor D, bool a_kmajor, bool b_kmajor, int64_t epi, double alpha, double beta,
           double slope, c10::optional<torch::Tensor> aux, c10::optional<torch::Tensor> colscale, c10::optional<torch::Tensor> D2,
-          int64_t splits, c10::optional<torch::Tensor> status) {
+          int64_t splits, c10::optional<torch::Tensor> status, c10::optional<torch::Tensor> wait_flag, int64_t wait_value) {
   check_bf16(A, "A");
   check_bf16(B, "B");
   TORCH_CHECK(A.dim() == B.dim() && A.dim() == D.dim() && (A.dim() == 2 || A.dim() == 3), "gemm: operands must all be 2-D or all 3-D");
@@ -78,6 +78,11 @@ void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor D, bool a_kmajor, bool
   g.slope = (float)slope;
   g.splits = (int)splits;
   g.status = status_ptr(status);
+  if (wait_flag.has_value()) {
+    TORCH_CHECK(wait_flag->is_cuda() && wait_flag->scalar_type() == torch::kInt32, "wait_flag must be a CUDA int32 tensor");
+    g.wait_flag = wait_flag->data_ptr<int>();
+    g.wait_value = (int)wait_value;
+  }
   pgb::gemm_bf16(g, cur_stream());
 }
 

@@ -38,6 +38,8 @@ struct GemmKernelParams {
   const float* colscale;
   float alpha, beta, slope;
   int* status;
+  const int* wait_flag;   // optional: B (the weights) is valid once *wait_flag >= wait_value (peer ranks push it)
+  int wait_value;
 };
 
 template <int BN>
@@ -191,6 +193,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if (p.wait_flag != nullptr) {
+        // The weight operand is written by peer GPUs (parameter all-gather fused here): poll the per-layer
+        // ready counter, bounded, then order the peer's generic-proxy stores before this CTA's TMA reads.
+        int seen;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.wait_flag) : "memory");
+        if (seen < p.wait_value) {
+          const uint64_t t0 = globaltimer_ns();
+          while (true) {
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.wait_flag) : "memory");
+            if (seen >= p.wait_value) break;
+            if (globaltimer_ns() - t0 > PGB_WAIT_LIMIT_NS) {
+              *abort_flag = 1;
+              report(p.status, ST_WAIT_FLAG, p.wait_value);
+              ok = false;
+              break;
+            }
+            __nanosleep(128);
+          }
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+      }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int b = tile / tiles_per_batch;
         int r = tile - b * tiles_per_batch;
@@ -390,6 +413,8 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   p.D = a.D; p.D2 = a.D2; p.aux = a.aux; p.colscale = a.colscale;
   p.alpha = a.alpha; p.beta = a.beta; p.slope = a.slope;
   p.status = a.status;
+  p.wait_flag = a.wait_flag;
+  p.wait_value = a.wait_value;
   const CUtensorMap ma = operand_map(a.A, a.a_kmajor, a.M, a.K, a.lda, a.stride_a, a.batch, BM);
   const CUtensorMap mb = operand_map(a.B, a.b_kmajor, a.N, a.K, a.ldb, a.stride_b, a.batch, bn);
   const int total = p.tiles_m * p.tiles_n * p.splits * a.batch;

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <stdexcept>
+#include <string>
 
 namespace pgb {
 
@@ -35,6 +36,8 @@ struct GemmArgs {
   int splits = 0;            // 0 = automatic
   float alpha = 1.f, beta = 0.f, slope = 0.f;
   int* status = nullptr;     // device status word (4 ints) or null
+  const int* wait_flag = nullptr;   // optional readiness counter for B (see comm.cu); polled with a bounded wait
+  int wait_value = 0;
 };
 
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
@@ -77,6 +80,23 @@ void muon_apply(float* p, const void* X, float* ema, const float* hp, long long 
 void adamw(float* p, const float* g, float* m, float* v, float* ema, const float* hp, long long n, float base_lr, float b1, float b2, float eps,
            float wd, float decay, cudaStream_t st);
 void sgd_momentum(float* p, const float* g, float* mom, const float* hp, long long n, float lr, float mu, cudaStream_t st);
+
+// ---- peer-memory collectives (comm.cu) and symmetric memory (symm.cpp) --------------------------------------------------
+void comm_barrier(int* const* sig_tbl, int my_rank, int world, int slot, int epoch, int* status, cudaStream_t st);
+void comm_reduce_peers(const float* const* src_tbl, int world, long long off, long long n, float* out, float scale, float* stats, float sq_weight,
+                       cudaStream_t st);
+void comm_scalar_allreduce(float* const* val_tbl, int* const* sig_tbl, int my_rank, int world, int val_slot, int sig_slot, int epoch, float* stats,
+                           int* status, cudaStream_t st);
+void comm_push_cast_rows(const float* src, void* const* dst_tbl, int world, long long dst_off, const float* rowscale, int scale_stride, int scale_mod,
+                         int rows, int cols, long long ld_dst, int qat, cudaStream_t st);
+void comm_push_copy(const float* src, float* const* dst_tbl, int world, int my_rank, long long off, long long n, cudaStream_t st);
+void comm_flag_add(int* const* sig_tbl, int world, int slot, int count, int value, cudaStream_t st);
+void comm_wait_flag(const int* flag, int want, int* status, cudaStream_t st);
+void* symm_alloc(size_t bytes);
+std::string symm_export(void* p);
+void* symm_import(const std::string& handle);
+void symm_close(void* p);
+void symm_free(void* p);
 
 // ---- misc (misc.cu) ------------------------------------------------------------------------------------------------------
 void expand_span_u16(const void* span, int* ids, int* targets, int n, cudaStream_t st);

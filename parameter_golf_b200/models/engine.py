@@ -80,7 +80,8 @@ class CudaEngine:
         self.stats = torch.zeros(4, dtype=torch.float32, device=self.dev)
         self.loss_sum = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.adam_t = 0
-        self.launches = 0
+        self.layer_flags = None          # set by the sharded optimizer: per-layer weight-ready counters
+        self.layer_flag_value = 0
         self.cast_weights()
 
     # ---- storage -----------------------------------------------------------------------------------------------
@@ -192,24 +193,23 @@ class CudaEngine:
                 self.d_bg = buf(T, m.bigram.dim)
 
     # ---- weights --------------------------------------------------------------------------------------------------
-    def cast_weights(self):
-        """fp32 master -> bf16 compute copies (packed QKV, output scales folded in, optional int6 fake-quant)."""
+    def cast_weights(self, banks: bool = True):
+        """fp32 master -> bf16 compute copies (packed QKV, output scales folded in, optional int6 fake-quant).
+        With ``banks=False`` only the replicated tables are refreshed (the sharded optimizer pushes bank weights itself)."""
         C, p, n, d, kv = self.C, self.p, self.n, self.d, self.kv
         q = self.qat
-        for i in range(n):       # packed [q; k; v] rows per layer
-            C.cast_rows(p["qo_bank"][i], self.Wqkv[i, :d], None, 0, 1, q)
-            C.cast_rows(p["kv_bank"][i], self.Wqkv[i, d:d + kv], None, 0, 1, q)
-            C.cast_rows(p["kv_bank"][n + i], self.Wqkv[i, d + kv:], None, 0, 1, q)
-        self.launches += 3 * n
-        C.cast_rows(p["qo_bank"][n:], self.Wo, p["attn_scale"], 1, n * d, q)
-        C.cast_rows(p["mlp_up_bank"], self.Wup, None, 0, 1, q)
-        C.cast_rows(p["mlp_down_bank"], self.Wd, p["mlp_scale"], 1, n * d, q)
+        if banks:
+            for i in range(n):       # packed [q; k; v] rows per layer
+                C.cast_rows(p["qo_bank"][i], self.Wqkv[i, :d], None, 0, 1, q)
+                C.cast_rows(p["kv_bank"][i], self.Wqkv[i, d:d + kv], None, 0, 1, q)
+                C.cast_rows(p["kv_bank"][n + i], self.Wqkv[i, d + kv:], None, 0, 1, q)
+            C.cast_rows(p["qo_bank"][n:], self.Wo, p["attn_scale"], 1, n * d, q)
+            C.cast_rows(p["mlp_up_bank"], self.Wup, None, 0, 1, q)
+            C.cast_rows(p["mlp_down_bank"], self.Wd, p["mlp_scale"], 1, n * d, q)
         C.cast_rows(p["tok_emb"], self.E, None, 0, 1, False)
-        self.launches += 4
         if self.m.bigram.enabled:
             C.cast_rows(p["bigram_embed"], self.BE, None, 0, 1, False)
             C.cast_rows(p["bigram_proj"], self.BP, p["bigram_scale"], 0, 1, False)
-            self.launches += 2
         if self.m.value_embedding.enabled:
             C.cast_rows(p["ve_embed"], self.VE, None, 0, 1, False)
             torch.mul(p["ve_layer_scales"], p["ve_scale"], out=self.ve_eff)
@@ -287,7 +287,10 @@ class CudaEngine:
             if self.unet and l >= self.enc and skips:
                 skip, sw = skips.pop(), p["skip_weights"][l - self.enc]
             C.mix_norm_fwd(x, self.x0, skip, sw, p["resid_mix"][l], self.x_in[li], self.h[li], s_l, self.eps)
-            N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li])
+            if self.layer_flags is not None:
+                N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li], wait_flag=self.layer_flags[l:l + 1], wait_value=self.layer_flag_value)
+            else:
+                N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li])
             if m.value_embedding.enabled and l in m.value_embedding.layers:
                 vi = m.value_embedding.layers.index(l)
                 vview = self.qkv_pre[li][:, d + kv:]
@@ -594,6 +597,12 @@ class EngineBackend:
             e.optimizer_step()
         return float(e.loss_sum[0]) / (e.T * len(batches))
 
+    def host_spans(self, count: int):
+        """Pinned host staging buffers for `count` micro-batch spans of T+1 uint16 tokens (stored as int16)."""
+        if not hasattr(self, "_span_host") or len(self._span_host) < count:
+            self._span_host = [torch.empty(self.engine.T + 1, dtype=torch.int16).pin_memory() for _ in range(count)]
+        return self._span_host[:count]
+
     def stage_spans(self, spans):
         """Copy uint16 spans (pinned host or device tensors of T+1 tokens, viewed as int16) into device staging buffers."""
         e = self.engine
@@ -609,7 +618,8 @@ class EngineBackend:
         e = self.engine
         if qat != e.qat:
             e.qat = qat
-            e.cast_weights()
+            # the sharded optimizer re-pushes every bank weight at the end of this step with the new setting
+            e.cast_weights(banks=self.dist is None or not self.dist.sharded)
         e.zero_grads()
         e.set_hp(lr_scale, momentum)
         dev_spans = spans if staged else self.stage_spans(spans)
@@ -624,8 +634,21 @@ class EngineBackend:
             return float(e.loss_sum[0]) / (e.T * len(dev_spans))
         return None
 
+    fused_ema = True
+
     def sync_params(self):
         return self.engine.p
+
+    def final_params(self, ema: bool = False):
+        """CPU fp32 parameter dict (EMA weights when requested), with sharded banks gathered from their owners."""
+        e = self.engine
+        if self.dist is not None and self.dist.sharded:
+            for k, v in self.dist.gather_banks(e.p).items():
+                e.p[k].copy_(v)
+            if ema and e.ema is not None:
+                for k, v in self.dist.gather_banks(e.ema).items():
+                    e.ema[k].copy_(v)
+        return e.export_params(ema=ema)
 
     def params_changed(self):
         self.engine.cast_weights()

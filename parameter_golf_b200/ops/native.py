@@ -84,8 +84,9 @@ def check_status(device=None, reset: bool = True):
         raise RuntimeError(f"kernel wait timed out: {STATUS_NAMES.get(code, code)} (block {block}, detail {detail}, {count} reports)")
 
 
-def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.0, slope=0.0, aux=None, colscale=None, D2=None, splits=0):
-    load().gemm(A, B, D, a_kmajor, b_kmajor, epi, alpha, beta, slope, aux, colscale, D2, splits, status_word(A.device))
+def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.0, slope=0.0, aux=None, colscale=None, D2=None, splits=0,
+         wait_flag=None, wait_value=0):
+    load().gemm(A, B, D, a_kmajor, b_kmajor, epi, alpha, beta, slope, aux, colscale, D2, splits, status_word(A.device), wait_flag, wait_value)
     return D
 
 

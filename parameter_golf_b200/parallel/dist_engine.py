@@ -1,0 +1,204 @@
+"""Distributed optimizer step on peer memory: sharded Parallel Muon and the replicated all-reduce variant.
+
+Sharded Parallel Muon (``distributed_optimizer_backend = "sharded_parallel_muon"``), per step, after the last backward:
+
+1. barrier kernel — every rank's gradients are complete;
+2. `comm_reduce_peers`: each rank sums the fp32 bank gradients of the slots it owns straight out of every peer's
+   gradient buffer (reduce-scatter, 1/world scale and global-norm partial in one pass), and all ranks sum the small
+   replicated gradients (one-shot all-reduce);
+3. `comm_scalar_allreduce`: exact global gradient norm; it also tells every rank that its gradients were consumed;
+4. AdamW on the replicated parameters (identical on every rank); Muon momentum + Newton–Schulz + update on the owned
+   bank slots only (fp32 master weights of a slot live on its owner);
+5. `comm_push_cast_rows`: the owner writes the new bf16 compute weights (packed QKV rows, output scales folded in,
+   optional int6 fake-quant) into EVERY rank's weight buffer and bumps that layer's ready counter on every rank;
+   the next forward's QKV GEMM of that layer polls the counter before its first TMA load — the parameter
+   all-gather is overlapped with the start of the next step instead of being waited for.
+
+Ownership follows the reference: a bank of B slots is padded to a multiple of world and cut in contiguous chunks of
+``ceil(B/world)`` slots (``parameter-golf-rs/crates/pg-train/src/lib.rs:577-591,733-813``; Python
+``records/track_10min_16mb/2026-03-23_LeakyReLU_LegalTTT_ParallelMuon/train_gpt.py:152-166``).
+
+The replicated variant all-reduces every gradient with the same kernels (two-shot for the banks) and then runs the
+single-GPU optimizer on every rank.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..models import gpt
+from ..ops import native as N
+from ..spec import RunSpec
+from .symm import SymmetricBuffer
+
+BF = torch.bfloat16
+SIG_BARRIER, SIG_SCALAR, SIG_BARRIER2, SIG_LAYER = 0, 32, 64, 128      # slots in the int32 signal pad
+
+
+def shard_range(slots: int, rank: int, world: int) -> Tuple[int, int]:
+    """[start, end) slots of a bank owned by ``rank`` (may be empty for trailing ranks)."""
+    chunk = -(-slots // world)
+    s0 = min(rank * chunk, slots)
+    return s0, min(s0 + chunk, slots)
+
+
+class DistributedStep:
+    def __init__(self, engine, spec: RunSpec, group=None):
+        self.e, self.spec, self.group = engine, spec, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.sharded = spec.train.distributed_optimizer_backend == "sharded_parallel_muon"
+        self.C = N.load()
+        self.epoch = 0
+        self.steps_done = 0
+        e = engine
+        # ---- re-home gradients into one symmetric fp32 region: [banks ... | flat groups ...] ---------------------
+        self.g_off: Dict[str, int] = {}
+        off = 0
+        for k in gpt.BANKS:
+            self.g_off[k] = off
+            off += e.g[k].numel()
+        self.grp_off: List[int] = []
+        for grp in e.groups:
+            self.grp_off.append(off)
+            off += grp["g"].numel()
+        self.g_total = off
+        self.gbuf = SymmetricBuffer(off * 4, group)
+        for k in gpt.BANKS:
+            new = self.gbuf.view(self.g_off[k] * 4, e.g[k].shape, torch.float32)
+            new.copy_(e.g[k])
+            e.g[k] = new
+        for gi, grp in enumerate(e.groups):
+            flat = self.gbuf.view(self.grp_off[gi] * 4, (grp["g"].numel(),), torch.float32)
+            flat.copy_(grp["g"])
+            grp["g"] = flat
+            o = 0
+            for name in grp["names"]:
+                nel = e.p[name].numel()
+                e.g[name] = flat[o:o + nel].view(e.p[name].shape)
+                o += -(-nel // 4) * 4
+            grp["g_red"] = torch.zeros_like(flat) if self.sharded else flat
+        # ---- re-home the bf16 bank weights into a symmetric region -------------------------------------------------------
+        self.w_off: Dict[str, int] = {}
+        off = 0
+        for name in ("Wqkv", "Wo", "Wup", "Wd"):
+            self.w_off[name] = off
+            off += getattr(e, name).numel()
+        self.wbuf = SymmetricBuffer(off * 2, group)
+        for name in ("Wqkv", "Wo", "Wup", "Wd"):
+            old = getattr(e, name)
+            new = self.wbuf.view(self.w_off[name] * 2, old.shape, BF)
+            new.copy_(old)
+            setattr(e, name, new)
+        self.sig = SymmetricBuffer(1024 * 4, group)
+        self.val = SymmetricBuffer(256 * 4, group)
+        self.sig_local = self.sig.view(0, (1024,), torch.int32)
+        e.layer_flags = self.sig_local[SIG_LAYER:SIG_LAYER + e.n] if self.sharded else None
+        e.layer_flag_value = 0
+        self.own = {k: shard_range(e.p[k].shape[0], self.rank, self.world) for k in gpt.BANKS}
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    # ---- pieces ------------------------------------------------------------------------------------------------------------
+    def _barrier(self, slot):
+        self.C.comm_barrier(self.sig.table, self.rank, self.world, slot, self.epoch, N.status_word())
+
+    def _push_slot(self, bank: str, s: int):
+        """Write the bf16 compute rows of bank slot ``s`` into every rank and bump that layer's ready counter."""
+        e, C = self.e, self.C
+        n, d, kv, mlp, q = e.n, e.d, e.kv, e.mlp, e.qat
+        src = e.p[bank][s]
+        if bank == "qo_bank" and s < n:
+            layer, dst, ld, rs = s, self.w_off["Wqkv"] + s * e.qkvw * d, d, None
+        elif bank == "qo_bank":
+            layer = s - n
+            dst, ld, rs = self.w_off["Wo"] + layer * d * d, d, e.p["attn_scale"][layer]
+        elif bank == "kv_bank":
+            layer = s % n
+            dst, ld, rs = self.w_off["Wqkv"] + layer * e.qkvw * d + (d if s < n else d + kv) * d, d, None
+        elif bank == "mlp_up_bank":
+            layer, dst, ld, rs = s, self.w_off["Wup"] + s * mlp * d, d, None
+        else:
+            layer, dst, ld, rs = s, self.w_off["Wd"] + s * d * mlp, mlp, e.p["mlp_scale"][s]
+        C.comm_push_cast_rows(src, self.wbuf.table, self.world, dst, rs, 1 if rs is not None else 0, src.shape[0] if rs is not None else 1, ld, q)
+        C.comm_flag_add(self.sig.table, self.world, SIG_LAYER + layer, 1, 1)
+
+    def step(self):
+        if self.sharded:
+            self._step_sharded()
+        else:
+            self._step_replicated()
+        self.steps_done += 1
+
+    def _step_sharded(self):
+        e, C, t = self.e, self.C, self.spec.train
+        w = self.world
+        self.epoch += 1
+        self._barrier(SIG_BARRIER)
+        for gi, grp in enumerate(e.groups):
+            C.comm_reduce_peers(self.gbuf.table, w, self.grp_off[gi], grp["g"].numel(), grp["g_red"], 1.0 / w, e.stats, 1.0 / w)
+        for k in gpt.BANKS:
+            s0, s1 = self.own[k]
+            if s1 > s0:
+                per = e.p[k][0].numel()
+                C.comm_reduce_peers(self.gbuf.table, w, self.g_off[k] + s0 * per, (s1 - s0) * per, e.g[k][s0:s1], 1.0 / w, e.stats, 1.0)
+        C.comm_scalar_allreduce(self.val.table, self.sig.table, self.rank, w, 0, SIG_SCALAR, self.epoch, e.stats, N.status_word())
+        C.clip_factor(e.stats, e.hp, 1.0, max(t.grad_clip_norm, 0.0))
+        decay = t.ema_decay
+        for grp in e.groups:
+            if grp["p"].numel():
+                C.adamw(grp["p"], grp["g_red"], grp["m"], grp["v"], grp.get("ema"), e.hp, grp["lr"], t.adam_beta1, t.adam_beta2, t.adam_eps, t.adam_wd, decay)
+        for k in sorted(gpt.BANKS, key=lambda b: -e.p[b].numel()):
+            s0, s1 = self.own[k]
+            if s1 <= s0:
+                continue
+            cnt = s1 - s0
+            st = e.ns[k]
+            st["sq"].zero_()
+            C.muon_momentum(e.g[k][s0:s1], e.mom[k][s0:s1], st["U"][:cnt], st["sq"][:cnt], e.hp, True)
+            C.muon_normalize(st["U"][:cnt], st["X0"][:cnt], st["sq"][:cnt], 1e-7)
+            X = e.newton_schulz(k, cnt)
+            scale = max(1.0, e.p[k].shape[-2] / e.p[k].shape[-1]) ** 0.5
+            C.muon_apply(e.p[k][s0:s1].view(-1), X.reshape(-1), e.ema[k][s0:s1].view(-1) if e.ema else None, e.hp, t.matrix_lr, t.muon_wd, scale, decay)
+            for s in range(s0, s1):
+                self._push_slot(k, s)
+        e.cast_weights(banks=False)
+        e.layer_flag_value = 6 * (self.steps_done + 1)
+
+    def _step_replicated(self):
+        """Two-shot all-reduce of every gradient (reduce my slice from all peers, write it back to all peers), then the
+        ordinary replicated optimizer on every rank."""
+        e, C, t = self.e, self.C, self.spec.train
+        w = self.world
+        self.epoch += 1
+        self._barrier(SIG_BARRIER)
+        n4 = self.g_total // 4
+        a, b = (n4 * self.rank // w) * 4, (n4 * (self.rank + 1) // w) * 4
+        mine = self.gbuf.view(a * 4, (b - a,), torch.float32)
+        C.comm_reduce_peers(self.gbuf.table, w, a, b - a, mine, 1.0 / w, None, 0.0)
+        self._barrier(SIG_BARRIER2)                      # every slice is reduced before anyone overwrites a peer's copy
+        C.comm_push_copy(mine, self.gbuf.table, w, self.rank, a)
+        self.epoch += 1
+        self._barrier(SIG_BARRIER)
+        e.clip()
+        e.optimizer_step()
+
+    # ---- parameter gathering for export / evaluation --------------------------------------------------------------------------------
+    def gather_banks(self, source: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """Full fp32 banks on every rank from the owners' authoritative slots (control-plane collective, end of run)."""
+        out = {}
+        for k in gpt.BANKS:
+            full = source[k].clone()
+            if self.sharded:
+                for r in range(self.world):
+                    s0, s1 = shard_range(full.shape[0], r, self.world)
+                    if s1 > s0:
+                        dist.broadcast(full[s0:s1], src=dist.get_global_rank(self.group, r) if self.group else r, group=self.group)
+            out[k] = full
+        return out
+
+    def close(self):
+        for b in (self.gbuf, self.wbuf, self.sig, self.val):
+            b.close()

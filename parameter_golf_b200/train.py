@@ -224,7 +224,8 @@ class VariantRunner:
         # ---- model + backend ------------------------------------------------------------------------
         params = gpt.init_params(m, t.seed, device="cpu")
         backend = self._make_backend(params)
-        ema = Ema(t.ema_decay) if t.ema_decay > 0 else None
+        fused_ema = getattr(backend, "fused_ema", False)       # CUDA engine: EMA is updated inside the optimizer kernels
+        ema = Ema(t.ema_decay) if (t.ema_decay > 0 and not fused_ema) else None
         swa = Swa(t.swa_every, t.swa_threshold) if t.swa_enabled else None
         step0 = 0
         if t.resume_from:
@@ -267,12 +268,17 @@ class VariantRunner:
                 log.info(f"late_qat:enabled step:{step} scale:{scale:.4f}")
             mom = muon_momentum_at(step, t.muon_momentum_warmup_start, t.muon_momentum, t.muon_momentum_warmup_steps)
             with timers.time("data"):
-                batches = []
-                for _ in range(accum):
-                    x, y = loader.next_batch(tokens_per_step, t.seq_len, accum)
-                    batches.append((torch.from_numpy(x), torch.from_numpy(y)))
+                batches, spans = [], None
+                if hasattr(backend, "train_step_spans"):
+                    spans = backend.host_spans(accum)          # pinned uint16 staging buffers (2 bytes per token over PCIe)
+                    for buf in spans:
+                        loader.next_span_u16(tokens_per_step, accum, out=buf.numpy().view(np.uint16))
+                else:
+                    for _ in range(accum):
+                        x, y = loader.next_batch(tokens_per_step, t.seq_len, accum)
+                        batches.append((torch.from_numpy(x), torch.from_numpy(y)))
             with timers.time("train_step"):
-                loss = backend.train_step(batches, scale, mom, qat)
+                loss = backend.train_step_spans(spans, scale, mom, qat) if spans is not None else backend.train_step(batches, scale, mom, qat)
             step += 1
             if step == step0 + 1:
                 res.train_loss_first = loss
@@ -281,7 +287,7 @@ class VariantRunner:
                 with timers.time("ema"):
                     ema.update(backend.sync_params())
             if swa is not None and swa.should_collect(step, scale):
-                swa.collect(backend.sync_params())
+                swa.collect(backend.final_params(ema=False) if fused_ema else backend.sync_params())
             now_ms = train_ms + 1000.0 * (time.perf_counter() - t_start)
             if t.train_log_every > 0 and (step <= 10 or step % t.train_log_every == 0 or step == max_steps):
                 log.info(f"step:{step}/{max_steps} train_loss:{loss:.4f} train_time:{now_ms:.0f}ms step_avg:{now_ms / (step - step0):.2f}ms")
@@ -298,7 +304,12 @@ class VariantRunner:
             log.info(f"peak memory allocated: {res.peak_mem_mib} MiB")
 
         # ---- weight averaging, export, budget ---------------------------------------------------------
-        final = {k: v.detach().cpu().float().clone() for k, v in backend.sync_params().items()}
+        if fused_ema:
+            final = backend.final_params(ema=t.ema_decay > 0)
+            if t.ema_decay > 0:
+                log.info("ema:applying EMA weights")
+        else:
+            final = {k: v.detach().cpu().float().clone() for k, v in backend.sync_params().items()}
         if swa is not None and swa.count > 1:
             log.info(f"swa:applying {swa.count} snapshots")
             final = {k: v.cpu() for k, v in swa.average().items()}

@@ -127,3 +127,22 @@ def test_short_training_trajectory_tracks_oracle():
         lg.append(gpu.train_step([(ids, tgt)], 1.0, 0.95, False))
         lc.append(cpu.train_step([(ids, tgt)], 1.0, 0.95, False))
     assert lg[-1] < lg[0] and all(abs(a - b) < 0.02 * max(1.0, abs(b)) for a, b in zip(lg, lc)), (lg, lc)
+
+
+def test_bounded_wait_times_out_and_reports():
+    """A flag that nothing sets: the kernel gives up after its time limit, writes the status word and returns;
+    the context stays usable."""
+    from parameter_golf_b200.ops import native
+    C = native.load()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    native.status_word().zero_()
+    C.comm_wait_flag(flag, 1, native.status_word())
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="wait_flag"):
+        native.check_status()
+    native.check_status()                                   # cleared
+    flag.fill_(3)
+    C.comm_wait_flag(flag, 1, native.status_word())
+    torch.cuda.synchronize()
+    native.check_status()
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0

@@ -157,11 +157,12 @@ orig = sp.RunSpec.validate
 sp.RunSpec.validate = lambda self: self
 res = VariantRunner(s, RunLog('r', rank=dist.get_rank(), console=False)).run()
 blob = open(s.train.artifact_path, 'rb').read() if dist.get_rank() == 0 else b''
-print('OK', dist.get_rank(), res.steps, res.val_bpb)
+print('OK', dist.get_rank(), res.steps, res.val_bpb, flush=True)
 """)
     env = dict(os.environ, PGB_DATA_ROOT=str(tmp_path / "d"), PYTHONPATH=ROOT)
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
                           "--master-port", "29611", str(script)], capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
     assert out.returncode == 0, out.stderr[-3000:]
-    oks = [l.split() for l in out.stdout.splitlines() if l.startswith("OK")]
-    assert len(oks) == 2 and oks[0][3] == oks[1][3]          # identical reduced val_bpb on both ranks
+    import re
+    oks = re.findall(r"OK (\d) (\d+) ([0-9.eE+-]+)", out.stdout)
+    assert len(oks) == 2 and oks[0][2] == oks[1][2], out.stdout[-500:]          # identical reduced val_bpb on both ranks

@@ -45,20 +45,34 @@ __global__ void __launch_bounds__(256) cast_rows_kernel(const float* __restrict_
   }
 }
 
-// Fold the gradient of a row-scaled weight:  W_eff = scale[r] * fq(W)  =>  dW += scale[r] * G,  dscale[r] += sum_c fq(W)[r,c] * G[r,c].
-__global__ void __launch_bounds__(256) fold_scaled_grad_kernel(const float* __restrict__ G, const float* __restrict__ W, const float* __restrict__ rowscale,
+// Fold the gradient of a row-scaled weight:  W_eff = scale[r] * Wq  =>  dW += scale[r] * G,  dscale[r] += sum_c Wq[r,c] * G[r,c].
+// Wq is the un-scaled weight as the forward saw it: either the fp32 master (optionally fake-quantised here) or the
+// un-scaled bf16 compute copy (already fake-quantised when QAT is on; this is what non-owner ranks of a sharded bank have).
+template <typename WT>
+__device__ __forceinline__ float4 load_w4(const WT* p);
+template <>
+__device__ __forceinline__ float4 load_w4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 load_w4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 q = *reinterpret_cast<const uint2*>(p);
+  const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename WT>
+__global__ void __launch_bounds__(256) fold_scaled_grad_kernel(const float* __restrict__ G, const WT* __restrict__ W, const float* __restrict__ rowscale,
                                                                int scale_stride, int scale_mod, float* __restrict__ dW, float* __restrict__ dscale,
                                                                int rows, int cols, int qat) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
     const float* g = G + (size_t)row * cols;
-    const float* w = W + (size_t)row * cols;
+    const WT* w = W + (size_t)row * cols;
     float* o = dW + (size_t)row * cols;
     float qs = 0.f;
     if (qat) {
       float mx = 0.f;
       for (int c = lane * 4; c < cols; c += 128) {
-        float4 a = *reinterpret_cast<const float4*>(w + c);
+        float4 a = load_w4<WT>(w + c);
         mx = fmaxf(mx, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
       }
       mx = warp_max(mx);
@@ -68,7 +82,7 @@ __global__ void __launch_bounds__(256) fold_scaled_grad_kernel(const float* __re
     const float rs = rowscale[sidx];
     float dot = 0.f;
     for (int c = lane * 4; c < cols; c += 128) {
-      float4 a = *reinterpret_cast<const float4*>(w + c);
+      float4 a = load_w4<WT>(w + c);
       float4 gg = *reinterpret_cast<const float4*>(g + c);
       if (qat) {
         a.x = fminf(fmaxf(rintf(a.x / qs), -32.f), 31.f) * qs;
@@ -234,8 +248,15 @@ void cast_rows(const float* src, void* dst, const float* rowscale, int scale_str
 void fold_scaled_grad(const float* G, const float* W, const float* rowscale, int scale_stride, int scale_mod, float* dW, float* dscale, int rows,
                       int cols, int qat, cudaStream_t st) {
   if (cols % 4) throw std::runtime_error("fold_scaled_grad: cols must be a multiple of 4");
-  fold_scaled_grad_kernel<<<std::min((rows + 7) / 8, 148 * 8), 256, 0, st>>>(G, W, rowscale, scale_stride, std::max(scale_mod, 1), dW, dscale, rows,
-                                                                            cols, qat);
+  fold_scaled_grad_kernel<float><<<std::min((rows + 7) / 8, 148 * 8), 256, 0, st>>>(G, W, rowscale, scale_stride, std::max(scale_mod, 1), dW, dscale,
+                                                                                   rows, cols, qat);
+}
+
+void fold_scaled_grad_bf16(const float* G, const void* W, const float* rowscale, int scale_stride, int scale_mod, float* dW, float* dscale, int rows,
+                           int cols, cudaStream_t st) {
+  if (cols % 4) throw std::runtime_error("fold_scaled_grad: cols must be a multiple of 4");
+  fold_scaled_grad_kernel<__nv_bfloat16><<<std::min((rows + 7) / 8, 148 * 8), 256, 0, st>>>(G, (const __nv_bfloat16*)W, rowscale, scale_stride,
+                                                                                           std::max(scale_mod, 1), dW, dscale, rows, cols, 0);
 }
 
 void sumsq(const float* x, long long n, float scale, float* out, cudaStream_t st) { sumsq_kernel<<<ew_grid(n, 4), 256, 0, st>>>(x, n, scale, out); }

@@ -65,12 +65,24 @@ void embed_gather(const int* ids, const void* table, void* out, int rows, int d,
 void embed_scatter_add(const int* ids, const void* g, float* dtable, int rows, int d, int table_rows, int bigram_buckets, int seq_len,
                        cudaStream_t st);
 
+// tuned variants (rowops_fast.cu), called by the launchers above when their preconditions hold
+void mix_norm_bwd_v2(const void* d_h, const void* d_res, const void* x_in, const void* x, const void* x0, const void* skip, const float* sw,
+                     const float* mix, const void* add_grad, void* d_x, void* d_x0, void* d_skip, float* d_mix, float* d_sw, int skip_to_dx, int rows,
+                     int d, float s, float eps, cudaStream_t st);
+bool qk_norm_rope_fast_ok(int H, int hd, int rope_dims);
+void qk_norm_rope_fwd64(const void* src, void* dst, const float* cosT, const float* sinT, const float* gain, int rows, int ld, int H, int Hkv,
+                        int rope_dims, int seq_len, float eps, cudaStream_t st);
+void qk_norm_rope_bwd64(const void* d_post, const void* pre, void* d_pre, const float* cosT, const float* sinT, const float* gain, float* d_gain,
+                        int rows, int ld, int H, int Hkv, int rope_dims, int seq_len, float eps, cudaStream_t st);
+
 // ---- optimizer / weight preparation (optim.cu) --------------------------------------------------------------------------
 // hp: device fp32[8] = {lr_scale, muon_momentum, adam_bias_corr1, adam_bias_corr2, grad_scale, ...}
 void cast_rows(const float* src, void* dst, const float* rowscale, int scale_stride, int scale_mod, int rows, int cols, long long ld_dst, int qat,
                cudaStream_t st);
 void fold_scaled_grad(const float* G, const float* W, const float* rowscale, int scale_stride, int scale_mod, float* dW, float* dscale, int rows,
                       int cols, int qat, cudaStream_t st);
+void fold_scaled_grad_bf16(const float* G, const void* W, const float* rowscale, int scale_stride, int scale_mod, float* dW, float* dscale, int rows,
+                           int cols, cudaStream_t st);
 void sumsq(const float* x, long long n, float scale, float* out, cudaStream_t st);
 void clip_factor(float* stats, float* hp, float base_scale, float max_norm, cudaStream_t st);
 void muon_momentum(const float* g, float* buf, void* U, float* sumsq_out, const float* hp, int matrices, long long per_matrix, int nesterov,

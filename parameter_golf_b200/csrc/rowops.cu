@@ -719,6 +719,10 @@ void mix_norm_fwd(const void* x, const void* x0, const void* skip, const float* 
 void mix_norm_bwd(const void* d_h, const void* d_res, const void* x_in, const void* x, const void* x0, const void* skip, const float* sw,
                   const float* mix, const void* add_grad, void* d_x, void* d_x0, void* d_skip, float* d_mix, float* d_sw, int skip_to_dx, int rows,
                   int d, float s, float eps, cudaStream_t st) {
+  if (d <= 1536) {      // specialised variants (no accumulators when there is no mix/skip term, two CTAs per SM)
+    mix_norm_bwd_v2(d_h, d_res, x_in, x, x0, skip, sw, mix, add_grad, d_x, d_x0, d_skip, d_mix, d_sw, skip_to_dx, rows, d, s, eps, st);
+    return;
+  }
   const int grid = std::min(row_grid(rows), 148 * 4);
   PGB_NV_DISPATCH(d, (mix_norm_bwd_kernel<NV><<<grid, ROW_THREADS, ROW_WARPS * NV * 256 * sizeof(float), st>>>(
                          (const __nv_bfloat16*)d_h, (const __nv_bfloat16*)d_res, (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)x,
@@ -743,6 +747,10 @@ void norm_smear_bwd(const void* g_out, const void* xe, const float* gate, const 
 void qk_norm_rope_fwd(const void* src, void* dst, const float* cosT, const float* sinT, const float* gain, int rows, int ld, int H, int Hkv, int hd,
                       int rope_dims, int seq_len, float eps, cudaStream_t st) {
   if (hd > 256 || hd % 8) throw std::runtime_error("head_dim must be a multiple of 8 and <= 256");
+  if (qk_norm_rope_fast_ok(H, hd, rope_dims)) {
+    qk_norm_rope_fwd64(src, dst, cosT, sinT, gain, rows, ld, H, Hkv, rope_dims, seq_len, eps, st);
+    return;
+  }
   const long long n = (long long)rows * (H + Hkv);
   auto kern = hd == 64 ? qk_norm_rope_fwd_kernel<64> : qk_norm_rope_fwd_kernel<0>;
   kern<<<(unsigned)((n + 127) / 128), 128, 0, st>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, cosT, sinT, gain, rows, ld, H,
@@ -752,6 +760,10 @@ void qk_norm_rope_fwd(const void* src, void* dst, const float* cosT, const float
 void qk_norm_rope_bwd(const void* d_post, const void* pre, void* d_pre, const float* cosT, const float* sinT, const float* gain, float* d_gain,
                       int rows, int ld, int H, int Hkv, int hd, int rope_dims, int seq_len, float eps, cudaStream_t st) {
   if (hd > 256 || hd % 8) throw std::runtime_error("head_dim must be a multiple of 8 and <= 256");
+  if (qk_norm_rope_fast_ok(H, hd, rope_dims)) {
+    qk_norm_rope_bwd64(d_post, pre, d_pre, cosT, sinT, gain, d_gain, rows, ld, H, Hkv, rope_dims, seq_len, eps, st);
+    return;
+  }
   const long long n = (long long)rows * (H + Hkv);
   auto kern = hd == 64 ? qk_norm_rope_bwd_kernel<64> : qk_norm_rope_bwd_kernel<0>;
   kern<<<(unsigned)((n + 127) / 128), 128, H * sizeof(float), st>>>(

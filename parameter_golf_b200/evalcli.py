@@ -1,0 +1,105 @@
+"""Evaluation entry point: ``python -m parameter_golf_b200.evalcli --artifact a.pgrs [--spec s.toml | --family f] [--leaderboard] …``.
+
+Flow (``parameter-golf-rs/crates/pg-eval/src/bin/run.rs:6-214``): flags → spec → leaderboard-mode validation → artifact + code byte
+budget → load artifact into a fresh model → validation tokens → byte counts (SentencePiece LUT | seeded table | placeholder)
+→ dispatch (sliding | score-first TTT variants | LoRA phased) → timing and one ``eval_audit_json=`` line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+from .data.bpb import BpbLuts
+from .data.shards import load_validation_tokens
+from .eval.sliding import eval_sliding
+from .eval.ttt import eval_lora_phased_ttt, eval_score_first_ttt
+from .quant.export import check_budget, code_bytes, load_artifact
+from .spec import RunSpec, family_preset
+
+
+def leaderboard_violations(spec: RunSpec, args) -> list:
+    """Fail-closed rules for a leaderboard evaluation (``run.rs:238-306``)."""
+    bad = []
+    if spec.eval.max_tokens is not None:
+        bad.append("leaderboard evaluation must cover the full validation set (eval.max_tokens is set)")
+    if spec.eval.adaptation_backend != "none" and not spec.eval.legal_score_first:
+        bad.append("test-time adaptation must be score-first")
+    if args.bytes == "placeholder":
+        bad.append("leaderboard evaluation needs real byte counts, not the 4-bytes-per-token placeholder")
+    if not args.val_pattern:
+        bad.append("leaderboard evaluation needs --val-pattern")
+    return bad
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="parameter_golf_b200.evalcli")
+    ap.add_argument("--artifact", required=True)
+    ap.add_argument("--spec")
+    ap.add_argument("--family", default="record_11l")
+    ap.add_argument("--val-pattern")
+    ap.add_argument("--bytes", choices=["tokenizer", "seeded", "placeholder"], default="seeded")
+    ap.add_argument("--leaderboard", action="store_true")
+    ap.add_argument("--device", default="cpu")
+    ap.add_argument("--max-tokens", type=int)
+    ap.add_argument("overrides", nargs="*")
+    a = ap.parse_args(argv)
+    spec = RunSpec.load(a.spec) if a.spec else family_preset(a.family)
+    spec.apply_overrides(a.overrides)
+    if a.max_tokens is not None:
+        spec.eval.max_tokens = a.max_tokens
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo" if a.device == "cpu" else "nccl")
+    if a.leaderboard:
+        bad = leaderboard_violations(spec, a)
+        if bad:
+            print("leaderboard validation failed: " + "; ".join(bad), file=sys.stderr)
+            return 2
+    blob = open(a.artifact, "rb").read()
+    cb = code_bytes()
+    ok = check_budget(len(blob), cb, spec.quant.target_artifact_bytes)
+    print(f"artifact_bytes={len(blob)}\ncode_bytes={cb}\nbudget_ok={ok}")
+    if a.leaderboard and not ok:
+        return 3
+    m = spec.model
+    params = load_artifact(blob, spec)
+    if not a.val_pattern:
+        raise SystemExit("--val-pattern is required")
+    val = load_validation_tokens(a.val_pattern, m.eval_seq_len, spec.eval.max_tokens)
+    luts = {"tokenizer": lambda: BpbLuts.from_sentencepiece(spec.eval.tokenizer_vocab_path, m.vocab_size),
+            "seeded": lambda: BpbLuts.seeded(m.vocab_size, spec.eval.byte_table_seed),
+            "placeholder": lambda: BpbLuts.placeholder(m.vocab_size)}[a.bytes]()
+    if a.device == "cpu":
+        from .models.runner import OracleRunner
+        runner = OracleRunner(m, params)
+    else:
+        from .models.engine import EngineRunner
+        runner = EngineRunner(spec, params, a.device)
+    t0 = time.perf_counter()
+    ab = spec.eval.adaptation_backend
+    if spec.eval.legal_score_first and ab in ("full_sgd", "cpu_q_only", "lact"):
+        mode = {"full_sgd": "full_sgd", "cpu_q_only": "q_only", "lact": "lact"}[ab]
+        loss, bpb = eval_score_first_ttt(runner, val, m, spec.eval, luts, rank, world, mode, a.device, print)
+        kind = f"score_first_{mode}"
+    elif spec.eval.legal_score_first and ab == "gpu_lora_phased":
+        loss, bpb = eval_lora_phased_ttt(runner, val, m, spec.eval, luts, rank, world, a.device, print)
+        kind = "lora_phased"
+    else:
+        loss, bpb = eval_sliding(runner.nll, val, m.eval_seq_len, spec.eval.stride, luts, rank, world, spec.eval.batch_windows, a.device)
+        kind = "sliding"
+    ms = 1000.0 * (time.perf_counter() - t0)
+    if rank == 0:
+        print(f"val_loss={loss}\nval_bpb={bpb}\neval_ms={ms:.1f}\neval_kind={kind}")
+        print("eval_audit_json=" + json.dumps({"artifact": a.artifact, "artifact_bytes": len(blob), "eval_kind": kind, "stride": spec.eval.stride,
+                                               "window": m.eval_seq_len, "tokens": int(val.shape[0] - 1), "world_size": world, "bytes": a.bytes,
+                                               "fingerprint": f"{spec.fingerprint():016x}", "eval_ms": round(ms, 1),
+                                               "within_budget_s": ms / 1000.0 <= spec.eval.max_eval_seconds}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

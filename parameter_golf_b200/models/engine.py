@@ -118,6 +118,8 @@ class CudaEngine:
         self.Wo = torch.empty(n, d, d, dtype=BF, device=dev)
         self.Wup = torch.empty(n, mlp, d, dtype=BF, device=dev)
         self.Wd = torch.empty(n, d, mlp, dtype=BF, device=dev)
+        self.Wo_u = torch.empty(n, d, d, dtype=BF, device=dev)       # un-scaled copies: only read by the scale-gradient fold
+        self.Wd_u = torch.empty(n, d, mlp, dtype=BF, device=dev)
         self.E = torch.empty(m.vocab_size, d, dtype=BF, device=dev)
         if m.bigram.enabled:
             self.BE = torch.empty(m.bigram.vocab_size, m.bigram.dim, dtype=BF, device=dev)
@@ -206,6 +208,8 @@ class CudaEngine:
             C.cast_rows(p["qo_bank"][n:], self.Wo, p["attn_scale"], 1, n * d, q)
             C.cast_rows(p["mlp_up_bank"], self.Wup, None, 0, 1, q)
             C.cast_rows(p["mlp_down_bank"], self.Wd, p["mlp_scale"], 1, n * d, q)
+            C.cast_rows(p["qo_bank"][n:], self.Wo_u, None, 0, 1, q)
+            C.cast_rows(p["mlp_down_bank"], self.Wd_u, None, 0, 1, q)
         C.cast_rows(p["tok_emb"], self.E, None, 0, 1, False)
         if self.m.bigram.enabled:
             C.cast_rows(p["bigram_embed"], self.BE, None, 0, 1, False)
@@ -331,7 +335,7 @@ class CudaEngine:
             # ---- MLP
             self.Gd.zero_()
             N.gemm(self.dx, self.a[l], self.Gd, False, False, A)
-            C.fold_scaled_grad(self.Gd, p["mlp_down_bank"][l], p["mlp_scale"][l], 1, d, g["mlp_down_bank"][l], g["mlp_scale"][l], self.qat)
+            C.fold_scaled_grad_bf16(self.Gd, self.Wd_u[l], p["mlp_scale"][l], 1, d, g["mlp_down_bank"][l], g["mlp_scale"][l])
             N.gemm(self.dx, self.Wd[l], self.d_hu, True, False, N.EPI_MUL_ACTGRAD, slope=self.slope, aux=self.hu[l])
             N.gemm(self.d_hu, self.mm[l], g["mlp_up_bank"][l], False, False, A)
             N.gemm(self.d_hu, self.Wup[l], self.d_m, True, False)
@@ -340,7 +344,7 @@ class CudaEngine:
             zz = self.z[l] if l in xsa_layers else self.y[l]
             self.Go.zero_()
             N.gemm(self.dx_mid, zz, self.Go, False, False, A)
-            C.fold_scaled_grad(self.Go, p["qo_bank"][n + l], p["attn_scale"][l], 1, d, g["qo_bank"][n + l], g["attn_scale"][l], self.qat)
+            C.fold_scaled_grad_bf16(self.Go, self.Wo_u[l], p["attn_scale"][l], 1, d, g["qo_bank"][n + l], g["attn_scale"][l])
             vview = self.qkv_pre[l][:, d + kv:]
             dv = self.d_qkv_pre[:, d + kv:]
             if l in xsa_layers:
@@ -617,9 +621,11 @@ class EngineBackend:
         ``staged`` means the spans already live on this device. Returns the mean loss (host float) when ``read_loss``."""
         e = self.engine
         if qat != e.qat:
-            e.qat = qat
-            # the sharded optimizer re-pushes every bank weight at the end of this step with the new setting
-            e.cast_weights(banks=self.dist is None or not self.dist.sharded)
+            e.qat = qat                 # every rank must flip at the same step (the trainer agrees on the LR scale first)
+            if self.dist is not None:
+                self.dist.repush_weights()
+            else:
+                e.cast_weights()
         e.zero_grads()
         e.set_hp(lr_scale, momentum)
         dev_spans = spans if staged else self.stage_spans(spans)

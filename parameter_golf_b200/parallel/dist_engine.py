@@ -53,6 +53,7 @@ class DistributedStep:
         self.C = N.load()
         self.epoch = 0
         self.steps_done = 0
+        self.repushes = 0
         e = engine
         # ---- re-home gradients into one symmetric fp32 region: [banks ... | flat groups ...] ---------------------
         self.g_off: Dict[str, int] = {}
@@ -83,11 +84,11 @@ class DistributedStep:
         # ---- re-home the bf16 bank weights into a symmetric region -------------------------------------------------------
         self.w_off: Dict[str, int] = {}
         off = 0
-        for name in ("Wqkv", "Wo", "Wup", "Wd"):
+        for name in ("Wqkv", "Wo", "Wup", "Wd", "Wo_u", "Wd_u"):
             self.w_off[name] = off
             off += getattr(e, name).numel()
         self.wbuf = SymmetricBuffer(off * 2, group)
-        for name in ("Wqkv", "Wo", "Wup", "Wd"):
+        for name in ("Wqkv", "Wo", "Wup", "Wd", "Wo_u", "Wd_u"):
             old = getattr(e, name)
             new = self.wbuf.view(self.w_off[name] * 2, old.shape, BF)
             new.copy_(old)
@@ -123,7 +124,23 @@ class DistributedStep:
         else:
             layer, dst, ld, rs = s, self.w_off["Wd"] + s * d * mlp, mlp, e.p["mlp_scale"][s]
         C.comm_push_cast_rows(src, self.wbuf.table, self.world, dst, rs, 1 if rs is not None else 0, src.shape[0] if rs is not None else 1, ld, q)
+        if rs is not None:      # the un-scaled copy that the scale-gradient fold reads
+            dst_u = self.w_off["Wo_u" if bank == "qo_bank" else "Wd_u"] + layer * src.numel()
+            C.comm_push_cast_rows(src, self.wbuf.table, self.world, dst_u, None, 0, 1, ld, q)
         C.comm_flag_add(self.sig.table, self.world, SIG_LAYER + layer, 1, 1)
+
+    def repush_weights(self):
+        """Re-publish the bf16 weights of the owned slots without an update (used when the fake-quant setting changes).
+        Every rank must call it at the same step."""
+        if not self.sharded:
+            self.e.cast_weights()
+            return
+        for k in gpt.BANKS:
+            for s in range(*self.own[k]):
+                self._push_slot(k, s)
+        self.e.cast_weights(banks=False)
+        self.repushes += 1
+        self.e.layer_flag_value = 6 * (self.steps_done + self.repushes)
 
     def step(self):
         if self.sharded:
@@ -165,7 +182,7 @@ class DistributedStep:
             for s in range(s0, s1):
                 self._push_slot(k, s)
         e.cast_weights(banks=False)
-        e.layer_flag_value = 6 * (self.steps_done + 1)
+        e.layer_flag_value = 6 * (self.steps_done + 1 + self.repushes)
 
     def _step_replicated(self):
         """Two-shot all-reduce of every gradient (reduce my slice from all peers, write it back to all peers), then the

@@ -263,6 +263,13 @@ class VariantRunner:
             else:
                 wd = int(round(max_steps * t.warmdown_frac)) if t.warmdown_frac > 0 else min(t.warmdown_iters, max_steps)
                 scale = lr_scale_with_floor(step, t.warmup_steps, max_steps, wd, t.min_lr_scale) if (wd or t.warmup_steps) else 1.0
+            if t.world_size > 1 and t.wallclock_warmdown and max_ms is not None:
+                # wallclock-derived scales differ slightly across ranks; agree on one so that schedule-driven
+                # switches (late QAT, SWA) flip on the same step everywhere
+                import torch.distributed as dist
+                sc = torch.tensor([scale], dtype=torch.float64, device=device if t.backend != "cpu" else "cpu")
+                dist.all_reduce(sc, op=dist.ReduceOp.MIN)
+                scale = float(sc[0])
             if t.late_qat_threshold > 0 and scale < t.late_qat_threshold and not qat:
                 qat = True
                 log.info(f"late_qat:enabled step:{step} scale:{scale:.4f}")

@@ -1,0 +1,159 @@
+"""PyTorch interop without third-party packages: safetensors reader/writer, state-dict name mapping, step parity.
+
+* safetensors (F32/BF16/F16): 8-byte little-endian header length, JSON header ``{name: {dtype, shape, data_offsets}}``,
+  then the raw little-endian payload (``parameter-golf-rs/crates/pg-compat/src/safetensors.rs:43-130``, ``writer.rs``).
+* Name map between the Python records' ``state_dict`` (per-block ``blocks.{i}.attn_scale`` …, ``bigram.embed.weight`` …) and
+  this framework's stacked parameter dict (``pg-compat/src/loader.rs:69-188``).
+* Parity report of two step dumps with the reference tolerances ``loss_atol = 1e-3``, ``grad_max_rel = 0.02``
+  (``pg-compat/src/parity.rs:30-34,85-198``).
+"""
+from __future__ import annotations
+
+import json
+import struct
+from dataclasses import dataclass, field
+from typing import Dict, List
+
+import numpy as np
+import torch
+
+from ..models.gpt import param_shapes
+from ..spec import ModelSpec
+
+_ST_DTYPES = {"F32": (np.dtype("<f4"), torch.float32), "F16": (np.dtype("<f2"), torch.float16), "BF16": (np.dtype("<u2"), torch.bfloat16)}
+LOSS_ATOL = 1e-3
+GRAD_MAX_REL = 0.02
+
+
+def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dict[str, str] | None = None) -> None:
+    header, blobs, off = {}, [], 0
+    if metadata:
+        header["__metadata__"] = metadata
+    for name, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        if t.dtype == torch.float32:
+            code, raw = "F32", t.numpy().astype("<f4").tobytes()
+        elif t.dtype == torch.float16:
+            code, raw = "F16", t.numpy().astype("<f2").tobytes()
+        elif t.dtype == torch.bfloat16:
+            code, raw = "BF16", t.view(torch.int16).numpy().astype("<i2").tobytes()
+        else:
+            raise TypeError(f"{name}: dtype {t.dtype} is not supported (F32/F16/BF16)")
+        header[name] = {"dtype": code, "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    hj = json.dumps(header, separators=(",", ":")).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+
+
+def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
+    with open(path, "rb") as f:
+        buf = f.read()
+    if len(buf) < 8:
+        raise ValueError("not a safetensors file")
+    (hl,) = struct.unpack_from("<Q", buf, 0)
+    if 8 + hl > len(buf):
+        raise ValueError("safetensors header length exceeds the file")
+    header = json.loads(buf[8:8 + hl])
+    out = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        if info["dtype"] not in _ST_DTYPES:
+            raise TypeError(f"{name}: dtype {info['dtype']} is not supported")
+        npdt, tdt = _ST_DTYPES[info["dtype"]]
+        a, b = info["data_offsets"]
+        raw = np.frombuffer(buf, dtype=npdt, count=(b - a) // npdt.itemsize, offset=8 + hl + a).copy()
+        t = torch.from_numpy(raw.view(np.int16) if info["dtype"] == "BF16" else raw)
+        if info["dtype"] == "BF16":
+            t = t.view(torch.bfloat16)
+        out[name] = t.reshape(info["shape"])
+    return out
+
+
+def from_python_state_dict(m: ModelSpec, sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """Map a record-style ``GPT.state_dict()`` onto this framework's parameter dict."""
+    n = m.num_layers
+    p: Dict[str, torch.Tensor] = {}
+    direct = {"tok_emb.weight": "tok_emb", "qo_bank": "qo_bank", "kv_bank": "kv_bank", "mlp_up_bank": "mlp_up_bank", "mlp_down_bank": "mlp_down_bank",
+              "skip_weights": "skip_weights", "smear.gate": "smear_gate", "bigram.embed.weight": "bigram_embed", "bigram.proj.weight": "bigram_proj",
+              "ve_shared.embed.weight": "ve_embed", "ve_shared.proj.weight": "ve_proj", "lm_head.weight": "lm_head"}
+    for src, dst in direct.items():
+        if src in sd:
+            p[dst] = sd[src].float()
+    for src, dst in (("bigram.scale", "bigram_scale"), ("ve_shared.scale", "ve_scale")):
+        if src in sd:
+            p[dst] = sd[src].float().reshape(1)
+    for k in ("attn_scale", "mlp_scale", "resid_mix"):
+        if f"blocks.0.{k}" in sd:
+            p[k] = torch.stack([sd[f"blocks.{i}.{k}"].float() for i in range(n)])
+    if "blocks.0.attn.q_gain" in sd:
+        p["q_gain"] = torch.stack([sd[f"blocks.{i}.attn.q_gain"].float() for i in range(n)])
+    ls = [sd[k].float().reshape(()) for k in sorted(sd) if k.startswith("ve_layer_scales.")]
+    if ls:
+        p["ve_layer_scales"] = torch.stack(ls)
+    want = param_shapes(m)
+    missing = [k for k in want if k not in p]
+    if missing:
+        raise KeyError(f"state dict lacks {missing}")
+    for k in want:
+        if tuple(p[k].shape) != tuple(want[k]):
+            raise ValueError(f"{k}: shape {tuple(p[k].shape)} != expected {want[k]}")
+    return p
+
+
+def to_python_state_dict(m: ModelSpec, p: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    n = m.num_layers
+    sd = {"tok_emb.weight": p["tok_emb"]}
+    for k in ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank", "skip_weights"):
+        if k in p:
+            sd[k] = p[k]
+    if "smear_gate" in p:
+        sd["smear.gate"] = p["smear_gate"]
+    if "bigram_embed" in p:
+        sd["bigram.embed.weight"] = p["bigram_embed"]
+        sd["bigram.scale"] = p["bigram_scale"].reshape(())
+        if "bigram_proj" in p:
+            sd["bigram.proj.weight"] = p["bigram_proj"]
+    if "ve_embed" in p:
+        sd["ve_shared.embed.weight"], sd["ve_shared.proj.weight"] = p["ve_embed"], p["ve_proj"]
+        sd["ve_shared.scale"] = p["ve_scale"].reshape(())
+        for i in range(p["ve_layer_scales"].numel()):
+            sd[f"ve_layer_scales.{i}"] = p["ve_layer_scales"][i].reshape(1)
+    for i in range(n):
+        for k in ("attn_scale", "mlp_scale", "resid_mix"):
+            sd[f"blocks.{i}.{k}"] = p[k][i]
+        sd[f"blocks.{i}.attn.q_gain"] = p["q_gain"][i]
+    return sd
+
+
+@dataclass
+class ParityReport:
+    loss_diff: float = 0.0
+    worst_grad_rel: float = 0.0
+    worst_grad_name: str = ""
+    per_tensor: Dict[str, float] = field(default_factory=dict)
+    missing: List[str] = field(default_factory=list)
+
+    @property
+    def ok(self) -> bool:
+        return self.loss_diff <= LOSS_ATOL and self.worst_grad_rel <= GRAD_MAX_REL and not self.missing
+
+
+def compare_step_dumps(a: Dict[str, torch.Tensor], b: Dict[str, torch.Tensor]) -> ParityReport:
+    """``a``/``b``: {"loss": scalar, "grad.<name>": tensor, …}. Relative error is max|a-b| / max|b| per tensor."""
+    rep = ParityReport()
+    rep.loss_diff = float((a["loss"].double() - b["loss"].double()).abs())
+    for k, vb in b.items():
+        if not k.startswith("grad."):
+            continue
+        if k not in a:
+            rep.missing.append(k)
+            continue
+        rel = float((a[k].double() - vb.double()).abs().max() / (vb.double().abs().max() + 1e-12))
+        rep.per_tensor[k] = rel
+        if rel > rep.worst_grad_rel:
+            rep.worst_grad_rel, rep.worst_grad_name = rel, k
+    return rep

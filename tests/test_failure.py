@@ -1,0 +1,99 @@
+"""Failure detection without touching a GPU: failures are made on the host (a rank that raises, never joins or exits;
+a corrupted or missing file; a mismatched fingerprint) and, for multi-rank cases, among gloo ranks on CPU."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+import pytest
+
+from parameter_golf_b200.data import shards as S
+from parameter_golf_b200.spec import family_preset
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(tmp_path, body, nproc=2, port=29690, timeout=120):
+    script = tmp_path / "w.py"
+    script.write_text("import os, sys, time, datetime\nsys.path.insert(0, %r)\nimport torch, torch.distributed as dist\n" % ROOT + textwrap.dedent(body))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    return subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+                           "--master-port", str(port), str(script)], capture_output=True, text=True, env=env, cwd=ROOT, timeout=timeout)
+
+
+def test_rank_that_never_joins_is_detected_by_timeout(tmp_path):
+    out = _run(tmp_path, """
+        dist.init_process_group('gloo', timeout=datetime.timedelta(seconds=3))
+        rank = dist.get_rank()
+        t = torch.ones(1)
+        if rank == 1:
+            time.sleep(8)                      # misses the collective
+            print('LATE', flush=True); sys.exit(0)
+        try:
+            dist.all_reduce(t)
+            print('UNEXPECTED', flush=True)
+        except Exception as e:
+            print('DETECTED', type(e).__name__, flush=True)
+        """, port=29691)
+    assert "DETECTED" in out.stdout and "UNEXPECTED" not in out.stdout, (out.stdout, out.stderr[-1500:])
+
+
+def test_rank_that_raises_is_reported_through_the_store(tmp_path):
+    out = _run(tmp_path, """
+        dist.init_process_group('gloo', timeout=datetime.timedelta(seconds=20))
+        rank = dist.get_rank()
+        store = dist.distributed_c10d._get_default_store()
+        for step in range(3):
+            if rank == 1 and step == 1:
+                store.set('failed', 'rank1: injected exception at step 1')      # heartbeat-style report, between steps
+                break
+            if store.num_keys() and store.check(['failed']):
+                print('PEER_FAILED', store.get('failed').decode(), flush=True); break
+            time.sleep(0.3)
+            if store.check(['failed']):
+                print('PEER_FAILED', store.get('failed').decode(), flush=True); break
+            dist.all_reduce(torch.ones(1))
+        """, port=29692)
+    assert "PEER_FAILED rank1: injected exception at step 1" in out.stdout, (out.stdout, out.stderr[-1500:])
+
+
+def test_missing_and_corrupt_shards_fail_loudly(tmp_path):
+    with pytest.raises(FileNotFoundError):
+        S.DistributedTokenLoader(str(tmp_path / "nothing_*.bin"))
+    p = tmp_path / "x_train_000000.bin"
+    S.write_shard(str(p), np.arange(100))
+    raw = bytearray(p.read_bytes())
+    raw[8:12] = (5000).to_bytes(4, "little")                 # header now promises more tokens than the file holds
+    p.write_bytes(raw)
+    with pytest.raises(S.ShardError, match="does not match"):
+        S.DistributedTokenLoader(str(tmp_path / "x_train_*.bin"))
+
+
+def test_wallclock_and_eval_deadlines_end_runs_cleanly(tmp_path, monkeypatch):
+    import math
+    import numpy as np
+    from parameter_golf_b200.data.bpb import BpbLuts
+    from parameter_golf_b200.eval.ttt import eval_score_first_ttt
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.runner import OracleRunner
+    s = family_preset("tiny_cpu")
+    m = s.model
+    m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads, m.eval_seq_len = 32, 1, 16, 2, 1, 16
+    s.eval.stride, s.eval.chunk_tokens, s.eval.max_eval_seconds = 4, 32, 1e-9
+    p = gpt.fill_deterministic(m)
+    before = {k: v.clone() for k, v in p.items()}
+    toks = np.random.default_rng(0).integers(0, 32, 16 * 6 + 1).astype(np.uint16)
+    loss, bpb = eval_score_first_ttt(OracleRunner(m, p), toks, m, s.eval, BpbLuts.seeded(32))
+    assert math.isfinite(loss) and all((p[k] == before[k]).all() for k in p)       # past the deadline: scoring only, no adaptation
+
+
+def test_fingerprint_mismatch_blocks_resume_and_artifact_mismatch_blocks_load(tmp_path):
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.quant.container import ArtifactError
+    from parameter_golf_b200.quant.export import export_model, load_artifact
+    a, b = family_preset("tiny_cpu"), family_preset("tiny_cpu")
+    b.model.num_heads = 2
+    blob = export_model(a, gpt.init_params(a.model, 0))
+    with pytest.raises(ArtifactError, match="num_heads"):
+        load_artifact(blob, b.validate())

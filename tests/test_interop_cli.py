@@ -1,0 +1,77 @@
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from parameter_golf_b200.models import gpt
+from parameter_golf_b200.spec import RunSpec, family_preset
+from parameter_golf_b200.utils import interop as I
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_safetensors_roundtrip_and_layout(tmp_path):
+    t = {"a": torch.randn(3, 4), "b": torch.randn(5).half(), "c": torch.randn(2, 2).bfloat16()}
+    p = str(tmp_path / "x.safetensors")
+    I.write_safetensors(p, t, {"k": "v"})
+    raw = open(p, "rb").read()
+    hl = int.from_bytes(raw[:8], "little")
+    hdr = json.loads(raw[8:8 + hl])
+    assert hdr["a"] == {"dtype": "F32", "shape": [3, 4], "data_offsets": [0, 48]} and hdr["__metadata__"] == {"k": "v"}
+    back = I.read_safetensors(p)
+    assert all(torch.equal(back[k], t[k]) for k in t)
+    with pytest.raises(ValueError):
+        open(p, "wb").write(raw[:4])
+        I.read_safetensors(p)
+
+
+def test_name_map_roundtrip():
+    s = family_preset("record_11l")
+    s.model.num_layers, s.model.model_dim, s.model.num_heads, s.model.num_kv_heads = 2, 64, 2, 1
+    s.model.value_embedding.enabled, s.model.value_embedding.layers = True, [0, 1]
+    p = gpt.fill_deterministic(s.model)
+    sd = I.to_python_state_dict(s.model, p)
+    assert "blocks.1.attn.q_gain" in sd and "bigram.proj.weight" in sd and "ve_layer_scales.1" in sd
+    back = I.from_python_state_dict(s.model, sd)
+    assert set(back) == set(p) and all(torch.equal(back[k], p[k]) for k in p)
+    del sd["qo_bank"]
+    with pytest.raises(KeyError):
+        I.from_python_state_dict(s.model, sd)
+
+
+def test_parity_report_tolerances():
+    a = {"loss": torch.tensor(1.0), "grad.w": torch.ones(4)}
+    b = {"loss": torch.tensor(1.0005), "grad.w": torch.ones(4) * 1.01, "grad.v": torch.ones(2)}
+    r = I.compare_step_dumps(a, b)
+    assert r.missing == ["grad.v"] and not r.ok and r.worst_grad_rel < 0.02
+    del b["grad.v"]
+    assert I.compare_step_dumps(a, b).ok
+    b["grad.w"] = torch.ones(4) * 1.5
+    assert not I.compare_step_dumps(a, b).ok
+
+
+def test_shipped_specs_load_and_validate():
+    for name in ("record_profile", "baseline_9l", "tiny_cpu"):
+        s = RunSpec.load(os.path.join(ROOT, "specs", f"{name}.toml")).validate()
+        assert s.fingerprint() == family_preset(s.model.family).fingerprint()
+
+
+def test_eval_cli_and_leaderboard_gate(tmp_path):
+    from parameter_golf_b200.data.shards import write_shard, generate_markov_tokens
+    from parameter_golf_b200.quant.export import export_model
+    s = family_preset("tiny_cpu")
+    art = str(tmp_path / "a.pgrs")
+    export_model(s, gpt.init_params(s.model, 1), art)
+    write_shard(str(tmp_path / "v_val_000000.bin"), generate_markov_tokens(256 * 3 + 1, 1024, 5))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    base = [sys.executable, "-m", "parameter_golf_b200.evalcli", "--artifact", art, "--family", "tiny_cpu", "--val-pattern", str(tmp_path / "v_val_*.bin")]
+    out = subprocess.run(base, capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr[-1500:]
+    kv = dict(l.split("=", 1) for l in out.stdout.splitlines() if "=" in l and not l.startswith("eval_audit_json"))
+    assert kv["eval_kind"] == "sliding" and float(kv["val_bpb"]) > 0 and "eval_audit_json=" in out.stdout
+    out = subprocess.run(base + ["--leaderboard", "--bytes", "placeholder", "--max-tokens", "300"], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode == 2 and "placeholder" in out.stderr and "full validation set" in out.stderr

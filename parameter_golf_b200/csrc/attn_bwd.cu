@@ -204,8 +204,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
       const size_t sidx = ((size_t)b * p.H + head) * p.S + qt * 128 + r;
-      p.Dsum[sidx] = Dr;
-      const float lse2 = p.lse[sidx] * LOG2E;
+      p.Dsum[sidx] = -Dr;                      // negated: the dK/dV kernel adds it
+      const float nlse2 = p.lse[sidx];         // -(log2-domain log-sum-exp), as written by the forward
       bool ok = true;
       for (int t = 0; t < nsteps; ++t) {
         if (!mbar_wait(&s_full[w], t & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
@@ -219,17 +219,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const bool diag = (t >> 1) == qt;
         const int kbase = (t & 1) * 64;                     // key offset of this sub-tile inside the 128-key tile
         uint32_t pk[32];
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(nlse2, nlse2), nd2 = make_float2(-Dr, -Dr);
+        if (!diag) {
 #pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          float p0 = ex2f(fmaf(__uint_as_float(s[c]), p.scale_log2, -lse2));
-          float p1 = ex2f(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -lse2));
-          if (diag) {
-            if (kbase + c > r) p0 = 0.f;
-            if (kbase + c + 1 > r) p1 = 0.f;
+          for (int c = 0; c < 64; c += 2) {
+            const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, nl2);
+            const float2 pr = make_float2(ex2f(tt.x), ex2f(tt.y));
+            const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), nd2));
+            pk[c >> 1] = pack_bf16x2(dd.x, dd.y);
           }
-          const float d0 = p0 * (__uint_as_float(dp[c]) - Dr) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dp[c + 1]) - Dr) * p.scale;
-          pk[c >> 1] = pack_bf16x2(d0, d1);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; c += 2) {
+            const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, nl2);
+            float2 pr = make_float2(ex2f(tt.x), ex2f(tt.y));
+            if (kbase + c > r) pr.x = 0.f;
+            if (kbase + c + 1 > r) pr.y = 0.f;
+            const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), nd2));
+            pk[c >> 1] = pack_bf16x2(dd.x, dd.y);
+          }
         }
         PGB_TMEM_ST16(tS, (pk));
         PGB_TMEM_ST16(tS + 16, (pk + 16));
@@ -248,8 +256,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
           for (int c = 0; c < 32; c += 8)
             *reinterpret_cast<uint4*>(out + h * 32 + c) =
-                make_uint4(pack_bf16x2(__uint_as_float(o[c]), __uint_as_float(o[c + 1])), pack_bf16x2(__uint_as_float(o[c + 2]), __uint_as_float(o[c + 3])),
-                           pack_bf16x2(__uint_as_float(o[c + 4]), __uint_as_float(o[c + 5])), pack_bf16x2(__uint_as_float(o[c + 6]), __uint_as_float(o[c + 7])));
+                make_uint4(pack_bf16x2(__uint_as_float(o[c]) * p.scale, __uint_as_float(o[c + 1]) * p.scale),
+                           pack_bf16x2(__uint_as_float(o[c + 2]) * p.scale, __uint_as_float(o[c + 3]) * p.scale),
+                           pack_bf16x2(__uint_as_float(o[c + 4]) * p.scale, __uint_as_float(o[c + 5]) * p.scale),
+                           pack_bf16x2(__uint_as_float(o[c + 6]) * p.scale, __uint_as_float(o[c + 7]) * p.scale));
         }
       }
     }
@@ -412,16 +422,29 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
       const bool diag = qi == j;
       const int qbase = hh * 64;
       uint32_t pp[32], pd[32];
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2* vl2 = reinterpret_cast<const float2*>(vl);     // -(log2 lse) of the 64 query rows of this unit
+      const float2* vd2 = reinterpret_cast<const float2*>(vd);     // -D of the same rows
+      if (!diag) {
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        float p0 = ex2f(fmaf(__uint_as_float(s[c]), p.scale_log2, -vl[c] * LOG2E));
-        float p1 = ex2f(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -vl[c + 1] * LOG2E));
-        if (diag) {
-          if (qbase + c < kk) p0 = 0.f;              // query position before the key: masked
-          if (qbase + c + 1 < kk) p1 = 0.f;
+        for (int c = 0; c < 64; c += 2) {
+          const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, vl2[c >> 1]);
+          const float2 pr = make_float2(ex2f(tt.x), ex2f(tt.y));
+          const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), vd2[c >> 1]));
+          pp[c >> 1] = pack_bf16x2(pr.x, pr.y);
+          pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
         }
-        pp[c >> 1] = pack_bf16x2(p0, p1);
-        pd[c >> 1] = pack_bf16x2(p0 * (__uint_as_float(dp[c]) - vd[c]) * p.scale, p1 * (__uint_as_float(dp[c + 1]) - vd[c + 1]) * p.scale);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, vl2[c >> 1]);
+          float2 pr = make_float2(ex2f(tt.x), ex2f(tt.y));
+          if (qbase + c < kk) pr.x = 0.f;              // query position before the key: masked
+          if (qbase + c + 1 < kk) pr.y = 0.f;
+          const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), vd2[c >> 1]));
+          pp[c >> 1] = pack_bf16x2(pr.x, pr.y);
+          pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
+        }
       }
       PGB_TMEM_ST16(tS, (pp));
       PGB_TMEM_ST16(tS + 16, (pp + 16));
@@ -446,7 +469,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
         for (int c = 0; c < 32; c += 8) {
           float f[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]);
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]) * (w == 0 ? p.scale : 1.f);
           if (acc) {
             uint4 q = *reinterpret_cast<const uint4*>(out + h * 32 + c);
             float2 a0 = unpack_bf16x2(q.x), a1 = unpack_bf16x2(q.y), a2 = unpack_bf16x2(q.z), a3 = unpack_bf16x2(q.w);

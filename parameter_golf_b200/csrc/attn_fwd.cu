@@ -195,9 +195,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int c = 0; c < 128; ++c)
             if (c > r) s[c] = 0xff800000u;          // -inf
         }
-        float mx = -INFINITY;
+        float mx8[8];
 #pragma unroll
-        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(s[c]));
+        for (int c = 0; c < 8; ++c) mx8[c] = __uint_as_float(s[c]);
+#pragma unroll
+        for (int c = 8; c < 128; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], __uint_as_float(s[c]));      // 8 independent chains
+        float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
         mx *= p.scale_log2;
         if (j > 0) {
           if (!mbar_wait(&o_full[w], (j - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
@@ -222,19 +225,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           l *= alpha;
           m_used = m_new;
         }
-        float sum = 0.f;
+        // packed fp32x2 arithmetic: one FFMA2 scales and shifts two scores, one FADD2 accumulates two probabilities
+        float2 sum2 = make_float2(0.f, 0.f), sum2b = make_float2(0.f, 0.f);
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_used, -m_used);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint32_t pk[16];
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
-            const float p0 = ex2(fmaf(__uint_as_float(s[q * 32 + 2 * c]), p.scale_log2, -m_used));
-            const float p1 = ex2(fmaf(__uint_as_float(s[q * 32 + 2 * c + 1]), p.scale_log2, -m_used));
-            sum += p0 + p1;
-            pk[c] = pack_bf16x2(p0, p1);
+            const float2 t = __ffma2_rn(make_float2(__uint_as_float(s[q * 32 + 2 * c]), __uint_as_float(s[q * 32 + 2 * c + 1])), sc2, nm2);
+            const float2 pr = make_float2(ex2(t.x), ex2(t.y));
+            if (c & 1) sum2b = __fadd2_rn(sum2b, pr); else sum2 = __fadd2_rn(sum2, pr);
+            pk[c] = pack_bf16x2(pr.x, pr.y);
           }
           PGB_TMEM_ST16(tS + q * 16, pk);
         }
+        const float sum = (sum2.x + sum2.y) + (sum2b.x + sum2b.y);
         l += sum;
         tmem_wait_st();
         tc_fence_before();
@@ -258,7 +264,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                            pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv),
                            pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv));
         }
-        p.lse[((size_t)b * p.H + head) * p.S + qt * AT_BM + r] = (m_used + log2f(l)) * 0.6931471805599453f;
+        p.lse[((size_t)b * p.H + head) * p.S + qt * AT_BM + r] = -(m_used + log2f(l));   // negated, log2 domain: what the backward FMAs consume
       }
     }
   }

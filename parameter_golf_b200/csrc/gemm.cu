@@ -12,8 +12,8 @@
 // (parameter-golf-rs/crates/pg-kernels/src/gemm.rs:158-179,501-698) and the elementwise kernels that
 // follow them, which become epilogues here.
 //
-// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs (one elected lane),
-// warps 2..5 read the accumulator back (tcgen05.ld, one row per thread) and run the epilogue. Two
+// CTA = 10 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues the MMAs (one elected lane),
+// warps 2..9 read the accumulator back (tcgen05.ld, one row per thread) and run the epilogue. Two
 // accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
 // Tile 128 x BN x 64, BN in {128, 256}; grid = min(#tiles, #SMs); tile index = n fastest so CTAs
 // working at the same time share the rows of the large operand in L2.
@@ -25,7 +25,7 @@ namespace pgb {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;     // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
 
 struct GemmKernelParams {
   int M, N, K, batch;
@@ -55,7 +55,7 @@ struct GemmSmem {
 __device__ __forceinline__ float act_fn(float x, float slope) { return x >= 0.f ? x : slope * x; }
 
 template <int EPI>
-__device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b, int m, int n0, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b, int m, int n0, const uint32_t (&r)[32], const uint4 (&ax)[4]) {
   // One thread: row m, columns n0 .. n0+31 of batch b. Caller guarantees m < M.
   const bool full = (n0 + 32 <= p.N);
   const long long off = (long long)b * p.stride_d + (long long)m * p.ldd + n0;
@@ -90,7 +90,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
       if (vec && ((reinterpret_cast<uintptr_t>(ap) & 15) == 0)) {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
-          uint4 q = *reinterpret_cast<const uint4*>(ap + i);
+          const uint4 q = ax[i >> 3];            // prefetched by the caller one chunk ahead
           float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
           a[i] = f0.x; a[i + 1] = f0.y; a[i + 2] = f1.x; a[i + 3] = f1.y;
           a[i + 4] = f2.x; a[i + 5] = f2.y; a[i + 6] = f3.x; a[i + 7] = f3.y;
@@ -166,7 +166,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 128);
+      mbar_init(&tempty_bar[a], 256);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -285,8 +285,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;             // which half of the tile's columns
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -300,14 +301,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, ST_WAIT_TMEM_FULL, tile)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      constexpr bool HAS_AUX = (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD);
+      constexpr int CH = BN / 64;                   // 32-column chunks per epilogue warp (the two warps of a quarter split the columns)
+      const int c_begin = half * CH;
+      auto load_aux = [&](int c, uint4 (&dst)[4]) {
+        if constexpr (HAS_AUX) {
+          const int n0 = tn * BN + c * 32;
+          if (m < p.M && n0 + 32 <= p.N) {
+            const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + (long long)m * p.ld_aux + n0;
+            if ((reinterpret_cast<uintptr_t>(ap) & 15) == 0) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) dst[i] = *reinterpret_cast<const uint4*>(ap + 8 * i);
+            }
+          }
+        }
+      };
+      uint4 ax[4] = {};
+      load_aux(c_begin, ax);
+#pragma unroll
+      for (int cc = 0; cc < CH; ++cc) {
+        const int c = c_begin + cc;
         const int n0 = tn * BN + c * 32;
         if (n0 >= p.N) break;                     // warp-uniform
+        uint4 axn[4] = {};
+        if (cc + 1 < CH) load_aux(c + 1, axn);    // next chunk's operand is in flight while this one is processed
         uint32_t rr[32];
         PGB_TMEM_LD32(taddr + c * 32, rr);
         tmem_wait_ld();
-        if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr);
+        if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ax[i] = axn[i];
       }
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);

@@ -91,7 +91,7 @@ def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.
 
 
 def attn_fwd(q, k, v, y, B, S, H, Hkv, hd, lse=None):
-    """Causal GQA attention forward; q/k/v are [B*S, heads*hd] (row-strided views allowed). Returns lse [B, H, S]."""
+    """Causal GQA attention forward; q/k/v are [B*S, heads*hd] (row-strided views allowed). Returns the side output [B, H, S] = -(log2-domain log-sum-exp), which `attn_bwd` consumes."""
     if lse is None:
         lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
     load().attn_fwd(q, k, v, y, lse, B, S, H, Hkv, hd, status_word(q.device))

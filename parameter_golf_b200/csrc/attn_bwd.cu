@@ -44,6 +44,7 @@ __device__ __forceinline__ float ex2f(float x) {
 
 struct AttnBwdParams {
   int B, S, H, Hkv, n_qt, pairs, group;
+  int n_items_q, n_items_kv;
   float scale, scale_log2;
   const __nv_bfloat16* O;      // [T, H*hd]
   const __nv_bfloat16* dO;
@@ -77,21 +78,29 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   uint64_t* s_full = kv_empty + DQ_STAGES;   // 2
   uint64_t* p_full = s_full + 2;             // 2
   uint64_t* dq_full = p_full + 2;            // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 2);
+  uint64_t* dq_empty = dq_full + 2;          // 2
+  uint64_t* q_empty = dq_empty + 2;          // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per_qt = p.B * p.Hkv * p.pairs;
-  const int qt = p.n_qt - 1 - (int)(blockIdx.x / per_qt);
-  int rem = (int)(blockIdx.x % per_qt);
-  const int b = rem / (p.Hkv * p.pairs);
-  rem -= b * p.Hkv * p.pairs;
-  const int kvh = rem / p.pairs, pair = rem % p.pairs;
-  const int head0 = kvh * p.group + pair * 2;
-  const int n_active = min(2, p.group - pair * 2);
-  const int n_kv = qt + 1;
-  const int nsteps = 2 * n_kv;
-  const int row0 = b * p.S + qt * 128;
+  struct Item { int qt, b, kvh, head0, n_active, n_kv, nsteps, row0; };
+  auto decode = [&](int item) {
+    Item it;
+    it.qt = p.n_qt - 1 - item / per_qt;
+    int rem = item % per_qt;
+    it.b = rem / (p.Hkv * p.pairs);
+    rem -= it.b * p.Hkv * p.pairs;
+    it.kvh = rem / p.pairs;
+    const int pair = rem % p.pairs;
+    it.head0 = it.kvh * p.group + pair * 2;
+    it.n_active = min(2, p.group - pair * 2);
+    it.n_kv = it.qt + 1;
+    it.nsteps = 2 * it.n_kv;
+    it.row0 = it.b * p.S + it.qt * 128;
+    return it;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -103,7 +112,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(&s_full[w], 1);
       mbar_init(&p_full[w], 128);
       mbar_init(&dq_full[w], 1);
+      mbar_init(&dq_empty[w], 128);
     }
+    mbar_init(q_empty, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -119,24 +130,29 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, n_active * 2 * AB_TILE);
-      for (int w = 0; w < n_active; ++w) {
-        tma2d(sQ + w * AB_TILE, &map_q, q_full, (head0 + w) * AB_HD, row0);
-        tma2d(sdO + w * AB_TILE, &map_do, q_full, (head0 + w) * AB_HD, row0);
-      }
       int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, item_par = 0;
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
-        uint8_t* sk = sKV + stage * 2 * AB_TILE;
-        mbar_expect_tx(&kv_full[stage], 2 * AB_TILE);
-        tma2d(sk, &map_k, &kv_full[stage], kvh * AB_HD, b * p.S + j * 128);
-        tma2d(sk + AB_TILE, &map_v, &kv_full[stage], kvh * AB_HD, b * p.S + j * 128);
-        if (++stage == DQ_STAGES) { stage = 0; phase ^= 1; }
+      for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x, item_par ^= 1) {
+        const Item it = decode(item);
+        if (!mbar_wait(q_empty, item_par ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, -1)) { ok = false; break; }
+        mbar_expect_tx(q_full, it.n_active * 2 * AB_TILE);
+        for (int w = 0; w < it.n_active; ++w) {
+          tma2d(sQ + w * AB_TILE, &map_q, q_full, (it.head0 + w) * AB_HD, it.row0);
+          tma2d(sdO + w * AB_TILE, &map_do, q_full, (it.head0 + w) * AB_HD, it.row0);
+        }
+        for (int j = 0; j < it.n_kv; ++j) {
+          if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
+          uint8_t* sk = sKV + stage * 2 * AB_TILE;
+          mbar_expect_tx(&kv_full[stage], 2 * AB_TILE);
+          tma2d(sk, &map_k, &kv_full[stage], it.kvh * AB_HD, it.b * p.S + j * 128);
+          tma2d(sk + AB_TILE, &map_v, &kv_full[stage], it.kvh * AB_HD, it.b * p.S + j * 128);
+          if (++stage == DQ_STAGES) { stage = 0; phase ^= 1; }
+        }
       }
       if (!ok) {
         mbar_drain(q_full, 0);
+        mbar_drain(q_full, 1);
         for (int s = 0; s < DQ_STAGES; ++s) mbar_drain(&kv_full[s], (s < stage) ? phase : (phase ^ 1));
       }
     }
@@ -144,52 +160,71 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (lane == 0) {
       constexpr uint32_t IDESC_S = make_idesc_bf16(128, 64, 0, 0);     // Q K^T, dO V^T (64-key sub-tiles)
       constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, 64, 0, 1);    // dS (TMEM) x K, K read N(=hd)-contiguous
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_WAIT_FULL, -1);
-      auto issue_sdp = [&](int w, int t) {
-        const int stage = (t >> 1) % DQ_STAGES, hh = t & 1;
-        const uint32_t sq = smem_u32(sQ + w * AB_TILE), sdo = smem_u32(sdO + w * AB_TILE);
-        const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE) + hh * AB_SUB, sv = sk + AB_TILE;
-        const uint32_t tS = tmem_base + w * 192, tP = tS + 64;
+      uint32_t item_par = 0;
+      uint32_t spar[2] = {0, 0};       // parity of the running per-head step counter (s_full / p_full)
+      uint32_t dqpar[2] = {0, 0};      // parity of the per-head count of finished items (dq_empty)
+      long long kv_base = 0;           // K/V tiles consumed by earlier items of this CTA
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x, item_par ^= 1) {
+        const Item it = decode(item);
+        auto kv_stage = [&](int tile) { return (int)((kv_base + tile) % DQ_STAGES); };
+        auto kv_phase = [&](int tile) { return (uint32_t)(((kv_base + tile) / DQ_STAGES) & 1); };
+        auto issue_sdp = [&](int w, int t) {
+          const int stage = kv_stage(t >> 1), hh = t & 1;
+          const uint32_t sq = smem_u32(sQ + w * AB_TILE), sdo = smem_u32(sdO + w * AB_TILE);
+          const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE) + hh * AB_SUB, sv = sk + AB_TILE;
+          const uint32_t tS = tmem_base + w * 192, tP = tS + 64;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_ss(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0);
+          for (int k = 0; k < 4; ++k) umma_ss(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_ss(tP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), IDESC_S, k > 0);
-        umma_commit(&s_full[w]);
-      };
-      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, ST_WAIT_FULL, 0);
-      if (ok) {
+          for (int k = 0; k < 4; ++k) umma_ss(tP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), IDESC_S, k > 0);
+          umma_commit(&s_full[w]);
+        };
+        if (!mbar_wait(q_full, item_par, abort_flag, p.status, ST_WAIT_FULL, -1)) { ok = false; break; }
+        if (!mbar_wait(&kv_full[kv_stage(0)], kv_phase(0), abort_flag, p.status, ST_WAIT_FULL, 0)) { ok = false; break; }
         tc_fence_after();
-        for (int w = 0; w < n_active; ++w) issue_sdp(w, 0);
-      }
-      for (int t = 0; t < nsteps && ok; ++t) {
-        const int tile = t >> 1, hh = t & 1, stage = tile % DQ_STAGES;
-        if (t + 1 < nsteps && ((t + 1) >> 1) != tile) {
-          const int nt = (t + 1) >> 1;
-          if (!mbar_wait(&kv_full[nt % DQ_STAGES], (nt / DQ_STAGES) & 1, abort_flag, p.status, ST_WAIT_FULL, nt)) { ok = false; break; }
-        }
-        const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE) + hh * AB_SUB;
-        for (int w = 0; w < n_active && ok; ++w) {
-          if (!mbar_wait(&p_full[w], t & 1, abort_flag, p.status, ST_WAIT_MISC, t)) { ok = false; break; }
-          tc_fence_after();
+        for (int w = 0; w < it.n_active; ++w) issue_sdp(w, 0);
+        for (int t = 0; t < it.nsteps && ok; ++t) {
+          const int tile = t >> 1, hh = t & 1, stage = kv_stage(tile);
+          if (t + 1 < it.nsteps && ((t + 1) >> 1) != tile) {
+            const int nt = (t + 1) >> 1;
+            if (!mbar_wait(&kv_full[kv_stage(nt)], kv_phase(nt), abort_flag, p.status, ST_WAIT_FULL, nt)) { ok = false; break; }
+          }
+          const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE) + hh * AB_SUB;
+          for (int w = 0; w < it.n_active && ok; ++w) {
+            if (!mbar_wait(&p_full[w], spar[w], abort_flag, p.status, ST_WAIT_MISC, t)) { ok = false; break; }
+            spar[w] ^= 1;
+            if (t == 0) {        // the previous item's dQ must have been read out before it is overwritten
+              if (!mbar_wait(&dq_empty[w], dqpar[w] ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
+              dqpar[w] ^= 1;
+            }
+            tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ts(tmem_base + w * 192 + 128, tmem_base + w * 192 + k * 8, make_smem_desc(sk + k * 2048, 8192, 1024), IDESC_DQ,
-                    (t > 0 || k > 0) ? 1u : 0u);
-          if (t + 1 < nsteps) issue_sdp(w, t + 1);
-          else umma_commit(&dq_full[w]);
+            for (int k = 0; k < 4; ++k)
+              umma_ts(tmem_base + w * 192 + 128, tmem_base + w * 192 + k * 8, make_smem_desc(sk + k * 2048, 8192, 1024), IDESC_DQ,
+                      (t > 0 || k > 0) ? 1u : 0u);
+            if (t + 1 < it.nsteps) issue_sdp(w, t + 1);
+            else umma_commit(&dq_full[w]);
+          }
+          if (!ok) break;
+          if (hh == 1) umma_commit(&kv_empty[stage]);
         }
-        if (!ok) break;
-        if (hh == 1) umma_commit(&kv_empty[stage]);
+        if (ok) umma_commit(q_empty);
+        kv_base += it.n_kv;
       }
     }
   } else {
     const int w = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    if (w < n_active) {
-      const int head = head0 + w;
-      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-      const uint32_t tS = tmem_base + w * 192 + lane_off, tP = tS + 64, tDQ = tS + 128;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + w * 192 + lane_off, tP = tS + 64, tDQ = tS + 128;
+    uint32_t spar = 0, ipar = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x) {
+      const Item it = decode(item);
+      if (w >= it.n_active) continue;
+      const int head = it.head0 + w, qt = it.qt, nsteps = it.nsteps, row0 = it.row0, b = it.b;
       // D = rowsum(dO * O) for this query row; also published for the dK/dV kernel
       float Dr = 0.f;
       {
@@ -206,9 +241,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const size_t sidx = ((size_t)b * p.H + head) * p.S + qt * 128 + r;
       p.Dsum[sidx] = -Dr;                      // negated: the dK/dV kernel adds it
       const float nlse2 = p.lse[sidx];         // -(log2-domain log-sum-exp), as written by the forward
-      bool ok = true;
       for (int t = 0; t < nsteps; ++t) {
-        if (!mbar_wait(&s_full[w], t & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
+        if (!mbar_wait(&s_full[w], spar, abort_flag, p.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
+        spar ^= 1;
         tc_fence_after();
         uint32_t s[64], dp[64];
         PGB_TMEM_LD32(tS, (s));
@@ -245,7 +280,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tc_fence_before();
         mbar_arrive(&p_full[w]);
       }
-      if (ok && mbar_wait(&dq_full[w], 0, abort_flag, p.status, ST_WAIT_MISC, nsteps)) {
+      if (ok && mbar_wait(&dq_full[w], ipar, abort_flag, p.status, ST_WAIT_MISC, nsteps)) {
+        ipar ^= 1;
         tc_fence_after();
         __nv_bfloat16* out = p.dq + (size_t)(row0 + r) * p.lddq + head * AB_HD;
 #pragma unroll
@@ -261,6 +297,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                            pack_bf16x2(__uint_as_float(o[c + 4]) * p.scale, __uint_as_float(o[c + 5]) * p.scale),
                            pack_bf16x2(__uint_as_float(o[c + 6]) * p.scale, __uint_as_float(o[c + 7]) * p.scale));
         }
+        tc_fence_before();
+        mbar_arrive(&dq_empty[w]);
+      } else {
+        ok = false;
       }
     }
   }
@@ -293,16 +333,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
   uint64_t* s_full = st_empty + KV_STAGES;    // 2
   uint64_t* p_full = s_full + 2;              // 2
   uint64_t* acc_full = p_full + 2;            // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_empty = acc_full + 1;         // 1
+  uint64_t* kv_empty = acc_empty + 1;         // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per_kt = p.B * p.Hkv;
-  const int j = (int)(blockIdx.x / per_kt);                 // key tile; low j = long query range = scheduled first
-  const int rem = (int)(blockIdx.x % per_kt);
-  const int b = rem / p.Hkv, kvh = rem % p.Hkv;
-  const int nu = (p.n_qt - j) * p.group * 2;                // units: (query tile, head, 64-row half)
-  const int key0 = b * p.S + j * 128;
+  struct Item { int j, b, kvh, nu, key0; };
+  auto decode = [&](int item) {
+    Item it;
+    it.j = item / per_kt;                                   // key tile; low j = long query range = scheduled first
+    const int rem = item % per_kt;
+    it.b = rem / p.Hkv;
+    it.kvh = rem % p.Hkv;
+    it.nu = (p.n_qt - it.j) * p.group * 2;                  // units: (query tile, head, 64-row half); always even
+    it.key0 = it.b * p.S + it.j * 128;
+    return it;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -315,6 +363,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
       mbar_init(&p_full[w], 128);
     }
     mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 256);
+    mbar_init(kv_empty, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -328,35 +378,44 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
   // buffer u&1: S^T at buf*128, dP^T at buf*128+64; dK at 256, dV at 320
 
-  auto unit_coords = [&](int u, int& qi, int& head, int& hh) {
+  auto unit_coords = [&](const Item& it, int u, int& qi, int& head, int& hh) {
     hh = u & 1;
     const int v = u >> 1;
-    head = kvh * p.group + (v % p.group);
-    qi = j + v / p.group;
+    head = it.kvh * p.group + (v % p.group);
+    qi = it.j + v / p.group;
   };
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(kv_full, 2 * AB_TILE);
-      tma2d(sK, &map_k, kv_full, kvh * AB_HD, key0);
-      tma2d(sV, &map_v, kv_full, kvh * AB_HD, key0);
       bool ok = true;
-      for (int u = 0; u < nu && ok; ++u) {
-        const int stage = u % KV_STAGES;
-        const uint32_t phase = (u / KV_STAGES) & 1;
-        if (!mbar_wait(&st_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, u)) { ok = false; break; }
-        int qi, head, hh;
-        unit_coords(u, qi, head, hh);
-        const int qrow = b * p.S + qi * 128 + hh * 64;
-        const size_t vidx = ((size_t)b * p.H + head) * p.S + qi * 128 + hh * 64;
-        mbar_expect_tx(&st_full[stage], 2 * AB_SUB + 512);
-        tma2d(sQD + stage * 2 * AB_SUB, &map_q64, &st_full[stage], head * AB_HD, qrow);
-        tma2d(sQD + stage * 2 * AB_SUB + AB_SUB, &map_do64, &st_full[stage], head * AB_HD, qrow);
-        bulk_g2s(sVec + stage * 128, p.lse + vidx, 256, &st_full[stage]);
-        bulk_g2s(sVec + stage * 128 + 64, p.Dsum + vidx, 256, &st_full[stage]);
+      uint32_t item_par = 0;
+      long long ubase = 0;
+      for (int item = blockIdx.x; item < p.n_items_kv && ok; item += gridDim.x, item_par ^= 1) {
+        const Item it = decode(item);
+        if (!mbar_wait(kv_empty, item_par ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, -1)) { ok = false; break; }
+        mbar_expect_tx(kv_full, 2 * AB_TILE);
+        tma2d(sK, &map_k, kv_full, it.kvh * AB_HD, it.key0);
+        tma2d(sV, &map_v, kv_full, it.kvh * AB_HD, it.key0);
+        for (int u = 0; u < it.nu && ok; ++u) {
+          const long long ug = ubase + u;
+          const int stage = (int)(ug % KV_STAGES);
+          const uint32_t phase = (uint32_t)((ug / KV_STAGES) & 1);
+          if (!mbar_wait(&st_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, u)) { ok = false; break; }
+          int qi, head, hh;
+          unit_coords(it, u, qi, head, hh);
+          const int qrow = it.b * p.S + qi * 128 + hh * 64;
+          const size_t vidx = ((size_t)it.b * p.H + head) * p.S + qi * 128 + hh * 64;
+          mbar_expect_tx(&st_full[stage], 2 * AB_SUB + 512);
+          tma2d(sQD + stage * 2 * AB_SUB, &map_q64, &st_full[stage], head * AB_HD, qrow);
+          tma2d(sQD + stage * 2 * AB_SUB + AB_SUB, &map_do64, &st_full[stage], head * AB_HD, qrow);
+          bulk_g2s(sVec + stage * 128, p.lse + vidx, 256, &st_full[stage]);
+          bulk_g2s(sVec + stage * 128 + 64, p.Dsum + vidx, 256, &st_full[stage]);
+        }
+        ubase += it.nu;
       }
       if (!ok) {
         mbar_drain(kv_full, 0);
+        mbar_drain(kv_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) mbar_drain(&st_full[s], 0), mbar_drain(&st_full[s], 1);
       }
     }
@@ -364,11 +423,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
     if (lane == 0) {
       constexpr uint32_t IDESC_T = make_idesc_bf16(128, 64, 0, 0);     // K Q^T and V dO^T
       constexpr uint32_t IDESC_A = make_idesc_bf16(128, 64, 0, 1);     // P^T (TMEM) x dO, dS^T (TMEM) x Q; B read N(=hd)-contiguous
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, ST_WAIT_FULL, -1);
       const uint32_t sk = smem_u32(sK), sv = smem_u32(sV);
-      auto issue_sdp = [&](int u) -> bool {
-        const int stage = u % KV_STAGES, buf = u & 1;
-        if (!mbar_wait(&st_full[stage], (u / KV_STAGES) & 1, abort_flag, p.status, ST_WAIT_FULL, u)) return false;
+      bool ok = true;
+      uint32_t item_par = 0;
+      long long ubase = 0;
+      auto issue_sdp = [&](long long ug) -> bool {
+        const int stage = (int)(ug % KV_STAGES), buf = (int)(ug & 1);
+        if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, (int)ug)) return false;
         tc_fence_after();
         const uint32_t sq = smem_u32(sQD + stage * 2 * AB_SUB), sdo = sq + AB_SUB;
         const uint32_t tS = tmem_base + buf * 128, tP = tS + 64;
@@ -379,23 +440,36 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
         umma_commit(&s_full[buf]);
         return true;
       };
-      for (int u = 0; u < 2 && u < nu && ok; ++u) ok = issue_sdp(u);
-      for (int u = 0; u < nu && ok; ++u) {
-        const int stage = u % KV_STAGES, buf = u & 1;
-        if (!mbar_wait(&p_full[buf], (u >> 1) & 1, abort_flag, p.status, ST_WAIT_MISC, u)) { ok = false; break; }
+      for (int item = blockIdx.x; item < p.n_items_kv && ok; item += gridDim.x, item_par ^= 1) {
+        const Item it = decode(item);
+        if (!mbar_wait(kv_full, item_par, abort_flag, p.status, ST_WAIT_FULL, -1)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sq = smem_u32(sQD + stage * 2 * AB_SUB), sdo = sq + AB_SUB;
-        const uint32_t tPt = tmem_base + buf * 128, tdSt = tPt + 64;
+        for (int u = 0; u < 2 && u < it.nu && ok; ++u) ok = issue_sdp(ubase + u);
+        for (int u = 0; u < it.nu && ok; ++u) {
+          const long long ug = ubase + u;
+          const int stage = (int)(ug % KV_STAGES), buf = (int)(ug & 1);
+          if (!mbar_wait(&p_full[buf], (uint32_t)((ug >> 1) & 1), abort_flag, p.status, ST_WAIT_MISC, u)) { ok = false; break; }
+          if (u == 0) {          // the previous item's dK/dV must have been read out before they are overwritten
+            if (!mbar_wait(acc_empty, item_par ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
+          }
+          tc_fence_after();
+          const uint32_t sq = smem_u32(sQD + stage * 2 * AB_SUB), sdo = sq + AB_SUB;
+          const uint32_t tPt = tmem_base + buf * 128, tdSt = tPt + 64;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)   // dV += P^T dO
-          umma_ts(tmem_base + 320, tPt + k * 8, make_smem_desc(sdo + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)   // dV += P^T dO
+            umma_ts(tmem_base + 320, tPt + k * 8, make_smem_desc(sdo + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)   // dK += dS^T Q
-          umma_ts(tmem_base + 256, tdSt + k * 8, make_smem_desc(sq + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&st_empty[stage]);
-        if (u + 2 < nu) ok = issue_sdp(u + 2);
+          for (int k = 0; k < 4; ++k)   // dK += dS^T Q
+            umma_ts(tmem_base + 256, tdSt + k * 8, make_smem_desc(sq + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&st_empty[stage]);
+          if (u + 2 < it.nu) ok = issue_sdp(ug + 2);
+        }
+        if (ok) {
+          umma_commit(acc_full);
+          umma_commit(kv_empty);        // K_j / V_j are no longer read once every MMA of this item has completed
+        }
+        ubase += it.nu;
       }
-      if (ok) umma_commit(acc_full);
     }
   } else {
     const int w = (warp - 2) >> 2;                 // this group handles units with (u & 1) == w
@@ -403,13 +477,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
     const int kk = quarter * 32 + lane;            // key row within the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     bool ok = true;
+    uint32_t item_par = 0;
+    long long ubase = 0;
+    for (int item = blockIdx.x; item < p.n_items_kv && ok; item += gridDim.x, item_par ^= 1) {
+    const Item it = decode(item);
+    const int j = it.j, kvh = it.kvh, key0 = it.key0, nu = it.nu;
     for (int u = w; u < nu; u += 2) {
-      const int stage = u % KV_STAGES;
-      if (!mbar_wait(&st_full[stage], (u / KV_STAGES) & 1, abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
-      if (!mbar_wait(&s_full[w], (u >> 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL, u)) { ok = false; break; }
+      const long long ug = ubase + u;
+      const int stage = (int)(ug % KV_STAGES);
+      if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
+      if (!mbar_wait(&s_full[w], (uint32_t)((ug >> 1) & 1), abort_flag, p.status, ST_WAIT_TMEM_FULL, u)) { ok = false; break; }
       tc_fence_after();
       int qi, head, hh;
-      unit_coords(u, qi, head, hh);
+      unit_coords(it, u, qi, head, hh);
       const uint32_t tS = tmem_base + w * 128 + lane_off, tP = tS + 64;
       uint32_t s[64], dp[64];
       PGB_TMEM_LD32(tS, (s));
@@ -454,7 +534,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
       tc_fence_before();
       mbar_arrive(&p_full[w]);
     }
-    if (ok && mbar_wait(acc_full, 0, abort_flag, p.status, ST_WAIT_MISC, nu)) {
+    if (ok && mbar_wait(acc_full, item_par, abort_flag, p.status, ST_WAIT_MISC, nu)) {
       tc_fence_after();
       // group 0 writes dK, group 1 writes dV
       const uint32_t tA = tmem_base + (w == 0 ? 256 : 320) + lane_off;
@@ -479,6 +559,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
               make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
         }
       }
+      tc_fence_before();
+      mbar_arrive(acc_empty);
+    } else {
+      ok = false;
+    }
+    ubase += nu;
     }
   }
   tc_fence_before();
@@ -516,6 +602,11 @@ void attn_bwd(const void* q, const void* k, const void* v, const void* o, const 
   p.lddq = lddq; p.lddk = lddk; p.lddv = lddv;
   p.accumulate_dv = accumulate_dv;
   p.status = status;
+  p.n_items_q = p.n_qt * B * Hkv * p.pairs;
+  p.n_items_kv = p.n_qt * B * Hkv;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
@@ -525,12 +616,12 @@ void attn_bwd(const void* q, const void* k, const void* v, const void* o, const 
   {
     const CUtensorMap mq = bwd_map(q, ldq, H * hd, T, 128), mk = bwd_map(k, ldk, Hkv * hd, T, 128), mv = bwd_map(v, ldv, Hkv * hd, T, 128),
                       mdo = bwd_map(d_o, lddo, H * hd, T, 128);
-    attn_bwd_dq_kernel<<<p.n_qt * B * Hkv * p.pairs, AB_THREADS, DQ_SMEM, st>>>(mq, mk, mv, mdo, p);
+    attn_bwd_dq_kernel<<<std::min(p.n_items_q, sms), AB_THREADS, DQ_SMEM, st>>>(mq, mk, mv, mdo, p);
   }
   {
     const CUtensorMap mq = bwd_map(q, ldq, H * hd, T, 64), mk = bwd_map(k, ldk, Hkv * hd, T, 128), mv = bwd_map(v, ldv, Hkv * hd, T, 128),
                       mdo = bwd_map(d_o, lddo, H * hd, T, 64);
-    attn_bwd_dkdv_kernel<<<p.n_qt * B * Hkv, AB_THREADS, KV_SMEM, st>>>(mq, mk, mv, mdo, p);
+    attn_bwd_dkdv_kernel<<<std::min(p.n_items_kv, sms), AB_THREADS, KV_SMEM, st>>>(mq, mk, mv, mdo, p);
   }
 }
 

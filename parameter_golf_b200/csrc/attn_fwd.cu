@@ -5,8 +5,10 @@
 // loaded once and used by both. Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer,
 // warps 2-5 softmax for head 0, warps 6-9 softmax for head 1. The two softmax groups ping-pong on the
 // tensor core: while one exponentiates its tile the other's QK^T / PV are in flight.
-//   TMEM: S0 [0,128) S1 [128,256) (fp32 scores; the bf16 probabilities P overwrite the first 64 columns
-//         of their own S and feed the PV MMA straight from tensor memory), O0 [256,320) O1 [320,384).
+//   TMEM: S0 [0,128) S1 [128,256) fp32 scores; P0 [256,320) P1 [320,384) bf16 probabilities (fed to the PV MMA straight
+//         from tensor memory); O0 [384,448) O1 [448,512).
+// P has its own columns so that the scores of tile j+1 can be issued as soon as the softmax group has pulled tile j
+// into registers (`s_free`), long before P(j) exists: the MMA round trip is off the softmax group's critical path.
 // The running maximum is updated lazily: probabilities are taken relative to a stale maximum and O is
 // rescaled in TMEM only when a row's maximum grows by more than 2^8, so the common iteration has no
 // accumulator traffic. Replaces the cuDNN SDPA graph of the reference
@@ -18,7 +20,7 @@
 
 namespace pgb {
 
-constexpr int AT_THREADS = 320;
+constexpr int AT_THREADS = 384;   // warp 0 TMA, warps 1 and 10 issue the MMAs of head 0 / head 1, warps 2..9 softmax, warp 11 idle
 constexpr int AT_BM = 128;   // query rows per tile
 constexpr int AT_BN = 128;   // keys per tile
 constexpr int AT_HD = 64;
@@ -60,8 +62,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint64_t* kv_empty = kv_full + AT_STAGES;
   uint64_t* s_full = kv_empty + AT_STAGES; // 2
   uint64_t* p_full = s_full + 2;           // 2
-  uint64_t* o_full = p_full + 2;           // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  uint64_t* o_full = p_full + 2;           // 2: one commit per PV
+  uint64_t* s_free = o_full + 2;           // 2: scores pulled into registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -83,12 +86,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(q_full, 1);
     for (int s = 0; s < AT_STAGES; ++s) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&kv_empty[s], n_active);
     }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&s_full[w], 1);
       mbar_init(&p_full[w], 128);
       mbar_init(&o_full[w], 1);
+      mbar_init(&s_free[w], 128);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -127,12 +131,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int s = 0; s < AT_STAGES; ++s) mbar_drain(&kv_full[s], (s < stage) ? phase : (phase ^ 1));
       }
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 10) {
+    const int w = warp == 1 ? 0 : 1;            // each head of the pair has its own issuing thread
+    if (lane == 0 && w < n_active) {
       constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);    // Q K^T : both K-major
       constexpr uint32_t IDESC_O = make_idesc_bf16(128, AT_HD, 0, 1);  // P V   : A from TMEM, V is N-contiguous
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_WAIT_FULL, -1);
-      auto issue_s = [&](int w, int stage) {
+      auto issue_s = [&](int stage) {
         const uint32_t sq = smem_u32(sQ + w * AT_TILE_BYTES);
         const uint32_t sk = smem_u32(sKV + stage * 2 * AT_TILE_BYTES);
 #pragma unroll
@@ -143,7 +148,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, ST_WAIT_FULL, 0);
       if (ok) {
         tc_fence_after();
-        for (int w = 0; w < n_active; ++w) issue_s(w, 0);
+        issue_s(0);
       }
       int stage = 0;
       uint32_t phase = 0;
@@ -153,32 +158,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (nstage == AT_STAGES) { nstage = 0; nphase ^= 1; }
         if (j + 1 < n_kv) {
           if (!mbar_wait(&kv_full[nstage], nphase, abort_flag, p.status, ST_WAIT_FULL, j + 1)) { ok = false; break; }
+          // scores of the next tile: only need the current ones to have been pulled into registers
+          if (!mbar_wait(&s_free[w], j & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, j)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(nstage);
         }
         const uint32_t sv = smem_u32(sKV + stage * 2 * AT_TILE_BYTES + AT_TILE_BYTES);
-        for (int w = 0; w < n_active && ok; ++w) {
-          if (!mbar_wait(&p_full[w], j & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
-          tc_fence_after();
+        if (!mbar_wait(&p_full[w], j & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < AT_BN / 16; ++k)
-            umma_ts(tmem_base + 256 + w * AT_HD, tmem_base + w * 128 + k * 8, make_smem_desc(sv + k * 2048, 8192, 1024), IDESC_O,
-                    (j > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&o_full[w]);
-          if (j + 1 < n_kv) issue_s(w, nstage);
-        }
-        if (!ok) break;
+        for (int k = 0; k < AT_BN / 16; ++k)
+          umma_ts(tmem_base + 384 + w * AT_HD, tmem_base + 256 + w * 64 + k * 8, make_smem_desc(sv + k * 2048, 8192, 1024), IDESC_O,
+                  (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&o_full[w]);
         umma_commit(&kv_empty[stage]);
         stage = nstage;
         phase = nphase;
       }
     }
   } else {
-    const int w = (warp - 2) >> 2;                 // softmax group / head within the pair
+    const int w = warp < 10 ? (warp - 2) >> 2 : 2; // softmax group / head within the pair (warp 11 idles)
     const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
     const int r = quarter * 32 + lane;             // query row within the tile
     if (w < n_active) {
       const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
       const uint32_t tS = tmem_base + w * 128 + lane_off;
-      const uint32_t tO = tmem_base + 256 + w * AT_HD + lane_off;
+      const uint32_t tO = tmem_base + 384 + w * AT_HD + lane_off;
+      const uint32_t tP = tmem_base + 256 + w * 64 + lane_off;
       float m_used = -INFINITY, l = 0.f;
       bool ok = true;
       for (int j = 0; j < n_kv; ++j) {
@@ -190,6 +196,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         PGB_TMEM_LD32(tS + 64, (s + 64));
         PGB_TMEM_LD32(tS + 96, (s + 96));
         tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&s_free[w]);                   // S(j) is in registers: the next tile's scores may overwrite it
         if (j == qt) {
 #pragma unroll
           for (int c = 0; c < 128; ++c)
@@ -202,30 +210,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int c = 8; c < 128; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], __uint_as_float(s[c]));      // 8 independent chains
         float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
         mx *= p.scale_log2;
-        if (j > 0) {
-          if (!mbar_wait(&o_full[w], (j - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
-        }
         const bool need = mx > m_used + 8.0f;
-        if (__any_sync(0xffffffffu, need)) {
+        const bool any_need = __any_sync(0xffffffffu, need);
+        float alpha = 1.f;
+        if (any_need) {
           const float m_new = need ? mx : m_used;
-          const float alpha = (m_used == -INFINITY) ? 0.f : ex2(m_used - m_new);
-          if (j > 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              uint32_t o[32];
-              PGB_TMEM_LD32(tO + h * 32, o);
-              tmem_wait_ld();
-#pragma unroll
-              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-              PGB_TMEM_ST16(tO + h * 32, (o));
-              PGB_TMEM_ST16(tO + h * 32 + 16, (o + 16));
-            }
-          }
+          alpha = (m_used == -INFINITY) ? 0.f : ex2(m_used - m_new);
           l *= alpha;
           m_used = m_new;
         }
-        // packed fp32x2 arithmetic: one FFMA2 scales and shifts two scores, one FADD2 accumulates two probabilities
         float2 sum2 = make_float2(0.f, 0.f), sum2b = make_float2(0.f, 0.f);
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-m_used, -m_used);
 #pragma unroll
@@ -238,8 +231,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             if (c & 1) sum2b = __fadd2_rn(sum2b, pr); else sum2 = __fadd2_rn(sum2, pr);
             pk[c] = pack_bf16x2(pr.x, pr.y);
           }
-          PGB_TMEM_ST16(tS + q * 16, pk);
+          if (q == 0 && j > 0) {
+            // P(j-1) is read by PV(j-1) and O is written by it: both must be finished before P(j) is stored / O rescaled.
+            // PV(j-1) was released a whole softmax phase ago, so this wait is normally already satisfied.
+            if (!mbar_wait(&o_full[w], (j - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
+            tc_fence_after();
+            if (any_need) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                uint32_t o[32];
+                PGB_TMEM_LD32(tO + h * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                PGB_TMEM_ST16(tO + h * 32, (o));
+                PGB_TMEM_ST16(tO + h * 32 + 16, (o + 16));
+              }
+            }
+          }
+          PGB_TMEM_ST16(tP + q * 16, pk);
         }
+        if (!ok) break;
         const float sum = (sum2.x + sum2.y) + (sum2b.x + sum2b.y);
         l += sum;
         tmem_wait_st();

@@ -94,8 +94,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` is a CTA-shared int: once any waiter gives up, every later wait in the
 // CTA returns false immediately.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                           int detail) {
+  if (mbar_test_wait(bar, parity)) return true;      // already complete: the non-suspending form answers much faster
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;

@@ -49,7 +49,7 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 32 * 80 /*epilogue staging*/;
 };
 
 __device__ __forceinline__ float act_fn(float x, float slope) { return x >= 0.f ? x : slope * x; }
@@ -139,6 +139,68 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
         }
     }
   }
+}
+
+// Aligned bf16 epilogue with coalesced global traffic. A thread owns one accumulator row, but 16-byte accesses of 32
+// different rows per instruction touch half a sector each; here rows are exchanged through a per-warp shared-memory
+// tile (32 rows x 64 B, 80-byte pitch) so that every global load/store instruction covers 8 rows x 64 contiguous bytes.
+// `ax` holds the aux operand in that coalesced pattern: piece i = row (i*8 + lane/4), bytes (lane%4)*16 .. +16.
+constexpr int STG_PITCH = 80;
+constexpr int STG_WARP_BYTES = 32 * STG_PITCH;
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p, int b, int m_base, int lane, int n0, const uint32_t (&r)[32],
+                                                      const uint4 (&ax)[4], uint8_t* stg) {
+  constexpr bool HAS_AUX = (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD);
+  const int srow = lane >> 2, spc = lane & 3;
+  float a[32];
+  if constexpr (HAS_AUX) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(stg + (i * 8 + srow) * STG_PITCH + spc * 16) = ax[i];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 q = *reinterpret_cast<const uint4*>(stg + lane * STG_PITCH + i * 16);
+      const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
+      a[8 * i] = f0.x; a[8 * i + 1] = f0.y; a[8 * i + 2] = f1.x; a[8 * i + 3] = f1.y;
+      a[8 * i + 4] = f2.x; a[8 * i + 5] = f2.y; a[8 * i + 6] = f3.x; a[8 * i + 7] = f3.y;
+    }
+    __syncwarp();
+  }
+  float o[32], o2[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float v = __uint_as_float(r[i]);
+    if constexpr (EPI == EPI_BF16) o[i] = v * p.alpha;
+    if constexpr (EPI == EPI_AXPBY_BF16) o[i] = p.alpha * v + p.beta * a[i];
+    if constexpr (EPI == EPI_RESID_BF16) o[i] = a[i] + p.colscale[n0 + i] * v;
+    if constexpr (EPI == EPI_ACT_SQ) {
+      const float h = __bfloat162float(__float2bfloat16(v));
+      const float t = act_fn(h, p.slope);
+      o[i] = h;
+      o2[i] = t * t;
+    }
+    if constexpr (EPI == EPI_MUL_ACTGRAD) {
+      const float h = a[i];
+      o[i] = v * 2.f * act_fn(h, p.slope) * (h >= 0.f ? 1.f : p.slope);
+    }
+  }
+  auto put = [&](const float (&x)[32], void* base) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      *reinterpret_cast<uint4*>(stg + lane * STG_PITCH + i * 16) = make_uint4(pack_bf16x2(x[8 * i], x[8 * i + 1]), pack_bf16x2(x[8 * i + 2], x[8 * i + 3]),
+                                                                             pack_bf16x2(x[8 * i + 4], x[8 * i + 5]), pack_bf16x2(x[8 * i + 6], x[8 * i + 7]));
+    __syncwarp();
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(base) + (long long)b * p.stride_d + n0 + spc * 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = m_base + i * 8 + srow;
+      if (row < p.M) *reinterpret_cast<uint4*>(d + (long long)row * p.ldd) = *reinterpret_cast<const uint4*>(stg + (i * 8 + srow) * STG_PITCH + spc * 16);
+    }
+    __syncwarp();
+  };
+  put(o, p.D);
+  if constexpr (EPI == EPI_ACT_SQ) put(o2, p.D2);
 }
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, int EPI>
@@ -288,6 +350,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may access
     const int half = (warp - 2) >> 2;             // which half of the tile's columns
+    uint8_t* stg = smem + S::TILE_BYTES + 256 + (warp - 2) * STG_WARP_BYTES;
+    const bool staged_ok = (p.ldd % 8 == 0) && (p.stride_d % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
+                           (p.aux == nullptr || ((p.ld_aux % 8 == 0) && (p.stride_aux % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0))) &&
+                           (p.D2 == nullptr || ((reinterpret_cast<uintptr_t>(p.D2) & 15) == 0));
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -304,10 +370,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       constexpr bool HAS_AUX = (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD);
       constexpr int CH = BN / 64;                   // 32-column chunks per epilogue warp (the two warps of a quarter split the columns)
       const int c_begin = half * CH;
+      constexpr bool BF16_OUT = !(EPI == EPI_F32 || EPI == EPI_F32_ATOMIC);
+      const int m_base = tm * BM + quarter * 32;
       auto load_aux = [&](int c, uint4 (&dst)[4]) {
         if constexpr (HAS_AUX) {
           const int n0 = tn * BN + c * 32;
-          if (m < p.M && n0 + 32 <= p.N) {
+          if (staged_ok && n0 + 32 <= p.N) {          // coalesced pattern: 8 rows x 64 B per instruction
+            const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + n0 + (lane & 3) * 8;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int row = m_base + i * 8 + (lane >> 2);
+              if (row < p.M) dst[i] = *reinterpret_cast<const uint4*>(ap + (long long)row * p.ld_aux);
+            }
+          } else if (m < p.M && n0 + 32 <= p.N) {
             const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + (long long)m * p.ld_aux + n0;
             if ((reinterpret_cast<uintptr_t>(ap) & 15) == 0) {
 #pragma unroll
@@ -328,7 +403,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t rr[32];
         PGB_TMEM_LD32(taddr + c * 32, rr);
         tmem_wait_ld();
-        if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax);
+        if constexpr (BF16_OUT) {
+          if (staged_ok && n0 + 32 <= p.N) epilogue_chunk_staged<EPI>(p, b, m_base, lane, n0, rr, ax, stg);
+          else if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax);
+        } else {
+          if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax);
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) ax[i] = axn[i];
       }

@@ -114,7 +114,8 @@ void symm_free(void* p);
 void expand_span_u16(const void* span, int* ids, int* targets, int n, cudaStream_t st);
 
 // ---- attention (attn_fwd.cu, attn_bwd.cu): causal, grouped KV heads, head_dim 64, bf16 ----------------------------------
-// q/k/v/y are [B*S, heads*hd] views with row strides ld* (elements); lse is fp32 [B, H, S] (natural log).
+// q/k/v/y are [B*S, heads*hd] views with row strides ld* (elements); lse is fp32 [B, H, S] and holds the NEGATED
+// base-2 log-sum-exp of the scaled scores (the form the backward kernels feed straight into their FMAs).
 void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, long long ldq, long long ldk, long long ldv, long long ldy, int B,
               int S, int H, int Hkv, int hd, int* status, cudaStream_t st);
 // dsum: fp32 [B, H, S] scratch-free side output (rowsum(dO * O)), written by the dQ kernel and read by the dK/dV kernel.

@@ -59,6 +59,7 @@ def build(force: bool = False, verbose: bool = True) -> str:
     from torch.utils import cpp_extension as ce
     os.makedirs(BUILD, exist_ok=True)
     cu, cpp, _ = _sources()
+    extra = os.environ.get("PGB_EXTRA_NVCC_FLAGS", "").split()     # development aid, e.g. -DPGB_DIAG_NO_EXP
     cuda_home = ce.CUDA_HOME or "/usr/local/cuda"
     nvcc = os.path.join(cuda_home, "bin", "nvcc")
     inc = [f"-I{p}" for p in ce.include_paths("cuda")] + [f"-I{sysconfig.get_paths()['include']}", f"-I{CSRC}"]
@@ -67,7 +68,7 @@ def build(force: bool = False, verbose: bool = True) -> str:
     for f in cu:
         o = os.path.join(BUILD, f + ".o")
         objs.append(o)
-        jobs.append(([nvcc, *NVCC_FLAGS, f"-I{CSRC}", "-c", os.path.join(CSRC, f), "-o", o], os.path.join(BUILD, f + ".log")))
+        jobs.append(([nvcc, *NVCC_FLAGS, *extra, f"-I{CSRC}", "-c", os.path.join(CSRC, f), "-o", o], os.path.join(BUILD, f + ".log")))
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     for f in cpp:
         o = os.path.join(BUILD, f + ".o")

@@ -92,7 +92,7 @@ def run_native(args):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from parameter_golf_b200.data.shards import DistributedTokenLoader
+    from parameter_golf_b200.data.native_loader import NativeTokenLoader
     from parameter_golf_b200.models import gpt
     from parameter_golf_b200.models.engine import EngineBackend
     from parameter_golf_b200.ops import native
@@ -121,13 +121,14 @@ def run_native(args):
     backend = EngineBackend(spec, params)
     T = backend.engine.T
     assert T * accum * world == GLOBAL_BATCH and backend.accum == accum
-    loader = DistributedTokenLoader(os.path.join(data_root, "fineweb_train_*.bin"), rank, world)
-    pinned = [torch.empty(T + 1, dtype=torch.int16).pin_memory() for _ in range(accum)]
+    # C++ loader: a worker thread reads the mmap'd shards ahead into a ring of page-locked buffers; one optimizer step's
+    # spans stay valid until the next step asks for its first one
+    loader = NativeTokenLoader(os.path.join(data_root, "fineweb_train_*.bin"), rank, world)
+    loader.start_prefetch(GLOBAL_BATCH, accum)
+    assert loader.pinned
 
     def next_spans():
-        for buf in pinned:
-            loader.next_span_u16(GLOBAL_BATCH, accum, out=buf.numpy().view(np.uint16))
-        return pinned
+        return [loader.next_prefetched() for _ in range(accum)]
 
     def sync_all():
         if world > 1:
@@ -141,7 +142,7 @@ def run_native(args):
     # ---- device-timed region: spans already resident on the GPU ----------------------------------------------------
     staged = []
     for _ in range(args.steps):
-        staged.append([s.to("cuda", non_blocking=True).clone() for s in next_spans()])
+        staged.append([s.to("cuda") for s in next_spans()])
     sync_all()
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -168,6 +169,7 @@ def run_native(args):
     e2e_ms = e2.elapsed_time(e3) / args.steps
     clocks = sampler.stop()
     native.check_status()
+    loader.stop_prefetch()
     t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

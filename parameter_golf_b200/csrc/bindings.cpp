@@ -2,6 +2,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <torch/extension.h>
 
+#include "loader.h"
 #include "pgb.h"
 
 namespace {

@@ -55,6 +55,11 @@ class _Counting:
         return call
 
 
+def load_raw():
+    """The extension module itself (classes and host-only helpers; nothing here counts as a kernel launch)."""
+    return load()._mod
+
+
 def launch_count() -> int:
     return 0 if _C is None else _C.launches
 

@@ -243,6 +243,13 @@ class VariantRunner:
             if hasattr(backend, "params_changed"):
                 backend.params_changed()
             log.info(f"resumed from {t.resume_from} at step {step0}")
+        if hasattr(backend, "train_step_spans"):
+            # CUDA backends read through the C++ loader: a worker thread keeps page-locked spans ahead of the step loop
+            from .data.native_loader import NativeTokenLoader
+            fast = NativeTokenLoader(t.train_data_pattern, t.rank, t.world_size)
+            fast.restore(loader.stream.state())
+            fast.start_prefetch(tokens_per_step, accum)
+            loader = fast
 
         max_steps = mode_max_steps(spec, mode)
         max_ms = 1000.0 * t.max_wallclock_seconds if t.max_wallclock_seconds > 0 else None
@@ -277,9 +284,7 @@ class VariantRunner:
             with timers.time("data"):
                 batches, spans = [], None
                 if hasattr(backend, "train_step_spans"):
-                    spans = backend.host_spans(accum)          # pinned uint16 staging buffers (2 bytes per token over PCIe)
-                    for buf in spans:
-                        loader.next_span_u16(tokens_per_step, accum, out=buf.numpy().view(np.uint16))
+                    spans = [loader.next_prefetched() for _ in range(accum)]     # page-locked uint16 spans (2 bytes per token over PCIe)
                 else:
                     for _ in range(accum):
                         x, y = loader.next_batch(tokens_per_step, t.seq_len, accum)
@@ -302,6 +307,8 @@ class VariantRunner:
                 save_checkpoint(t.checkpoint_path, res.fingerprint, step, backend.sync_params(), backend.state_dict(),
                                 loader.state(), ema.shadow if ema else None)
         train_ms += 1000.0 * (time.perf_counter() - t_start)
+        if hasattr(loader, "stop_prefetch"):
+            loader.stop_prefetch()
         res.steps = step - step0
         res.train_ms = train_ms
         res.step_avg_ms = train_ms / max(res.steps, 1)

@@ -105,3 +105,77 @@ def test_bpb_formula_and_luts():
     s = BpbLuts.seeded(1024)
     assert s.base_bytes.min() >= 1 and s.base_bytes.max() <= 6 and np.array_equal(s.base_bytes, BpbLuts.seeded(1024).base_bytes)
     assert BpbLuts.placeholder(8).base_bytes.tolist() == [4] * 8
+
+
+# ---- native (C++) loader --------------------------------------------------------------------------------------------
+
+def _native_or_skip():
+    from parameter_golf_b200.ops import native
+    try:
+        native.load_raw()
+    except Exception as e:          # no compiler / no torch headers on this machine
+        pytest.skip(f"extension unavailable: {e}")
+    from parameter_golf_b200.data.native_loader import NativeTokenLoader
+    return NativeTokenLoader
+
+
+def _write_three_shards(tmp_path):
+    import numpy as np
+    from parameter_golf_b200.data.shards import write_shard
+    rng = np.random.default_rng(3)
+    sizes = [1000, 0, 777]
+    for i, n in enumerate(sizes):
+        write_shard(str(tmp_path / f"tok_train_{i:06d}.bin"), rng.integers(0, 1024, size=n, dtype=np.uint16))
+    return str(tmp_path / "tok_train_*.bin")
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_native_loader_matches_python_loader(tmp_path, world):
+    import numpy as np
+    from parameter_golf_b200.data.shards import DistributedTokenLoader
+    Native = _native_or_skip()
+    pattern = _write_three_shards(tmp_path)
+    for rank in range(world):
+        a, b = DistributedTokenLoader(pattern, rank, world), Native(pattern, rank, world)
+        for step in range(9):                        # crosses shard ends, the empty shard and the wrap-around
+            x = a.next_span_u16(384, 2)
+            y = b.next_span_u16(384, 2)
+            assert np.array_equal(x, y), (rank, step)
+        assert a.stream.state() == b.state()
+
+
+def test_native_loader_prefetch_and_restore(tmp_path):
+    import numpy as np
+    from parameter_golf_b200.data.shards import DistributedTokenLoader
+    Native = _native_or_skip()
+    pattern = _write_three_shards(tmp_path)
+    ref = DistributedTokenLoader(pattern, 1, 2)
+    nat = Native(pattern, 1, 2)
+    nat.start_prefetch(256, 2)
+    got = []
+    for _ in range(6):
+        got.append(nat.next_prefetched().numpy().view(np.uint16).copy())
+    want = [ref.next_span_u16(256, 2).copy() for _ in range(6)]
+    for x, y in zip(want, got):
+        assert np.array_equal(x, y)
+    st = nat.state()
+    assert st == ref.stream.state()                  # spans the worker fetched ahead do not count
+    more_ref = [ref.next_span_u16(256, 2).copy() for _ in range(3)]
+    nat.restore(st)                                   # restarts the worker from the consumed position
+    more = [nat.next_prefetched().numpy().view(np.uint16).copy() for _ in range(3)]
+    for x, y in zip(more_ref, more):
+        assert np.array_equal(x, y)
+    nat.stop_prefetch()
+    z = nat.next_span_u16(256, 2)                     # synchronous path resumes where the consumer stopped
+    assert np.array_equal(z, ref.next_span_u16(256, 2))
+
+
+def test_native_loader_rejects_bad_shards(tmp_path):
+    import numpy as np
+    Native = _native_or_skip()
+    p = tmp_path / "bad_train_000000.bin"
+    hdr = np.zeros(256, dtype="<i4")
+    hdr[0], hdr[1], hdr[2] = 20240520, 1, 10
+    p.write_bytes(hdr.tobytes() + b"\x00" * 18)       # one token short
+    with pytest.raises(RuntimeError, match="does not match"):
+        Native(str(tmp_path / "bad_train_*.bin"))

@@ -115,10 +115,11 @@ def test_softcap_cross_entropy():
 
 
 def test_fake_quant_ste_forward_and_gradient():
+    torch.manual_seed(7)
     w = torch.randn(4, 16, requires_grad=True)
     wq = R.fake_quant_int6_ste(w)
     scale = (w.detach().abs().amax(1, keepdim=True) / 31).clamp_min(1 / 31)
     codes = wq.detach() / scale
-    assert torch.allclose(codes, codes.round(), atol=1e-5) and codes.min() >= -32 and codes.max() <= 31
+    assert torch.allclose(codes, codes.round(), atol=1e-5) and codes.min() >= -32 - 1e-4 and codes.max() <= 31 + 1e-4
     wq.sum().backward()
     assert torch.allclose(w.grad, torch.ones_like(w))

@@ -168,28 +168,68 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p,
     __syncwarp();
   }
   float o[32], o2[32];
+  float cs[32];
+  if constexpr (EPI == EPI_RESID_BF16) {
+    if ((reinterpret_cast<uintptr_t>(p.colscale + n0) & 15) == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(p.colscale + n0) + i);
+        cs[4 * i] = t.x; cs[4 * i + 1] = t.y; cs[4 * i + 2] = t.z; cs[4 * i + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) cs[i] = p.colscale[n0 + i];
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     const float v = __uint_as_float(r[i]);
     if constexpr (EPI == EPI_BF16) o[i] = v * p.alpha;
     if constexpr (EPI == EPI_AXPBY_BF16) o[i] = p.alpha * v + p.beta * a[i];
-    if constexpr (EPI == EPI_RESID_BF16) o[i] = a[i] + p.colscale[n0 + i] * v;
-    if constexpr (EPI == EPI_ACT_SQ) {
-      const float h = __bfloat162float(__float2bfloat16(v));
-      const float t = act_fn(h, p.slope);
-      o[i] = h;
-      o2[i] = t * t;
-    }
+    if constexpr (EPI == EPI_RESID_BF16) o[i] = a[i] + cs[i] * v;
     if constexpr (EPI == EPI_MUL_ACTGRAD) {
       const float h = a[i];
       o[i] = v * 2.f * act_fn(h, p.slope) * (h >= 0.f ? 1.f : p.slope);
     }
   }
-  auto put = [&](const float (&x)[32], void* base) {
+  uint32_t pk[16], pk2[16];
+  bool packed = false;
+  if constexpr (EPI == EPI_ACT_SQ) {
+    // With a slope that is zero or a power of two, slope*h is exact in bf16 and the square of a bf16 value rounds
+    // once either way, so the whole activation can run on packed bf16 pairs with bit-identical results.
+    if ((__float_as_uint(p.slope) & 0x007fffffu) == 0u && p.slope >= 0.f && p.slope < 1.f) {
+      packed = true;
+      const __nv_bfloat162 sl = __float2bfloat162_rn(p.slope);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const __nv_bfloat162 hb = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        const __nv_bfloat162 t = __hmax2(hb, __hmul2(hb, sl));
+        const __nv_bfloat162 sq = __hmul2(t, t);
+        pk[i] = *reinterpret_cast<const uint32_t*>(&hb);
+        pk2[i] = *reinterpret_cast<const uint32_t*>(&sq);
+      }
+    }
+  }
+  if (!packed) {
+    if constexpr (EPI == EPI_ACT_SQ) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float h = __bfloat162float(__float2bfloat16(__uint_as_float(r[i])));
+        const float t = act_fn(h, p.slope);
+        o[i] = h;
+        o2[i] = t * t;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      pk[i] = pack_bf16x2(o[2 * i], o[2 * i + 1]);
+      if constexpr (EPI == EPI_ACT_SQ) pk2[i] = pack_bf16x2(o2[2 * i], o2[2 * i + 1]);
+    }
+  }
+  auto put = [&](const uint32_t (&x)[16], void* base) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
-      *reinterpret_cast<uint4*>(stg + lane * STG_PITCH + i * 16) = make_uint4(pack_bf16x2(x[8 * i], x[8 * i + 1]), pack_bf16x2(x[8 * i + 2], x[8 * i + 3]),
-                                                                             pack_bf16x2(x[8 * i + 4], x[8 * i + 5]), pack_bf16x2(x[8 * i + 6], x[8 * i + 7]));
+      *reinterpret_cast<uint4*>(stg + lane * STG_PITCH + i * 16) = make_uint4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
     __syncwarp();
     __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(base) + (long long)b * p.stride_d + n0 + spc * 8;
 #pragma unroll
@@ -199,8 +239,8 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p,
     }
     __syncwarp();
   };
-  put(o, p.D);
-  if constexpr (EPI == EPI_ACT_SQ) put(o2, p.D2);
+  put(pk, p.D);
+  if constexpr (EPI == EPI_ACT_SQ) put(pk2, p.D2);
 }
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, int EPI>
@@ -364,8 +404,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       r -= split * p.tiles_m * p.tiles_n;
       const int tm = r / p.tiles_n, tn = r - tm * p.tiles_n;
       const int m = tm * BM + quarter * 32 + lane;
-      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, ST_WAIT_TMEM_FULL, tile)) { ok = false; break; }
-      tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       constexpr bool HAS_AUX = (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD);
       constexpr int CH = BN / 64;                   // 32-column chunks per epilogue warp (the two warps of a quarter split the columns)
@@ -391,26 +429,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       };
-      uint4 ax[4] = {};
-      load_aux(c_begin, ax);
+      // The whole tile's second operand is requested before the accumulator is waited for: its DRAM latency hides
+      // behind the main loop of this tile instead of stalling the first chunk.
+      uint4 ax[CH][4] = {};
+#pragma unroll
+      for (int cc = 0; cc < CH; ++cc)
+        if (tn * BN + (c_begin + cc) * 32 < p.N) load_aux(c_begin + cc, ax[cc]);
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, ST_WAIT_TMEM_FULL, tile)) { ok = false; break; }
+      tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < CH; ++cc) {
         const int c = c_begin + cc;
         const int n0 = tn * BN + c * 32;
         if (n0 >= p.N) break;                     // warp-uniform
-        uint4 axn[4] = {};
-        if (cc + 1 < CH) load_aux(c + 1, axn);    // next chunk's operand is in flight while this one is processed
         uint32_t rr[32];
         PGB_TMEM_LD32(taddr + c * 32, rr);
         tmem_wait_ld();
         if constexpr (BF16_OUT) {
-          if (staged_ok && n0 + 32 <= p.N) epilogue_chunk_staged<EPI>(p, b, m_base, lane, n0, rr, ax, stg);
-          else if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax);
+          if (staged_ok && n0 + 32 <= p.N) epilogue_chunk_staged<EPI>(p, b, m_base, lane, n0, rr, ax[cc], stg);
+          else if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax[cc]);
         } else {
-          if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax);
+          if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax[cc]);
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) ax[i] = axn[i];
       }
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);

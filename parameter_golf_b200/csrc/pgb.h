@@ -113,6 +113,11 @@ void symm_free(void* p);
 // ---- misc (misc.cu) ------------------------------------------------------------------------------------------------------
 void expand_span_u16(const void* span, int* ids, int* targets, int n, cudaStream_t st);
 
+// ---- post-training quantisation (gptq.cu) --------------------------------------------------------------------------------
+// GPTQ with fixed per-row scales: Wp [rows, cols] fp32 (columns already in activation order), U [cols, cols] upper
+// Cholesky factor of the inverse Hessian, Q int8 codes out. Column blocks of 128.
+void gptq_rows(const float* Wp, const float* U, const float* scales, int8_t* Q, int rows, int cols, int bits, cudaStream_t st);
+
 // ---- attention (attn_fwd.cu, attn_bwd.cu): causal, grouped KV heads, head_dim 64, bf16 ----------------------------------
 // q/k/v/y are [B*S, heads*hd] views with row strides ld* (elements); lse is fp32 [B, H, S] and holds the NEGATED
 // base-2 log-sum-exp of the scaled scores (the form the backward kernels feed straight into their FMAs).

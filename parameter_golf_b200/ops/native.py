@@ -42,6 +42,7 @@ class _Counting:
     def __init__(self, mod):
         self._mod = mod
         self.launches = 0
+        self.timing = None           # list of (key, start event, end event) while per-op timing is on
 
     def __getattr__(self, name):
         fn = getattr(self._mod, name)
@@ -49,10 +50,47 @@ class _Counting:
 
         def call(*a, **k):
             self.launches += n
-            return fn(*a, **k)
+            if self.timing is None:
+                return fn(*a, **k)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*a, **k)
+            e1.record()
+            self.timing.append((_timing_key(name, a, k), e0, e1))
+            return out
 
         self.__dict__[name] = call
         return call
+
+
+_EPI_NAMES = {0: "bf16", 1: "f32", 2: "f32_atomic", 3: "axpby", 4: "resid", 5: "act_sq", 6: "mul_actgrad"}
+
+
+def _timing_key(name, a, k):
+    if name == "gemm":           # (A, B, D, a_kmajor, b_kmajor, epi, ...): tell the products of the step apart
+        A, B, D = a[0], a[1], a[2]
+        kdim = A.shape[-1] if a[3] else A.shape[-2]
+        return f"gemm {_EPI_NAMES.get(int(a[5]), a[5])} N={D.shape[-1]} K={kdim} {'T' if a[3] else 'N'}{'T' if a[4] else 'N'}"
+    return name
+
+
+def enable_timing(on: bool = True) -> None:
+    """Per-op device timing: every call through the extension is bracketed by two CUDA events on the current stream
+    (no synchronisation is added; `timing_report` reads them afterwards). A development aid for step breakdowns."""
+    load().timing = [] if on else None
+
+
+def timing_report(reset: bool = True):
+    """{key: (calls, total_ms)} of the calls recorded since `enable_timing`."""
+    C = load()
+    torch.cuda.synchronize()
+    out = {}
+    for key, e0, e1 in C.timing or []:
+        c, t = out.get(key, (0, 0.0))
+        out[key] = (c + 1, t + e0.elapsed_time(e1))
+    if reset and C.timing is not None:
+        C.timing = []
+    return out
 
 
 def load_raw():
@@ -109,3 +147,12 @@ def attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=F
         dsum = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
     load().attn_bwd(q, k, v, o, d_o, lse, dsum, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv, status_word(q.device))
     return dsum
+
+
+def gptq_rows(Wp, U, scales, bits, block=128):
+    """GPTQ row kernel (one clip candidate): int8 codes for the permuted rows ``Wp`` given the Cholesky factor ``U``."""
+    if block != 128:
+        raise ValueError("the GPTQ kernel works on 128-column blocks")
+    Q = torch.empty(Wp.shape, dtype=torch.int8, device=Wp.device)
+    load().gptq_rows(Wp.contiguous().float(), U.contiguous().float(), scales.contiguous().float(), Q, bits)
+    return Q

@@ -75,7 +75,12 @@ def gptq_quantize(W: torch.Tensor, H: torch.Tensor, bits: int = 6, block: int = 
     perm, inv_perm, U = gptq_prepare(H.to(W.device), damping)
     Wp = W[:, perm].contiguous()
     srt = W.abs().sort(dim=1).values
-    rows_fn = rows_fn or gptq_rows_torch
+    if rows_fn is None:
+        if W.is_cuda and block == 128:
+            from ..ops import native                  # on a GPU the hand-written row kernel is the path; no silent fallback
+            rows_fn = native.gptq_rows
+        else:
+            rows_fn = gptq_rows_torch
     best_err = torch.full((rows,), float("inf"), device=W.device)
     best_q = torch.zeros_like(Wp, dtype=torch.int8)
     best_s = torch.ones(rows, device=W.device)

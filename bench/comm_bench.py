@@ -8,7 +8,8 @@ Counterpart of the reference's ``nccl-bench`` (all-reduce / reduce-scatter / all
 the four weight banks of the 11-layer model (QKV 512x1024, O 512x512, MLP 512x1536 and 1536x512 per layer), scaled
 ``width`` times in both dimensions.
 
-Two pipelines are timed per width, each as (ours) vs (NCCL + torch/cuBLAS):
+Two pipelines are timed per width, each as (ours) vs (NCCL + torch/cuBLAS), and the collective step of each alone
+(``rs``: peer-load reduce vs ``reduce_scatter_tensor``; ``ag``: store fan-out + ready counters vs ``all_gather_into_tensor``):
 
 * ``rs_ns``  gradient reduce-scatter fused with the Newton-Schulz input: every rank reduces its own slots of the fp32
   gradient banks straight out of its peers' memory (plain NVLink loads, no staging copy), then momentum + Frobenius
@@ -141,11 +142,29 @@ def main():
             torch.cuda.synchronize()
             dist.barrier()
 
+        def ours_rs_only():
+            barrier()
+            for k, s in shapes.items():
+                s0, s1 = own[k]
+                if s1 > s0:
+                    per = s[1] * s[2]
+                    C.comm_reduce_peers(gbuf.table, world, g_off[k] + s0 * per, (s1 - s0) * per, red[k], 1.0 / world, stats, 1.0)
+
+        def nccl_rs_only():
+            for k in shapes:
+                dist.reduce_scatter_tensor(shard[k], gpad[k], op=dist.ReduceOp.AVG)
+
         total = off
         rs_bytes = total * 4 * (world - 1) / world
+        roof = rs_bytes / (LINK_GBS * 1e9) * 1e3
+        t_ours = timed(ours_rs_only, args.iters, pre)
+        t_nccl = timed(nccl_rs_only, args.iters, pre)
+        rows.append({"pipeline": "rs", "width": w, "gpus": world, "ours_ms": round(t_ours, 4), "nccl_ms": round(t_nccl, 4),
+                     "nvlink_bytes_per_rank": int(rs_bytes), "ours_bus_gbs": round(rs_bytes / t_ours / 1e6, 1),
+                     "nccl_bus_gbs": round(rs_bytes / t_nccl / 1e6, 1), "roofline_ms": round(roof, 4),
+                     "ours_frac_of_roofline": round(roof / t_ours, 3), "nccl_frac_of_roofline": round(roof / t_nccl, 3)})
         t_ours = timed(ours_rs, args.iters, pre)
         t_nccl = timed(nccl_rs, args.iters, pre)
-        roof = rs_bytes / (LINK_GBS * 1e9) * 1e3
         rows.append({"pipeline": "rs_ns", "width": w, "gpus": world, "ours_ms": round(t_ours, 4), "nccl_ms": round(t_nccl, 4),
                      "nvlink_bytes_per_rank": int(rs_bytes), "ours_bus_gbs": round(rs_bytes / t_ours / 1e6, 1),
                      "nccl_bus_gbs": round(rs_bytes / t_nccl / 1e6, 1), "roofline_ms": round(roof, 4),
@@ -177,29 +196,54 @@ def main():
                 return s, w_off["up"] + s * 3 * d * d
             return s, w_off["down"] + s * 3 * d * d
 
+        desc = {}
+        for k, s in shapes.items():
+            s0, s1 = own[k]
+            rows_d = []
+            for slot in range(s0, s1):
+                layer, dst = dst_of(k, slot)
+                rows_d.append([dst, -1, 0, 128 + layer])
+            desc[k] = torch.tensor(rows_d, dtype=torch.int64, device="cuda").reshape(-1, 4)
+
+        def ours_push():
+            for k, s in shapes.items():
+                if own[k][1] > own[k][0]:
+                    C.comm_push_cast_slots(master[k], wbuf.table, world, desc[k], s[2], False)     # one launch per bank shard
+                    C.comm_flag_add_slots(sig.table, world, desc[k], 1)
+
         def ours_ag():
             step[0] += 1
-            for k, s in shapes.items():
-                s0, s1 = own[k]
-                for slot in range(s0, s1):
-                    layer, dst = dst_of(k, slot)
-                    C.comm_push_cast_rows(master[k][slot - s0], wbuf.table, world, dst, None, 0, 1, s[2], False)
-                    C.comm_flag_add(sig.table, world, 128 + layer, 1, 1)
+            ours_push()
             # layer 0 is complete once its Q, K, V, O, up and down slots have all arrived: 6 increments per step
             N.gemm(X, Wqkv0, Y, wait_flag=flags[128:129], wait_value=6 * step[0])
+
+        def ours_ag_only():
+            step[0] += 1
+            ours_push()
+            C.comm_wait_flag(flags[128:129], 6 * step[0], N.status_word())
 
         shard_w = {k: torch.randn((pad[k],) + s[1:], device="cuda").bfloat16() for k, s in shapes.items()}
         full_w = {k: torch.empty((pad[k] * world,) + s[1:], device="cuda", dtype=torch.bfloat16) for k, s in shapes.items()}
         Wq_lib = torch.randn(qkvw, d, device="cuda").bfloat16()
 
-        def nccl_ag():
+        def nccl_ag_only():
             for k in shapes:
                 dist.all_gather_into_tensor(full_w[k], shard_w[k])
+
+        def nccl_ag():
+            nccl_ag_only()
             torch.matmul(X, Wq_lib.t(), out=Y)
 
         params = sum(s[0] * s[1] * s[2] for s in shapes.values())
         ag_bytes = params * 2 * (world - 1) / world
         flops = 2.0 * T * qkvw * d
+        roof = ag_bytes / (LINK_GBS * 1e9) * 1e3
+        t_ours = timed(ours_ag_only, args.iters, pre)
+        t_nccl = timed(nccl_ag_only, args.iters, pre)
+        rows.append({"pipeline": "ag", "width": w, "gpus": world, "ours_ms": round(t_ours, 4), "nccl_ms": round(t_nccl, 4),
+                     "nvlink_bytes_per_rank": int(ag_bytes), "ours_bus_gbs": round(ag_bytes / t_ours / 1e6, 1),
+                     "nccl_bus_gbs": round(ag_bytes / t_nccl / 1e6, 1), "roofline_ms": round(roof, 4),
+                     "ours_frac_of_roofline": round(roof / t_ours, 3), "nccl_frac_of_roofline": round(roof / t_nccl, 3)})
         t_ours = timed(ours_ag, args.iters, pre)
         t_nccl = timed(nccl_ag, args.iters, pre)
         roof = max(ag_bytes / (LINK_GBS * 1e9), flops / (peak_tf * 1e12)) * 1e3
@@ -213,7 +257,7 @@ def main():
         wbuf.close()
         torch.cuda.empty_cache()
         if rank == 0:
-            for r in rows[-2:]:
+            for r in rows[-4:]:
                 print(f"[w={w} N={world}] {r['pipeline']:7s} ours {r['ours_ms']:9.3f} ms ({r['ours_bus_gbs']:7.1f} GB/s, {r['ours_frac_of_roofline']:.2f} of roofline)"
                       f"   NCCL {r['nccl_ms']:9.3f} ms ({r['nccl_bus_gbs']:7.1f} GB/s, {r['nccl_frac_of_roofline']:.2f})", flush=True)
     if rank == 0:

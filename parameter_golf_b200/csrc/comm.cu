@@ -54,19 +54,39 @@ __global__ void barrier_kernel(int* const* __restrict__ sig_tbl, int my_rank, in
 }
 
 // out[i] = scale * sum_r src_tbl[r][off + i], i in [0, n); stats[0] += sq_weight * sum(out^2). n, off multiples of 4.
-__global__ void __launch_bounds__(256) reduce_peers_kernel(const float* const* __restrict__ src_tbl, int world, long long off, long long n,
+// WORLD > 0 fixes the rank count at compile time: all peers' 16-byte loads of one element group are issued before the
+// first add, so a thread keeps WORLD NVLink requests in flight instead of one.
+template <int WORLD>
+__global__ void __launch_bounds__(256) reduce_peers_kernel(const float* const* __restrict__ src_tbl, int world_rt, long long off, long long n,
                                                            float* __restrict__ out, float scale, float* __restrict__ stats, float sq_weight) {
   float s = 0.f;
   const long long stride = (long long)gridDim.x * blockDim.x * 4;
-  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < world; ++r) {
-      const float4 v = *reinterpret_cast<const float4*>(src_tbl[r] + off + i);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  if constexpr (WORLD > 0) {
+    const float* src[WORLD];
+#pragma unroll
+    for (int r = 0; r < WORLD; ++r) src[r] = src_tbl[r] + off;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+      float4 v[WORLD];
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) v[r] = *reinterpret_cast<const float4*>(src[r] + i);
+      float4 acc = v[0];
+#pragma unroll
+      for (int r = 1; r < WORLD; ++r) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      *reinterpret_cast<float4*>(out + i) = acc;
+      s += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
     }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-    *reinterpret_cast<float4*>(out + i) = acc;
-    s += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  } else {
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world_rt; ++r) {
+        const float4 v = *reinterpret_cast<const float4*>(src_tbl[r] + off + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      *reinterpret_cast<float4*>(out + i) = acc;
+      s += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    }
   }
   if (stats) {
     s = warp_sum(s);
@@ -134,6 +154,57 @@ __global__ void __launch_bounds__(256) push_cast_rows_kernel(const float* __rest
   }
 }
 
+// The same for a run of consecutive bank slots in ONE launch.  desc[s] = {destination element offset of slot s,
+// offset of its un-scaled twin or -1, address of its first row scale or 0, index of its ready counter}; slot s starts
+// at src + s * rows * cols.  Slots with a row scale write both the scaled rows and the un-scaled twin.
+__global__ void __launch_bounds__(256) push_cast_slots_kernel(const float* __restrict__ src, __nv_bfloat16* const* __restrict__ dst_tbl, int world,
+                                                              const long long* __restrict__ desc, int n_slots, int rows, int cols, long long ld_dst,
+                                                              int qat) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long total = (long long)n_slots * rows;
+  for (long long item = (long long)blockIdx.x * 8 + warp; item < total; item += (long long)gridDim.x * 8) {
+    const int slot = (int)(item / rows), row = (int)(item - (long long)slot * rows);
+    const long long dst_off = desc[slot * 4], dst_plain = desc[slot * 4 + 1];
+    const float* rowscale = reinterpret_cast<const float*>(desc[slot * 4 + 2]);
+    const float* s = src + ((size_t)slot * rows + row) * cols;
+    float qs = 0.f;
+    if (qat) {
+      float mx = 0.f;
+      for (int c = lane * 4; c < cols; c += 128) {
+        float4 a = *reinterpret_cast<const float4*>(s + c);
+        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+      }
+      mx = warp_max(mx);
+      qs = fmaxf(mx / 31.f, 1.f / 31.f);
+    }
+    const float rs = rowscale ? rowscale[row] : 1.f;
+    for (int c = lane * 4; c < cols; c += 128) {
+      float4 a = *reinterpret_cast<const float4*>(s + c);
+      if (qat) {
+        a.x = fminf(fmaxf(rintf(a.x / qs), -32.f), 31.f) * qs;
+        a.y = fminf(fmaxf(rintf(a.y / qs), -32.f), 31.f) * qs;
+        a.z = fminf(fmaxf(rintf(a.z / qs), -32.f), 31.f) * qs;
+        a.w = fminf(fmaxf(rintf(a.w / qs), -32.f), 31.f) * qs;
+      }
+      const uint2 p = make_uint2(pack_bf16x2(a.x * rs, a.y * rs), pack_bf16x2(a.z * rs, a.w * rs));
+      for (int r = 0; r < world; ++r) *reinterpret_cast<uint2*>(dst_tbl[r] + dst_off + (size_t)row * ld_dst + c) = p;
+      if (dst_plain >= 0) {
+        const uint2 q = make_uint2(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w));
+        for (int r = 0; r < world; ++r) *reinterpret_cast<uint2*>(dst_tbl[r] + dst_plain + (size_t)row * ld_dst + c) = q;
+      }
+    }
+  }
+}
+
+// One increment per (rank, slot) on the ready counter that desc names for the slot.
+__global__ void flag_add_slots_kernel(int* const* __restrict__ sig_tbl, int world, const long long* __restrict__ desc, int n_slots, int value) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < world * n_slots) {
+    __threadfence_system();
+    red_release_sys_add(sig_tbl[i / n_slots] + (int)desc[(i % n_slots) * 4 + 3], value);
+  }
+}
+
 // Fan-out copy: dst_tbl[r][off + i] = src[i] for every rank r != my_rank (second half of a two-shot all-reduce).
 __global__ void __launch_bounds__(256) push_copy_kernel(const float* __restrict__ src, float* const* __restrict__ dst_tbl, int world, int my_rank,
                                                         long long off, long long n) {
@@ -165,8 +236,13 @@ void comm_reduce_peers(const float* const* src_tbl, int world, long long off, lo
                        cudaStream_t st) {
   if ((off % 4) || (n % 4)) throw std::runtime_error("reduce_peers: offset and count must be multiples of 4");
   if (n == 0) return;
-  const int grid = (int)std::max<long long>(1, std::min<long long>((n / 4 + 255) / 256, 148 * 4));
-  reduce_peers_kernel<<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight);
+  const int grid = (int)std::max<long long>(1, std::min<long long>((n / 4 + 255) / 256, 148 * 8));
+  switch (world) {
+    case 2: reduce_peers_kernel<2><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight); break;
+    case 4: reduce_peers_kernel<4><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight); break;
+    case 8: reduce_peers_kernel<8><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight); break;
+    default: reduce_peers_kernel<0><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight); break;
+  }
 }
 void comm_scalar_allreduce(float* const* val_tbl, int* const* sig_tbl, int my_rank, int world, int val_slot, int sig_slot, int epoch, float* stats,
                            int* status, cudaStream_t st) {
@@ -177,6 +253,18 @@ void comm_push_cast_rows(const float* src, void* const* dst_tbl, int world, long
   if (cols % 4) throw std::runtime_error("push_cast_rows: cols must be a multiple of 4");
   push_cast_rows_kernel<<<std::min((rows + 7) / 8, 148 * 8), 256, 0, st>>>(src, (__nv_bfloat16* const*)dst_tbl, world, dst_off, rowscale, scale_stride,
                                                                           std::max(scale_mod, 1), rows, cols, ld_dst, qat);
+}
+void comm_push_cast_slots(const float* src, void* const* dst_tbl, int world, const long long* desc, int n_slots, int rows, int cols, long long ld_dst,
+                          int qat, cudaStream_t st) {
+  if (cols % 4) throw std::runtime_error("push_cast_slots: cols must be a multiple of 4");
+  if (n_slots <= 0) return;
+  const long long blocks = ((long long)n_slots * rows + 7) / 8;
+  push_cast_slots_kernel<<<(int)std::min<long long>(blocks, 148 * 8), 256, 0, st>>>(src, (__nv_bfloat16* const*)dst_tbl, world, desc, n_slots, rows, cols,
+                                                                                   ld_dst, qat);
+}
+void comm_flag_add_slots(int* const* sig_tbl, int world, const long long* desc, int n_slots, int value, cudaStream_t st) {
+  if (n_slots <= 0) return;
+  flag_add_slots_kernel<<<(world * n_slots + 63) / 64, 64, 0, st>>>(sig_tbl, world, desc, n_slots, value);
 }
 void comm_push_copy(const float* src, float* const* dst_tbl, int world, int my_rank, long long off, long long n, cudaStream_t st) {
   if ((off % 4) || (n % 4)) throw std::runtime_error("push_copy: offset and count must be multiples of 4");

@@ -101,6 +101,11 @@ void comm_scalar_allreduce(float* const* val_tbl, int* const* sig_tbl, int my_ra
                            int* status, cudaStream_t st);
 void comm_push_cast_rows(const float* src, void* const* dst_tbl, int world, long long dst_off, const float* rowscale, int scale_stride, int scale_mod,
                          int rows, int cols, long long ld_dst, int qat, cudaStream_t st);
+// A run of consecutive bank slots in one launch; desc = int64 [n_slots][4] on the device:
+// {destination offset, offset of the un-scaled twin or -1, address of the slot's row scales or 0, ready-counter index}.
+void comm_push_cast_slots(const float* src, void* const* dst_tbl, int world, const long long* desc, int n_slots, int rows, int cols, long long ld_dst,
+                          int qat, cudaStream_t st);
+void comm_flag_add_slots(int* const* sig_tbl, int world, const long long* desc, int n_slots, int value, cudaStream_t st);
 void comm_push_copy(const float* src, float* const* dst_tbl, int world, int my_rank, long long off, long long n, cudaStream_t st);
 void comm_flag_add(int* const* sig_tbl, int world, int slot, int count, int value, cudaStream_t st);
 void comm_wait_flag(const int* flag, int want, int* status, cudaStream_t st);

@@ -99,6 +99,14 @@ class DistributedStep:
         e.layer_flags = self.sig_local[SIG_LAYER:SIG_LAYER + e.n] if self.sharded else None
         e.layer_flag_value = 0
         self.own = {k: shard_range(e.p[k].shape[0], self.rank, self.world) for k in gpt.BANKS}
+        # one descriptor row per owned slot: where its bf16 rows go on every rank, where the un-scaled twin goes, which row
+        # scales apply, and which per-layer ready counter it bumps; a whole bank shard is then pushed by one launch
+        self.push_desc: Dict[str, torch.Tensor] = {}
+        if self.sharded:
+            for k in gpt.BANKS:
+                s0, s1 = self.own[k]
+                rows = [self._slot_desc(k, s) for s in range(s0, s1)]
+                self.push_desc[k] = torch.tensor(rows, dtype=torch.int64, device="cuda").reshape(-1, 4)
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
@@ -106,28 +114,32 @@ class DistributedStep:
     def _barrier(self, slot):
         self.C.comm_barrier(self.sig.table, self.rank, self.world, slot, self.epoch, N.status_word())
 
-    def _push_slot(self, bank: str, s: int):
-        """Write the bf16 compute rows of bank slot ``s`` into every rank and bump that layer's ready counter."""
-        e, C = self.e, self.C
-        n, d, kv, mlp, q = e.n, e.d, e.kv, e.mlp, e.qat
-        src = e.p[bank][s]
+    def _slot_desc(self, bank: str, s: int):
+        """(destination offset, un-scaled twin offset or -1, address of the row scales or 0, ready-counter index) of a slot."""
+        e = self.e
+        n, d, kv, mlp = e.n, e.d, e.kv, e.mlp
+        per = e.p[bank][0].numel()
         if bank == "qo_bank" and s < n:
-            layer, dst, ld, rs = s, self.w_off["Wqkv"] + s * e.qkvw * d, d, None
-        elif bank == "qo_bank":
+            return [self.w_off["Wqkv"] + s * e.qkvw * d, -1, 0, SIG_LAYER + s]
+        if bank == "qo_bank":
             layer = s - n
-            dst, ld, rs = self.w_off["Wo"] + layer * d * d, d, e.p["attn_scale"][layer]
-        elif bank == "kv_bank":
+            return [self.w_off["Wo"] + layer * d * d, self.w_off["Wo_u"] + layer * per, e.p["attn_scale"][layer].data_ptr(), SIG_LAYER + layer]
+        if bank == "kv_bank":
             layer = s % n
-            dst, ld, rs = self.w_off["Wqkv"] + layer * e.qkvw * d + (d if s < n else d + kv) * d, d, None
-        elif bank == "mlp_up_bank":
-            layer, dst, ld, rs = s, self.w_off["Wup"] + s * mlp * d, d, None
-        else:
-            layer, dst, ld, rs = s, self.w_off["Wd"] + s * d * mlp, mlp, e.p["mlp_scale"][s]
-        C.comm_push_cast_rows(src, self.wbuf.table, self.world, dst, rs, 1 if rs is not None else 0, src.shape[0] if rs is not None else 1, ld, q)
-        if rs is not None:      # the un-scaled copy that the scale-gradient fold reads
-            dst_u = self.w_off["Wo_u" if bank == "qo_bank" else "Wd_u"] + layer * src.numel()
-            C.comm_push_cast_rows(src, self.wbuf.table, self.world, dst_u, None, 0, 1, ld, q)
-        C.comm_flag_add(self.sig.table, self.world, SIG_LAYER + layer, 1, 1)
+            return [self.w_off["Wqkv"] + layer * e.qkvw * d + (d if s < n else d + kv) * d, -1, 0, SIG_LAYER + layer]
+        if bank == "mlp_up_bank":
+            return [self.w_off["Wup"] + s * mlp * d, -1, 0, SIG_LAYER + s]
+        return [self.w_off["Wd"] + s * d * mlp, self.w_off["Wd_u"] + s * per, e.p["mlp_scale"][s].data_ptr(), SIG_LAYER + s]
+
+    def _push_bank(self, bank: str):
+        """Write the bf16 compute rows of every owned slot of ``bank`` into every rank (one launch) and bump the ready
+        counters of the layers they belong to (one more)."""
+        s0, s1 = self.own[bank]
+        if s1 <= s0:
+            return
+        e, C = self.e, self.C
+        C.comm_push_cast_slots(e.p[bank][s0:s1], self.wbuf.table, self.world, self.push_desc[bank], e.p[bank].shape[-1], e.qat)
+        C.comm_flag_add_slots(self.sig.table, self.world, self.push_desc[bank], 1)
 
     def repush_weights(self):
         """Re-publish the bf16 weights of the owned slots without an update (used when the fake-quant setting changes).
@@ -136,8 +148,7 @@ class DistributedStep:
             self.e.cast_weights()
             return
         for k in gpt.BANKS:
-            for s in range(*self.own[k]):
-                self._push_slot(k, s)
+            self._push_bank(k)
         self.e.cast_weights(banks=False)
         self.repushes += 1
         self.e.layer_flag_value = 6 * (self.steps_done + self.repushes)
@@ -179,8 +190,7 @@ class DistributedStep:
             X = e.newton_schulz(k, cnt)
             scale = max(1.0, e.p[k].shape[-2] / e.p[k].shape[-1]) ** 0.5
             C.muon_apply(e.p[k][s0:s1].view(-1), X.reshape(-1), e.ema[k][s0:s1].view(-1) if e.ema else None, e.hp, t.matrix_lr, t.muon_wd, scale, decay)
-            for s in range(s0, s1):
-                self._push_slot(k, s)
+            self._push_bank(k)
         e.cast_weights(banks=False)
         e.layer_flag_value = 6 * (self.steps_done + 1 + self.repushes)
 

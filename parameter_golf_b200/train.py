@@ -338,7 +338,7 @@ class VariantRunner:
                 hess = self_generated_hessians(spec, final, device=device if t.backend != "cpu" else "cpu",
                                                num_seqs=spec.quant.gptq_calibration_batches if mode == "record" else 2,
                                                seq_len=m.train_seq_len if mode == "record" else min(m.train_seq_len, 64))
-                precomputed = gptq_quantize_model(spec, final, hess)
+                precomputed = gptq_quantize_model(spec, final, hess, device=device if t.backend != "cpu" else None)
             blob = export_model(spec, final, t.artifact_path if t.rank == 0 else None, precomputed) if spec.quant.scheme != "none" else b""
         res.artifact_bytes = len(blob)
         res.code_bytes = code_bytes()

@@ -29,8 +29,21 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-PUBLISHED_TOKENS_PER_S = 786_432 / 0.0834          # 8xH100, 83.4 ms/step
-GLOBAL_BATCH, SEQ_LEN, VOCAB = 786_432, 2048, 1024
+VOCAB = 1024
+# name -> (spec family, tokens per step, seq_len, published tokens/s on 8xH100, description)
+CONFIGS = {
+    "record_11l": ("record_11l", 786_432, 2048, 786_432 / 0.0834,
+                   "record_11l (11L d512 8H/4KV MLP3x LeakyReLU^2 XSA4 RoPE16 BigramHash3072x128 SmearGate tied-1024)"),
+    "baseline_9l": ("baseline_9l", 524_288, 1024, 524_288 / 0.04354,
+                    "baseline_9l (9L d512 8H/4KV MLP2x relu^2 full RoPE tied-1024 softcap 30)"),
+}
+PUBLISHED_TOKENS_PER_S = CONFIGS["record_11l"][3]
+GLOBAL_BATCH, SEQ_LEN = 786_432, 2048
+
+
+def select_config(name: str):
+    global GLOBAL_BATCH, SEQ_LEN, PUBLISHED_TOKENS_PER_S
+    _, GLOBAL_BATCH, SEQ_LEN, PUBLISHED_TOKENS_PER_S, _ = CONFIGS[name]
 
 
 class ClockSampler:
@@ -106,7 +119,7 @@ def run_native(args):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    spec = family_preset("record_11l")
+    spec = family_preset(CONFIGS[args.config][0])
     spec.mode = "record_shaped_proxy"
     spec.train.rank, spec.train.world_size = rank, world
     spec.train.backend = "cuda_distributed" if world > 1 else "cuda_single"
@@ -181,10 +194,12 @@ def run_native(args):
             "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": value / PUBLISHED_TOKENS_PER_S,
             "dtype": "bf16", "data": "synthetic seeded Zipf(1.1) order-1 Markov uint16 shards; random-init weights",
             "impl": "native",
-            "config": {"model": "record_11l (11L d512 8H/4KV MLP3x LeakyReLU^2 XSA4 RoPE16 BigramHash3072x128 SmearGate tied-1024)",
-                       "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "parallelism": f"dp{world}" + (" sharded Parallel Muon" if world > 1 else ""),
-                       "grad_accum": accum, "micro_batch_tokens": T, "optimizer": "Muon quintic NS5 + AdamW + EMA 0.997",
-                       "l2": "inputs_larger_than_L2 (18 GB of saved activations per micro-batch; no flush needed)"},
+            "config": {"model": CONFIGS[args.config][4],
+                       "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN,
+                       "parallelism": f"dp{world}" + ((" sharded Parallel Muon" if backend.dist is not None and backend.dist.sharded else " peer-memory gradient all-reduce") if world > 1 else ""),
+                       "grad_accum": accum, "micro_batch_tokens": T,
+                       "optimizer": f"Muon {spec.train.muon_ns_profile} NS{spec.train.muon_ns_steps} + AdamW" + (f" + EMA {spec.train.ema_decay}" if spec.train.ema_decay > 0 else ""),
+                       "l2": "inputs_larger_than_L2 (gigabytes of saved activations per micro-batch; no flush needed)"},
             "clocks": clocks,
             "e2e": {"value": GLOBAL_BATCH / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": accum * (T + 1) * 2 + 32, "d2h_bytes_per_step": 4, "last_loss": last_loss},
@@ -201,7 +216,8 @@ class _BenchDone(Exception):
 def run_reference(args):
     """The unmodified record script, driven through its own environment-variable interface and main()."""
     ref_root = os.path.join(ROOT, "baseline", "_ref")
-    script = os.path.join(ref_root, "parameter_golf_reference", "train_gpt_record_2026_03_23.py")
+    record = args.config == "record_11l"
+    script = os.path.join(ref_root, "parameter_golf_reference", "train_gpt_record_2026_03_23.py" if record else "train_gpt_root.py")
     rank = int(os.environ.get("RANK", "0"))
 
     def unavailable(why):
@@ -240,8 +256,8 @@ def run_reference(args):
         t0 = time.time()
         while not os.path.exists(done_flag) and time.time() - t0 < 600:
             time.sleep(0.5)
-    run_id = f"bench_ref_n{world}"
-    workdir = os.path.join(tempfile.gettempdir(), f"pgb200_ref_run_{world}")
+    run_id = f"bench_ref_{args.config}_n{world}"
+    workdir = os.path.join(tempfile.gettempdir(), f"pgb200_ref_run_{args.config}_{world}")
     os.makedirs(workdir, exist_ok=True)
     os.chdir(workdir)
     env = {"DATA_PATH": data_root, "TOKENIZER_PATH": tok, "RUN_ID": run_id, "ITERATIONS": str(args.steps), "WARMUP_STEPS": str(args.warmup),
@@ -250,6 +266,11 @@ def run_reference(args):
            "NUM_LAYERS": "11", "MODEL_DIM": "512", "NUM_HEADS": "8", "NUM_KV_HEADS": "4", "MLP_MULT": "3.0", "BIGRAM_VOCAB_SIZE": "3072",
            "BIGRAM_DIM": "128", "XSA_LAST_N": "4", "ROPE_DIMS": "16", "LN_SCALE": "1", "VE_ENABLED": "0", "MATRIX_LR": "0.025", "MUON_WD": "0.04",
            "ADAM_WD": "0.04", "SWA_ENABLED": "0", "QAT_ENABLED": "0", "LATE_QAT_THRESHOLD": "0", "TTT_ENABLED": "0", "SEED": "1337"}
+    if not record:       # the root trainer: 9 layers, MLP 2x relu^2, its own defaults for everything it does not know
+        env = {k: v for k, v in env.items() if k in ("DATA_PATH", "TOKENIZER_PATH", "RUN_ID", "ITERATIONS", "WARMUP_STEPS", "WARMDOWN_ITERS",
+                                                     "MAX_WALLCLOCK_SECONDS", "VAL_LOSS_EVERY", "TRAIN_LOG_EVERY", "TRAIN_BATCH_TOKENS", "TRAIN_SEQ_LEN",
+                                                     "VOCAB_SIZE", "MODEL_DIM", "NUM_HEADS", "NUM_KV_HEADS", "SEED")}
+        env.update({"NUM_LAYERS": "9", "MLP_MULT": "2", "VAL_BATCH_SIZE": str(GLOBAL_BATCH)})
     os.environ.update(env)
     sys.path.insert(0, os.path.join(ROOT, "baseline", "fa3_shim"))      # flash_attn_interface -> torch SDPA (FA3 is Hopper-only)
     sys.path.insert(0, ref_root)
@@ -295,9 +316,12 @@ def run_reference(args):
                 "metric": "train_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": value / PUBLISHED_TOKENS_PER_S, "dtype": "bf16",
                 "data": "synthetic seeded Zipf(1.1) order-1 Markov uint16 shards; random-init weights", "impl": "reference",
-                "config": {"model": "records/track_10min_16mb/2026-03-23_LeakyReLU_LegalTTT_ParallelMuon/train_gpt.py (unmodified), VE off, BigramHash 3072",
-                           "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN, "parallelism": f"dp{world} Parallel Muon (NCCL)", "grad_accum": accum,
-                           "attention": "flash_attn_interface shim -> torch SDPA flash backend", "timing": "the script's own synchronized train_time"},
+                "config": {"model": ("records/track_10min_16mb/2026-03-23_LeakyReLU_LegalTTT_ParallelMuon/train_gpt.py (unmodified), VE off, BigramHash 3072"
+                                     if record else "train_gpt.py (unmodified root trainer, 9L baseline)"),
+                           "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN,
+                           "parallelism": f"dp{world} Parallel Muon (NCCL)" if record else f"dp{world} DDP + Muon (NCCL)", "grad_accum": accum,
+                           "attention": "flash_attn_interface shim -> torch SDPA flash backend" if record else "torch SDPA",
+                           "timing": "the script's own synchronized train_time"},
                 "clocks": clocks,
                 "e2e": {"value": value, "unit": "tokens/s", "note": "the script's loop already copies each batch host->device and logs from the host",
                         "h2d_bytes_per_step": 2 * 8 * (GLOBAL_BATCH // world), "d2h_bytes_per_step": 4},
@@ -314,7 +338,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--config", default="record_11l", choices=sorted(CONFIGS), help="record_11l is the headline; baseline_9l is the 9-layer DDP baseline")
     args = ap.parse_args()
+    select_config(args.config)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

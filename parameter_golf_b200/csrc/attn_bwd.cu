@@ -1,14 +1,16 @@
 // Causal GQA flash-attention backward for sm_100a (head_dim 64), two kernels, no atomics:
 //
-//   attn_bwd_dq_kernel    query-stationary: for a 128-row query tile of two heads sharing a KV head, streams
-//                         the K/V tiles, recomputes P from the saved log-sum-exp, forms dS and accumulates
-//                         dQ += dS K in tensor memory. Also produces D = rowsum(dO * O).
-//   attn_bwd_dkdv_kernel  key-stationary: for a 128-key tile of one KV head, streams 64-row Q/dO sub-tiles of
+//   attn_bwd_dq_kernel    query-stationary: for a 128-row query tile of one head, streams the K/V tiles,
+//                         recomputes P from the saved log-sum-exp, forms dS and accumulates dQ += dS K in tensor
+//                         memory. Also produces D = rowsum(dO * O).
+//   attn_bwd_dkdv_kernel  key-stationary: for a 128-key tile of one KV head, streams the 128-row Q/dO tiles of
 //                         every query head of the group, computes the TRANSPOSED scores S^T = K Q^T and
-//                         dP^T = V dO^T (one thread per key row), and accumulates dV += P^T dO, dK += dS^T Q.
+//                         dP^T = V dO^T (one thread per key row and half of the query columns), and accumulates
+//                         dV += P^T dO, dK += dS^T Q.
 //
-// In both kernels the bf16 P / dS operands are written over their own fp32 scores in TMEM and consumed by
-// tcgen05.mma straight from there, so probabilities never touch shared or global memory. Accumulating dQ in
+// In both kernels the bf16 P / dS operands are written to TMEM columns of their own and consumed by tcgen05.mma
+// straight from there, so probabilities never touch shared or global memory, and the fp32 score buffers are handed
+// back to the MMA-issuing thread as soon as they have been read. Accumulating dQ in
 // a second pass costs two extra small GEMMs per tile but removes the fp32 atomics a single-pass design
 // needs (tens of GB of L2 atomic traffic per layer at this problem size).
 // Same role as the cuDNN SDPA backward graph of the reference
@@ -19,10 +21,8 @@
 
 namespace pgb {
 
-constexpr int AB_THREADS = 320;
 constexpr int AB_HD = 64;
 constexpr int AB_TILE = 128 * AB_HD * 2;     // 16 KB
-constexpr int AB_SUB = 64 * AB_HD * 2;       // 8 KB
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void tma2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
@@ -43,7 +43,7 @@ __device__ __forceinline__ float ex2f(float x) {
 }
 
 struct AttnBwdParams {
-  int B, S, H, Hkv, n_qt, pairs, group;
+  int B, S, H, Hkv, n_qt, group;
   int n_items_q, n_items_kv;
   float scale, scale_log2;
   const __nv_bfloat16* O;      // [T, H*hd]
@@ -60,61 +60,65 @@ struct AttnBwdParams {
 };
 
 // ------------------------------------------------------------------------------------------------------------------
+// Query-stationary kernel.  One item = a 128-row query tile of one head; it streams the key tiles 0..qt.  Per key tile:
+// S = Q K^T and dP = dO V^T (128 x 128, N = 128 MMAs) land in TMEM; the two softmax groups each take 64 key columns,
+// pull them into registers and release the score buffers at once (`s_free`), so the next tile's scores are computed
+// while this tile's dS is; dS goes to its own TMEM columns as bf16 and feeds dQ += dS K.  Two issuing threads (scores /
+// dQ) keep the tensor pipe fed; Q/dO are double-buffered across items.
+// TMEM: S [0,128) dP [128,256) dS [256,320) dQ [320,384).
 constexpr int DQ_STAGES = 3;
+constexpr int DQ_THREADS = 352;              // warp 0 TMA, warp 1 score MMAs, warps 2..9 softmax, warp 10 dQ MMAs
 constexpr int DQ_SMEM = (4 + 2 * DQ_STAGES) * AB_TILE + 1024 + 256;
 
-__global__ void __launch_bounds__(AB_THREADS, 1)
+__global__ void __launch_bounds__(DQ_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __grid_constant__ CUtensorMap map_do, const AttnBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;                       // 2 tiles
-  uint8_t* sdO = smem + 2 * AB_TILE;        // 2 tiles
+  uint8_t* sQD = smem;                      // 2 buffers of {Q, dO}
   uint8_t* sKV = smem + 4 * AB_TILE;        // stages {K, V}
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (4 + 2 * DQ_STAGES) * AB_TILE);
-  uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
+  uint64_t* q_full = bars;                   // 2
+  uint64_t* q_empty = q_full + 2;            // 2
+  uint64_t* kv_full = q_empty + 2;
   uint64_t* kv_empty = kv_full + DQ_STAGES;
-  uint64_t* s_full = kv_empty + DQ_STAGES;   // 2
-  uint64_t* p_full = s_full + 2;             // 2
-  uint64_t* dq_full = p_full + 2;            // 2
-  uint64_t* dq_empty = dq_full + 2;          // 2
-  uint64_t* q_empty = dq_empty + 2;          // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + 1);
+  uint64_t* s_full = kv_empty + DQ_STAGES;   // 1
+  uint64_t* s_free = s_full + 1;             // 1
+  uint64_t* p_full = s_free + 1;             // 1
+  uint64_t* dq_full = p_full + 1;            // 1
+  uint64_t* dq_empty = dq_full + 1;          // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int per_qt = p.B * p.Hkv * p.pairs;
-  struct Item { int qt, b, kvh, head0, n_active, n_kv, nsteps, row0; };
+  const int per_qt = p.B * p.H;
+  struct Item { int qt, b, head, kvh, n_kv, row0; };
   auto decode = [&](int item) {
     Item it;
-    it.qt = p.n_qt - 1 - item / per_qt;
-    int rem = item % per_qt;
-    it.b = rem / (p.Hkv * p.pairs);
-    rem -= it.b * p.Hkv * p.pairs;
-    it.kvh = rem / p.pairs;
-    const int pair = rem % p.pairs;
-    it.head0 = it.kvh * p.group + pair * 2;
-    it.n_active = min(2, p.group - pair * 2);
+    it.qt = p.n_qt - 1 - item / per_qt;     // long key ranges first
+    const int rem = item % per_qt;
+    it.b = rem / p.H;
+    it.head = rem % p.H;
+    it.kvh = it.head / p.group;
     it.n_kv = it.qt + 1;
-    it.nsteps = 2 * it.n_kv;
     it.row0 = it.b * p.S + it.qt * 128;
     return it;
   };
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+    }
     for (int s = 0; s < DQ_STAGES; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    for (int w = 0; w < 2; ++w) {
-      mbar_init(&s_full[w], 1);
-      mbar_init(&p_full[w], 128);
-      mbar_init(&dq_full[w], 1);
-      mbar_init(&dq_empty[w], 128);
-    }
-    mbar_init(q_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 256);
+    mbar_init(p_full, 256);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -126,105 +130,100 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // per head w: S at w*192, dP at w*192+64, dQ at w*192+128 (64 columns each); bf16 dS overwrites S[0,32)
 
   if (warp == 0) {
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0, item_par = 0;
+      long long tg = 0;                     // key tiles loaded by this CTA so far
+      int il = 0;                           // items handled by this CTA so far
       bool ok = true;
-      for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x, item_par ^= 1) {
+      for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x, ++il) {
         const Item it = decode(item);
-        if (!mbar_wait(q_empty, item_par ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, -1)) { ok = false; break; }
-        mbar_expect_tx(q_full, it.n_active * 2 * AB_TILE);
-        for (int w = 0; w < it.n_active; ++w) {
-          tma2d(sQ + w * AB_TILE, &map_q, q_full, (it.head0 + w) * AB_HD, it.row0);
-          tma2d(sdO + w * AB_TILE, &map_do, q_full, (it.head0 + w) * AB_HD, it.row0);
-        }
-        for (int j = 0; j < it.n_kv; ++j) {
-          if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
+        const int qb = il & 1;
+        if (!mbar_wait(&q_empty[qb], (uint32_t)(((il >> 1) & 1) ^ 1), abort_flag, p.status, ST_WAIT_EMPTY, -1)) { ok = false; break; }
+        mbar_expect_tx(&q_full[qb], 2 * AB_TILE);
+        tma2d(sQD + qb * 2 * AB_TILE, &map_q, &q_full[qb], it.head * AB_HD, it.row0);
+        tma2d(sQD + qb * 2 * AB_TILE + AB_TILE, &map_do, &q_full[qb], it.head * AB_HD, it.row0);
+        for (int j = 0; j < it.n_kv; ++j, ++tg) {
+          const int stage = (int)(tg % DQ_STAGES);
+          if (!mbar_wait(&kv_empty[stage], (uint32_t)(((tg / DQ_STAGES) & 1) ^ 1), abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
           uint8_t* sk = sKV + stage * 2 * AB_TILE;
           mbar_expect_tx(&kv_full[stage], 2 * AB_TILE);
           tma2d(sk, &map_k, &kv_full[stage], it.kvh * AB_HD, it.b * p.S + j * 128);
           tma2d(sk + AB_TILE, &map_v, &kv_full[stage], it.kvh * AB_HD, it.b * p.S + j * 128);
-          if (++stage == DQ_STAGES) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok) {
-        mbar_drain(q_full, 0);
-        mbar_drain(q_full, 1);
-        for (int s = 0; s < DQ_STAGES; ++s) mbar_drain(&kv_full[s], (s < stage) ? phase : (phase ^ 1));
+        for (int i = 0; i < 2; ++i) mbar_drain(&q_full[i], 0), mbar_drain(&q_full[i], 1);
+        for (int s = 0; s < DQ_STAGES; ++s) mbar_drain(&kv_full[s], 0), mbar_drain(&kv_full[s], 1);
       }
     }
   } else if (warp == 1) {
+    // scores: S(j) and dP(j) as soon as the previous tile's scores have been pulled into registers
     if (lane == 0) {
-      constexpr uint32_t IDESC_S = make_idesc_bf16(128, 64, 0, 0);     // Q K^T, dO V^T (64-key sub-tiles)
-      constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, 64, 0, 1);    // dS (TMEM) x K, K read N(=hd)-contiguous
-      uint32_t item_par = 0;
-      uint32_t spar[2] = {0, 0};       // parity of the running per-head step counter (s_full / p_full)
-      uint32_t dqpar[2] = {0, 0};      // parity of the per-head count of finished items (dq_empty)
-      long long kv_base = 0;           // K/V tiles consumed by earlier items of this CTA
+      constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);    // Q K^T, dO V^T
+      long long tg = 0;
+      int il = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x, item_par ^= 1) {
+      for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x, ++il) {
         const Item it = decode(item);
-        auto kv_stage = [&](int tile) { return (int)((kv_base + tile) % DQ_STAGES); };
-        auto kv_phase = [&](int tile) { return (uint32_t)(((kv_base + tile) / DQ_STAGES) & 1); };
-        auto issue_sdp = [&](int w, int t) {
-          const int stage = kv_stage(t >> 1), hh = t & 1;
-          const uint32_t sq = smem_u32(sQ + w * AB_TILE), sdo = smem_u32(sdO + w * AB_TILE);
-          const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE) + hh * AB_SUB, sv = sk + AB_TILE;
-          const uint32_t tS = tmem_base + w * 192, tP = tS + 64;
+        const int qb = il & 1;
+        if (!mbar_wait(&q_full[qb], (uint32_t)((il >> 1) & 1), abort_flag, p.status, ST_WAIT_FULL, -1)) { ok = false; break; }
+        const uint32_t sq = smem_u32(sQD + qb * 2 * AB_TILE), sdo = sq + AB_TILE;
+        for (int j = 0; j < it.n_kv && ok; ++j, ++tg) {
+          const int stage = (int)(tg % DQ_STAGES);
+          if (tg > 0 && !mbar_wait(s_free, (uint32_t)((tg - 1) & 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, j)) { ok = false; break; }
+          if (!mbar_wait(&kv_full[stage], (uint32_t)((tg / DQ_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, j)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE), sv = sk + AB_TILE;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_ss(tS, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0);
+          for (int k = 0; k < 4; ++k) umma_ss(tmem_base, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_ss(tP, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), IDESC_S, k > 0);
-          umma_commit(&s_full[w]);
-        };
-        if (!mbar_wait(q_full, item_par, abort_flag, p.status, ST_WAIT_FULL, -1)) { ok = false; break; }
-        if (!mbar_wait(&kv_full[kv_stage(0)], kv_phase(0), abort_flag, p.status, ST_WAIT_FULL, 0)) { ok = false; break; }
-        tc_fence_after();
-        for (int w = 0; w < it.n_active; ++w) issue_sdp(w, 0);
-        for (int t = 0; t < it.nsteps && ok; ++t) {
-          const int tile = t >> 1, hh = t & 1, stage = kv_stage(tile);
-          if (t + 1 < it.nsteps && ((t + 1) >> 1) != tile) {
-            const int nt = (t + 1) >> 1;
-            if (!mbar_wait(&kv_full[kv_stage(nt)], kv_phase(nt), abort_flag, p.status, ST_WAIT_FULL, nt)) { ok = false; break; }
-          }
-          const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE) + hh * AB_SUB;
-          for (int w = 0; w < it.n_active && ok; ++w) {
-            if (!mbar_wait(&p_full[w], spar[w], abort_flag, p.status, ST_WAIT_MISC, t)) { ok = false; break; }
-            spar[w] ^= 1;
-            if (t == 0) {        // the previous item's dQ must have been read out before it is overwritten
-              if (!mbar_wait(&dq_empty[w], dqpar[w] ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
-              dqpar[w] ^= 1;
-            }
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_ts(tmem_base + w * 192 + 128, tmem_base + w * 192 + k * 8, make_smem_desc(sk + k * 2048, 8192, 1024), IDESC_DQ,
-                      (t > 0 || k > 0) ? 1u : 0u);
-            if (t + 1 < it.nsteps) issue_sdp(w, t + 1);
-            else umma_commit(&dq_full[w]);
-          }
-          if (!ok) break;
-          if (hh == 1) umma_commit(&kv_empty[stage]);
+          for (int k = 0; k < 4; ++k)
+            umma_ss(tmem_base + 128, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), IDESC_S, k > 0);
+          umma_commit(s_full);
         }
-        if (ok) umma_commit(q_empty);
-        kv_base += it.n_kv;
+        if (ok) umma_commit(&q_empty[qb]);    // Q / dO of this item are read by the score MMAs only
+      }
+    }
+  } else if (warp == 10) {
+    // dQ += dS K once both softmax groups have stored their halves of dS
+    if (lane == 0) {
+      constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, 64, 0, 1);    // dS (TMEM) x K, K read N(=hd)-contiguous
+      long long tg = 0;
+      int il = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x, ++il) {
+        const Item it = decode(item);
+        for (int j = 0; j < it.n_kv && ok; ++j, ++tg) {
+          const int stage = (int)(tg % DQ_STAGES);
+          if (!mbar_wait(&kv_full[stage], (uint32_t)((tg / DQ_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, j)) { ok = false; break; }
+          if (!mbar_wait(p_full, (uint32_t)(tg & 1), abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
+          if (j == 0) {        // the previous item's dQ must have been read out before it is overwritten
+            if (!mbar_wait(dq_empty, (uint32_t)((il & 1) ^ 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
+          }
+          tc_fence_after();
+          const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_ts(tmem_base + 320, tmem_base + 256 + k * 8, make_smem_desc(sk + k * 2048, 8192, 1024), IDESC_DQ, (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&kv_empty[stage]);      // frees the K/V stage and tells the softmax groups that dS may be overwritten
+        }
+        if (ok) umma_commit(dq_full);
       }
     }
   } else {
-    const int w = (warp - 2) >> 2;
+    const int w = (warp - 2) >> 2;                 // this group owns key columns [64 w, 64 w + 64) of every tile
     const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;
+    const int r = quarter * 32 + lane;             // query row within the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tS = tmem_base + w * 192 + lane_off, tP = tS + 64, tDQ = tS + 128;
-    uint32_t spar = 0, ipar = 0;
+    const uint32_t tS = tmem_base + w * 64 + lane_off, tdP = tmem_base + 128 + w * 64 + lane_off;
+    const uint32_t tdS = tmem_base + 256 + w * 32 + lane_off, tDQ = tmem_base + 320 + w * 32 + lane_off;
+    long long tg = 0;
+    int il = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x) {
+    for (int item = blockIdx.x; item < p.n_items_q && ok; item += gridDim.x, ++il) {
       const Item it = decode(item);
-      if (w >= it.n_active) continue;
-      const int head = it.head0 + w, qt = it.qt, nsteps = it.nsteps, row0 = it.row0, b = it.b;
+      const int head = it.head, qt = it.qt, row0 = it.row0, b = it.b;
       // D = rowsum(dO * O) for this query row; also published for the dK/dV kernel
       float Dr = 0.f;
       {
@@ -239,22 +238,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
       const size_t sidx = ((size_t)b * p.H + head) * p.S + qt * 128 + r;
-      p.Dsum[sidx] = -Dr;                      // negated: the dK/dV kernel adds it
+      if (w == 0) p.Dsum[sidx] = -Dr;          // negated: the dK/dV kernel adds it
       const float nlse2 = p.lse[sidx];         // -(log2-domain log-sum-exp), as written by the forward
-      for (int t = 0; t < nsteps; ++t) {
-        if (!mbar_wait(&s_full[w], spar, abort_flag, p.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
-        spar ^= 1;
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(nlse2, nlse2), nd2 = make_float2(-Dr, -Dr);
+      for (int j = 0; j < it.n_kv; ++j, ++tg) {
+        if (!mbar_wait(s_full, (uint32_t)(tg & 1), abort_flag, p.status, ST_WAIT_TMEM_FULL, j)) { ok = false; break; }
         tc_fence_after();
         uint32_t s[64], dp[64];
         PGB_TMEM_LD32(tS, (s));
         PGB_TMEM_LD32(tS + 32, (s + 32));
-        PGB_TMEM_LD32(tP, (dp));
-        PGB_TMEM_LD32(tP + 32, (dp + 32));
+        PGB_TMEM_LD32(tdP, (dp));
+        PGB_TMEM_LD32(tdP + 32, (dp + 32));
         tmem_wait_ld();
-        const bool diag = (t >> 1) == qt;
-        const int kbase = (t & 1) * 64;                     // key offset of this sub-tile inside the 128-key tile
+        tc_fence_before();
+        mbar_arrive(s_free);                       // the score buffers may take the next tile
+        const bool diag = j == qt;
+        const int kbase = w * 64;                           // key offset of this group's columns inside the tile
         uint32_t pk[32];
-        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(nlse2, nlse2), nd2 = make_float2(-Dr, -Dr);
         if (!diag) {
 #pragma unroll
           for (int c = 0; c < 64; c += 2) {
@@ -274,31 +274,33 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             pk[c >> 1] = pack_bf16x2(dd.x, dd.y);
           }
         }
-        PGB_TMEM_ST16(tS, (pk));
-        PGB_TMEM_ST16(tS + 16, (pk + 16));
+        if (tg > 0) {            // the dQ MMAs of the previous tile still read dS until their commit arrives
+          const long long pg = tg - 1;
+          if (!mbar_wait(&kv_empty[(int)(pg % DQ_STAGES)], (uint32_t)((pg / DQ_STAGES) & 1), abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
+          tc_fence_after();
+        }
+        PGB_TMEM_ST16(tdS, (pk));
+        PGB_TMEM_ST16(tdS + 16, (pk + 16));
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&p_full[w]);
+        mbar_arrive(p_full);
       }
-      if (ok && mbar_wait(&dq_full[w], ipar, abort_flag, p.status, ST_WAIT_MISC, nsteps)) {
-        ipar ^= 1;
+      if (ok && mbar_wait(dq_full, (uint32_t)(il & 1), abort_flag, p.status, ST_WAIT_MISC, it.n_kv)) {
         tc_fence_after();
-        __nv_bfloat16* out = p.dq + (size_t)(row0 + r) * p.lddq + head * AB_HD;
+        // each group writes 32 of the 64 columns of its row
+        __nv_bfloat16* out = p.dq + (size_t)(row0 + r) * p.lddq + head * AB_HD + w * 32;
+        uint32_t o[32];
+        PGB_TMEM_LD32(tDQ, o);
+        tmem_wait_ld();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t o[32];
-          PGB_TMEM_LD32(tDQ + h * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; c += 8)
-            *reinterpret_cast<uint4*>(out + h * 32 + c) =
-                make_uint4(pack_bf16x2(__uint_as_float(o[c]) * p.scale, __uint_as_float(o[c + 1]) * p.scale),
-                           pack_bf16x2(__uint_as_float(o[c + 2]) * p.scale, __uint_as_float(o[c + 3]) * p.scale),
-                           pack_bf16x2(__uint_as_float(o[c + 4]) * p.scale, __uint_as_float(o[c + 5]) * p.scale),
-                           pack_bf16x2(__uint_as_float(o[c + 6]) * p.scale, __uint_as_float(o[c + 7]) * p.scale));
-        }
+        for (int c = 0; c < 32; c += 8)
+          *reinterpret_cast<uint4*>(out + c) =
+              make_uint4(pack_bf16x2(__uint_as_float(o[c]) * p.scale, __uint_as_float(o[c + 1]) * p.scale),
+                         pack_bf16x2(__uint_as_float(o[c + 2]) * p.scale, __uint_as_float(o[c + 3]) * p.scale),
+                         pack_bf16x2(__uint_as_float(o[c + 4]) * p.scale, __uint_as_float(o[c + 5]) * p.scale),
+                         pack_bf16x2(__uint_as_float(o[c + 6]) * p.scale, __uint_as_float(o[c + 7]) * p.scale));
         tc_fence_before();
-        mbar_arrive(&dq_empty[w]);
+        mbar_arrive(dq_empty);
       } else {
         ok = false;
       }
@@ -313,26 +315,34 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int KV_STAGES = 6;
-// one stage holds a Q sub-tile, a dO sub-tile, lse[64] and D[64]
-constexpr int KV_SMEM = 2 * AB_TILE + KV_STAGES * (2 * AB_SUB) + KV_STAGES * 512 + 1024 + 256;
+// Key-stationary kernel.  One item = a 128-key tile of one KV head; its units are the (128-row query tile, query head)
+// pairs that attend to it.  Per unit: S^T = K Q^T and dP^T = V dO^T (128 x 128 each, N = 128 MMAs) land in TMEM; the two
+// softmax groups each take 64 query columns, pull them into registers and release the score buffers at once
+// (`s_free`), so the next unit's scores are computed while this unit's probabilities are; P^T and dS^T go back to
+// their own TMEM columns as bf16 and feed dV += P^T dO and dK += dS^T Q.  Two issuing threads (scores / gradients) keep
+// the tensor pipe fed.  TMEM: S^T [0,128) dP^T [128,256) P^T [256,320) dS^T [320,384) dK [384,448) dV [448,512).
+constexpr int KV_STAGES = 4;
+constexpr int KV_THREADS = 352;              // warp 0 TMA, warp 1 score MMAs, warps 2..9 softmax, warp 10 gradient MMAs
+// one stage holds a 128-row Q tile, a 128-row dO tile, lse[128] and D[128]
+constexpr int KV_SMEM = 2 * AB_TILE + KV_STAGES * (2 * AB_TILE) + KV_STAGES * 1024 + 1024 + 256;
 
-__global__ void __launch_bounds__(AB_THREADS, 1)
-attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                     const __grid_constant__ CUtensorMap map_do64, const AttnBwdParams p) {
+__global__ void __launch_bounds__(KV_THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                     const __grid_constant__ CUtensorMap map_do, const AttnBwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = smem + AB_TILE;
-  uint8_t* sQD = smem + 2 * AB_TILE;                                   // stages of {Q64, dO64}
-  float* sVec = reinterpret_cast<float*>(smem + 2 * AB_TILE + KV_STAGES * 2 * AB_SUB);   // stages of {lse[64], D[64]}
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sVec) + KV_STAGES * 512);
+  uint8_t* sQD = smem + 2 * AB_TILE;                                   // stages of {Q, dO}
+  float* sVec = reinterpret_cast<float*>(smem + 2 * AB_TILE + KV_STAGES * 2 * AB_TILE);   // stages of {lse[128], D[128]}
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sVec) + KV_STAGES * 1024);
   uint64_t* kv_full = bars;
   uint64_t* st_full = bars + 1;
   uint64_t* st_empty = st_full + KV_STAGES;
-  uint64_t* s_full = st_empty + KV_STAGES;    // 2
-  uint64_t* p_full = s_full + 2;              // 2
-  uint64_t* acc_full = p_full + 2;            // 1
+  uint64_t* s_full = st_empty + KV_STAGES;    // 1
+  uint64_t* s_free = s_full + 1;              // 1
+  uint64_t* p_full = s_free + 1;              // 1
+  uint64_t* acc_full = p_full + 1;            // 1
   uint64_t* acc_empty = acc_full + 1;         // 1
   uint64_t* kv_empty = acc_empty + 1;         // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_empty + 1);
@@ -347,7 +357,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
     const int rem = item % per_kt;
     it.b = rem / p.Hkv;
     it.kvh = rem % p.Hkv;
-    it.nu = (p.n_qt - it.j) * p.group * 2;                  // units: (query tile, head, 64-row half); always even
+    it.nu = (p.n_qt - it.j) * p.group;                      // units: (query tile, head)
     it.key0 = it.b * p.S + it.j * 128;
     return it;
   };
@@ -358,10 +368,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
       mbar_init(&st_full[s], 1);
       mbar_init(&st_empty[s], 1);
     }
-    for (int w = 0; w < 2; ++w) {
-      mbar_init(&s_full[w], 1);
-      mbar_init(&p_full[w], 128);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 256);
+    mbar_init(p_full, 256);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 256);
     mbar_init(kv_empty, 1);
@@ -376,13 +385,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // buffer u&1: S^T at buf*128, dP^T at buf*128+64; dK at 256, dV at 320
 
-  auto unit_coords = [&](const Item& it, int u, int& qi, int& head, int& hh) {
-    hh = u & 1;
-    const int v = u >> 1;
-    head = it.kvh * p.group + (v % p.group);
-    qi = it.j + v / p.group;
+  auto unit_coords = [&](const Item& it, int u, int& qi, int& head) {
+    head = it.kvh * p.group + (u % p.group);
+    qi = it.j + u / p.group;
   };
 
   if (warp == 0) {
@@ -401,15 +407,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
           const int stage = (int)(ug % KV_STAGES);
           const uint32_t phase = (uint32_t)((ug / KV_STAGES) & 1);
           if (!mbar_wait(&st_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, u)) { ok = false; break; }
-          int qi, head, hh;
-          unit_coords(it, u, qi, head, hh);
-          const int qrow = it.b * p.S + qi * 128 + hh * 64;
-          const size_t vidx = ((size_t)it.b * p.H + head) * p.S + qi * 128 + hh * 64;
-          mbar_expect_tx(&st_full[stage], 2 * AB_SUB + 512);
-          tma2d(sQD + stage * 2 * AB_SUB, &map_q64, &st_full[stage], head * AB_HD, qrow);
-          tma2d(sQD + stage * 2 * AB_SUB + AB_SUB, &map_do64, &st_full[stage], head * AB_HD, qrow);
-          bulk_g2s(sVec + stage * 128, p.lse + vidx, 256, &st_full[stage]);
-          bulk_g2s(sVec + stage * 128 + 64, p.Dsum + vidx, 256, &st_full[stage]);
+          int qi, head;
+          unit_coords(it, u, qi, head);
+          const int qrow = it.b * p.S + qi * 128;
+          const size_t vidx = ((size_t)it.b * p.H + head) * p.S + qi * 128;
+          mbar_expect_tx(&st_full[stage], 2 * AB_TILE + 1024);
+          tma2d(sQD + stage * 2 * AB_TILE, &map_q, &st_full[stage], head * AB_HD, qrow);
+          tma2d(sQD + stage * 2 * AB_TILE + AB_TILE, &map_do, &st_full[stage], head * AB_HD, qrow);
+          bulk_g2s(sVec + stage * 256, p.lse + vidx, 512, &st_full[stage]);
+          bulk_g2s(sVec + stage * 256 + 128, p.Dsum + vidx, 512, &st_full[stage]);
         }
         ubase += it.nu;
       }
@@ -420,151 +426,169 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q64, const __grid_c
       }
     }
   } else if (warp == 1) {
+    // scores: S^T(u) and dP^T(u) as soon as the previous unit's scores have been pulled into registers
     if (lane == 0) {
-      constexpr uint32_t IDESC_T = make_idesc_bf16(128, 64, 0, 0);     // K Q^T and V dO^T
-      constexpr uint32_t IDESC_A = make_idesc_bf16(128, 64, 0, 1);     // P^T (TMEM) x dO, dS^T (TMEM) x Q; B read N(=hd)-contiguous
+      constexpr uint32_t IDESC_T = make_idesc_bf16(128, 128, 0, 0);    // K Q^T and V dO^T
       const uint32_t sk = smem_u32(sK), sv = smem_u32(sV);
       bool ok = true;
       uint32_t item_par = 0;
       long long ubase = 0;
-      auto issue_sdp = [&](long long ug) -> bool {
-        const int stage = (int)(ug % KV_STAGES), buf = (int)(ug & 1);
-        if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, (int)ug)) return false;
-        tc_fence_after();
-        const uint32_t sq = smem_u32(sQD + stage * 2 * AB_SUB), sdo = sq + AB_SUB;
-        const uint32_t tS = tmem_base + buf * 128, tP = tS + 64;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) umma_ss(tS, make_smem_desc(sk + k * 32, 16, 1024), make_smem_desc(sq + k * 32, 16, 1024), IDESC_T, k > 0);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) umma_ss(tP, make_smem_desc(sv + k * 32, 16, 1024), make_smem_desc(sdo + k * 32, 16, 1024), IDESC_T, k > 0);
-        umma_commit(&s_full[buf]);
-        return true;
-      };
       for (int item = blockIdx.x; item < p.n_items_kv && ok; item += gridDim.x, item_par ^= 1) {
         const Item it = decode(item);
         if (!mbar_wait(kv_full, item_par, abort_flag, p.status, ST_WAIT_FULL, -1)) { ok = false; break; }
-        tc_fence_after();
-        for (int u = 0; u < 2 && u < it.nu && ok; ++u) ok = issue_sdp(ubase + u);
         for (int u = 0; u < it.nu && ok; ++u) {
           const long long ug = ubase + u;
-          const int stage = (int)(ug % KV_STAGES), buf = (int)(ug & 1);
-          if (!mbar_wait(&p_full[buf], (uint32_t)((ug >> 1) & 1), abort_flag, p.status, ST_WAIT_MISC, u)) { ok = false; break; }
+          const int stage = (int)(ug % KV_STAGES);
+          if (ug > 0 && !mbar_wait(s_free, (uint32_t)((ug - 1) & 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, u)) { ok = false; break; }
+          if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sq = smem_u32(sQD + stage * 2 * AB_TILE), sdo = sq + AB_TILE;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_ss(tmem_base, make_smem_desc(sk + k * 32, 16, 1024), make_smem_desc(sq + k * 32, 16, 1024), IDESC_T, k > 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_ss(tmem_base + 128, make_smem_desc(sv + k * 32, 16, 1024), make_smem_desc(sdo + k * 32, 16, 1024), IDESC_T, k > 0);
+          umma_commit(s_full);
+        }
+        ubase += it.nu;
+      }
+    }
+  } else if (warp == 10) {
+    // gradients: dV += P^T dO and dK += dS^T Q once both softmax groups have stored their halves of P^T / dS^T
+    if (lane == 0) {
+      constexpr uint32_t IDESC_A = make_idesc_bf16(128, 64, 0, 1);     // A from TMEM; B (dO, Q) read N(=hd)-contiguous
+      bool ok = true;
+      uint32_t item_par = 0;
+      long long ubase = 0;
+      for (int item = blockIdx.x; item < p.n_items_kv && ok; item += gridDim.x, item_par ^= 1) {
+        const Item it = decode(item);
+        for (int u = 0; u < it.nu && ok; ++u) {
+          const long long ug = ubase + u;
+          const int stage = (int)(ug % KV_STAGES);
+          if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
+          if (!mbar_wait(p_full, (uint32_t)(ug & 1), abort_flag, p.status, ST_WAIT_MISC, u)) { ok = false; break; }
           if (u == 0) {          // the previous item's dK/dV must have been read out before they are overwritten
             if (!mbar_wait(acc_empty, item_par ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
           }
           tc_fence_after();
-          const uint32_t sq = smem_u32(sQD + stage * 2 * AB_SUB), sdo = sq + AB_SUB;
-          const uint32_t tPt = tmem_base + buf * 128, tdSt = tPt + 64;
+          const uint32_t sq = smem_u32(sQD + stage * 2 * AB_TILE), sdo = sq + AB_TILE;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)   // dV += P^T dO
-            umma_ts(tmem_base + 320, tPt + k * 8, make_smem_desc(sdo + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 8; ++k)   // dV += P^T dO
+            umma_ts(tmem_base + 448, tmem_base + 256 + k * 8, make_smem_desc(sdo + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)   // dK += dS^T Q
-            umma_ts(tmem_base + 256, tdSt + k * 8, make_smem_desc(sq + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&st_empty[stage]);
-          if (u + 2 < it.nu) ok = issue_sdp(ug + 2);
+          for (int k = 0; k < 8; ++k)   // dK += dS^T Q
+            umma_ts(tmem_base + 384, tmem_base + 320 + k * 8, make_smem_desc(sq + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&st_empty[stage]);      // frees the Q/dO stage and tells the softmax groups that P^T / dS^T may be overwritten
         }
         if (ok) {
           umma_commit(acc_full);
-          umma_commit(kv_empty);        // K_j / V_j are no longer read once every MMA of this item has completed
+          umma_commit(kv_empty);        // every score MMA of the item finished before its probabilities existed, so K_j / V_j are free too
         }
         ubase += it.nu;
       }
     }
   } else {
-    const int w = (warp - 2) >> 2;                 // this group handles units with (u & 1) == w
+    const int w = (warp - 2) >> 2;                 // this group owns query columns [64 w, 64 w + 64) of every unit
     const int quarter = warp & 3;
     const int kk = quarter * 32 + lane;            // key row within the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + w * 64 + lane_off, tdP = tmem_base + 128 + w * 64 + lane_off;
+    const uint32_t tPt = tmem_base + 256 + w * 32 + lane_off, tdSt = tmem_base + 320 + w * 32 + lane_off;
     bool ok = true;
     uint32_t item_par = 0;
     long long ubase = 0;
     for (int item = blockIdx.x; item < p.n_items_kv && ok; item += gridDim.x, item_par ^= 1) {
-    const Item it = decode(item);
-    const int j = it.j, kvh = it.kvh, key0 = it.key0, nu = it.nu;
-    for (int u = w; u < nu; u += 2) {
-      const long long ug = ubase + u;
-      const int stage = (int)(ug % KV_STAGES);
-      if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
-      if (!mbar_wait(&s_full[w], (uint32_t)((ug >> 1) & 1), abort_flag, p.status, ST_WAIT_TMEM_FULL, u)) { ok = false; break; }
-      tc_fence_after();
-      int qi, head, hh;
-      unit_coords(it, u, qi, head, hh);
-      const uint32_t tS = tmem_base + w * 128 + lane_off, tP = tS + 64;
-      uint32_t s[64], dp[64];
-      PGB_TMEM_LD32(tS, (s));
-      PGB_TMEM_LD32(tS + 32, (s + 32));
-      PGB_TMEM_LD32(tP, (dp));
-      PGB_TMEM_LD32(tP + 32, (dp + 32));
-      tmem_wait_ld();
-      const float* vl = sVec + stage * 128;
-      const float* vd = vl + 64;
-      const bool diag = qi == j;
-      const int qbase = hh * 64;
-      uint32_t pp[32], pd[32];
-      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
-      const float2* vl2 = reinterpret_cast<const float2*>(vl);     // -(log2 lse) of the 64 query rows of this unit
-      const float2* vd2 = reinterpret_cast<const float2*>(vd);     // -D of the same rows
-      if (!diag) {
-#pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, vl2[c >> 1]);
-          const float2 pr = make_float2(ex2f(tt.x), ex2f(tt.y));
-          const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), vd2[c >> 1]));
-          pp[c >> 1] = pack_bf16x2(pr.x, pr.y);
-          pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, vl2[c >> 1]);
-          float2 pr = make_float2(ex2f(tt.x), ex2f(tt.y));
-          if (qbase + c < kk) pr.x = 0.f;              // query position before the key: masked
-          if (qbase + c + 1 < kk) pr.y = 0.f;
-          const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), vd2[c >> 1]));
-          pp[c >> 1] = pack_bf16x2(pr.x, pr.y);
-          pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
-        }
-      }
-      PGB_TMEM_ST16(tS, (pp));
-      PGB_TMEM_ST16(tS + 16, (pp + 16));
-      PGB_TMEM_ST16(tP, (pd));
-      PGB_TMEM_ST16(tP + 16, (pd + 16));
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&p_full[w]);
-    }
-    if (ok && mbar_wait(acc_full, item_par, abort_flag, p.status, ST_WAIT_MISC, nu)) {
-      tc_fence_after();
-      // group 0 writes dK, group 1 writes dV
-      const uint32_t tA = tmem_base + (w == 0 ? 256 : 320) + lane_off;
-      __nv_bfloat16* out = (w == 0 ? p.dk + (size_t)(key0 + kk) * p.lddk : p.dv + (size_t)(key0 + kk) * p.lddv) + kvh * AB_HD;
-      const bool acc = (w == 1) && p.accumulate_dv;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t o[32];
-        PGB_TMEM_LD32(tA + h * 32, o);
+      const Item it = decode(item);
+      const int j = it.j, kvh = it.kvh, key0 = it.key0, nu = it.nu;
+      for (int u = 0; u < nu; ++u) {
+        const long long ug = ubase + u;
+        const int stage = (int)(ug % KV_STAGES);
+        if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
+        if (!mbar_wait(s_full, (uint32_t)(ug & 1), abort_flag, p.status, ST_WAIT_TMEM_FULL, u)) { ok = false; break; }
+        tc_fence_after();
+        int qi, head;
+        unit_coords(it, u, qi, head);
+        uint32_t s[64], dp[64];
+        PGB_TMEM_LD32(tS, (s));
+        PGB_TMEM_LD32(tS + 32, (s + 32));
+        PGB_TMEM_LD32(tdP, (dp));
+        PGB_TMEM_LD32(tdP + 32, (dp + 32));
         tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(s_free);                       // the score buffers may take the next unit
+        const float* vl = sVec + stage * 256 + w * 64;
+        const float* vd = sVec + stage * 256 + 128 + w * 64;
+        const bool diag = qi == j;
+        const int qbase = w * 64;
+        uint32_t pp[32], pd[32];
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2* vl2 = reinterpret_cast<const float2*>(vl);     // -(log2 lse) of this group's 64 query rows
+        const float2* vd2 = reinterpret_cast<const float2*>(vd);     // -D of the same rows
+        if (!diag) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 8) {
-          float f[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]) * (w == 0 ? p.scale : 1.f);
-          if (acc) {
-            uint4 q = *reinterpret_cast<const uint4*>(out + h * 32 + c);
-            float2 a0 = unpack_bf16x2(q.x), a1 = unpack_bf16x2(q.y), a2 = unpack_bf16x2(q.z), a3 = unpack_bf16x2(q.w);
-            f[0] += a0.x; f[1] += a0.y; f[2] += a1.x; f[3] += a1.y; f[4] += a2.x; f[5] += a2.y; f[6] += a3.x; f[7] += a3.y;
+          for (int c = 0; c < 64; c += 2) {
+            const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, vl2[c >> 1]);
+            const float2 pr = make_float2(ex2f(tt.x), ex2f(tt.y));
+            const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), vd2[c >> 1]));
+            pp[c >> 1] = pack_bf16x2(pr.x, pr.y);
+            pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
           }
-          *reinterpret_cast<uint4*>(out + h * 32 + c) =
-              make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; c += 2) {
+            const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, vl2[c >> 1]);
+            float2 pr = make_float2(ex2f(tt.x), ex2f(tt.y));
+            if (qbase + c < kk) pr.x = 0.f;              // query position before the key: masked
+            if (qbase + c + 1 < kk) pr.y = 0.f;
+            const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), vd2[c >> 1]));
+            pp[c >> 1] = pack_bf16x2(pr.x, pr.y);
+            pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
+          }
         }
+        if (ug > 0) {            // the gradient MMAs of the previous unit still read P^T / dS^T until their commit arrives
+          const long long pg = ug - 1;
+          if (!mbar_wait(&st_empty[(int)(pg % KV_STAGES)], (uint32_t)((pg / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_EMPTY, u)) { ok = false; break; }
+          tc_fence_after();
+        }
+        PGB_TMEM_ST16(tPt, (pp));
+        PGB_TMEM_ST16(tPt + 16, (pp + 16));
+        PGB_TMEM_ST16(tdSt, (pd));
+        PGB_TMEM_ST16(tdSt + 16, (pd + 16));
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(p_full);
       }
-      tc_fence_before();
-      mbar_arrive(acc_empty);
-    } else {
-      ok = false;
-    }
-    ubase += nu;
+      if (ok && mbar_wait(acc_full, item_par, abort_flag, p.status, ST_WAIT_MISC, nu)) {
+        tc_fence_after();
+        // group 0 writes dK, group 1 writes dV
+        const uint32_t tA = tmem_base + (w == 0 ? 384 : 448) + lane_off;
+        __nv_bfloat16* out = (w == 0 ? p.dk + (size_t)(key0 + kk) * p.lddk : p.dv + (size_t)(key0 + kk) * p.lddv) + kvh * AB_HD;
+        const bool acc = (w == 1) && p.accumulate_dv;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t o[32];
+          PGB_TMEM_LD32(tA + h * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[c + e]) * (w == 0 ? p.scale : 1.f);
+            if (acc) {
+              uint4 q = *reinterpret_cast<const uint4*>(out + h * 32 + c);
+              float2 a0 = unpack_bf16x2(q.x), a1 = unpack_bf16x2(q.y), a2 = unpack_bf16x2(q.z), a3 = unpack_bf16x2(q.w);
+              f[0] += a0.x; f[1] += a0.y; f[2] += a1.x; f[3] += a1.y; f[4] += a2.x; f[5] += a2.y; f[6] += a3.x; f[7] += a3.y;
+            }
+            *reinterpret_cast<uint4*>(out + h * 32 + c) =
+                make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(acc_empty);
+      } else {
+        ok = false;
+      }
+      ubase += nu;
     }
   }
   tc_fence_before();
@@ -592,7 +616,6 @@ void attn_bwd(const void* q, const void* k, const void* v, const void* o, const 
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
   p.n_qt = S / 128;
   p.group = H / Hkv;
-  p.pairs = (p.group + 1) / 2;
   p.scale = 1.f / sqrtf((float)hd);
   p.scale_log2 = p.scale * LOG2E;
   p.O = (const __nv_bfloat16*)o; p.dO = (const __nv_bfloat16*)d_o;
@@ -602,7 +625,7 @@ void attn_bwd(const void* q, const void* k, const void* v, const void* o, const 
   p.lddq = lddq; p.lddk = lddk; p.lddv = lddv;
   p.accumulate_dv = accumulate_dv;
   p.status = status;
-  p.n_items_q = p.n_qt * B * Hkv * p.pairs;
+  p.n_items_q = p.n_qt * B * H;
   p.n_items_kv = p.n_qt * B * Hkv;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -616,12 +639,12 @@ void attn_bwd(const void* q, const void* k, const void* v, const void* o, const 
   {
     const CUtensorMap mq = bwd_map(q, ldq, H * hd, T, 128), mk = bwd_map(k, ldk, Hkv * hd, T, 128), mv = bwd_map(v, ldv, Hkv * hd, T, 128),
                       mdo = bwd_map(d_o, lddo, H * hd, T, 128);
-    attn_bwd_dq_kernel<<<std::min(p.n_items_q, sms), AB_THREADS, DQ_SMEM, st>>>(mq, mk, mv, mdo, p);
+    attn_bwd_dq_kernel<<<std::min(p.n_items_q, sms), DQ_THREADS, DQ_SMEM, st>>>(mq, mk, mv, mdo, p);
   }
   {
-    const CUtensorMap mq = bwd_map(q, ldq, H * hd, T, 64), mk = bwd_map(k, ldk, Hkv * hd, T, 128), mv = bwd_map(v, ldv, Hkv * hd, T, 128),
-                      mdo = bwd_map(d_o, lddo, H * hd, T, 64);
-    attn_bwd_dkdv_kernel<<<std::min(p.n_items_kv, sms), AB_THREADS, KV_SMEM, st>>>(mq, mk, mv, mdo, p);
+    const CUtensorMap mq = bwd_map(q, ldq, H * hd, T, 128), mk = bwd_map(k, ldk, Hkv * hd, T, 128), mv = bwd_map(v, ldv, Hkv * hd, T, 128),
+                      mdo = bwd_map(d_o, lddo, H * hd, T, 128);
+    attn_bwd_dkdv_kernel<<<std::min(p.n_items_kv, sms), KV_THREADS, KV_SMEM, st>>>(mq, mk, mv, mdo, p);
   }
 }
 

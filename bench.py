@@ -123,6 +123,7 @@ def run_native(args):
     spec.mode = "record_shaped_proxy"
     spec.train.rank, spec.train.world_size = rank, world
     spec.train.backend = "cuda_distributed" if world > 1 else "cuda_single"
+    spec.train.cuda_graph = bool(args.cuda_graph)
     spec.validate()
     data_root = os.path.join(tempfile.gettempdir(), "pgb200_bench_data")
     if rank == 0:
@@ -339,6 +340,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--config", default="record_11l", choices=sorted(CONFIGS), help="record_11l is the headline; baseline_9l is the 9-layer DDP baseline")
+    ap.add_argument("--cuda-graph", action="store_true", help="replay each micro-batch forward+backward from a captured CUDA graph (native arm)")
     args = ap.parse_args()
     select_config(args.config)
     if args.warmup < 3:

@@ -59,6 +59,7 @@ struct AttnBwdParams {
   int* status;
 };
 
+
 // ------------------------------------------------------------------------------------------------------------------
 // Query-stationary kernel.  One item = a 128-row query tile of one head; it streams the key tiles 0..qt.  Per key tile:
 // S = Q K^T and dP = dO V^T (128 x 128, N = 128 MMAs) land in TMEM; the two softmax groups each take 64 key columns,
@@ -67,7 +68,7 @@ struct AttnBwdParams {
 // dQ) keep the tensor pipe fed; Q/dO are double-buffered across items.
 // TMEM: S [0,128) dP [128,256) dS [256,320) dQ [320,384).
 constexpr int DQ_STAGES = 3;
-constexpr int DQ_THREADS = 352;              // warp 0 TMA, warp 1 score MMAs, warps 2..9 softmax, warp 10 dQ MMAs
+constexpr int DQ_THREADS = 384;              // warpgroup 0: warp 0 TMA, warp 1 score MMAs, warp 2 dQ MMAs, warp 3 idle; warpgroups 1, 2: softmax
 constexpr int DQ_SMEM = (4 + 2 * DQ_STAGES) * AB_TILE + 1024 + 256;
 
 __global__ void __launch_bounds__(DQ_THREADS, 1)
@@ -131,6 +132,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp < 4) {
+  // the data-movement warpgroup hands most of its registers to the two softmax warpgroups (128 live values per thread)
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     if (lane == 0) {
       long long tg = 0;                     // key tiles loaded by this CTA so far
@@ -185,7 +189,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (ok) umma_commit(&q_empty[qb]);    // Q / dO of this item are read by the score MMAs only
       }
     }
-  } else if (warp == 10) {
+  } else if (warp == 2) {
     // dQ += dS K once both softmax groups have stored their halves of dS
     if (lane == 0) {
       constexpr uint32_t IDESC_DQ = make_idesc_bf16(128, 64, 0, 1);    // dS (TMEM) x K, K read N(=hd)-contiguous
@@ -211,8 +215,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (ok) umma_commit(dq_full);
       }
     }
+  }
   } else {
-    const int w = (warp - 2) >> 2;                 // this group owns key columns [64 w, 64 w + 64) of every tile
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int w = (warp - 4) >> 2;                 // this group owns key columns [64 w, 64 w + 64) of every tile
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;             // query row within the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
@@ -235,6 +241,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
           float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
           Dr += a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y + a2.x * g2.x + a2.y * g2.y + a3.x * g3.x + a3.y * g3.y;
+        }
+      }
+      {
+        // the next item's O / dO rows are read the same way: start them on their way into L2/L1 now
+        const int nitem = item + (int)gridDim.x;
+        if (nitem < p.n_items_q) {
+          const Item nx = decode(nitem);
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.O + (size_t)(nx.row0 + r) * p.ldo + nx.head * AB_HD));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.dO + (size_t)(nx.row0 + r) * p.lddo + nx.head * AB_HD));
         }
       }
       const size_t sidx = ((size_t)b * p.H + head) * p.S + qt * 128 + r;
@@ -322,7 +337,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // their own TMEM columns as bf16 and feed dV += P^T dO and dK += dS^T Q.  Two issuing threads (scores / gradients) keep
 // the tensor pipe fed.  TMEM: S^T [0,128) dP^T [128,256) P^T [256,320) dS^T [320,384) dK [384,448) dV [448,512).
 constexpr int KV_STAGES = 4;
-constexpr int KV_THREADS = 352;              // warp 0 TMA, warp 1 score MMAs, warps 2..9 softmax, warp 10 gradient MMAs
+constexpr int KV_THREADS = 384;              // warpgroup 0: warp 0 TMA, warp 1 score MMAs, warp 2 gradient MMAs, warp 3 idle; warpgroups 1, 2: softmax
 // one stage holds a 128-row Q tile, a 128-row dO tile, lse[128] and D[128]
 constexpr int KV_SMEM = 2 * AB_TILE + KV_STAGES * (2 * AB_TILE) + KV_STAGES * 1024 + 1024 + 256;
 
@@ -391,6 +406,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     qi = it.j + u / p.group;
   };
 
+  if (warp < 4) {
+  // the data-movement warpgroup hands most of its registers to the two softmax warpgroups (128 live values per thread)
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true;
@@ -453,7 +471,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ubase += it.nu;
       }
     }
-  } else if (warp == 10) {
+  } else if (warp == 2) {
     // gradients: dV += P^T dO and dK += dS^T Q once both softmax groups have stored their halves of P^T / dS^T
     if (lane == 0) {
       constexpr uint32_t IDESC_A = make_idesc_bf16(128, 64, 0, 1);     // A from TMEM; B (dO, Q) read N(=hd)-contiguous
@@ -487,8 +505,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ubase += it.nu;
       }
     }
+  }
   } else {
-    const int w = (warp - 2) >> 2;                 // this group owns query columns [64 w, 64 w + 64) of every unit
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int w = (warp - 4) >> 2;                 // this group owns query columns [64 w, 64 w + 64) of every unit
     const int quarter = warp & 3;
     const int kk = quarter * 32 + lane;            // key row within the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;

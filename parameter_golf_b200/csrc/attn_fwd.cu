@@ -2,9 +2,10 @@
 // S/P/O in tensor memory, online softmax by one thread per query row.
 //
 // One CTA handles one 128-row query tile of TWO query heads that share a KV head, so every K/V tile is
-// loaded once and used by both. Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer,
-// warps 2-5 softmax for head 0, warps 6-9 softmax for head 1. The two softmax groups ping-pong on the
-// tensor core: while one exponentiates its tile the other's QK^T / PV are in flight.
+// loaded once and used by both. Warp roles (384 threads = three warpgroups): warpgroup 0 holds the TMA producer
+// (warp 0) and one MMA-issuing warp per head (warps 1, 2); warpgroups 1 and 2 are the softmax groups of head 0 and
+// head 1, one thread per query row. Warpgroup 0 gives up most of its registers (`setmaxnreg`) so that a softmax
+// thread can hold its 128 scores and still leave the scheduler room to overlap MUFU, FMA and conversion latencies.
 //   TMEM: S0 [0,128) S1 [128,256) fp32 scores; P0 [256,320) P1 [320,384) bf16 probabilities (fed to the PV MMA straight
 //         from tensor memory); O0 [384,448) O1 [448,512).
 // P has its own columns so that the scores of tile j+1 can be issued as soon as the softmax group has pulled tile j
@@ -20,7 +21,7 @@
 
 namespace pgb {
 
-constexpr int AT_THREADS = 384;   // warp 0 TMA, warps 1 and 10 issue the MMAs of head 0 / head 1, warps 2..9 softmax, warp 11 idle
+constexpr int AT_THREADS = 384;   // warpgroup 0: warp 0 TMA, warps 1 and 2 issue the MMAs of head 0 / head 1, warp 3 idle; warpgroups 1, 2: softmax
 constexpr int AT_BM = 128;   // query rows per tile
 constexpr int AT_BN = 128;   // keys per tile
 constexpr int AT_HD = 64;
@@ -47,6 +48,12 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));      // one half-rate instruction instead of two
+  return r;
 }
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
@@ -111,6 +118,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(q_full, n_active * AT_TILE_BYTES);
@@ -131,8 +140,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int s = 0; s < AT_STAGES; ++s) mbar_drain(&kv_full[s], (s < stage) ? phase : (phase ^ 1));
       }
     }
-  } else if (warp == 1 || warp == 10) {
-    const int w = warp == 1 ? 0 : 1;            // each head of the pair has its own issuing thread
+  } else if (warp == 1 || warp == 2) {
+    const int w = warp - 1;                     // each head of the pair has its own issuing thread
     if (lane == 0 && w < n_active) {
       constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);    // Q K^T : both K-major
       constexpr uint32_t IDESC_O = make_idesc_bf16(128, AT_HD, 0, 1);  // P V   : A from TMEM, V is N-contiguous
@@ -176,8 +185,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         phase = nphase;
       }
     }
+  }
   } else {
-    const int w = warp < 10 ? (warp - 2) >> 2 : 2; // softmax group / head within the pair (warp 11 idles)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int w = (warp - 4) >> 2;                 // softmax group / head within the pair
     const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
     const int r = quarter * 32 + lane;             // query row within the tile
     if (w < n_active) {
@@ -205,10 +216,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         float mx8[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) mx8[c] = __uint_as_float(s[c]);
+        for (int c = 0; c < 8; ++c) mx8[c] = max3(__uint_as_float(s[c]), __uint_as_float(s[8 + c]), __uint_as_float(s[16 + c]));
 #pragma unroll
-        for (int c = 8; c < 128; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], __uint_as_float(s[c]));      // 8 independent chains
-        float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        for (int c = 24; c < 120; c += 16)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) mx8[e] = max3(mx8[e], __uint_as_float(s[c + e]), __uint_as_float(s[c + 8 + e]));      // 8 independent chains
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], __uint_as_float(s[120 + e]));
+        float mx = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
         mx *= p.scale_log2;
         const bool need = mx > m_used + 8.0f;
         const bool any_need = __any_sync(0xffffffffu, need);

@@ -24,7 +24,8 @@ int* status_ptr(const c10::optional<torch::Tensor>& status) {
 // a_kmajor: A is [.., M, K]; otherwise A is [.., K, M]. Same for B with N.
 void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor D, bool a_kmajor, bool b_kmajor, int64_t epi, double alpha, double beta,
           double slope, c10::optional<torch::Tensor> aux, c10::optional<torch::Tensor> colscale, c10::optional<torch::Tensor> D2,
-          int64_t splits, c10::optional<torch::Tensor> status, c10::optional<torch::Tensor> wait_flag, int64_t wait_value) {
+          int64_t splits, c10::optional<torch::Tensor> status, c10::optional<torch::Tensor> wait_flag, int64_t wait_value,
+          int64_t seg_row0, c10::optional<torch::Tensor> seg_D0, int64_t seg_row1, c10::optional<torch::Tensor> seg_D1) {
   check_bf16(A, "A");
   check_bf16(B, "B");
   TORCH_CHECK(A.dim() == B.dim() && A.dim() == D.dim() && (A.dim() == 2 || A.dim() == 3), "gemm: operands must all be 2-D or all 3-D");
@@ -39,7 +40,25 @@ void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor D, bool a_kmajor, bool
   g.N = (int)(b_kmajor ? B.size(-2) : B.size(-1));
   const int kb = (int)(b_kmajor ? B.size(-1) : B.size(-2));
   TORCH_CHECK(kb == g.K, "gemm: reduction dims differ: ", g.K, " vs ", kb);
-  TORCH_CHECK(D.size(-2) == g.M && D.size(-1) == g.N, "gemm: D must be [M, N]");
+  const bool segmented = seg_D0.has_value();
+  TORCH_CHECK(D.size(-1) == g.N && (segmented ? D.size(-2) == seg_row0 : D.size(-2) == g.M), "gemm: D must be [M, N]");
+  if (segmented) {
+    // rows [0, seg_row0) -> D, [seg_row0, seg_row1) -> seg_D0, [seg_row1, M) -> seg_D1 (when given)
+    const int64_t end0 = seg_D1.has_value() ? seg_row1 : g.M;
+    TORCH_CHECK(seg_row0 > 0 && seg_D0->scalar_type() == torch::kFloat32 && seg_D0->is_cuda() && seg_D0->dim() == nd && seg_D0->size(-1) == g.N &&
+                    seg_D0->size(-2) == end0 - seg_row0 && seg_D0->stride(-2) == D.stride(-2) && seg_D0->stride(-1) == 1,
+                "gemm: first row segment must be fp32 [rows, N] with D's row stride");
+    g.seg_rows[0] = (int)seg_row0;
+    g.seg_D[0] = seg_D0->data_ptr<float>();
+    if (seg_D1.has_value()) {
+      TORCH_CHECK(seg_row1 > seg_row0 && seg_D1->scalar_type() == torch::kFloat32 && seg_D1->is_cuda() && seg_D1->dim() == nd &&
+                      seg_D1->size(-1) == g.N && seg_D1->size(-2) == g.M - seg_row1 && seg_D1->stride(-2) == D.stride(-2) && seg_D1->stride(-1) == 1,
+                  "gemm: second row segment must be fp32 [rows, N] with D's row stride");
+      g.seg_rows[1] = (int)seg_row1;
+      g.seg_D[1] = seg_D1->data_ptr<float>();
+    }
+    TORCH_CHECK(nd == 2, "gemm: row segments are for un-batched products");
+  }
   if (nd == 3) TORCH_CHECK(B.size(0) == g.batch && D.size(0) == g.batch, "gemm: batch sizes differ");
   g.A = A.data_ptr();
   g.B = B.data_ptr();

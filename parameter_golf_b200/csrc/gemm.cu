@@ -40,6 +40,8 @@ struct GemmKernelParams {
   int* status;
   const int* wait_flag;   // optional: B (the weights) is valid once *wait_flag >= wait_value (peer ranks push it)
   int wait_value;
+  int seg_rows[2];        // fp32 epilogues: rows >= seg_rows[k] (> 0) are written to seg_D[k] as row m - seg_rows[k]
+  float* seg_D[2];
 };
 
 template <int BN>
@@ -65,6 +67,9 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
 
   if constexpr (EPI == EPI_F32 || EPI == EPI_F32_ATOMIC) {
     float* d = reinterpret_cast<float*>(p.D) + off;
+    // one product, several output matrices (e.g. the packed QKV weight gradient lands in three gradient banks)
+    if (p.seg_rows[1] > 0 && m >= p.seg_rows[1]) d = p.seg_D[1] + (long long)b * p.stride_d + (long long)(m - p.seg_rows[1]) * p.ldd + n0;
+    else if (p.seg_rows[0] > 0 && m >= p.seg_rows[0]) d = p.seg_D[0] + (long long)b * p.stride_d + (long long)(m - p.seg_rows[0]) * p.ldd + n0;
     if (full && ((reinterpret_cast<uintptr_t>(d) & 15) == 0)) {
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
@@ -558,6 +563,12 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.wait_flag = a.wait_flag;
   p.wait_value = a.wait_value;
+  for (int k = 0; k < 2; ++k) {
+    p.seg_rows[k] = a.seg_rows[k];
+    p.seg_D[k] = a.seg_D[k];
+  }
+  if ((a.seg_rows[0] > 0 || a.seg_rows[1] > 0) && !(a.epi == EPI_F32 || a.epi == EPI_F32_ATOMIC))
+    throw std::runtime_error("gemm: row segments need an fp32 epilogue");
   const CUtensorMap ma = operand_map(a.A, a.a_kmajor, a.M, a.K, a.lda, a.stride_a, a.batch, BM);
   const CUtensorMap mb = operand_map(a.B, a.b_kmajor, a.N, a.K, a.ldb, a.stride_b, a.batch, bn);
   const int total = p.tiles_m * p.tiles_n * p.splits * a.batch;

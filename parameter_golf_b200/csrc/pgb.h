@@ -38,6 +38,8 @@ struct GemmArgs {
   int* status = nullptr;     // device status word (4 ints) or null
   const int* wait_flag = nullptr;   // optional readiness counter for B (see comm.cu); polled with a bounded wait
   int wait_value = 0;
+  int seg_rows[2] = {0, 0};  // fp32 epilogues: output rows >= seg_rows[k] go to seg_D[k] (row index rebased), same ldd
+  float* seg_D[2] = {nullptr, nullptr};
 };
 
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
@@ -59,6 +61,12 @@ void qk_norm_rope_bwd(const void* d_post, const void* pre, void* d_pre, const fl
 void xsa_fwd(const void* y, const void* v, void* z, int rows, int Hkv, int group, int hd, int ld_y, int ld_v, float eps, cudaStream_t st);
 void xsa_bwd(const void* dz, const void* y, const void* v, void* dy, void* dv, int accumulate_dv, int rows, int Hkv, int group, int hd, int ld_y,
              int ld_v, int ld_dv, float eps, cudaStream_t st);
+// Per-head output gates (gates.cu): out_h = y_h * mult * sigmoid(scale * <W_h, x[:w]> + bias_h); `gate` [rows, H] keeps the factors
+// for the backward, which rewrites d_out in place into the gradient of y and adds the input-feature part into d_x[:, :w].
+void head_gate_fwd(const void* y, const void* x, const float* W, const float* bias, void* out, float* gate, int rows, int H, int hd, int w, int ld_x,
+                   float scale, float mult, cudaStream_t st);
+void head_gate_bwd(void* d_out, const void* y, const void* x, const float* W, const float* gate, float* dW, float* dbias, void* d_x, int accumulate_dx,
+                   int rows, int H, int hd, int w, int ld_x, int ld_dx, float scale, float mult, cudaStream_t st);
 void softcap_ce(const void* logits, const int* targets, float* nll, void* dlogits, float* loss_sum, int rows, int V, float cap, float gscale,
                 cudaStream_t st);
 void embed_gather(const int* ids, const void* table, void* out, int rows, int d, int bigram_buckets, int seq_len, cudaStream_t st);

@@ -15,6 +15,12 @@ one execution path per op and the element-wise work folded into GEMM epilogues a
 * tied-embedding logits are produced in bf16 and overwritten in place by their gradient in the
   soft-capped cross-entropy kernel.
 
+Model variants follow the same path: depth recurrence runs a layer's block twice with per-pass activation slots
+(``pg-model/src/model.rs:666-671``), the parallel residual feeds the MLP from the attention branch's normed input
+(so its gradient joins the QKV input gradient in that GEMM's epilogue), the attention-output and sparse attention
+gates are one head kernel pair (``pg-kernels/src/gpu_kernels.rs:4973-5413``), and an untied output head is a second
+bf16 weight copy with its own AdamW group.
+
 Gradients of bf16 activations are bf16; weight gradients accumulate in fp32 across micro-batches.
 """
 from __future__ import annotations
@@ -35,14 +41,6 @@ EMB_NAMES = ("tok_emb", "bigram_embed", "ve_embed")
 
 
 def _unsupported(m: ModelSpec) -> Optional[str]:
-    if m.recurrence.enabled:
-        return "recurrence"
-    if m.parallel_residual.enabled:
-        return "parallel_residual"
-    if m.attn_out_gate.enabled or m.sparse_attn_gate.enabled:
-        return "attention gates"
-    if not m.tie_embeddings:
-        return "untied lm_head"
     if m.model_dim % 64 or m.kv_dim % 64 or m.mlp_dim % 64 or m.head_dim % 8 or m.vocab_size % 64:
         return "dims that are not multiples of 64"
     if m.bigram.enabled and (m.bigram.dim % 64 or m.bigram.dim == m.model_dim):
@@ -69,6 +67,18 @@ class CudaEngine:
         self.qkvw = self.d + 2 * self.kv
         self.slope = m.leaky_slope if m.activation == "leaky_relu_sq" else 0.0
         self.enc = self.n // 2
+        self.sched = gpt.layer_schedule(m)                     # (layer, pass) per activation slot
+        self.nslots = len(self.sched)
+        self.last_slot = {l: j for j, (l, _) in enumerate(self.sched)}
+        self.first_slot = {}
+        for j, (l, _) in enumerate(self.sched):
+            self.first_slot.setdefault(l, j)
+        self.parallel = m.parallel_residual.enabled
+        self.gates = []                                        # (weight name, bias name or None, scale, multiplier)
+        if m.attn_out_gate.enabled:
+            self.gates.append(("attn_gate_weight", "attn_gate_bias", 1.0, 2.0))
+        if m.sparse_attn_gate.enabled:
+            self.gates.append(("sparse_attn_gate_weight", None, float(m.sparse_attn_gate.scale), 1.0))
         self.unet = m.skip_topology == "unet" and "skip_weights" in params
         self.eps = R.RMS_EPS
         self._alloc_params(params)
@@ -95,9 +105,13 @@ class CudaEngine:
             if self.train:
                 self.g[k] = torch.zeros_like(self.p[k])
         emb = [k for k in EMB_NAMES if k in shapes]
-        sca = [k for k in shapes if k not in gpt.BANKS and k not in emb]
+        head = [k for k in ("lm_head",) if k in shapes]
+        sca = [k for k in shapes if k not in gpt.BANKS and k not in emb and k not in head]
         self.groups = []
-        for names, lr in ((emb, self.t.tied_embed_lr if m.tie_embeddings else self.t.embed_lr), (sca, self.t.scalar_lr)):
+        plan = [(emb, self.t.tied_embed_lr if m.tie_embeddings else self.t.embed_lr), (sca, self.t.scalar_lr)]
+        if head:
+            plan.append((head, self.t.head_lr))
+        for names, lr in plan:
             total = sum(-(-math.prod(shapes[k]) // 4) * 4 for k in names)
             flat_p = torch.zeros(total, dtype=torch.float32, device=dev)
             flat_g = torch.zeros(total, dtype=torch.float32, device=dev) if self.train else None
@@ -121,6 +135,7 @@ class CudaEngine:
         self.Wo_u = torch.empty(n, d, d, dtype=BF, device=dev)       # un-scaled copies: only read by the scale-gradient fold
         self.Wd_u = torch.empty(n, d, mlp, dtype=BF, device=dev)
         self.E = torch.empty(m.vocab_size, d, dtype=BF, device=dev)
+        self.LM = self.E if m.tie_embeddings else torch.empty(m.vocab_size, d, dtype=BF, device=dev)   # output projection
         if m.bigram.enabled:
             self.BE = torch.empty(m.bigram.vocab_size, m.bigram.dim, dtype=BF, device=dev)
             self.BP = torch.empty(d, m.bigram.dim, dtype=BF, device=dev)
@@ -162,17 +177,22 @@ class CudaEngine:
         if m.value_embedding.enabled:
             self.ve_e = buf(T, m.value_embedding.dim)
         self.x0 = buf(T, d)
-        L = n if self.train else 1           # inference reuses one layer's worth of buffers
+        L = self.nslots if self.train else 1  # inference reuses one slot's worth of buffers
 
         def per_layer(*shape):
             return [buf(*shape) for _ in range(L)]
 
         self.x_in, self.h = per_layer(T, d), per_layer(T, d)
         self.qkv_pre, self.qk_post = per_layer(T, self.qkvw), per_layer(T, self.qkvw)
-        self.y, self.x_mid, self.mm = per_layer(T, d), per_layer(T, d), per_layer(T, d)
-        self.z = [buf(T, d) if (self.train and i in m.xsa_layers()) or (not self.train and i == 0 and m.xsa_last_n > 0) else None for i in range(L)]
+        self.y, self.x_mid = per_layer(T, d), per_layer(T, d)
+        self.mm = self.h if self.parallel else per_layer(T, d)      # parallel residual: the MLP reads the attention branch's normed input
+        self.z = [buf(T, d) if (self.train and self.sched[i][0] in m.xsa_layers()) or (not self.train and i == 0 and m.xsa_last_n > 0) else None
+                  for i in range(L)]
+        self.yg = [[buf(T, d) for _ in range(L)] for _ in self.gates]          # gated attention outputs, one list per gate
+        self.gv = [[torch.empty(T, self.H, dtype=torch.float32, device=dev) for _ in range(L)] for _ in self.gates]
+        self.zz = [None] * L                 # what the output projection consumed in each slot
         self.hu, self.a = per_layer(T, self.mlp), per_layer(T, self.mlp)
-        self.x_out = [buf(T, d) for _ in range(n)]
+        self.x_out = [buf(T, d) for _ in range(self.nslots)]
         self.lse = [None] * L
         self.hf = buf(T, d)
         self.logits = buf(T, m.vocab_size)
@@ -188,6 +208,8 @@ class CudaEngine:
             self.d_hu = buf(T, self.mlp)
             self.d_qk_post, self.d_qkv_pre = buf(T, self.qkvw), buf(T, self.qkvw)
             self.d_x0 = buf(T, d)
+            if self.gates and not self.parallel:
+                self.d_hx = torch.zeros(T, d, dtype=BF, device=dev)     # only its first `width` columns are ever written
             self.dsum = torch.empty(self.B, self.H, self.S, dtype=torch.float32, device=dev)
             self.d_skip = [buf(T, d) for _ in range(max(self.enc - 1, 0))] if self.unet else []
             self.d_xe = buf(T, d)
@@ -211,6 +233,8 @@ class CudaEngine:
             C.cast_rows(p["qo_bank"][n:], self.Wo_u, None, 0, 1, q)
             C.cast_rows(p["mlp_down_bank"], self.Wd_u, None, 0, 1, q)
         C.cast_rows(p["tok_emb"], self.E, None, 0, 1, False)
+        if not self.m.tie_embeddings:
+            C.cast_rows(p["lm_head"], self.LM, None, 0, 1, False)
         if self.m.bigram.enabled:
             C.cast_rows(p["bigram_embed"], self.BE, None, 0, 1, False)
             C.cast_rows(p["bigram_proj"], self.BP, p["bigram_scale"], 0, 1, False)
@@ -238,16 +262,16 @@ class CudaEngine:
         out = torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=(H != Hkv))
         self.y[li].copy_(out.transpose(1, 2).reshape(self.T, d))
 
-    def _attn_bwd(self, l):
+    def _attn_bwd(self, l, j):
         d, kv, B, S, H, Hkv, hd = self.d, self.kv, self.B, self.S, self.H, self.Hkv, self.hd
-        q = self.qk_post[l][:, :d]
-        k = self.qk_post[l][:, d:d + kv]
-        v = self.qkv_pre[l][:, d + kv:]
+        q = self.qk_post[j][:, :d]
+        k = self.qk_post[j][:, d:d + kv]
+        v = self.qkv_pre[j][:, d + kv:]
         dq, dk = self.d_qk_post[:, :d], self.d_qk_post[:, d:d + kv]
         dv = self.d_qkv_pre[:, d + kv:]
         xsa = l in self.m.xsa_layers()
         if self.attention == "native":
-            N.attn_bwd(q, k, v, self.y[l], self.d_y, self.lse[l], dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=xsa, dsum=self.dsum)
+            N.attn_bwd(q, k, v, self.y[j], self.d_y, self.lse[j], dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=xsa, dsum=self.dsum)
             return
         with torch.enable_grad():
             q4 = q.reshape(B, S, H, hd).transpose(1, 2).detach().requires_grad_(True)
@@ -284,11 +308,11 @@ class CudaEngine:
         x = self.x0
         skips: List[torch.Tensor] = []
         xsa_layers = m.xsa_layers()
-        for l in range(self.n):
-            li = l if self.train else 0
+        for j, (l, rep) in enumerate(self.sched):
+            li = j if self.train else 0
             s_l = gpt.layer_ln_scale(m, l)
             skip = sw = None
-            if self.unet and l >= self.enc and skips:
+            if self.unet and l >= self.enc and rep == 0 and skips:
                 skip, sw = skips.pop(), p["skip_weights"][l - self.enc]
             C.mix_norm_fwd(x, self.x0, skip, sw, p["resid_mix"][l], self.x_in[li], self.h[li], s_l, self.eps)
             if self.layer_flags is not None:
@@ -305,17 +329,24 @@ class CudaEngine:
             if l in xsa_layers:
                 zz = self.z[li]
                 C.xsa_fwd(self.y[li], self.qkv_pre[li][:, d + kv:], zz, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+            for gi, (wname, bname, gscale_, gmult) in enumerate(self.gates):
+                out = self.yg[gi][li]
+                C.head_gate_fwd(zz, self.h[li], p[wname][l], p[bname][l] if bname else None, out, self.gv[gi][li], self.H, self.hd, gscale_, gmult)
+                zz = out
+            self.zz[li] = zz
             N.gemm(zz, self.Wo[l], self.x_mid[li], epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.x_in[li])
-            C.mix_norm_fwd(self.x_mid[li], None, None, None, None, None, self.mm[li], s_l, self.eps)
+            if not self.parallel:
+                C.mix_norm_fwd(self.x_mid[li], None, None, None, None, None, self.mm[li], s_l, self.eps)
             N.gemm(self.mm[li], self.Wup[l], self.hu[li], epi=N.EPI_ACT_SQ, slope=self.slope, D2=self.a[li])
-            xo = self.x_out[l]
+            xo = self.x_out[j]
             N.gemm(self.a[li], self.Wd[l], xo, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.x_mid[li])
             x = xo
-            if self.unet and l < self.enc:
+            last_pass = j + 1 == self.nslots or self.sched[j + 1][0] != l
+            if self.unet and l < self.enc and last_pass:
                 skips.append(x)
         self.x_last = x
         C.mix_norm_fwd(x, None, None, None, None, None, self.hf, 1.0, self.eps)
-        N.gemm(self.hf, self.E, self.logits)
+        N.gemm(self.hf, self.LM, self.logits)
         if targets is not None:
             C.softcap_ce(self.logits, self.tgt, self.nll, self.logits if want_grad else None, self.loss_sum, m.logit_softcap, gscale)
 
@@ -325,35 +356,48 @@ class CudaEngine:
         C, m, p, g = self.C, self.m, self.p, self.g
         n, d, kv, S = self.n, self.d, self.kv, self.S
         A = N.EPI_F32_ATOMIC
-        N.gemm(self.logits, self.E, self.d_h, True, False)                               # d_hf
-        N.gemm(self.logits, self.hf, g["tok_emb"], False, False, A)
+        N.gemm(self.logits, self.LM, self.d_h, True, False)                              # d_hf
+        N.gemm(self.logits, self.hf, g["tok_emb"] if m.tie_embeddings else g["lm_head"], False, False, A)
         C.mix_norm_bwd(self.d_h, None, self.x_last, None, None, None, None, None, None, self.dx, None, None, None, None, False, 1.0, self.eps)
         self.d_x0.zero_()
         xsa_layers = m.xsa_layers()
-        for l in range(n - 1, -1, -1):
+        for j in range(self.nslots - 1, -1, -1):
+            l, rep = self.sched[j]
             s_l = gpt.layer_ln_scale(m, l)
             # ---- MLP
             self.Gd.zero_()
-            N.gemm(self.dx, self.a[l], self.Gd, False, False, A)
+            N.gemm(self.dx, self.a[j], self.Gd, False, False, A)
             C.fold_scaled_grad_bf16(self.Gd, self.Wd_u[l], p["mlp_scale"][l], 1, d, g["mlp_down_bank"][l], g["mlp_scale"][l])
-            N.gemm(self.dx, self.Wd[l], self.d_hu, True, False, N.EPI_MUL_ACTGRAD, slope=self.slope, aux=self.hu[l])
-            N.gemm(self.d_hu, self.mm[l], g["mlp_up_bank"][l], False, False, A)
+            N.gemm(self.dx, self.Wd[l], self.d_hu, True, False, N.EPI_MUL_ACTGRAD, slope=self.slope, aux=self.hu[j])
+            N.gemm(self.d_hu, self.mm[j], g["mlp_up_bank"][l], False, False, A)
             N.gemm(self.d_hu, self.Wup[l], self.d_m, True, False)
-            C.mix_norm_bwd(self.d_m, self.dx, self.x_mid[l], None, None, None, None, None, None, self.dx_mid, None, None, None, None, False, s_l, self.eps)
-            # ---- attention output projection
-            zz = self.z[l] if l in xsa_layers else self.y[l]
-            self.Go.zero_()
-            N.gemm(self.dx_mid, zz, self.Go, False, False, A)
-            C.fold_scaled_grad_bf16(self.Go, self.Wo_u[l], p["attn_scale"][l], 1, d, g["qo_bank"][n + l], g["attn_scale"][l])
-            vview = self.qkv_pre[l][:, d + kv:]
-            dv = self.d_qkv_pre[:, d + kv:]
-            if l in xsa_layers:
-                N.gemm(self.dx_mid, self.Wo[l], self.d_z, True, False)
-                C.xsa_bwd(self.d_z, self.y[l], vview, self.d_y, dv, False, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+            if self.parallel:
+                dx_mid, dx_next = self.dx, self.dx_mid      # no norm between x_mid and the MLP: the residual gradient passes through
+                d_hx = self.d_m                             # and the MLP-input gradient joins the QKV-input gradient below
             else:
-                N.gemm(self.dx_mid, self.Wo[l], self.d_y, True, False)
-            self._attn_bwd(l)
-            C.qk_norm_rope_bwd(self.d_qk_post, self.qkv_pre[l], self.d_qkv_pre, self.cos, self.sin, p["q_gain"][l], g["q_gain"][l], self.H, self.Hkv,
+                C.mix_norm_bwd(self.d_m, self.dx, self.x_mid[j], None, None, None, None, None, None, self.dx_mid, None, None, None, None, False, s_l, self.eps)
+                dx_mid, dx_next = self.dx_mid, self.dx
+                d_hx = self.d_hx if self.gates else None
+            # ---- attention output projection
+            zz = self.zz[j]
+            self.Go.zero_()
+            N.gemm(dx_mid, zz, self.Go, False, False, A)
+            C.fold_scaled_grad_bf16(self.Go, self.Wo_u[l], p["attn_scale"][l], 1, d, g["qo_bank"][n + l], g["attn_scale"][l])
+            vview = self.qkv_pre[j][:, d + kv:]
+            dv = self.d_qkv_pre[:, d + kv:]
+            xsa = l in xsa_layers
+            d_att = self.d_z if xsa else self.d_y            # gradient of what the gates / the output projection consumed
+            N.gemm(dx_mid, self.Wo[l], d_att, True, False)
+            for gi in range(len(self.gates) - 1, -1, -1):
+                wname, bname, gscale_, gmult = self.gates[gi]
+                gate_in = self.yg[gi - 1][j] if gi > 0 else (self.z[j] if xsa else self.y[j])
+                first_writer = (not self.parallel) and gi == len(self.gates) - 1
+                C.head_gate_bwd(d_att, gate_in, self.h[j], p[wname][l], self.gv[gi][j], g[wname][l], g[bname][l] if bname else None, d_hx,
+                                not first_writer, self.H, self.hd, gscale_, gmult)
+            if xsa:
+                C.xsa_bwd(self.d_z, self.y[j], vview, self.d_y, dv, False, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+            self._attn_bwd(l, j)
+            C.qk_norm_rope_bwd(self.d_qk_post, self.qkv_pre[j], self.d_qkv_pre, self.cos, self.sin, p["q_gain"][l], g["q_gain"][l], self.H, self.Hkv,
                                self.hd, m.rope_dims, S, self.eps)
             if m.value_embedding.enabled and l in m.value_embedding.layers:
                 vi = m.value_embedding.layers.index(l)
@@ -368,24 +412,31 @@ class CudaEngine:
                     self.d_ve_acc = torch.zeros_like(self.ve_e, dtype=torch.float32)
                 N.gemm(dv, self.VP[vi], self.d_ve_e, True, False)
                 self.d_ve_acc.add_(self.d_ve_e)
-            N.gemm(self.d_qkv_pre[:, :d], self.h[l], g["qo_bank"][l], False, False, A)
-            N.gemm(self.d_qkv_pre[:, d:d + kv], self.h[l], g["kv_bank"][l], False, False, A)
-            N.gemm(dv, self.h[l], g["kv_bank"][n + l], False, False, A)
-            N.gemm(self.d_qkv_pre, self.Wqkv[l], self.d_h, True, False)
+            # one weight-gradient product for the packed QKV rows, written to the Q, K and V slots of the gradient banks
+            N.gemm(self.d_qkv_pre, self.h[j], g["qo_bank"][l], False, False, A, segs=((d, g["kv_bank"][l]), (d + kv, g["kv_bank"][n + l])))
+            if d_hx is not None:
+                N.gemm(self.d_qkv_pre, self.Wqkv[l], self.d_h, True, False, N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=d_hx)
+            else:
+                N.gemm(self.d_qkv_pre, self.Wqkv[l], self.d_h, True, False)
             # ---- block input: RMSNorm backward, residual mix, U-Net skip
-            x_prev = self.x_out[l - 1] if l > 0 else self.x0
+            x_prev = self.x_out[j - 1] if j > 0 else self.x0
             skip = sw = d_skip = d_sw = add_grad = None
             self_pair = False
-            if self.unet and l >= self.enc and (2 * self.enc - 1 - l) >= 0:
-                e_idx = 2 * self.enc - 1 - l                     # encoder layer whose output this decoder layer consumed
-                skip, sw, d_sw = self.x_out[e_idx], p["skip_weights"][l - self.enc], g["skip_weights"][l - self.enc]
-                self_pair = e_idx == l - 1
+            e_idx = 2 * self.enc - 1 - l                         # encoder layer whose output a decoder layer's first pass consumed
+            if self.unet and l >= self.enc and rep == 0 and e_idx >= 0:
+                e_slot = self.last_slot[e_idx]
+                skip, sw, d_sw = self.x_out[e_slot], p["skip_weights"][l - self.enc], g["skip_weights"][l - self.enc]
+                self_pair = e_slot == j - 1
                 if not self_pair:
                     d_skip = self.d_skip[e_idx]
-            if self.unet and 1 <= l <= self.enc - 1:
-                add_grad = self.d_skip[l - 1]                     # the layer below is an encoder layer with a (non-adjacent) skip consumer
-            C.mix_norm_bwd(self.d_h, self.dx_mid, self.x_in[l], x_prev, self.x0, skip, sw, p["resid_mix"][l], add_grad, self.dx, self.d_x0, d_skip,
+            if self.unet and j > 0:
+                lp = self.sched[j - 1][0]                        # x_prev is the (last-pass) output of an encoder layer whose skip
+                if lp != l and lp < self.enc and self.first_slot.get(2 * self.enc - 1 - lp, -1) not in (-1, j):   # consumer is further up
+                    add_grad = self.d_skip[lp]
+            C.mix_norm_bwd(self.d_h, dx_mid, self.x_in[j], x_prev, self.x0, skip, sw, p["resid_mix"][l], add_grad, dx_next, self.d_x0, d_skip,
                            g["resid_mix"][l], d_sw, self_pair, s_l, self.eps)
+            if self.parallel:
+                self.dx, self.dx_mid = self.dx_mid, self.dx
         self.dx.add_(self.d_x0)
         bid = m.smear_gate_boundary_token_id
         C.norm_smear_bwd(self.dx, self.xe, p["smear_gate"] if m.smear_gate else None, self.ids if (m.smear_gate and bid is not None) else None,
@@ -630,7 +681,10 @@ class EngineBackend:
         e.set_hp(lr_scale, momentum)
         dev_spans = spans if staged else self.stage_spans(spans)
         for sp in dev_spans:
-            e.micro_step_span(sp, len(dev_spans))
+            if self.spec.train.cuda_graph and e.layer_flags is None:
+                self._graphed_micro_step(sp, len(dev_spans))
+            else:
+                e.micro_step_span(sp, len(dev_spans))
         if self.dist is not None:
             self.dist.step()
         else:
@@ -639,6 +693,35 @@ class EngineBackend:
         if read_loss:
             return float(e.loss_sum[0]) / (e.T * len(dev_spans))
         return None
+
+    def _graphed_micro_step(self, span: torch.Tensor, accum: int):
+        """Forward+backward of one micro-batch replayed from a CUDA graph. The engine allocates nothing per step and
+        every kernel argument is a fixed device address (hyper-parameters live in the device array ``hp``), so the
+        ~900 launches of a micro-batch are captured once per accumulation count and replayed; the span is copied into
+        a static staging buffer first. The first call runs eagerly (it also warms every lazily created buffer), the
+        second captures. Same idea as the reference's captured no-loss backward
+        (``parameter-golf-rs/crates/pg-train/src/lib.rs:2063-2133``), extended to the whole micro-step.
+        The sharded optimizer's weight-ready counters are compared against a host-side step count, so that path stays
+        eager (see `CudaEngine.forward`)."""
+        e = self.engine
+        st = getattr(self, "_graph_state", None)
+        if st is None or st["accum"] != accum:
+            st = self._graph_state = {"accum": accum, "graph": None, "calls": 0,
+                                      "span": torch.empty(e.T + 1, dtype=torch.int16, device=self.device)}
+        st["span"].copy_(span, non_blocking=True)
+        if st["calls"] == 0:
+            n0 = N.launch_count()
+            e.micro_step_span(st["span"], accum)
+            st["kernels"] = N.launch_count() - n0          # kernel nodes of one replay, for the launch counter
+        else:
+            if st["graph"] is None:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    e.micro_step_span(st["span"], accum)
+                st["graph"] = g
+            st["graph"].replay()
+            N.load().launches += st["kernels"]
+        st["calls"] += 1
 
     fused_ema = True
 

@@ -70,7 +70,9 @@ def _timing_key(name, a, k):
     if name == "gemm":           # (A, B, D, a_kmajor, b_kmajor, epi, ...): tell the products of the step apart
         A, B, D = a[0], a[1], a[2]
         kdim = A.shape[-1] if a[3] else A.shape[-2]
-        return f"gemm {_EPI_NAMES.get(int(a[5]), a[5])} N={D.shape[-1]} K={kdim} {'T' if a[3] else 'N'}{'T' if a[4] else 'N'}"
+        mdim = A.shape[-2] if a[3] else A.shape[-1]
+        seg = f" M={mdim} (row segments)" if len(a) > 17 and a[17] is not None else ""
+        return f"gemm {_EPI_NAMES.get(int(a[5]), a[5])} N={D.shape[-1]} K={kdim} {'T' if a[3] else 'N'}{'T' if a[4] else 'N'}{seg}"
     return name
 
 
@@ -128,8 +130,13 @@ def check_status(device=None, reset: bool = True):
 
 
 def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.0, slope=0.0, aux=None, colscale=None, D2=None, splits=0,
-         wait_flag=None, wait_value=0):
-    load().gemm(A, B, D, a_kmajor, b_kmajor, epi, alpha, beta, slope, aux, colscale, D2, splits, status_word(A.device), wait_flag, wait_value)
+         wait_flag=None, wait_value=0, segs=()):
+    """``segs``: up to two ``(first_row, tensor)`` pairs; with an fp32 epilogue the output rows from ``first_row`` on land in that
+    tensor instead of ``D`` (one product feeding several gradient matrices)."""
+    s0 = segs[0] if len(segs) > 0 else (0, None)
+    s1 = segs[1] if len(segs) > 1 else (0, None)
+    load().gemm(A, B, D, a_kmajor, b_kmajor, epi, alpha, beta, slope, aux, colscale, D2, splits, status_word(A.device), wait_flag, wait_value,
+                s0[0], s0[1], s1[0], s1[1])
     return D
 
 

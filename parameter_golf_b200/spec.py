@@ -186,6 +186,7 @@ class TrainSpec:
     train_log_every: int = 200
     val_batch_size: int = 524_288
     grad_wire_dtype: str = "bf16"       # wire dtype of bank-gradient reduce-scatter
+    cuda_graph: bool = False            # replay the micro-batch forward+backward from a captured CUDA graph
     checkpoint_every: int = 0
     checkpoint_path: Optional[str] = None
     resume_from: Optional[str] = None

@@ -30,7 +30,7 @@ def test_attention_forward(B, S, H, Hkv):
     torch.cuda.synchronize()
     n.check_status()
     ref = _ref(q, k, v, B, S, H, Hkv, hd)
-    assert (y.float() - ref).abs().max() < 0.03, (y.float() - ref).abs().max()
+    assert (y.float() - ref).abs().max() < 0.04, (y.float() - ref).abs().max()      # one bf16 ulp of an output in [4, 8) is 0.031
     lse_nat = -lse * 0.6931471805599453               # the kernel stores -(log2-domain lse), the form its backward consumes
     assert (lse_nat - _ref_lse(q, k, B, S, H, Hkv, hd)).abs().max().item() < 0.02
 

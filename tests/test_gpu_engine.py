@@ -31,7 +31,7 @@ def rel_err(a, b):
     return float((a.double().cpu() - b.double().cpu()).norm() / (b.double().cpu().norm() + 1e-12))
 
 
-@pytest.mark.parametrize("variant", ["record", "baseline", "ve"])
+@pytest.mark.parametrize("variant", ["record", "baseline", "ve", "recurrence", "parallel", "attn_gate", "sparse_gate", "parallel_gate", "untied"])
 def test_one_step_loss_and_gradients_match_oracle(variant):
     from parameter_golf_b200.models import gpt
     from parameter_golf_b200.models.engine import CudaEngine
@@ -42,6 +42,16 @@ def test_one_step_loss_and_gradients_match_oracle(variant):
               "model.ln_scale": "false", "model.activation": "relu_sq"}
     if variant == "ve":
         ov = {"model.value_embedding.enabled": "true", "model.value_embedding.dim": 64, "model.value_embedding.layers": "[2,3]"}
+    if variant == "recurrence":                  # layers 1 and 2 run twice; layer 1 is an encoder layer feeding a U-Net skip
+        ov = {"model.recurrence.enabled": "true", "model.recurrence.start_layer": 1, "model.recurrence.repeat_layers": 2}
+    if variant in ("parallel", "parallel_gate"):
+        ov = {"model.parallel_residual.enabled": "true"}
+    if variant == "attn_gate":
+        ov = {"model.attn_out_gate.enabled": "true", "model.attn_out_gate.width": 12}
+    if variant in ("sparse_gate", "parallel_gate"):
+        ov.update({"model.sparse_attn_gate.enabled": "true", "model.sparse_attn_gate.width": 12, "model.sparse_attn_gate.scale": 1.5})
+    if variant == "untied":
+        ov = {"model.tie_embeddings": "false"}
     spec = small_spec(**ov)
     params = gpt.fill_deterministic(spec.model)
     torch.manual_seed(0)
@@ -58,7 +68,8 @@ def test_one_step_loss_and_gradients_match_oracle(variant):
     worst = {}
     for k, g in ref.items():
         worst[k] = rel_err(eng.g[k], g)
-    bad = {k: v for k, v in worst.items() if v > 0.06}          # bf16 activations/gradients vs an fp64 oracle
+    # bf16 activations/gradients vs an fp64 oracle; q_gain is one number per head summed over every token with heavy cancellation
+    bad = {k: v for k, v in worst.items() if v > (0.2 if k == "q_gain" else 0.06)}
     assert not bad, worst
 
 
@@ -127,6 +138,31 @@ def test_short_training_trajectory_tracks_oracle():
         lg.append(gpu.train_step([(ids, tgt)], 1.0, 0.95, False))
         lc.append(cpu.train_step([(ids, tgt)], 1.0, 0.95, False))
     assert lg[-1] < lg[0] and all(abs(a - b) < 0.02 * max(1.0, abs(b)) for a, b in zip(lg, lc)), (lg, lc)
+
+
+def test_cuda_graph_micro_step_matches_eager():
+    """The captured forward+backward replays to the same losses and parameters as the eager launch sequence."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import EngineBackend
+    res = {}
+    for graph in (False, True):
+        spec = small_spec(**{"train.cuda_graph": "true" if graph else "false", "train.ema_decay": 0.0})
+        spec.mode = "record"
+        spec.allow_unsupported_variants = True
+        be = EngineBackend(spec, gpt.fill_deterministic(spec.model))
+        T = be.engine.T
+        gen = torch.Generator().manual_seed(5)
+        losses = []
+        for step in range(3):
+            spans = [torch.randint(0, 256, (T + 1,), generator=gen).to(torch.int16) for _ in range(be.accum)]
+            losses.append(be.train_step_spans(spans, 1.0, 0.95))
+        res[graph] = (losses, {k: v.clone() for k, v in be.engine.p.items()})
+    # split-K atomics make weight gradients order-dependent in their last bits and the bf16 Newton-Schulz iteration amplifies
+    # that, so two eager runs differ by as much: the first two losses (same weights) agree closely, the third loosely
+    assert res[True][0][:2] == pytest.approx(res[False][0][:2], abs=1e-4), (res[True][0], res[False][0])
+    assert res[True][0][2] == pytest.approx(res[False][0][2], abs=2e-2), (res[True][0], res[False][0])
+    for k, v in res[False][1].items():
+        assert (res[True][1][k] - v).abs().max().item() <= 5e-2 * (v.abs().max().item() + 1e-6), k
 
 
 def test_bounded_wait_times_out_and_reports():

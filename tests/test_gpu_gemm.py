@@ -104,3 +104,23 @@ def test_many_tiles_persistent_schedule_matches():
     torch.cuda.synchronize()
     n.check_status()
     _close(D, _ref(A, B, True, True))
+
+
+def test_row_segments_scatter_one_product_into_three_gradient_matrices():
+    """dW of a packed [q; k; v] projection: rows 0..255 / 256..383 / 384..511 of the product accumulate into three matrices."""
+    n = _n()
+    torch.manual_seed(3)
+    T, d, dq, dkv = 4096, 192, 256, 128
+    dY, X = _rand(T, dq + 2 * dkv, scale=0.3), _rand(T, d, scale=0.3)
+    bank = torch.randn(dq + 2 * dkv + 64, d, device="cuda")                  # three slots of one fp32 buffer, out of order
+    Gq, Gk, Gv = bank[dkv + 64:dkv + 64 + dq], bank[:dkv], bank[dkv + 64 + dq:]
+    before = bank.clone()
+    n.gemm(dY, X, Gq, False, False, n.EPI_F32_ATOMIC, segs=((dq, Gk), (dq + dkv, Gv)))
+    torch.cuda.synchronize()
+    n.check_status()
+    ref = dY.float().t() @ X.float()
+    upd = bank - before
+    _close(upd[dkv + 64:dkv + 64 + dq], ref[:dq], 5e-3)
+    _close(upd[:dkv], ref[dq:dq + dkv], 5e-3)
+    _close(upd[dkv + 64 + dq:], ref[dq + dkv:], 5e-3)
+    assert upd[dkv:dkv + 64].abs().max().item() == 0.0                        # the gap between the slots is untouched

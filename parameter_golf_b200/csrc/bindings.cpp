@@ -1,7 +1,10 @@
 // pybind11 bindings: torch tensors in, raw pointers + the current CUDA stream out to the kernel library.
 #include <ATen/cuda/CUDAContext.h>
+#include <pybind11/numpy.h>
+#include <pybind11/stl.h>
 #include <torch/extension.h>
 
+#include "artifact.h"
 #include "loader.h"
 #include "pgb.h"
 
@@ -110,5 +113,46 @@ void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor D, bool a_kmajor, bool
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "tcgen05 bf16 GEMM with fused epilogue");
+  // ---- host-side artifact primitives (artifact.cpp) -----------------------------------------------------------------
+  m.def("pack_bits", [](py::buffer q, int bits) {
+    py::buffer_info info = q.request();
+    TORCH_CHECK(info.itemsize == 1, "pack_bits expects int8 codes");
+    std::string out;
+    {
+      py::gil_scoped_release nogil;
+      out = pgb::pack_bits(static_cast<const int8_t*>(info.ptr), (size_t)info.size, bits);
+    }
+    return py::bytes(out);
+  });
+  m.def("unpack_bits", [](py::bytes data, size_t count, int bits) {
+    const std::string d = data;
+    py::array_t<int8_t> out((py::ssize_t)count);
+    pgb::unpack_bits(reinterpret_cast<const uint8_t*>(d.data()), d.size(), count, bits, out.mutable_data());
+    return out;
+  });
+  m.def("crc32", [](py::bytes data) {
+    const std::string d = data;
+    return pgb::crc32_ieee(reinterpret_cast<const uint8_t*>(d.data()), d.size());
+  });
+  m.def("write_pgrs", [](const std::vector<std::tuple<std::string, std::vector<uint32_t>, int, py::bytes>>& tensors, const std::string& metadata) {
+    std::vector<pgb::PgrsTensor> ts;
+    ts.reserve(tensors.size());
+    for (const auto& t : tensors) {
+      pgb::PgrsTensor r;
+      r.name = std::get<0>(t);
+      r.dims = std::get<1>(t);
+      r.dtype = (uint8_t)std::get<2>(t);
+      r.data = std::get<3>(t);
+      ts.push_back(std::move(r));
+    }
+    return py::bytes(pgb::write_pgrs(ts, metadata));
+  });
+  m.def("read_pgrs", [](py::bytes buf) {
+    std::string meta;
+    const std::vector<pgb::PgrsTensor> ts = pgb::read_pgrs(buf, &meta);
+    py::list out;
+    for (const auto& t : ts) out.append(py::make_tuple(t.name, t.dims, (int)t.dtype, py::bytes(t.data)));
+    return py::make_tuple(out, meta);
+  });
 #include "bindings_more.inc"
 }

@@ -30,6 +30,13 @@ __device__ __forceinline__ V8 ldf(const float* p) {
   return r;
 }
 __device__ __forceinline__ float bfr(float x) { return __bfloat162float(__float2bfloat16(x)); }
+__device__ __forceinline__ uint4 ldraw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ V8 cvt8(const uint4& q) {
+  V8 r;
+  float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z), d = unpack_bf16x2(q.w);
+  r.v[0] = a.x; r.v[1] = a.y; r.v[2] = b.x; r.v[3] = b.y; r.v[4] = c.x; r.v[5] = c.y; r.v[6] = d.x; r.v[7] = d.y;
+  return r;
+}
 }  // namespace
 
 constexpr int RT = 256, RW = 8;
@@ -76,13 +83,24 @@ mix_norm_bwd2_kernel(const __nv_bfloat16* __restrict__ d_h, const __nv_bfloat16*
   for (int row = blockIdx.x * RW + warp; row < rows; row += gridDim.x * RW) {
     const size_t base = (size_t)row * d;
     V8 xi[NV], dy[NV];
+    // every operand of the row is requested before the first reduction, so one DRAM round trip covers them all
+    uint4 q_res[NV], q_x0[MIX ? NV : 1], q_x[MIX ? NV : 1], q_acc0[MIX ? NV : 1], q_skip[SKIP ? NV : 1], q_ag[NV];
     float ss = 0.f, dot = 0.f;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int c = (j * 32 + lane) * 8;
       if (c < d) {
-        xi[j] = ldv(x_in + base + c);
-        dy[j] = ldv(d_h + base + c);
+        const uint4 r_xi = ldraw(x_in + base + c), r_dy = ldraw(d_h + base + c);
+        if (d_res) q_res[j] = ldraw(d_res + base + c);
+        if constexpr (MIX) {
+          q_x0[j] = ldraw(x0 + base + c);
+          q_x[j] = ldraw(x + base + c);
+          q_acc0[j] = ldraw(d_x0 + base + c);
+        }
+        if constexpr (SKIP) q_skip[j] = ldraw(skip + base + c);
+        if (add_grad) q_ag[j] = ldraw(add_grad + base + c);
+        xi[j] = cvt8(r_xi);
+        dy[j] = cvt8(r_dy);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           ss += xi[j].v[e] * xi[j].v[e];
@@ -102,20 +120,20 @@ mix_norm_bwd2_kernel(const __nv_bfloat16* __restrict__ d_h, const __nv_bfloat16*
 #pragma unroll
         for (int e = 0; e < 8; ++e) g.v[e] = k1 * (dy[j].v[e] - xi[j].v[e] * k2);
         if (d_res) {
-          V8 r = ldv(d_res + base + c);
+          const V8 r = cvt8(q_res[j]);
 #pragma unroll
           for (int e = 0; e < 8; ++e) g.v[e] += r.v[e];
         }
         if constexpr (MIX) {
-          V8 m0 = ldf(mix + c), m1 = ldf(mix + d + c), b = ldv(x0 + base + c), a = ldv(x + base + c);
+          V8 m0 = ldf(mix + c), m1 = ldf(mix + d + c), b = cvt8(q_x0[j]), a = cvt8(q_x[j]);
           V8 k, w;
           if constexpr (SKIP) {
-            k = ldv(skip + base + c);
+            k = cvt8(q_skip[j]);
             w = ldf(sw + c);
 #pragma unroll
             for (int e = 0; e < 8; ++e) a.v[e] = bfr(a.v[e] + w.v[e] * k.v[e]);
           }
-          V8 acc0 = ldv(d_x0 + base + c);
+          V8 acc0 = cvt8(q_acc0[j]);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             am0[j][e] += g.v[e] * a.v[e];
@@ -140,7 +158,7 @@ mix_norm_bwd2_kernel(const __nv_bfloat16* __restrict__ d_h, const __nv_bfloat16*
           }
         }
         if (add_grad) {
-          V8 ag = ldv(add_grad + base + c);
+          const V8 ag = cvt8(q_ag[j]);
 #pragma unroll
           for (int e = 0; e < 8; ++e) g.v[e] += ag.v[e];
         }
@@ -210,16 +228,18 @@ __device__ __forceinline__ void rope8(V8& n, int sub, int hp, int pos, int half,
 
 __global__ void __launch_bounds__(256) qk_norm_rope_fwd64_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                                                  const float* __restrict__ cosT, const float* __restrict__ sinT,
-                                                                 const float* __restrict__ gain, long long nvec, int ld, int H, int Hkv, int rope_dims,
+                                                                 const float* __restrict__ gain, int nvec, int ld, int H, int Hkv, int rope_dims,
                                                                  int seq_len, float eps) {
   const int sub = threadIdx.x & 7;
   const int nh = H + Hkv, half = rope_dims / 2, hp = half / 8;
-  const long long vstride = (long long)gridDim.x * (blockDim.x / 8);
-  const long long nvec_pad = (nvec + 3) / 4 * 4;           // whole warps stay converged for the shuffles
-  for (long long v = (long long)blockIdx.x * (blockDim.x / 8) + (threadIdx.x >> 3); v < nvec_pad; v += vstride) {
+  // 32-bit index arithmetic throughout: the vector count (rows x heads) fits, and a 64-bit divide per vector costs
+  // more instructions than the rest of the loop body
+  const int vstride = (int)gridDim.x * (blockDim.x / 8);
+  const int nvec_pad = (nvec + 3) / 4 * 4;                 // whole warps stay converged for the shuffles
+  for (int v = (int)blockIdx.x * (blockDim.x / 8) + (threadIdx.x >> 3); v < nvec_pad; v += vstride) {
     const bool live = v < nvec;
-    const long long vv = live ? v : nvec - 1;
-    const int row = (int)(vv / nh), head = (int)(vv % nh);
+    const int vv = live ? v : nvec - 1;
+    const int row = (int)((unsigned)vv / (unsigned)nh), head = vv - row * nh;
     const size_t off = (size_t)row * ld + head * 64 + sub * 8;
     V8 a = ldv(src + off);
     float ss = 0.f;
@@ -230,11 +250,11 @@ __global__ void __launch_bounds__(256) qk_norm_rope_fwd64_kernel(const __nv_bflo
     ss += __shfl_xor_sync(0xffffffffu, ss, 4);
     const float inv = rsqrtf(ss / 64.f + eps);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) a.v[e] = bfr(a.v[e] * inv);
-    if (hp > 0) rope8(a, sub, hp, row % seq_len, half, cosT, sinT, false);
+    for (int e = 0; e < 8; ++e) a.v[e] *= inv;
+    if (hp > 0) rope8(a, sub, hp, (int)((unsigned)row % (unsigned)seq_len), half, cosT, sinT, false);
     const float g = (head < H && gain) ? gain[head] : 1.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) a.v[e] = bfr(a.v[e]) * g;
+    for (int e = 0; e < 8; ++e) a.v[e] *= g;                // one rounding, at the store
     if (live) stv(dst + off, a);
   }
 }
@@ -242,19 +262,19 @@ __global__ void __launch_bounds__(256) qk_norm_rope_fwd64_kernel(const __nv_bflo
 __global__ void __launch_bounds__(256) qk_norm_rope_bwd64_kernel(const __nv_bfloat16* __restrict__ d_post, const __nv_bfloat16* __restrict__ pre,
                                                                  __nv_bfloat16* __restrict__ d_pre, const float* __restrict__ cosT,
                                                                  const float* __restrict__ sinT, const float* __restrict__ gain, float* __restrict__ d_gain,
-                                                                 long long nvec, int ld, int H, int Hkv, int rope_dims, int seq_len, float eps) {
+                                                                 int nvec, int ld, int H, int Hkv, int rope_dims, int seq_len, float eps) {
   __shared__ float sg[64];
   for (int i = threadIdx.x; i < 64; i += blockDim.x) sg[i] = 0.f;
   __syncthreads();
   const int sub = threadIdx.x & 7;
   const int nh = H + Hkv, half = rope_dims / 2, hp = half / 8;
-  const long long vstride = (long long)gridDim.x * (blockDim.x / 8);
-  const long long nvec_pad = (nvec + 3) / 4 * 4;
-  for (long long v = (long long)blockIdx.x * (blockDim.x / 8) + (threadIdx.x >> 3); v < nvec_pad; v += vstride) {
+  const int vstride = (int)gridDim.x * (blockDim.x / 8);
+  const int nvec_pad = (nvec + 3) / 4 * 4;
+  for (int v = (int)blockIdx.x * (blockDim.x / 8) + (threadIdx.x >> 3); v < nvec_pad; v += vstride) {
     const bool live = v < nvec;
-    const long long vv = live ? v : nvec - 1;
-    const int row = (int)(vv / nh), head = (int)(vv % nh);
-    const int pos = row % seq_len;
+    const int vv = live ? v : nvec - 1;
+    const int row = (int)((unsigned)vv / (unsigned)nh), head = vv - row * nh;
+    const int pos = (int)((unsigned)row % (unsigned)seq_len);
     const size_t off = (size_t)row * ld + head * 64 + sub * 8;
     const V8 x = ldv(pre + off);
     V8 dy = ldv(d_post + off);
@@ -270,11 +290,11 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd64_kernel(const __nv_bflo
     if (d_gain != nullptr) {                       // warp-uniform
       V8 r;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) r.v[e] = bfr(x.v[e] * inv);
+      for (int e = 0; e < 8; ++e) r.v[e] = x.v[e] * inv;
       if (hp > 0) rope8(r, sub, hp, pos, half, cosT, sinT, false);
       float acc = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc += dy.v[e] * bfr(r.v[e]);
+      for (int e = 0; e < 8; ++e) acc += dy.v[e] * r.v[e];
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
@@ -305,16 +325,18 @@ bool qk_norm_rope_fast_ok(int H, int hd, int rope_dims) { return hd == 64 && H <
 
 void qk_norm_rope_fwd64(const void* src, void* dst, const float* cosT, const float* sinT, const float* gain, int rows, int ld, int H, int Hkv,
                         int rope_dims, int seq_len, float eps, cudaStream_t st) {
-  const long long nvec = (long long)rows * (H + Hkv);
-  const int grid = (int)std::max<long long>(1, std::min<long long>((nvec + 31) / 32, 148 * 16));
+  if ((long long)rows * (H + Hkv) > 0x7fffff00ll) throw std::runtime_error("qk_norm_rope: too many head vectors for 32-bit indexing");
+  const int nvec = rows * (H + Hkv);
+  const int grid = std::max(1, std::min((nvec + 31) / 32, 148 * 16));
   qk_norm_rope_fwd64_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, cosT, sinT, gain, nvec, ld, H, Hkv, rope_dims, seq_len,
                                                   eps);
 }
 
 void qk_norm_rope_bwd64(const void* d_post, const void* pre, void* d_pre, const float* cosT, const float* sinT, const float* gain, float* d_gain,
                         int rows, int ld, int H, int Hkv, int rope_dims, int seq_len, float eps, cudaStream_t st) {
-  const long long nvec = (long long)rows * (H + Hkv);
-  const int grid = (int)std::max<long long>(1, std::min<long long>((nvec + 31) / 32, 148 * 8));
+  if ((long long)rows * (H + Hkv) > 0x7fffff00ll) throw std::runtime_error("qk_norm_rope: too many head vectors for 32-bit indexing");
+  const int nvec = rows * (H + Hkv);
+  const int grid = std::max(1, std::min((nvec + 31) / 32, 148 * 8));
   qk_norm_rope_bwd64_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)d_post, (const __nv_bfloat16*)pre, (__nv_bfloat16*)d_pre, cosT, sinT, gain,
                                                   d_gain, nvec, ld, H, Hkv, rope_dims, seq_len, eps);
 }

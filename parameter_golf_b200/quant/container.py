@@ -41,6 +41,23 @@ class TensorRecord:
     data: bytes         # raw payload (bit-packed payloads are shorter than prod(dims)*itemsize)
 
 
+# ---- native primitives ----------------------------------------------------------------------------
+_native_mod = None
+
+
+def _native():
+    """The C++ implementations of bit packing, CRC-32 and the PGRS container (``csrc/artifact.cpp``), or ``None`` when the
+    extension has not been built; the NumPy forms below are the specification they are tested against."""
+    global _native_mod
+    if _native_mod is None:
+        try:
+            from ..ops import native
+            _native_mod = native.load_raw() if native.available() else False
+        except Exception:
+            _native_mod = False
+    return _native_mod or None
+
+
 # ---- zstd via ctypes ------------------------------------------------------------------------------
 _zstd = None
 
@@ -87,7 +104,10 @@ def zstd_decompress(data: bytes) -> bytes:
 
 # ---- PGRS -------------------------------------------------------------------------------------------
 
-def write_pgrs(tensors: List[TensorRecord], metadata: str) -> bytes:
+def write_pgrs(tensors: List[TensorRecord], metadata: str, native: bool = True) -> bytes:
+    nat = _native() if native else None
+    if nat is not None:
+        return nat.write_pgrs([(t.name, [int(d) for d in t.dims], DTYPE_CODES[t.dtype], bytes(t.data)) for t in tensors], metadata)
     out = bytearray(b"PGRS")
     out += struct.pack("<II", 1, len(tensors))
     for t in tensors:
@@ -102,7 +122,14 @@ def write_pgrs(tensors: List[TensorRecord], metadata: str) -> bytes:
     return bytes(out)
 
 
-def read_pgrs(buf: bytes) -> Tuple[List[TensorRecord], str]:
+def read_pgrs(buf: bytes, native: bool = True) -> Tuple[List[TensorRecord], str]:
+    nat = _native() if native else None
+    if nat is not None:
+        try:
+            recs, meta = nat.read_pgrs(bytes(buf))
+        except RuntimeError as e:
+            raise ArtifactError(str(e)) from None
+        return [TensorRecord(n, tuple(d), CODE_NAMES[c], data) for n, d, c, data in recs], meta
     if len(buf) < 12 or buf[:4] != b"PGRS":
         raise ArtifactError("not a PGRS file")
     pos = 4
@@ -188,9 +215,15 @@ def decompress_payload(buf: bytes) -> bytes:
 
 # ---- bit packing --------------------------------------------------------------------------------------
 
-def pack_bits(q: np.ndarray, bits: int) -> bytes:
+def pack_bits(q: np.ndarray, bits: int, native: bool = True) -> bytes:
     """LSB-first little-endian bit stream of ``q - qmin`` (unsigned, ``bits`` wide), elements back to
     back with no row padding (``pg-quant/src/export.rs:542-558``)."""
+    nat = _native() if native else None
+    if nat is not None and 2 <= bits <= 8 and q.size and int(np.abs(q).max()) < 128:
+        try:
+            return nat.pack_bits(np.ascontiguousarray(q.reshape(-1).astype(np.int8)), bits)
+        except RuntimeError as e:
+            raise ArtifactError(str(e)) from None
     qmin = -(1 << (bits - 1))
     e = (q.astype(np.int32).reshape(-1) - qmin).astype(np.uint32)
     if e.size and int(e.max()) >= (1 << bits):
@@ -199,7 +232,13 @@ def pack_bits(q: np.ndarray, bits: int) -> bytes:
     return np.packbits(b, bitorder="little").tobytes()
 
 
-def unpack_bits(data: bytes, count: int, bits: int) -> np.ndarray:
+def unpack_bits(data: bytes, count: int, bits: int, native: bool = True) -> np.ndarray:
+    nat = _native() if native else None
+    if nat is not None and 2 <= bits <= 8:
+        try:
+            return nat.unpack_bits(bytes(data), count, bits).astype(np.int32)
+        except RuntimeError as e:
+            raise ArtifactError(str(e)) from None
     qmin = -(1 << (bits - 1))
     need = (count * bits + 7) // 8
     if len(data) < need:

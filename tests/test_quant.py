@@ -189,3 +189,34 @@ def test_selective_prune_hits_target():
     assert size(out) <= int(full * 0.93) and n > 0
     changed = out["a"] != q["a"]
     assert (q["a"][changed].abs() == 1).all() and (out["a"][changed] == 0).all()
+
+
+def test_native_artifact_primitives_match_numpy_forms():
+    """C++ bit packing, CRC-32 and PGRS container against the NumPy/zlib specification, both directions."""
+    import zlib
+    import numpy as np
+    from parameter_golf_b200.quant import container as C
+    if C._native() is None:
+        pytest.skip("native extension not built")
+    rng = np.random.default_rng(0)
+    for bits in (4, 5, 6, 8):
+        lo, hi = -(1 << (bits - 1)), (1 << (bits - 1)) - 1
+        q = rng.integers(lo, hi + 1, size=1001).astype(np.int8)
+        packed = C.pack_bits(q, bits, native=True)
+        assert packed == C.pack_bits(q, bits, native=False)
+        assert (C.unpack_bits(packed, q.size, bits, native=True) == q).all()
+        assert (C.unpack_bits(packed, q.size, bits, native=False) == q).all()
+    with pytest.raises(C.ArtifactError):
+        C.pack_bits(np.array([40], dtype=np.int8), 6)                     # outside [-32, 31]
+    blob = rng.integers(0, 256, size=100003).astype(np.uint8).tobytes()
+    assert C._native().crc32(blob) == zlib.crc32(blob) & 0xFFFFFFFF
+    recs = [C.TensorRecord("a.q", (3, 7), "i8", bytes(range(16))), C.TensorRecord("b", (2,), "f16", b"\x00\x3c\x00\x40")]
+    raw = C.write_pgrs(recs, '{"k": 1}', native=True)
+    assert raw == C.write_pgrs(recs, '{"k": 1}', native=False)
+    for nat in (True, False):
+        got, meta = C.read_pgrs(raw, native=nat)
+        assert meta == '{"k": 1}' and [(r.name, tuple(r.dims), r.dtype, r.data) for r in got] == [(r.name, r.dims, r.dtype, r.data) for r in recs]
+        bad = bytearray(raw)
+        bad[40] ^= 0xFF
+        with pytest.raises(C.ArtifactError):
+            C.read_pgrs(bytes(bad), native=nat)

@@ -61,16 +61,13 @@ struct AttnBwdParams {
 
 
 // ------------------------------------------------------------------------------------------------------------------
-// Query-stationary kernel.  One item = a 128-row query tile of one head; it streams the key tiles 0..qt.  A key tile is
-// two units of 64 keys, one per softmax group, each with its own score buffers and barriers: S_u = Q K_u^T and
-// dP_u = dO V_u^T (128 x 64, N = 64 MMAs) land in TMEM, the group pulls them into registers and releases the buffers at
-// once (`s_free[u]`), dS_u goes to its own TMEM columns as bf16 and feeds dQ += dS_u K_u.  Nothing couples the two
-// groups, and the first unit of group 1 is issued half a unit period late, so that one group exponentiates (MUFU)
-// while the other loads, stores and waits.  Two issuing threads (scores / dQ) keep the tensor pipe fed; Q/dO are
-// double-buffered across items.
-// TMEM: unit u: S_u [128u, 128u+64) dP_u [128u+64, 128u+128); dS_u [256+32u, 288+32u); dQ [320,384).
+// Query-stationary kernel.  One item = a 128-row query tile of one head; it streams the key tiles 0..qt.  Per key tile:
+// S = Q K^T and dP = dO V^T (128 x 128, N = 128 MMAs) land in TMEM; the two softmax groups each take 64 key columns,
+// pull them into registers and release the score buffers at once (`s_free`), so the next tile's scores are computed
+// while this tile's dS is; dS goes to its own TMEM columns as bf16 and feeds dQ += dS K.  Two issuing threads (scores /
+// dQ) keep the tensor pipe fed; Q/dO are double-buffered across items.
+// TMEM: S [0,128) dP [128,256) dS [256,320) dQ [320,384).
 constexpr int DQ_STAGES = 3;
-constexpr long long DQ_GROUP_OFFSET_CLK = 700;
 constexpr int DQ_THREADS = 384;              // warpgroup 0: warp 0 TMA, warp 1 score MMAs, warp 2 dQ MMAs, warp 3 idle; warpgroups 1, 2: softmax
 constexpr int DQ_SMEM = (4 + 2 * DQ_STAGES) * AB_TILE + 1024 + 256;
 
@@ -86,11 +83,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   uint64_t* q_empty = q_full + 2;            // 2
   uint64_t* kv_full = q_empty + 2;
   uint64_t* kv_empty = kv_full + DQ_STAGES;
-  uint64_t* s_full = kv_empty + DQ_STAGES;   // 2: one per unit
-  uint64_t* s_free = s_full + 2;             // 2
-  uint64_t* p_full = s_free + 2;             // 2
-  uint64_t* ds_free = p_full + 2;            // 2: the dQ MMAs of a unit have consumed its dS
-  uint64_t* dq_full = ds_free + 2;           // 1
+  uint64_t* s_full = kv_empty + DQ_STAGES;   // 1
+  uint64_t* s_free = s_full + 1;             // 1
+  uint64_t* p_full = s_free + 1;             // 1
+  uint64_t* dq_full = p_full + 1;            // 1
   uint64_t* dq_empty = dq_full + 1;          // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -119,12 +115,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    for (int u = 0; u < 2; ++u) {
-      mbar_init(&s_full[u], 1);
-      mbar_init(&s_free[u], 128);
-      mbar_init(&p_full[u], 128);
-      mbar_init(&ds_free[u], 1);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 256);
+    mbar_init(p_full, 256);
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, 256);
     *abort_flag = 0;
@@ -171,7 +164,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   } else if (warp == 1) {
     // scores: S(j) and dP(j) as soon as the previous tile's scores have been pulled into registers
     if (lane == 0) {
-      constexpr uint32_t IDESC_S = make_idesc_bf16(128, 64, 0, 0);     // Q K_u^T, dO V_u^T
+      constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);    // Q K^T, dO V^T
       long long tg = 0;
       int il = 0;
       bool ok = true;
@@ -182,24 +175,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint32_t sq = smem_u32(sQD + qb * 2 * AB_TILE), sdo = sq + AB_TILE;
         for (int j = 0; j < it.n_kv && ok; ++j, ++tg) {
           const int stage = (int)(tg % DQ_STAGES);
+          if (tg > 0 && !mbar_wait(s_free, (uint32_t)((tg - 1) & 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, j)) { ok = false; break; }
           if (!mbar_wait(&kv_full[stage], (uint32_t)((tg / DQ_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, j)) { ok = false; break; }
+          tc_fence_after();
           const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE), sv = sk + AB_TILE;
-          for (int u = 0; u < 2 && ok; ++u) {
-            if (tg > 0 && !mbar_wait(&s_free[u], (uint32_t)((tg - 1) & 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, j)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t tu = tmem_base + u * 128, ku = u * 8192;        // keys 64u.. of the tile: 64 rows of 128 bytes further on
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_ss(tu, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + ku + k * 32, 16, 1024), IDESC_S, k > 0);
+          for (int k = 0; k < 4; ++k) umma_ss(tmem_base, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_ss(tu + 64, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + ku + k * 32, 16, 1024), IDESC_S, k > 0);
-            umma_commit(&s_full[u]);
-            if (tg == 0 && u == 0) {          // once per CTA: put group 1 half a unit period behind group 0
-              const long long t0 = clock64();
-              while (clock64() - t0 < DQ_GROUP_OFFSET_CLK) {}
-            }
-          }
+          for (int k = 0; k < 4; ++k)
+            umma_ss(tmem_base + 128, make_smem_desc(sdo + k * 32, 16, 1024), make_smem_desc(sv + k * 32, 16, 1024), IDESC_S, k > 0);
+          umma_commit(s_full);
         }
         if (ok) umma_commit(&q_empty[qb]);    // Q / dO of this item are read by the score MMAs only
       }
@@ -216,20 +201,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int j = 0; j < it.n_kv && ok; ++j, ++tg) {
           const int stage = (int)(tg % DQ_STAGES);
           if (!mbar_wait(&kv_full[stage], (uint32_t)((tg / DQ_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, j)) { ok = false; break; }
-          const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE);
-          for (int u = 0; u < 2 && ok; ++u) {
-            if (!mbar_wait(&p_full[u], (uint32_t)(tg & 1), abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
-            if (j == 0 && u == 0) {        // the previous item's dQ must have been read out before it is overwritten
-              if (!mbar_wait(dq_empty, (uint32_t)((il & 1) ^ 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
-            }
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_ts(tmem_base + 320, tmem_base + 256 + u * 32 + k * 8, make_smem_desc(sk + (4 * u + k) * 2048, 8192, 1024), IDESC_DQ,
-                      (j > 0 || u > 0 || k > 0) ? 1u : 0u);
-            umma_commit(&ds_free[u]);         // this unit's dS may be overwritten
+          if (!mbar_wait(p_full, (uint32_t)(tg & 1), abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
+          if (j == 0) {        // the previous item's dQ must have been read out before it is overwritten
+            if (!mbar_wait(dq_empty, (uint32_t)((il & 1) ^ 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
           }
-          if (ok) umma_commit(&kv_empty[stage]);      // both units done: the K/V stage is free
+          tc_fence_after();
+          const uint32_t sk = smem_u32(sKV + stage * 2 * AB_TILE);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_ts(tmem_base + 320, tmem_base + 256 + k * 8, make_smem_desc(sk + k * 2048, 8192, 1024), IDESC_DQ, (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&kv_empty[stage]);      // frees the K/V stage and tells the softmax groups that dS may be overwritten
         }
         if (ok) umma_commit(dq_full);
       }
@@ -241,7 +222,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;             // query row within the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tS = tmem_base + w * 128 + lane_off, tdP = tS + 64;
+    const uint32_t tS = tmem_base + w * 64 + lane_off, tdP = tmem_base + 128 + w * 64 + lane_off;
     const uint32_t tdS = tmem_base + 256 + w * 32 + lane_off, tDQ = tmem_base + 320 + w * 32 + lane_off;
     long long tg = 0;
     int il = 0;
@@ -276,7 +257,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const float nlse2 = p.lse[sidx];         // -(log2-domain log-sum-exp), as written by the forward
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nl2 = make_float2(nlse2, nlse2), nd2 = make_float2(-Dr, -Dr);
       for (int j = 0; j < it.n_kv; ++j, ++tg) {
-        if (!mbar_wait(&s_full[w], (uint32_t)(tg & 1), abort_flag, p.status, ST_WAIT_TMEM_FULL, j)) { ok = false; break; }
+        if (!mbar_wait(s_full, (uint32_t)(tg & 1), abort_flag, p.status, ST_WAIT_TMEM_FULL, j)) { ok = false; break; }
         tc_fence_after();
         uint32_t s[64], dp[64];
         PGB_TMEM_LD32(tS, (s));
@@ -285,7 +266,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         PGB_TMEM_LD32(tdP + 32, (dp + 32));
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(&s_free[w]);                   // this unit's score buffers may take the next tile
+        mbar_arrive(s_free);                       // the score buffers may take the next tile
         const bool diag = j == qt;
         const int kbase = w * 64;                           // key offset of this group's columns inside the tile
         uint32_t pk[32];
@@ -308,15 +289,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             pk[c >> 1] = pack_bf16x2(dd.x, dd.y);
           }
         }
-        if (tg > 0) {            // the dQ MMAs of the previous tile still read this unit's dS until their commit arrives
-          if (!mbar_wait(&ds_free[w], (uint32_t)((tg - 1) & 1), abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
+        if (tg > 0) {            // the dQ MMAs of the previous tile still read dS until their commit arrives
+          const long long pg = tg - 1;
+          if (!mbar_wait(&kv_empty[(int)(pg % DQ_STAGES)], (uint32_t)((pg / DQ_STAGES) & 1), abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
           tc_fence_after();
         }
         PGB_TMEM_ST16(tdS, (pk));
         PGB_TMEM_ST16(tdS + 16, (pk + 16));
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&p_full[w]);
+        mbar_arrive(p_full);
       }
       if (ok && mbar_wait(dq_full, (uint32_t)(il & 1), abort_flag, p.status, ST_WAIT_MISC, it.n_kv)) {
         tc_fence_after();
@@ -349,15 +331,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 // ------------------------------------------------------------------------------------------------------------------
 // Key-stationary kernel.  One item = a 128-key tile of one KV head; its units are the (128-row query tile, query head)
-// pairs that attend to it.  A unit is two halves of 64 query rows, one per softmax group, each with its own score buffers
-// and barriers: S^T_h = K Q_h^T and dP^T_h = V dO_h^T (128 x 64, N = 64 MMAs) land in TMEM, the group pulls them into
-// registers and releases the buffers at once (`s_free[h]`); P^T_h and dS^T_h go back to their own TMEM columns as bf16
-// and feed dV += P^T_h dO_h and dK += dS^T_h Q_h.  Nothing couples the two groups, and group 1 starts half a period late,
-// so that one group exponentiates while the other loads, stores and waits.  Two issuing threads (scores / gradients)
-// keep the tensor pipe fed.
-// TMEM: half h: S^T_h [128h, 128h+64) dP^T_h [128h+64, 128h+128); P^T_h [256+32h, ..+32) dS^T_h [320+32h, ..+32); dK [384,448) dV [448,512).
+// pairs that attend to it.  Per unit: S^T = K Q^T and dP^T = V dO^T (128 x 128 each, N = 128 MMAs) land in TMEM; the two
+// softmax groups each take 64 query columns, pull them into registers and release the score buffers at once
+// (`s_free`), so the next unit's scores are computed while this unit's probabilities are; P^T and dS^T go back to
+// their own TMEM columns as bf16 and feed dV += P^T dO and dK += dS^T Q.  Two issuing threads (scores / gradients) keep
+// the tensor pipe fed.  TMEM: S^T [0,128) dP^T [128,256) P^T [256,320) dS^T [320,384) dK [384,448) dV [448,512).
 constexpr int KV_STAGES = 4;
-constexpr long long KV_GROUP_OFFSET_CLK = 800;
 constexpr int KV_THREADS = 384;              // warpgroup 0: warp 0 TMA, warp 1 score MMAs, warp 2 gradient MMAs, warp 3 idle; warpgroups 1, 2: softmax
 // one stage holds a 128-row Q tile, a 128-row dO tile, lse[128] and D[128]
 constexpr int KV_SMEM = 2 * AB_TILE + KV_STAGES * (2 * AB_TILE) + KV_STAGES * 1024 + 1024 + 256;
@@ -375,11 +354,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   uint64_t* kv_full = bars;
   uint64_t* st_full = bars + 1;
   uint64_t* st_empty = st_full + KV_STAGES;
-  uint64_t* s_full = st_empty + KV_STAGES;    // 2: one per half
-  uint64_t* s_free = s_full + 2;              // 2
-  uint64_t* p_full = s_free + 2;              // 2
-  uint64_t* pt_free = p_full + 2;             // 2: the gradient MMAs of a half have consumed its P^T / dS^T
-  uint64_t* acc_full = pt_free + 2;           // 1
+  uint64_t* s_full = st_empty + KV_STAGES;    // 1
+  uint64_t* s_free = s_full + 1;              // 1
+  uint64_t* p_full = s_free + 1;              // 1
+  uint64_t* acc_full = p_full + 1;            // 1
   uint64_t* acc_empty = acc_full + 1;         // 1
   uint64_t* kv_empty = acc_empty + 1;         // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_empty + 1);
@@ -405,12 +383,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(&st_full[s], 1);
       mbar_init(&st_empty[s], 1);
     }
-    for (int h = 0; h < 2; ++h) {
-      mbar_init(&s_full[h], 1);
-      mbar_init(&s_free[h], 128);
-      mbar_init(&p_full[h], 128);
-      mbar_init(&pt_free[h], 1);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 256);
+    mbar_init(p_full, 256);
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 256);
     mbar_init(kv_empty, 1);
@@ -471,7 +446,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   } else if (warp == 1) {
     // scores: S^T(u) and dP^T(u) as soon as the previous unit's scores have been pulled into registers
     if (lane == 0) {
-      constexpr uint32_t IDESC_T = make_idesc_bf16(128, 64, 0, 0);     // K Q_h^T and V dO_h^T
+      constexpr uint32_t IDESC_T = make_idesc_bf16(128, 128, 0, 0);    // K Q^T and V dO^T
       const uint32_t sk = smem_u32(sK), sv = smem_u32(sV);
       bool ok = true;
       uint32_t item_par = 0;
@@ -482,24 +457,16 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         for (int u = 0; u < it.nu && ok; ++u) {
           const long long ug = ubase + u;
           const int stage = (int)(ug % KV_STAGES);
+          if (ug > 0 && !mbar_wait(s_free, (uint32_t)((ug - 1) & 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, u)) { ok = false; break; }
           if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
+          tc_fence_after();
           const uint32_t sq = smem_u32(sQD + stage * 2 * AB_TILE), sdo = sq + AB_TILE;
-          for (int h = 0; h < 2 && ok; ++h) {
-            if (ug > 0 && !mbar_wait(&s_free[h], (uint32_t)((ug - 1) & 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, u)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t th = tmem_base + h * 128, qh = h * 8192;        // query rows 64h.. of the tile
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_ss(th, make_smem_desc(sk + k * 32, 16, 1024), make_smem_desc(sq + qh + k * 32, 16, 1024), IDESC_T, k > 0);
+          for (int k = 0; k < 4; ++k) umma_ss(tmem_base, make_smem_desc(sk + k * 32, 16, 1024), make_smem_desc(sq + k * 32, 16, 1024), IDESC_T, k > 0);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_ss(th + 64, make_smem_desc(sv + k * 32, 16, 1024), make_smem_desc(sdo + qh + k * 32, 16, 1024), IDESC_T, k > 0);
-            umma_commit(&s_full[h]);
-            if (ug == 0 && h == 0) {          // once per CTA: put group 1 half a period behind group 0
-              const long long t0 = clock64();
-              while (clock64() - t0 < KV_GROUP_OFFSET_CLK) {}
-            }
-          }
+          for (int k = 0; k < 4; ++k)
+            umma_ss(tmem_base + 128, make_smem_desc(sv + k * 32, 16, 1024), make_smem_desc(sdo + k * 32, 16, 1024), IDESC_T, k > 0);
+          umma_commit(s_full);
         }
         ubase += it.nu;
       }
@@ -517,25 +484,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           const long long ug = ubase + u;
           const int stage = (int)(ug % KV_STAGES);
           if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
-          const uint32_t sq = smem_u32(sQD + stage * 2 * AB_TILE), sdo = sq + AB_TILE;
-          for (int h = 0; h < 2 && ok; ++h) {
-            if (!mbar_wait(&p_full[h], (uint32_t)(ug & 1), abort_flag, p.status, ST_WAIT_MISC, u)) { ok = false; break; }
-            if (u == 0 && h == 0) {          // the previous item's dK/dV must have been read out before they are overwritten
-              if (!mbar_wait(acc_empty, item_par ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
-            }
-            tc_fence_after();
-            const uint32_t first = (u > 0 || h > 0) ? 1u : 0u;
-#pragma unroll
-            for (int k = 0; k < 4; ++k)   // dV += P^T_h dO_h
-              umma_ts(tmem_base + 448, tmem_base + 256 + h * 32 + k * 8, make_smem_desc(sdo + (4 * h + k) * 2048, 8192, 1024), IDESC_A,
-                      (k > 0) ? 1u : first);
-#pragma unroll
-            for (int k = 0; k < 4; ++k)   // dK += dS^T_h Q_h
-              umma_ts(tmem_base + 384, tmem_base + 320 + h * 32 + k * 8, make_smem_desc(sq + (4 * h + k) * 2048, 8192, 1024), IDESC_A,
-                      (k > 0) ? 1u : first);
-            umma_commit(&pt_free[h]);         // this half's P^T / dS^T may be overwritten
+          if (!mbar_wait(p_full, (uint32_t)(ug & 1), abort_flag, p.status, ST_WAIT_MISC, u)) { ok = false; break; }
+          if (u == 0) {          // the previous item's dK/dV must have been read out before they are overwritten
+            if (!mbar_wait(acc_empty, item_par ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, item)) { ok = false; break; }
           }
-          if (ok) umma_commit(&st_empty[stage]);      // both halves done: the Q/dO stage is free
+          tc_fence_after();
+          const uint32_t sq = smem_u32(sQD + stage * 2 * AB_TILE), sdo = sq + AB_TILE;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)   // dV += P^T dO
+            umma_ts(tmem_base + 448, tmem_base + 256 + k * 8, make_smem_desc(sdo + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)   // dK += dS^T Q
+            umma_ts(tmem_base + 384, tmem_base + 320 + k * 8, make_smem_desc(sq + k * 2048, 8192, 1024), IDESC_A, (u > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&st_empty[stage]);      // frees the Q/dO stage and tells the softmax groups that P^T / dS^T may be overwritten
         }
         if (ok) {
           umma_commit(acc_full);
@@ -551,7 +512,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int quarter = warp & 3;
     const int kk = quarter * 32 + lane;            // key row within the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tS = tmem_base + w * 128 + lane_off, tdP = tS + 64;
+    const uint32_t tS = tmem_base + w * 64 + lane_off, tdP = tmem_base + 128 + w * 64 + lane_off;
     const uint32_t tPt = tmem_base + 256 + w * 32 + lane_off, tdSt = tmem_base + 320 + w * 32 + lane_off;
     bool ok = true;
     uint32_t item_par = 0;
@@ -563,7 +524,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const long long ug = ubase + u;
         const int stage = (int)(ug % KV_STAGES);
         if (!mbar_wait(&st_full[stage], (uint32_t)((ug / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
-        if (!mbar_wait(&s_full[w], (uint32_t)(ug & 1), abort_flag, p.status, ST_WAIT_TMEM_FULL, u)) { ok = false; break; }
+        if (!mbar_wait(s_full, (uint32_t)(ug & 1), abort_flag, p.status, ST_WAIT_TMEM_FULL, u)) { ok = false; break; }
         tc_fence_after();
         int qi, head;
         unit_coords(it, u, qi, head);
@@ -574,7 +535,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         PGB_TMEM_LD32(tdP + 32, (dp + 32));
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(&s_free[w]);                   // this half's score buffers may take the next unit
+        mbar_arrive(s_free);                       // the score buffers may take the next unit
         const float* vl = sVec + stage * 256 + w * 64;
         const float* vd = sVec + stage * 256 + 128 + w * 64;
         const bool diag = qi == j;
@@ -604,8 +565,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
           }
         }
-        if (ug > 0) {            // the gradient MMAs of the previous unit still read this half's P^T / dS^T until their commit arrives
-          if (!mbar_wait(&pt_free[w], (uint32_t)((ug - 1) & 1), abort_flag, p.status, ST_WAIT_EMPTY, u)) { ok = false; break; }
+        if (ug > 0) {            // the gradient MMAs of the previous unit still read P^T / dS^T until their commit arrives
+          const long long pg = ug - 1;
+          if (!mbar_wait(&st_empty[(int)(pg % KV_STAGES)], (uint32_t)((pg / KV_STAGES) & 1), abort_flag, p.status, ST_WAIT_EMPTY, u)) { ok = false; break; }
           tc_fence_after();
         }
         PGB_TMEM_ST16(tPt, (pp));
@@ -614,7 +576,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         PGB_TMEM_ST16(tdSt + 16, (pd + 16));
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&p_full[w]);
+        mbar_arrive(p_full);
       }
       if (ok && mbar_wait(acc_full, item_par, abort_flag, p.status, ST_WAIT_MISC, nu)) {
         tc_fence_after();

@@ -26,6 +26,7 @@ Gradients of bf16 activations are bf16; weight gradients accumulate in fp32 acro
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -34,6 +35,7 @@ from ..ops import native as N
 from ..ops import reference as R
 from ..optim.muon import ns_coeff
 from ..spec import ModelSpec, RunSpec
+from ..utils.logging import nvtx_range
 from . import gpt
 
 BF = torch.bfloat16
@@ -92,6 +94,8 @@ class CudaEngine:
         self.adam_t = 0
         self.layer_flags = None          # set by the sharded optimizer: per-layer weight-ready counters
         self.layer_flag_value = 0
+        self.param_generation = 0        # bumped by every write to the fp32 master parameters
+        self.cast_generation = -1        # generation the bf16 compute copies were made from
         self.cast_weights()
 
     # ---- storage -----------------------------------------------------------------------------------------------
@@ -164,7 +168,13 @@ class CudaEngine:
     def _alloc_acts(self):
         dev, T, d, n = self.dev, self.T, self.d, self.n
 
+        poison = os.environ.get("PGB_POISON", "0") not in ("", "0")
+
         def buf(*shape, dtype=BF):
+            # debug aid: activations start as NaN, so a kernel that reads a buffer before its producer ran shows up as a
+            # NaN loss instead of silently using stale data (role of the reference's poison fill, pg-model/src/gpu.rs:637-733)
+            if poison and dtype in (BF, torch.float32):
+                return torch.full(shape, float("nan"), dtype=dtype, device=dev)
             return torch.empty(*shape, dtype=dtype, device=dev)
 
         m = self.m
@@ -222,6 +232,7 @@ class CudaEngine:
         With ``banks=False`` only the replicated tables are refreshed (the sharded optimizer pushes bank weights itself)."""
         C, p, n, d, kv = self.C, self.p, self.n, self.d, self.kv
         q = self.qat
+        self.cast_generation = self.param_generation
         if banks:
             for i in range(n):       # packed [q; k; v] rows per layer
                 C.cast_rows(p["qo_bank"][i], self.Wqkv[i, :d], None, 0, 1, q)
@@ -245,7 +256,14 @@ class CudaEngine:
                 C.cast_rows(p["ve_proj"], self.VP[li], self.ve_eff[li:li + 1], 0, 1, False)
 
     def params_changed(self):
+        self.param_generation += 1
         self.cast_weights()
+
+    def mark_params_dirty(self):
+        """Call after writing to ``self.p`` directly; the next `forward` refuses to run on the stale bf16 copies until
+        `cast_weights` (or `params_changed`) has refreshed them. Same role as the reference's BF16 freshness stamps
+        (``pg-model/src/gpu.rs:637-733``)."""
+        self.param_generation += 1
 
     # ---- attention -----------------------------------------------------------------------------------------------------
     def _attn_fwd(self, l, li):
@@ -292,6 +310,9 @@ class CudaEngine:
         ``gscale * dL/dlogits``. Per-token NLL lands in ``self.nll``; the sum is added to ``self.loss_sum``."""
         C, m, p = self.C, self.m, self.p
         d, kv, S = self.d, self.kv, self.S
+        if self.cast_generation != self.param_generation:
+            raise RuntimeError(f"stale bf16 weights: parameters are at generation {self.param_generation}, the compute copies at "
+                               f"{self.cast_generation}; call cast_weights() after changing parameters")
         if ids is not None:                       # otherwise self.ids / self.tgt were filled by `load_span`
             self.ids.copy_(ids.reshape(-1))
             if targets is not None and targets is not True:
@@ -467,13 +488,17 @@ class CudaEngine:
 
     def micro_step_span(self, span_u16: torch.Tensor, accum: int):
         self.load_span(span_u16)
-        self.forward(None, True, gscale=1.0 / (self.T * accum), want_grad=True)
-        self.backward()
+        with nvtx_range("forward"):
+            self.forward(None, True, gscale=1.0 / (self.T * accum), want_grad=True)
+        with nvtx_range("backward"):
+            self.backward()
 
     def micro_step(self, ids, targets, accum: int):
         """One micro-batch forward+backward; gradients are scaled so that `accum` of them sum to the mean."""
-        self.forward(ids, targets, gscale=1.0 / (self.T * accum), want_grad=True)
-        self.backward()
+        with nvtx_range("forward"):
+            self.forward(ids, targets, gscale=1.0 / (self.T * accum), want_grad=True)
+        with nvtx_range("backward"):
+            self.backward()
 
     def set_hp(self, lr_scale: float, momentum: float):
         self.adam_t += 1
@@ -536,6 +561,7 @@ class CudaEngine:
             X = self.newton_schulz(k)
             scale = max(1.0, self.p[k].shape[-2] / self.p[k].shape[-1]) ** 0.5
             C.muon_apply(self.p[k].view(-1), X.view(-1), self.ema[k].view(-1) if self.ema else None, self.hp, t.matrix_lr, t.muon_wd, scale, decay)
+        self.param_generation += 1
         self.cast_weights()
 
     def export_params(self, ema: bool = False) -> Dict[str, torch.Tensor]:
@@ -556,6 +582,7 @@ class CudaEngine:
     def load_params(self, params: Dict[str, torch.Tensor]):
         for k, v in params.items():
             self.p[k].copy_(v.to(self.dev, torch.float32))
+        self.param_generation += 1
         self.cast_weights()
 
 
@@ -685,11 +712,12 @@ class EngineBackend:
                 self._graphed_micro_step(sp, len(dev_spans))
             else:
                 e.micro_step_span(sp, len(dev_spans))
-        if self.dist is not None:
-            self.dist.step()
-        else:
-            e.clip()
-            e.optimizer_step()
+        with nvtx_range("optimizer"):
+            if self.dist is not None:
+                self.dist.step()
+            else:
+                e.clip()
+                e.optimizer_step()
         if read_loss:
             return float(e.loss_sum[0]) / (e.T * len(dev_spans))
         return None

@@ -98,3 +98,25 @@ class CudaStageTimers:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             m = dict(zip(keys, t.tolist()))
         return m
+
+
+_NVTX = os.environ.get("PGB_NVTX", "0") not in ("", "0")
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """NVTX range around a stage (forward, backward, optimizer, collectives) so that a timeline profiler groups the
+    launches of one stage. Off unless ``PGB_NVTX=1`` (a push/pop per stage per micro-batch is otherwise wasted work);
+    a no-op when CUDA is not available."""
+    if not _NVTX:
+        yield
+        return
+    import torch
+    if not torch.cuda.is_available():
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()

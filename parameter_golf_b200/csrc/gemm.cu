@@ -548,9 +548,22 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   int splits = a.splits;
   if (splits <= 0) {
     splits = 1;
-    if (a.epi == EPI_F32_ATOMIC) {        // fill the machine when the output is small and K is long
-      const int base = p.tiles_m * p.tiles_n * a.batch;
-      splits = std::max(1, std::min(p.kb_total / 8, (2 * num_sms() + base - 1) / base));
+    if (a.epi == EPI_F32_ATOMIC) {
+      // Fill the machine when the output is small and K is long, in whole waves: with `base` output tiles, base * splits
+      // work items run in ceil(items / SMs) rounds, so 2 * SMs + a few items would cost a third round for nothing.
+      // Two rounds are preferred (the second tile's main loop hides the first one's epilogue), then one, then three.
+      const int base = p.tiles_m * p.tiles_n * a.batch, sms = num_sms();
+      const int max_splits = std::max(1, p.kb_total / 8);
+      double best_eff = 0.0;
+      for (int waves : {2, 1, 3}) {
+        const int sp = std::min(max_splits, std::max(1, waves * sms / base));
+        const int items = base * sp;
+        const double eff = (double)items / ((double)((items + sms - 1) / sms) * sms);
+        if (eff > best_eff + 0.02) {
+          best_eff = eff;
+          splits = sp;
+        }
+      }
     }
   }
   if (splits > 1 && a.epi != EPI_F32_ATOMIC) throw std::runtime_error("gemm: split-K needs the atomic fp32 epilogue");

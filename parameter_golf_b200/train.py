@@ -15,6 +15,7 @@ record_shaped_proxy|record] [--env] [key=value …]`` and ``… train sweep --fa
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import math
 import os
@@ -259,7 +260,13 @@ class VariantRunner:
         train_ms = 0.0
         step = step0
         t_start = time.perf_counter()
+        health = None
+        if t.world_size > 1:
+            from .parallel.health import RankHealth
+            health = RankHealth.from_process_group(timeout_s=float(os.environ.get("PGB_HEALTH_TIMEOUT_S", "120")))
         while step < max_steps:
+            if health is not None:
+                health.check()        # a peer that failed or went silent ends this rank on the host, before its next launch
             elapsed = train_ms + 1000.0 * (time.perf_counter() - t_start)
             if max_ms is not None and elapsed >= max_ms:
                 res.stopped_early = True
@@ -289,9 +296,11 @@ class VariantRunner:
                     for _ in range(accum):
                         x, y = loader.next_batch(tokens_per_step, t.seq_len, accum)
                         batches.append((torch.from_numpy(x), torch.from_numpy(y)))
-            with timers.time("train_step"):
+            with timers.time("train_step"), (health.guard() if health is not None else contextlib.nullcontext()):
                 loss = backend.train_step_spans(spans, scale, mom, qat) if spans is not None else backend.train_step(batches, scale, mom, qat)
             step += 1
+            if health is not None:
+                health.beat(step)
             if step == step0 + 1:
                 res.train_loss_first = loss
             res.train_loss_last = loss

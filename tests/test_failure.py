@@ -97,3 +97,74 @@ def test_fingerprint_mismatch_blocks_resume_and_artifact_mismatch_blocks_load(tm
     blob = export_model(a, gpt.init_params(a.model, 0))
     with pytest.raises(ArtifactError, match="num_heads"):
         load_artifact(blob, b.validate())
+
+
+class _FakeStore:
+    def __init__(self):
+        self.d = {}
+
+    def set(self, k, v):
+        self.d[k] = v.encode() if isinstance(v, str) else v
+
+    def get(self, k):
+        return self.d[k]
+
+    def check(self, keys):
+        return all(k in self.d for k in keys)
+
+
+def test_rank_health_reports_failures_and_silent_peers():
+    from parameter_golf_b200.parallel.health import PeerFailure, RankHealth
+    store, now = _FakeStore(), [1000.0]
+    a = RankHealth(store, 0, 2, timeout_s=5.0, clock=lambda: now[0])
+    b = RankHealth(store, 1, 2, timeout_s=5.0, clock=lambda: now[0])
+    a.check()                                   # nobody has beaten yet: start-up is not policed
+    a.beat(1)
+    b.beat(1)
+    now[0] += 4.0
+    a.check()
+    now[0] += 2.0                               # rank 1 silent for 6 s > 5 s
+    with pytest.raises(PeerFailure, match="rank1 silent"):
+        a.check()
+    b.beat(2)
+    a.check()
+    with pytest.raises(ValueError):
+        with b.guard():
+            raise ValueError("shard 7 is truncated")
+    with pytest.raises(PeerFailure, match="rank1: ValueError: shard 7 is truncated"):
+        a.check()
+
+
+def test_training_ranks_stop_on_the_host_when_a_peer_fails_between_steps(tmp_path):
+    """Two gloo ranks run the real training loop on the CPU backend; rank 1's backend raises in its third step. Rank 0 must
+    end with PeerFailure before its next step instead of waiting in a collective."""
+    out = _run(tmp_path, """
+        dist.init_process_group('gloo', timeout=datetime.timedelta(seconds=30))
+        rank = dist.get_rank()
+        from parameter_golf_b200.spec import family_preset
+        from parameter_golf_b200.train import VariantRunner, OracleBackend
+        from parameter_golf_b200.parallel.health import PeerFailure
+        spec = family_preset('tiny_cpu')
+        spec.train.world_size, spec.train.rank, spec.train.backend = 2, rank, 'cuda_distributed'   # the factory below supplies a CPU backend
+        spec.train.total_iterations, spec.train.max_wallclock_seconds, spec.mode = 6, 0.0, 'proxy'
+
+        class Flaky(OracleBackend):
+            calls = 0
+            def train_step(self, *a, **k):
+                Flaky.calls += 1
+                if rank == 1 and Flaky.calls == 3:
+                    raise RuntimeError('injected: device lost')
+                time.sleep(0.2)
+                return super().train_step(*a, **k)
+
+        try:
+            VariantRunner(spec, backend_factory=lambda s, p: Flaky(s, p)).run('proxy')
+            print('RANK', rank, 'FINISHED', flush=True)
+        except PeerFailure as e:
+            print('RANK', rank, 'PEER_FAILURE', e, 'after', Flaky.calls, 'steps', flush=True)
+        except RuntimeError as e:
+            print('RANK', rank, 'RAISED', e, flush=True)
+        """, port=29695, timeout=240)
+    assert "RANK 1 RAISED injected: device lost" in out.stdout, (out.stdout, out.stderr[-2000:])
+    assert "RANK 0 PEER_FAILURE rank1: RuntimeError: injected: device lost" in out.stdout, (out.stdout, out.stderr[-2000:])
+    assert "RANK 0 FINISHED" not in out.stdout

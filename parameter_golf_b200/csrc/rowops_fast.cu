@@ -215,14 +215,19 @@ __device__ __forceinline__ void rope8(V8& n, int sub, int hp, int pos, int half,
   const bool in_rope = sub < 2 * hp;
   const bool first = sub < hp;
   const int partner = in_rope ? (first ? lane + hp : lane - hp) : lane;
-  const int ibase = pos * half + (first ? sub : sub - hp) * 8;
+  const int ibase = pos * half + (first ? sub : sub - hp) * 8;          // half is a multiple of 8: 32-byte aligned table rows
+  float cs[8], sn[8];
+  if (in_rope) {
+    const float4 c0 = __ldg(reinterpret_cast<const float4*>(cosT + ibase)), c1 = __ldg(reinterpret_cast<const float4*>(cosT + ibase) + 1);
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sinT + ibase)), s1 = __ldg(reinterpret_cast<const float4*>(sinT + ibase) + 1);
+    cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+  }
+  const float sgn = (first != inverse) ? 1.f : -1.f;       // first half: +sin (forward) ; second half: -sin; the inverse rotation flips both
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     const float other = __shfl_sync(0xffffffffu, n.v[e], partner);
-    if (in_rope) {
-      const float cs = cosT[ibase + e], sn = inverse ? -sinT[ibase + e] : sinT[ibase + e];
-      n.v[e] = first ? n.v[e] * cs + other * sn : -other * sn + n.v[e] * cs;
-    }
+    if (in_rope) n.v[e] = n.v[e] * cs[e] + sgn * other * sn[e];
   }
 }
 
@@ -287,21 +292,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd64_kernel(const __nv_bflo
     const float ms = ss / 64.f + eps;
     const float inv = rsqrtf(ms);
     const float g = (head < H && gain) ? gain[head] : 1.f;
-    if (d_gain != nullptr) {                       // warp-uniform
-      V8 r;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) r.v[e] = x.v[e] * inv;
-      if (hp > 0) rope8(r, sub, hp, pos, half, cosT, sinT, false);
-      float acc = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc += dy.v[e] * r.v[e];
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (live && sub == 0 && head < H) atomicAdd(&sg[head], acc);
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) dy.v[e] *= g;
+    // post = g * R(inv * x) with R the rotation: d_gain = <dy, R(inv x)> = inv * <R^T dy, x>, and the same inner product
+    // (times g) is the norm backward's, so one inverse rotation and one reduction serve both
     if (hp > 0) rope8(dy, sub, hp, pos, half, cosT, sinT, true);
     float dot = 0.f;
 #pragma unroll
@@ -309,10 +301,11 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd64_kernel(const __nv_bflo
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     dot += __shfl_xor_sync(0xffffffffu, dot, 2);
     dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-    const float k2 = dot / (ms * 64.f);
+    if (d_gain != nullptr && live && sub == 0 && head < H) atomicAdd(&sg[head], dot * inv);
+    const float k2 = g * dot / (ms * 64.f), gi = g * inv;
     V8 o;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o.v[e] = inv * (dy.v[e] - x.v[e] * k2);
+    for (int e = 0; e < 8; ++e) o.v[e] = gi * dy.v[e] - inv * x.v[e] * k2;
     if (live) stv(d_pre + off, o);
   }
   __syncthreads();

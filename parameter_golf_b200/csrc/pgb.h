@@ -83,6 +83,10 @@ void qk_norm_rope_fwd64(const void* src, void* dst, const float* cosT, const flo
 void qk_norm_rope_bwd64(const void* d_post, const void* pre, void* d_pre, const float* cosT, const float* sinT, const float* gain, float* d_gain,
                         int rows, int ld, int H, int Hkv, int rope_dims, int seq_len, float eps, cudaStream_t st);
 
+void xsa_fwd64(const void* y, const void* v, void* z, int rows, int Hkv, int group, int ld_y, int ld_v, float eps, cudaStream_t st);
+void xsa_bwd64(const void* dz, const void* y, const void* v, void* dy, void* dv, int accumulate_dv, int rows, int Hkv, int group, int ld_y, int ld_v,
+               int ld_dv, float eps, cudaStream_t st);
+
 // ---- optimizer / weight preparation (optim.cu) --------------------------------------------------------------------------
 // hp: device fp32[8] = {lr_scale, muon_momentum, adam_bias_corr1, adam_bias_corr2, grad_scale, ...}
 void cast_rows(const float* src, void* dst, const float* rowscale, int scale_stride, int scale_mod, int rows, int cols, long long ld_dst, int qat,

@@ -334,4 +334,106 @@ void qk_norm_rope_bwd64(const void* d_post, const void* pre, void* d_pre, const 
                                                   d_gain, nvec, ld, H, Hkv, rope_dims, seq_len, eps);
 }
 
+// ---- XSA forward / backward, head_dim 64, 8 lanes per (token, KV head) ------------------------------------------------------
+// z_h = y_h - (<y_h, v> / (|v|^2 + eps)) v for the `group` query heads h that share one value head. A lane holds 8 of the 64
+// features (one 16-byte load, 128 contiguous bytes per head vector), the three inner products are 8-lane shuffles, and no
+// thread keeps a whole head vector in registers (the one-thread-per-vector form needed ~170 registers and ran at 3 CTAs/SM).
+__device__ __forceinline__ float sum8(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  return x;
+}
+
+__global__ void __launch_bounds__(256) xsa_fwd64_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ v,
+                                                        __nv_bfloat16* __restrict__ z, int nvec, int Hkv, int group, int ld_y, int ld_v, float eps) {
+  const int sub = threadIdx.x & 7;
+  const int vstride = (int)gridDim.x * (blockDim.x / 8);
+  const int nvec_pad = (nvec + 3) / 4 * 4;                 // whole warps stay converged for the shuffles
+  for (int i = (int)blockIdx.x * (blockDim.x / 8) + (threadIdx.x >> 3); i < nvec_pad; i += vstride) {
+    const bool live = i < nvec;
+    const int ii = live ? i : nvec - 1;
+    const int row = (int)((unsigned)ii / (unsigned)Hkv), kh = ii - row * Hkv;
+    const V8 vv = ldv(v + (size_t)row * ld_v + kh * 64 + sub * 8);
+    float n = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) n += vv.v[e] * vv.v[e];
+    n = sum8(n) + eps;
+    for (int g = 0; g < group; ++g) {
+      const size_t off = (size_t)row * ld_y + (kh * group + g) * 64 + sub * 8;
+      V8 a = ldv(y + off);
+      float dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot += a.v[e] * vv.v[e];
+      const float coef = sum8(dot) / n;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a.v[e] -= coef * vv.v[e];
+      if (live) stv(z + off, a);
+    }
+  }
+}
+
+// dy_h = dz_h - (<dz_h,v>/n) v ;  dv (+)= sum_h [ -c_h dz_h - (<dz_h,v>/n) y_h + 2 c_h (<dz_h,v>/n) v ],  c_h = <y_h,v>/n
+__global__ void __launch_bounds__(256) xsa_bwd64_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ y,
+                                                        const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ dy,
+                                                        __nv_bfloat16* __restrict__ dv, int accumulate_dv, int nvec, int Hkv, int group, int ld_y,
+                                                        int ld_v, int ld_dv, float eps) {
+  const int sub = threadIdx.x & 7;
+  const int vstride = (int)gridDim.x * (blockDim.x / 8);
+  const int nvec_pad = (nvec + 3) / 4 * 4;
+  for (int i = (int)blockIdx.x * (blockDim.x / 8) + (threadIdx.x >> 3); i < nvec_pad; i += vstride) {
+    const bool live = i < nvec;
+    const int ii = live ? i : nvec - 1;
+    const int row = (int)((unsigned)ii / (unsigned)Hkv), kh = ii - row * Hkv;
+    const V8 vv = ldv(v + (size_t)row * ld_v + kh * 64 + sub * 8);
+    __nv_bfloat16* dvp = dv + (size_t)row * ld_dv + kh * 64 + sub * 8;
+    V8 acc;
+    if (accumulate_dv) {
+      acc = ldv(dvp);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc.v[e] = 0.f;
+    }
+    float n = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) n += vv.v[e] * vv.v[e];
+    n = sum8(n) + eps;
+    for (int g = 0; g < group; ++g) {
+      const size_t off = (size_t)row * ld_y + (kh * group + g) * 64 + sub * 8;
+      const V8 a = ldv(y + off), b = ldv(dz + off);
+      float yv = 0.f, gv = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        yv += a.v[e] * vv.v[e];
+        gv += b.v[e] * vv.v[e];
+      }
+      const float ch = sum8(yv) / n, gn = sum8(gv) / n;
+      V8 o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        o.v[e] = b.v[e] - gn * vv.v[e];
+        acc.v[e] += -ch * b.v[e] - gn * a.v[e] + 2.f * ch * gn * vv.v[e];
+      }
+      if (live) stv(dy + off, o);
+    }
+    if (live) stv(dvp, acc);
+  }
+}
+
+void xsa_fwd64(const void* y, const void* v, void* z, int rows, int Hkv, int group, int ld_y, int ld_v, float eps, cudaStream_t st) {
+  if ((long long)rows * Hkv > 0x7fffff00ll) throw std::runtime_error("xsa: too many head vectors for 32-bit indexing");
+  const int nvec = rows * Hkv;
+  const int grid = std::max(1, std::min((nvec + 31) / 32, 148 * 16));
+  xsa_fwd64_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)v, (__nv_bfloat16*)z, nvec, Hkv, group, ld_y, ld_v, eps);
+}
+
+void xsa_bwd64(const void* dz, const void* y, const void* v, void* dy, void* dv, int accumulate_dv, int rows, int Hkv, int group, int ld_y, int ld_v,
+               int ld_dv, float eps, cudaStream_t st) {
+  if ((long long)rows * Hkv > 0x7fffff00ll) throw std::runtime_error("xsa: too many head vectors for 32-bit indexing");
+  const int nvec = rows * Hkv;
+  const int grid = std::max(1, std::min((nvec + 31) / 32, 148 * 16));
+  xsa_bwd64_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dz, (const __nv_bfloat16*)y, (const __nv_bfloat16*)v, (__nv_bfloat16*)dy,
+                                         (__nv_bfloat16*)dv, accumulate_dv, nvec, Hkv, group, ld_y, ld_v, ld_dv, eps);
+}
+
 }  // namespace pgb

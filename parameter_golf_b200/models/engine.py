@@ -51,8 +51,12 @@ def _unsupported(m: ModelSpec) -> Optional[str]:
 
 
 class CudaEngine:
-    def __init__(self, spec: RunSpec, params: Dict[str, torch.Tensor], device, micro_batch: int, seq_len: int, train: bool = True,
-                 attention: str = "native"):
+    def __init__(self, spec: RunSpec, params: Optional[Dict[str, torch.Tensor]], device, micro_batch: int, seq_len: int, train: bool = True,
+                 attention: str = "native", share: Optional["CudaEngine"] = None):
+        """``share``: another engine of the same spec and device whose parameters, gradients, optimizer state and bf16 weight
+        copies this one aliases (everything that does not depend on the batch shape); only the activation buffers are new.
+        Evaluation and test-time training switch between a scoring shape and a training shape many times per second, and
+        rebuilding an engine per switch (parameters through the host included) used to dominate their time."""
         bad = _unsupported(spec.model)
         if bad:
             raise NotImplementedError(f"the CUDA engine does not cover {bad}; use the cpu backend for this variant")
@@ -81,9 +85,16 @@ class CudaEngine:
             self.gates.append(("attn_gate_weight", "attn_gate_bias", 1.0, 2.0))
         if m.sparse_attn_gate.enabled:
             self.gates.append(("sparse_attn_gate_weight", None, float(m.sparse_attn_gate.scale), 1.0))
-        self.unet = m.skip_topology == "unet" and "skip_weights" in params
+        self.unet = m.skip_topology == "unet" and "skip_weights" in (share.p if share is not None else params)
         self.eps = R.RMS_EPS
-        self._alloc_params(params)
+        if share is not None:
+            assert share.dev == self.dev and share.train == train and share.m == self.m
+            for name in ("p", "g", "groups", "Wqkv", "Wo", "Wup", "Wd", "Wo_u", "Wd_u", "E", "LM", "BE", "BP", "VE", "VP", "ve_eff", "ema", "mom",
+                         "ns", "Gd", "Go", "Gbp", "Gvp"):
+                if hasattr(share, name):
+                    setattr(self, name, getattr(share, name))
+        else:
+            self._alloc_params(params)
         self._alloc_acts()
         self.hp_host = torch.zeros(8, dtype=torch.float32).pin_memory()
         self.hp = torch.zeros(8, dtype=torch.float32, device=self.dev)
@@ -96,7 +107,12 @@ class CudaEngine:
         self.layer_flag_value = 0
         self.param_generation = 0        # bumped by every write to the fp32 master parameters
         self.cast_generation = -1        # generation the bf16 compute copies were made from
-        self.cast_weights()
+        if share is not None:            # the shared bf16 copies are already current
+            self.hp, self.hp_host, self.stats = share.hp, share.hp_host, share.stats
+            self.adam_t, self.qat = share.adam_t, share.qat
+            self.param_generation, self.cast_generation = share.param_generation, share.cast_generation
+        else:
+            self.cast_weights()
 
     # ---- storage -----------------------------------------------------------------------------------------------
     def _alloc_params(self, params):
@@ -598,12 +614,21 @@ class EngineRunner:
         self.train = train
         self.lora = None
 
+    MAX_LIVE_SHAPES = 3
+
     def _engine(self, B: int, S: int) -> CudaEngine:
+        """Engine for a batch shape. All shapes of one runner alias the first engine's parameters and bf16 weights
+        (`CudaEngine(share=...)`), so switching between the scoring and the training shape costs nothing; the least recently
+        created activation set is dropped beyond `MAX_LIVE_SHAPES`."""
         key = (B, S)
         if key not in self.engines:
-            src = next(iter(self.engines.values())).export_params() if self.engines else self._params
-            self.engines.clear()                       # one live shape at a time keeps memory bounded
-            self.engines[key] = CudaEngine(self.spec, src, self.device, B, S, train=self.train)
+            if not self.engines:
+                self.engines[key] = CudaEngine(self.spec, self._params, self.device, B, S, train=self.train)
+            else:
+                first = next(iter(self.engines.values()))
+                if len(self.engines) >= self.MAX_LIVE_SHAPES:
+                    del self.engines[list(self.engines)[1]]           # never the first: it owns nothing the others lack, but keeps order simple
+                self.engines[key] = CudaEngine(self.spec, None, self.device, B, S, train=self.train, share=first)
         return self.engines[key]
 
     @property
@@ -613,8 +638,11 @@ class EngineRunner:
         return self._params
 
     def params_changed(self):
-        for e in self.engines.values():
-            e.cast_weights()
+        es = list(self.engines.values())
+        if es:
+            es[0].cast_weights()                 # every shape aliases the same bf16 weight buffers
+            for e in es[1:]:
+                e.cast_generation = e.param_generation
 
     @torch.no_grad()
     def nll(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

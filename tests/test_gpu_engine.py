@@ -182,3 +182,26 @@ def test_bounded_wait_times_out_and_reports():
     torch.cuda.synchronize()
     native.check_status()
     assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
+
+
+def test_runner_shapes_share_weights_and_see_updates():
+    """Two batch shapes of one runner alias the same parameters and bf16 weights: an in-place parameter change followed by
+    `params_changed` is seen by both, and no engine is rebuilt when the shape alternates."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import EngineRunner
+    spec = small_spec()
+    params = gpt.fill_deterministic(spec.model)
+    r = EngineRunner(spec, params, "cuda", train=True)
+    torch.manual_seed(4)
+    a_ids, a_tgt = torch.randint(0, 256, (3, 128)), torch.randint(0, 256, (3, 128))
+    b_ids, b_tgt = torch.randint(0, 256, (2, 128)), torch.randint(0, 256, (2, 128))
+    na0, nb0 = r.nll(a_ids, a_tgt), r.nll(b_ids, b_tgt)
+    ea, eb = r.engines[(3, 128)], r.engines[(2, 128)]
+    assert ea.p["tok_emb"].data_ptr() == eb.p["tok_emb"].data_ptr() and ea.Wqkv.data_ptr() == eb.Wqkv.data_ptr()
+    assert torch.equal(r.nll(a_ids, a_tgt), na0) and r.engines[(3, 128)] is ea          # alternating shapes rebuilds nothing
+    r.params["tok_emb"].mul_(1.5)
+    r.params_changed()
+    na1, nb1 = r.nll(a_ids, a_tgt), r.nll(b_ids, b_tgt)
+    assert (na1 - na0).abs().max() > 1e-3 and (nb1 - nb0).abs().max() > 1e-3
+    fresh = EngineRunner(spec, {k: v.clone() for k, v in r.params.items()}, "cuda", train=True)
+    assert torch.allclose(fresh.nll(b_ids, b_tgt), nb1, atol=1e-5)

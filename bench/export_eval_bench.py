@@ -99,7 +99,12 @@ def main():
     if a.ttt_chunks > 0:
         n_tok = a.ttt_chunks * spec.eval.chunk_tokens
         t0 = tick()
-        loss, bpb = eval_score_first_ttt(runner, val[: n_tok + 1], m, spec.eval, luts, rank, world, "full_sgd", dev, (print if rank == 0 else (lambda *x: None)))
+        par = None
+        if world > 1:          # packed gradient all-reduce on the peer-memory kernels instead of NCCL
+            from parameter_golf_b200.parallel.peer_allreduce import PeerAllReduce
+            par = PeerAllReduce(gpt.count_params(m) + 64)
+        loss, bpb = eval_score_first_ttt(runner, val[: n_tok + 1], m, spec.eval, luts, rank, world, "full_sgd", dev, (print if rank == 0 else (lambda *x: None)),
+                                         all_reduce=(par.mean_ if par is not None else None))
         t1 = tick()
         per = (t1 - t0) / a.ttt_chunks
         out.update({"ttt_chunks": a.ttt_chunks, "ttt_s_per_chunk": round(per, 3), "ttt_1893_chunks_projection_s": round(per * 1893, 1), "ttt_val_loss": loss})

@@ -83,7 +83,12 @@ def main(argv=None) -> int:
     ab = spec.eval.adaptation_backend
     if spec.eval.legal_score_first and ab in ("full_sgd", "cpu_q_only", "lact"):
         mode = {"full_sgd": "full_sgd", "cpu_q_only": "q_only", "lact": "lact"}[ab]
-        loss, bpb = eval_score_first_ttt(runner, val, m, spec.eval, luts, rank, world, mode, a.device, print)
+        hook = None
+        if world > 1 and a.device != "cpu":       # packed gradient all-reduce on the peer-memory kernels instead of NCCL
+            from .models import gpt
+            from .parallel.peer_allreduce import PeerAllReduce
+            hook = PeerAllReduce(gpt.count_params(m) + 64).mean_
+        loss, bpb = eval_score_first_ttt(runner, val, m, spec.eval, luts, rank, world, mode, a.device, print, all_reduce=hook)
         kind = f"score_first_{mode}"
     elif spec.eval.legal_score_first and ab == "gpu_lora_phased":
         loss, bpb = eval_lora_phased_ttt(runner, val, m, spec.eval, luts, rank, world, a.device, print)

@@ -69,7 +69,22 @@ def main():
         torch.cuda.synchronize()
         native.check_status()
         out["twoshot_err"] = float((x - ref).abs().max())
+        # the packaged form used by distributed test-time training, odd length, twice in a row
+        from parameter_golf_b200.parallel.peer_allreduce import PeerAllReduce
+        par = PeerAllReduce(100_003)
+        errs = []
+        for rep in range(2):
+            torch.manual_seed(100 * rep + rank)
+            y = torch.randn(100_003 - 7 * rep, device="cuda")
+            yr = y.clone()
+            dist.all_reduce(yr)
+            par.mean_(y)
+            torch.cuda.synchronize()
+            native.check_status()
+            errs.append(float((y - yr / world).abs().max()))
+        out["packaged_err"] = max(errs)
         dist.barrier()
+        par.close()
         for bb in (buf, sig, val):
             bb.close()
     else:

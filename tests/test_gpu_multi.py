@@ -29,7 +29,7 @@ def run_workers(mode, nproc=2, port=29731):
 def test_peer_collectives_match_nccl():
     res = run_workers("collectives", port=29731)
     for r in res.values():
-        assert r["allreduce_err"] < 1e-5 and r["twoshot_err"] < 1e-5 and r["sumsq_rel"] < 1e-5, r
+        assert r["allreduce_err"] < 1e-5 and r["twoshot_err"] < 1e-5 and r["sumsq_rel"] < 1e-5 and r["packaged_err"] < 1e-5, r
 
 
 @pytest.mark.parametrize("mode,port", [("sharded", 29732), ("replicated", 29733)])

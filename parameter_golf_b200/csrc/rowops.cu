@@ -563,10 +563,14 @@ __global__ void xsa_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_
 // One warp per row; V <= 32*64.
 __global__ void __launch_bounds__(ROW_THREADS) softcap_ce_kernel(const __nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
                                                                  float* __restrict__ nll, __nv_bfloat16* __restrict__ dlogits,
-                                                                 float* __restrict__ loss_sum, int rows, int V, float cap, float gscale) {
+                                                                 float* __restrict__ loss_sum, int rows, int V, float cap, float gscale,
+                                                                 const float* __restrict__ tok_w, const float* __restrict__ w_total) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   __shared__ float wsum[ROW_WARPS];
   float local = 0.f;
+  // Per-token loss weights (complementary training): the loss becomes sum(w l) / sum(w). `loss_sum` and the gradient
+  // are rescaled by rows / sum(w) so that callers keep dividing by the row count.
+  const float wnorm = (tok_w && w_total) ? (float)rows / fmaxf(*w_total, 1e-12f) : 1.f;
   for (int row = blockIdx.x * ROW_WARPS + warp; row < rows; row += gridDim.x * ROW_WARPS) {
     const __nv_bfloat16* z = logits + (size_t)row * V;
     const int tgt = targets[row];
@@ -601,12 +605,14 @@ __global__ void __launch_bounds__(ROW_THREADS) softcap_ce_kernel(const __nv_bflo
     ct = warp_sum(ct);
     const float lse = mx + __logf(se);
     const float l = lse - ct;
+    const float tw = tok_w ? tok_w[row] * wnorm : 1.f;
     if (lane == 0) {
       if (nll) nll[row] = l;
-      local += l;
+      local += l * tw;
     }
     if (dlogits) {
       __nv_bfloat16* dz = dlogits + (size_t)row * V;
+      const float gs = gscale * tw;
 #pragma unroll
       for (int it = 0; it < 8; ++it) {
         const int col = lane * 8 + it * 256, cnt = it * 8;
@@ -616,7 +622,7 @@ __global__ void __launch_bounds__(ROW_THREADS) softcap_ce_kernel(const __nv_bflo
           for (int e = 0; e < 8; ++e) {
             const float p = __expf(c[cnt + e] - lse);
             const float th = c[cnt + e] / cap;
-            o.v[e] = gscale * (p - (col + e == tgt ? 1.f : 0.f)) * (1.f - th * th);
+            o.v[e] = gs * (p - (col + e == tgt ? 1.f : 0.f)) * (1.f - th * th);
           }
           st8(dz + col, o);
         }
@@ -631,6 +637,28 @@ __global__ void __launch_bounds__(ROW_THREADS) softcap_ce_kernel(const __nv_bflo
       for (int w = 0; w < ROW_WARPS; ++w) s += wsum[w];
       atomicAdd(loss_sum, s);
     }
+  }
+}
+
+// Weight of every (previous token, target) pair from a [V, V] table, and the sum of the weights (complementary training,
+// parameter-golf-rs/crates/pg-kernels/src/complementary.rs:204-224). `w_total` must be zero on entry.
+__global__ void __launch_bounds__(256) pair_weights_kernel(const int* __restrict__ prev, const int* __restrict__ curr, const float* __restrict__ table,
+                                                           float* __restrict__ w, float* __restrict__ w_total, int rows, int V) {
+  __shared__ float part[8];
+  float local = 0.f;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x) {
+    const int a = prev[i], b = curr[i];
+    const float x = ((unsigned)a < (unsigned)V && (unsigned)b < (unsigned)V) ? __ldg(table + (size_t)a * V + b) : 1.f;
+    w[i] = x;
+    local += x;
+  }
+  local = warp_sum(local);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int k = 0; k < 8; ++k) s += part[k];
+    atomicAdd(w_total, s);
   }
 }
 
@@ -796,10 +824,16 @@ void xsa_bwd(const void* dz, const void* y, const void* v, void* dy, void* dv, i
 }
 
 void softcap_ce(const void* logits, const int* targets, float* nll, void* dlogits, float* loss_sum, int rows, int V, float cap, float gscale,
-                cudaStream_t st) {
+                cudaStream_t st, const float* tok_w, const float* w_total) {
   if (V % 8 || V > 2048) throw std::runtime_error("vocab must be a multiple of 8 and <= 2048 for the fused CE kernel");
   softcap_ce_kernel<<<row_grid(rows), ROW_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets, nll, (__nv_bfloat16*)dlogits, loss_sum, rows, V,
-                                                            cap, gscale);
+                                                            cap, gscale, tok_w, w_total);
+}
+
+void pair_weights(const int* prev, const int* curr, const float* table, float* w, float* w_total, int rows, int V, cudaStream_t st) {
+  cudaMemsetAsync(w_total, 0, sizeof(float), st);
+  const int grid = std::max(1, std::min(148 * 4, (rows + 255) / 256));
+  pair_weights_kernel<<<grid, 256, 0, st>>>(prev, curr, table, w, w_total, rows, V);
 }
 
 void embed_gather(const int* ids, const void* table, void* out, int rows, int d, int bigram_buckets, int seq_len, cudaStream_t st) {

@@ -102,6 +102,7 @@ class CudaEngine:
         self.hp.copy_(self.hp_host)
         self.stats = torch.zeros(4, dtype=torch.float32, device=self.dev)
         self.loss_sum = torch.zeros(1, dtype=torch.float32, device=self.dev)
+        self.pair_w_table = self.tok_w = self.w_total = None       # complementary training, see `set_token_weight_table`
         self.adam_t = 0
         self.layer_flags = None          # set by the sharded optimizer: per-layer weight-ready counters
         self.layer_flag_value = 0
@@ -385,7 +386,26 @@ class CudaEngine:
         C.mix_norm_fwd(x, None, None, None, None, None, self.hf, 1.0, self.eps)
         N.gemm(self.hf, self.LM, self.logits)
         if targets is not None:
-            C.softcap_ce(self.logits, self.tgt, self.nll, self.logits if want_grad else None, self.loss_sum, m.logit_softcap, gscale)
+            if self.pair_w_table is not None and want_grad:
+                # complementary training: the loss of this micro-batch is sum(w l) / sum(w), w looked up per (input, target) pair
+                C.pair_weights(self.ids, self.tgt, self.pair_w_table, self.tok_w, self.w_total)
+                C.softcap_ce(self.logits, self.tgt, self.nll, self.logits, self.loss_sum, m.logit_softcap, gscale, self.tok_w, self.w_total)
+            else:
+                C.softcap_ce(self.logits, self.tgt, self.nll, self.logits if want_grad else None, self.loss_sum, m.logit_softcap, gscale)
+
+    def set_token_weight_table(self, table) -> None:
+        """Install (or with ``None`` remove) the ``[V, V]`` fp32 table of training-loss weights per (previous token, target)
+        pair (`ops.complementary.weight_table`). Training steps then minimise the weighted mean; scoring (`want_grad=False`)
+        is never weighted."""
+        if table is None:
+            self.pair_w_table = None
+            return
+        V = self.m.vocab_size
+        t = torch.as_tensor(table, dtype=torch.float32).reshape(V, V).contiguous().to(self.dev)
+        self.pair_w_table = t
+        if self.tok_w is None:
+            self.tok_w = torch.empty(self.T, dtype=torch.float32, device=self.dev)
+            self.w_total = torch.zeros(1, dtype=torch.float32, device=self.dev)
 
     # ---- backward ---------------------------------------------------------------------------------------------------------------
     def backward(self):
@@ -690,6 +710,10 @@ class EngineBackend:
         if t.world_size > 1:
             from ..parallel.dist_engine import DistributedStep
             self.dist = DistributedStep(self.engine, spec)
+
+    def set_token_weight_table(self, table) -> None:
+        self._graph_state = None      # a captured micro-step would keep replaying the unweighted loss kernel
+        self.engine.set_token_weight_table(table)
 
     def train_step(self, batches, lr_scale: float, momentum: float, qat: bool) -> float:
         e = self.engine

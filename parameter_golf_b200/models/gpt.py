@@ -237,12 +237,17 @@ def gpt_logits(m: ModelSpec, p, ids, qat: bool = False, lora=None, dtype=None):
     return m.logit_softcap * torch.tanh(z.float() / m.logit_softcap)
 
 
-def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dtype=None, reduction: str = "mean"):
+def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dtype=None, reduction: str = "mean", token_weights=None):
     """Training loss: mean soft-capped cross-entropy over all tokens (``reduction='none'`` gives the
-    per-token losses [B,T])."""
+    per-token losses [B,T]). With ``token_weights`` (same shape as ``targets``) the mean is weighted and normalised
+    by the sum of the weights (complementary training, ``pg-kernels/src/complementary.rs:226-240``)."""
     h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
     w = p["tok_emb"] if m.tie_embeddings else p["lm_head"]
     z = F.linear(h, w.to(h.dtype))
+    if token_weights is not None and reduction == "mean":
+        per = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction="none").reshape(-1).float()
+        tw = token_weights.reshape(-1).to(per.dtype)
+        return (per * tw).sum() / tw.sum().clamp_min(1e-12)
     loss = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction=reduction)
     return loss.reshape(ids.shape) if reduction == "none" else loss
 

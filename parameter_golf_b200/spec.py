@@ -190,6 +190,14 @@ class TrainSpec:
     checkpoint_every: int = 0
     checkpoint_path: Optional[str] = None
     resume_from: Optional[str] = None
+    # complementary training: loss weight per (previous token, target) pair from bigram statistics; 0 disables
+    complementary_alpha: float = 0.0
+    complementary_shape: str = "floored"        # "linear" | "power" | "floored"
+    complementary_power: float = 2.0
+    complementary_floor: float = 0.2
+    complementary_min_w: float = 0.25
+    complementary_stats_tokens: int = 4_194_304  # training tokens counted into the bigram table at start-up
+    complementary_stats_path: Optional[str] = None   # load the table from this file if it exists, else build and save it
 
 
 @dataclass
@@ -404,6 +412,8 @@ class RunSpec:
         chk(q.compression != "lzma9", "compression lzma9 is declared but not supported by the artifact writer")
         chk(q.calibration in CALIBRATION_MODES, "unknown quant.calibration")
         chk(e.adaptation_backend in ADAPTATION_BACKENDS, "unknown eval.adaptation_backend")
+        chk(0.0 <= t.complementary_alpha <= 1.0, "train.complementary_alpha must be in [0, 1]")
+        chk(t.complementary_shape in ("linear", "power", "floored"), "unknown train.complementary_shape")
         chk(t.muon_ns_profile in NS_PROFILES, f"train.muon_ns_profile must be one of {NS_PROFILES}")
         chk(m.activation in ("relu_sq", "leaky_relu_sq"), "model.activation must be relu_sq or leaky_relu_sq")
         chk(m.rope.mode in ("none", "partial", "yarn"), "unknown rope.mode")

@@ -87,6 +87,7 @@ class OracleBackend:
         self.spec = spec
         self.params = params
         self.runner = OracleRunner(spec.model, params)
+        self.token_weight_table = None      # [V, V] fp32 loss weights per (input token, target), see `set_token_weight_table`
         t = spec.train
         self.bank_names, self.adam_groups = split_param_groups(spec, params)
         self.muon = Muon([params[k] for k in self.bank_names], t.matrix_lr, t.muon_momentum, t.muon_ns_steps,
@@ -99,7 +100,10 @@ class OracleBackend:
         total: Optional[Dict[str, torch.Tensor]] = None
         loss_sum = 0.0
         for ids, tgt in batches:
-            loss, g = self.runner.loss_and_grads(ids, tgt, qat=qat)
+            tw = None
+            if self.token_weight_table is not None:
+                tw = torch.from_numpy(self.token_weight_table[ids.numpy().astype(np.int64), tgt.numpy().astype(np.int64)])
+            loss, g = self.runner.loss_and_grads(ids, tgt, qat=qat, token_weights=tw)
             loss_sum += float(loss)
             total = g if total is None else {k: total[k] + g[k] for k in g}
         inv = 1.0 / len(batches)
@@ -119,6 +123,9 @@ class OracleBackend:
         self.muon.step([grads[k] for k in self.bank_names], lr=self.spec.train.matrix_lr * lr_scale, momentum=momentum)
         return loss_sum * inv
 
+    def set_token_weight_table(self, table) -> None:
+        self.token_weight_table = None if table is None else np.ascontiguousarray(table, dtype=np.float32)
+
     def state_dict(self):
         return {"muon": self.muon.state_dict(), "adam": self.adam.state_dict()}
 
@@ -128,6 +135,34 @@ class OracleBackend:
 
     def sync_params(self) -> Dict[str, torch.Tensor]:
         return self.params
+
+
+def complementary_table(spec: RunSpec, log=None) -> np.ndarray:
+    """``[V, V]`` loss-weight table of complementary training: bigram counts over the first
+    ``train.complementary_stats_tokens`` training tokens (every rank reads the same shards, so the tables agree without
+    a collective), loaded from / saved to ``train.complementary_stats_path`` in the reference's byte layout when set."""
+    from .ops import complementary as comp
+    t, V = spec.train, spec.model.vocab_size
+    stats = None
+    path = t.complementary_stats_path
+    if path and os.path.exists(path):
+        with open(path, "rb") as f:
+            stats = comp.BigramStats.from_bytes(f.read())
+        if stats.vocab_size != V:
+            raise RuntimeError(f"bigram table at {path} has vocab {stats.vocab_size}, the model {V}")
+    if stats is None:
+        stats = comp.stats_from_stream(t.train_data_pattern, V, t.complementary_stats_tokens)
+        if path and t.rank == 0:
+            tmp = path + ".tmp"
+            with open(tmp, "wb") as f:
+                f.write(stats.to_bytes())
+            os.replace(tmp, path)
+    shape = comp.WeightShape(t.complementary_shape, t.complementary_power, t.complementary_floor, t.complementary_min_w)
+    table = comp.weight_table(stats, t.complementary_alpha, shape)
+    if log is not None:
+        log.info(f"complementary_training: alpha:{t.complementary_alpha} shape:{t.complementary_shape} "
+                 f"pairs:{int(stats.row_sums.sum())} mean_weight:{float(table.mean()):.4f}")
+    return table
 
 
 @dataclass
@@ -152,6 +187,7 @@ class VariantResult:
     eval_ms: float = 0.0
     eval_kind: str = "none"
     peak_mem_mib: int = 0
+    complementary_mean_weight: float = 1.0
     timers: dict = field(default_factory=dict)
 
     def key_value_lines(self) -> List[str]:
@@ -225,6 +261,10 @@ class VariantRunner:
         # ---- model + backend ------------------------------------------------------------------------
         params = gpt.init_params(m, t.seed, device="cpu")
         backend = self._make_backend(params)
+        if t.complementary_alpha > 0:
+            table = complementary_table(spec, log)
+            backend.set_token_weight_table(table)
+            res.complementary_mean_weight = float(table.mean())
         fused_ema = getattr(backend, "fused_ema", False)       # CUDA engine: EMA is updated inside the optimizer kernels
         ema = Ema(t.ema_decay) if (t.ema_decay > 0 and not fused_ema) else None
         swa = Swa(t.swa_every, t.swa_threshold) if t.swa_enabled else None

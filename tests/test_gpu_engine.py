@@ -205,3 +205,49 @@ def test_runner_shapes_share_weights_and_see_updates():
     assert (na1 - na0).abs().max() > 1e-3 and (nb1 - nb0).abs().max() > 1e-3
     fresh = EngineRunner(spec, {k: v.clone() for k, v in r.params.items()}, "cuda", train=True)
     assert torch.allclose(fresh.nll(b_ids, b_tgt), nb1, atol=1e-5)
+
+
+def test_complementary_token_weights_match_oracle():
+    """Weighted-mean loss and its gradients with a [V, V] pair-weight table; scoring stays unweighted."""
+    import numpy as np
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine
+    from parameter_golf_b200.models.runner import OracleRunner
+    from parameter_golf_b200.ops import complementary as comp
+    from parameter_golf_b200.ops import native
+    spec = small_spec()
+    params = gpt.fill_deterministic(spec.model)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 256, (4, 128))
+    tgt = torch.randint(0, 256, (4, 128))
+    st = comp.BigramStats(256)
+    rng = np.random.default_rng(0)
+    st.add_sequence(rng.integers(0, 16, 20000))           # concentrated counts: a wide spread of weights
+    st.add_sequence(ids.reshape(-1).numpy())
+    table = comp.weight_table(st, 0.9)
+    tw = torch.from_numpy(table[ids.numpy(), tgt.numpy()])
+    assert float(tw.min()) < 1.0
+    eng = CudaEngine(spec, params, "cuda", 4, 128)
+    eng.set_token_weight_table(table)
+    eng.zero_grads()
+    eng.micro_step(ids.cuda().int(), tgt.cuda().int(), 1)
+    torch.cuda.synchronize()
+    native.check_status()
+    np.testing.assert_allclose(eng.tok_w.cpu().numpy(), tw.reshape(-1).numpy(), rtol=1e-6)
+    assert float(eng.w_total[0]) == pytest.approx(float(tw.sum()), rel=1e-5)
+    loss = float(eng.loss_sum[0]) / eng.T
+    p64 = {k: v.double() for k, v in params.items()}
+    ref_loss, ref = OracleRunner(spec.model, p64).loss_and_grads(ids, tgt, token_weights=tw.double())
+    assert abs(loss - float(ref_loss)) < 2e-2, (loss, float(ref_loss))
+    worst = {k: rel_err(eng.g[k], g) for k, g in ref.items()}
+    bad = {k: v for k, v in worst.items() if v > (0.2 if k == "q_gain" else 0.06)}
+    assert not bad, worst
+    # the same engine without gradients scores plain per-token losses
+    eng.forward(ids.cuda().int(), tgt.cuda().int())
+    plain = OracleRunner(spec.model, p64).nll(ids, tgt)
+    assert float((eng.nll.view(4, 128).cpu().double() - plain).abs().max()) < 0.1
+    eng.set_token_weight_table(None)
+    eng.zero_grads()
+    eng.micro_step(ids.cuda().int(), tgt.cuda().int(), 1)
+    ref_loss2, _ = oracle_grads(spec, params, ids, tgt)
+    assert abs(float(eng.loss_sum[0]) / eng.T - float(ref_loss2)) < 2e-2

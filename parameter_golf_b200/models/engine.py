@@ -79,6 +79,17 @@ class CudaEngine:
         self.first_slot = {}
         for j, (l, _) in enumerate(self.sched):
             self.first_slot.setdefault(l, j)
+        # Activation checkpointing (saved-activation policies of pg-model/src/gpu.rs:1159-1201, 1742-1744): slots whose
+        # block activations are not kept share ONE set of buffers and the block is run again from its kept input right
+        # before its backward. Block outputs (T x d per slot) are always kept: they are the recompute inputs and skips.
+        self.saved = self._saved_slots(getattr(spec.train, "save_layer_acts", "all")) if train else [False] * self.nslots
+        self.act_slot, nsaved = [], 0
+        for keep in self.saved:
+            self.act_slot.append(nsaved if keep else -1)
+            nsaved += int(keep)
+        self.nact = nsaved + (0 if all(self.saved) else 1)     # number of activation buffer sets
+        self.act_slot = [a if a >= 0 else self.nact - 1 for a in self.act_slot]
+        self.block_in = [None] * self.nslots                   # (x, skip, skip weight) each slot's block consumed
         self.parallel = m.parallel_residual.enabled
         self.gates = []                                        # (weight name, bias name or None, scale, multiplier)
         if m.attn_out_gate.enabled:
@@ -116,6 +127,28 @@ class CudaEngine:
             self.cast_weights()
 
     # ---- storage -----------------------------------------------------------------------------------------------
+    def _saved_slots(self, mode: str) -> List[bool]:
+        """Which activation slots keep their block activations between forward and backward. ``all`` (default: 180 GB of
+        HBM holds every layer of the record shape many times over), ``edges`` (layers 0-2 and the last two, single-pass
+        layers only; layers 3-8 and repeated layers recompute), ``inner`` (the complement of the edge rule: layers 3-8),
+        ``recurrent`` (only layers that run more than once), ``none`` (every block recomputes)."""
+        mode = str(mode).lower()
+        passes = {}
+        for l, _ in self.sched:
+            passes[l] = passes.get(l, 0) + 1
+        inner = lambda l: 3 <= l <= 8
+        if mode in ("all", "1", "true"):
+            return [True] * self.nslots
+        if mode in ("none", "0", "false", "off"):
+            return [False] * self.nslots
+        if mode in ("edges", "checkpoint"):
+            return [(not inner(l)) and passes[l] == 1 for l, _ in self.sched]
+        if mode in ("inner", "checkpointed"):
+            return [inner(l) for l, _ in self.sched]
+        if mode == "recurrent":
+            return [passes[l] > 1 for l, _ in self.sched]
+        raise ValueError(f"train.save_layer_acts: unknown mode {mode!r}")
+
     def _alloc_params(self, params):
         dev, m = self.dev, self.m
         shapes = gpt.param_shapes(m)
@@ -204,7 +237,7 @@ class CudaEngine:
         if m.value_embedding.enabled:
             self.ve_e = buf(T, m.value_embedding.dim)
         self.x0 = buf(T, d)
-        L = self.nslots if self.train else 1  # inference reuses one slot's worth of buffers
+        L = self.nact if self.train else 1    # inference reuses one slot's worth of buffers
 
         def per_layer(*shape):
             return [buf(*shape) for _ in range(L)]
@@ -213,8 +246,8 @@ class CudaEngine:
         self.qkv_pre, self.qk_post = per_layer(T, self.qkvw), per_layer(T, self.qkvw)
         self.y, self.x_mid = per_layer(T, d), per_layer(T, d)
         self.mm = self.h if self.parallel else per_layer(T, d)      # parallel residual: the MLP reads the attention branch's normed input
-        self.z = [buf(T, d) if (self.train and self.sched[i][0] in m.xsa_layers()) or (not self.train and i == 0 and m.xsa_last_n > 0) else None
-                  for i in range(L)]
+        xsa_sets = {self.act_slot[j] for j, (l, _) in enumerate(self.sched) if l in m.xsa_layers()} if self.train else ({0} if m.xsa_last_n > 0 else set())
+        self.z = [buf(T, d) if i in xsa_sets else None for i in range(L)]
         self.yg = [[buf(T, d) for _ in range(L)] for _ in self.gates]          # gated attention outputs, one list per gate
         self.gv = [[torch.empty(T, self.H, dtype=torch.float32, device=dev) for _ in range(L)] for _ in self.gates]
         self.zz = [None] * L                 # what the output projection consumed in each slot
@@ -321,6 +354,44 @@ class CudaEngine:
         else:
             dv.copy_(gv.transpose(1, 2).reshape(self.T, kv))
 
+    def _block_fwd(self, j: int, x, skip, sw, recompute: bool = False):
+        """Block of activation slot ``j`` on input ``x`` (with the U-Net skip it consumes, if any); returns the block output.
+        ``recompute`` is the second run of a checkpointed block inside the backward pass: it refills the shared activation
+        buffers and leaves out the last product, whose output is still in ``x_out[j]``."""
+        C, m, p = self.C, self.m, self.p
+        d, kv, S = self.d, self.kv, self.S
+        l, rep = self.sched[j]
+        li = self.act_slot[j] if self.train else 0
+        s_l = gpt.layer_ln_scale(m, l)
+        C.mix_norm_fwd(x, self.x0, skip, sw, p["resid_mix"][l], self.x_in[li], self.h[li], s_l, self.eps)
+        if self.layer_flags is not None and not recompute:
+            N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li], wait_flag=self.layer_flags[l:l + 1], wait_value=self.layer_flag_value)
+        else:
+            N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li])
+        if m.value_embedding.enabled and l in m.value_embedding.layers:
+            vi = m.value_embedding.layers.index(l)
+            vview = self.qkv_pre[li][:, d + kv:]
+            N.gemm(self.ve_e, self.VP[vi], vview, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=vview)
+        C.qk_norm_rope_fwd(self.qkv_pre[li], self.qk_post[li], self.cos, self.sin, p["q_gain"][l], self.H, self.Hkv, self.hd, m.rope_dims, S, self.eps)
+        self._attn_fwd(l, li)
+        zz = self.y[li]
+        if l in m.xsa_layers():
+            zz = self.z[li]
+            C.xsa_fwd(self.y[li], self.qkv_pre[li][:, d + kv:], zz, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+        for gi, (wname, bname, gscale_, gmult) in enumerate(self.gates):
+            out = self.yg[gi][li]
+            C.head_gate_fwd(zz, self.h[li], p[wname][l], p[bname][l] if bname else None, out, self.gv[gi][li], self.H, self.hd, gscale_, gmult)
+            zz = out
+        self.zz[li] = zz
+        N.gemm(zz, self.Wo[l], self.x_mid[li], epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.x_in[li])
+        if not self.parallel:
+            C.mix_norm_fwd(self.x_mid[li], None, None, None, None, None, self.mm[li], s_l, self.eps)
+        N.gemm(self.mm[li], self.Wup[l], self.hu[li], epi=N.EPI_ACT_SQ, slope=self.slope, D2=self.a[li])
+        xo = self.x_out[j]
+        if not recompute:
+            N.gemm(self.a[li], self.Wd[l], xo, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.x_mid[li])
+        return xo
+
     # ---- forward -------------------------------------------------------------------------------------------------------------
     def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor], gscale: float = 0.0, want_grad: bool = False):
         """Runs the model on one micro-batch. With ``want_grad`` the logits buffer ends up holding
@@ -347,38 +418,11 @@ class CudaEngine:
         skips: List[torch.Tensor] = []
         xsa_layers = m.xsa_layers()
         for j, (l, rep) in enumerate(self.sched):
-            li = j if self.train else 0
-            s_l = gpt.layer_ln_scale(m, l)
             skip = sw = None
             if self.unet and l >= self.enc and rep == 0 and skips:
                 skip, sw = skips.pop(), p["skip_weights"][l - self.enc]
-            C.mix_norm_fwd(x, self.x0, skip, sw, p["resid_mix"][l], self.x_in[li], self.h[li], s_l, self.eps)
-            if self.layer_flags is not None:
-                N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li], wait_flag=self.layer_flags[l:l + 1], wait_value=self.layer_flag_value)
-            else:
-                N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li])
-            if m.value_embedding.enabled and l in m.value_embedding.layers:
-                vi = m.value_embedding.layers.index(l)
-                vview = self.qkv_pre[li][:, d + kv:]
-                N.gemm(self.ve_e, self.VP[vi], vview, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=vview)
-            C.qk_norm_rope_fwd(self.qkv_pre[li], self.qk_post[li], self.cos, self.sin, p["q_gain"][l], self.H, self.Hkv, self.hd, m.rope_dims, S, self.eps)
-            self._attn_fwd(l, li)
-            zz = self.y[li]
-            if l in xsa_layers:
-                zz = self.z[li]
-                C.xsa_fwd(self.y[li], self.qkv_pre[li][:, d + kv:], zz, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
-            for gi, (wname, bname, gscale_, gmult) in enumerate(self.gates):
-                out = self.yg[gi][li]
-                C.head_gate_fwd(zz, self.h[li], p[wname][l], p[bname][l] if bname else None, out, self.gv[gi][li], self.H, self.hd, gscale_, gmult)
-                zz = out
-            self.zz[li] = zz
-            N.gemm(zz, self.Wo[l], self.x_mid[li], epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.x_in[li])
-            if not self.parallel:
-                C.mix_norm_fwd(self.x_mid[li], None, None, None, None, None, self.mm[li], s_l, self.eps)
-            N.gemm(self.mm[li], self.Wup[l], self.hu[li], epi=N.EPI_ACT_SQ, slope=self.slope, D2=self.a[li])
-            xo = self.x_out[j]
-            N.gemm(self.a[li], self.Wd[l], xo, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.x_mid[li])
-            x = xo
+            self.block_in[j] = (x, skip, sw)
+            x = self._block_fwd(j, x, skip, sw)
             last_pass = j + 1 == self.nslots or self.sched[j + 1][0] != l
             if self.unet and l < self.enc and last_pass:
                 skips.append(x)
@@ -421,40 +465,43 @@ class CudaEngine:
         for j in range(self.nslots - 1, -1, -1):
             l, rep = self.sched[j]
             s_l = gpt.layer_ln_scale(m, l)
+            aj = self.act_slot[j]
+            if not self.saved[j]:
+                self._block_fwd(j, *self.block_in[j], recompute=True)
             # ---- MLP
             self.Gd.zero_()
-            N.gemm(self.dx, self.a[j], self.Gd, False, False, A)
+            N.gemm(self.dx, self.a[aj], self.Gd, False, False, A)
             C.fold_scaled_grad_bf16(self.Gd, self.Wd_u[l], p["mlp_scale"][l], 1, d, g["mlp_down_bank"][l], g["mlp_scale"][l])
-            N.gemm(self.dx, self.Wd[l], self.d_hu, True, False, N.EPI_MUL_ACTGRAD, slope=self.slope, aux=self.hu[j])
-            N.gemm(self.d_hu, self.mm[j], g["mlp_up_bank"][l], False, False, A)
+            N.gemm(self.dx, self.Wd[l], self.d_hu, True, False, N.EPI_MUL_ACTGRAD, slope=self.slope, aux=self.hu[aj])
+            N.gemm(self.d_hu, self.mm[aj], g["mlp_up_bank"][l], False, False, A)
             N.gemm(self.d_hu, self.Wup[l], self.d_m, True, False)
             if self.parallel:
                 dx_mid, dx_next = self.dx, self.dx_mid      # no norm between x_mid and the MLP: the residual gradient passes through
                 d_hx = self.d_m                             # and the MLP-input gradient joins the QKV-input gradient below
             else:
-                C.mix_norm_bwd(self.d_m, self.dx, self.x_mid[j], None, None, None, None, None, None, self.dx_mid, None, None, None, None, False, s_l, self.eps)
+                C.mix_norm_bwd(self.d_m, self.dx, self.x_mid[aj], None, None, None, None, None, None, self.dx_mid, None, None, None, None, False, s_l, self.eps)
                 dx_mid, dx_next = self.dx_mid, self.dx
                 d_hx = self.d_hx if self.gates else None
             # ---- attention output projection
-            zz = self.zz[j]
+            zz = self.zz[aj]
             self.Go.zero_()
             N.gemm(dx_mid, zz, self.Go, False, False, A)
             C.fold_scaled_grad_bf16(self.Go, self.Wo_u[l], p["attn_scale"][l], 1, d, g["qo_bank"][n + l], g["attn_scale"][l])
-            vview = self.qkv_pre[j][:, d + kv:]
+            vview = self.qkv_pre[aj][:, d + kv:]
             dv = self.d_qkv_pre[:, d + kv:]
             xsa = l in xsa_layers
             d_att = self.d_z if xsa else self.d_y            # gradient of what the gates / the output projection consumed
             N.gemm(dx_mid, self.Wo[l], d_att, True, False)
             for gi in range(len(self.gates) - 1, -1, -1):
                 wname, bname, gscale_, gmult = self.gates[gi]
-                gate_in = self.yg[gi - 1][j] if gi > 0 else (self.z[j] if xsa else self.y[j])
+                gate_in = self.yg[gi - 1][aj] if gi > 0 else (self.z[aj] if xsa else self.y[aj])
                 first_writer = (not self.parallel) and gi == len(self.gates) - 1
-                C.head_gate_bwd(d_att, gate_in, self.h[j], p[wname][l], self.gv[gi][j], g[wname][l], g[bname][l] if bname else None, d_hx,
+                C.head_gate_bwd(d_att, gate_in, self.h[aj], p[wname][l], self.gv[gi][aj], g[wname][l], g[bname][l] if bname else None, d_hx,
                                 not first_writer, self.H, self.hd, gscale_, gmult)
             if xsa:
-                C.xsa_bwd(self.d_z, self.y[j], vview, self.d_y, dv, False, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
-            self._attn_bwd(l, j)
-            C.qk_norm_rope_bwd(self.d_qk_post, self.qkv_pre[j], self.d_qkv_pre, self.cos, self.sin, p["q_gain"][l], g["q_gain"][l], self.H, self.Hkv,
+                C.xsa_bwd(self.d_z, self.y[aj], vview, self.d_y, dv, False, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+            self._attn_bwd(l, aj)
+            C.qk_norm_rope_bwd(self.d_qk_post, self.qkv_pre[aj], self.d_qkv_pre, self.cos, self.sin, p["q_gain"][l], g["q_gain"][l], self.H, self.Hkv,
                                self.hd, m.rope_dims, S, self.eps)
             if m.value_embedding.enabled and l in m.value_embedding.layers:
                 vi = m.value_embedding.layers.index(l)
@@ -470,7 +517,7 @@ class CudaEngine:
                 N.gemm(dv, self.VP[vi], self.d_ve_e, True, False)
                 self.d_ve_acc.add_(self.d_ve_e)
             # one weight-gradient product for the packed QKV rows, written to the Q, K and V slots of the gradient banks
-            N.gemm(self.d_qkv_pre, self.h[j], g["qo_bank"][l], False, False, A, segs=((d, g["kv_bank"][l]), (d + kv, g["kv_bank"][n + l])))
+            N.gemm(self.d_qkv_pre, self.h[aj], g["qo_bank"][l], False, False, A, segs=((d, g["kv_bank"][l]), (d + kv, g["kv_bank"][n + l])))
             if d_hx is not None:
                 N.gemm(self.d_qkv_pre, self.Wqkv[l], self.d_h, True, False, N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=d_hx)
             else:
@@ -490,7 +537,7 @@ class CudaEngine:
                 lp = self.sched[j - 1][0]                        # x_prev is the (last-pass) output of an encoder layer whose skip
                 if lp != l and lp < self.enc and self.first_slot.get(2 * self.enc - 1 - lp, -1) not in (-1, j):   # consumer is further up
                     add_grad = self.d_skip[lp]
-            C.mix_norm_bwd(self.d_h, dx_mid, self.x_in[j], x_prev, self.x0, skip, sw, p["resid_mix"][l], add_grad, dx_next, self.d_x0, d_skip,
+            C.mix_norm_bwd(self.d_h, dx_mid, self.x_in[aj], x_prev, self.x0, skip, sw, p["resid_mix"][l], add_grad, dx_next, self.d_x0, d_skip,
                            g["resid_mix"][l], d_sw, self_pair, s_l, self.eps)
             if self.parallel:
                 self.dx, self.dx_mid = self.dx_mid, self.dx

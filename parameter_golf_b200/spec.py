@@ -187,6 +187,7 @@ class TrainSpec:
     val_batch_size: int = 524_288
     grad_wire_dtype: str = "bf16"       # wire dtype of bank-gradient reduce-scatter
     cuda_graph: bool = False            # replay the micro-batch forward+backward from a captured CUDA graph
+    save_layer_acts: str = "all"        # CUDA engine activation checkpointing: all | edges | inner | recurrent | none
     checkpoint_every: int = 0
     checkpoint_path: Optional[str] = None
     resume_from: Optional[str] = None
@@ -412,6 +413,7 @@ class RunSpec:
         chk(q.compression != "lzma9", "compression lzma9 is declared but not supported by the artifact writer")
         chk(q.calibration in CALIBRATION_MODES, "unknown quant.calibration")
         chk(e.adaptation_backend in ADAPTATION_BACKENDS, "unknown eval.adaptation_backend")
+        chk(t.save_layer_acts in ("all", "edges", "inner", "recurrent", "none"), "train.save_layer_acts must be all|edges|inner|recurrent|none")
         chk(0.0 <= t.complementary_alpha <= 1.0, "train.complementary_alpha must be in [0, 1]")
         chk(t.complementary_shape in ("linear", "power", "floored"), "unknown train.complementary_shape")
         chk(t.muon_ns_profile in NS_PROFILES, f"train.muon_ns_profile must be one of {NS_PROFILES}")

@@ -440,7 +440,7 @@ class VariantRunner:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="parameter_golf_b200.train")
     sub = ap.add_subparsers(dest="cmd", required=True)
-    for name in ("run", "sweep"):
+    for name in ("run", "sweep", "plan"):
         sp = sub.add_parser(name)
         sp.add_argument("--spec")
         sp.add_argument("--family", default=None)
@@ -451,7 +451,7 @@ def main(argv=None) -> int:
         sp.add_argument("--artifact", default=None)
         sp.add_argument("overrides", nargs="*")
     a = ap.parse_args(argv)
-    fams = [a.family] if (a.cmd == "run" and a.family) else ([None] if a.cmd == "run" else a.families.split(","))
+    fams = [a.family] if (a.cmd != "sweep" and a.family) else ([None] if a.cmd != "sweep" else a.families.split(","))
     rc = 0
     for fam in fams:
         spec = RunSpec.load(a.spec) if a.spec else family_preset(fam or "tiny_cpu")
@@ -466,10 +466,14 @@ def main(argv=None) -> int:
         spec.apply_overrides(a.overrides)
         if a.mode:
             spec.mode = a.mode
-        if spec.train.world_size > 1:
+        if spec.train.world_size > 1 and a.cmd != "plan":
             import torch.distributed as dist
             if not dist.is_initialized():
                 dist.init_process_group("gloo" if spec.train.backend == "cpu" else "nccl")
+        if a.cmd == "plan":              # print the execution plan (layout, block schedule, memory estimate) and stop
+            from .plan import ExecutionPlan
+            print("\n".join(ExecutionPlan.from_run_spec(spec).summary_lines()))
+            continue
         res = VariantRunner(spec).run()
         if spec.train.rank == 0:
             print("\n".join(res.key_value_lines()))

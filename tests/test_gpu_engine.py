@@ -222,11 +222,14 @@ def test_complementary_token_weights_match_oracle():
     tgt = torch.randint(0, 256, (4, 128))
     st = comp.BigramStats(256)
     rng = np.random.default_rng(0)
-    st.add_sequence(rng.integers(0, 16, 20000))           # concentrated counts: a wide spread of weights
-    st.add_sequence(ids.reshape(-1).numpy())
+    st.add_sequence(rng.integers(0, 256, 20000))
+    seen = rng.random(ids.numel()) < 0.5                  # half of the (input, target) pairs of this batch are frequent bigrams
+    a, b = ids.reshape(-1).numpy()[seen], tgt.reshape(-1).numpy()[seen]
+    np.add.at(st.counts, (a, b), 2000)
+    st.row_sums = st.counts.sum(axis=1, dtype=np.uint64)
     table = comp.weight_table(st, 0.9)
     tw = torch.from_numpy(table[ids.numpy(), tgt.numpy()])
-    assert float(tw.min()) < 1.0
+    assert float(tw.min()) < 0.9 and float(tw.max()) == 1.0
     eng = CudaEngine(spec, params, "cuda", 4, 128)
     eng.set_token_weight_table(table)
     eng.zero_grads()
@@ -245,9 +248,63 @@ def test_complementary_token_weights_match_oracle():
     # the same engine without gradients scores plain per-token losses
     eng.forward(ids.cuda().int(), tgt.cuda().int())
     plain = OracleRunner(spec.model, p64).nll(ids, tgt)
-    assert float((eng.nll.view(4, 128).cpu().double() - plain).abs().max()) < 0.1
+    assert float((eng.nll.view(4, 128).cpu().double() - plain).abs().mean()) < 6e-2
     eng.set_token_weight_table(None)
     eng.zero_grads()
     eng.micro_step(ids.cuda().int(), tgt.cuda().int(), 1)
     ref_loss2, _ = oracle_grads(spec, params, ids, tgt)
     assert abs(float(eng.loss_sum[0]) / eng.T - float(ref_loss2)) < 2e-2
+
+
+@pytest.mark.parametrize("mode,variant", [("none", "record"), ("edges", "record"), ("recurrent", "recurrence"), ("none", "recurrence"),
+                                          ("none", "parallel_gate"), ("inner", "ve")])
+def test_activation_checkpointing_gives_the_same_gradients(mode, variant):
+    """A block whose activations are not kept is run again inside the backward; every kernel is deterministic except the
+    split-K fp32 atomics of the weight gradients, so the gradients agree with the keep-everything engine to rounding."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine
+    from parameter_golf_b200.ops import native
+    ov = {"model.num_layers": 6}
+    if variant == "recurrence":
+        ov.update({"model.recurrence.enabled": "true", "model.recurrence.start_layer": 1, "model.recurrence.repeat_layers": 2})
+    if variant == "parallel_gate":
+        ov.update({"model.parallel_residual.enabled": "true", "model.sparse_attn_gate.enabled": "true", "model.sparse_attn_gate.width": 12})
+    if variant == "ve":
+        ov.update({"model.value_embedding.enabled": "true", "model.value_embedding.dim": 64, "model.value_embedding.layers": "[3,5]"})
+    torch.manual_seed(0)
+    ids = torch.randint(0, 256, (4, 128)).cuda().int()
+    tgt = torch.randint(0, 256, (4, 128)).cuda().int()
+    out = {}
+    for m_ in ("all", mode):
+        spec = small_spec(**dict(ov, **{"train.save_layer_acts": m_}))
+        params = gpt.fill_deterministic(spec.model)
+        eng = CudaEngine(spec, params, "cuda", 4, 128)
+        if m_ == "all":
+            assert eng.nact == eng.nslots
+        else:
+            assert eng.nact < eng.nslots and not all(eng.saved)
+        eng.zero_grads()
+        eng.micro_step(ids, tgt, 1)
+        torch.cuda.synchronize()
+        native.check_status()
+        out[m_] = (float(eng.loss_sum[0]), {k: v.clone() for k, v in eng.g.items()})
+    assert out["all"][0] == pytest.approx(out[mode][0], rel=1e-6)
+    worst = {k: rel_err(out[mode][1][k], g) for k, g in out["all"][1].items()}
+    assert max(worst.values()) < 2e-3, worst
+
+
+@pytest.mark.parametrize("mode", ["all", "none"])
+def test_memory_estimate_tracks_engine_allocation(mode):
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine
+    from parameter_golf_b200.plan import estimate_engine_memory
+    spec = small_spec(**{"train.save_layer_acts": mode, "model.num_layers": 6})
+    params = gpt.fill_deterministic(spec.model)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    before = torch.cuda.memory_allocated()
+    eng = CudaEngine(spec, params, "cuda", 16, 128)
+    eng.enable_ema()
+    used = torch.cuda.memory_allocated() - before
+    est = estimate_engine_memory(spec, 16 * 128).total
+    assert 0.7 * used < est < 1.3 * used, (est, used)

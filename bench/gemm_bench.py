@@ -70,6 +70,8 @@ def main():
         }
         if name in ("attn_out", "mlp_down"):
             products["fwd+resid"] = (lambda: n.gemm(X, W, Y, epi=n.EPI_RESID_BF16, aux=resid, colscale=col), None)
+        if name in ("attn_out", "mlp_down"):      # what the engine runs: residual add with the output scale folded into W
+            products["fwd+axpby"] = (lambda: n.gemm(X, W, Y, epi=n.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=resid), None)
         if name == "mlp_up":
             products["fwd+act"] = (lambda: n.gemm(X, W, Y, epi=n.EPI_ACT_SQ, slope=0.5, D2=Y2), None)
         if name == "mlp_down":

@@ -42,6 +42,8 @@ struct GemmKernelParams {
   int wait_value;
   int seg_rows[2];        // fp32 epilogues: rows >= seg_rows[k] (> 0) are written to seg_D[k] as row m - seg_rows[k]
   float* seg_D[2];
+  int diag;
+  int aux_l2_prefetch;     // the producer warp pulls the next tile's second operand into L2 through `map_x`
 };
 
 template <int BN>
@@ -148,10 +150,14 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
 
 // Aligned bf16 epilogue with coalesced global traffic. A thread owns one accumulator row, but 16-byte accesses of 32
 // different rows per instruction touch half a sector each; here rows are exchanged through a per-warp shared-memory
-// tile (32 rows x 64 B, 80-byte pitch) so that every global load/store instruction covers 8 rows x 64 contiguous bytes.
+// tile (32 rows x 64 B) so that every global load/store instruction covers 8 rows x 64 contiguous bytes.
 // `ax` holds the aux operand in that coalesced pattern: piece i = row (i*8 + lane/4), bytes (lane%4)*16 .. +16.
-constexpr int STG_PITCH = 80;
-constexpr int STG_WARP_BYTES = 32 * STG_PITCH;
+// The tile is XOR-swizzled: the 16-byte piece p of row r sits at piece p ^ ((r >> 1) & 3). Both access patterns are
+// then free of bank conflicts (8 consecutive rows x one piece, and 2 consecutive rows x 4 pieces, each cover all 32
+// banks once); a padded pitch can only satisfy one of the two.
+constexpr int STG_PITCH = 64;
+constexpr int STG_WARP_BYTES = 32 * 80;     // carve-out per warp (unchanged footprint)
+__device__ __forceinline__ int stg_off(int row, int piece) { return row * STG_PITCH + ((piece ^ ((row >> 1) & 3)) << 4); }
 
 template <int EPI>
 __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p, int b, int m_base, int lane, int n0, const uint32_t (&r)[32],
@@ -161,11 +167,11 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p,
   float a[32];
   if constexpr (HAS_AUX) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(stg + (i * 8 + srow) * STG_PITCH + spc * 16) = ax[i];
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(stg + stg_off(i * 8 + srow, spc)) = ax[i];
     __syncwarp();
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 q = *reinterpret_cast<const uint4*>(stg + lane * STG_PITCH + i * 16);
+      const uint4 q = *reinterpret_cast<const uint4*>(stg + stg_off(lane, i));
       const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
       a[8 * i] = f0.x; a[8 * i + 1] = f0.y; a[8 * i + 2] = f1.x; a[8 * i + 3] = f1.y;
       a[8 * i + 4] = f2.x; a[8 * i + 5] = f2.y; a[8 * i + 6] = f3.x; a[8 * i + 7] = f3.y;
@@ -234,13 +240,13 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p,
   auto put = [&](const uint32_t (&x)[16], void* base) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
-      *reinterpret_cast<uint4*>(stg + lane * STG_PITCH + i * 16) = make_uint4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+      *reinterpret_cast<uint4*>(stg + stg_off(lane, i)) = make_uint4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
     __syncwarp();
     __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(base) + (long long)b * p.stride_d + n0 + spc * 8;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = m_base + i * 8 + srow;
-      if (row < p.M) *reinterpret_cast<uint4*>(d + (long long)row * p.ldd) = *reinterpret_cast<const uint4*>(stg + (i * 8 + srow) * STG_PITCH + spc * 16);
+      if (row < p.M && !(p.diag & 1)) *reinterpret_cast<uint4*>(d + (long long)row * p.ldd) = *reinterpret_cast<const uint4*>(stg + stg_off(i * 8 + srow, spc));
     }
     __syncwarp();
   };
@@ -250,7 +256,8 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p,
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_x, const GemmKernelParams p) {
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::STAGES;
   constexpr uint32_t TMEM_COLS = 2 * BN;            // 256 or 512: two accumulators
@@ -330,6 +337,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int m0 = tm * BM, n0 = tn * BN;
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+        if (p.aux_l2_prefetch && tile + (int)gridDim.x < total_tiles) {
+          // The epilogue warps read the second operand of this CTA's NEXT tile while they finish this one; ask for it now
+          // so that those reads find it in L2.
+          const int nt = tile + gridDim.x;
+          const int pb = nt / tiles_per_batch;
+          int pr = nt - pb * tiles_per_batch;
+          pr -= (pr / (p.tiles_m * p.tiles_n)) * p.tiles_m * p.tiles_n;
+          const int ptm = pr / p.tiles_n, ptn = pr - ptm * p.tiles_n;
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            if (ptn * BN + 64 * j < p.N) tma_prefetch_l2_3d(&map_x, ptn * BN + 64 * j, ptm * BM, pb);
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, kb)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
@@ -402,60 +421,84 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int b = tile / tiles_per_batch;
+    constexpr bool HAS_AUX = (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD);
+    constexpr int CH = BN / 64;                   // 32-column chunks per epilogue warp (the two warps of a quarter split the columns)
+    constexpr bool BF16_OUT = !(EPI == EPI_F32 || EPI == EPI_F32_ATOMIC);
+    const int c_begin = half * CH;
+    auto tile_coords = [&](int tile, int& b, int& tm, int& tn) {
+      b = tile / tiles_per_batch;
       int r = tile - b * tiles_per_batch;
       const int split = r / (p.tiles_m * p.tiles_n);
       r -= split * p.tiles_m * p.tiles_n;
-      const int tm = r / p.tiles_n, tn = r - tm * p.tiles_n;
-      const int m = tm * BM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-      constexpr bool HAS_AUX = (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD);
-      constexpr int CH = BN / 64;                   // 32-column chunks per epilogue warp (the two warps of a quarter split the columns)
-      const int c_begin = half * CH;
-      constexpr bool BF16_OUT = !(EPI == EPI_F32 || EPI == EPI_F32_ATOMIC);
-      const int m_base = tm * BM + quarter * 32;
-      auto load_aux = [&](int c, uint4 (&dst)[4]) {
-        if constexpr (HAS_AUX) {
-          const int n0 = tn * BN + c * 32;
-          if (staged_ok && n0 + 32 <= p.N) {          // coalesced pattern: 8 rows x 64 B per instruction
-            const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + n0 + (lane & 3) * 8;
+      tm = r / p.tiles_n;
+      tn = r - tm * p.tiles_n;
+    };
+    // Second operand of chunk c of tile (b, tm, tn), in the pattern its consumer expects.
+    auto load_aux = [&](int b, int tm, int tn, int c, uint4 (&dst)[4]) {
+      if constexpr (HAS_AUX) {
+        const int n0 = tn * BN + c * 32;
+        if ((p.diag & 2) || n0 >= p.N) return;
+        const int m_base = tm * BM + quarter * 32;
+        if (staged_ok && n0 + 32 <= p.N) {          // coalesced pattern: 8 rows x 64 B per instruction
+          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + n0 + (lane & 3) * 8;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int row = m_base + i * 8 + (lane >> 2);
-              if (row < p.M) dst[i] = *reinterpret_cast<const uint4*>(ap + (long long)row * p.ld_aux);
-            }
-          } else if (m < p.M && n0 + 32 <= p.N) {
-            const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + (long long)m * p.ld_aux + n0;
-            if ((reinterpret_cast<uintptr_t>(ap) & 15) == 0) {
+          for (int i = 0; i < 4; ++i) {
+            const int row = m_base + i * 8 + (lane >> 2);
+            if (row < p.M) dst[i] = *reinterpret_cast<const uint4*>(ap + (long long)row * p.ld_aux);
+          }
+        } else if (m_base + lane < p.M && n0 + 32 <= p.N) {
+          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + (long long)(m_base + lane) * p.ld_aux + n0;
+          if ((reinterpret_cast<uintptr_t>(ap) & 15) == 0) {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) dst[i] = *reinterpret_cast<const uint4*>(ap + 8 * i);
-            }
+            for (int i = 0; i < 4; ++i) dst[i] = *reinterpret_cast<const uint4*>(ap + 8 * i);
           }
         }
-      };
-      // The whole tile's second operand is requested before the accumulator is waited for: its DRAM latency hides
-      // behind the main loop of this tile instead of stalling the first chunk.
-      uint4 ax[CH][4] = {};
+      }
+    };
+    // The second operand runs one tile ahead of the accumulator: the registers of chunk c are refilled with the NEXT tile's
+    // chunk c as soon as this tile's chunk c has consumed them, so its DRAM latency hides behind the rest of this epilogue
+    // and the wait for the next accumulator instead of stalling every tile.
+    // (The column-scale epilogue issues other global loads per chunk, which would queue behind the early ones; it keeps
+    // loading at the top of its own tile.)
+    constexpr bool AUX_AHEAD = HAS_AUX && EPI != EPI_RESID_BF16;
+    uint4 ax[CH][4] = {};
+    if (AUX_AHEAD && blockIdx.x < total_tiles) {
+      int b0, tm0, tn0;
+      tile_coords(blockIdx.x, b0, tm0, tn0);
 #pragma unroll
-      for (int cc = 0; cc < CH; ++cc)
-        if (tn * BN + (c_begin + cc) * 32 < p.N) load_aux(c_begin + cc, ax[cc]);
+      for (int cc = 0; cc < CH; ++cc) load_aux(b0, tm0, tn0, c_begin + cc, ax[cc]);
+    }
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int b, tm, tn;
+      tile_coords(tile, b, tm, tn);
+      const int next = tile + gridDim.x;
+      int nb = 0, ntm = 0, ntn = 0;
+      if (next < total_tiles) tile_coords(next, nb, ntm, ntn);
+      const int m = tm * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      const int m_base = tm * BM + quarter * 32;
+      if constexpr (HAS_AUX && !AUX_AHEAD) {
+#pragma unroll
+        for (int cc = 0; cc < CH; ++cc) load_aux(b, tm, tn, c_begin + cc, ax[cc]);
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, ST_WAIT_TMEM_FULL, tile)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < CH; ++cc) {
         const int c = c_begin + cc;
         const int n0 = tn * BN + c * 32;
-        if (n0 >= p.N) break;                     // warp-uniform
-        uint32_t rr[32];
-        PGB_TMEM_LD32(taddr + c * 32, rr);
-        tmem_wait_ld();
-        if constexpr (BF16_OUT) {
-          if (staged_ok && n0 + 32 <= p.N) epilogue_chunk_staged<EPI>(p, b, m_base, lane, n0, rr, ax[cc], stg);
-          else if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax[cc]);
-        } else {
-          if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax[cc]);
+        if (n0 < p.N) {                           // warp-uniform
+          uint32_t rr[32];
+          PGB_TMEM_LD32(taddr + c * 32, rr);
+          tmem_wait_ld();
+          if constexpr (BF16_OUT) {
+            if (staged_ok && n0 + 32 <= p.N) epilogue_chunk_staged<EPI>(p, b, m_base, lane, n0, rr, ax[cc], stg);
+            else if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax[cc]);
+          } else {
+            if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax[cc]);
+          }
         }
+        if (AUX_AHEAD && next < total_tiles) load_aux(nb, ntm, ntn, c, ax[cc]);
       }
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
@@ -502,36 +545,36 @@ static CUtensorMap operand_map(const void* ptr, bool kmajor, int rows, int K, lo
 }
 
 template <int BN, bool AK, bool BKM, int EPI>
-static void launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const GemmKernelParams& p, int grid, cudaStream_t stream) {
+static void launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mx, const GemmKernelParams& p, int grid, cudaStream_t stream) {
   auto kern = gemm_tcgen05_kernel<BN, AK, BKM, EPI>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL);
     configured = true;
   }
-  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(ma, mb, p);
+  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(ma, mb, mx, p);
 }
 
 template <int BN, int EPI>
-static void launch_major(const GemmArgs& a, const CUtensorMap& ma, const CUtensorMap& mb, const GemmKernelParams& p, int grid,
+static void launch_major(const GemmArgs& a, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mx, const GemmKernelParams& p, int grid,
                          cudaStream_t stream) {
-  if (a.a_kmajor && a.b_kmajor) launch_variant<BN, true, true, EPI>(ma, mb, p, grid, stream);
-  else if (a.a_kmajor && !a.b_kmajor) launch_variant<BN, true, false, EPI>(ma, mb, p, grid, stream);
-  else if (!a.a_kmajor && a.b_kmajor) launch_variant<BN, false, true, EPI>(ma, mb, p, grid, stream);
-  else launch_variant<BN, false, false, EPI>(ma, mb, p, grid, stream);
+  if (a.a_kmajor && a.b_kmajor) launch_variant<BN, true, true, EPI>(ma, mb, mx, p, grid, stream);
+  else if (a.a_kmajor && !a.b_kmajor) launch_variant<BN, true, false, EPI>(ma, mb, mx, p, grid, stream);
+  else if (!a.a_kmajor && a.b_kmajor) launch_variant<BN, false, true, EPI>(ma, mb, mx, p, grid, stream);
+  else launch_variant<BN, false, false, EPI>(ma, mb, mx, p, grid, stream);
 }
 
 template <int BN>
-static void launch_epi(const GemmArgs& a, const CUtensorMap& ma, const CUtensorMap& mb, const GemmKernelParams& p, int grid,
+static void launch_epi(const GemmArgs& a, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mx, const GemmKernelParams& p, int grid,
                        cudaStream_t stream) {
   switch (a.epi) {
-    case EPI_BF16: launch_major<BN, EPI_BF16>(a, ma, mb, p, grid, stream); break;
-    case EPI_F32: launch_major<BN, EPI_F32>(a, ma, mb, p, grid, stream); break;
-    case EPI_F32_ATOMIC: launch_major<BN, EPI_F32_ATOMIC>(a, ma, mb, p, grid, stream); break;
-    case EPI_AXPBY_BF16: launch_major<BN, EPI_AXPBY_BF16>(a, ma, mb, p, grid, stream); break;
-    case EPI_RESID_BF16: launch_major<BN, EPI_RESID_BF16>(a, ma, mb, p, grid, stream); break;
-    case EPI_ACT_SQ: launch_major<BN, EPI_ACT_SQ>(a, ma, mb, p, grid, stream); break;
-    case EPI_MUL_ACTGRAD: launch_major<BN, EPI_MUL_ACTGRAD>(a, ma, mb, p, grid, stream); break;
+    case EPI_BF16: launch_major<BN, EPI_BF16>(a, ma, mb, mx, p, grid, stream); break;
+    case EPI_F32: launch_major<BN, EPI_F32>(a, ma, mb, mx, p, grid, stream); break;
+    case EPI_F32_ATOMIC: launch_major<BN, EPI_F32_ATOMIC>(a, ma, mb, mx, p, grid, stream); break;
+    case EPI_AXPBY_BF16: launch_major<BN, EPI_AXPBY_BF16>(a, ma, mb, mx, p, grid, stream); break;
+    case EPI_RESID_BF16: launch_major<BN, EPI_RESID_BF16>(a, ma, mb, mx, p, grid, stream); break;
+    case EPI_ACT_SQ: launch_major<BN, EPI_ACT_SQ>(a, ma, mb, mx, p, grid, stream); break;
+    case EPI_MUL_ACTGRAD: launch_major<BN, EPI_MUL_ACTGRAD>(a, ma, mb, mx, p, grid, stream); break;
     default: throw std::runtime_error("gemm: unknown epilogue");
   }
 }
@@ -576,6 +619,7 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.wait_flag = a.wait_flag;
   p.wait_value = a.wait_value;
+  { const char* e = getenv("PGB_GEMM_DIAG"); p.diag = e ? atoi(e) : 0; }
   for (int k = 0; k < 2; ++k) {
     p.seg_rows[k] = a.seg_rows[k];
     p.seg_D[k] = a.seg_D[k];
@@ -586,8 +630,13 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   const CUtensorMap mb = operand_map(a.B, a.b_kmajor, a.N, a.K, a.ldb, a.stride_b, a.batch, bn);
   const int total = p.tiles_m * p.tiles_n * p.splits * a.batch;
   const int grid = std::min(total, num_sms());
-  if (bn == 256) launch_epi<256>(a, ma, mb, p, grid, stream);
-  else launch_epi<128>(a, ma, mb, p, grid, stream);
+  // L2 prefetch of the epilogue's second operand ([batch][M][N] bf16, row pitch ld_aux) one tile ahead of its readers
+  const bool has_aux = a.aux != nullptr && (a.epi == EPI_AXPBY_BF16 || a.epi == EPI_MUL_ACTGRAD);
+  p.aux_l2_prefetch = (has_aux && !(p.diag & 4) && a.ld_aux % 8 == 0 && (a.batch == 1 || a.stride_aux % 8 == 0) &&
+                       (reinterpret_cast<uintptr_t>(a.aux) & 15) == 0 && total > grid) ? 1 : 0;
+  const CUtensorMap mx = p.aux_l2_prefetch ? operand_map(a.aux, true, a.M, a.N, a.ld_aux, a.stride_aux, a.batch, BM) : ma;
+  if (bn == 256) launch_epi<256>(a, ma, mb, mx, p, grid, stream);
+  else launch_epi<128>(a, ma, mb, mx, p, grid, stream);
 }
 
 }  // namespace pgb

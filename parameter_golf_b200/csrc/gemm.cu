@@ -42,10 +42,14 @@ struct GemmKernelParams {
   int wait_value;
   int seg_rows[2];        // fp32 epilogues: rows >= seg_rows[k] (> 0) are written to seg_D[k] as row m - seg_rows[k]
   float* seg_D[2];
-  int diag;
   int aux_l2_prefetch;     // the producer warp pulls the next tile's second operand into L2 through `map_x`
 };
 
+constexpr int STG_PITCH = 64;
+constexpr int STG_WARP_BYTES = 32 * STG_PITCH;      // one 32-row x 32-column bf16 chunk
+
+// Epilogue staging: two chunk-sized slots per epilogue warp. A slot first receives a chunk of the epilogue's second
+// operand (cp.async, two chunks ahead of its use), is read, then stages the output chunk in place.
 template <int BN>
 struct GemmSmem {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -53,13 +57,14 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * 32 * 80 /*epilogue staging*/;
+  static constexpr int STG_BYTES = 8 * 2 * STG_WARP_BYTES;
+  static constexpr int TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + STG_BYTES;
 };
 
 __device__ __forceinline__ float act_fn(float x, float slope) { return x >= 0.f ? x : slope * x; }
 
 template <int EPI>
-__device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b, int m, int n0, const uint32_t (&r)[32], const uint4 (&ax)[4]) {
+__device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b, int m, int n0, const uint32_t (&r)[32]) {
   // One thread: row m, columns n0 .. n0+31 of batch b. Caller guarantees m < M.
   const bool full = (n0 + 32 <= p.N);
   const long long off = (long long)b * p.stride_d + (long long)m * p.ldd + n0;
@@ -97,7 +102,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
       if (vec && ((reinterpret_cast<uintptr_t>(ap) & 15) == 0)) {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
-          const uint4 q = ax[i >> 3];            // prefetched by the caller one chunk ahead
+          const uint4 q = *reinterpret_cast<const uint4*>(ap + i);
           float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
           a[i] = f0.x; a[i + 1] = f0.y; a[i + 2] = f1.x; a[i + 3] = f1.y;
           a[i + 4] = f2.x; a[i + 5] = f2.y; a[i + 6] = f3.x; a[i + 7] = f3.y;
@@ -151,32 +156,26 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
 // Aligned bf16 epilogue with coalesced global traffic. A thread owns one accumulator row, but 16-byte accesses of 32
 // different rows per instruction touch half a sector each; here rows are exchanged through a per-warp shared-memory
 // tile (32 rows x 64 B) so that every global load/store instruction covers 8 rows x 64 contiguous bytes.
-// `ax` holds the aux operand in that coalesced pattern: piece i = row (i*8 + lane/4), bytes (lane%4)*16 .. +16.
+// `auxs` is this chunk of the second operand, already in shared memory in the same swizzled layout (cp.async wrote it).
 // The tile is XOR-swizzled: the 16-byte piece p of row r sits at piece p ^ ((r >> 1) & 3). Both access patterns are
 // then free of bank conflicts (8 consecutive rows x one piece, and 2 consecutive rows x 4 pieces, each cover all 32
 // banks once); a padded pitch can only satisfy one of the two.
-constexpr int STG_PITCH = 64;
-constexpr int STG_WARP_BYTES = 32 * 80;     // carve-out per warp (unchanged footprint)
 __device__ __forceinline__ int stg_off(int row, int piece) { return row * STG_PITCH + ((piece ^ ((row >> 1) & 3)) << 4); }
 
 template <int EPI>
 __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p, int b, int m_base, int lane, int n0, const uint32_t (&r)[32],
-                                                      const uint4 (&ax)[4], uint8_t* stg) {
+                                                      const uint8_t* auxs, uint8_t* stg) {
   constexpr bool HAS_AUX = (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD);
   const int srow = lane >> 2, spc = lane & 3;
   float a[32];
   if constexpr (HAS_AUX) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(stg + stg_off(i * 8 + srow, spc)) = ax[i];
-    __syncwarp();
-#pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint4 q = *reinterpret_cast<const uint4*>(stg + stg_off(lane, i));
+      const uint4 q = *reinterpret_cast<const uint4*>(auxs + stg_off(lane, i));
       const float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z), f3 = unpack_bf16x2(q.w);
       a[8 * i] = f0.x; a[8 * i + 1] = f0.y; a[8 * i + 2] = f1.x; a[8 * i + 3] = f1.y;
       a[8 * i + 4] = f2.x; a[8 * i + 5] = f2.y; a[8 * i + 6] = f3.x; a[8 * i + 7] = f3.y;
     }
-    __syncwarp();
   }
   float o[32], o2[32];
   float cs[32];
@@ -246,7 +245,7 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p,
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = m_base + i * 8 + srow;
-      if (row < p.M && !(p.diag & 1)) *reinterpret_cast<uint4*>(d + (long long)row * p.ldd) = *reinterpret_cast<const uint4*>(stg + stg_off(i * 8 + srow, spc));
+      if (row < p.M) *reinterpret_cast<uint4*>(d + (long long)row * p.ldd) = *reinterpret_cast<const uint4*>(stg + stg_off(i * 8 + srow, spc));
     }
     __syncwarp();
   };
@@ -414,7 +413,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;                 // TMEM lane quarter this warp may access
     const int half = (warp - 2) >> 2;             // which half of the tile's columns
-    uint8_t* stg = smem + S::TILE_BYTES + 256 + (warp - 2) * STG_WARP_BYTES;
+    uint8_t* slots = smem + S::TILE_BYTES + 256 + (warp - 2) * 2 * STG_WARP_BYTES;
     const bool staged_ok = (p.ldd % 8 == 0) && (p.stride_d % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15) == 0) &&
                            (p.aux == nullptr || ((p.ld_aux % 8 == 0) && (p.stride_aux % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.aux) & 15) == 0))) &&
                            (p.D2 == nullptr || ((reinterpret_cast<uintptr_t>(p.D2) & 15) == 0));
@@ -433,40 +432,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tm = r / p.tiles_n;
       tn = r - tm * p.tiles_n;
     };
-    // Second operand of chunk c of tile (b, tm, tn), in the pattern its consumer expects.
-    auto load_aux = [&](int b, int tm, int tn, int c, uint4 (&dst)[4]) {
+    // Second operand: a 32-row x 32-column chunk goes into one of this warp's two staging slots with 16-byte asynchronous
+    // copies (8 rows x 64 contiguous bytes per instruction), one commit group per chunk, two chunks ahead of its use
+    // (across the tile boundary too), so its DRAM latency hides behind the chunks processed meanwhile. cp.async is used
+    // rather than loads into registers because pending register loads share the warp's few scoreboard counters with the
+    // shared-memory and tensor-memory traffic of those chunks, which then wait for DRAM as well. The slot is read by the
+    // thread that owns the row, reused in place to stage the output chunk, and refilled once the stores have read it.
+    const bool aux_async = HAS_AUX && staged_ok;
+    auto issue_aux = [&](int b, int tm, int tn, int cc, uint8_t* slot) {
       if constexpr (HAS_AUX) {
-        const int n0 = tn * BN + c * 32;
-        if ((p.diag & 2) || n0 >= p.N) return;
-        const int m_base = tm * BM + quarter * 32;
-        if (staged_ok && n0 + 32 <= p.N) {          // coalesced pattern: 8 rows x 64 B per instruction
+        const int n0 = tn * BN + (c_begin + cc) * 32;
+        if (n0 + 32 <= p.N) {
+          const int m_base = tm * BM + quarter * 32;
           const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + n0 + (lane & 3) * 8;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int row = m_base + i * 8 + (lane >> 2);
-            if (row < p.M) dst[i] = *reinterpret_cast<const uint4*>(ap + (long long)row * p.ld_aux);
-          }
-        } else if (m_base + lane < p.M && n0 + 32 <= p.N) {
-          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)b * p.stride_aux + (long long)(m_base + lane) * p.ld_aux + n0;
-          if ((reinterpret_cast<uintptr_t>(ap) & 15) == 0) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = *reinterpret_cast<const uint4*>(ap + 8 * i);
+            if (row < p.M) cp_async16(slot + stg_off(i * 8 + (lane >> 2), lane & 3), ap + (long long)row * p.ld_aux);
           }
         }
+        cp_async_commit();          // one group per chunk, also when nothing was copied: the wait below counts groups
       }
     };
-    // The second operand runs one tile ahead of the accumulator: the registers of chunk c are refilled with the NEXT tile's
-    // chunk c as soon as this tile's chunk c has consumed them, so its DRAM latency hides behind the rest of this epilogue
-    // and the wait for the next accumulator instead of stalling every tile.
-    // (The column-scale epilogue issues other global loads per chunk, which would queue behind the early ones; it keeps
-    // loading at the top of its own tile.)
-    constexpr bool AUX_AHEAD = HAS_AUX && EPI != EPI_RESID_BF16;
-    uint4 ax[CH][4] = {};
-    if (AUX_AHEAD && blockIdx.x < total_tiles) {
+    static_assert(CH % 2 == 0, "slot parity follows the chunk index within the tile");
+    if (aux_async && blockIdx.x < total_tiles) {
       int b0, tm0, tn0;
       tile_coords(blockIdx.x, b0, tm0, tn0);
-#pragma unroll
-      for (int cc = 0; cc < CH; ++cc) load_aux(b0, tm0, tn0, c_begin + cc, ax[cc]);
+      issue_aux(b0, tm0, tn0, 0, slots);
+      issue_aux(b0, tm0, tn0, 1, slots + STG_WARP_BYTES);
     }
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       int b, tm, tn;
@@ -477,28 +470,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m = tm * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       const int m_base = tm * BM + quarter * 32;
-      if constexpr (HAS_AUX && !AUX_AHEAD) {
-#pragma unroll
-        for (int cc = 0; cc < CH; ++cc) load_aux(b, tm, tn, c_begin + cc, ax[cc]);
-      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, ST_WAIT_TMEM_FULL, tile)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < CH; ++cc) {
         const int c = c_begin + cc;
         const int n0 = tn * BN + c * 32;
+        uint8_t* slot = slots + (cc & 1) * STG_WARP_BYTES;
         if (n0 < p.N) {                           // warp-uniform
           uint32_t rr[32];
           PGB_TMEM_LD32(taddr + c * 32, rr);
-          tmem_wait_ld();
+          if constexpr (HAS_AUX) {
+            if (aux_async) {                      // two groups are pending; this chunk's is the older one
+              cp_async_wait<1>();
+              __syncwarp();
+            }
+          }
+          PGB_TMEM_WAIT_LD32(rr);
           if constexpr (BF16_OUT) {
-            if (staged_ok && n0 + 32 <= p.N) epilogue_chunk_staged<EPI>(p, b, m_base, lane, n0, rr, ax[cc], stg);
-            else if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax[cc]);
+            if (staged_ok && n0 + 32 <= p.N && (aux_async || !HAS_AUX)) epilogue_chunk_staged<EPI>(p, b, m_base, lane, n0, rr, slot, slot);
+            else if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr);
           } else {
-            if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr, ax[cc]);
+            if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr);
           }
         }
-        if (AUX_AHEAD && next < total_tiles) load_aux(nb, ntm, ntn, c, ax[cc]);
+        if constexpr (HAS_AUX) {
+          if (aux_async) {
+            __syncwarp();                         // every lane is done with this slot
+            if (cc + 2 < CH) issue_aux(b, tm, tn, cc + 2, slot);
+            else if (next < total_tiles) issue_aux(nb, ntm, ntn, cc + 2 - CH, slot);
+            else cp_async_commit();
+          }
+        }
       }
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
@@ -619,7 +622,6 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.wait_flag = a.wait_flag;
   p.wait_value = a.wait_value;
-  { const char* e = getenv("PGB_GEMM_DIAG"); p.diag = e ? atoi(e) : 0; }
   for (int k = 0; k < 2; ++k) {
     p.seg_rows[k] = a.seg_rows[k];
     p.seg_D[k] = a.seg_D[k];
@@ -632,7 +634,7 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   const int grid = std::min(total, num_sms());
   // L2 prefetch of the epilogue's second operand ([batch][M][N] bf16, row pitch ld_aux) one tile ahead of its readers
   const bool has_aux = a.aux != nullptr && (a.epi == EPI_AXPBY_BF16 || a.epi == EPI_MUL_ACTGRAD);
-  p.aux_l2_prefetch = (has_aux && !(p.diag & 4) && a.ld_aux % 8 == 0 && (a.batch == 1 || a.stride_aux % 8 == 0) &&
+  p.aux_l2_prefetch = (has_aux && a.ld_aux % 8 == 0 && (a.batch == 1 || a.stride_aux % 8 == 0) &&
                        (reinterpret_cast<uintptr_t>(a.aux) & 15) == 0 && total > grid) ? 1 : 0;
   const CUtensorMap mx = p.aux_l2_prefetch ? operand_map(a.aux, true, a.M, a.N, a.ld_aux, a.stride_aux, a.batch, BM) : ma;
   if (bn == 256) launch_epi<256>(a, ma, mb, mx, p, grid, stream);

@@ -21,6 +21,7 @@ class BpbLuts:
     base_bytes: np.ndarray          # int16 [V]
     has_leading_space: np.ndarray   # bool  [V]
     is_boundary: np.ndarray         # bool  [V]
+    sidecar: "np.ndarray | None" = None   # float32 [tokens]: bytes of the token at each validation position, when given
 
     @staticmethod
     def placeholder(vocab: int) -> "BpbLuts":
@@ -62,7 +63,18 @@ class BpbLuts:
         byte_ids = {i for i in range(n) if sp.is_byte(i)}
         return BpbLuts.from_pieces([sp.id_to_piece(i) for i in range(n)], vocab, control, byte_ids)
 
-    def token_bytes(self, prev_ids: np.ndarray, tgt_ids: np.ndarray) -> np.ndarray:
+    def with_sidecar(self, bytes_per_position: np.ndarray) -> "BpbLuts":
+        """Byte counts read from a sidecar aligned one-to-one with the validation tokens (CaseOps / SP8192 validation,
+        ``pg-data/src/token_stream.rs:354-369``) instead of derived from token surfaces."""
+        return BpbLuts(self.base_bytes, self.has_leading_space, self.is_boundary, np.asarray(bytes_per_position, dtype=np.float32))
+
+    def token_bytes(self, prev_ids: np.ndarray, tgt_ids: np.ndarray, positions: "np.ndarray | None" = None) -> np.ndarray:
+        """Bytes of each target token. ``positions`` are the targets' indices in the validation stream; they select
+        from the sidecar when one is attached."""
+        if self.sidecar is not None:
+            if positions is None:
+                raise ValueError("a byte sidecar is attached: token positions are required")
+            return self.sidecar[np.asarray(positions, dtype=np.int64)].astype(np.float64)
         b = self.base_bytes[tgt_ids].astype(np.int64)
         b += (self.has_leading_space[tgt_ids] & ~self.is_boundary[prev_ids]).astype(np.int64)
         return b

@@ -216,10 +216,30 @@ class DistributedTokenLoader:
         self.stream.restore(st)
 
 
+def is_byte_sidecar_path(path: str) -> bool:
+    """Byte-count sidecars share the shard format and often the directory of the token shards; their file names carry
+    ``_bytes_`` or ``val_bytes`` (``pg-data/src/token_stream.rs:347-352``)."""
+    name = os.path.basename(path)
+    return "_bytes_" in name or "val_bytes" in name
+
+
+def load_validation_byte_sidecar(pattern: str, max_tokens: Optional[int] = None) -> np.ndarray:
+    """Bytes per validation position as float32, from shards aligned one-to-one with the token shards
+    (``pg-data/src/token_stream.rs:354-369``). ``max_tokens`` keeps the same ``max_tokens + 1`` prefix as the token loader."""
+    files = sorted(glob.glob(pattern))
+    if not files:
+        raise FileNotFoundError(f"no byte sidecar matches {pattern!r}")
+    raw = np.concatenate([np.asarray(open_shard(f)) for f in files])
+    if max_tokens is not None:
+        raw = raw[: max_tokens + 1]
+    return raw.astype(np.float32)
+
+
 def load_validation_tokens(pattern: str, seq_len: int, max_tokens: Optional[int] = None) -> np.ndarray:
     """All validation shards concatenated, truncated to ``k*seq_len + 1`` tokens
-    (``train_gpt.py:211-219``; limit variant ``pg-data/src/token_stream.rs:300-336``)."""
-    files = sorted(glob.glob(pattern))
+    (``train_gpt.py:211-219``; limit variant ``pg-data/src/token_stream.rs:300-336``). Byte-count sidecars that the
+    pattern happens to match are left out."""
+    files = sorted(f for f in glob.glob(pattern) if not is_byte_sidecar_path(f))
     if not files:
         raise FileNotFoundError(f"no shard matches {pattern!r}")
     toks = np.concatenate([np.asarray(open_shard(f)) for f in files])

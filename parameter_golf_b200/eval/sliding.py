@@ -82,16 +82,18 @@ def score_windows(nll_fn: Callable, tokens: np.ndarray, starts: List[int], windo
         x = np.zeros((len(batch), window), dtype=np.int64)
         y = np.zeros((len(batch), window), dtype=np.int64)
         mask = np.zeros((len(batch), window), dtype=bool)
+        pos = np.zeros((len(batch), window), dtype=np.int64)          # index of each target in the validation stream
         for i, ws in enumerate(batch):
             s, wlen = scored_range(ws, total, window, stride)
             x[i, :wlen] = tok64[ws:ws + wlen]
             y[i, :wlen] = tok64[ws + 1:ws + wlen + 1]
+            pos[i, :wlen] = np.arange(ws + 1, ws + wlen + 1)
             mask[i, s:wlen] = True
         nll = nll_fn(torch.from_numpy(x).to(device), torch.from_numpy(y).to(device))
         mt = torch.from_numpy(mask).to(nll.device)
         sums.loss += float((nll.double() * mt).sum())
         sums.tokens += float(mask.sum())
-        sums.bytes += float(luts.token_bytes(x[mask], y[mask]).sum())
+        sums.bytes += float(luts.token_bytes(x[mask], y[mask], pos[mask]).sum())
     return sums
 
 
@@ -119,7 +121,7 @@ def eval_contiguous(nll_fn: Callable, tokens: np.ndarray, seq_len: int, luts: Bp
         nll = nll_fn(torch.from_numpy(x).to(device), torch.from_numpy(y).to(device))
         sums.loss += float(nll.double().sum())
         sums.tokens += float(x.size)
-        sums.bytes += float(luts.token_bytes(x.reshape(-1), y.reshape(-1)).sum())
+        sums.bytes += float(luts.token_bytes(x.reshape(-1), y.reshape(-1), np.arange(s0 * seq_len + 1, s1 * seq_len + 1)).sum())
     return sums.all_reduce(device).result()
 
 

@@ -73,6 +73,12 @@ def main(argv=None) -> int:
     luts = {"tokenizer": lambda: BpbLuts.from_sentencepiece(spec.eval.tokenizer_vocab_path, m.vocab_size),
             "seeded": lambda: BpbLuts.seeded(m.vocab_size, spec.eval.byte_table_seed),
             "placeholder": lambda: BpbLuts.placeholder(m.vocab_size)}[a.bytes]()
+    if spec.eval.caseops_byte_sidecar_pattern:     # byte counts per validation position instead of per token surface
+        from .data.shards import load_validation_byte_sidecar
+        side = load_validation_byte_sidecar(spec.eval.caseops_byte_sidecar_pattern)
+        if side.shape[0] < val.shape[0]:
+            raise SystemExit(f"byte sidecar has {side.shape[0]} entries, the validation split {val.shape[0]} tokens")
+        luts = luts.with_sidecar(side[: val.shape[0]])
     if a.device == "cpu":
         from .models.runner import OracleRunner
         runner = OracleRunner(m, params)

@@ -404,6 +404,9 @@ class VariantRunner:
                                          min(spec.eval.max_tokens or (1 << 62), 8 * m.eval_seq_len))
             luts = (BpbLuts.from_sentencepiece(spec.eval.tokenizer_vocab_path, m.vocab_size) if spec.eval.tokenizer_vocab_path
                     else BpbLuts.seeded(m.vocab_size, spec.eval.byte_table_seed))
+            if spec.eval.caseops_byte_sidecar_pattern:
+                from .data.shards import load_validation_byte_sidecar
+                luts = luts.with_sidecar(load_validation_byte_sidecar(spec.eval.caseops_byte_sidecar_pattern)[: val.shape[0]])
             if t.backend == "cpu":
                 runner = OracleRunner(m, eval_params)
                 edev = "cpu"

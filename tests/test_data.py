@@ -179,3 +179,39 @@ def test_native_loader_rejects_bad_shards(tmp_path):
     p.write_bytes(hdr.tobytes() + b"\x00" * 18)       # one token short
     with pytest.raises(RuntimeError, match="does not match"):
         Native(str(tmp_path / "bad_train_*.bin"))
+
+
+def test_byte_sidecar_is_filtered_from_tokens_and_drives_the_byte_count(tmp_path):
+    """Sidecar shards share the directory and the format of the token shards; they must not be read as tokens, and when
+    attached to the byte tables the byte count of a scored token is the sidecar entry at its position."""
+    import torch
+    from parameter_golf_b200.data.bpb import BpbLuts
+    from parameter_golf_b200.data.shards import (is_byte_sidecar_path, load_validation_byte_sidecar, load_validation_tokens,
+                                                 write_shard)
+    from parameter_golf_b200.eval.sliding import eval_contiguous, eval_sliding
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, 64, 16 * 8 + 1).astype(np.uint16)
+    side = rng.integers(1, 9, toks.shape[0]).astype(np.uint16)
+    write_shard(str(tmp_path / "fineweb_val_000000.bin"), toks)
+    write_shard(str(tmp_path / "fineweb_val_bytes_000000.bin"), side)
+    assert is_byte_sidecar_path("x/fineweb_val_bytes_000000.bin") and is_byte_sidecar_path("val_bytes.bin")
+    assert not is_byte_sidecar_path("x/fineweb_val_000000.bin")
+    got = load_validation_tokens(str(tmp_path / "fineweb_val_*.bin"), 16)
+    assert np.array_equal(got, toks)                                   # the sidecar matched the glob and was left out
+    sc = load_validation_byte_sidecar(str(tmp_path / "fineweb_val_bytes_*.bin"))
+    assert sc.dtype == np.float32 and np.array_equal(sc, side.astype(np.float32))
+    luts = BpbLuts.seeded(64).with_sidecar(sc)
+    nll = lambda x, y: torch.ones(x.shape, dtype=torch.float32)
+    loss, bpb = eval_contiguous(nll, got, 16, luts)
+    want = (1.0 / np.log(2.0)) * (128 / side[1:129].sum())
+    assert loss == pytest.approx(1.0) and bpb == pytest.approx(want, rel=1e-6)
+    from parameter_golf_b200.eval.sliding import scored_range, window_starts
+    nbytes = ntok = 0.0                                                # the tail windows re-score their last tokens, as in the reference
+    for ws in window_starts(128, 16, 4):
+        s0, wlen = scored_range(ws, 128, 16, 4)
+        nbytes += side[ws + 1 + s0: ws + 1 + wlen].sum()
+        ntok += wlen - s0
+    loss2, bpb2 = eval_sliding(nll, got, 16, 4, luts)
+    assert bpb2 == pytest.approx((1.0 / np.log(2.0)) * (ntok / nbytes), rel=1e-6)
+    with pytest.raises(ValueError):
+        luts.token_bytes(np.array([1]), np.array([2]))

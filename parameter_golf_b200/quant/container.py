@@ -8,7 +8,8 @@ Byte formats (all little-endian):
   then u32 metadata_len and the metadata JSON.
 * **PGPG** (``pg-quant/src/compress.rs:33-53``): ``"PGPG"``, u32 version=1, u64 raw_len, u32 chunk_bytes,
   u32 group_count, then per group u32 raw_len, u32 comp_len, one zstd frame.
-* Sniffing (``compress.rs:101-109``): ``PGPG`` -> per-group, ``PGRS`` -> raw, anything else -> one zstd frame.
+* Sniffing (``compress.rs:101-109``): ``PGPG`` -> per-group, ``PGRS`` -> raw, the xz magic -> one xz stream (``lzma9``,
+  which the reference declares but does not write), anything else -> one zstd frame.
 
 The image ships the zstd runtime library without headers or Python bindings, so the five entry
 points used here are declared through ctypes.
@@ -200,6 +201,9 @@ def compress_payload(raw: bytes, mode: str) -> bytes:
         return raw
     if mode == "zstd22":
         return zstd_compress(raw, 22)
+    if mode == "lzma9":        # one xz stream, preset 9 (the reference declares this mode and rejects it, export.rs:195-198)
+        import lzma
+        return lzma.compress(raw, format=lzma.FORMAT_XZ, preset=9 | lzma.PRESET_EXTREME)
     if mode == "pergroup":
         return compress_pergroup(raw)
     raise ArtifactError(f"unsupported compression mode {mode!r}")
@@ -210,6 +214,12 @@ def decompress_payload(buf: bytes) -> bytes:
         return decompress_pergroup(buf)
     if buf[:4] == b"PGRS":
         return buf
+    if buf[:6] == b"\xfd7zXZ\x00":
+        import lzma
+        try:
+            return lzma.decompress(buf, format=lzma.FORMAT_XZ)
+        except lzma.LZMAError as e:
+            raise ArtifactError(f"xz decompression failed: {e}") from e
     return zstd_decompress(buf)
 
 

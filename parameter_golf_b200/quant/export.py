@@ -118,7 +118,11 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
 
 
 def export_model(spec: RunSpec, params: Dict[str, torch.Tensor], path: Optional[str] = None, precomputed=None) -> bytes:
-    blob = C.compress_payload(build_artifact(spec, params, precomputed), spec.quant.compression)
+    if spec.quant.scheme == "int8_zlib":         # the baseline trainer's own artifact, outside the PGRS family
+        from .int8_baseline import export_int8_zlib
+        blob, _ = export_int8_zlib({k: v.detach().float().cpu() for k, v in params.items()})
+    else:
+        blob = C.compress_payload(build_artifact(spec, params, precomputed), spec.quant.compression)
     if path:
         os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
         with open(path, "wb") as f:
@@ -136,6 +140,14 @@ def _np(rec: C.TensorRecord) -> np.ndarray:
 
 def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32) -> Dict[str, torch.Tensor]:
     """De-quantise an artifact into a parameter dict laid out as `param_shapes`."""
+    if blob[:1] == b"\x78":                      # zlib stream: the baseline's int8 export
+        import zlib
+        from .int8_baseline import MAGIC, dequantize_state_dict_int8, deserialize
+        raw = zlib.decompress(blob)
+        if raw[:4] != MAGIC:
+            raise C.ArtifactError("zlib stream does not hold an int8 baseline container")
+        out = dequantize_state_dict_int8(deserialize(raw))
+        return {k: v.to(device=device, dtype=dtype if v.is_floating_point() else v.dtype) for k, v in out.items()}
     recs, metadata = C.read_pgrs(C.decompress_payload(blob))
     md = json.loads(metadata)
     m = spec.model

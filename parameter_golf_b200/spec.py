@@ -26,7 +26,8 @@ from typing import Any, Optional
 RUN_MODES = ("smoke", "proxy", "record_shaped_proxy", "record")
 TRAIN_BACKENDS = ("cpu", "cuda_single", "cuda_single_parity", "cuda_distributed")
 DIST_OPT_BACKENDS = ("all_reduce_replicated_muon", "sharded_parallel_muon")
-QUANT_SCHEMES = ("none", "gptq_lite_int6", "mixed_int5_int6", "aggressive", "tight_int7_int4", "full_gptq_int6")
+QUANT_SCHEMES = ("none", "gptq_lite_int6", "mixed_int5_int6", "aggressive", "tight_int7_int4", "full_gptq_int6",
+                 "int8_zlib")       # int8_zlib: the baseline trainer's per-row int8 + zlib-9 export (train_gpt.py:342-422)
 COMPRESSION_MODES = ("none", "zstd22", "lzma9", "pergroup")
 CALIBRATION_MODES = ("disabled", "self_generated")
 ADAPTATION_BACKENDS = ("none", "cpu_q_only", "gpu_lora_phased", "full_sgd", "lact", "slot")
@@ -410,7 +411,6 @@ class RunSpec:
         chk(t.distributed_optimizer_backend in DIST_OPT_BACKENDS, "unknown distributed_optimizer_backend")
         chk(q.scheme in QUANT_SCHEMES, f"quant.scheme must be one of {QUANT_SCHEMES}")
         chk(q.compression in COMPRESSION_MODES, "unknown quant.compression")
-        chk(q.compression != "lzma9", "compression lzma9 is declared but not supported by the artifact writer")
         chk(q.calibration in CALIBRATION_MODES, "unknown quant.calibration")
         chk(e.adaptation_backend in ADAPTATION_BACKENDS, "unknown eval.adaptation_backend")
         chk(t.save_layer_acts in ("all", "edges", "inner", "recurrent", "none"), "train.save_layer_acts must be all|edges|inner|recurrent|none")

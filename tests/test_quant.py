@@ -52,8 +52,12 @@ def test_zstd_and_pergroup_roundtrip_and_sniffing():
     g = C.compress_pergroup(raw, chunk_bytes=300)
     assert g[:4] == b"PGPG" and struct.unpack_from("<IQII", g, 4) == (1, len(raw), 300, 4)
     assert C.decompress_payload(g) == raw and C.decompress_payload(raw) == raw
+    x = C.compress_payload(raw, "lzma9")
+    assert x[:6] == b"\xfd7zXZ\x00" and len(x) < len(raw) and C.decompress_payload(x) == raw
     with pytest.raises(C.ArtifactError):
-        C.compress_payload(raw, "lzma9")
+        C.decompress_payload(x[:-8] + b"\x00" * 8)
+    with pytest.raises(C.ArtifactError):
+        C.compress_payload(raw, "brotli")
 
 
 @pytest.mark.parametrize("bits", [4, 5, 6, 7, 8])
@@ -220,3 +224,50 @@ def test_native_artifact_primitives_match_numpy_forms():
         bad[40] ^= 0xFF
         with pytest.raises(C.ArtifactError):
             C.read_pgrs(bytes(bad), native=nat)
+
+
+def test_int8_zlib_baseline_export_round_trip():
+    """Per-row int8 with the 99.99984 % clip, small tensors kept in fp16 / control tensors in fp32, zlib-9 container."""
+    import zlib
+    from parameter_golf_b200.quant import int8_baseline as I8
+    g = torch.Generator().manual_seed(0)
+    state = {"w": torch.randn(300, 400, generator=g), "bank": torch.randn(3, 160, 200, generator=g) * 0.1,
+             "small": torch.randn(8, 16, generator=g), "q_gain": torch.randn(8, generator=g), "ids": torch.arange(5)}
+    q, s = I8.quantize_float_tensor(state["w"])
+    ref_clip = torch.quantile(state["w"].abs(), I8.CLIP_Q, dim=1)
+    ref_scale = (ref_clip / 127.0).clamp_min(1.0 / 127.0)
+    assert torch.allclose(s.float(), ref_scale.to(torch.float16).float())
+    ref_q = torch.clamp(torch.round(torch.maximum(torch.minimum(state["w"], ref_clip[:, None]), -ref_clip[:, None]) / ref_scale[:, None]), -127, 127)
+    assert torch.equal(q, ref_q.to(torch.int8))
+    obj, stats = I8.quantize_state_dict_int8(state)
+    assert set(obj["quantized"]) == {"w", "bank"} and set(obj["passthrough"]) == {"small", "q_gain", "ids"}
+    assert obj["passthrough"]["small"].dtype == torch.float16 and obj["passthrough"]["q_gain"].dtype == torch.float32
+    assert obj["scales"]["bank"].shape == (3, 160) and obj["qmeta"]["w"]["scheme"] == "per_row"
+    assert stats["param_count"] == sum(t.numel() for t in state.values())
+    blob, st = I8.export_int8_zlib(state)
+    assert blob[:1] == b"\x78" and zlib.decompress(blob)[:4] == I8.MAGIC and st["compressed_bytes"] == len(blob) < st["raw_bytes"]
+    back = I8.load_int8_zlib(blob)
+    assert torch.equal(back["ids"], state["ids"]) and torch.equal(back["q_gain"], state["q_gain"])
+    assert back["small"].dtype == torch.float32 and torch.allclose(back["small"], state["small"], atol=2e-3)
+    for k in ("w", "bank"):
+        err = (back[k] - state[k]).abs().max() / state[k].abs().max()
+        assert back[k].dtype == torch.float32 and float(err) < 0.02, (k, float(err))
+    with pytest.raises(ValueError):
+        I8.deserialize(b"nope" + b"\x00" * 16)
+
+
+def test_int8_zlib_scheme_through_export_and_load():
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.quant.export import export_model, load_artifact
+    from parameter_golf_b200.spec import family_preset
+    s = family_preset("tiny_cpu")
+    s.quant.scheme = "int8_zlib"
+    s.validate()
+    p = gpt.init_params(s.model, 1)
+    blob = export_model(s, p)
+    back = load_artifact(blob, s)
+    assert set(back) == set(p)
+    for k in p:
+        assert back[k].shape == p[k].shape
+        # the scale floor of 1/127 (reference rule) bounds the error of small-valued matrices by half a step
+        assert float((back[k] - p[k]).abs().max()) <= 0.02 * float(p[k].abs().max()) + 0.5 / 127 + 1e-3, k

@@ -41,7 +41,7 @@ def test_overrides():
         s.apply_overrides(["train.nope=1"])
 
 
-@pytest.mark.parametrize("ov", ["model.num_heads=7", "model.rope.mode=yarn", "quant.compression=lzma9", "train.world_size=2",
+@pytest.mark.parametrize("ov", ["model.num_heads=7", "model.rope.mode=yarn", "quant.compression=brotli", "train.world_size=2",
                                 "model.vocab_size=70000", "quant.matrix_bits=3", "train.batch_tokens=1000"])
 def test_validation_rejects(ov):
     with pytest.raises(ValueError):

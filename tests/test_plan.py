@@ -52,3 +52,17 @@ def test_plan_cli_prints_key_value_lines(capsys):
     assert main(["plan", "--family", "record_11l", "train.save_layer_acts=edges"]) == 0
     out = capsys.readouterr().out
     assert "plan.saved_mode=edges" in out and "plan.saved_blocks=5" in out and "plan.block.10.0=decoder:xsa+saved" in out
+
+
+def test_preliminary_sweep_script_runs_on_cpu():
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench", "preliminary.py"), "--only", "arch"], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    fams = {row["family"]: row for row in out["arch"]}
+    assert fams["record_11l"]["fits"] and fams["record_11l"]["params"] > 26_000_000 and fams["tiny_cpu"]["engine_gib"] < 5

@@ -640,6 +640,81 @@ __global__ void __launch_bounds__(ROW_THREADS) softcap_ce_kernel(const __nv_bflo
   }
 }
 
+// Wide-vocabulary form of the kernel above (V > 2048, e.g. the 8192-token vocabularies): one CTA per row, the row is
+// streamed twice from L2 instead of being held in registers. Pass 1 keeps a running (max, sum of exponentials) per thread
+// and merges them across the CTA; pass 2 recomputes the capped logits and writes the gradient. Counterpart of the
+// reference's tiled output cross-entropy (pg-kernels/src/gpu_kernels.rs:4241-4386, online max/sum across vocabulary tiles).
+__global__ void __launch_bounds__(256) softcap_ce_wide_kernel(const __nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                                                              float* __restrict__ nll, __nv_bfloat16* __restrict__ dlogits,
+                                                              float* __restrict__ loss_sum, int rows, int V, float cap, float gscale,
+                                                              const float* __restrict__ tok_w, const float* __restrict__ w_total) {
+  __shared__ float s_mx[8], s_se[8], s_ct[8], s_bcast[2];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float wnorm = (tok_w && w_total) ? (float)rows / fmaxf(*w_total, 1e-12f) : 1.f;
+  const float inv_cap = 1.f / cap;
+  float local = 0.f;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* z = logits + (size_t)row * V;
+    const int tgt = targets[row];
+    float mx = -1e30f, se = 0.f, ct = 0.f;
+    for (int col = threadIdx.x * 8; col < V; col += 256 * 8) {
+      F8 a = ld8(z + col);
+      float c[8], m8 = -1e30f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        c[e] = cap * tanhf(a.v[e] * inv_cap);
+        m8 = fmaxf(m8, c[e]);
+        if (col + e == tgt) ct = c[e];
+      }
+      if (m8 > mx) {
+        se *= __expf(mx - m8);
+        mx = m8;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) se += __expf(c[e] - mx);
+    }
+    // merge (max, sum) pairs: first inside the warp, then across the 8 warps
+    const float wm = warp_max(mx);
+    se = warp_sum(se * __expf(mx - wm));
+    ct = warp_sum(ct);
+    if (lane == 0) { s_mx[warp] = wm; s_se[warp] = se; s_ct[warp] = ct; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float M = s_mx[0], C = 0.f;
+      for (int w = 1; w < 8; ++w) M = fmaxf(M, s_mx[w]);
+      float S = 0.f;
+      for (int w = 0; w < 8; ++w) { S += s_se[w] * __expf(s_mx[w] - M); C += s_ct[w]; }
+      const float lse = M + __logf(S);
+      s_bcast[0] = lse;
+      s_bcast[1] = lse - C;
+    }
+    __syncthreads();
+    const float lse = s_bcast[0], l = s_bcast[1];
+    const float tw = tok_w ? tok_w[row] * wnorm : 1.f;
+    if (threadIdx.x == 0) {
+      if (nll) nll[row] = l;
+      local += l * tw;
+    }
+    if (dlogits) {
+      __nv_bfloat16* dz = dlogits + (size_t)row * V;
+      const float gs = gscale * tw;
+      for (int col = threadIdx.x * 8; col < V; col += 256 * 8) {
+        F8 a = ld8(z + col);
+        F8 o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float th = tanhf(a.v[e] * inv_cap);
+          const float p = __expf(cap * th - lse);
+          o.v[e] = gs * (p - (col + e == tgt ? 1.f : 0.f)) * (1.f - th * th);
+        }
+        st8(dz + col, o);
+      }
+    }
+    __syncthreads();            // s_bcast is rewritten by the next row
+  }
+  if (loss_sum && threadIdx.x == 0) atomicAdd(loss_sum, local);
+}
+
 // Weight of every (previous token, target) pair from a [V, V] table, and the sum of the weights (complementary training,
 // parameter-golf-rs/crates/pg-kernels/src/complementary.rs:204-224). `w_total` must be zero on entry.
 __global__ void __launch_bounds__(256) pair_weights_kernel(const int* __restrict__ prev, const int* __restrict__ curr, const float* __restrict__ table,
@@ -712,6 +787,28 @@ __global__ void __launch_bounds__(256) embed_scatter_kernel(const int* __restric
     const int r = i / SLICE, c = i % SLICE;
     const float v = tile[i];
     if (v != 0.f && c0 + c < d) atomicAdd(dtable + (size_t)r * d + c0 + c, v);
+  }
+}
+
+// Tables too tall for the shared-memory tile (8192-row vocabularies): one warp per gradient row, fp32 atomics straight into
+// the table gradient. With thousands of table rows the atomics rarely collide.
+__global__ void __launch_bounds__(256) embed_scatter_atomic_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ g,
+                                                                   float* __restrict__ dtable, int rows, int d, int bigram_buckets, int seq_len) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    int id;
+    if (bigram_buckets > 0) {
+      if (row % seq_len == 0) id = bigram_buckets - 1;
+      else id = (int)(((36313u * (uint32_t)ids[row]) ^ (27191u * (uint32_t)ids[row - 1])) % (uint32_t)(bigram_buckets - 1));
+    } else {
+      id = ids[row];
+    }
+    float* dst = dtable + (size_t)id * d;
+    for (int col = lane * 8; col < d; col += 256) {
+      F8 a = ld8(g + (size_t)row * d + col);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) atomicAdd(dst + col + e, a.v[e]);
+    }
   }
 }
 
@@ -825,7 +922,15 @@ void xsa_bwd(const void* dz, const void* y, const void* v, void* dy, void* dv, i
 
 void softcap_ce(const void* logits, const int* targets, float* nll, void* dlogits, float* loss_sum, int rows, int V, float cap, float gscale,
                 cudaStream_t st, const float* tok_w, const float* w_total) {
-  if (V % 8 || V > 2048) throw std::runtime_error("vocab must be a multiple of 8 and <= 2048 for the fused CE kernel");
+  if (V % 8) throw std::runtime_error("vocab must be a multiple of 8 for the fused CE kernel");
+  if (V > 2048) {             // the row no longer fits the registers of one warp: one CTA per row, two passes
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    softcap_ce_wide_kernel<<<std::max(1, std::min(rows, sms * 8)), 256, 0, st>>>((const __nv_bfloat16*)logits, targets, nll, (__nv_bfloat16*)dlogits,
+                                                                                 loss_sum, rows, V, cap, gscale, tok_w, w_total);
+    return;
+  }
   softcap_ce_kernel<<<row_grid(rows), ROW_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets, nll, (__nv_bfloat16*)dlogits, loss_sum, rows, V,
                                                             cap, gscale, tok_w, w_total);
 }
@@ -847,7 +952,11 @@ void embed_scatter_add(const int* ids, const void* g, float* dtable, int rows, i
   // slice width so that table_rows * slice * 4 bytes fits in ~200 KB of shared memory
   int slice = 32;
   while (slice > 8 && (size_t)table_rows * slice * 4 > 200 * 1024) slice /= 2;
-  if ((size_t)table_rows * slice * 4 > 200 * 1024) throw std::runtime_error("embedding table too tall for the shared-memory scatter");
+  if ((size_t)table_rows * slice * 4 > 200 * 1024) {
+    embed_scatter_atomic_kernel<<<std::max(1, std::min((rows + 7) / 8, 148 * 8)), 256, 0, st>>>(ids, (const __nv_bfloat16*)g, dtable, rows, d,
+                                                                                               bigram_buckets, seq_len);
+    return;
+  }
   const int cslices = (d + slice - 1) / slice;
   const int ychunks = std::max(1, std::min(148 * 2 / cslices, (rows + 2047) / 2048));
   const int rows_per = (rows + ychunks - 1) / ychunks;

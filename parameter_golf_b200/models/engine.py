@@ -114,6 +114,11 @@ class CudaEngine:
         self.stats = torch.zeros(4, dtype=torch.float32, device=self.dev)
         self.loss_sum = torch.zeros(1, dtype=torch.float32, device=self.dev)
         self.pair_w_table = self.tok_w = self.w_total = None       # complementary training, see `set_token_weight_table`
+        # Called as ``backward_observer(layer, slot)`` right after the backward of each block has been enqueued: every
+        # gradient of that layer is then final for this micro-batch unless the layer runs again in an earlier slot. Hook
+        # for per-layer gradient reduction overlapped with the rest of the backward (role of `GpuBackwardLayerObserver`,
+        # pg-model/src/gpu.rs:517-525).
+        self.backward_observer = None
         self.adam_t = 0
         self.layer_flags = None          # set by the sharded optimizer: per-layer weight-ready counters
         self.layer_flag_value = 0
@@ -541,6 +546,8 @@ class CudaEngine:
                            g["resid_mix"][l], d_sw, self_pair, s_l, self.eps)
             if self.parallel:
                 self.dx, self.dx_mid = self.dx_mid, self.dx
+            if self.backward_observer is not None:
+                self.backward_observer(l, j)
         self.dx.add_(self.d_x0)
         bid = m.smear_gate_boundary_token_id
         C.norm_smear_bwd(self.dx, self.xe, p["smear_gate"] if m.smear_gate else None, self.ids if (m.smear_gate and bid is not None) else None,

@@ -367,3 +367,25 @@ def test_tall_embedding_table_scatter_and_vocab_8192_step():
     worst = {k: rel_err(eng.g[k], v) for k, v in ref.items()}
     bad = {k: v for k, v in worst.items() if v > (0.2 if k == "q_gain" else 0.06)}
     assert not bad, worst
+
+
+def test_backward_observer_sees_every_block_in_reverse_order():
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine
+    spec = small_spec(**{"model.recurrence.enabled": "true", "model.recurrence.start_layer": 1, "model.recurrence.repeat_layers": 2})
+    eng = CudaEngine(spec, gpt.fill_deterministic(spec.model), "cuda", 2, 128)
+    seen = []
+    done = {}
+    def obs(layer, slot):
+        seen.append((layer, slot))
+        if slot == eng.first_slot[layer]:                  # last time this layer appears in the backward: its gradient is complete
+            done[layer] = float(eng.g["mlp_up_bank"][layer].abs().sum())
+    eng.backward_observer = obs
+    ids = torch.randint(0, 256, (2, 128), device="cuda", dtype=torch.int32)
+    eng.zero_grads()
+    eng.micro_step(ids, ids.roll(-1, 1), 1)
+    torch.cuda.synchronize()
+    assert [s for _, s in seen] == list(range(eng.nslots - 1, -1, -1))
+    assert [l for l, _ in seen] == [l for l, _ in reversed(eng.sched)]
+    for layer, v in done.items():                          # nothing touched that layer's gradient after its last block
+        assert v > 0 and v == float(eng.g["mlp_up_bank"][layer].abs().sum())

@@ -271,3 +271,37 @@ def test_int8_zlib_scheme_through_export_and_load():
         assert back[k].shape == p[k].shape
         # the scale floor of 1/127 (reference rule) bounds the error of small-valued matrices by half a step
         assert float((back[k] - p[k]).abs().max()) <= 0.02 * float(p[k].abs().max()) + 0.5 / 127 + 1e-3, k
+
+
+def test_ternary_quantiser_base3_packing_and_scale_fix():
+    from parameter_golf_b200.quant import ternary as T3
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(64, 300, generator=g) * 0.05                    # 300 columns: the last group of 128 is ragged
+    q, s = T3.quantize_ternary(w)
+    assert q.dtype == torch.int8 and set(q.unique().tolist()) <= {-1, 0, 1} and s.shape == (64, 3)
+    q0, s0 = T3.quantize_ternary(w, fix_scale=False)
+    assert torch.equal(q, q0)                                        # the fix changes the scale, not the codes
+    e_fix = (w - T3.dequantize_ternary(q, s)).pow(2).mean()
+    e_raw = (w - T3.dequantize_ternary(q0, s0)).pow(2).mean()
+    assert float(e_fix) < float(e_raw)                               # least-squares scale for the chosen codes
+    # group 0 of row 0, by hand
+    blk = w[0, :128]
+    s_h = blk.abs().mean()
+    q_h = torch.clamp(torch.round(blk / s_h), -1, 1)
+    assert torch.equal(q[0, :128].float(), q_h) and float(s0[0, 0]) == pytest.approx(float(s_h), rel=1e-6)
+    assert float(s[0, 0]) == pytest.approx(float(blk.abs()[q_h != 0].mean()), rel=1e-6)
+    # packing: five trits per byte, exact round trip, bytes < 243
+    codes = np.array([-1, 0, 1, 1, -1, 0, 1], dtype=np.int8)
+    raw = T3.pack_trits(codes)
+    assert len(raw) == 2 and raw[0] == 0 + 3 * 1 + 9 * 2 + 27 * 2 + 81 * 0
+    assert np.array_equal(T3.unpack_trits(raw, 7), codes)
+    with pytest.raises(ValueError):
+        T3.pack_trits(np.array([2], dtype=np.int8))
+    with pytest.raises(ValueError):
+        T3.unpack_trits(bytes([250]), 5)
+    blob = T3.compress(q, s)
+    back = T3.decompress(blob)
+    assert back.shape == w.shape and torch.allclose(back, T3.dequantize_ternary(q, s.half().float()), atol=1e-6)
+    assert 1.0 < T3.bits_per_param(q, s) < 2.2                       # ~1.6 bits of entropy per weight plus scales
+    with pytest.raises(ValueError):
+        T3.deserialize(T3.serialize(q, s)[:-1])

@@ -24,6 +24,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("overrides", nargs="*", help="spec overrides, key=value")
     args = ap.parse_args()
     from parameter_golf_b200.data.native_loader import NativeTokenLoader
     from parameter_golf_b200.data.shards import write_synthetic_dataset
@@ -35,6 +36,7 @@ def main():
     spec = family_preset("record_11l")
     spec.mode = "record_shaped_proxy"
     spec.train.backend = "cuda_single"
+    spec.apply_overrides(args.overrides)          # e.g. train.save_layer_acts=none
     spec.validate()
     root = write_synthetic_dataset(os.path.join(tempfile.gettempdir(), "pgb200_bench_data"), 1024, train_tokens=1 << 24,
                                    val_tokens=64 * 2048 + 1, train_shards=1, seed=1337)

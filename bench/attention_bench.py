@@ -49,8 +49,10 @@ def main():
     fl = 4.0 * B * H * S * S * hd / 2
     f = timeit(lambda: n.attn_fwd(q, k, v, y, B, S, H, Hkv, hd, lse), a.iters, a.warmup)
     b = timeit(lambda: n.attn_bwd(q, k, v, y, dy, lse, dq, dk, dv, B, S, H, Hkv, hd, dsum=ds), a.iters, a.warmup)
+    b2 = timeit(lambda: n.attn_bwd(q, k, v, y, dy, lse, dq, dk, dv, B, S, H, Hkv, hd, dsum=ds, reproducible=True), a.iters, a.warmup)
     n.check_status()
-    print(f"native  fwd {f:.3f} ms ({fl / f / 1e9:.0f} TFLOP/s)  bwd {b:.3f} ms ({2.5 * fl / b / 1e9:.0f} TFLOP/s at 2.5x forward FLOPs)")
+    print(f"native  fwd {f:.3f} ms ({fl / f / 1e9:.0f} TFLOP/s)  bwd {b:.3f} ms ({2.5 * fl / b / 1e9:.0f} TFLOP/s at 2.5x forward FLOPs)"
+          f"  two-kernel reproducible bwd {b2:.3f} ms")
     if not a.no_sdpa:
         import torch.nn.functional as F
         from torch.nn.attention import SDPBackend, sdpa_kernel

@@ -92,6 +92,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint (nanoseconds): the thread sleeps in hardware until the phase completes or the hint
+// runs out, instead of re-polling shared memory, whose data pipe the tensor core's operand reads share.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
+#ifndef PGB_WAIT_HINT_NS
+#define PGB_WAIT_HINT_NS 100000u
+#endif
+
 // Bounded wait. `abort_flag` is a CTA-shared int: once any waiter gives up, every later wait in the
 // CTA returns false immediately.
 __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
@@ -115,7 +135,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, PGB_WAIT_HINT_NS)) return true;
     if ((++spins & 63u) == 0) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > PGB_WAIT_LIMIT_NS) {

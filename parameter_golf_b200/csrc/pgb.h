@@ -147,5 +147,12 @@ void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, 
 void attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, float* dsum, void* dq, void* dk, void* dv,
               long long ldq, long long ldk, long long ldv, long long ldo, long long lddo, long long lddq, long long lddk, long long lddv, int B, int S,
               int H, int Hkv, int hd, int accumulate_dv, int* status, cudaStream_t st);
+// Single-pass form (attn_bwd_fused.cu): scores computed once per tile pair, dQ summed with fp32 `red.add` into `dq_acc`
+// (attn_bwd_fused_scratch_floats(B, S, H) floats, ZERO on entry, left zero on return), then scaled and cast into `dq`.
+// dsum is written by a small pre-kernel. dQ is reproducible to fp32 rounding only; attn_bwd is bit-reproducible.
+size_t attn_bwd_fused_scratch_floats(int B, int S, int H);
+void attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, float* dsum, float* dq_acc, void* dq,
+                    void* dk, void* dv, long long ldq, long long ldk, long long ldv, long long ldo, long long lddo, long long lddq, long long lddk,
+                    long long lddv, int B, int S, int H, int Hkv, int hd, int accumulate_dv, int* status, cudaStream_t st);
 
 }  // namespace pgb

@@ -40,9 +40,11 @@ def write_shard(path: str, tokens: np.ndarray) -> None:
     header = np.zeros(HEADER_INTS, dtype="<i4")
     header[0], header[1], header[2] = SHARD_MAGIC, SHARD_VERSION, tokens.size
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
-    with open(path, "wb") as f:
+    tmp = f"{path}.tmp{os.getpid()}"          # readers never see a partially written shard: write aside, then rename
+    with open(tmp, "wb") as f:
         f.write(header.tobytes())
         f.write(tokens.astype("<u2", copy=False).tobytes())
+    os.replace(tmp, path)
 
 
 def read_shard_header(path: str) -> int:

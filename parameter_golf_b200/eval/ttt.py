@@ -27,6 +27,7 @@ import numpy as np
 import torch
 
 from ..data.bpb import BpbLuts
+from ..parallel.agree import agree
 from ..spec import EvalSpec, ModelSpec
 from .sliding import ScoreSums, build_ttt_chunks, cosine_over_chunks, rank_slice, score_windows
 
@@ -90,7 +91,9 @@ def eval_score_first_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalS
     sums = ScoreSums()
     t0 = time.perf_counter()
     tok64 = tokens.astype(np.int64)
-    deadline = (lambda: time.perf_counter() - t0 > ev.max_eval_seconds) if ev.max_eval_seconds > 0 else None
+    # The adapt phase contains a collective (the packed gradient all-reduce), so every rank must skip it on the same
+    # chunk: the decision is taken on the slowest rank's elapsed time, not on each rank's own.
+    deadline = (lambda: agree([time.perf_counter() - t0], "max", world, device)[0] > ev.max_eval_seconds) if ev.max_eval_seconds > 0 else None
     for ci, windows in enumerate(chunks):
         if not windows:
             continue
@@ -188,7 +191,7 @@ def eval_lora_phased_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalS
     t0 = time.perf_counter()
     tok64 = tokens.astype(np.int64)
     for ci, windows in enumerate(chunks):
-        if ev.max_eval_seconds > 0 and time.perf_counter() - t0 > ev.max_eval_seconds:
+        if ev.max_eval_seconds > 0 and agree([time.perf_counter() - t0], "max", world, device)[0] > ev.max_eval_seconds:
             log(f"ttt_deadline_reached chunk={ci}")
             break
         if ci % per_phase == 0 and ci > 0:

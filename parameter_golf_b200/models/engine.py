@@ -107,7 +107,13 @@ class CudaEngine:
         else:
             self._alloc_params(params)
         self._alloc_acts()
-        self.hp_host = torch.zeros(8, dtype=torch.float32).pin_memory()
+        # Pinned staging for the per-step hyper-parameters: a ring of buffers, each guarded by the event recorded after its
+        # asynchronous upload, so that a host that runs ahead of the stream (no per-step synchronisation, graph replay)
+        # never rewrites a buffer whose copy has not executed yet.
+        self.hp_ring = [torch.zeros(8, dtype=torch.float32).pin_memory() for _ in range(4)]
+        self.hp_ring_events = [None] * len(self.hp_ring)
+        self.hp_ring_pos = 0
+        self.hp_host = self.hp_ring[0]
         self.hp = torch.zeros(8, dtype=torch.float32, device=self.dev)
         self.hp_host[0], self.hp_host[4] = 1.0, 1.0
         self.hp.copy_(self.hp_host)
@@ -126,6 +132,7 @@ class CudaEngine:
         self.cast_generation = -1        # generation the bf16 compute copies were made from
         if share is not None:            # the shared bf16 copies are already current
             self.hp, self.hp_host, self.stats = share.hp, share.hp_host, share.stats
+            self.hp_ring, self.hp_ring_events, self.hp_ring_pos = share.hp_ring, share.hp_ring_events, 0
             self.adam_t, self.qat = share.adam_t, share.qat
             self.param_generation, self.cast_generation = share.param_generation, share.cast_generation
         else:
@@ -592,12 +599,18 @@ class CudaEngine:
 
     def set_hp(self, lr_scale: float, momentum: float):
         self.adam_t += 1
-        h = self.hp_host
+        i = self.hp_ring_pos = (self.hp_ring_pos + 1) % len(self.hp_ring)
+        if self.hp_ring_events[i] is not None:
+            self.hp_ring_events[i].synchronize()          # the upload that last used this buffer has executed
+        h = self.hp_host = self.hp_ring[i]
         h[0], h[1] = lr_scale, momentum
         h[2] = 1.0 - self.t.adam_beta1 ** self.adam_t
         h[3] = 1.0 - self.t.adam_beta2 ** self.adam_t
         h[4] = 1.0
         self.hp.copy_(h, non_blocking=True)
+        ev = self.hp_ring_events[i] or torch.cuda.Event()
+        ev.record()
+        self.hp_ring_events[i] = ev
 
     def clip(self, extra_sumsq: Optional[torch.Tensor] = None):
         """Global-norm clip factor into hp[4] (all gradient buffers of this engine)."""
@@ -783,7 +796,7 @@ class EngineBackend:
         else:
             e.clip()
             e.optimizer_step()
-        return float(e.loss_sum[0]) / (e.T * len(batches))
+        return self._read_loss_and_status(len(batches))
 
     def host_spans(self, count: int):
         """Pinned host staging buffers for `count` micro-batch spans of T+1 uint16 tokens (stored as int16)."""
@@ -825,8 +838,27 @@ class EngineBackend:
                 e.clip()
                 e.optimizer_step()
         if read_loss:
-            return float(e.loss_sum[0]) / (e.T * len(dev_spans))
+            return self._read_loss_and_status(len(dev_spans))
         return None
+
+    def _read_loss_and_status(self, micro_batches: int) -> float:
+        """One device->host read of the loss and of the bounded-wait status word. A wait that ran out inside the step (a
+        barrier, a gradient or weight-ready flag a peer never set) leaves wrong gradients or weights behind it, so it must
+        end the run here: the caller holds `RankHealth.guard()`, which reports the exception to the peers."""
+        e = self.engine
+        st = N.status_word(self.device)
+        if not hasattr(self, "_readback"):
+            self._readback = torch.zeros(8, dtype=torch.float32).pin_memory()
+        rb = self._readback
+        rb[:1].copy_(e.loss_sum[:1], non_blocking=True)
+        rb[4:8].view(torch.int32).copy_(st, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        code, block, detail, count = rb[4:8].view(torch.int32).tolist()
+        if code:
+            st.zero_()
+            raise RuntimeError(f"kernel wait timed out during the training step: {N.STATUS_NAMES.get(code, code)} "
+                               f"(block {block}, detail {detail}, {count} reports); gradients or weights of this step are not trustworthy")
+        return float(rb[0]) / (e.T * micro_batches)
 
     def _graphed_micro_step(self, span: torch.Tensor, accum: int):
         """Forward+backward of one micro-batch replayed from a CUDA graph. The engine allocates nothing per step and
@@ -877,9 +909,25 @@ class EngineBackend:
         self.engine.cast_weights()
 
     def state_dict(self):
+        """Full optimizer state on the host. A COLLECTIVE when the optimizer is sharded: every rank must call it at the same
+        step, because the fp32 master weights, the momentum and the EMA shadow of a bank slot are current only on the rank
+        that owns the slot and are gathered from the owners here (the master weights land in ``engine.p``, which the
+        caller saves next)."""
         e = self.engine
-        return {"mom": {k: v.cpu() for k, v in e.mom.items()}, "adam_t": e.adam_t,
-                "m": [g["m"].cpu() for g in e.groups], "v": [g["v"].cpu() for g in e.groups]}
+        mom = e.mom
+        ema_banks = e.ema
+        if self.dist is not None and self.dist.sharded:
+            for k, v in self.dist.gather_banks(e.p).items():
+                e.p[k].copy_(v)
+            mom = self.dist.gather_banks(e.mom)
+            if e.ema is not None:
+                ema_banks = self.dist.gather_banks(e.ema)
+        st = {"mom": {k: v.cpu() for k, v in mom.items()}, "adam_t": e.adam_t,
+              "m": [g["m"].cpu() for g in e.groups], "v": [g["v"].cpu() for g in e.groups]}
+        if e.ema is not None:
+            st["ema_banks"] = {k: v.cpu() for k, v in ema_banks.items()}
+            st["ema_groups"] = [g["ema"].cpu() for g in e.groups]
+        return st
 
     def load_state_dict(self, st):
         e = self.engine
@@ -889,3 +937,10 @@ class EngineBackend:
         for g, mm, vv in zip(e.groups, st["m"], st["v"]):
             g["m"].copy_(mm)
             g["v"].copy_(vv)
+        if e.ema is not None:
+            if "ema_banks" not in st:
+                raise RuntimeError("the checkpoint holds no EMA state but this run averages weights (train.ema_decay > 0)")
+            for k, v in st["ema_banks"].items():
+                e.ema[k].copy_(v)
+            for g, sh in zip(e.groups, st["ema_groups"]):
+                g["ema"].copy_(sh)

@@ -37,7 +37,7 @@ def load():
 class _Counting:
     """Forwards to the extension and counts kernel launches issued through it (`launch_count`)."""
 
-    _PER_CALL = {"attn_bwd": 2}
+    _PER_CALL = {"attn_bwd": 2, "attn_bwd_fused": 3}
 
     def __init__(self, mod):
         self._mod = mod
@@ -148,11 +148,35 @@ def attn_fwd(q, k, v, y, B, S, H, Hkv, hd, lse=None):
     return lse
 
 
-def attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=False, dsum=None):
-    """Causal GQA attention backward. Writes dq, dk and dv (dv is added to when ``accumulate_dv``)."""
+_DQ_ACC = {}
+
+
+def attn_dq_scratch(device, B, S, H, hd=64):
+    """Zero-filled fp32 accumulator of the single-pass attention backward, one per device, grown on demand. The kernels
+    leave it zero, so every call on the device can share it (calls on one device are stream-ordered)."""
+    need = B * H * S * hd
+    key = torch.device(device).index
+    buf = _DQ_ACC.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros(need, dtype=torch.float32, device=device)
+        _DQ_ACC[key] = buf
+    return buf
+
+
+def attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=False, dsum=None, dq_acc=None, reproducible=False):
+    """Causal GQA attention backward. Writes dq, dk and dv (dv is added to when ``accumulate_dv``).
+
+    Default: the single-pass kernel (scores computed once per tile pair; dQ summed in an fp32 accumulator with `red.add`,
+    so its last fp32 bits depend on scheduling). ``reproducible=True`` runs the two-kernel form, which recomputes the
+    scores for dQ and is bit-reproducible."""
     if dsum is None:
         dsum = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
-    load().attn_bwd(q, k, v, o, d_o, lse, dsum, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv, status_word(q.device))
+    if reproducible:
+        load().attn_bwd(q, k, v, o, d_o, lse, dsum, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv, status_word(q.device))
+        return dsum
+    if dq_acc is None:
+        dq_acc = attn_dq_scratch(q.device, B, S, H, hd)
+    load().attn_bwd_fused(q, k, v, o, d_o, lse, dsum, dq_acc, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv, status_word(q.device))
     return dsum
 
 

@@ -439,8 +439,9 @@ class RunSpec:
             chk(m.recurrence.start_layer + m.recurrence.repeat_layers <= m.num_layers, "recurrence range out of bounds")
         chk(t.seq_len > 0 and t.batch_tokens % t.seq_len == 0, "batch_tokens must be a multiple of seq_len")
         chk(t.world_size >= 1 and 0 <= t.rank < t.world_size, "rank must be in [0, world_size)")
-        if t.backend in ("cpu", "cuda_single", "cuda_single_parity"):
+        if t.backend in ("cuda_single", "cuda_single_parity"):
             chk(t.world_size == 1, f"backend {t.backend} requires world_size == 1")
+        # the cpu backend with world_size > 1 is data parallel over a gloo process group (host-side logic and its tests)
         chk(4 <= q.matrix_bits <= 8 and 4 <= q.embed_bits <= 8, "quant bits must be in [4, 8]")
         chk(e.stride >= 1, "eval.stride must be >= 1")
         chk(t.grad_wire_dtype in ("bf16", "f32"), "grad_wire_dtype must be bf16 or f32")

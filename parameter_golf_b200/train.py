@@ -33,6 +33,7 @@ from .eval.sliding import eval_contiguous, eval_sliding
 from .eval.ttt import eval_lora_phased_ttt, eval_score_first_ttt
 from .models import gpt
 from .models.runner import OracleRunner
+from .parallel.agree import agree
 from .optim.muon import AdamW, Ema, Muon, Swa, clip_grads_, lr_scale_with_floor, muon_momentum_at, wallclock_lr_scale
 from .quant.export import check_budget, code_bytes, export_model, load_artifact
 from .spec import RunSpec, family_preset
@@ -223,6 +224,7 @@ class VariantRunner:
         self.spec = spec.validate()
         self.log = log or RunLog(spec.name)
         self.backend_factory = backend_factory
+        self.clock: Callable[[], float] = time.perf_counter      # seconds; the training loop's only time source
 
     def _make_backend(self, params):
         if self.backend_factory is not None:
@@ -249,9 +251,17 @@ class VariantRunner:
         # ---- data ----------------------------------------------------------------------------------
         if not t.train_data_pattern:
             root = os.path.join(os.environ.get("PGB_DATA_ROOT", "/tmp/pgb200_synth"), f"v{m.vocab_size}_s{t.seed}")
-            if t.rank == 0 or not os.path.exists(os.path.join(root, "fineweb_val_000000.bin")):
+            # One writer: rank 0 generates (each shard is written to a temporary name and renamed), the others wait at a
+            # barrier before any of them opens a shard.
+            if t.rank == 0:
                 write_synthetic_dataset(root, m.vocab_size, train_tokens=max(4 * t.batch_tokens, 1 << 20),
                                         val_tokens=max(4 * m.eval_seq_len * 8 + 1, 1 << 16), seed=t.seed)
+            if t.world_size > 1:
+                import torch.distributed as dist
+                if dist.is_available() and dist.is_initialized():
+                    dist.barrier()
+                elif not os.path.exists(os.path.join(root, "fineweb_val_000000.bin")):
+                    raise RuntimeError("synthetic data is generated by rank 0; the other ranks need a process group to wait for it")
             t.train_data_pattern = os.path.join(root, "fineweb_train_*.bin")
             t.validation_data_pattern = os.path.join(root, "fineweb_val_*.bin")
         loader = DistributedTokenLoader(t.train_data_pattern, t.rank, t.world_size)
@@ -299,7 +309,7 @@ class VariantRunner:
                  f"train_batch_tokens:{tokens_per_step} train_seq_len:{t.seq_len} iterations:{max_steps}")
         train_ms = 0.0
         step = step0
-        t_start = time.perf_counter()
+        t_start = self.clock()
         health = None
         if t.world_size > 1:
             from .parallel.health import RankHealth
@@ -307,7 +317,12 @@ class VariantRunner:
         while step < max_steps:
             if health is not None:
                 health.check()        # a peer that failed or went silent ends this rank on the host, before its next launch
-            elapsed = train_ms + 1000.0 * (time.perf_counter() - t_start)
+            elapsed = train_ms + 1000.0 * (self.clock() - t_start)
+            if max_ms is not None and t.world_size > 1:
+                # Every rank acts on the slowest rank's clock: the stop, the wall-clock learning-rate scale and the switches
+                # driven by it (late QAT, SWA) then flip on the same step everywhere (train_gpt.py:1049-1053 reduces its
+                # reached_cap flag the same way). A rank that left the loop alone would strand its peers' collectives.
+                elapsed = agree([elapsed], "max", t.world_size, device)[0]
             if max_ms is not None and elapsed >= max_ms:
                 res.stopped_early = True
                 log.info(f"stopping_early: wallclock_cap train_time:{elapsed:.0f}ms step:{step}/{max_steps}")
@@ -317,13 +332,6 @@ class VariantRunner:
             else:
                 wd = int(round(max_steps * t.warmdown_frac)) if t.warmdown_frac > 0 else min(t.warmdown_iters, max_steps)
                 scale = lr_scale_with_floor(step, t.warmup_steps, max_steps, wd, t.min_lr_scale) if (wd or t.warmup_steps) else 1.0
-            if t.world_size > 1 and t.wallclock_warmdown and max_ms is not None:
-                # wallclock-derived scales differ slightly across ranks; agree on one so that schedule-driven
-                # switches (late QAT, SWA) flip on the same step everywhere
-                import torch.distributed as dist
-                sc = torch.tensor([scale], dtype=torch.float64, device=device if t.backend != "cpu" else "cpu")
-                dist.all_reduce(sc, op=dist.ReduceOp.MIN)
-                scale = float(sc[0])
             if t.late_qat_threshold > 0 and scale < t.late_qat_threshold and not qat:
                 qat = True
                 log.info(f"late_qat:enabled step:{step} scale:{scale:.4f}")
@@ -349,13 +357,22 @@ class VariantRunner:
                     ema.update(backend.sync_params())
             if swa is not None and swa.should_collect(step, scale):
                 swa.collect(backend.final_params(ema=False) if fused_ema else backend.sync_params())
-            now_ms = train_ms + 1000.0 * (time.perf_counter() - t_start)
+            now_ms = train_ms + 1000.0 * (self.clock() - t_start)
             if t.train_log_every > 0 and (step <= 10 or step % t.train_log_every == 0 or step == max_steps):
                 log.info(f"step:{step}/{max_steps} train_loss:{loss:.4f} train_time:{now_ms:.0f}ms step_avg:{now_ms / (step - step0):.2f}ms")
-            if t.checkpoint_every > 0 and t.checkpoint_path and step % t.checkpoint_every == 0 and t.rank == 0:
-                save_checkpoint(t.checkpoint_path, res.fingerprint, step, backend.sync_params(), backend.state_dict(),
-                                loader.state(), ema.shadow if ema else None)
-        train_ms += 1000.0 * (time.perf_counter() - t_start)
+            if t.checkpoint_every > 0 and t.checkpoint_path and step % t.checkpoint_every == 0:
+                # Every rank takes part: the sharded optimizer gathers its state from the slot owners (a collective), rank 0
+                # writes, and the others wait for the write at a host barrier instead of starting a step whose device-side
+                # waits would run out while rank 0 is still in fsync.
+                opt_state = backend.state_dict()
+                if t.rank == 0:
+                    save_checkpoint(t.checkpoint_path, res.fingerprint, step, backend.sync_params(), opt_state,
+                                    loader.state(), ema.shadow if ema else None)
+                if t.world_size > 1:
+                    import torch.distributed as dist
+                    if dist.is_available() and dist.is_initialized():
+                        dist.barrier()
+        train_ms += 1000.0 * (self.clock() - t_start)
         if hasattr(loader, "stop_prefetch"):
             loader.stop_prefetch()
         res.steps = step - step0

@@ -168,3 +168,34 @@ def test_training_ranks_stop_on_the_host_when_a_peer_fails_between_steps(tmp_pat
     assert "RANK 1 RAISED injected: device lost" in out.stdout, (out.stdout, out.stderr[-2000:])
     assert "RANK 0 PEER_FAILURE rank1: RuntimeError: injected: device lost" in out.stdout, (out.stdout, out.stderr[-2000:])
     assert "RANK 0 FINISHED" not in out.stdout
+
+
+def test_wallclock_cap_is_agreed_across_ranks_when_one_clock_runs_ahead(tmp_path):
+    """Two gloo ranks run the real training loop with a wall-clock cap; rank 1's clock jumps past the cap after a few
+    steps. Both ranks must leave the loop on the same step (the decision is all-reduced), so neither is left waiting in
+    the gradient all-reduce of a step its peer never starts."""
+    out = _run(tmp_path, """
+        dist.init_process_group('gloo', timeout=datetime.timedelta(seconds=20))
+        rank = dist.get_rank()
+        from parameter_golf_b200.spec import family_preset
+        from parameter_golf_b200.train import VariantRunner
+        spec = family_preset('tiny_cpu')
+        spec.train.world_size, spec.train.rank = 2, rank
+        spec.train.total_iterations, spec.train.max_wallclock_seconds, spec.mode = 30, 500.0, 'proxy'
+        spec.train.wallclock_warmdown, spec.train.late_qat_threshold = True, 0.5
+        spec.quant.scheme = 'none'
+        spec.train.artifact_path = os.path.join(%r, 'a.pgrs')
+        r = VariantRunner(spec)
+        calls = [0]
+        def clock():
+            calls[0] += 1
+            return time.perf_counter() + (1000.0 if rank == 1 and calls[0] > 9 else 0.0)
+        r.clock = clock
+        res = r.run('proxy')
+        print('RANK', rank, 'STEPS', res.steps, 'EARLY', res.stopped_early, flush=True)
+        """ % str(tmp_path), port=29697, timeout=240)
+    lines = sorted(l for l in out.stdout.splitlines() if l.startswith("RANK"))
+    assert len(lines) == 2, (out.stdout, out.stderr[-2000:])
+    steps = [int(l.split()[3]) for l in lines]
+    assert steps[0] == steps[1] and 0 < steps[0] < 30, lines
+    assert all(l.endswith("EARLY True") for l in lines), lines

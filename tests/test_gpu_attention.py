@@ -51,8 +51,9 @@ def test_attention_forward_large_scores_trigger_rescale():
     assert (y.float() - _ref(q, k, v, B, S, H, Hkv, hd)).abs().max() < 0.05
 
 
-@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 2, 1), (2, 256, 4, 2), (1, 640, 8, 4), (2, 384, 2, 2), (1, 512, 4, 1)])
-def test_attention_backward(B, S, H, Hkv):
+@pytest.mark.parametrize("reproducible", [False, True])
+@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 2, 1), (2, 256, 4, 2), (1, 640, 8, 4), (2, 384, 2, 2), (1, 512, 4, 1), (3, 896, 4, 2)])
+def test_attention_backward(B, S, H, Hkv, reproducible):
     from parameter_golf_b200.ops import native as n
     from parameter_golf_b200.ops.reference import causal_gqa_attention
     hd = 64
@@ -66,7 +67,7 @@ def test_attention_backward(B, S, H, Hkv):
     dq, dk, dv = dqkv[:, :H * hd], dqkv[:, H * hd:(H + Hkv) * hd], dqkv[:, (H + Hkv) * hd:]
     base = (torch.randn(B * S, Hkv * hd, device="cuda") * 0.1).bfloat16()
     dv.copy_(base)
-    n.attn_bwd(q, k, v, y, dy, lse, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=True)
+    n.attn_bwd(q, k, v, y, dy, lse, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=True, reproducible=reproducible)
     torch.cuda.synchronize()
     n.check_status()
     qf = q.float().reshape(B, S, H, hd).requires_grad_(True)
@@ -78,3 +79,28 @@ def test_attention_backward(B, S, H, Hkv):
         err = (got.float() - ref).abs().max().item()
         scale = ref.abs().max().item()
         assert err < 0.03 * scale + 0.02, (name, err, scale)
+
+
+def test_attention_backward_single_pass_many_tiles_and_clean_scratch():
+    """More CTA-level items than SMs (several items per persistent CTA, both K/V buffers and every Q/dO stage reused),
+    checked against the two-kernel form; the shared accumulator must be left zero, and a second call must agree."""
+    from parameter_golf_b200.ops import native as n
+    B, S, H, Hkv, hd = 10, 1024, 8, 4, 64
+    torch.manual_seed(7)
+    qkv = torch.randn(B * S, (H + 2 * Hkv) * hd, device="cuda").bfloat16()
+    q, k, v = qkv[:, :H * hd], qkv[:, H * hd:(H + Hkv) * hd], qkv[:, (H + Hkv) * hd:]
+    dy = (torch.randn(B * S, H * hd, device="cuda") * 0.5).bfloat16()
+    y = torch.empty(B * S, H * hd, device="cuda", dtype=torch.bfloat16)
+    lse = n.attn_fwd(q, k, v, y, B, S, H, Hkv, hd)
+    ref = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    n.attn_bwd(q, k, v, y, dy, lse, *ref, B, S, H, Hkv, hd, reproducible=True)
+    acc = n.attn_dq_scratch(q.device, B, S, H, hd)
+    for _ in range(2):
+        got = [torch.full_like(q, 7.0), torch.full_like(k, 7.0), torch.full_like(v, 7.0)]
+        n.attn_bwd(q, k, v, y, dy, lse, *got, B, S, H, Hkv, hd)
+        torch.cuda.synchronize()
+        n.check_status()
+        assert float(acc.abs().max()) == 0.0
+        for g, r in zip(got, ref):
+            err = (g.float() - r.float()).abs().max().item()
+            assert err <= 0.01 * r.float().abs().max().item() + 1e-3, err

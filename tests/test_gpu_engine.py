@@ -389,3 +389,53 @@ def test_backward_observer_sees_every_block_in_reverse_order():
     assert [l for l, _ in seen] == [l for l, _ in reversed(eng.sched)]
     for layer, v in done.items():                          # nothing touched that layer's gradient after its last block
         assert v > 0 and v == float(eng.g["mlp_up_bank"][layer].abs().sum())
+
+
+def test_checkpoint_state_round_trip_restores_ema_and_trajectory():
+    """Optimizer state (momentum, Adam moments, EMA shadows) saved after two steps and loaded into a fresh backend gives the
+    same EMA export and the same third step as the backend that kept running."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import EngineBackend
+    spec = small_spec(**{"train.ema_decay": 0.9})
+    spec.mode = "record"
+    spec.allow_unsupported_variants = True
+    gen = torch.Generator().manual_seed(11)
+    batches = [[(torch.randint(0, 256, (4, 128), generator=gen), torch.randint(0, 256, (4, 128), generator=gen))] for _ in range(3)]
+    a = EngineBackend(spec, gpt.init_params(spec.model, 3))
+    for b in batches[:2]:
+        a.train_step(b, 1.0, 0.95, False)
+    params = {k: v.detach().cpu().clone() for k, v in a.sync_params().items()}
+    state = a.state_dict()
+    assert "ema_banks" in state and len(state["ema_groups"]) == len(a.engine.groups)
+    fresh = EngineBackend(spec, gpt.init_params(spec.model, 99))          # different initial weights: nothing may survive from them
+    for k, v in params.items():
+        fresh.sync_params()[k].copy_(v)
+    fresh.load_state_dict(state)
+    fresh.params_changed()
+    ea, ef = a.final_params(ema=True), fresh.final_params(ema=True)
+    for k in ea:
+        assert torch.equal(ea[k], ef[k]), k
+    la, lf = a.train_step(batches[2], 1.0, 0.95, False), fresh.train_step(batches[2], 1.0, 0.95, False)
+    assert lf == pytest.approx(la, abs=1e-5)
+    state.pop("ema_banks")
+    with pytest.raises(RuntimeError, match="no EMA state"):
+        fresh.load_state_dict(state)
+
+
+def test_training_step_raises_when_a_device_wait_ran_out():
+    """A bounded wait that gave up (here: a flag nothing sets) must surface from the training backend's own step, not only
+    from an explicit status check, and the context must stay usable afterwards."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import EngineBackend
+    from parameter_golf_b200.ops import native
+    spec = small_spec(**{"train.ema_decay": 0.0})
+    spec.mode = "record"
+    spec.allow_unsupported_variants = True
+    be = EngineBackend(spec, gpt.init_params(spec.model, 3))
+    ids = torch.randint(0, 256, (4, 128))
+    be.train_step([(ids, ids)], 1.0, 0.95, False)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    native.load().comm_wait_flag(flag, 1, native.status_word())             # runs out after its time limit and records it
+    with pytest.raises(RuntimeError, match="timed out during the training step"):
+        be.train_step([(ids, ids)], 1.0, 0.95, False)
+    assert math.isfinite(be.train_step([(ids, ids)], 1.0, 0.95, False))     # status cleared, context alive

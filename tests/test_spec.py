@@ -41,11 +41,17 @@ def test_overrides():
         s.apply_overrides(["train.nope=1"])
 
 
-@pytest.mark.parametrize("ov", ["model.num_heads=7", "model.rope.mode=yarn", "quant.compression=brotli", "train.world_size=2",
+@pytest.mark.parametrize("ov", ["model.num_heads=7", "model.rope.mode=yarn", "quant.compression=brotli", "train.rank=3",
                                 "model.vocab_size=70000", "quant.matrix_bits=3", "train.batch_tokens=1000"])
 def test_validation_rejects(ov):
     with pytest.raises(ValueError):
         family_preset("tiny_cpu").apply_overrides([ov]).validate()
+
+
+def test_single_gpu_backends_reject_more_than_one_rank_but_cpu_runs_data_parallel():
+    with pytest.raises(ValueError):
+        family_preset("tiny_cpu").apply_overrides(["train.backend=cuda_single", "train.world_size=2"]).validate()
+    family_preset("tiny_cpu").apply_overrides(["train.world_size=2", "train.rank=1"]).validate()      # gloo ranks on the CPU backend
 
 
 def test_gates_mutually_exclusive():

@@ -56,7 +56,7 @@ def test_matches_regular_entry_point_twice_in_a_row():
         q, k, v, o, d_o, lse = _case(B, S, H, Hkv, seed)
         want = [torch.empty(B * S, H * HD, device="cuda", dtype=torch.bfloat16), torch.empty(B * S, Hkv * HD, device="cuda", dtype=torch.bfloat16),
                 torch.empty(B * S, Hkv * HD, device="cuda", dtype=torch.bfloat16)]
-        n.attn_bwd(q, k, v, o, d_o, lse, *want, B, S, H, Hkv, HD)
+        n.attn_bwd(q, k, v, o, d_o, lse, *want, B, S, H, Hkv, HD, reproducible=True)
         got = [torch.zeros_like(t) for t in want]
         prepared.append((q, k, v, o, d_o, lse, want, got, B, S, H, Hkv))
     torch.cuda.synchronize()
@@ -83,7 +83,7 @@ def test_accumulating_into_dv_matches():
     base = torch.randn(B * S, Hkv * HD, device="cuda").bfloat16()
     want = [torch.empty(B * S, H * HD, device="cuda", dtype=torch.bfloat16), torch.empty(B * S, Hkv * HD, device="cuda", dtype=torch.bfloat16), base.clone()]
     got = [torch.empty_like(want[0]), torch.empty_like(want[1]), base.clone()]
-    n.attn_bwd(q, k, v, o, d_o, lse, *want, B, S, H, Hkv, HD, accumulate_dv=True)
+    n.attn_bwd(q, k, v, o, d_o, lse, *want, B, S, H, Hkv, HD, accumulate_dv=True, reproducible=True)
     assert _call(lib, q, k, v, o, d_o, lse, *got, B, S, H, Hkv, accumulate=1) == 0, lib.pgb_noalloc_last_error()
     torch.cuda.synchronize()
     n.check_status()

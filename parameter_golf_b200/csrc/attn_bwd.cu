@@ -650,11 +650,11 @@ void attn_bwd(const void* q, const void* k, const void* v, const void* o, const 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};          // the attribute is a per-device property of the kernel
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
     cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM);
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   {
     const CUtensorMap mq = bwd_map(q, ldq, H * hd, T, 128), mk = bwd_map(k, ldk, Hkv * hd, T, 128), mv = bwd_map(v, ldv, Hkv * hd, T, 128),

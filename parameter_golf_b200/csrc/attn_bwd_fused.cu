@@ -37,6 +37,7 @@ namespace {
 constexpr int F_HD = 64;
 constexpr int F_TILE = 128 * F_HD * 2;       // 16 KB: one 128-row bf16 tile of one head
 constexpr float F_LOG2E = 1.4426950408889634f;
+constexpr uint32_t F_BACKOFF_NS = 96;         // sleep between barrier polls of the single-thread roles
 constexpr int F_STAGES = 3;                  // {Q, dO, lse, D} stages
 #ifndef PGB_ATTN_BWD_GROUPS
 #define PGB_ATTN_BWD_GROUPS 2
@@ -194,7 +195,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           if (rc == 2) break;
           if (rc == 1) continue;
           const int kvb = il & 1;
-          if (!mbar_wait(&kv_empty[kvb], (uint32_t)(((il >> 1) & 1) ^ 1), abort_flag, p.status, ST_WAIT_EMPTY, -1)) { ok = false; break; }
+          if (!mbar_wait(&kv_empty[kvb], (uint32_t)(((il >> 1) & 1) ^ 1), abort_flag, p.status, ST_WAIT_EMPTY, -1, F_BACKOFF_NS)) { ok = false; break; }
           uint8_t* sk = sKV + kvb * 2 * F_TILE;
           mbar_expect_tx(&kv_full[kvb], 2 * F_TILE);
           f_tma2d(sk, &map_k, &kv_full[kvb], it.kvh * F_HD, it.key0);
@@ -202,7 +203,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           int head = it.kvh * p.group, qi = it.j, g = 0;
           for (int u = 0; u < it.nu; ++u, up.next()) {
             const int stage = up.stage;
-            if (!mbar_wait(&st_empty[stage], up.phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, u)) { ok = false; break; }
+            if (!mbar_wait(&st_empty[stage], up.phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, u, F_BACKOFF_NS)) { ok = false; break; }
             const int qrow = it.b * p.S + qi * 128;
             const size_t vidx = ((size_t)it.b * p.H + head) * p.S + qi * 128;
             mbar_expect_tx(&st_full[stage], 2 * F_TILE + 1024);
@@ -232,13 +233,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           if (rc == 2) break;
           if (rc == 1) continue;
           const int kvb = il & 1;
-          if (!mbar_wait(&kv_full[kvb], (uint32_t)((il >> 1) & 1), abort_flag, p.status, ST_WAIT_FULL, -1)) { ok = false; break; }
+          if (!mbar_wait(&kv_full[kvb], (uint32_t)((il >> 1) & 1), abort_flag, p.status, ST_WAIT_FULL, -1, F_BACKOFF_NS)) { ok = false; break; }
           const uint32_t sk = smem_u32(sKV + kvb * 2 * F_TILE);
           const uint64_t dk0 = make_smem_desc(sk, 16, 1024), dv0 = make_smem_desc(sk + F_TILE, 16, 1024);
           for (int u = 0; u < it.nu; ++u, up.next()) {
             const int stage = up.stage;
-            if (!up.first && !mbar_wait(s_free, up.par ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, u)) { ok = false; break; }
-            if (!mbar_wait(&st_full[stage], up.phase, abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
+            if (!up.first && !mbar_wait(s_free, up.par ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, u, F_BACKOFF_NS)) { ok = false; break; }
+            if (!mbar_wait(&st_full[stage], up.phase, abort_flag, p.status, ST_WAIT_FULL, u, F_BACKOFF_NS)) { ok = false; break; }
             tc_fence_after();
             const uint32_t sq = smem_u32(sQD + stage * 2 * F_TILE);
             const uint64_t dq0 = make_smem_desc(sq, 16, 1024), ddo0 = make_smem_desc(sq + F_TILE, 16, 1024);
@@ -272,10 +273,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           const uint64_t kb0 = make_smem_desc(smem_u32(sKV + kvb * 2 * F_TILE), 8192, 1024);
           for (int u = 0; u < it.nu; ++u, up.next()) {
             const int stage = up.stage;
-            if (!mbar_wait(&st_full[stage], up.phase, abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
-            if (!mbar_wait(p_full, up.par, abort_flag, p.status, ST_WAIT_MISC, u)) { ok = false; break; }
+            if (!mbar_wait(&st_full[stage], up.phase, abort_flag, p.status, ST_WAIT_FULL, u, F_BACKOFF_NS)) { ok = false; break; }
+            if (!mbar_wait(p_full, up.par, abort_flag, p.status, ST_WAIT_MISC, u, F_BACKOFF_NS)) { ok = false; break; }
             if (u == 0) {          // the previous item's dK/dV must have been read out before they are overwritten
-              if (!mbar_wait(acc_empty, (uint32_t)((il & 1) ^ 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, seq)) { ok = false; break; }
+              if (!mbar_wait(acc_empty, (uint32_t)((il & 1) ^ 1), abort_flag, p.status, ST_WAIT_TMEM_EMPTY, seq, F_BACKOFF_NS)) { ok = false; break; }
             }
             tc_fence_after();
             const uint32_t sq = smem_u32(sQD + stage * 2 * F_TILE);
@@ -552,10 +553,10 @@ void attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  static bool configured[64] = {};
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  static bool configured[64] = {};          // the attribute is a per-device property of the kernel
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM);
-    configured[dev] = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const long long n_chunks = T * H * 8;
   attn_bwd_prep_kernel<<<(unsigned)((n_chunks + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, ldo, lddo, dsum, T, S, H);

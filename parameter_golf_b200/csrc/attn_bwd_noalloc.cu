@@ -60,7 +60,8 @@ extern "C" int pgb_attn_bwd_noalloc(const void* q, const void* k, const void* v,
   const int rc = pgb_attn_bwd_noalloc_setup();
   if (rc) return rc;
   int dev = 0;
-  cudaGetDevice(&dev);
+  const cudaError_t ge = cudaGetDevice(&dev);
+  if (ge != cudaSuccess || dev < 0 || dev >= kMaxDevices || g_scratch_ptr[dev] == nullptr) return fail(3, "cudaGetDevice", cudaGetErrorString(ge));
   try {
     pgb::attn_bwd(q, k, v, o, d_o, lse, g_scratch_ptr[dev], dq, dk, dv, ldq, ldk, ldv, ldo, lddo, lddq, lddk, lddv, B, S, H, Hkv, hd, accumulate_dv,
                   status, (cudaStream_t)stream);

@@ -345,10 +345,12 @@ void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, 
   p.ldy = ldy;
   p.lse = lse;
   p.status = status;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};          // the attribute is a per-device property of the kernel
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int grid = p.n_qt * B * Hkv * p.pairs;
   attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(mq, mk, mv, p);

@@ -128,13 +128,17 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// `backoff_ns` > 0 puts the thread to sleep between polls. Every poll is a shared-memory access, and shared memory's data
+// pipe also feeds the tensor core its operands: a single-thread role that waits most of the time (TMA producer, MMA
+// issuer) should poll a few times per microsecond, not a few hundred.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
-                                          int detail) {
+                                          int detail, uint32_t backoff_ns = 0) {
   if (mbar_test_wait(bar, parity)) return true;      // already complete: the non-suspending form answers much faster
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
+    if (backoff_ns) __nanosleep(backoff_ns);
     if (mbar_try_wait_hint(bar, parity, PGB_WAIT_HINT_NS)) return true;
     if ((++spins & 63u) == 0) {
       if (*abort_flag) return false;

@@ -550,10 +550,12 @@ static CUtensorMap operand_map(const void* ptr, bool kmajor, int rows, int K, lo
 template <int BN, bool AK, bool BKM, int EPI>
 static void launch_variant(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mx, const GemmKernelParams& p, int grid, cudaStream_t stream) {
   auto kern = gemm_tcgen05_kernel<BN, AK, BKM, EPI>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};          // the attribute is a per-device property of the kernel
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL);
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(ma, mb, mx, p);
 }

@@ -101,10 +101,12 @@ void gptq_rows(const float* Wp, const float* U, const float* scales, int8_t* Q, 
   if (bits < 2 || bits > 8) throw std::runtime_error("gptq_rows: bits must be in 2..8");
   const size_t smem = ((size_t)GQ_BLOCK * GQ_BLOCK + (size_t)GQ_WARPS * cols + GQ_WARPS * GQ_BLOCK) * sizeof(float);
   if (smem > 227 * 1024) throw std::runtime_error("gptq_rows: rows of more than " + std::to_string((227 * 1024 / 4 - GQ_BLOCK * GQ_BLOCK - GQ_WARPS * GQ_BLOCK) / GQ_WARPS) + " columns do not fit in shared memory");
-  static size_t configured = 0;
-  if (smem > configured) {
+  static size_t configured[64] = {};        // largest size set so far, per device (the attribute is a per-device property)
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || smem > configured[dev]) {
     cudaFuncSetAttribute(gptq_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    configured = smem;
+    if (dev >= 0 && dev < 64) configured[dev] = smem;
   }
   const float qmax = (float)((1 << (bits - 1)) - 1), qmin = -(float)(1 << (bits - 1));
   gptq_rows_kernel<<<(rows + GQ_WARPS - 1) / GQ_WARPS, GQ_WARPS * 32, smem, st>>>(Wp, U, scales, Q, rows, cols, qmin, qmax);

@@ -52,7 +52,7 @@ def _unsupported(m: ModelSpec) -> Optional[str]:
 
 class CudaEngine:
     def __init__(self, spec: RunSpec, params: Optional[Dict[str, torch.Tensor]], device, micro_batch: int, seq_len: int, train: bool = True,
-                 attention: str = "native", share: Optional["CudaEngine"] = None):
+                 share: Optional["CudaEngine"] = None):
         """``share``: another engine of the same spec and device whose parameters, gradients, optimizer state and bf16 weight
         copies this one aliases (everything that does not depend on the batch shape); only the activation buffers are new.
         Evaluation and test-time training switch between a scoring shape and a training shape many times per second, and
@@ -66,7 +66,6 @@ class CudaEngine:
         self.B, self.S = micro_batch, seq_len
         self.T = micro_batch * seq_len
         self.train = train
-        self.attention = attention
         self.qat = False
         m = self.m
         self.n, self.d, self.kv, self.mlp, self.H, self.Hkv, self.hd = m.num_layers, m.model_dim, m.kv_dim, m.mlp_dim, m.num_heads, m.num_kv_heads, m.head_dim
@@ -283,6 +282,8 @@ class CudaEngine:
             if self.gates and not self.parallel:
                 self.d_hx = torch.zeros(T, d, dtype=BF, device=dev)     # only its first `width` columns are ever written
             self.dsum = torch.empty(self.B, self.H, self.S, dtype=torch.float32, device=dev)
+            # fp32 dQ accumulator of the single-pass attention backward: zero between calls (the kernels restore that)
+            self.dq_acc = None if self.t.reproducible_backward else torch.zeros(self.B * self.H * self.S * self.hd, dtype=torch.float32, device=dev)
             self.d_skip = [buf(T, d) for _ in range(max(self.enc - 1, 0))] if self.unet else []
             self.d_xe = buf(T, d)
             if m.bigram.enabled:
@@ -333,14 +334,7 @@ class CudaEngine:
         q = self.qk_post[li][:, :d]
         k = self.qk_post[li][:, d:d + kv]
         v = self.qkv_pre[li][:, d + kv:]
-        if self.attention == "native":
-            self.lse[li] = N.attn_fwd(q, k, v, self.y[li], B, S, H, Hkv, hd, self.lse[li])
-            return
-        q4 = q.reshape(B, S, H, hd).transpose(1, 2)
-        k4 = k.reshape(B, S, Hkv, hd).transpose(1, 2)
-        v4 = v.reshape(B, S, Hkv, hd).transpose(1, 2)
-        out = torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=(H != Hkv))
-        self.y[li].copy_(out.transpose(1, 2).reshape(self.T, d))
+        self.lse[li] = N.attn_fwd(q, k, v, self.y[li], B, S, H, Hkv, hd, self.lse[li])
 
     def _attn_bwd(self, l, j):
         d, kv, B, S, H, Hkv, hd = self.d, self.kv, self.B, self.S, self.H, self.Hkv, self.hd
@@ -350,21 +344,8 @@ class CudaEngine:
         dq, dk = self.d_qk_post[:, :d], self.d_qk_post[:, d:d + kv]
         dv = self.d_qkv_pre[:, d + kv:]
         xsa = l in self.m.xsa_layers()
-        if self.attention == "native":
-            N.attn_bwd(q, k, v, self.y[j], self.d_y, self.lse[j], dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=xsa, dsum=self.dsum)
-            return
-        with torch.enable_grad():
-            q4 = q.reshape(B, S, H, hd).transpose(1, 2).detach().requires_grad_(True)
-            k4 = k.reshape(B, S, Hkv, hd).transpose(1, 2).detach().requires_grad_(True)
-            v4 = v.reshape(B, S, Hkv, hd).transpose(1, 2).detach().requires_grad_(True)
-            out = torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=(H != Hkv))
-            gq, gk, gv = torch.autograd.grad(out, (q4, k4, v4), self.d_y.reshape(B, S, H, hd).transpose(1, 2))
-        dq.copy_(gq.transpose(1, 2).reshape(self.T, d))
-        dk.copy_(gk.transpose(1, 2).reshape(self.T, kv))
-        if xsa:
-            dv.add_(gv.transpose(1, 2).reshape(self.T, kv))
-        else:
-            dv.copy_(gv.transpose(1, 2).reshape(self.T, kv))
+        N.attn_bwd(q, k, v, self.y[j], self.d_y, self.lse[j], dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=xsa, dsum=self.dsum,
+                   dq_acc=self.dq_acc, reproducible=self.t.reproducible_backward)
 
     def _block_fwd(self, j: int, x, skip, sw, recompute: bool = False):
         """Block of activation slot ``j`` on input ``x`` (with the U-Net skip it consumes, if any); returns the block output.

@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = True) -> str:
     from torch.utils import cpp_extension as ce
     os.makedirs(BUILD, exist_ok=True)
     cu, cpp, _ = _sources()
-    extra = os.environ.get("PGB_EXTRA_NVCC_FLAGS", "").split()     # development aid, e.g. -DPGB_DIAG_NO_EXP
+    extra = os.environ.get("PGB_EXTRA_NVCC_FLAGS", "").split()     # development aid, e.g. -DPGB_WAIT_LIMIT_NS=50000000ull
     cuda_home = ce.CUDA_HOME or "/usr/local/cuda"
     nvcc = os.path.join(cuda_home, "bin", "nvcc")
     inc = [f"-I{p}" for p in ce.include_paths("cuda")] + [f"-I{sysconfig.get_paths()['include']}", f"-I{CSRC}"]

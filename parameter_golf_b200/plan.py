@@ -201,6 +201,8 @@ def estimate_engine_memory(spec: RunSpec, micro_batch_tokens: int, train: bool =
         scratch = 2 * T * d * 7 + 2 * T * mlp + 2 * 2 * T * qkvw + 4 * T * H           # dx, dx_mid, d_m, d_z, d_y, d_h, d_x0, d_hu, d_qk_post, d_qkv_pre, dsum
         scratch += 2 * T * d * (max(enc - 1, 0) if m.skip_topology == "unet" else 0)    # U-Net skip gradients
         scratch += 2 * T * d                                                            # d_xe
+        if not t.reproducible_backward:
+            scratch += 4 * T * d                                                        # fp32 dQ accumulator of the single-pass attention backward
         if m.bigram.enabled:
             scratch += 2 * T * m.bigram.dim
         if gates and not m.parallel_residual.enabled:

@@ -188,6 +188,7 @@ class TrainSpec:
     val_batch_size: int = 524_288
     grad_wire_dtype: str = "bf16"       # wire dtype of bank-gradient reduce-scatter
     cuda_graph: bool = False            # replay the micro-batch forward+backward from a captured CUDA graph
+    reproducible_backward: bool = False # CUDA engine: bit-reproducible gradient kernels (two-kernel attention backward) instead of the faster fp32 red.add forms
     save_layer_acts: str = "all"        # CUDA engine activation checkpointing: all | edges | inner | recurrent | none
     checkpoint_every: int = 0
     checkpoint_path: Optional[str] = None

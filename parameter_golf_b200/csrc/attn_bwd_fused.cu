@@ -22,6 +22,15 @@
 // first so that the CTAs running at any time add into a few MB of the accumulator, which therefore stays in L2 between
 // the contributions of different key tiles.
 //
+// The per-query terms ride on the tensor core. P^T = exp2(c S^T - lse[q]) and dS^T = P^T (dP^T - D[q]) need one lse and one
+// D per query COLUMN of the transposed tiles, i.e. every thread would need every value: broadcast loads from shared memory
+// whose register write-back (128 B per value and warp) cost as many shared-memory data-pipe cycles per unit as the MMA
+// operand reads, and that pipe is what bounds this kernel. Instead a fifth 16-wide K step is appended to each score
+// product: A = a constant 128x16 tile whose first two columns are 1, B = a 128x16 tile per unit whose first two columns
+// hold the value split into a bf16 high and low part (-lse / c for S^T, -D for dP^T). The sums come out of the fp32
+// accumulator with the term already added (error of the split: 2^-17 relative), and the softmax threads read no shared
+// memory at all. The two small tiles are built by the fourth warp of the data-movement warpgroup.
+//
 // The accumulator uses a tile-local layout chosen for the adds: for each (batch, head, 128-row query tile) a 32 KB
 // block of 16 column chunks x 128 rows x 4 floats, so a warp's vector add covers 512 contiguous bytes.
 //
@@ -54,8 +63,10 @@ constexpr int F_REGS_LAUNCH = F_GROUPS == 4 ? 96 : 168, F_REGS_MOVE = F_GROUPS =
 static_assert(F_THREADS * F_REGS_LAUNCH <= 65536, "launch register count");
 static_assert(128 * (F_REGS_LAUNCH - F_REGS_MOVE) >= F_SOFTMAX_THREADS * (F_REGS_SOFTMAX - F_REGS_LAUNCH),
               "the softmax warpgroups would wait forever for registers nobody released");
-// K/V double-buffered, Q/dO stages, one dS^T tile (128 keys x 128 queries), lse/D vectors, barriers, alignment slack
-constexpr int F_SMEM = 4 * F_TILE + F_STAGES * 2 * F_TILE + 2 * F_TILE + F_STAGES * 1024 + 256 + 1024;
+constexpr int F_BIAS_TILE = 128 * 16 * 2;    // 4 KB: 128 rows x 16 bf16, un-swizzled K-major core matrices (8 rows x 16 B)
+// K/V double-buffered, Q/dO stages, one dS^T tile (128 keys x 128 queries), the bias-step tiles (one constant A tile,
+// {lse, D} B tiles per stage), barriers, alignment slack
+constexpr int F_SMEM = 4 * F_TILE + F_STAGES * 2 * F_TILE + 2 * F_TILE + (1 + 2 * F_STAGES) * F_BIAS_TILE + 256 + 1024;
 
 __device__ __forceinline__ void f_tma2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
@@ -83,6 +94,19 @@ __device__ __forceinline__ void red_add_v4(float* dst, uint32_t a, uint32_t b, u
 __device__ __forceinline__ uint64_t desc_at(uint64_t base, uint32_t bytes) {
   return (base & 0xFFFFFFFF00000000ull) | (uint64_t)((uint32_t)base + (bytes >> 4));
 }
+
+// Un-swizzled K-major operand of one 16-wide K step: core matrices of 8 rows x 16 bytes; the two matrices of a row group
+// that are adjacent along K sit `lbo` bytes apart, consecutive 8-row groups `sbo` bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc_plain(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+// byte offset of (row, first 16-byte K chunk) inside a bias tile
+__device__ __forceinline__ int bias_row_off(int r) { return (r >> 3) * 256 + (r & 7) * 16; }
 
 struct FusedParams {
   int B, S, H, Hkv, n_qt, group;
@@ -136,8 +160,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   uint8_t* sKV = smem;                                            // 2 buffers of {K, V}
   uint8_t* sQD = smem + 4 * F_TILE;                               // stages of {Q, dO}
   uint8_t* sDS = sQD + F_STAGES * 2 * F_TILE;                     // dS^T: 2 blocks (64 queries each) of 128 key rows x 128 B
-  float* sVec = reinterpret_cast<float*>(sDS + 2 * F_TILE);       // stages of {lse[128], D[128]}
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sVec) + F_STAGES * 1024);
+  uint8_t* sAX = sDS + 2 * F_TILE;                                // constant A tile of the bias step: columns 0, 1 = 1
+  uint8_t* sBX = sAX + F_BIAS_TILE;                               // stages of {lse tile, D tile}: columns 0, 1 = high, low part
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sBX + 2 * F_STAGES * F_BIAS_TILE);
   uint64_t* kv_full = bars;                   // 2
   uint64_t* kv_empty = kv_full + 2;           // 2
   uint64_t* st_full = kv_empty + 2;           // F_STAGES
@@ -158,7 +183,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_init(&kv_empty[i], 1);
     }
     for (int s = 0; s < F_STAGES; ++s) {
-      mbar_init(&st_full[s], 1);
+      mbar_init(&st_full[s], 2);                 // the TMA thread (with the tile bytes) and the bias-tile warp
       mbar_init(&st_empty[s], 1);
     }
     mbar_init(s_full, 1);
@@ -175,6 +200,16 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
+  if (warp >= 4) {
+    // bias-step tiles: everything zero except columns 0 and 1 of the constant A tile, which are 1
+    const int t = threadIdx.x - 128;
+    uint4* z = reinterpret_cast<uint4*>(sAX);
+    for (int i = t; i < (1 + 2 * F_STAGES) * F_BIAS_TILE / 16; i += F_SOFTMAX_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  __syncthreads();
+  if (threadIdx.x >= 128 && threadIdx.x < 256)
+    *reinterpret_cast<uint32_t*>(sAX + bias_row_off(threadIdx.x - 128)) = 0x3F803F80u;       // bf16 (1, 1)
+  fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -205,12 +240,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const int stage = up.stage;
             if (!mbar_wait(&st_empty[stage], up.phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, u, F_BACKOFF_NS)) { ok = false; break; }
             const int qrow = it.b * p.S + qi * 128;
-            const size_t vidx = ((size_t)it.b * p.H + head) * p.S + qi * 128;
-            mbar_expect_tx(&st_full[stage], 2 * F_TILE + 1024);
+            mbar_expect_tx(&st_full[stage], 2 * F_TILE);
             f_tma2d(sQD + stage * 2 * F_TILE, &map_q, &st_full[stage], head * F_HD, qrow);
             f_tma2d(sQD + stage * 2 * F_TILE + F_TILE, &map_do, &st_full[stage], head * F_HD, qrow);
-            f_bulk_g2s(sVec + stage * 256, p.lse + vidx, 512, &st_full[stage]);
-            f_bulk_g2s(sVec + stage * 256 + 128, p.Dsum + vidx, 512, &st_full[stage]);
             if (++g == p.group) { g = 0; head -= p.group - 1; ++qi; } else { ++head; }
           }
           ++il;
@@ -236,6 +268,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           if (!mbar_wait(&kv_full[kvb], (uint32_t)((il >> 1) & 1), abort_flag, p.status, ST_WAIT_FULL, -1, F_BACKOFF_NS)) { ok = false; break; }
           const uint32_t sk = smem_u32(sKV + kvb * 2 * F_TILE);
           const uint64_t dk0 = make_smem_desc(sk, 16, 1024), dv0 = make_smem_desc(sk + F_TILE, 16, 1024);
+          const uint64_t dax = make_smem_desc_plain(smem_u32(sAX), 128, 256);
           for (int u = 0; u < it.nu; ++u, up.next()) {
             const int stage = up.stage;
             if (!up.first && !mbar_wait(s_free, up.par ^ 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, u, F_BACKOFF_NS)) { ok = false; break; }
@@ -243,10 +276,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             tc_fence_after();
             const uint32_t sq = smem_u32(sQD + stage * 2 * F_TILE);
             const uint64_t dq0 = make_smem_desc(sq, 16, 1024), ddo0 = make_smem_desc(sq + F_TILE, 16, 1024);
+            const uint64_t dbl = make_smem_desc_plain(smem_u32(sBX + stage * 2 * F_BIAS_TILE), 128, 256);
 #pragma unroll
             for (int k = 0; k < 4; ++k) umma_ss(tmem_base, desc_at(dk0, k * 32), desc_at(dq0, k * 32), IDESC_T, k > 0);
+            umma_ss(tmem_base, dax, dbl, IDESC_T, 1u);                                    // S^T += 1 (-lse / c)^T
 #pragma unroll
             for (int k = 0; k < 4; ++k) umma_ss(tmem_base + 128, desc_at(dv0, k * 32), desc_at(ddo0, k * 32), IDESC_T, k > 0);
+            umma_ss(tmem_base + 128, dax, desc_at(dbl, F_BIAS_TILE), IDESC_T, 1u);        // dP^T += 1 (-D)^T
             umma_commit(s_full);
           }
           ++il;
@@ -301,6 +337,40 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
       }
     }
+    else {
+      // warp 3: the B tiles of the bias step. Lane l owns query rows 4 l .. 4 l + 3 of every unit.
+      bool ok = true;
+      UnitPos up;
+      const float inv_c = 1.f / p.scale_log2;
+      for (int seq = 0; ok; ++seq) {
+        FItem it;
+        const int rc = f_decode(p, seq, it);
+        if (rc == 2) break;
+        if (rc == 1) continue;
+        int head = it.kvh * p.group, qi = it.j, g = 0;
+        for (int u = 0; u < it.nu; ++u, up.next()) {
+          const int stage = up.stage;
+          const size_t vidx = ((size_t)it.b * p.H + head) * p.S + qi * 128 + lane * 4;
+          const float4 l4 = *reinterpret_cast<const float4*>(p.lse + vidx), d4 = *reinterpret_cast<const float4*>(p.Dsum + vidx);
+          if (!mbar_wait(&st_empty[stage], up.phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, u, F_BACKOFF_NS)) { ok = false; break; }
+          uint8_t* tl = sBX + stage * 2 * F_BIAS_TILE;
+          const float lv[4] = {l4.x * inv_c, l4.y * inv_c, l4.z * inv_c, l4.w * inv_c}, dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int off = bias_row_off(lane * 4 + e);
+            const __nv_bfloat16 lh = __float2bfloat16_rn(lv[e]), dh = __float2bfloat16_rn(dv4[e]);
+            const __nv_bfloat16 ll = __float2bfloat16_rn(lv[e] - __bfloat162float(lh)), dl = __float2bfloat16_rn(dv4[e] - __bfloat162float(dh));
+            *reinterpret_cast<uint32_t*>(tl + off) = (uint32_t)__bfloat16_as_ushort(lh) | ((uint32_t)__bfloat16_as_ushort(ll) << 16);
+            *reinterpret_cast<uint32_t*>(tl + F_BIAS_TILE + off) = (uint32_t)__bfloat16_as_ushort(dh) | ((uint32_t)__bfloat16_as_ushort(dl) << 16);
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&st_full[stage]);
+          if (++g == p.group) { g = 0; head -= p.group - 1; ++qi; } else { ++head; }
+        }
+      }
+      if (!ok) __syncwarp();
+    }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(F_REGS_SOFTMAX));
     const int w = (warp - 4) >> 2;                 // this group owns query columns [w F_GCOLS, (w + 1) F_GCOLS) of every unit
@@ -338,33 +408,29 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if constexpr (F_GCOLS == 64) PGB_TMEM_LD32(tS + 32, (s + 32));
         PGB_TMEM_LD32(tdP, dp);
         if constexpr (F_GCOLS == 64) PGB_TMEM_LD32(tdP + 32, (dp + 32));
-        // the lse / D vectors of this stage arrived with Q and dO; the wait overlaps the tensor-memory loads
-        if (!mbar_wait(&st_full[stage], up.phase, abort_flag, p.status, ST_WAIT_FULL, u)) { ok = false; break; }
         tmem_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free);        // the score buffers may take the next unit
-        const float2* vl2 = reinterpret_cast<const float2*>(sVec + stage * 256 + qbase);         // -(log2 lse) of this group's query rows
-        const float2* vd2 = reinterpret_cast<const float2*>(sVec + stage * 256 + 128 + qbase);   // -D of the same rows
         const bool diag = qi == j;
         uint32_t pp[F_GCOLS / 2], pd[F_GCOLS / 2];
         if (!diag) {
 #pragma unroll
           for (int c = 0; c < F_GCOLS; c += 2) {
-            const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, vl2[c >> 1]);
+            const float2 tt = __fmul2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2);   // the tile already holds S - lse / c
             const float2 pr = make_float2(f_ex2(tt.x), f_ex2(tt.y));
-            const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), vd2[c >> 1]));
+            const float2 dd = __fmul2_rn(pr, make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])));   // ... and dP - D
             pp[c >> 1] = pack_bf16x2(pr.x, pr.y);
             pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
           }
         } else {
 #pragma unroll
           for (int c = 0; c < F_GCOLS; c += 2) {
-            const float2 tt = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2, vl2[c >> 1]);
+            const float2 tt = __fmul2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2);   // the tile already holds S - lse / c
             float2 pr = make_float2(f_ex2(tt.x), f_ex2(tt.y));
             if (qbase + c < kk) pr.x = 0.f;              // query position before the key: masked
             if (qbase + c + 1 < kk) pr.y = 0.f;
-            const float2 dd = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])), vd2[c >> 1]));
+            const float2 dd = __fmul2_rn(pr, make_float2(__uint_as_float(dp[c]), __uint_as_float(dp[c + 1])));   // ... and dP - D
             pp[c >> 1] = pack_bf16x2(pr.x, pr.y);
             pd[c >> 1] = pack_bf16x2(dd.x, dd.y);
           }

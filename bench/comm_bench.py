@@ -119,7 +119,7 @@ def main():
                 s0, s1 = own[k]
                 if s1 > s0:
                     per = s[1] * s[2]
-                    C.comm_reduce_peers(gbuf.table, world, g_off[k] + s0 * per, (s1 - s0) * per, red[k], 1.0 / world, stats, 1.0)
+                    C.comm_reduce_peers(gbuf.table, world, g_off[k] + s0 * per, (s1 - s0) * per, red[k], 1.0 / world, stats, 1.0, None, 0, None)
                     ns_input(k, red[k])
 
         # NCCL baseline: equal padded shards, as the reference's Parallel Muon lays its banks out
@@ -148,7 +148,7 @@ def main():
                 s0, s1 = own[k]
                 if s1 > s0:
                     per = s[1] * s[2]
-                    C.comm_reduce_peers(gbuf.table, world, g_off[k] + s0 * per, (s1 - s0) * per, red[k], 1.0 / world, stats, 1.0)
+                    C.comm_reduce_peers(gbuf.table, world, g_off[k] + s0 * per, (s1 - s0) * per, red[k], 1.0 / world, stats, 1.0, None, 0, None)
 
         def nccl_rs_only():
             for k in shapes:

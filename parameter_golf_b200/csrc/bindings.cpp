@@ -28,7 +28,8 @@ int* status_ptr(const c10::optional<torch::Tensor>& status) {
 void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor D, bool a_kmajor, bool b_kmajor, int64_t epi, double alpha, double beta,
           double slope, c10::optional<torch::Tensor> aux, c10::optional<torch::Tensor> colscale, c10::optional<torch::Tensor> D2,
           int64_t splits, c10::optional<torch::Tensor> status, c10::optional<torch::Tensor> wait_flag, int64_t wait_value,
-          int64_t seg_row0, c10::optional<torch::Tensor> seg_D0, int64_t seg_row1, c10::optional<torch::Tensor> seg_D1) {
+          int64_t seg_row0, c10::optional<torch::Tensor> seg_D0, int64_t seg_row1, c10::optional<torch::Tensor> seg_D1,
+          c10::optional<torch::Tensor> batch_sumsq, int64_t sumsq_pow) {
   check_bf16(A, "A");
   check_bf16(B, "B");
   TORCH_CHECK(A.dim() == B.dim() && A.dim() == D.dim() && (A.dim() == 2 || A.dim() == 3), "gemm: operands must all be 2-D or all 3-D");
@@ -105,6 +106,13 @@ void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor D, bool a_kmajor, bool
     TORCH_CHECK(wait_flag->is_cuda() && wait_flag->scalar_type() == torch::kInt32, "wait_flag must be a CUDA int32 tensor");
     g.wait_flag = wait_flag->data_ptr<int>();
     g.wait_value = (int)wait_value;
+  }
+  if (batch_sumsq.has_value()) {
+    TORCH_CHECK(batch_sumsq->is_cuda() && batch_sumsq->scalar_type() == torch::kFloat32 && batch_sumsq->is_contiguous() && batch_sumsq->numel() >= g.batch &&
+                    (sumsq_pow == 1 || sumsq_pow == 2) && !f32_out,
+                "gemm: batch_sumsq must be fp32[batch] (power 1 or 2) with a bf16 epilogue");
+    g.batch_sumsq = batch_sumsq->data_ptr<float>();
+    g.sumsq_pow = (int)sumsq_pow;
   }
   pgb::gemm_bf16(g, cur_stream());
 }

@@ -56,9 +56,19 @@ __global__ void barrier_kernel(int* const* __restrict__ sig_tbl, int my_rank, in
 // out[i] = scale * sum_r src_tbl[r][off + i], i in [0, n); stats[0] += sq_weight * sum(out^2). n, off multiples of 4.
 // WORLD > 0 fixes the rank count at compile time: all peers' 16-byte loads of one element group are issued before the
 // first add, so a thread keeps WORLD NVLink requests in flight instead of one.
+// `wait_flag` (optional): a local counter that every rank bumps once its part of these gradients is final (release at
+// system scope after the producing kernels); each block polls it, bounded, before its first peer load, so the kernel can
+// be queued on a side stream while the backward pass that produces the gradients is still running.
 template <int WORLD>
 __global__ void __launch_bounds__(256) reduce_peers_kernel(const float* const* __restrict__ src_tbl, int world_rt, long long off, long long n,
-                                                           float* __restrict__ out, float scale, float* __restrict__ stats, float sq_weight) {
+                                                           float* __restrict__ out, float scale, float* __restrict__ stats, float sq_weight,
+                                                           const int* __restrict__ wait_flag, int wait_value, int* status) {
+  if (wait_flag != nullptr) {
+    __shared__ int ready;
+    if (threadIdx.x == 0) ready = wait_flag_ge(wait_flag, wait_value, status, wait_value) ? 1 : 0;
+    __syncthreads();
+    if (!ready) return;
+  }
   float s = 0.f;
   const long long stride = (long long)gridDim.x * blockDim.x * 4;
   if constexpr (WORLD > 0) {
@@ -233,15 +243,15 @@ void comm_barrier(int* const* sig_tbl, int my_rank, int world, int slot, int epo
   barrier_kernel<<<1, 32, 0, st>>>(sig_tbl, my_rank, world, slot, epoch, status);
 }
 void comm_reduce_peers(const float* const* src_tbl, int world, long long off, long long n, float* out, float scale, float* stats, float sq_weight,
-                       cudaStream_t st) {
+                       const int* wait_flag, int wait_value, int* status, cudaStream_t st) {
   if ((off % 4) || (n % 4)) throw std::runtime_error("reduce_peers: offset and count must be multiples of 4");
   if (n == 0) return;
   const int grid = (int)std::max<long long>(1, std::min<long long>((n / 4 + 255) / 256, 148 * 8));
   switch (world) {
-    case 2: reduce_peers_kernel<2><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight); break;
-    case 4: reduce_peers_kernel<4><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight); break;
-    case 8: reduce_peers_kernel<8><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight); break;
-    default: reduce_peers_kernel<0><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight); break;
+    case 2: reduce_peers_kernel<2><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight, wait_flag, wait_value, status); break;
+    case 4: reduce_peers_kernel<4><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight, wait_flag, wait_value, status); break;
+    case 8: reduce_peers_kernel<8><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight, wait_flag, wait_value, status); break;
+    default: reduce_peers_kernel<0><<<grid, 256, 0, st>>>(src_tbl, world, off, n, out, scale, stats, sq_weight, wait_flag, wait_value, status); break;
   }
 }
 void comm_scalar_allreduce(float* const* val_tbl, int* const* sig_tbl, int my_rank, int world, int val_slot, int sig_slot, int epoch, float* stats,

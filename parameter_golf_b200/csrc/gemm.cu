@@ -43,6 +43,8 @@ struct GemmKernelParams {
   int seg_rows[2];        // fp32 epilogues: rows >= seg_rows[k] (> 0) are written to seg_D[k] as row m - seg_rows[k]
   float* seg_D[2];
   int aux_l2_prefetch;     // the producer warp pulls the next tile's second operand into L2 through `map_x`
+  const float* batch_sumsq;   // optional: alpha and beta of batch b are multiplied by 1 / (sqrt(batch_sumsq[b]) + 1e-7) ^ sumsq_pow
+  int sumsq_pow;
 };
 
 constexpr int STG_PITCH = 64;
@@ -64,7 +66,7 @@ struct GemmSmem {
 __device__ __forceinline__ float act_fn(float x, float slope) { return x >= 0.f ? x : slope * x; }
 
 template <int EPI>
-__device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b, int m, int n0, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, float alpha, float beta, int b, int m, int n0, const uint32_t (&r)[32]) {
   // One thread: row m, columns n0 .. n0+31 of batch b. Caller guarantees m < M.
   const bool full = (n0 + 32 <= p.N);
   const long long off = (long long)b * p.stride_d + (long long)m * p.ldd + n0;
@@ -80,15 +82,15 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
     if (full && ((reinterpret_cast<uintptr_t>(d) & 15) == 0)) {
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
-        float4 q = make_float4(v[i] * p.alpha, v[i + 1] * p.alpha, v[i + 2] * p.alpha, v[i + 3] * p.alpha);
+        float4 q = make_float4(v[i] * alpha, v[i + 1] * alpha, v[i + 2] * alpha, v[i + 3] * alpha);
         if constexpr (EPI == EPI_F32) *reinterpret_cast<float4*>(d + i) = q;
         else atomicAdd(reinterpret_cast<float4*>(d + i), q);
       }
     } else {
       for (int i = 0; i < 32; ++i)
         if (n0 + i < p.N) {
-          if constexpr (EPI == EPI_F32) d[i] = v[i] * p.alpha;
-          else atomicAdd(d + i, v[i] * p.alpha);
+          if constexpr (EPI == EPI_F32) d[i] = v[i] * alpha;
+          else atomicAdd(d + i, v[i] * alpha);
         }
     }
     return;
@@ -115,8 +117,8 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
     float o2[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      if constexpr (EPI == EPI_BF16) o[i] = v[i] * p.alpha;
-      if constexpr (EPI == EPI_AXPBY_BF16) o[i] = p.alpha * v[i] + p.beta * a[i];
+      if constexpr (EPI == EPI_BF16) o[i] = v[i] * alpha;
+      if constexpr (EPI == EPI_AXPBY_BF16) o[i] = alpha * v[i] + beta * a[i];
       if constexpr (EPI == EPI_RESID_BF16) o[i] = a[i] + ((n0 + i < p.N) ? p.colscale[n0 + i] : 0.f) * v[i];
       if constexpr (EPI == EPI_ACT_SQ) {
         // the pre-activation is stored in bf16 and the activation is computed from that stored value,
@@ -163,7 +165,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmKernelParams& p, int b,
 __device__ __forceinline__ int stg_off(int row, int piece) { return row * STG_PITCH + ((piece ^ ((row >> 1) & 3)) << 4); }
 
 template <int EPI>
-__device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p, int b, int m_base, int lane, int n0, const uint32_t (&r)[32],
+__device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p, float alpha, float beta, int b, int m_base, int lane, int n0, const uint32_t (&r)[32],
                                                       const uint8_t* auxs, uint8_t* stg) {
   constexpr bool HAS_AUX = (EPI == EPI_AXPBY_BF16 || EPI == EPI_RESID_BF16 || EPI == EPI_MUL_ACTGRAD);
   const int srow = lane >> 2, spc = lane & 3;
@@ -194,8 +196,8 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p,
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     const float v = __uint_as_float(r[i]);
-    if constexpr (EPI == EPI_BF16) o[i] = v * p.alpha;
-    if constexpr (EPI == EPI_AXPBY_BF16) o[i] = p.alpha * v + p.beta * a[i];
+    if constexpr (EPI == EPI_BF16) o[i] = v * alpha;
+    if constexpr (EPI == EPI_AXPBY_BF16) o[i] = alpha * v + beta * a[i];
     if constexpr (EPI == EPI_RESID_BF16) o[i] = a[i] + cs[i] * v;
     if constexpr (EPI == EPI_MUL_ACTGRAD) {
       const float h = a[i];
@@ -470,6 +472,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m = tm * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       const int m_base = tm * BM + quarter * 32;
+      float alpha = p.alpha, beta = p.beta;
+      if (p.batch_sumsq != nullptr) {
+        // Newton-Schulz on an un-normalised input: the matrix norm enters as a per-matrix factor of the whole output
+        const float inv = 1.f / (sqrtf(p.batch_sumsq[b]) + 1e-7f);
+        const float f = p.sumsq_pow == 2 ? inv * inv : inv;
+        alpha *= f;
+        beta *= f;
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, ST_WAIT_TMEM_FULL, tile)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
@@ -488,10 +498,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
           PGB_TMEM_WAIT_LD32(rr);
           if constexpr (BF16_OUT) {
-            if (staged_ok && n0 + 32 <= p.N && (aux_async || !HAS_AUX)) epilogue_chunk_staged<EPI>(p, b, m_base, lane, n0, rr, slot, slot);
-            else if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr);
+            if (staged_ok && n0 + 32 <= p.N && (aux_async || !HAS_AUX)) epilogue_chunk_staged<EPI>(p, alpha, beta, b, m_base, lane, n0, rr, slot, slot);
+            else if (m < p.M) epilogue_chunk<EPI>(p, alpha, beta, b, m, n0, rr);
           } else {
-            if (m < p.M) epilogue_chunk<EPI>(p, b, m, n0, rr);
+            if (m < p.M) epilogue_chunk<EPI>(p, alpha, beta, b, m, n0, rr);
           }
         }
         if constexpr (HAS_AUX) {
@@ -624,6 +634,8 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.wait_flag = a.wait_flag;
   p.wait_value = a.wait_value;
+  p.batch_sumsq = a.batch_sumsq;
+  p.sumsq_pow = a.sumsq_pow;
   for (int k = 0; k < 2; ++k) {
     p.seg_rows[k] = a.seg_rows[k];
     p.seg_D[k] = a.seg_D[k];

@@ -40,6 +40,10 @@ struct GemmArgs {
   int wait_value = 0;
   int seg_rows[2] = {0, 0};  // fp32 epilogues: output rows >= seg_rows[k] go to seg_D[k] (row index rebased), same ldd
   float* seg_D[2] = {nullptr, nullptr};
+  // optional per-batch normalisation: the output of batch b is scaled by (1 / (sqrt(batch_sumsq[b]) + 1e-7)) ^ sumsq_pow
+  // (alpha and beta both), so a Newton-Schulz iteration can start from an un-normalised matrix
+  const float* batch_sumsq = nullptr;
+  int sumsq_pow = 1;
 };
 
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
@@ -111,7 +115,7 @@ void sgd_momentum(float* p, const float* g, float* mom, const float* hp, long lo
 // ---- peer-memory collectives (comm.cu) and symmetric memory (symm.cpp) --------------------------------------------------
 void comm_barrier(int* const* sig_tbl, int my_rank, int world, int slot, int epoch, int* status, cudaStream_t st);
 void comm_reduce_peers(const float* const* src_tbl, int world, long long off, long long n, float* out, float scale, float* stats, float sq_weight,
-                       cudaStream_t st);
+                       const int* wait_flag, int wait_value, int* status, cudaStream_t st);
 void comm_scalar_allreduce(float* const* val_tbl, int* const* sig_tbl, int my_rank, int world, int val_slot, int sig_slot, int epoch, float* stats,
                            int* status, cudaStream_t st);
 void comm_push_cast_rows(const float* src, void* const* dst_tbl, int world, long long dst_off, const float* rowscale, int scale_stride, int scale_mod,

@@ -127,6 +127,7 @@ class CudaEngine:
         self.adam_t = 0
         self.layer_flags = None          # set by the sharded optimizer: per-layer weight-ready counters
         self.layer_flag_value = 0
+        self.layer_wait_needed = False   # set after a sharded update: the next forward gates each layer with a one-thread wait kernel
         self.param_generation = 0        # bumped by every write to the fp32 master parameters
         self.cast_generation = -1        # generation the bf16 compute copies were made from
         if share is not None:            # the shared bf16 copies are already current
@@ -358,6 +359,13 @@ class CudaEngine:
         s_l = gpt.layer_ln_scale(m, l)
         C.mix_norm_fwd(x, self.x0, skip, sw, p["resid_mix"][l], self.x_in[li], self.h[li], s_l, self.eps)
         if self.layer_flags is not None and not recompute:
+            if self.layer_wait_needed:
+                # First forward after a sharded update: the layer's weights may still be on their way (this rank's own
+                # Newton-Schulz chain included, which needs SMs). A one-thread kernel waits for the ready counter here, so
+                # the persistent GEMM behind it never spins while holding every SM.
+                C.comm_wait_flag(self.layer_flags[l:l + 1], self.layer_flag_value, N.status_word(self.dev))
+                if l == self.n - 1:
+                    self.layer_wait_needed = False
             N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li], wait_flag=self.layer_flags[l:l + 1], wait_value=self.layer_flag_value)
         else:
             N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li])
@@ -610,24 +618,29 @@ class CudaEngine:
             grp["ema"] = grp["p"].clone()
 
     def newton_schulz(self, key: str, Bcount: Optional[int] = None) -> torch.Tensor:
-        """Orthogonalise ns[key]["X0"] (already normalised) in place of the ping-pong buffers; returns the result buffer."""
+        """Orthogonalise the momentum update ns[key]["U"] (bf16, NOT normalised; ns[key]["sq"] holds each matrix's sum of
+        squares) and return the result buffer. The first iteration folds the normalisation X0 = U / (|U| + 1e-7) into its
+        GEMM epilogues as a per-matrix factor (A = X0 X0^T = UU^T / |U|^2, X1 = a X0 + B X0 = (a U + B U) / |U|), so no
+        pass over the shard is spent on dividing by the norm (the reference normalises in a kernel of its own,
+        ``pg-kernels/src/gpu_kernels.rs:4520``)."""
         st = self.ns[key]
-        X, Xn, Am, Bm = st["X0"], st["X1"], st["A"], st["Bm"]
+        X, Xn, Am, Bm, Xalt, sq = st["U"], st["X1"], st["A"], st["Bm"], st["X0"], st["sq"]
         if Bcount is not None:
-            X, Xn, Am, Bm = X[:Bcount], Xn[:Bcount], Am[:Bcount], Bm[:Bcount]
+            X, Xn, Am, Bm, Xalt, sq = X[:Bcount], Xn[:Bcount], Am[:Bcount], Bm[:Bcount], Xalt[:Bcount], sq[:Bcount]
         tall = X.shape[1] > X.shape[2]
         for s in range(self.t.muon_ns_steps):
             a, b, c = ns_coeff(self.t.muon_ns_profile, s)
+            first = s == 0
             if tall:
-                N.gemm(X, X, Am, False, False)                                           # A = X^T X
+                N.gemm(X, X, Am, False, False, batch_sumsq=sq if first else None, sumsq_pow=2)                 # A = X^T X
             else:
-                N.gemm(X, X, Am, True, True)                                             # A = X X^T
+                N.gemm(X, X, Am, True, True, batch_sumsq=sq if first else None, sumsq_pow=2)                   # A = X X^T
             N.gemm(Am, Am, Bm, True, True, N.EPI_AXPBY_BF16, alpha=c, beta=b, aux=Am)    # B = b A + c A A   (A symmetric)
             if tall:
-                N.gemm(X, Bm, Xn, True, True, N.EPI_AXPBY_BF16, alpha=1.0, beta=a, aux=X)    # X = a X + X B
+                N.gemm(X, Bm, Xn, True, True, N.EPI_AXPBY_BF16, alpha=1.0, beta=a, aux=X, batch_sumsq=sq if first else None)    # X = a X + X B
             else:
-                N.gemm(Bm, X, Xn, True, False, N.EPI_AXPBY_BF16, alpha=1.0, beta=a, aux=X)   # X = a X + B X
-            X, Xn = Xn, X
+                N.gemm(Bm, X, Xn, True, False, N.EPI_AXPBY_BF16, alpha=1.0, beta=a, aux=X, batch_sumsq=sq if first else None)   # X = a X + B X
+            X, Xn = Xn, (Xalt if first else X)           # U itself is never overwritten: later iterations ping-pong between X1 and X0
         return X
 
     def optimizer_step(self):
@@ -641,7 +654,6 @@ class CudaEngine:
             st = self.ns[k]
             st["sq"].zero_()
             C.muon_momentum(self.g[k], self.mom[k], st["U"], st["sq"], self.hp, True)
-            C.muon_normalize(st["U"], st["X0"], st["sq"], 1e-7)
             X = self.newton_schulz(k)
             scale = max(1.0, self.p[k].shape[-2] / self.p[k].shape[-1]) ** 0.5
             C.muon_apply(self.p[k].view(-1), X.view(-1), self.ema[k].view(-1) if self.ema else None, self.hp, t.matrix_lr, t.muon_wd, scale, decay)
@@ -770,7 +782,9 @@ class EngineBackend:
             e.cast_weights()
         e.zero_grads()
         e.set_hp(lr_scale, momentum)
-        for ids, tgt in batches:
+        for i, (ids, tgt) in enumerate(batches):
+            if self.dist is not None and i == len(batches) - 1:
+                self.dist.arm()            # the last backward hands finished layers to the gradient reduction
             e.micro_step(ids.to(self.device, torch.int32, non_blocking=True), tgt.to(self.device, torch.int32, non_blocking=True), len(batches))
         if self.dist is not None:
             self.dist.step()
@@ -807,7 +821,9 @@ class EngineBackend:
         e.zero_grads()
         e.set_hp(lr_scale, momentum)
         dev_spans = spans if staged else self.stage_spans(spans)
-        for sp in dev_spans:
+        for i, sp in enumerate(dev_spans):
+            if self.dist is not None and i == len(dev_spans) - 1:
+                self.dist.arm()            # the last backward hands finished layers to the gradient reduction
             if self.spec.train.cuda_graph and e.layer_flags is None:
                 self._graphed_micro_step(sp, len(dev_spans))
             else:

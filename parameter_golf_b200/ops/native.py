@@ -130,13 +130,15 @@ def check_status(device=None, reset: bool = True):
 
 
 def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.0, slope=0.0, aux=None, colscale=None, D2=None, splits=0,
-         wait_flag=None, wait_value=0, segs=()):
+         wait_flag=None, wait_value=0, segs=(), batch_sumsq=None, sumsq_pow=1):
     """``segs``: up to two ``(first_row, tensor)`` pairs; with an fp32 epilogue the output rows from ``first_row`` on land in that
-    tensor instead of ``D`` (one product feeding several gradient matrices)."""
+    tensor instead of ``D`` (one product feeding several gradient matrices).
+    ``batch_sumsq``: fp32 ``[batch]``; the output of batch ``b`` (alpha and beta terms alike) is scaled by
+    ``(1 / (sqrt(batch_sumsq[b]) + 1e-7)) ** sumsq_pow``."""
     s0 = segs[0] if len(segs) > 0 else (0, None)
     s1 = segs[1] if len(segs) > 1 else (0, None)
     load().gemm(A, B, D, a_kmajor, b_kmajor, epi, alpha, beta, slope, aux, colscale, D2, splits, status_word(A.device), wait_flag, wait_value,
-                s0[0], s0[1], s1[0], s1[1])
+                s0[0], s0[1], s1[0], s1[1], batch_sumsq, sumsq_pow)
     return D
 
 

@@ -47,7 +47,7 @@ class PeerAllReduce:
         a, b = (n4 * r // w) * 4, (n4 * (r + 1) // w) * 4
         if b > a:
             mine = self.local[a:b]
-            self.C.comm_reduce_peers(self.buf.table, w, a, b - a, mine, 1.0 / w, None, 0.0)
+            self.C.comm_reduce_peers(self.buf.table, w, a, b - a, mine, 1.0 / w, None, 0.0, None, 0, None)
         self._barrier(_SIG_B)                       # every slice is reduced before anyone overwrites a peer's copy
         if b > a:
             self.C.comm_push_copy(self.local[a:b], self.buf.table, w, r, a)

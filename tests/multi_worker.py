@@ -10,6 +10,9 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+MICRO = 8            # micro-batches per step over all ranks: divisible by every tested world size (1, 2, 4, 8)
+
+
 def small_spec(world, backend):
     from parameter_golf_b200.spec import family_preset
     s = family_preset("record_11l")
@@ -20,8 +23,8 @@ def small_spec(world, backend):
     m.train_seq_len = m.eval_seq_len = 128
     t = s.train
     t.seq_len, t.world_size, t.backend = 128, world, "cuda_distributed" if world > 1 else "cuda_single"
-    t.batch_tokens = 2 * 4 * 128                     # two micro-batches of 4 sequences, whatever the world size
-    t.grad_accum_steps = 2 // world
+    t.batch_tokens = MICRO * 4 * 128                 # MICRO micro-batches of 4 sequences, whatever the world size
+    t.grad_accum_steps = MICRO // world
     t.distributed_optimizer_backend = backend
     t.tied_embed_lr = 0.01
     s.mode = "record"
@@ -53,7 +56,7 @@ def main():
         stats = torch.zeros(4, device="cuda")
         C.comm_barrier(sig.table, rank, world, 0, 1, native.status_word())
         red = torch.empty(n, device="cuda")
-        C.comm_reduce_peers(buf.table, world, 0, n, red, 1.0 / world, stats, 1.0 / world)
+        C.comm_reduce_peers(buf.table, world, 0, n, red, 1.0 / world, stats, 1.0 / world, None, 0, None)
         C.comm_scalar_allreduce(val.table, sig.table, rank, world, 0, 32, 1, stats, native.status_word())
         torch.cuda.synchronize()
         native.check_status()
@@ -62,7 +65,7 @@ def main():
         # reduce-scatter in place on my slice, then fan-out copy = two-shot all-reduce
         a, b = n * rank // world, n * (rank + 1) // world
         mine = buf.view(a * 4, (b - a,), torch.float32)
-        C.comm_reduce_peers(buf.table, world, a, b - a, mine, 1.0 / world, None, 0.0)
+        C.comm_reduce_peers(buf.table, world, a, b - a, mine, 1.0 / world, None, 0.0, None, 0, None)
         C.comm_barrier(sig.table, rank, world, 64, 1, native.status_word())
         C.comm_push_copy(mine, buf.table, world, rank, a)
         C.comm_barrier(sig.table, rank, world, 0, 2, native.status_word())
@@ -95,10 +98,11 @@ def main():
         T = be.engine.T
         g = torch.Generator().manual_seed(11)
         steps = 3
-        data = torch.randint(0, 256, (steps, 2, T + 1), generator=g).to(torch.int16)      # [step, micro-batch, span]
+        data = torch.randint(0, 256, (steps, MICRO, T + 1), generator=g).to(torch.int16)      # [step, micro-batch, span]
+        per = MICRO // world
         losses = []
         for s in range(steps):
-            mine = [data[s, rank].cuda()] if world == 2 else [data[s, 0].cuda(), data[s, 1].cuda()]
+            mine = [data[s, rank * per + i].cuda() for i in range(per)]
             losses.append(be.train_step_spans(mine, 1.0, 0.95, qat=(s == 2), staged=True))
         final = be.final_params()
         torch.cuda.synchronize()
@@ -106,10 +110,10 @@ def main():
         # single-GPU reference on rank 0 with both micro-batches accumulated locally
         if rank == 0:
             spec1 = small_spec(1, "all_reduce_replicated_muon")
-            spec1.train.grad_accum_steps = 2
+            spec1.train.grad_accum_steps = MICRO
             ref = EngineBackend(spec1, {k: v.clone() for k, v in params.items()})
             for s in range(steps):
-                ref.train_step_spans([data[s, 0].cuda(), data[s, 1].cuda()], 1.0, 0.95, qat=(s == 2), staged=True)
+                ref.train_step_spans([data[s, i].cuda() for i in range(MICRO)], 1.0, 0.95, qat=(s == 2), staged=True)
             rp = ref.final_params()
             errs = {}
             for k in final:

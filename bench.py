@@ -246,7 +246,7 @@ def run_native(args):
                        "l2": "inputs_larger_than_L2 (gigabytes of saved activations per micro-batch; no flush needed)"},
             "clocks": clocks,
             "e2e": {"value": GLOBAL_BATCH / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": accum * (T + 1) * 2 + 32, "d2h_bytes_per_step": 4, "last_loss": last_loss},
+                    "h2d_bytes_per_step": accum * (T + 1) * 2 + 32, "d2h_bytes_per_step": 20, "last_loss": last_loss},
             "gpu_launches": launches,
         }))
     if world > 1:

@@ -1,7 +1,7 @@
 """Muon collective sweep: the framework's peer-memory paths against NCCL (+cuBLAS) on the record parameter set.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 bench/comm_bench.py \
-        [--widths 1,2,4] [--iters 10] [--tokens 98304]
+        [--widths 1,2,4,8,16] [--iters 10] [--tokens 98304]
 
 Counterpart of the reference's ``nccl-bench`` (all-reduce / reduce-scatter / all-gather bus-bandwidth sweep,
 ``parameter-golf-rs/crates/pg-bench/src/bin/nccl_bench.rs:7-17``), restated on the tensors the optimizer really moves:
@@ -12,9 +12,10 @@ Two pipelines are timed per width, each as (ours) vs (NCCL + torch/cuBLAS), and 
 (``rs``: peer-load reduce vs ``reduce_scatter_tensor``; ``ag``: store fan-out + ready counters vs ``all_gather_into_tensor``):
 
 * ``rs_ns``  gradient reduce-scatter fused with the Newton-Schulz input: every rank reduces its own slots of the fp32
-  gradient banks straight out of its peers' memory (plain NVLink loads, no staging copy), then momentum + Frobenius
-  normalisation produce the bf16 Newton-Schulz input.  Baseline: ``reduce_scatter_tensor`` per bank (fp32, padded to
-  equal shards as the reference's Parallel Muon does) followed by the same two kernels.
+  gradient banks straight out of its peers' memory (plain NVLink loads, no staging copy), then one kernel applies
+  momentum and Nesterov and writes the bf16 Newton-Schulz input with its sum of squares (the normalisation itself rides
+  on the first Newton-Schulz products).  Baseline: ``reduce_scatter_tensor`` per bank (fp32, padded to equal shards as
+  the reference's Parallel Muon does) followed by the momentum kernel and a normalisation kernel, the reference's sequence.
 * ``ag_qkv`` updated-weight all-gather fused with the next forward's first QKV GEMM: owners cast their fp32 slots to
   bf16 and store them into every rank's weight buffer, bump per-layer ready counters, and the GEMM's producer warp
   polls layer 0's counter before its first weight tile.  Baseline: ``all_gather_into_tensor`` per bank (bf16) followed
@@ -23,7 +24,8 @@ Two pipelines are timed per width, each as (ours) vs (NCCL + torch/cuBLAS), and 
 Device-timed with CUDA events, max over ranks, 3 warm-ups.  Every timed repetition starts with a barrier so that no
 rank's clock starts while a peer still works on the previous one.  Reports, per pipeline: milliseconds, the bytes that
 have to cross NVLink per rank, bus GB/s (bytes / time) and the fraction of the roofline
-``max(bytes / 770 GB/s, GEMM FLOPs / measured bf16 peak)``.
+``max(bytes / link bandwidth, GEMM FLOPs / measured bf16 peak)`` for both link figures: the 770 GB/s peer copy measured on
+this pool and the 900 GB/s nominal.
 """
 import argparse
 import json
@@ -39,6 +41,7 @@ from parameter_golf_b200.parallel.dist_engine import shard_range  # noqa: E402
 from parameter_golf_b200.parallel.symm import SymmetricBuffer  # noqa: E402
 
 LINK_GBS = 770.0        # measured peer copy bandwidth per direction per GPU on this pool
+LINK_NOMINAL_GBS = 900.0   # NVLink 5 nominal per direction per GPU
 LAYERS = 11
 
 
@@ -65,7 +68,7 @@ def timed(fn, iters, pre):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--widths", default="1,2,4")
+    ap.add_argument("--widths", default="1,2,4,8,16")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--tokens", type=int, default=98304)
     args = ap.parse_args()
@@ -111,7 +114,6 @@ def main():
             if g.shape[0]:
                 sq[k].zero_()
                 C.muon_momentum(g, mom[k], U[k], sq[k], hp, True)
-                C.muon_normalize(U[k], X0[k], sq[k], 1e-7)
 
         def ours_rs():
             barrier()                                  # every rank's gradients are final before anyone reads them
@@ -256,10 +258,17 @@ def main():
         del shard_w, full_w, master, X, Y
         wbuf.close()
         torch.cuda.empty_cache()
+        for r in rows[-4:]:
+            nominal = r["nvlink_bytes_per_rank"] / (LINK_NOMINAL_GBS * 1e9) * 1e3
+            if "gemm_gflop" in r:
+                nominal = max(nominal, r["gemm_gflop"] * 1e9 / (peak_tf * 1e12) * 1e3)
+            r["ours_frac_of_nominal_roofline"] = round(nominal / r["ours_ms"], 3)
+            r["nccl_frac_of_nominal_roofline"] = round(nominal / r["nccl_ms"], 3)
         if rank == 0:
             for r in rows[-4:]:
-                print(f"[w={w} N={world}] {r['pipeline']:7s} ours {r['ours_ms']:9.3f} ms ({r['ours_bus_gbs']:7.1f} GB/s, {r['ours_frac_of_roofline']:.2f} of roofline)"
-                      f"   NCCL {r['nccl_ms']:9.3f} ms ({r['nccl_bus_gbs']:7.1f} GB/s, {r['nccl_frac_of_roofline']:.2f})", flush=True)
+                print(f"[w={w} N={world}] {r['pipeline']:7s} ours {r['ours_ms']:9.3f} ms ({r['ours_bus_gbs']:7.1f} GB/s, {r['ours_frac_of_roofline']:.2f} of the 770 GB/s roofline, "
+                      f"{r['ours_frac_of_nominal_roofline']:.2f} of the 900 GB/s one)   NCCL {r['nccl_ms']:9.3f} ms ({r['nccl_bus_gbs']:7.1f} GB/s, {r['nccl_frac_of_roofline']:.2f}, "
+                      f"{r['nccl_frac_of_nominal_roofline']:.2f})", flush=True)
     if rank == 0:
         print(json.dumps({"bench": "muon_collectives", "gpus": world, "link_gbs": LINK_GBS, "bf16_peak_tflops": peak_tf, "rows": rows}))
     sig.close()

@@ -753,7 +753,7 @@ class EngineRunner:
 class EngineBackend:
     """Training backend used by `parameter_golf_b200.train.VariantRunner` for the CUDA backends."""
 
-    def __init__(self, spec: RunSpec, params: Dict[str, torch.Tensor]):
+    def __init__(self, spec: RunSpec, params: Dict[str, torch.Tensor], overlap_optimizer: bool = True):
         import os
         from ..train import step_batch_plan
         self.spec = spec
@@ -769,7 +769,7 @@ class EngineBackend:
         self.dist = None
         if t.world_size > 1:
             from ..parallel.dist_engine import DistributedStep
-            self.dist = DistributedStep(self.engine, spec)
+            self.dist = DistributedStep(self.engine, spec, overlap=overlap_optimizer)
 
     def set_token_weight_table(self, table) -> None:
         self._graph_state = None      # a captured micro-step would keep replaying the unweighted loss kernel

@@ -63,8 +63,11 @@ def shard_range(slots: int, rank: int, world: int) -> Tuple[int, int]:
 
 
 class DistributedStep:
-    def __init__(self, engine, spec: RunSpec, group=None):
+    def __init__(self, engine, spec: RunSpec, group=None, overlap: bool = True):
+        """``overlap=False`` queues the whole sharded step on the caller's stream after the backward pass (the serial
+        schedule; kept so that the overlap can be measured against it, `bench/dist_tail_profile.py`)."""
         self.e, self.spec, self.group = engine, spec, group
+        self.overlap = overlap
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.sharded = spec.train.distributed_optimizer_backend == "sharded_parallel_muon"
         self.C = N.load()
@@ -133,9 +136,13 @@ class DistributedStep:
         """Streams, events and buffers of the overlapped sharded step."""
         e = self.e
         dev = e.dev
-        self.comm_stream = torch.cuda.Stream(device=dev, priority=-1)
         self.bank_order = sorted(gpt.BANKS, key=lambda b: -e.p[b].numel())
-        self.bank_streams = {k: torch.cuda.Stream(device=dev, priority=-1) for k in self.bank_order}
+        if self.overlap:
+            self.comm_stream = torch.cuda.Stream(device=dev, priority=-1)
+            self.bank_streams = {k: torch.cuda.Stream(device=dev, priority=-1) for k in self.bank_order}
+        else:
+            self.comm_stream = torch.cuda.current_stream(dev)
+            self.bank_streams = {k: self.comm_stream for k in self.bank_order}
         self.ev_layer = [torch.cuda.Event() for _ in range(e.n + 1)]          # index n: end of the backward pass
         self.ev_clip, self.ev_adam = torch.cuda.Event(), torch.cuda.Event()
         self.ev_bank = {k: torch.cuda.Event() for k in self.bank_order}
@@ -233,7 +240,7 @@ class DistributedStep:
     def arm(self):
         """Call before the last micro-batch of a step: its backward pass then hands every finished layer to the
         communication stream (`_layer_done`)."""
-        if not self.sharded:
+        if not self.sharded or not self.overlap:
             return
         self.armed = True
         self.e.backward_observer = self._layer_done
@@ -318,6 +325,7 @@ class DistributedStep:
                 self._mark("bank_" + k, bs)
         self.bank_pending = True
         main.wait_event(self.ev_adam)               # peers have consumed this rank's gradients; replicated weights are current
+        self._mark("main stream resumes", main)
         e.layer_flag_value = 6 * (self.steps_done + 1 + self.repushes)
         e.layer_wait_needed = True                  # the next forward gates each layer on its ready counter with a one-thread kernel
         # the bank chains keep reading this step's hyper-parameters; the next step uploads into the other buffer

@@ -46,5 +46,5 @@ def test_distributed_step_matches_single_gpu(mode, port, nproc):
     reach the 4- and 8-peer reduction kernels and shard maps in which some ranks own no slot of a bank."""
     res = run_workers(mode, nproc=nproc, port=port + nproc)
     assert res[0]["worst_rel_update_err"] < 0.05, res[0]
-    for r in range(1, nproc):
-        assert res[0]["mean_losses"] == res[r]["mean_losses"]
+    for r in range(1, nproc):          # the all-reduced loss: equal up to the summation order of the library's all-reduce
+        assert res[r]["mean_losses"] == pytest.approx(res[0]["mean_losses"], rel=1e-9)

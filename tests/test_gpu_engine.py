@@ -64,13 +64,43 @@ def test_one_step_loss_and_gradients_match_oracle(variant):
     native.check_status()
     loss = float(eng.loss_sum[0]) / eng.T
     ref_loss, ref = oracle_grads(spec, params, ids, tgt)
-    assert abs(loss - float(ref_loss)) < 2e-2, (loss, float(ref_loss))
+    assert abs(loss - float(ref_loss)) < 5e-3, (loss, float(ref_loss))
     worst = {}
     for k, g in ref.items():
         worst[k] = rel_err(eng.g[k], g)
     # bf16 activations/gradients vs an fp64 oracle; q_gain is one number per head summed over every token with heavy cancellation
-    bad = {k: v for k, v in worst.items() if v > (0.2 if k == "q_gain" else 0.06)}
+    bad = {k: v for k, v in worst.items() if v > (0.06 if k == "q_gain" else 0.03)}
     assert not bad, worst
+
+
+def test_one_step_at_the_record_width_matches_the_oracle():
+    """The shapes the product runs: d = 512, 8 query / 4 KV heads, MLP 1536, vocabulary 1024, bigram table 3072 x 128,
+    sequences of 2048 (three layers, two of them with XSA, two sequences). The oracle is the autograd model in fp32 on the
+    GPU. This is where the 256-wide GEMM tiles with N = 1536, the two-vector row kernels and 8/4-head attention meet a
+    reference; the small-shape tests select other template instances."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine
+    from parameter_golf_b200.models.runner import OracleRunner
+    from parameter_golf_b200.ops import native
+    from parameter_golf_b200.spec import family_preset
+    spec = family_preset("record_11l")
+    spec.model.num_layers, spec.model.xsa_last_n = 3, 2
+    spec.train.backend, spec.train.world_size, spec.train.seq_len, spec.train.batch_tokens = "cuda_single", 1, 2048, 2 * 2048
+    spec.validate()
+    params = gpt.fill_deterministic(spec.model)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 1024, (2, 2048))
+    tgt = torch.randint(0, 1024, (2, 2048))
+    eng = CudaEngine(spec, params, "cuda", 2, 2048)
+    eng.zero_grads()
+    eng.micro_step(ids.cuda().int(), tgt.cuda().int(), 1)
+    torch.cuda.synchronize()
+    native.check_status()
+    loss = float(eng.loss_sum[0]) / eng.T
+    ref_loss, ref = OracleRunner(spec.model, {k: v.cuda().float() for k, v in params.items()}).loss_and_grads(ids.cuda(), tgt.cuda())
+    assert abs(loss - float(ref_loss)) < 2e-3 * float(ref_loss), (loss, float(ref_loss))
+    worst = {k: rel_err(eng.g[k], g) for k, g in ref.items()}
+    assert max(worst.values()) < 0.05, worst
 
 
 def test_forward_logits_and_nll_match_oracle():

@@ -124,3 +124,26 @@ def test_row_segments_scatter_one_product_into_three_gradient_matrices():
     _close(upd[:dkv], ref[dq:dq + dkv], 5e-3)
     _close(upd[dkv + 64 + dq:], ref[dq + dkv:], 5e-3)
     assert upd[dkv:dkv + 64].abs().max().item() == 0.0                        # the gap between the slots is untouched
+
+
+def test_gemm_producer_gives_up_on_a_weight_flag_nobody_sets_and_the_context_survives():
+    """The weight operand of a QKV product may be gated on a ready counter that peer ranks bump. If it never reaches the
+    expected value the producer warp's bounded wait runs out: the kernel reports to the status word, every role unwinds
+    (no tensor-memory or bulk-copy state is left behind) and the next product on the same context is correct."""
+    from parameter_golf_b200.ops import native as n
+    torch.manual_seed(0)
+    A = (torch.randn(512, 512, device="cuda") * 0.5).bfloat16()
+    W = (torch.randn(1024, 512, device="cuda") * 0.5).bfloat16()
+    D = torch.zeros(512, 1024, device="cuda", dtype=torch.bfloat16)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    n.status_word().zero_()
+    n.gemm(A, W, D, wait_flag=flag, wait_value=3)            # nothing ever bumps the flag
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="wait_flag"):
+        n.check_status()
+    flag.fill_(3)
+    n.gemm(A, W, D, wait_flag=flag, wait_value=3)
+    torch.cuda.synchronize()
+    n.check_status()
+    ref = A.float() @ W.float().t()
+    assert (D.float() - ref).abs().max().item() < 0.02 * ref.abs().max().item()

@@ -251,3 +251,24 @@ def load_validation_tokens(pattern: str, seq_len: int, max_tokens: Optional[int]
     if usable <= 0:
         raise ShardError(f"validation split is shorter than one sequence of {seq_len}")
     return toks[: usable + 1]
+
+
+def _main(argv=None) -> int:
+    """``python -m parameter_golf_b200.data.shards --root DIR [--vocab 1024] [--train-tokens N] [--val-tokens N] [--train-shards K] [--seed S]``:
+    write the seeded Zipf/Markov dataset (stand-in for the reference's FineWeb download and tokenisation tooling, ``data/``)."""
+    import argparse
+    ap = argparse.ArgumentParser(prog="parameter_golf_b200.data.shards")
+    ap.add_argument("--root", required=True)
+    ap.add_argument("--vocab", type=int, default=1024)
+    ap.add_argument("--train-tokens", type=int, default=1 << 24)
+    ap.add_argument("--val-tokens", type=int, default=1 << 20)
+    ap.add_argument("--train-shards", type=int, default=1)
+    ap.add_argument("--seed", type=int, default=1337)
+    a = ap.parse_args(argv)
+    write_synthetic_dataset(a.root, a.vocab, a.train_tokens, a.val_tokens, a.train_shards, a.seed)
+    print(f"wrote {a.train_shards} training shard(s) of {a.train_tokens // max(a.train_shards, 1)} tokens and {a.val_tokens} validation tokens under {a.root}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_main())

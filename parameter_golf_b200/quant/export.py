@@ -51,7 +51,7 @@ def metadata_json(spec: RunSpec, bits: Dict[str, int]) -> str:
         "num_kv_heads": m.num_kv_heads, "head_dim": m.head_dim, "mlp_dim": m.mlp_dim,
         "attn_out_gate_enabled": int(m.attn_out_gate.enabled), "attn_out_gate_width": m.attn_out_gate.width,
         "sparse_attn_gate_enabled": int(m.sparse_attn_gate.enabled), "sparse_attn_gate_width": m.sparse_attn_gate.width,
-        "groups": {g: bits[g] for g in GROUPS},
+        "groups": {g: bits[g] for g in GROUPS}, "code_storage": q.code_storage,
     }
     return json.dumps(md, separators=(",", ":"))
 
@@ -72,10 +72,16 @@ def quantize_groups(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed:
     return out, bits
 
 
-def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=None) -> bytes:
-    """Serialise to the (uncompressed) PGRS byte string."""
+def _store_codes(q: torch.Tensor, bits: int, storage: str) -> bytes:
+    if storage == "bytes":
+        return q.cpu().numpy().astype(np.int8).tobytes()
+    return C.pack_bits(q.cpu().numpy(), bits)
+
+
+def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=None, quantized=None) -> bytes:
+    """Serialise to the (uncompressed) PGRS byte string. ``quantized`` = (codes and scales per group, bits) skips quantisation."""
     m = spec.model
-    qs, bits = quantize_groups(spec, params, precomputed)
+    qs, bits = quantized if quantized is not None else quantize_groups(spec, params, precomputed)
     views = bank_views(m, params)
     recs = []
     for g in GROUPS:
@@ -88,7 +94,7 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
             recs.append(_f16(f"{g}.lqer.a.scale", f.a_s))
             recs.append(C.TensorRecord(f"{g}.lqer.b.weight", tuple(f.b_q.shape), "i8", C.pack_bits(f.b_q.numpy(), spec.quant.lqer.b_bits)))
             recs.append(_f16(f"{g}.lqer.b.scale", f.b_s))
-        recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", C.pack_bits(q.cpu().numpy(), bits[g])))
+        recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", _store_codes(q, bits[g], spec.quant.code_storage)))
         recs.append(_f16(f"{g}.scale", s16))
     if m.bigram.enabled:
         recs.append(_f16("bigram_embed", params["bigram_embed"].reshape(-1)))
@@ -122,7 +128,26 @@ def export_model(spec: RunSpec, params: Dict[str, torch.Tensor], path: Optional[
         from .int8_baseline import export_int8_zlib
         blob, _ = export_int8_zlib({k: v.detach().float().cpu() for k, v in params.items()})
     else:
-        blob = C.compress_payload(build_artifact(spec, params, precomputed), spec.quant.compression)
+        qs, bits = quantize_groups(spec, params, precomputed)
+        blob = C.compress_payload(build_artifact(spec, params, quantized=(qs, bits)), spec.quant.compression)
+        limit = spec.quant.target_artifact_bytes - code_bytes()
+        if spec.quant.prune_to_target and spec.quant.scheme != "none" and len(blob) > limit > 0:
+            # +-1 pruning to the byte budget (the 2026-03-25 record's selective prune, train_gpt.py:1997-2040): the codes whose
+            # removal costs least squared error go to zero until the compressed artifact fits beside the code
+            from .quantize import selective_prune_to_target
+            codes = {g: qs[g][0] for g in GROUPS if g != "tok_emb"}
+            scales = {g: qs[g][1] for g in GROUPS if g != "tok_emb"}
+
+            def size_of(cand):
+                merged = dict(qs)
+                merged.update({g: (cand[g], qs[g][1]) for g in cand})
+                return len(C.compress_payload(build_artifact(spec, params, quantized=(merged, bits)), spec.quant.compression))
+
+            pruned, count = selective_prune_to_target(codes, scales, size_of, limit, max_iters=8)
+            merged = dict(qs)
+            merged.update({g: (pruned[g], qs[g][1]) for g in pruned})
+            blob = C.compress_payload(build_artifact(spec, params, quantized=(merged, bits)), spec.quant.compression)
+            export_model.last_pruned = count
     if path:
         os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
         with open(path, "wb") as f:
@@ -167,7 +192,7 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
         bits = 6 if legacy else int(md["groups"][g])
         wrec, srec = by[f"{g}.weight"], by[f"{g}.scale"]
         rows, cols = wrec.dims
-        if legacy and len(wrec.data) == rows * cols:
+        if (legacy or md.get("code_storage") == "bytes") and len(wrec.data) == rows * cols:
             q = torch.from_numpy(np.frombuffer(wrec.data, dtype=np.int8).astype(np.int32).reshape(rows, cols))
         else:
             q = torch.from_numpy(C.unpack_bits(wrec.data, rows * cols, bits).reshape(rows, cols))

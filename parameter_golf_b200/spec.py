@@ -221,6 +221,9 @@ class QuantSpec:
     prune_keep_ratio: Optional[float] = None
     lqer: LqerSpec = field(default_factory=LqerSpec)
     compression: str = "zstd22"
+    code_storage: str = "bit_packed"    # bit_packed: codes packed LSB-first at their bit width (the Rust engine's artifact);
+                                        # bytes: one int8 per code (the Python records' container: the entropy coder then sees the code distribution)
+    prune_to_target: bool = True        # zero the cheapest +-1 codes until artifact + code fit target_artifact_bytes
     matrix_bits: int = 6
     embed_bits: int = 8
     attn_gate_bits: int = 8
@@ -412,6 +415,7 @@ class RunSpec:
         chk(t.distributed_optimizer_backend in DIST_OPT_BACKENDS, "unknown distributed_optimizer_backend")
         chk(q.scheme in QUANT_SCHEMES, f"quant.scheme must be one of {QUANT_SCHEMES}")
         chk(q.compression in COMPRESSION_MODES, "unknown quant.compression")
+        chk(q.code_storage in ("bit_packed", "bytes"), "quant.code_storage must be bit_packed or bytes")
         chk(q.calibration in CALIBRATION_MODES, "unknown quant.calibration")
         chk(e.adaptation_backend in ADAPTATION_BACKENDS, "unknown eval.adaptation_backend")
         chk(t.save_layer_acts in ("all", "edges", "inner", "recurrent", "none"), "train.save_layer_acts must be all|edges|inner|recurrent|none")

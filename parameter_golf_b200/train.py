@@ -183,6 +183,8 @@ class VariantResult:
     artifact_bytes: int = 0
     code_bytes: int = 0
     budget_ok: bool = True
+    prequant_val_loss: float = float("nan")
+    prequant_val_bpb: float = float("nan")
     val_loss: float = float("nan")
     val_bpb: float = float("nan")
     eval_ms: float = 0.0
@@ -396,6 +398,24 @@ class VariantRunner:
         elif ema is not None and ema.shadow is not None:
             log.info("ema:applying EMA weights")
             final = {k: v.cpu().clone() for k, v in ema.shadow.items()}
+        # ---- diagnostic before quantisation: the averaged fp32 weights on non-overlapping validation sequences ----------
+        # (the reference logs the same right after applying EMA, train_gpt.py of the 2026-03-23 record: "post-EMA diagnostic")
+        if mode == "record" and t.validation_data_pattern:
+            with timers.time("prequant_eval"):
+                t_diag = time.perf_counter()
+                val_d = load_validation_tokens(t.validation_data_pattern, m.eval_seq_len, spec.eval.max_tokens)
+                luts_d = (BpbLuts.from_sentencepiece(spec.eval.tokenizer_vocab_path, m.vocab_size) if spec.eval.tokenizer_vocab_path
+                          else BpbLuts.seeded(m.vocab_size, spec.eval.byte_table_seed))
+                if t.backend == "cpu":
+                    runner_d, ddev = OracleRunner(m, final), "cpu"
+                else:
+                    from .models.engine import EngineRunner
+                    runner_d, ddev = EngineRunner(spec, final, device, train=False), device
+                res.prequant_val_loss, res.prequant_val_bpb = eval_contiguous(runner_d.nll, val_d, m.eval_seq_len, luts_d, t.rank, t.world_size,
+                                                                              spec.eval.batch_windows, ddev)
+                del runner_d
+                log.info(f"prequant_diagnostic val_loss:{res.prequant_val_loss:.4f} val_bpb:{res.prequant_val_bpb:.4f} "
+                         f"eval_time:{1000.0 * (time.perf_counter() - t_diag):.0f}ms")
         with timers.time("export"):
             precomputed = None
             if spec.quant.scheme == "full_gptq_int6" and spec.quant.calibration == "self_generated":

@@ -305,3 +305,32 @@ def test_ternary_quantiser_base3_packing_and_scale_fix():
     assert 1.0 < T3.bits_per_param(q, s) < 2.2                       # ~1.6 bits of entropy per weight plus scales
     with pytest.raises(ValueError):
         T3.deserialize(T3.serialize(q, s)[:-1])
+
+
+def test_byte_per_code_storage_round_trips_and_prune_to_target_meets_the_budget():
+    """`quant.code_storage = "bytes"` keeps one int8 per code (the container of the Python records, which lets the entropy
+    coder see the code distribution); it must load to the same weights as the bit-packed form. With a byte target below the
+    artifact's size the exporter zeroes the cheapest +-1 codes until the compressed artifact fits beside the code."""
+    import torch
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.quant import export as E
+    from parameter_golf_b200.spec import family_preset
+    spec = family_preset("tiny_cpu")
+    spec.quant.scheme = "gptq_lite_int6"
+    spec.validate()
+    torch.manual_seed(0)
+    params = {k: (torch.randn_like(v) * 0.05 if v.ndim >= 2 else v.clone()) for k, v in gpt.init_params(spec.model, 0).items()}
+    packed = E.load_artifact(E.export_model(spec, params), spec)
+    spec.quant.code_storage = "bytes"
+    blob = E.export_model(spec, params)
+    loaded = E.load_artifact(blob, spec)
+    for k in packed:
+        assert torch.equal(packed[k], loaded[k]), k
+    code = E.code_bytes()
+    spec.quant.target_artifact_bytes = code + int(len(blob) * 0.992)
+    small = E.export_model(spec, params)
+    assert len(small) <= spec.quant.target_artifact_bytes - code < len(blob)
+    assert E.export_model.last_pruned > 0
+    pruned = E.load_artifact(small, spec)
+    changed = sum(int((pruned[k] != loaded[k]).sum()) for k in ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank"))
+    assert 0 < changed and torch.equal(pruned["tok_emb"], loaded["tok_emb"])          # only matrix codes of magnitude one were dropped

@@ -149,6 +149,8 @@ def _apply_sgd(runner, model, grads, names, mom, lr, ev: EvalSpec, mode, all_red
     with torch.no_grad():
         for n in names:
             g = grads[n].float() * f
+            if mom[n].device != g.device:          # the runner moves its parameters to the device on first use
+                mom[n] = mom[n].to(g.device)
             mom[n].mul_(ev.ttt_momentum).add_(g)
             runner.params[n].add_(mom[n].to(runner.params[n].dtype), alpha=-lr)
     if hasattr(runner, "params_changed"):

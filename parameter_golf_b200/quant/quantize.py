@@ -177,38 +177,55 @@ def lqer_reconstruct(f: LqerFactors) -> torch.Tensor:
 # ---- ±1 pruning to a byte target ------------------------------------------------------------------------------------
 
 def selective_prune_to_target(qs: Dict[str, torch.Tensor], scales: Dict[str, torch.Tensor], size_fn, target_bytes: int,
-                              max_iters: int = 24) -> Tuple[Dict[str, torch.Tensor], int]:
+                              max_iters: int = 24, max_magnitude: int = 1) -> Tuple[Dict[str, torch.Tensor], int]:
     """Zero the cheapest ``|q| == 1`` entries (ordered by ``scale^2``, the squared error their removal
     adds) until ``size_fn(qs) <= target_bytes``, by bisection on the count
-    (``records/track_10min_16mb/2026-03-25_ValCalib_GPTQ_XSA_BigramHash3072/train_gpt.py:1997-2040``)."""
+    (``records/track_10min_16mb/2026-03-25_ValCalib_GPTQ_XSA_BigramHash3072/train_gpt.py:1997-2040``).
+    ``max_magnitude`` > 1 extends the candidates to ``|q| <= max_magnitude`` (cost ``(q * scale)^2``) when zeroing every
+    +-1 is not enough: a barely trained model has near-uniform codes and few ones. Magnitudes are tried in turn, so a
+    target that +-1 can reach is reached with +-1 only."""
     if size_fn(qs) <= target_bytes:
         return qs, 0
-    cand = []
-    for name, q in qs.items():
-        idx = (q.abs() == 1).nonzero(as_tuple=False)
-        if idx.numel():
-            cost = scales[name].float()[idx[:, 0]].pow(2)
-            cand.append((name, idx, cost))
-    if not cand:
-        return qs, 0
-    costs = torch.cat([c for _, _, c in cand])
-    order = costs.argsort()
-    owners = torch.cat([torch.full((c.numel(),), i) for i, (_, _, c) in enumerate(cand)])
-    local = torch.cat([torch.arange(c.numel()) for _, _, c in cand])
+    result, used = qs, 0
+    for mag in range(1, max(1, max_magnitude) + 1):
+        cand = []
+        for name, q in qs.items():
+            idx = ((q.abs() <= mag) & (q != 0)).nonzero(as_tuple=False)
+            if idx.numel():
+                qv = q[idx[:, 0], idx[:, 1]].float()
+                cost = (scales[name].float()[idx[:, 0]] * qv).pow(2)
+                cand.append((name, idx, cost))
+        if not cand:
+            continue
+        costs = torch.cat([c for _, _, c in cand])
+        order = costs.argsort()
+        owners = torch.cat([torch.full((c.numel(),), i) for i, (_, _, c) in enumerate(cand)])
+        local = torch.cat([torch.arange(c.numel()) for _, _, c in cand])
 
-    def apply(count: int):
-        out = {k: v.clone() for k, v in qs.items()}
-        sel = order[:count]
-        for i, (name, idx, _) in enumerate(cand):
-            pick = local[sel][owners[sel] == i]
-            if pick.numel():
-                rc = idx[pick]
-                out[name][rc[:, 0], rc[:, 1]] = 0
-        return out
+        def apply(count: int):
+            out = {k: v.clone() for k, v in qs.items()}
+            sel = order[:count]
+            for i, (name, idx, _) in enumerate(cand):
+                pick = local[sel][owners[sel] == i]
+                if pick.numel():
+                    rc = idx[pick]
+                    out[name][rc[:, 0], rc[:, 1]] = 0
+            return out
 
-    lo, hi = 0, costs.numel()
-    if size_fn(apply(hi)) > target_bytes:
+        lo, hi = 0, costs.numel()
+        result, used = apply(hi), hi
+        if size_fn(result) > target_bytes:
+            continue                                  # not enough at this magnitude: widen the candidate set
+        for _ in range(max_iters):
+            if hi - lo <= max(1, costs.numel() // 512):
+                break
+            mid = (lo + hi) // 2
+            if size_fn(apply(mid)) <= target_bytes:
+                hi = mid
+            else:
+                lo = mid
         return apply(hi), hi
+    return result, used
     for _ in range(max_iters):
         if hi - lo <= max(1, costs.numel() // 512):
             break

@@ -224,6 +224,7 @@ class QuantSpec:
     code_storage: str = "bit_packed"    # bit_packed: codes packed LSB-first at their bit width (the Rust engine's artifact);
                                         # bytes: one int8 per code (the Python records' container: the entropy coder then sees the code distribution)
     prune_to_target: bool = True        # zero the cheapest +-1 codes until artifact + code fit target_artifact_bytes
+    prune_max_magnitude: int = 1        # widen the candidates to |code| <= this when the +-1 codes are not enough
     matrix_bits: int = 6
     embed_bits: int = 8
     attn_gate_bits: int = 8

@@ -51,9 +51,17 @@ def main(argv=None) -> int:
     if a.max_tokens is not None:
         spec.eval.max_tokens = a.max_tokens
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if a.device == "cuda":                        # one process per GPU: each rank evaluates on its own device
+        import torch
+        a.device = f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}"
+        torch.cuda.set_device(a.device)
     if world > 1:
+        import torch
         import torch.distributed as dist
-        dist.init_process_group("gloo" if a.device == "cpu" else "nccl")
+        if a.device == "cpu":
+            dist.init_process_group("gloo")
+        else:
+            dist.init_process_group("nccl", device_id=torch.device(a.device))
     if a.leaderboard:
         bad = leaderboard_violations(spec, a)
         if bad:

@@ -524,6 +524,7 @@ def family_preset(family: str) -> RunSpec:
         t.batch_tokens, t.seq_len = 786_432, 2048
         s.quant.scheme = "full_gptq_int6"
         s.quant.calibration = "self_generated"
+        s.quant.code_storage, s.quant.prune_max_magnitude = "bytes", 3      # the Python records' container and prune-to-budget step
         s.eval.legal_score_first = True
         s.eval.adaptation_backend = "full_sgd"
     else:

@@ -91,16 +91,20 @@ def markov_row_maps(vocab: int, seed: int):
     return mul, add
 
 
-def generate_markov_tokens(n: int, vocab: int = 1024, seed: int = 0, s: float = 1.1, streams: int = 4096) -> np.ndarray:
+def generate_markov_tokens(n: int, vocab: int = 1024, seed: int = 0, s: float = 1.1, streams: int = 4096,
+                           chain_seed: Optional[int] = None) -> np.ndarray:
     """``n`` ids from a seeded order-1 Markov chain whose transition rows are Zipf(``s``) over ``vocab``
     ids. ``streams`` independent chains are advanced in lock-step (vectorised) and laid out
-    back to back, so the result is a function of ``(n, vocab, seed, s, streams)`` only."""
+    back to back, so the result is a function of ``(n, vocab, seed, s, streams, chain_seed)`` only.
+    ``chain_seed`` fixes the transition structure (which id each rank of a row maps to) separately from the sampling
+    ``seed``: shards of one dataset share the chain and differ in the draws, so a model trained on one shard is
+    evaluated on the same process."""
     if n <= 0:
         return np.zeros(0, dtype=np.uint16)
     streams = max(1, min(streams, n))
     steps = -(-n // streams)
     cdf = zipf_cdf(vocab, s)
-    mul, add = markov_row_maps(vocab, seed)
+    mul, add = markov_row_maps(vocab, seed if chain_seed is None else chain_seed)
     rng = np.random.default_rng(seed)
     out = np.empty((streams, steps), dtype=np.uint16)
     prev = rng.integers(0, vocab, size=streams, dtype=np.int64)
@@ -120,10 +124,10 @@ def write_synthetic_dataset(root: str, vocab: int = 1024, train_tokens: int = 1 
     for i in range(train_shards):
         p = os.path.join(root, f"{prefix}_train_{i:06d}.bin")
         if not (os.path.exists(p) and os.path.getsize(p) == HEADER_BYTES + 2 * per):
-            write_shard(p, generate_markov_tokens(per, vocab, seed + 17 * i))
+            write_shard(p, generate_markov_tokens(per, vocab, seed + 17 * i, chain_seed=seed))
     p = os.path.join(root, f"{prefix}_val_000000.bin")
     if not (os.path.exists(p) and os.path.getsize(p) == HEADER_BYTES + 2 * val_tokens):
-        write_shard(p, generate_markov_tokens(val_tokens, vocab, seed + 99991))
+        write_shard(p, generate_markov_tokens(val_tokens, vocab, seed + 99991, chain_seed=seed))
     return root
 
 

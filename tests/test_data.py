@@ -1,3 +1,5 @@
+import os
+
 import numpy as np
 import pytest
 
@@ -215,3 +217,22 @@ def test_byte_sidecar_is_filtered_from_tokens_and_drives_the_byte_count(tmp_path
     assert bpb2 == pytest.approx((1.0 / np.log(2.0)) * (ntok / nbytes), rel=1e-6)
     with pytest.raises(ValueError):
         luts.token_bytes(np.array([1]), np.array([2]))
+
+
+def test_synthetic_validation_shard_follows_the_training_chain(tmp_path):
+    """Training and validation shards are different draws from ONE Markov chain: the most likely successor of a token is the
+    same in both (a model fitted to the training shard must be scorable on the validation shard)."""
+    root = str(tmp_path / "d")
+    S.write_synthetic_dataset(root, vocab=64, train_tokens=1 << 18, val_tokens=1 << 17, train_shards=2, seed=5)
+
+    def top_successor(path):
+        t = S.open_shard(path).astype(np.int64)
+        counts = np.zeros((64, 64), dtype=np.int64)
+        np.add.at(counts, (t[:-1], t[1:]), 1)
+        return counts.argmax(1)
+
+    a = top_successor(os.path.join(root, "fineweb_train_000000.bin"))
+    b = top_successor(os.path.join(root, "fineweb_train_000001.bin"))
+    v = top_successor(os.path.join(root, "fineweb_val_000000.bin"))
+    assert (a == v).mean() > 0.9 and (a == b).mean() > 0.9
+    assert not np.array_equal(S.open_shard(os.path.join(root, "fineweb_train_000000.bin"))[:1000], S.open_shard(os.path.join(root, "fineweb_val_000000.bin"))[:1000])

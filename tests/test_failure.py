@@ -192,7 +192,7 @@ def test_wallclock_cap_is_agreed_across_ranks_when_one_clock_runs_ahead(tmp_path
             return time.perf_counter() + (1000.0 if rank == 1 and calls[0] > 9 else 0.0)
         r.clock = clock
         res = r.run('proxy')
-        print('RANK', rank, 'STEPS', res.steps, 'EARLY', res.stopped_early, flush=True)
+        sys.stdout.write(chr(10) + f'RANK {rank} STEPS {res.steps} EARLY {res.stopped_early}' + chr(10)); sys.stdout.flush()      # one write per rank: the two ranks share a pipe
         """ % str(tmp_path), port=29697, timeout=240)
     lines = sorted(l for l in out.stdout.splitlines() if l.startswith("RANK"))
     assert len(lines) == 2, (out.stdout, out.stderr[-2000:])

@@ -123,6 +123,21 @@ __global__ void __launch_bounds__(256) sumsq_kernel(const float* __restrict__ x,
   }
 }
 
+// dst[i] += sum_s part[s * split_stride + i], s ascending: the fixed-order second half of a deterministic split-K product
+// (each partial was written by exactly one CTA with a fixed K order, so the result does not depend on scheduling).
+__global__ void __launch_bounds__(256) sum_splits_add_kernel(const float* __restrict__ part, int splits, long long split_stride,
+                                                             float* __restrict__ dst, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x * 4;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+    float4 acc = *reinterpret_cast<const float4*>(dst + i);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(part + (size_t)s * split_stride + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(dst + i) = acc;
+  }
+}
+
 // hp[4] = base_scale * min(1, max_norm / (sqrt(sumsq) * base_scale + 1e-6));  stats[1] = norm (for logging); stats[0] reset.
 __global__ void clip_factor_kernel(float* __restrict__ stats, float* __restrict__ hp, float base_scale, float max_norm) {
   const float norm = sqrtf(stats[0]) * base_scale;
@@ -260,6 +275,12 @@ void fold_scaled_grad_bf16(const float* G, const void* W, const float* rowscale,
 }
 
 void sumsq(const float* x, long long n, float scale, float* out, cudaStream_t st) { sumsq_kernel<<<ew_grid(n, 4), 256, 0, st>>>(x, n, scale, out); }
+
+void sum_splits_add(const float* part, int splits, long long split_stride, float* dst, long long n, cudaStream_t st) {
+  if ((n % 4) || (split_stride % 4)) throw std::runtime_error("sum_splits_add: sizes must be multiples of 4");
+  if (n == 0 || splits <= 0) return;
+  sum_splits_add_kernel<<<ew_grid(n, 4), 256, 0, st>>>(part, splits, split_stride, dst, n);
+}
 
 void clip_factor(float* stats, float* hp, float base_scale, float max_norm, cudaStream_t st) {
   clip_factor_kernel<<<1, 1, 0, st>>>(stats, hp, base_scale, max_norm);

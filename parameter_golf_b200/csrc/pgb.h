@@ -103,6 +103,7 @@ void fold_scaled_grad(const float* G, const float* W, const float* rowscale, int
 void fold_scaled_grad_bf16(const float* G, const void* W, const float* rowscale, int scale_stride, int scale_mod, float* dW, float* dscale, int rows,
                            int cols, cudaStream_t st);
 void sumsq(const float* x, long long n, float scale, float* out, cudaStream_t st);
+void sum_splits_add(const float* part, int splits, long long split_stride, float* dst, long long n, cudaStream_t st);
 void clip_factor(float* stats, float* hp, float base_scale, float max_norm, cudaStream_t st);
 void muon_momentum(const float* g, float* buf, void* U, float* sumsq_out, const float* hp, int matrices, long long per_matrix, int nesterov,
                    cudaStream_t st);

@@ -128,6 +128,8 @@ class CudaEngine:
         self.layer_flags = None          # set by the sharded optimizer: per-layer weight-ready counters
         self.layer_flag_value = 0
         self.layer_wait_needed = False   # set after a sharded update: the next forward gates each layer with a one-thread wait kernel
+        self.lora = None                 # Q-LoRA adapter {"a": [n, r, d], "b": [n, d, r], "alpha", "trainable"} (test-time training); see `set_lora`
+        self._lora_rank = 0
         self.param_generation = 0        # bumped by every write to the fp32 master parameters
         self.cast_generation = -1        # generation the bf16 compute copies were made from
         if share is not None:            # the shared bf16 copies are already current
@@ -329,6 +331,81 @@ class CudaEngine:
         (``pg-model/src/gpu.rs:637-733``)."""
         self.param_generation += 1
 
+    # ---- weight-gradient products ----------------------------------------------------------------------------------------------
+    def _dw(self, dY: torch.Tensor, X: torch.Tensor, G: torch.Tensor, segs=()):
+        """``G += dY^T X`` (both operands token-major; ``segs`` scatters row ranges of the result into further matrices).
+        Default: one split-K launch whose CTAs add their partial tiles with fp32 `red.add` (order depends on scheduling).
+        With ``train.reproducible_backward`` the reduction over tokens is cut into equal chunks computed as a BATCHED product
+        into a partial buffer (one CTA per partial tile, fixed K order) and summed in ascending chunk order by a second
+        kernel, so two runs give the same bits (the fixed-order fp32 reduction the reference's parity mode relies on,
+        ``parameter-golf-rs/crates/pg-bench/src/bin/parity_step.rs:9-14``)."""
+        if not self.t.reproducible_backward:
+            N.gemm(dY, X, G, False, False, N.EPI_F32_ATOMIC, segs=segs)
+            return
+        T, M, Nn = dY.shape[0], dY.shape[1], X.shape[1]
+        splits = 1
+        for cand in (32, 16, 8, 4, 2):
+            if T % cand == 0 and (T // cand) % 64 == 0:
+                splits = cand
+                break
+        need = splits * M * Nn
+        if getattr(self, "_dw_ws", None) is None or self._dw_ws.numel() < need:
+            self._dw_ws = torch.empty(need, dtype=torch.float32, device=self.dev)
+        ws = self._dw_ws[:need].view(splits, M, Nn)
+        N.gemm(dY.unflatten(0, (splits, T // splits)), X.unflatten(0, (splits, T // splits)), ws, False, False, N.EPI_F32)
+        bounds = [(G, 0)] + [(t_, r_) for r_, t_ in segs if t_ is not None]
+        for i, (dst, start) in enumerate(bounds):            # row range [start, end) of every partial goes to `dst`
+            self.C.sum_splits_add(self._dw_ws, start * Nn, splits, M * Nn, dst)
+
+    # ---- Q-LoRA (test-time training) ---------------------------------------------------------------------------------------
+    def set_lora(self, lora: Optional[dict]):
+        """Attach (or with ``None`` detach) a low-rank adapter on the query projection: ``q += (alpha / r) (h A^T) B^T`` with
+        ``A = lora["a"][layer]`` [r, d] and ``B = lora["b"][layer]`` [d, r] (fp32 masters owned by the caller, re-read on every
+        forward). Counterpart of the reference's GPU Q-LoRA path (``parameter-golf-rs/crates/pg-model/src/gpu.rs:2035-2114``,
+        ``:3312-3513``, LoRA GEMMs ``:3861-3999``): two skinny products through the same tcgen05 GEMM in the forward, four in the
+        backward (dB, the gradient of the rank-r activations, dA, and the adapter's share of the input gradient)."""
+        self.lora = lora
+        if lora is None:
+            return
+        r = int(lora["a"].shape[1])
+        if r % 8 or r > 256:
+            raise ValueError("LoRA rank must be a multiple of 8 and at most 256")
+        if r != self._lora_rank:
+            n, d, dev = self.n, self.d, self.dev
+            L = self.nact if self.train else 1
+            self._lora_rank = r
+            self.lora_a_bf = torch.empty(n, r, d, dtype=BF, device=dev)
+            self.lora_b_bf = torch.empty(n, d, r, dtype=BF, device=dev)
+            self.lora_t = [torch.empty(self.T, r, dtype=BF, device=dev) for _ in range(L)]
+            if self.train:
+                self.lora_dt = torch.empty(self.T, r, dtype=BF, device=dev)
+                self.g_lora_a = torch.zeros(n, r, d, dtype=torch.float32, device=dev)
+                self.g_lora_b = torch.zeros(n, d, r, dtype=torch.float32, device=dev)
+
+    def _lora_refresh(self):
+        self.lora_a_bf.copy_(self.lora["a"])
+        self.lora_b_bf.copy_(self.lora["b"])
+
+    def _lora_fwd(self, l, li):
+        d = self.d
+        s = float(self.lora["alpha"]) / self._lora_rank
+        qv = self.qkv_pre[li][:, :d]
+        N.gemm(self.h[li], self.lora_a_bf[l], self.lora_t[li])                                                   # t = h A^T      [T, r]
+        N.gemm(self.lora_t[li], self.lora_b_bf[l], qv, epi=N.EPI_AXPBY_BF16, alpha=s, beta=1.0, aux=qv)          # q += s t B^T
+
+    def _lora_bwd(self, l, aj):
+        """Adapter gradients of layer l and the adapter's share of d_h (added in place). ``d_qkv_pre[:, :d]`` holds dL/dq_pre."""
+        d = self.d
+        s = float(self.lora["alpha"]) / self._lora_rank
+        dq = self.d_qkv_pre[:, :d]
+        A = N.EPI_F32_ATOMIC
+        if self.lora.get("trainable", False):
+            N.gemm(dq, self.lora_t[aj], self.g_lora_b[l], False, False, A, alpha=s)                             # dB += s dq^T t  [d, r]
+        N.gemm(dq, self.lora_b_bf[l], self.lora_dt, True, False, alpha=s)                                        # d_t = s dq B    [T, r]
+        if self.lora.get("trainable", False):
+            N.gemm(self.lora_dt, self.h[aj], self.g_lora_a[l], False, False, A)                                  # dA += d_t^T h   [r, d]
+        N.gemm(self.lora_dt, self.lora_a_bf[l], self.d_h, True, False, N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.d_h)   # d_h += d_t A
+
     # ---- attention -----------------------------------------------------------------------------------------------------
     def _attn_fwd(self, l, li):
         d, kv, B, S, H, Hkv, hd = self.d, self.kv, self.B, self.S, self.H, self.Hkv, self.hd
@@ -373,6 +450,8 @@ class CudaEngine:
             vi = m.value_embedding.layers.index(l)
             vview = self.qkv_pre[li][:, d + kv:]
             N.gemm(self.ve_e, self.VP[vi], vview, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=vview)
+        if self.lora is not None:
+            self._lora_fwd(l, li)
         C.qk_norm_rope_fwd(self.qkv_pre[li], self.qk_post[li], self.cos, self.sin, p["q_gain"][l], self.H, self.Hkv, self.hd, m.rope_dims, S, self.eps)
         self._attn_fwd(l, li)
         zz = self.y[li]
@@ -402,6 +481,8 @@ class CudaEngine:
         if self.cast_generation != self.param_generation:
             raise RuntimeError(f"stale bf16 weights: parameters are at generation {self.param_generation}, the compute copies at "
                                f"{self.cast_generation}; call cast_weights() after changing parameters")
+        if self.lora is not None:
+            self._lora_refresh()
         if ids is not None:                       # otherwise self.ids / self.tgt were filled by `load_span`
             self.ids.copy_(ids.reshape(-1))
             if targets is not None and targets is not True:
@@ -459,7 +540,7 @@ class CudaEngine:
         n, d, kv, S = self.n, self.d, self.kv, self.S
         A = N.EPI_F32_ATOMIC
         N.gemm(self.logits, self.LM, self.d_h, True, False)                              # d_hf
-        N.gemm(self.logits, self.hf, g["tok_emb"] if m.tie_embeddings else g["lm_head"], False, False, A)
+        self._dw(self.logits, self.hf, g["tok_emb"] if m.tie_embeddings else g["lm_head"])
         C.mix_norm_bwd(self.d_h, None, self.x_last, None, None, None, None, None, None, self.dx, None, None, None, None, False, 1.0, self.eps)
         self.d_x0.zero_()
         xsa_layers = m.xsa_layers()
@@ -471,10 +552,10 @@ class CudaEngine:
                 self._block_fwd(j, *self.block_in[j], recompute=True)
             # ---- MLP
             self.Gd.zero_()
-            N.gemm(self.dx, self.a[aj], self.Gd, False, False, A)
+            self._dw(self.dx, self.a[aj], self.Gd)
             C.fold_scaled_grad_bf16(self.Gd, self.Wd_u[l], p["mlp_scale"][l], 1, d, g["mlp_down_bank"][l], g["mlp_scale"][l])
             N.gemm(self.dx, self.Wd[l], self.d_hu, True, False, N.EPI_MUL_ACTGRAD, slope=self.slope, aux=self.hu[aj])
-            N.gemm(self.d_hu, self.mm[aj], g["mlp_up_bank"][l], False, False, A)
+            self._dw(self.d_hu, self.mm[aj], g["mlp_up_bank"][l])
             N.gemm(self.d_hu, self.Wup[l], self.d_m, True, False)
             if self.parallel:
                 dx_mid, dx_next = self.dx, self.dx_mid      # no norm between x_mid and the MLP: the residual gradient passes through
@@ -486,7 +567,7 @@ class CudaEngine:
             # ---- attention output projection
             zz = self.zz[aj]
             self.Go.zero_()
-            N.gemm(dx_mid, zz, self.Go, False, False, A)
+            self._dw(dx_mid, zz, self.Go)
             C.fold_scaled_grad_bf16(self.Go, self.Wo_u[l], p["attn_scale"][l], 1, d, g["qo_bank"][n + l], g["attn_scale"][l])
             vview = self.qkv_pre[aj][:, d + kv:]
             dv = self.d_qkv_pre[:, d + kv:]
@@ -518,11 +599,13 @@ class CudaEngine:
                 N.gemm(dv, self.VP[vi], self.d_ve_e, True, False)
                 self.d_ve_acc.add_(self.d_ve_e)
             # one weight-gradient product for the packed QKV rows, written to the Q, K and V slots of the gradient banks
-            N.gemm(self.d_qkv_pre, self.h[aj], g["qo_bank"][l], False, False, A, segs=((d, g["kv_bank"][l]), (d + kv, g["kv_bank"][n + l])))
+            self._dw(self.d_qkv_pre, self.h[aj], g["qo_bank"][l], segs=((d, g["kv_bank"][l]), (d + kv, g["kv_bank"][n + l])))
             if d_hx is not None:
                 N.gemm(self.d_qkv_pre, self.Wqkv[l], self.d_h, True, False, N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=d_hx)
             else:
                 N.gemm(self.d_qkv_pre, self.Wqkv[l], self.d_h, True, False)
+            if self.lora is not None:
+                self._lora_bwd(l, aj)
             # ---- block input: RMSNorm backward, residual mix, U-Net skip
             x_prev = self.x_out[j - 1] if j > 0 else self.x0
             skip = sw = d_skip = d_sw = add_grad = None
@@ -551,7 +634,7 @@ class CudaEngine:
         C.embed_scatter_add(self.ids, self.d_xe, g["tok_emb"], 0, S)
         if m.bigram.enabled:
             self.Gbp.zero_()
-            N.gemm(self.d_xe, self.bg, self.Gbp, False, False, A)
+            self._dw(self.d_xe, self.bg, self.Gbp)
             C.fold_scaled_grad(self.Gbp, p["bigram_proj"], p["bigram_scale"], 0, 1, g["bigram_proj"], g["bigram_scale"], False)
             N.gemm(self.d_xe, self.BP, self.d_bg, True, False)
             C.embed_scatter_add(self.ids, self.d_bg, g["bigram_embed"], m.bigram.vocab_size, S)
@@ -562,6 +645,9 @@ class CudaEngine:
 
     # ---- public pieces -----------------------------------------------------------------------------------------------------------
     def zero_grads(self):
+        if self.lora is not None and self.train:
+            self.g_lora_a.zero_()
+            self.g_lora_b.zero_()
         for k in gpt.BANKS:
             self.g[k].zero_()
         for grp in self.groups:
@@ -727,12 +813,14 @@ class EngineRunner:
     @torch.no_grad()
     def nll(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         e = self._engine(ids.shape[0], ids.shape[1])
+        e.set_lora(self.lora)
         e.forward(ids.to(self.device, torch.int32), targets.to(self.device, torch.int32))
         return e.nll.view(ids.shape).clone()
 
     @torch.no_grad()
     def logits(self, ids: torch.Tensor) -> torch.Tensor:
         e = self._engine(ids.shape[0], ids.shape[1])
+        e.set_lora(self.lora)
         e.forward(ids.to(self.device, torch.int32), None)
         z = e.logits.view(*ids.shape, -1).float()
         return self.model.logit_softcap * torch.tanh(z / self.model.logit_softcap)
@@ -743,11 +831,15 @@ class EngineRunner:
         if e.qat != qat:
             e.qat = qat
             e.cast_weights()
+        e.set_lora(self.lora)
         e.zero_grads()
         e.micro_step(ids.to(self.device, torch.int32), targets.to(self.device, torch.int32), 1)
         loss = e.loss_sum[0] / e.T
         names = list(e.g) if names is None else list(names)
-        return loss.clone(), {k: e.g[k] for k in names}
+        grads = {k: e.g[k] for k in names}
+        if self.lora is not None and self.lora.get("trainable", False):
+            grads["lora.a"], grads["lora.b"] = e.g_lora_a, e.g_lora_b
+        return loss.clone(), grads
 
 
 class EngineBackend:

@@ -182,7 +182,11 @@ def schedule_prefix_docs(tokens: np.ndarray, boundary_id: Optional[int], prefix_
 
 
 def eval_lora_phased_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalSpec, luts: BpbLuts, rank: int = 0, world: int = 1,
-                         device="cpu", log: Callable = lambda s: None) -> Tuple[float, float]:
+                         device="cpu", log: Callable = lambda s: None, all_reduce: Optional[Callable] = None) -> Tuple[float, float]:
+    """Phased Q-LoRA test-time training: score a chunk with the adapter as it stands (guarded against mutation), then one
+    pass of SGD with weight decay on the adapter only, its gradients averaged over ranks with one packed collective
+    (``all_reduce``: an in-place mean over ranks, e.g. `PeerAllReduce.mean_`; default the process group); B is reset at every
+    phase change. Runs on any runner, the CUDA engine included (``parameter-golf-rs/crates/pg-eval/src/gpu_lora_ttt.rs:258-568``)."""
     window, stride = model.eval_seq_len, ev.stride
     total = tokens.shape[0] - 1
     chunks = build_ttt_chunks(total, window, stride, ev.chunk_tokens)
@@ -220,7 +224,7 @@ def eval_lora_phased_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalS
                 _, g = runner.loss_and_grads(x, y, names=[])
             else:
                 g = {"lora.a": torch.zeros_like(runner.lora["a"]), "lora.b": torch.zeros_like(runner.lora["b"])}
-            packed_all_reduce_mean(g, ["lora.a", "lora.b"])
+            packed_all_reduce_mean(g, ["lora.a", "lora.b"], all_reduce)
             with torch.no_grad():
                 for key, gk in (("a", "lora.a"), ("b", "lora.b")):
                     if ev.phased_ttt_weight_decay > 0:

@@ -105,7 +105,11 @@ def main(argv=None) -> int:
         loss, bpb = eval_score_first_ttt(runner, val, m, spec.eval, luts, rank, world, mode, a.device, print, all_reduce=hook)
         kind = f"score_first_{mode}"
     elif spec.eval.legal_score_first and ab == "gpu_lora_phased":
-        loss, bpb = eval_lora_phased_ttt(runner, val, m, spec.eval, luts, rank, world, a.device, print)
+        hook = None
+        if world > 1 and a.device != "cpu":       # packed adapter-gradient all-reduce on the peer-memory kernels
+            from .parallel.peer_allreduce import PeerAllReduce
+            hook = PeerAllReduce(2 * m.num_layers * m.model_dim * spec.eval.lora_rank + 64).mean_
+        loss, bpb = eval_lora_phased_ttt(runner, val, m, spec.eval, luts, rank, world, a.device, print, all_reduce=hook)
         kind = "lora_phased"
     else:
         loss, bpb = eval_sliding(runner.nll, val, m.eval_seq_len, spec.eval.stride, luts, rank, world, spec.eval.batch_windows, a.device)

@@ -530,3 +530,28 @@ def test_reproducible_backward_gives_bit_identical_bank_gradients():
     ref_loss, ref = oracle_grads(spec, params, ids, tgt)         # and they are the right gradients
     for k in gpt.BANKS:
         assert rel_err(grads[0][k], ref[k]) < 0.03, k
+
+
+def test_lora_phased_ttt_on_the_engine_tracks_the_oracle():
+    """The whole phased Q-LoRA evaluation loop (score, guard, adapter gradients, SGD with weight decay, phase reset) on the
+    CUDA engine and on the autograd model from the same start: the scores agree and the base weights are untouched."""
+    import numpy as np
+    from parameter_golf_b200.data.bpb import BpbLuts
+    from parameter_golf_b200.eval import ttt as T
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import EngineRunner
+    from parameter_golf_b200.models.runner import OracleRunner
+    spec = small_spec()
+    m, ev = spec.model, spec.eval
+    ev.stride, ev.chunk_tokens, ev.lora_rank, ev.lora_alpha, ev.phased_ttt_phases = 64, 4 * 128, 16, 16.0, 2
+    ev.ttt_lr, ev.ttt_batch_seqs, ev.batch_windows, ev.phased_ttt_weight_decay, ev.max_eval_seconds = 0.05, 4, 4, 0.01, 0.0
+    params = gpt.init_params(m, 7)
+    toks = np.random.default_rng(2).integers(0, 256, 128 * 12 + 1).astype(np.uint16)
+    luts = BpbLuts.seeded(256)
+    ref = T.eval_lora_phased_ttt(OracleRunner(m, {k: v.clone() for k, v in params.items()}), toks, m, ev, luts)
+    runner = EngineRunner(spec, params, "cuda", batch=4)
+    got = T.eval_lora_phased_ttt(runner, toks, m, ev, luts, device="cuda")
+    assert abs(got[0] - ref[0]) < 2e-2 and abs(got[1] - ref[1]) < 2e-2, (got, ref)
+    for k, v in params.items():
+        assert torch.allclose(runner.params[k].cpu(), v), k
+    assert runner.lora is None

@@ -42,6 +42,9 @@ BF = torch.bfloat16
 EMB_NAMES = ("tok_emb", "bigram_embed", "ve_embed")
 
 
+CANARY_BYTE = 0xA5
+
+
 def _unsupported(m: ModelSpec) -> Optional[str]:
     if m.model_dim % 64 or m.kv_dim % 64 or m.mlp_dim % 64 or m.head_dim % 8 or m.vocab_size % 64:
         return "dims that are not multiples of 64"
@@ -233,10 +236,26 @@ class CudaEngine:
         dev, T, d, n = self.dev, self.T, self.d, self.n
 
         poison = os.environ.get("PGB_POISON", "0") not in ("", "0")
+        canary = os.environ.get("PGB_CANARY", "0") not in ("", "0")
+        self._canaries: List[Tuple[str, torch.Tensor]] = []
 
         def buf(*shape, dtype=BF):
-            # debug aid: activations start as NaN, so a kernel that reads a buffer before its producer ran shows up as a
-            # NaN loss instead of silently using stale data (role of the reference's poison fill, pg-model/src/gpu.rs:637-733)
+            # debug aids. PGB_POISON: activations start as NaN, so a kernel that reads a buffer before its producer ran shows up
+            # as a NaN loss instead of silently using stale data (role of the reference's poison fill, pg-model/src/gpu.rs:637-733).
+            # PGB_CANARY: every buffer sits between two 512-byte guard zones filled with a byte pattern; `check_canaries` finds
+            # the kernel output that ran past its end (the stand-in for a memory checker, which this pool does not offer).
+            if canary:
+                n = 1
+                for x in shape:
+                    n *= int(x)
+                esz = torch.empty(0, dtype=dtype).element_size()
+                nbytes = -(-n * esz // 512) * 512
+                raw = torch.full((nbytes + 1024,), CANARY_BYTE, dtype=torch.uint8, device=dev)
+                body = raw[512:512 + n * esz].view(dtype).view(*shape)
+                if poison and dtype in (BF, torch.float32):
+                    body.fill_(float("nan"))
+                self._canaries.append((f"buffer {len(self._canaries)} {tuple(shape)} {dtype}", raw, n * esz))
+                return body
             if poison and dtype in (BF, torch.float32):
                 return torch.full(shape, float("nan"), dtype=dtype, device=dev)
             return torch.empty(*shape, dtype=dtype, device=dev)
@@ -291,6 +310,15 @@ class CudaEngine:
             self.d_xe = buf(T, d)
             if m.bigram.enabled:
                 self.d_bg = buf(T, m.bigram.dim)
+
+    def check_canaries(self):
+        """With ``PGB_CANARY=1``: raise if any byte of a guard zone around an activation / scratch buffer was overwritten."""
+        torch.cuda.synchronize(self.dev)
+        for name, raw, used in getattr(self, "_canaries", []):
+            head, tail = raw[:512], raw[512 + used:]
+            if not (bool((head == CANARY_BYTE).all()) and bool((tail == CANARY_BYTE).all())):
+                where = "before" if not bool((head == CANARY_BYTE).all()) else "after"
+                raise RuntimeError(f"guard zone {where} {name} was overwritten")
 
     # ---- weights --------------------------------------------------------------------------------------------------
     def cast_weights(self, banks: bool = True):

@@ -555,3 +555,22 @@ def test_lora_phased_ttt_on_the_engine_tracks_the_oracle():
     for k, v in params.items():
         assert torch.allclose(runner.params[k].cpu(), v), k
     assert runner.lora is None
+
+
+def test_guard_zones_around_buffers_stay_intact_and_detect_an_overrun(monkeypatch):
+    """`PGB_CANARY=1` places every activation and scratch buffer between guard zones: a full training micro-step (all
+    kernels, odd and even tails) leaves them intact, and a byte written one past a buffer's end is reported."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine
+    monkeypatch.setenv("PGB_CANARY", "1")
+    spec = small_spec()
+    eng = CudaEngine(spec, gpt.fill_deterministic(spec.model), "cuda", 3, 128)
+    ids = torch.randint(0, 256, (3, 128))
+    eng.zero_grads()
+    eng.micro_step(ids.cuda().int(), ids.cuda().int(), 1)
+    eng.check_canaries()
+    assert len(eng._canaries) > 20
+    name, raw, used = eng._canaries[5]
+    raw[512 + used] = 0                                   # host-side store one byte past the end of the buffer
+    with pytest.raises(RuntimeError, match="guard zone after"):
+        eng.check_canaries()

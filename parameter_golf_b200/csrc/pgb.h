@@ -71,9 +71,10 @@ void head_gate_fwd(const void* y, const void* x, const float* W, const float* bi
                    float scale, float mult, cudaStream_t st);
 void head_gate_bwd(void* d_out, const void* y, const void* x, const float* W, const float* gate, float* dW, float* dbias, void* d_x, int accumulate_dx,
                    int rows, int H, int hd, int w, int ld_x, int ld_dx, float scale, float mult, cudaStream_t st);
-// tok_w / w_total (both or neither): per-row loss weights and their sum, as written by `pair_weights`
+// tok_w / w_total (both or neither): per-row loss weights and their sum, as written by `pair_weights`; norm_rows: the number
+// of rows the sum covers when this call sees only a chunk of them (0: the same `rows`)
 void softcap_ce(const void* logits, const int* targets, float* nll, void* dlogits, float* loss_sum, int rows, int V, float cap, float gscale,
-                cudaStream_t st, const float* tok_w = nullptr, const float* w_total = nullptr);
+                cudaStream_t st, const float* tok_w = nullptr, const float* w_total = nullptr, int norm_rows = 0);
 // w[i] = table[prev[i] * V + curr[i]], *w_total = sum_i w[i] (zeroed here first)
 void pair_weights(const int* prev, const int* curr, const float* table, float* w, float* w_total, int rows, int V, cudaStream_t st);
 void embed_gather(const int* ids, const void* table, void* out, int rows, int d, int bigram_buckets, int seq_len, cudaStream_t st);

@@ -573,13 +573,14 @@ __device__ __forceinline__ float tanh_fast(float x) {
 __global__ void __launch_bounds__(ROW_THREADS) softcap_ce_kernel(const __nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
                                                                  float* __restrict__ nll, __nv_bfloat16* __restrict__ dlogits,
                                                                  float* __restrict__ loss_sum, int rows, int V, float cap, float gscale,
-                                                                 const float* __restrict__ tok_w, const float* __restrict__ w_total) {
+                                                                 const float* __restrict__ tok_w, const float* __restrict__ w_total, int norm_rows) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   __shared__ float wsum[ROW_WARPS];
   float local = 0.f;
   // Per-token loss weights (complementary training): the loss becomes sum(w l) / sum(w). `loss_sum` and the gradient
-  // are rescaled by rows / sum(w) so that callers keep dividing by the row count.
-  const float wnorm = (tok_w && w_total) ? (float)rows / fmaxf(*w_total, 1e-12f) : 1.f;
+  // are rescaled by norm_rows / sum(w) so that callers keep dividing by the row count; `norm_rows` is the number of rows
+  // the weights were summed over (more than `rows` when the batch is processed in chunks of rows).
+  const float wnorm = (tok_w && w_total) ? (float)norm_rows / fmaxf(*w_total, 1e-12f) : 1.f;
   for (int row = blockIdx.x * ROW_WARPS + warp; row < rows; row += gridDim.x * ROW_WARPS) {
     const __nv_bfloat16* z = logits + (size_t)row * V;
     const int tgt = targets[row];
@@ -656,10 +657,10 @@ __global__ void __launch_bounds__(ROW_THREADS) softcap_ce_kernel(const __nv_bflo
 __global__ void __launch_bounds__(256) softcap_ce_wide_kernel(const __nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
                                                               float* __restrict__ nll, __nv_bfloat16* __restrict__ dlogits,
                                                               float* __restrict__ loss_sum, int rows, int V, float cap, float gscale,
-                                                              const float* __restrict__ tok_w, const float* __restrict__ w_total) {
+                                                              const float* __restrict__ tok_w, const float* __restrict__ w_total, int norm_rows) {
   __shared__ float s_mx[8], s_se[8], s_ct[8], s_bcast[2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const float wnorm = (tok_w && w_total) ? (float)rows / fmaxf(*w_total, 1e-12f) : 1.f;
+  const float wnorm = (tok_w && w_total) ? (float)norm_rows / fmaxf(*w_total, 1e-12f) : 1.f;
   const float inv_cap = 1.f / cap;
   float local = 0.f;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -930,18 +931,19 @@ void xsa_bwd(const void* dz, const void* y, const void* v, void* dy, void* dv, i
 }
 
 void softcap_ce(const void* logits, const int* targets, float* nll, void* dlogits, float* loss_sum, int rows, int V, float cap, float gscale,
-                cudaStream_t st, const float* tok_w, const float* w_total) {
+                cudaStream_t st, const float* tok_w, const float* w_total, int norm_rows) {
   if (V % 8) throw std::runtime_error("vocab must be a multiple of 8 for the fused CE kernel");
+  if (norm_rows <= 0) norm_rows = rows;
   if (V > 2048) {             // the row no longer fits the registers of one warp: one CTA per row, two passes
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     softcap_ce_wide_kernel<<<std::max(1, std::min(rows, sms * 8)), 256, 0, st>>>((const __nv_bfloat16*)logits, targets, nll, (__nv_bfloat16*)dlogits,
-                                                                                 loss_sum, rows, V, cap, gscale, tok_w, w_total);
+                                                                                 loss_sum, rows, V, cap, gscale, tok_w, w_total, norm_rows);
     return;
   }
   softcap_ce_kernel<<<row_grid(rows), ROW_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets, nll, (__nv_bfloat16*)dlogits, loss_sum, rows, V,
-                                                            cap, gscale, tok_w, w_total);
+                                                            cap, gscale, tok_w, w_total, norm_rows);
 }
 
 void pair_weights(const int* prev, const int* curr, const float* table, float* w, float* w_total, int rows, int V, cudaStream_t st) {

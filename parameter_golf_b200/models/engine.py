@@ -288,7 +288,11 @@ class CudaEngine:
         self.x_out = [buf(T, d) for _ in range(self.nslots)]
         self.lse = [None] * L
         self.hf = buf(T, d)
-        self.logits = buf(T, m.vocab_size)
+        from ..plan import logit_chunk_rows
+        self.logit_rows = logit_chunk_rows(T, m.vocab_size, self.t.logit_chunk_rows)      # < T: the head runs per chunk of rows
+        self.logits = buf(self.logit_rows, m.vocab_size)
+        self._logits_full = None                   # only for callers that ask for every logit (`forward(targets=None)`) while chunking
+        self._head_grads_done = False
         self.nll = buf(T, dtype=torch.float32)
         rd = m.rope_dims
         if rd > 0:
@@ -538,14 +542,36 @@ class CudaEngine:
                 skips.append(x)
         self.x_last = x
         C.mix_norm_fwd(x, None, None, None, None, None, self.hf, 1.0, self.eps)
-        N.gemm(self.hf, self.LM, self.logits)
-        if targets is not None:
-            if self.pair_w_table is not None and want_grad:
-                # complementary training: the loss of this micro-batch is sum(w l) / sum(w), w looked up per (input, target) pair
-                C.pair_weights(self.ids, self.tgt, self.pair_w_table, self.tok_w, self.w_total)
-                C.softcap_ce(self.logits, self.tgt, self.nll, self.logits, self.loss_sum, m.logit_softcap, gscale, self.tok_w, self.w_total)
-            else:
-                C.softcap_ce(self.logits, self.tgt, self.nll, self.logits if want_grad else None, self.loss_sum, m.logit_softcap, gscale)
+        weighted = targets is not None and self.pair_w_table is not None and want_grad
+        if weighted:
+            # complementary training: the loss of this micro-batch is sum(w l) / sum(w), w looked up per (input, target) pair
+            C.pair_weights(self.ids, self.tgt, self.pair_w_table, self.tok_w, self.w_total)
+        self._head_grads_done = False
+        R, T = self.logit_rows, self.T
+        if R >= T or targets is None:
+            logits = self.logits
+            if R < T:                              # every logit was asked for: a full buffer, allocated on first use
+                if self._logits_full is None:
+                    self._logits_full = torch.empty(T, m.vocab_size, dtype=BF, device=self.dev)
+                logits = self._logits_full
+            N.gemm(self.hf, self.LM, logits)
+            if targets is not None:
+                C.softcap_ce(logits, self.tgt, self.nll, logits if want_grad else None, self.loss_sum, m.logit_softcap, gscale,
+                             self.tok_w if weighted else None, self.w_total if weighted else None)
+            return
+        # Chunked head: projection, cross-entropy and (when training) the two products that consume the logits gradient, one
+        # chunk of rows at a time; the [T, V] logits never exist. The backward pass then starts at the final norm.
+        gW = (self.g["tok_emb"] if m.tie_embeddings else self.g["lm_head"]) if want_grad else None
+        for r0 in range(0, T, R):
+            r1 = min(r0 + R, T)
+            lg = self.logits[:r1 - r0]
+            N.gemm(self.hf[r0:r1], self.LM, lg)
+            C.softcap_ce(lg, self.tgt[r0:r1], self.nll[r0:r1], lg if want_grad else None, self.loss_sum, m.logit_softcap, gscale,
+                         self.tok_w[r0:r1] if weighted else None, self.w_total if weighted else None, T)
+            if want_grad:
+                N.gemm(lg, self.LM, self.d_h[r0:r1], True, False)          # d_hf rows
+                self._dw(lg, self.hf[r0:r1], gW)
+        self._head_grads_done = want_grad
 
     def set_token_weight_table(self, table) -> None:
         """Install (or with ``None`` remove) the ``[V, V]`` fp32 table of training-loss weights per (previous token, target)
@@ -567,8 +593,9 @@ class CudaEngine:
         C, m, p, g = self.C, self.m, self.p, self.g
         n, d, kv, S = self.n, self.d, self.kv, self.S
         A = N.EPI_F32_ATOMIC
-        N.gemm(self.logits, self.LM, self.d_h, True, False)                              # d_hf
-        self._dw(self.logits, self.hf, g["tok_emb"] if m.tie_embeddings else g["lm_head"])
+        if not self._head_grads_done:              # the chunked head has already produced d_hf and the output-embedding gradient
+            N.gemm(self.logits, self.LM, self.d_h, True, False)                              # d_hf
+            self._dw(self.logits, self.hf, g["tok_emb"] if m.tie_embeddings else g["lm_head"])
         C.mix_norm_bwd(self.d_h, None, self.x_last, None, None, None, None, None, None, self.dx, None, None, None, None, False, 1.0, self.eps)
         self.d_x0.zero_()
         xsa_layers = m.xsa_layers()
@@ -850,7 +877,7 @@ class EngineRunner:
         e = self._engine(ids.shape[0], ids.shape[1])
         e.set_lora(self.lora)
         e.forward(ids.to(self.device, torch.int32), None)
-        z = e.logits.view(*ids.shape, -1).float()
+        z = (e.logits if e.logit_rows >= e.T else e._logits_full).view(*ids.shape, -1).float()
         return self.model.logit_softcap * torch.tanh(z / self.model.logit_softcap)
 
     @torch.no_grad()

@@ -147,6 +147,20 @@ def saved_slots(sched, mode: str) -> List[bool]:
     raise ValueError(f"unknown save_layer_acts mode {mode!r}")
 
 
+
+def logit_chunk_rows(T: int, V: int, override: int = 0) -> int:
+    """Rows of the output projection the CUDA engine materialises at a time. The full ``[T, V]`` logits are kept when they are
+    small (vocabulary 1024: 201 MB per micro-batch); above 2^27 elements (vocabulary 8192 at 98,304 tokens: 1.6 GB) the
+    projection, the cross-entropy and the two products that consume its gradient run per chunk of rows, so only
+    ``[rows, V]`` ever exists (the reference reaches the same end with a vocabulary-tiled online log-sum-exp,
+    ``parameter-golf-rs/crates/pg-kernels/src/gpu_kernels.rs:4241-4386``). ``override`` > 0 forces a chunk size."""
+    if override > 0:
+        return min(T, max(128, override // 128 * 128))
+    if T * V <= (1 << 27):
+        return T
+    return min(T, max(128, ((1 << 26) // V) // 128 * 128))
+
+
 def estimate_engine_memory(spec: RunSpec, micro_batch_tokens: int, train: bool = True) -> MemoryEstimate:
     """Bytes of the buffers `CudaEngine` allocates for one micro-batch of ``micro_batch_tokens`` tokens."""
     m, t = spec.model, spec.train
@@ -190,7 +204,7 @@ def estimate_engine_memory(spec: RunSpec, micro_batch_tokens: int, train: bool =
         act += 2 * T * m.value_embedding.dim
     act += 8 * T                                                  # ids, targets
     est.activations = act
-    est.logits = 2 * T * V + 4 * T
+    est.logits = 2 * logit_chunk_rows(T, V, t.logit_chunk_rows) * V + 4 * T
     if train:
         est.grads_fp32 = 4 * nparam
         est.optimizer_state = 4 * bank_elems + 2 * 4 * (nparam - bank_elems)          # Muon momentum; AdamW m and v

@@ -190,6 +190,7 @@ class TrainSpec:
     cuda_graph: bool = False            # replay the micro-batch forward+backward from a captured CUDA graph
     reproducible_backward: bool = False # CUDA engine: bit-reproducible gradient kernels (two-kernel attention backward) instead of the faster fp32 red.add forms
     save_layer_acts: str = "all"        # CUDA engine activation checkpointing: all | edges | inner | recurrent | none
+    logit_chunk_rows: int = 0           # CUDA engine: rows of logits materialised at a time (0 = automatic: everything unless [T, V] exceeds 2^27 elements)
     checkpoint_every: int = 0
     checkpoint_path: Optional[str] = None
     resume_from: Optional[str] = None

@@ -574,3 +574,38 @@ def test_guard_zones_around_buffers_stay_intact_and_detect_an_overrun(monkeypatc
     raw[512 + used] = 0                                   # host-side store one byte past the end of the buffer
     with pytest.raises(RuntimeError, match="guard zone after"):
         eng.check_canaries()
+
+
+@pytest.mark.parametrize("weighted", [False, True])
+def test_chunked_output_head_matches_the_full_logits_path(weighted):
+    """`train.logit_chunk_rows` makes the output projection, the cross-entropy and the two products that consume the logits
+    gradient run per chunk of rows (the automatic setting for 8192-token vocabularies, where [T, V] would be gigabytes): loss,
+    per-token NLL and every gradient must match the path that keeps all logits, with and without per-token loss weights."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import CudaEngine, EngineRunner
+    from parameter_golf_b200.ops import native
+    torch.manual_seed(1)
+    ids = torch.randint(0, 256, (4, 128))
+    tgt = torch.randint(0, 256, (4, 128))
+    table = (torch.rand(256, 256) + 0.5) if weighted else None
+    out = {}
+    for rows in (0, 128):
+        spec = small_spec(**{"train.logit_chunk_rows": rows})
+        params = gpt.fill_deterministic(spec.model)
+        eng = CudaEngine(spec, params, "cuda", 4, 128)
+        assert eng.logit_rows == (512 if rows == 0 else 128) and eng.logits.shape[0] == eng.logit_rows
+        if weighted:
+            eng.set_token_weight_table(table)
+        eng.zero_grads()
+        eng.micro_step(ids.cuda().int(), tgt.cuda().int(), 1)
+        torch.cuda.synchronize()
+        native.check_status()
+        out[rows] = (float(eng.loss_sum[0]), eng.nll.clone(), {k: v.clone() for k, v in eng.g.items()})
+    assert out[128][0] == pytest.approx(out[0][0], rel=1e-5)
+    assert torch.allclose(out[128][1], out[0][1], atol=1e-5)
+    for k, g in out[0][2].items():
+        assert rel_err(out[128][2][k], g) < 1e-3, k               # same products, summed in a different order
+    spec = small_spec(**{"train.logit_chunk_rows": 128})
+    r = EngineRunner(spec, gpt.fill_deterministic(spec.model), "cuda", batch=4, train=False)
+    full = EngineRunner(small_spec(), gpt.fill_deterministic(spec.model), "cuda", batch=4, train=False)
+    assert torch.allclose(r.logits(ids), full.logits(ids), atol=1e-3) and torch.allclose(r.nll(ids, tgt), full.nll(ids, tgt), atol=1e-5)

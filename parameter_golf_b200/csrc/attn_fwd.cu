@@ -1,13 +1,12 @@
 // Causal GQA flash-attention forward for sm_100a (head_dim 64): TMA -> smem, QK^T and PV on tcgen05 with
 // S/P/O in tensor memory, online softmax by one thread per query row.
 //
-// One CTA handles one 128-row query tile of TWO query heads that share a KV head, so every K/V tile is
-// loaded once and used by both. Warp roles (384 threads = three warpgroups): warpgroup 0 holds the TMA producer
-// (warp 0) and one MMA-issuing warp per head (warps 1, 2); warpgroups 1 and 2 are the softmax groups of head 0 and
-// head 1, one thread per query row. Warpgroup 0 gives up most of its registers (`setmaxnreg`) so that a softmax
-// thread can hold its 128 scores and still leave the scheduler room to overlap MUFU, FMA and conversion latencies.
-//   TMEM: S0 [0,128) S1 [128,256) fp32 scores; P0 [256,320) P1 [320,384) bf16 probabilities (fed to the PV MMA straight
-//         from tensor memory); O0 [384,448) O1 [448,512).
+// A persistent kernel, two CTAs per SM. A CTA owns one softmax group (128 threads, one per query row of a 128-row tile) and
+// draws (batch, head, query tile) work items from a device-wide counter, heavy tiles first. Its other warpgroup holds the
+// single-thread roles: a TMA producer, a thread that issues the score products and a thread that issues the PV products;
+// it gives up most of its registers (`setmaxnreg`) so that a softmax thread can hold its 128 scores.
+//   TMEM (256 columns per CTA): S [0,128) fp32 scores; P [128,192) bf16 probabilities (fed to the PV MMA straight from
+//   tensor memory); O [192,256).
 // P has its own columns so that the scores of tile j+1 can be issued as soon as the softmax group has pulled tile j
 // into registers (`s_free`), long before P(j) exists: the MMA round trip is off the softmax group's critical path.
 // The running maximum is updated lazily: probabilities are taken relative to a stale maximum and O is
@@ -17,28 +16,26 @@
 // (pg-kernels/src/gpu_kernels.rs:4751-4843).
 #include "common.cuh"
 #include "pgb.h"
+#include <algorithm>
 #include <cstdlib>
 
 #include "tma_host.h"
 
 namespace pgb {
 
-constexpr int AT_THREADS = 384;   // warpgroup 0: warp 0 TMA, warps 1 and 2 issue the MMAs of head 0 / head 1, warp 3 idle; warpgroups 1, 2: softmax
 constexpr int AT_BM = 128;   // query rows per tile
 constexpr int AT_BN = 128;   // keys per tile
 constexpr int AT_HD = 64;
-constexpr int AT_STAGES = 4;
 constexpr int AT_TILE_BYTES = 128 * AT_HD * 2;   // 16 KB: one Q, K or V tile
-constexpr int AT_SMEM = (2 + 2 * AT_STAGES) * AT_TILE_BYTES + 1024 + 256;
 
 struct AttnFwdParams {
-  int B, S, H, Hkv, n_qt, pairs;     // pairs = ceil(group / 2)
+  int B, S, H, Hkv, n_qt;
   float scale_log2;
-  int head1_delay_clk;               // head start of head 0's softmax group over head 1's, in SM clocks
   __nv_bfloat16* Y;
   long long ldy;
   float* lse;
   int* status;
+  unsigned* sched;                   // {next work item, CTAs finished}: both zero between launches
 };
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
@@ -59,56 +56,90 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// Between work items nothing is torn down: the producer is already fetching the next item's Q/K/V while the last tiles of
+// the current one are in flight, the next item's first score product is issued as soon as the last scores of this item have
+// been pulled into registers, and an item's output is read out of tensor memory and stored while the next item's first tile
+// is being processed, when its last PV product has long completed. Work items are drawn from a counter because the two CTAs
+// of an SM do not run at the same speed. K and V tiles are fetched once per head (not once per KV head); the heads of a KV
+// group are neighbours in the item order, so the repeated fetches hit L2.
+//   warps 0-3: TMA producer (warp 0), score-product issuer (warp 1), PV issuer (warp 2), one idle; warps 4-7: softmax, one
+//   thread per query row.
+//   TMEM (256 columns): S [0,128) fp32 scores, P [128,192) bf16 probabilities, O [192,256).
+//   Shared memory: 2 Q tiles (this item's and the next one's), a ring of 2 K tiles (a K tile is free once its score product
+//   has completed) and a ring of 2 V tiles.
+constexpr int A1_THREADS = 256;
+constexpr int A1_KST = 2, A1_VST = 2;
+constexpr int A1_SMEM = (2 + A1_KST + A1_VST) * AT_TILE_BYTES + 1024 + 256;
+// Register budget: 2 CTAs x 256 threads => 128 registers per thread at launch. `setmaxnreg.inc` can only take what the
+// role warps released; a request for more never completes, so the two sides must balance exactly.
+constexpr int A1_REG_LAUNCH = 128, A1_REG_ROLE = 40, A1_REG_SOFTMAX = 216;
+static_assert(128 * A1_REG_ROLE + 128 * A1_REG_SOFTMAX == A1_THREADS * A1_REG_LAUNCH, "setmaxnreg: released and requested registers must balance");
+static_assert(2 * (A1_SMEM + 1024) <= 227 * 1024, "two CTAs must fit the shared memory of one SM");
+
+struct FwdItem {
+  int qt, b, head, kvh, n_kv, row0;
+};
+__device__ __forceinline__ FwdItem fwd_item(const AttnFwdParams& p, int item) {
+  FwdItem w;
+  const int per_qt = p.B * p.H;
+  w.qt = p.n_qt - 1 - item / per_qt;         // heavy (long KV range) query tiles first
+  const int rem = item % per_qt;
+  w.b = rem / p.H;
+  w.head = rem % p.H;                        // the heads of a KV group are neighbours, so their K/V fetches share L2 lines
+  w.kvh = w.head / (p.H / p.Hkv);
+  w.n_kv = w.qt + 1;
+  w.row0 = w.b * p.S + w.qt * AT_BM;
+  return w;
+}
+
+// Work counters of the persistent kernel, one pair per launch in flight: consecutive launches rotate through the slots, and the
+// last CTA of a launch zeroes its pair again. Launches that run concurrently on one device must therefore be fewer than the
+// number of slots apart in issue order (the engine issues all attention calls on one stream).
+constexpr int A1_SCHED_SLOTS = 64;
+__device__ unsigned g_fwd_sched[A1_SCHED_SLOTS * 2];
+
+__global__ void __launch_bounds__(A1_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                const AttnFwdParams p) {
+                 const AttnFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;                                   // 2 tiles
-  uint8_t* sKV = smem + 2 * AT_TILE_BYTES;              // stages of {K, V}
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * AT_STAGES) * AT_TILE_BYTES);
-  uint64_t* q_full = bars;                 // 1
-  uint64_t* kv_full = bars + 1;            // STAGES
-  uint64_t* kv_empty = kv_full + AT_STAGES;
-  uint64_t* s_full = kv_empty + AT_STAGES; // 2
-  uint64_t* p_full = s_full + 2;           // 2
-  uint64_t* o_full = p_full + 2;           // 2: one commit per PV
-  uint64_t* s_free = o_full + 2;           // 2: scores pulled into registers
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
+  uint8_t* sQ = smem;                      // two tiles: the next item's Q lands while this item's score products still read theirs
+  uint8_t* sK = smem + 2 * AT_TILE_BYTES;
+  uint8_t* sV = sK + A1_KST * AT_TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + A1_VST * AT_TILE_BYTES);
+  uint64_t* q_full = bars;                 // 2: Q of the item has landed
+  uint64_t* q_empty = bars + 2;            // 2: the item's last score product has completed, its Q tile may be overwritten
+  uint64_t* k_full = bars + 4;             // KST
+  uint64_t* k_empty = k_full + A1_KST;     // KST
+  uint64_t* v_full = k_empty + A1_KST;     // VST
+  uint64_t* v_empty = v_full + A1_VST;     // VST
+  uint64_t* s_full = v_empty + A1_VST;     // scores in tensor memory
+  uint64_t* p_full = s_full + 1;           // probabilities in tensor memory
+  uint64_t* o_full = p_full + 1;           // one commit per PV
+  uint64_t* s_free = o_full + 1;           // scores pulled into registers
+  uint64_t* sched_full = s_free + 1;       // 2: the slot holds the next work item
+  uint64_t* sched_empty = sched_full + 2;  // 2: every consumer has read the slot
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* sched_item = abort_flag + 1;   // 2 slots; -1 ends the list
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // work item: heavy (long KV range) tiles first
-  const int per_qt = p.B * p.Hkv * p.pairs;
-  const int qt = p.n_qt - 1 - (int)(blockIdx.x / per_qt);
-  int rem = (int)(blockIdx.x % per_qt);
-  const int b = rem / (p.Hkv * p.pairs);
-  rem -= b * p.Hkv * p.pairs;
-  const int kvh = rem / p.pairs, pair = rem % p.pairs;
-  const int group = p.H / p.Hkv;
-  const int head0 = kvh * group + pair * 2;
-  const int n_active = min(2, group - pair * 2);
-  const int n_kv = qt + 1;
-  const int row0 = b * p.S + qt * AT_BM;
+  const int n_items = p.n_qt * p.B * p.H;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int s = 0; s < AT_STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], n_active);
-    }
-    for (int w = 0; w < 2; ++w) {
-      mbar_init(&s_full[w], 1);
-      mbar_init(&p_full[w], 128);
-      mbar_init(&o_full[w], 1);
-      mbar_init(&s_free[w], 128);
-    }
+    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+    for (int s = 0; s < A1_KST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < A1_VST; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);                  // one arrival per softmax warp
+    mbar_init(o_full, 1);
+    mbar_init(s_free, 4);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sched_full[s], 1); mbar_init(&sched_empty[s], 6); }   // readers: two issuers, four softmax warps
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
   if (warp == 0 && lane == 0) {
@@ -122,94 +153,144 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(q_full, n_active * AT_TILE_BYTES);
-      for (int w = 0; w < n_active; ++w) tma_load_2d(sQ + w * AT_TILE_BYTES, &map_q, q_full, (head0 + w) * AT_HD, row0);
-      int stage = 0;
-      uint32_t phase = 0;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A1_REG_ROLE));
+    if (warp == 0 && lane == 0) {
+      // ---- TMA producer ----
+      int ks = 0, vs = 0;
+      uint32_t kph = 0, vph = 0, ic = 0, q_issued = 0;
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
-        uint8_t* sk = sKV + stage * 2 * AT_TILE_BYTES;
-        mbar_expect_tx(&kv_full[stage], 2 * AT_TILE_BYTES);
-        tma_load_2d(sk, &map_k, &kv_full[stage], kvh * AT_HD, b * p.S + j * AT_BN);
-        tma_load_2d(sk + AT_TILE_BYTES, &map_v, &kv_full[stage], kvh * AT_HD, b * p.S + j * AT_BN);
-        if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
+      for (;; ++ic) {
+        // work items are handed out by a device-wide counter: the two CTAs of an SM do not run at the same speed (the warp
+        // scheduler favours one of them), and a fixed split would leave the fast half of the grid idle at the end
+        const int slot = ic & 1;
+        if (!mbar_wait(&sched_empty[slot], ((ic >> 1) & 1) ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, -3)) { ok = false; break; }
+        int item = (int)atomicAdd(p.sched, 1u);
+        if (item >= n_items) item = -1;
+        sched_item[slot] = item;
+        mbar_arrive(&sched_full[slot]);
+        if (item < 0) break;
+        const FwdItem w = fwd_item(p, item);
+        if (!mbar_wait(&q_empty[slot], ((ic >> 1) & 1) ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, -1)) { ok = false; break; }
+        mbar_expect_tx(&q_full[slot], AT_TILE_BYTES);
+        tma_load_2d(sQ + slot * AT_TILE_BYTES, &map_q, &q_full[slot], w.head * AT_HD, w.row0);
+        ++q_issued;
+        for (int j = 0; j < w.n_kv; ++j) {
+          if (!mbar_wait(&k_empty[ks], kph ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
+          mbar_expect_tx(&k_full[ks], AT_TILE_BYTES);
+          tma_load_2d(sK + ks * AT_TILE_BYTES, &map_k, &k_full[ks], w.kvh * AT_HD, w.b * p.S + j * AT_BN);
+          if (++ks == A1_KST) { ks = 0; kph ^= 1; }
+          if (!mbar_wait(&v_empty[vs], vph ^ 1, abort_flag, p.status, ST_WAIT_EMPTY, j)) { ok = false; break; }
+          mbar_expect_tx(&v_full[vs], AT_TILE_BYTES);
+          tma_load_2d(sV + vs * AT_TILE_BYTES, &map_v, &v_full[vs], w.kvh * AT_HD, w.b * p.S + j * AT_BN);
+          if (++vs == A1_VST) { vs = 0; vph ^= 1; }
+        }
       }
       if (!ok) {
-        mbar_drain(q_full, 0);
-        for (int s = 0; s < AT_STAGES; ++s) mbar_drain(&kv_full[s], (s < stage) ? phase : (phase ^ 1));
-      }
-    }
-  } else if (warp == 1 || warp == 2) {
-    const int w = warp - 1;                     // each head of the pair has its own issuing thread
-    if (lane == 0 && w < n_active) {
-      constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);    // Q K^T : both K-major
-      constexpr uint32_t IDESC_O = make_idesc_bf16(128, AT_HD, 0, 1);  // P V   : A from TMEM, V is N-contiguous
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_WAIT_FULL, -1);
-      auto issue_s = [&](int stage) {
-        const uint32_t sq = smem_u32(sQ + w * AT_TILE_BYTES);
-        const uint32_t sk = smem_u32(sKV + stage * 2 * AT_TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < AT_HD / 16; ++k)
-          umma_ss(tmem_base + w * 128, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
-        umma_commit(&s_full[w]);
-      };
-      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, ST_WAIT_FULL, 0);
-      if (ok) {
-        tc_fence_after();
-        if (w == 1 && p.head1_delay_clk > 0) {
-          // The two softmax groups share the MUFU. Started together they stay in lock step and the unit idles while both
-          // load scores and take row maxima; started half a tile period apart, one group's exponentials cover the other's
-          // loads, maxima and hand-overs.
-          const long long t0 = clock64();
-          while (clock64() - t0 < p.head1_delay_clk) {}
+        // copies still in flight must land before the CTA's shared memory is given back: the most recent phase of every
+        // barrier a copy was issued on (stages below the ring position are in the current phase, the rest in the previous one)
+        for (int s = 0; s < 2; ++s) {
+          const uint32_t n = (q_issued + 1 - s) / 2;       // Q loads issued on this slot
+          if (n > 0) mbar_drain(&q_full[s], (n - 1) & 1);
         }
-        issue_s(0);
+        for (int s = 0; s < A1_KST; ++s) mbar_drain(&k_full[s], (s < ks) ? kph : (kph ^ 1));
+        for (int s = 0; s < A1_VST; ++s) mbar_drain(&v_full[s], (s < vs) ? vph : (vph ^ 1));
       }
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        int nstage = stage + 1;
-        uint32_t nphase = phase;
-        if (nstage == AT_STAGES) { nstage = 0; nphase ^= 1; }
-        if (j + 1 < n_kv) {
-          if (!mbar_wait(&kv_full[nstage], nphase, abort_flag, p.status, ST_WAIT_FULL, j + 1)) { ok = false; break; }
-          // scores of the next tile: only need the current ones to have been pulled into registers
-          if (!mbar_wait(&s_free[w], j & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, j)) { ok = false; break; }
+    } else if (warp == 1 && lane == 0) {
+      // ---- score products: S = Q K^T as soon as K has landed and the previous scores have been pulled into registers ----
+      constexpr uint32_t IDESC_S = make_idesc_bf16(128, 128, 0, 0);    // both operands K-major
+      int ks = 0;
+      uint32_t kph = 0, it = 0, ic = 0;
+      bool ok = true;
+      for (; ok; ++ic) {
+        const int slot = ic & 1;
+        if (!mbar_wait(&sched_full[slot], (ic >> 1) & 1, abort_flag, p.status, ST_WAIT_FULL, -3)) break;
+        const int item = sched_item[slot];
+        mbar_arrive(&sched_empty[slot]);
+        if (item < 0) break;
+        const int n_kv = fwd_item(p, item).n_kv;
+        if (!mbar_wait(&q_full[slot], (ic >> 1) & 1, abort_flag, p.status, ST_WAIT_FULL, -1)) break;
+        const uint32_t sq = smem_u32(sQ + slot * AT_TILE_BYTES);
+        for (int j = 0; j < n_kv; ++j, ++it) {
+          if (!mbar_wait(&k_full[ks], kph, abort_flag, p.status, ST_WAIT_FULL, j)) { ok = false; break; }
+          if (it > 0 && !mbar_wait(s_free, (it - 1) & 1, abort_flag, p.status, ST_WAIT_TMEM_EMPTY, j)) { ok = false; break; }
           tc_fence_after();
-          issue_s(nstage);
-        }
-        const uint32_t sv = smem_u32(sKV + stage * 2 * AT_TILE_BYTES + AT_TILE_BYTES);
-        if (!mbar_wait(&p_full[w], j & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
-        tc_fence_after();
+          const uint32_t sk = smem_u32(sK + ks * AT_TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < AT_BN / 16; ++k)
-          umma_ts(tmem_base + 384 + w * AT_HD, tmem_base + 256 + w * 64 + k * 8, make_smem_desc(sv + k * 2048, 8192, 1024), IDESC_O,
-                  (j > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&o_full[w]);
-        umma_commit(&kv_empty[stage]);
-        stage = nstage;
-        phase = nphase;
+          for (int k = 0; k < AT_HD / 16; ++k)
+            umma_ss(tmem_base, make_smem_desc(sq + k * 32, 16, 1024), make_smem_desc(sk + k * 32, 16, 1024), IDESC_S, k > 0 ? 1u : 0u);
+          umma_commit(s_full);
+          umma_commit(&k_empty[ks]);
+          if (++ks == A1_KST) { ks = 0; kph ^= 1; }
+        }
+        umma_commit(&q_empty[slot]);
+      }
+    } else if (warp == 2 && lane == 0) {
+      // ---- O += P V: its own issuing thread, so that a score product never queues behind a wait for probabilities ----
+      constexpr uint32_t IDESC_O = make_idesc_bf16(128, AT_HD, 0, 1);  // A from TMEM, V is N-contiguous
+      int vs = 0;
+      uint32_t vph = 0, it = 0, ic = 0;
+      bool ok = true;
+      for (; ok; ++ic) {
+        const int slot = ic & 1;
+        if (!mbar_wait(&sched_full[slot], (ic >> 1) & 1, abort_flag, p.status, ST_WAIT_FULL, -3)) break;
+        const int item = sched_item[slot];
+        mbar_arrive(&sched_empty[slot]);
+        if (item < 0) break;
+        const int n_kv = fwd_item(p, item).n_kv;
+        for (int j = 0; j < n_kv; ++j, ++it) {
+          if (!mbar_wait(&v_full[vs], vph, abort_flag, p.status, ST_WAIT_FULL, j)) { ok = false; break; }
+          // the first product of an item overwrites O; the softmax group reads the previous item's output out of tensor
+          // memory before it releases these probabilities
+          if (!mbar_wait(p_full, it & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sv = smem_u32(sV + vs * AT_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < AT_BN / 16; ++k)
+            umma_ts(tmem_base + 192, tmem_base + 128 + k * 8, make_smem_desc(sv + k * 2048, 8192, 1024), IDESC_O, (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(o_full);
+          umma_commit(&v_empty[vs]);
+          if (++vs == A1_VST) { vs = 0; vph ^= 1; }
+        }
       }
     }
-  }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
-    const int w = (warp - 4) >> 2;                 // softmax group / head within the pair
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A1_REG_SOFTMAX));
     const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
     const int r = quarter * 32 + lane;             // query row within the tile
-    if (w < n_active) {
-      const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-      const uint32_t tS = tmem_base + w * 128 + lane_off;
-      const uint32_t tO = tmem_base + 384 + w * AT_HD + lane_off;
-      const uint32_t tP = tmem_base + 256 + w * 64 + lane_off;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem_base + lane_off;
+    const uint32_t tP = tmem_base + 128 + lane_off;
+    const uint32_t tO = tmem_base + 192 + lane_off;
+    uint32_t it = 0, ic = 0;                       // tiles / items processed by this CTA: the phases of the barriers
+    bool ok = true;
+    // The output of an item is written while the next item's first tile is in flight: its last PV product has long completed
+    // by the time that tile's probabilities are ready, so no wait for the tensor core is exposed between items.
+    bool pend = false;
+    FwdItem wp = {};
+    float m_p = 0.f, l_p = 1.f;
+    auto store_out = [&](const uint32_t* o, const FwdItem& w, float m, float lsum) {
+      const float inv = 1.f / lsum;
+      __nv_bfloat16* yrow = p.Y + (size_t)(w.row0 + r) * p.ldy + w.head * AT_HD;
+#pragma unroll
+      for (int c = 0; c < 64; c += 8)
+        *reinterpret_cast<uint4*>(yrow + c) =
+            make_uint4(pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv),
+                       pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv),
+                       pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv),
+                       pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv));
+      p.lse[((size_t)w.b * p.H + w.head) * p.S + w.qt * AT_BM + r] = -(m + log2f(lsum));   // negated, log2 domain: what the backward consumes
+    };
+    for (; ok; ++ic) {
+      const int slot = ic & 1;
+      if (!mbar_wait(&sched_full[slot], (ic >> 1) & 1, abort_flag, p.status, ST_WAIT_FULL, -3)) { ok = false; break; }
+      const int item = sched_item[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sched_empty[slot]);
+      if (item < 0) break;
+      const FwdItem w = fwd_item(p, item);
       float m_used = -INFINITY, l = 0.f;
-      bool ok = true;
-      for (int j = 0; j < n_kv; ++j) {
-        if (!mbar_wait(&s_full[w], j & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL, j)) { ok = false; break; }
+      for (int j = 0; j < w.n_kv; ++j, ++it) {
+        if (!mbar_wait(s_full, it & 1, abort_flag, p.status, ST_WAIT_TMEM_FULL, j)) { ok = false; break; }
         tc_fence_after();
         uint32_t s[128];
         PGB_TMEM_LD32(tS, (s));
@@ -218,11 +299,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         PGB_TMEM_LD32(tS + 96, (s + 96));
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(&s_free[w]);                   // S(j) is in registers: the next tile's scores may overwrite it
-        if (j == qt) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);          // the scores are in registers: the next tile's may overwrite them
+        if (j == w.qt) {
 #pragma unroll
           for (int c = 0; c < 128; ++c)
-            if (c > r) s[c] = 0xff800000u;          // -inf
+            if (c > r) s[c] = 0xff800000u;            // -inf
         }
         float mx8[8];
 #pragma unroll
@@ -235,6 +317,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int e = 0; e < 8; ++e) mx8[e] = fmaxf(mx8[e], __uint_as_float(s[120 + e]));
         float mx = max3(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
         mx *= p.scale_log2;
+        // lazy running maximum: probabilities stay relative to a stale maximum until a row's maximum has grown by more than 2^8
         const bool need = mx > m_used + 8.0f;
         const bool any_need = __any_sync(0xffffffffu, need);
         float alpha = 1.f;
@@ -256,12 +339,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             if (c & 1) sum2b = __fadd2_rn(sum2b, pr); else sum2 = __fadd2_rn(sum2, pr);
             pk[c] = pack_bf16x2(pr.x, pr.y);
           }
-          if (q == 0 && j > 0) {
-            // P(j-1) is read by PV(j-1) and O is written by it: both must be finished before P(j) is stored / O rescaled.
-            // PV(j-1) was released a whole softmax phase ago, so this wait is normally already satisfied.
-            if (!mbar_wait(&o_full[w], (j - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
+          if (q == 0 && it > 0) {
+            // The previous PV product reads P and writes O: it must be finished before P is stored again / O rescaled.
+            // It was released a whole softmax phase ago, so this wait is normally already satisfied.
+            if (!mbar_wait(o_full, (it - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, j)) { ok = false; break; }
             tc_fence_after();
-            if (any_need) {
+            if (any_need && j > 0) {
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
                 uint32_t o[32];
@@ -277,31 +360,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           PGB_TMEM_ST16(tP + q * 16, pk);
         }
         if (!ok) break;
-        const float sum = (sum2.x + sum2.y) + (sum2b.x + sum2b.y);
-        l += sum;
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&p_full[w]);
-      }
-      if (ok && mbar_wait(&o_full[w], (n_kv - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, n_kv)) {
-        tc_fence_after();
-        const float inv = 1.f / l;
-        const int head = head0 + w;
-        __nv_bfloat16* yrow = p.Y + (size_t)(row0 + r) * p.ldy + head * AT_HD;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t o[32];
-          PGB_TMEM_LD32(tO + h * 32, o);
+        l += (sum2.x + sum2.y) + (sum2b.x + sum2b.y);
+        if (j == 0 && pend) {
+          // the previous item's O is still in tensor memory (the PV product that overwrites it needs the arrival below)
+          uint32_t o[64];
+          PGB_TMEM_LD32(tO, (o));
+          PGB_TMEM_LD32(tO + 32, (o + 32));
           tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; c += 8)
-            *reinterpret_cast<uint4*>(yrow + h * 32 + c) =
-                make_uint4(pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv),
-                           pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv),
-                           pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv),
-                           pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv));
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_full);
+          store_out(o, wp, m_p, l_p);
+          pend = false;
+        } else {
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_full);
         }
-        p.lse[((size_t)b * p.H + head) * p.S + qt * AT_BM + r] = -(m_used + log2f(l));   // negated, log2 domain: what the backward FMAs consume
+      }
+      if (!ok) break;
+      pend = true;
+      wp = w;
+      m_p = m_used;
+      l_p = l;
+    }
+    if (ok && pend) {
+      if (mbar_wait(o_full, (it - 1) & 1, abort_flag, p.status, ST_WAIT_MISC, -4)) {
+        tc_fence_after();
+        uint32_t o[64];
+        PGB_TMEM_LD32(tO, (o));
+        PGB_TMEM_LD32(tO + 32, (o + 32));
+        tmem_wait_ld();
+        store_out(o, wp, m_p, l_p);
       }
     }
   }
@@ -310,7 +402,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, 256);
+  }
+  // the last CTA to leave puts the work counter back for the next launch (every CTA has drawn its end marker by now)
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
   }
 }
 
@@ -331,29 +432,39 @@ void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, 
   AttnFwdParams p;
   p.B = B; p.S = S; p.H = H; p.Hkv = Hkv;
   p.n_qt = S / AT_BM;
-  p.pairs = (H / Hkv + 1) / 2;
   p.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-  {
-    static int delay = -1;
-    if (delay < 0) {
-      const char* e = getenv("PGB_ATTN_FWD_DELAY");
-      delay = e ? atoi(e) : 800;      // measured plateau 600-1200 clk at B=48, S=2048: 0.398 -> 0.381 ms
-    }
-    p.head1_delay_clk = delay;
-  }
   p.Y = (__nv_bfloat16*)y;
   p.ldy = ldy;
   p.lse = lse;
   p.status = status;
   static bool configured[64] = {};          // the attribute is a per-device property of the kernel
+  static unsigned* sched_base[64] = {};
+  static unsigned sched_next = 0;
+  static int sm_count[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+  const bool cached = dev >= 0 && dev < 64;
+  if (!cached || !configured[dev]) {
+    cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A1_SMEM);
+    cudaFuncAttributes fa;
+    // the register hand-over inside the kernel is balanced for exactly this launch allocation; anything else would never complete
+    if (cudaFuncGetAttributes(&fa, attn_fwd_kernel) != cudaSuccess || fa.numRegs != A1_REG_LAUNCH)
+      throw std::runtime_error("attn_fwd_kernel was not built with the register allocation its setmaxnreg hand-over assumes");
   }
-  const int grid = p.n_qt * B * Hkv * p.pairs;
-  attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(mq, mk, mv, p);
+  unsigned* base = cached ? sched_base[dev] : nullptr;
+  int sms = cached ? sm_count[dev] : 0;
+  if (!base || !sms) {
+    if (cudaGetSymbolAddress((void**)&base, g_fwd_sched) != cudaSuccess) throw std::runtime_error("attn_fwd: no scheduler counters");
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cached) {
+      sched_base[dev] = base;
+      sm_count[dev] = sms;
+      configured[dev] = true;
+    }
+  }
+  p.sched = base + 2 * (sched_next++ % A1_SCHED_SLOTS);
+  const int grid = std::min(p.n_qt * B * H, 2 * sms);
+  attn_fwd_kernel<<<grid, A1_THREADS, A1_SMEM, st>>>(mq, mk, mv, p);
 }
 
 }  // namespace pgb

@@ -5,8 +5,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstring>
 #include <stdexcept>
 #include <string>
+#include <unordered_map>
 
 namespace pgb {
 
@@ -27,10 +29,45 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Everything `cuTensorMapEncodeTiled` is given. The encoded map is a pure function of these values, so a map built once for
+// a (pointer, shape, box) can be reused by every later launch on the same buffers: the training step calls each product with
+// the same pre-allocated tensors, step after step.
+struct TmapKey {
+  const void* base;
+  uint64_t dims[4];
+  uint64_t strides[3];
+  uint32_t box[4];
+  int32_t rank;
+  int32_t swz;
+  bool operator==(const TmapKey& o) const { return std::memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    const unsigned char* b = reinterpret_cast<const unsigned char*>(&k);
+    uint64_t h = 1469598103934665603ull;                     // FNV-1a over the (zero-padded) key
+    for (size_t i = 0; i < sizeof(TmapKey); ++i) h = (h ^ b[i]) * 1099511628211ull;
+    return (size_t)h;
+  }
+};
+
 // bf16 tensor of up to 4 dims. dims[0] is the contiguous one; strides_bytes[i] is the stride of dim i+1.
-// 128-byte swizzle; out-of-range elements read as zero.
+// 128-byte swizzle; out-of-range elements read as zero. Encoded maps are cached per host thread.
 inline CUtensorMap make_tmap_bf16(const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
                                   const uint32_t* box, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
+  if (rank < 1 || rank > 4) throw std::runtime_error("TMA tensor maps of rank 1 to 4 only");
+  thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  TmapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.rank = rank;
+  key.swz = (int32_t)swz;
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+  }
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides_bytes[i];
+  auto hit = cache.find(key);
+  if (hit != cache.end()) return hit->second;
   CUtensorMap m;
   cuuint64_t gd[5];
   cuuint64_t gs[4];
@@ -49,6 +86,8 @@ inline CUtensorMap make_tmap_bf16(const void* base, int rank, const uint64_t* di
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  if (cache.size() >= 8192) cache.clear();                   // evaluation over many differently shaped views: start over
+  cache.emplace(key, m);
   return m;
 }
 

@@ -595,7 +595,7 @@ size_t attn_bwd_fused_scratch_floats(int B, int S, int H) { return (size_t)B * H
 
 void attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, float* dsum, float* dq_acc, void* dq,
                     void* dk, void* dv, long long ldq, long long ldk, long long ldv, long long ldo, long long lddo, long long lddq, long long lddk,
-                    long long lddv, int B, int S, int H, int Hkv, int hd, int accumulate_dv, int* status, cudaStream_t st) {
+                    long long lddv, int B, int S, int H, int Hkv, int hd, int accumulate_dv, int* status, cudaStream_t st, int dsum_ready) {
   if (hd != F_HD) throw std::runtime_error("attention kernel is specialised for head_dim 64");
   if (S % 128) throw std::runtime_error("attention kernel needs seq_len to be a multiple of 128");
   if (H % Hkv) throw std::runtime_error("attention: the number of KV heads must divide the number of query heads");
@@ -623,7 +623,8 @@ void attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, 
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const long long n_chunks = T * H * 8;
-  attn_bwd_prep_kernel<<<(unsigned)((n_chunks + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, ldo, lddo, dsum, T, S, H);
+  if (!dsum_ready)          // otherwise the producer of d_o has already written -rowsum(d_o * o) (`xsa_bwd` does)
+    attn_bwd_prep_kernel<<<(unsigned)((n_chunks + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, ldo, lddo, dsum, T, S, H);
   const CUtensorMap mq = fused_map(q, ldq, H * hd, T), mk = fused_map(k, ldk, Hkv * hd, T), mv = fused_map(v, ldv, Hkv * hd, T),
                     mdo = fused_map(d_o, lddo, H * hd, T);
   attn_bwd_fused_kernel<<<std::min(p.n_super, sms), F_THREADS, F_SMEM, st>>>(mq, mk, mv, mdo, p);

@@ -36,6 +36,13 @@ struct AttnFwdParams {
   float* lse;
   int* status;
   unsigned* sched;                   // {next work item, CTAs finished}: both zero between launches
+  // Optional second output z_h = y_h - (<y_h, v> / (|v|^2 + eps)) v with the token's own value vector of the head's KV group
+  // (exclusive self attention); null when the layer does not use it.
+  __nv_bfloat16* Z;
+  long long ldz;
+  const __nv_bfloat16* V;
+  long long ldv;
+  float xsa_eps;
 };
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
@@ -279,6 +286,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                        pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv),
                        pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv));
       p.lse[((size_t)w.b * p.H + w.head) * p.S + w.qt * AT_BM + r] = -(m + log2f(lsum));   // negated, log2 domain: what the backward consumes
+      if (p.Z != nullptr) {
+        // the row's own value vector: the diagonal V tile held it a moment ago, so these 128 bytes come from L2
+        const uint4* vp = reinterpret_cast<const uint4*>(p.V + (size_t)(w.row0 + r) * p.ldv + w.kvh * AT_HD);
+        uint32_t vv[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 t = __ldg(vp + c);
+          vv[4 * c] = t.x; vv[4 * c + 1] = t.y; vv[4 * c + 2] = t.z; vv[4 * c + 3] = t.w;
+        }
+        float n = p.xsa_eps, dot = 0.f;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float2 f = unpack_bf16x2(vv[c]);
+          n += f.x * f.x + f.y * f.y;
+          dot += __uint_as_float(o[2 * c]) * f.x + __uint_as_float(o[2 * c + 1]) * f.y;
+        }
+        const float coef = dot * inv / n;
+        __nv_bfloat16* zrow = p.Z + (size_t)(w.row0 + r) * p.ldz + w.head * AT_HD;
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          uint32_t out[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = unpack_bf16x2(vv[c + e]);
+            out[e] = pack_bf16x2(__uint_as_float(o[2 * (c + e)]) * inv - coef * f.x, __uint_as_float(o[2 * (c + e) + 1]) * inv - coef * f.y);
+          }
+          *reinterpret_cast<uint4*>(zrow + 2 * c) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+      }
     };
     for (; ok; ++ic) {
       const int slot = ic & 1;
@@ -423,7 +459,7 @@ static CUtensorMap attn_map(const void* ptr, long long ld, int cols, long long r
 }
 
 void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, long long ldq, long long ldk, long long ldv, long long ldy, int B,
-              int S, int H, int Hkv, int hd, int* status, cudaStream_t st) {
+              int S, int H, int Hkv, int hd, int* status, cudaStream_t st, void* z, long long ldz, float xsa_eps) {
   if (hd != AT_HD) throw std::runtime_error("attention kernel is specialised for head_dim 64");
   if (S % 128) throw std::runtime_error("attention kernel needs seq_len to be a multiple of 128");
   if (H % Hkv) throw std::runtime_error("num_heads must be divisible by num_kv_heads");
@@ -437,6 +473,13 @@ void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, 
   p.ldy = ldy;
   p.lse = lse;
   p.status = status;
+  if (z && ((ldz % 8) || (ldv % 8) || (reinterpret_cast<uintptr_t>(z) & 15) || (reinterpret_cast<uintptr_t>(v) & 15)))
+    throw std::runtime_error("attention: the second output and the value rows must be 16-byte aligned");
+  p.Z = (__nv_bfloat16*)z;
+  p.ldz = ldz;
+  p.V = (const __nv_bfloat16*)v;
+  p.ldv = ldv;
+  p.xsa_eps = xsa_eps;
   static bool configured[64] = {};          // the attribute is a per-device property of the kernel
   static unsigned* sched_base[64] = {};
   static unsigned sched_next = 0;

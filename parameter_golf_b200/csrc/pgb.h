@@ -63,8 +63,10 @@ void qk_norm_rope_fwd(const void* src, void* dst, const float* cosT, const float
 void qk_norm_rope_bwd(const void* d_post, const void* pre, void* d_pre, const float* cosT, const float* sinT, const float* gain, float* d_gain,
                       int rows, int ld, int H, int Hkv, int hd, int rope_dims, int seq_len, float eps, cudaStream_t st);
 void xsa_fwd(const void* y, const void* v, void* z, int rows, int Hkv, int group, int hd, int ld_y, int ld_v, float eps, cudaStream_t st);
+// dsum (optional, head_dim 64 only): fp32 [B, H, S] with -rowsum(dy * y), the per-query term the attention backward needs, so
+// that its own pass over dy and y can be skipped; seq_len gives the [B, S] split of the rows.
 void xsa_bwd(const void* dz, const void* y, const void* v, void* dy, void* dv, int accumulate_dv, int rows, int Hkv, int group, int hd, int ld_y,
-             int ld_v, int ld_dv, float eps, cudaStream_t st);
+             int ld_v, int ld_dv, float eps, cudaStream_t st, float* dsum = nullptr, int seq_len = 0);
 // Per-head output gates (gates.cu): out_h = y_h * mult * sigmoid(scale * <W_h, x[:w]> + bias_h); `gate` [rows, H] keeps the factors
 // for the backward, which rewrites d_out in place into the gradient of y and adds the input-feature part into d_x[:, :w].
 void head_gate_fwd(const void* y, const void* x, const float* W, const float* bias, void* out, float* gate, int rows, int H, int hd, int w, int ld_x,
@@ -93,7 +95,7 @@ void qk_norm_rope_bwd64(const void* d_post, const void* pre, void* d_pre, const 
 
 void xsa_fwd64(const void* y, const void* v, void* z, int rows, int Hkv, int group, int ld_y, int ld_v, float eps, cudaStream_t st);
 void xsa_bwd64(const void* dz, const void* y, const void* v, void* dy, void* dv, int accumulate_dv, int rows, int Hkv, int group, int ld_y, int ld_v,
-               int ld_dv, float eps, cudaStream_t st);
+               int ld_dv, float eps, cudaStream_t st, float* dsum = nullptr, int seq_len = 0);
 
 // ---- optimizer / weight preparation (optim.cu) --------------------------------------------------------------------------
 // hp: device fp32[8] = {lr_scale, muon_momentum, adam_bias_corr1, adam_bias_corr2, grad_scale, ...}
@@ -147,8 +149,9 @@ void gptq_rows(const float* Wp, const float* U, const float* scales, int8_t* Q, 
 // ---- attention (attn_fwd.cu, attn_bwd.cu): causal, grouped KV heads, head_dim 64, bf16 ----------------------------------
 // q/k/v/y are [B*S, heads*hd] views with row strides ld* (elements); lse is fp32 [B, H, S] and holds the NEGATED
 // base-2 log-sum-exp of the scaled scores (the form the backward kernels feed straight into their FMAs).
+// z (optional): second output with the exclusive-self-attention projection applied, z_h = y_h - (<y_h, v> / (|v|^2 + eps)) v
 void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, long long ldq, long long ldk, long long ldv, long long ldy, int B,
-              int S, int H, int Hkv, int hd, int* status, cudaStream_t st);
+              int S, int H, int Hkv, int hd, int* status, cudaStream_t st, void* z = nullptr, long long ldz = 0, float xsa_eps = 0.f);
 // dsum: fp32 [B, H, S] scratch-free side output (rowsum(dO * O)), written by the dQ kernel and read by the dK/dV kernel.
 void attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, float* dsum, void* dq, void* dk, void* dv,
               long long ldq, long long ldk, long long ldv, long long ldo, long long lddo, long long lddq, long long lddk, long long lddv, int B, int S,
@@ -159,6 +162,6 @@ void attn_bwd(const void* q, const void* k, const void* v, const void* o, const 
 size_t attn_bwd_fused_scratch_floats(int B, int S, int H);
 void attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, float* dsum, float* dq_acc, void* dq,
                     void* dk, void* dv, long long ldq, long long ldk, long long ldv, long long ldo, long long lddo, long long lddq, long long lddk,
-                    long long lddv, int B, int S, int H, int Hkv, int hd, int accumulate_dv, int* status, cudaStream_t st);
+                    long long lddv, int B, int S, int H, int Hkv, int hd, int accumulate_dv, int* status, cudaStream_t st, int dsum_ready = 0);
 
 }  // namespace pgb

@@ -918,11 +918,12 @@ void xsa_fwd(const void* y, const void* v, void* z, int rows, int Hkv, int group
 }
 
 void xsa_bwd(const void* dz, const void* y, const void* v, void* dy, void* dv, int accumulate_dv, int rows, int Hkv, int group, int hd, int ld_y,
-             int ld_v, int ld_dv, float eps, cudaStream_t st) {
+             int ld_v, int ld_dv, float eps, cudaStream_t st, float* dsum, int seq_len) {
   if (hd == 64 && ld_y % 8 == 0 && ld_v % 8 == 0 && ld_dv % 8 == 0) {
-    xsa_bwd64(dz, y, v, dy, dv, accumulate_dv, rows, Hkv, group, ld_y, ld_v, ld_dv, eps, st);
+    xsa_bwd64(dz, y, v, dy, dv, accumulate_dv, rows, Hkv, group, ld_y, ld_v, ld_dv, eps, st, dsum, seq_len);
     return;
   }
+  if (dsum) throw std::runtime_error("xsa: the attention term is only produced by the head_dim 64 kernel");
   const long long n = (long long)rows * Hkv;
   auto kern = hd == 64 ? xsa_bwd_kernel<64> : xsa_bwd_kernel<0>;
   kern<<<(unsigned)((n + 127) / 128), 128, 0, st>>>((const __nv_bfloat16*)dz, (const __nv_bfloat16*)y, (const __nv_bfloat16*)v,

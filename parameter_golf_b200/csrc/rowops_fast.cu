@@ -377,7 +377,7 @@ __global__ void __launch_bounds__(256) xsa_fwd64_kernel(const __nv_bfloat16* __r
 __global__ void __launch_bounds__(256) xsa_bwd64_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ y,
                                                         const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ dy,
                                                         __nv_bfloat16* __restrict__ dv, int accumulate_dv, int nvec, int Hkv, int group, int ld_y,
-                                                        int ld_v, int ld_dv, float eps) {
+                                                        int ld_v, int ld_dv, float eps, float* __restrict__ dsum, int seq_len) {
   const int sub = threadIdx.x & 7;
   const int vstride = (int)gridDim.x * (blockDim.x / 8);
   const int nvec_pad = (nvec + 3) / 4 * 4;
@@ -409,12 +409,22 @@ __global__ void __launch_bounds__(256) xsa_bwd64_kernel(const __nv_bfloat16* __r
       }
       const float ch = sum8(yv) / n, gn = sum8(gv) / n;
       V8 o;
+      float dd = 0.f;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         o.v[e] = b.v[e] - gn * vv.v[e];
         acc.v[e] += -ch * b.v[e] - gn * a.v[e] + 2.f * ch * gn * vv.v[e];
+        dd += __bfloat162float(__float2bfloat16_rn(o.v[e])) * a.v[e];       // with dy as the attention backward will read it
       }
       if (live) stv(dy + off, o);
+      if (dsum != nullptr) {
+        // -rowsum(dy * y) per (token, head): the attention backward's per-query term, here for free
+        dd = sum8(dd);
+        if (live && sub == 0) {
+          const int bb = row / seq_len, ss = row - bb * seq_len;
+          dsum[((size_t)bb * (Hkv * group) + kh * group + g) * seq_len + ss] = -dd;
+        }
+      }
     }
     if (live) stv(dvp, acc);
   }
@@ -428,12 +438,13 @@ void xsa_fwd64(const void* y, const void* v, void* z, int rows, int Hkv, int gro
 }
 
 void xsa_bwd64(const void* dz, const void* y, const void* v, void* dy, void* dv, int accumulate_dv, int rows, int Hkv, int group, int ld_y, int ld_v,
-               int ld_dv, float eps, cudaStream_t st) {
+               int ld_dv, float eps, cudaStream_t st, float* dsum, int seq_len) {
+  if (dsum && (seq_len <= 0 || rows % seq_len)) throw std::runtime_error("xsa: the rows must be whole sequences when the attention term is requested");
   if ((long long)rows * Hkv > 0x7fffff00ll) throw std::runtime_error("xsa: too many head vectors for 32-bit indexing");
   const int nvec = rows * Hkv;
   const int grid = std::max(1, std::min((nvec + 31) / 32, 148 * 16));
   xsa_bwd64_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dz, (const __nv_bfloat16*)y, (const __nv_bfloat16*)v, (__nv_bfloat16*)dy,
-                                         (__nv_bfloat16*)dv, accumulate_dv, nvec, Hkv, group, ld_y, ld_v, ld_dv, eps);
+                                         (__nv_bfloat16*)dv, accumulate_dv, nvec, Hkv, group, ld_y, ld_v, ld_dv, eps, dsum, seq_len);
 }
 
 }  // namespace pgb

@@ -444,7 +444,10 @@ class CudaEngine:
         q = self.qk_post[li][:, :d]
         k = self.qk_post[li][:, d:d + kv]
         v = self.qkv_pre[li][:, d + kv:]
-        self.lse[li] = N.attn_fwd(q, k, v, self.y[li], B, S, H, Hkv, hd, self.lse[li])
+        # exclusive self attention: the projection off the token's own value vector is applied to the accumulator in the
+        # attention kernel's output stage, which writes both y (the backward needs it) and z
+        z = self.z[li] if l in self.m.xsa_layers() else None
+        self.lse[li] = N.attn_fwd(q, k, v, self.y[li], B, S, H, Hkv, hd, self.lse[li], z, 1e-8)
 
     def _attn_bwd(self, l, j):
         d, kv, B, S, H, Hkv, hd = self.d, self.kv, self.B, self.S, self.H, self.Hkv, self.hd
@@ -454,8 +457,9 @@ class CudaEngine:
         dq, dk = self.d_qk_post[:, :d], self.d_qk_post[:, d:d + kv]
         dv = self.d_qkv_pre[:, d + kv:]
         xsa = l in self.m.xsa_layers()
+        # in XSA layers `xsa_bwd` has just produced d_y and, in the same pass, the -rowsum(d_y * y) term of the single-pass form
         N.attn_bwd(q, k, v, self.y[j], self.d_y, self.lse[j], dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=xsa, dsum=self.dsum,
-                   dq_acc=self.dq_acc, reproducible=self.t.reproducible_backward)
+                   dq_acc=self.dq_acc, reproducible=self.t.reproducible_backward, dsum_ready=xsa and not self.t.reproducible_backward)
 
     def _block_fwd(self, j: int, x, skip, sw, recompute: bool = False):
         """Block of activation slot ``j`` on input ``x`` (with the U-Net skip it consumes, if any); returns the block output.
@@ -486,10 +490,7 @@ class CudaEngine:
             self._lora_fwd(l, li)
         C.qk_norm_rope_fwd(self.qkv_pre[li], self.qk_post[li], self.cos, self.sin, p["q_gain"][l], self.H, self.Hkv, self.hd, m.rope_dims, S, self.eps)
         self._attn_fwd(l, li)
-        zz = self.y[li]
-        if l in m.xsa_layers():
-            zz = self.z[li]
-            C.xsa_fwd(self.y[li], self.qkv_pre[li][:, d + kv:], zz, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+        zz = self.z[li] if l in m.xsa_layers() else self.y[li]
         for gi, (wname, bname, gscale_, gmult) in enumerate(self.gates):
             out = self.yg[gi][li]
             C.head_gate_fwd(zz, self.h[li], p[wname][l], p[bname][l] if bname else None, out, self.gv[gi][li], self.H, self.hd, gscale_, gmult)
@@ -636,7 +637,10 @@ class CudaEngine:
                 C.head_gate_bwd(d_att, gate_in, self.h[aj], p[wname][l], self.gv[gi][aj], g[wname][l], g[bname][l] if bname else None, d_hx,
                                 not first_writer, self.H, self.hd, gscale_, gmult)
             if xsa:
-                C.xsa_bwd(self.d_z, self.y[aj], vview, self.d_y, dv, False, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+                if self.t.reproducible_backward:
+                    C.xsa_bwd(self.d_z, self.y[aj], vview, self.d_y, dv, False, self.Hkv, self.H // self.Hkv, self.hd, 1e-8)
+                else:
+                    C.xsa_bwd(self.d_z, self.y[aj], vview, self.d_y, dv, False, self.Hkv, self.H // self.Hkv, self.hd, 1e-8, self.dsum, S)
             self._attn_bwd(l, aj)
             C.qk_norm_rope_bwd(self.d_qk_post, self.qkv_pre[aj], self.d_qkv_pre, self.cos, self.sin, p["q_gain"][l], g["q_gain"][l], self.H, self.Hkv,
                                self.hd, m.rope_dims, S, self.eps)

@@ -49,7 +49,8 @@ class _Counting:
         n = self._PER_CALL.get(name, 1)
 
         def call(*a, **k):
-            self.launches += n
+            # the single-pass attention backward skips its first kernel when the caller supplies the per-query term
+            self.launches += n - 1 if (name == "attn_bwd_fused" and len(a) >= 19 and a[18]) else n
             if self.timing is None:
                 return fn(*a, **k)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -142,11 +143,13 @@ def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.
     return D
 
 
-def attn_fwd(q, k, v, y, B, S, H, Hkv, hd, lse=None):
-    """Causal GQA attention forward; q/k/v are [B*S, heads*hd] (row-strided views allowed). Returns the side output [B, H, S] = -(log2-domain log-sum-exp), which `attn_bwd` consumes."""
+def attn_fwd(q, k, v, y, B, S, H, Hkv, hd, lse=None, z=None, xsa_eps=1e-8):
+    """Causal GQA attention forward; q/k/v are [B*S, heads*hd] (row-strided views allowed). Returns the side output [B, H, S] = -(log2-domain log-sum-exp), which `attn_bwd` consumes.
+    With ``z`` the kernel also writes the exclusive-self-attention output z_h = y_h - (<y_h, v> / (|v|^2 + eps)) v from the
+    accumulator it already holds (`xsa_fwd` as a separate pass is then not needed)."""
     if lse is None:
         lse = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
-    load().attn_fwd(q, k, v, y, lse, B, S, H, Hkv, hd, status_word(q.device))
+    load().attn_fwd(q, k, v, y, lse, B, S, H, Hkv, hd, status_word(q.device), z, xsa_eps)
     return lse
 
 
@@ -165,20 +168,23 @@ def attn_dq_scratch(device, B, S, H, hd=64):
     return buf
 
 
-def attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=False, dsum=None, dq_acc=None, reproducible=False):
+def attn_bwd(q, k, v, o, d_o, lse, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv=False, dsum=None, dq_acc=None, reproducible=False,
+             dsum_ready=False):
     """Causal GQA attention backward. Writes dq, dk and dv (dv is added to when ``accumulate_dv``).
 
     Default: the single-pass kernel (scores computed once per tile pair; dQ summed in an fp32 accumulator with `red.add`,
     so its last fp32 bits depend on scheduling). ``reproducible=True`` runs the two-kernel form, which recomputes the
-    scores for dQ and is bit-reproducible."""
+    scores for dQ and is bit-reproducible. ``dsum_ready``: ``dsum`` already holds -rowsum(d_o * o) (`xsa_bwd` writes it on
+    request), so the single-pass form skips its own pass over d_o and o."""
     if dsum is None:
+        dsum_ready = False
         dsum = torch.empty(B, H, S, dtype=torch.float32, device=q.device)
     if reproducible:
         load().attn_bwd(q, k, v, o, d_o, lse, dsum, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv, status_word(q.device))
         return dsum
     if dq_acc is None:
         dq_acc = attn_dq_scratch(q.device, B, S, H, hd)
-    load().attn_bwd_fused(q, k, v, o, d_o, lse, dsum, dq_acc, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv, status_word(q.device))
+    load().attn_bwd_fused(q, k, v, o, d_o, lse, dsum, dq_acc, dq, dk, dv, B, S, H, Hkv, hd, accumulate_dv, status_word(q.device), dsum_ready)
     return dsum
 
 

@@ -35,6 +35,30 @@ def test_attention_forward(B, S, H, Hkv):
     assert (lse_nat - _ref_lse(q, k, B, S, H, Hkv, hd)).abs().max().item() < 0.02
 
 
+@pytest.mark.parametrize("B,S,H,Hkv", [(2, 256, 4, 2), (1, 640, 8, 4), (3, 128, 2, 2)])
+def test_attention_forward_with_exclusive_self_attention_output(B, S, H, Hkv):
+    """The optional second output: y with its component along the token's own value vector removed, from the same kernel."""
+    from parameter_golf_b200.ops import native as n
+    from parameter_golf_b200.ops import reference as R
+    hd = 64
+    torch.manual_seed(S + 7 * H)
+    qkv = (torch.randn(B * S, (H + 2 * Hkv) * hd, device="cuda") * 1.5).bfloat16()
+    q, k, v = qkv[:, :H * hd], qkv[:, H * hd:(H + Hkv) * hd], qkv[:, (H + Hkv) * hd:]
+    y = torch.zeros(B * S, H * hd, device="cuda", dtype=torch.bfloat16)
+    z = torch.zeros_like(y)
+    n.attn_fwd(q, k, v, y, B, S, H, Hkv, hd, z=z, xsa_eps=1e-8)
+    torch.cuda.synchronize()
+    n.check_status()
+    ref = _ref(q, k, v, B, S, H, Hkv, hd)
+    assert (y.float() - ref).abs().max() < 0.04
+    z_ref = R.xsa(ref.reshape(B, S, H, hd), v.float().reshape(B, S, Hkv, hd)).reshape(B * S, H * hd)
+    assert (z.float() - z_ref).abs().max() < 0.04, (z.float() - z_ref).abs().max()
+    # z is orthogonal to the value vector of its KV group
+    zz = z.float().reshape(B * S, Hkv, H // Hkv, hd)
+    vv = torch.nn.functional.normalize(v.float().reshape(B * S, Hkv, 1, hd), dim=-1)
+    assert (zz * vv).sum(-1).abs().max() < 0.12
+
+
 def test_attention_forward_large_scores_trigger_rescale():
     """Scores that keep growing along the sequence force the lazy rescale of the accumulator."""
     from parameter_golf_b200.ops import native as n

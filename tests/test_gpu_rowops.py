@@ -137,6 +137,25 @@ def test_xsa_forward_and_backward(T, H, Hkv):
     assert rel(dv, vf.grad.reshape(T, Hkv * hd)) < 0.015
 
 
+@pytest.mark.parametrize("B,S,H,Hkv", [(3, 128, 8, 4), (2, 384, 2, 1)])
+def test_xsa_backward_also_yields_the_attention_backward_term(B, S, H, Hkv):
+    """With `dsum` the kernel writes -rowsum(dy * y) per (batch, head, position) next to dy and dv, from the values it holds."""
+    hd, T = 64, B * S
+    y = bf(T, H * hd, seed=4)
+    qkv = bf(T, (H + 2 * Hkv) * hd, seed=5)
+    v = qkv[:, (H + Hkv) * hd:]
+    dz = bf(T, H * hd, scale=0.5, seed=6)
+    dy, dy2 = torch.empty_like(y), torch.empty_like(y)
+    dv, dv2 = torch.zeros(T, Hkv * hd, device="cuda", dtype=BF), torch.zeros(T, Hkv * hd, device="cuda", dtype=BF)
+    dsum = torch.full((B, H, S), float("nan"), device="cuda")
+    C().xsa_bwd(dz, y, v, dy, dv, False, Hkv, H // Hkv, hd, 1e-8, dsum, S)
+    C().xsa_bwd(dz, y, v, dy2, dv2, False, Hkv, H // Hkv, hd, 1e-8)
+    torch.cuda.synchronize()
+    assert torch.equal(dy, dy2) and torch.equal(dv, dv2)
+    ref = -(dy.float() * y.float()).reshape(B, S, H, hd).sum(-1).permute(0, 2, 1)
+    assert (dsum - ref).abs().max() < 1e-3 * max(1.0, float(ref.abs().max()))
+
+
 @pytest.mark.parametrize("B,S,d,boundary", [(3, 128, 512, -1), (2, 257, 512, 7), (1, 640, 128, -1)])
 def test_norm_smear_forward_and_backward(B, S, d, boundary):
     from parameter_golf_b200.ops import reference as R

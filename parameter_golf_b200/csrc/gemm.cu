@@ -45,6 +45,11 @@ struct GemmKernelParams {
   int aux_l2_prefetch;     // the producer warp pulls the next tile's second operand into L2 through `map_x`
   const float* batch_sumsq;   // optional: alpha and beta of batch b are multiplied by 1 / (sqrt(batch_sumsq[b]) + 1e-7) ^ sumsq_pow
   int sumsq_pow;
+  const float* rope_cos;      // EPI_QKV_NORM_ROPE
+  const float* rope_sin;
+  const float* head_gain;
+  int q_heads, qk_heads, rope_half, seq_len;
+  float norm_eps;
 };
 
 constexpr int STG_PITCH = 64;
@@ -253,6 +258,83 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmKernelParams& p,
   };
   put(pk, p.D);
   if constexpr (EPI == EPI_ACT_SQ) put(pk2, p.D2);
+}
+
+// Half-split rotary on the first 2*HALF of a head's 64 values, tables [seq_len][HALF] (the layout of `qk_norm_rope_fwd`).
+template <int HALF>
+__device__ __forceinline__ void rope_head(float (&x)[64], const float* __restrict__ cosT, const float* __restrict__ sinT, int pos) {
+  if constexpr (HALF > 0) {
+    const float4* c4 = reinterpret_cast<const float4*>(cosT + (size_t)pos * HALF);
+    const float4* s4 = reinterpret_cast<const float4*>(sinT + (size_t)pos * HALF);
+#pragma unroll
+    for (int i = 0; i < HALF; i += 4) {
+      const float4 c = __ldg(c4 + i / 4), sn = __ldg(s4 + i / 4);
+      const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x1 = x[i + e], x2 = x[i + e + HALF];
+        x[i + e] = x1 * cc[e] + x2 * ss[e];
+        x[i + e + HALF] = x2 * cc[e] - x1 * ss[e];
+      }
+    }
+  }
+}
+
+// EPI_QKV_NORM_ROPE on one head (two 32-column chunks) of 32 rows: the raw projection goes to D; for query and key heads the
+// RMS-normalised, rotated and (queries) gain-scaled head goes to D2. The norm is taken of the bf16-rounded projection, the
+// values the backward recomputes it from. Replaces a pass over the projection (`qk_norm_rope_fwd`, kept for the LoRA path);
+// same math as the reference's fused QK kernels (parameter-golf-rs/crates/pg-kernels/src/gpu_kernels.rs:2640-2822).
+__device__ __forceinline__ void epilogue_qkv_head_staged(const GemmKernelParams& p, int b, int m_base, int lane, int n0, const uint32_t (&ra)[32],
+                                                         const uint32_t (&rb)[32], uint8_t* stg) {
+  const int srow = lane >> 2, spc = lane & 3;
+  auto put = [&](const uint32_t* x, void* base, int col0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      *reinterpret_cast<uint4*>(stg + stg_off(lane, i)) = make_uint4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+    __syncwarp();
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(base) + (long long)b * p.stride_d + col0 + spc * 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = m_base + i * 8 + srow;
+      if (row < p.M) *reinterpret_cast<uint4*>(d + (long long)row * p.ldd) = *reinterpret_cast<const uint4*>(stg + stg_off(i * 8 + srow, spc));
+    }
+    __syncwarp();
+  };
+  uint32_t pk[32];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    pk[i] = pack_bf16x2(__uint_as_float(ra[2 * i]) * p.alpha, __uint_as_float(ra[2 * i + 1]) * p.alpha);
+    pk[16 + i] = pack_bf16x2(__uint_as_float(rb[2 * i]) * p.alpha, __uint_as_float(rb[2 * i + 1]) * p.alpha);
+  }
+  put(pk, p.D, n0);
+  put(pk + 16, p.D, n0 + 32);
+  const int head = n0 >> 6;
+  if (head >= p.qk_heads) return;                  // value heads: the projection as it is (warp-uniform)
+  float x[64];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float2 f = unpack_bf16x2(pk[i]);
+    x[2 * i] = f.x;
+    x[2 * i + 1] = f.y;
+    ss += f.x * f.x + f.y * f.y;
+  }
+  const float inv = rsqrtf(ss * (1.f / 64.f) + p.norm_eps);
+#pragma unroll
+  for (int i = 0; i < 64; ++i) x[i] *= inv;
+  const int row = min(m_base + lane, p.M - 1);
+  const int pos = row % p.seq_len;
+  switch (p.rope_half) {
+    case 8: rope_head<8>(x, p.rope_cos, p.rope_sin, pos); break;
+    case 16: rope_head<16>(x, p.rope_cos, p.rope_sin, pos); break;
+    case 32: rope_head<32>(x, p.rope_cos, p.rope_sin, pos); break;
+    default: break;
+  }
+  const float g = (head < p.q_heads && p.head_gain != nullptr) ? p.head_gain[head] : 1.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(x[2 * i] * g, x[2 * i + 1] * g);     // one rounding, at the store
+  put(pk, p.D2, n0);
+  put(pk + 16, p.D2, n0 + 32);
 }
 
 template <int BN, bool A_KMAJOR, bool B_KMAJOR, int EPI>
@@ -482,6 +564,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, ST_WAIT_TMEM_FULL, tile)) { ok = false; break; }
       tc_fence_after();
+      if constexpr (EPI == EPI_QKV_NORM_ROPE) {
+        // one head (two chunks) at a time: the norm needs all 64 values of the row before either chunk can be written
+#pragma unroll
+        for (int cc = 0; cc < CH; cc += 2) {
+          const int c = c_begin + cc;
+          const int n0 = tn * BN + c * 32;
+          if (n0 < p.N) {                         // warp-uniform; N is a multiple of 64 (checked on the host)
+            uint32_t ra[32], rb[32];
+            PGB_TMEM_LD32(taddr + c * 32, ra);
+            PGB_TMEM_LD32(taddr + c * 32 + 32, rb);
+            PGB_TMEM_WAIT_LD32(ra);
+            PGB_TMEM_WAIT_LD32(rb);
+            epilogue_qkv_head_staged(p, b, m_base, lane, n0, ra, rb, slots);
+          }
+        }
+      } else {
 #pragma unroll
       for (int cc = 0; cc < CH; ++cc) {
         const int c = c_begin + cc;
@@ -512,6 +610,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             else cp_async_commit();
           }
         }
+      }
       }
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
@@ -590,6 +689,10 @@ static void launch_epi(const GemmArgs& a, const CUtensorMap& ma, const CUtensorM
     case EPI_RESID_BF16: launch_major<BN, EPI_RESID_BF16>(a, ma, mb, mx, p, grid, stream); break;
     case EPI_ACT_SQ: launch_major<BN, EPI_ACT_SQ>(a, ma, mb, mx, p, grid, stream); break;
     case EPI_MUL_ACTGRAD: launch_major<BN, EPI_MUL_ACTGRAD>(a, ma, mb, mx, p, grid, stream); break;
+    case EPI_QKV_NORM_ROPE:
+      if (!(a.a_kmajor && a.b_kmajor)) throw std::runtime_error("gemm: the QKV epilogue takes row-major activations and [N][K] weights");
+      launch_variant<BN, true, true, EPI_QKV_NORM_ROPE>(ma, mb, mx, p, grid, stream);
+      break;
     default: throw std::runtime_error("gemm: unknown epilogue");
   }
 }
@@ -642,6 +745,21 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   }
   if ((a.seg_rows[0] > 0 || a.seg_rows[1] > 0) && !(a.epi == EPI_F32 || a.epi == EPI_F32_ATOMIC))
     throw std::runtime_error("gemm: row segments need an fp32 epilogue");
+  p.rope_cos = a.rope_cos;
+  p.rope_sin = a.rope_sin;
+  p.head_gain = a.head_gain;
+  p.q_heads = a.q_heads;
+  p.qk_heads = a.q_heads + a.kv_heads;
+  p.rope_half = a.rope_dims / 2;
+  p.seq_len = a.seq_len;
+  p.norm_eps = a.norm_eps;
+  if (a.epi == EPI_QKV_NORM_ROPE) {
+    const bool rope_ok = a.rope_dims == 0 || ((a.rope_dims == 16 || a.rope_dims == 32 || a.rope_dims == 64) && a.rope_cos && a.rope_sin &&
+                                              (reinterpret_cast<uintptr_t>(a.rope_cos) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.rope_sin) & 15) == 0);
+    if (a.batch != 1 || a.D2 == nullptr || a.N != (a.q_heads + 2 * a.kv_heads) * 64 || a.seq_len <= 0 || !rope_ok || (a.ldd % 8) ||
+        (reinterpret_cast<uintptr_t>(a.D) & 15) || (reinterpret_cast<uintptr_t>(a.D2) & 15))
+      throw std::runtime_error("gemm: the QKV epilogue needs heads of 64, rope_dims in {0,16,32,64}, 16-byte aligned outputs of one row pitch and a sequence length");
+  }
   const CUtensorMap ma = operand_map(a.A, a.a_kmajor, a.M, a.K, a.lda, a.stride_a, a.batch, BM);
   const CUtensorMap mb = operand_map(a.B, a.b_kmajor, a.N, a.K, a.ldb, a.stride_b, a.batch, bn);
   const int total = p.tiles_m * p.tiles_n * p.splits * a.batch;

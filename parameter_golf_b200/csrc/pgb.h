@@ -18,6 +18,8 @@ enum GemmEpilogue : int {
   EPI_RESID_BF16 = 4,   // D = bf16(aux + colscale[n] * acc)    (residual add with per-feature scale)
   EPI_ACT_SQ = 5,       // D = bf16(acc), D2 = bf16(leaky_relu(acc, slope)^2)
   EPI_MUL_ACTGRAD = 6,  // D = bf16(acc * d/dh leaky_relu(h, slope)^2), h = aux
+  EPI_QKV_NORM_ROPE = 7,  // D = bf16(acc) and, for the query and key heads (64 columns each), D2 = gain_h * rope(rms_norm(D)):
+                          // the QKV projection with per-head RMSNorm, partial RoPE and the query gain in its output stage
 };
 
 struct GemmArgs {
@@ -44,6 +46,13 @@ struct GemmArgs {
   // (alpha and beta both), so a Newton-Schulz iteration can start from an un-normalised matrix
   const float* batch_sumsq = nullptr;
   int sumsq_pow = 1;
+  // EPI_QKV_NORM_ROPE: columns are [q_heads | kv_heads | kv_heads] heads of 64; cos/sin tables [seq_len][rope_dims / 2];
+  // row m is position m % seq_len; head_gain (q_heads floats) may be null; rope_dims in {0, 16, 32, 64}
+  const float* rope_cos = nullptr;
+  const float* rope_sin = nullptr;
+  const float* head_gain = nullptr;
+  int q_heads = 0, kv_heads = 0, rope_dims = 0, seq_len = 0;
+  float norm_eps = 0.f;
 };
 
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);

@@ -471,6 +471,10 @@ class CudaEngine:
         li = self.act_slot[j] if self.train else 0
         s_l = gpt.layer_ln_scale(m, l)
         C.mix_norm_fwd(x, self.x0, skip, sw, p["resid_mix"][l], self.x_in[li], self.h[li], s_l, self.eps)
+        # Per-head RMSNorm, partial RoPE and the query gain run in the output stage of the QKV product unless something has to
+        # touch the raw queries first (a Q-LoRA adapter) or the shape is outside what that stage handles.
+        fused_qk = self.lora is None and N.qkv_epilogue_supported(self.hd, m.rope_dims)
+        wait = {}
         if self.layer_flags is not None and not recompute:
             if self.layer_wait_needed:
                 # First forward after a sharded update: the layer's weights may still be on their way (this rank's own
@@ -479,16 +483,20 @@ class CudaEngine:
                 C.comm_wait_flag(self.layer_flags[l:l + 1], self.layer_flag_value, N.status_word(self.dev))
                 if l == self.n - 1:
                     self.layer_wait_needed = False
-            N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li], wait_flag=self.layer_flags[l:l + 1], wait_value=self.layer_flag_value)
+            wait = dict(wait_flag=self.layer_flags[l:l + 1], wait_value=self.layer_flag_value)
+        if fused_qk:
+            N.gemm_qkv_norm_rope(self.h[li], self.Wqkv[l], self.qkv_pre[li], self.qk_post[li], self.cos, self.sin, p["q_gain"][l], self.H, self.Hkv,
+                                 m.rope_dims, S, self.eps, **wait)
         else:
-            N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li])
+            N.gemm(self.h[li], self.Wqkv[l], self.qkv_pre[li], **wait)
         if m.value_embedding.enabled and l in m.value_embedding.layers:
             vi = m.value_embedding.layers.index(l)
             vview = self.qkv_pre[li][:, d + kv:]
             N.gemm(self.ve_e, self.VP[vi], vview, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=vview)
         if self.lora is not None:
             self._lora_fwd(l, li)
-        C.qk_norm_rope_fwd(self.qkv_pre[li], self.qk_post[li], self.cos, self.sin, p["q_gain"][l], self.H, self.Hkv, self.hd, m.rope_dims, S, self.eps)
+        if not fused_qk:
+            C.qk_norm_rope_fwd(self.qkv_pre[li], self.qk_post[li], self.cos, self.sin, p["q_gain"][l], self.H, self.Hkv, self.hd, m.rope_dims, S, self.eps)
         self._attn_fwd(l, li)
         zz = self.z[li] if l in m.xsa_layers() else self.y[li]
         for gi, (wname, bname, gscale_, gmult) in enumerate(self.gates):

@@ -143,6 +143,18 @@ def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.
     return D
 
 
+def gemm_qkv_norm_rope(h, W, pre, post, cos, sin, gain, H, Hkv, rope_dims, seq_len, eps, wait_flag=None, wait_value=0):
+    """QKV projection whose output stage also applies the per-head RMSNorm, the partial RoPE and the query gain: ``pre`` = h W^T
+    for all heads (the backward of the norm and the attention read it), ``post`` = the normalised, rotated, gain-scaled query
+    and key heads. Heads of 64; ``rope_dims`` in {0, 16, 32, 64}."""
+    load().gemm_qkv_norm_rope(h, W, pre, post, cos, sin, gain, H, Hkv, rope_dims, seq_len, eps, status_word(h.device), wait_flag, wait_value)
+    return post
+
+
+def qkv_epilogue_supported(hd, rope_dims):
+    return hd == 64 and rope_dims in (0, 16, 32, 64)
+
+
 def attn_fwd(q, k, v, y, B, S, H, Hkv, hd, lse=None, z=None, xsa_eps=1e-8):
     """Causal GQA attention forward; q/k/v are [B*S, heads*hd] (row-strided views allowed). Returns the side output [B, H, S] = -(log2-domain log-sum-exp), which `attn_bwd` consumes.
     With ``z`` the kernel also writes the exclusive-self-attention output z_h = y_h - (<y_h, v> / (|v|^2 + eps)) v from the

@@ -147,3 +147,39 @@ def test_gemm_producer_gives_up_on_a_weight_flag_nobody_sets_and_the_context_sur
     n.check_status()
     ref = A.float() @ W.float().t()
     assert (D.float() - ref).abs().max().item() < 0.02 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("T,d,H,Hkv,rope,S", [(1000, 512, 8, 4, 16, 250), (384, 128, 2, 1, 16, 128), (257, 192, 1, 1, 0, 257), (640, 256, 4, 4, 64, 128),
+                                              (300, 128, 2, 2, 32, 100)])
+def test_qkv_product_with_norm_rope_and_gain_in_its_output_stage(T, d, H, Hkv, rope, S):
+    """pre = h W^T and post = gain * rope(rms_norm(pre)) from one kernel, against the plain product followed by the row kernel,
+    and against the fp32 reference of the op."""
+    from parameter_golf_b200.ops import reference as R
+    n = _n()
+    C = n.load()
+    hd, eps = 64, 1e-6
+    N = (H + 2 * Hkv) * hd
+    h, W = _rand(T, d), _rand(N, d, scale=d ** -0.5)
+    gain = torch.rand(H, device="cuda") + 0.75
+    cos = sin = None
+    if rope:
+        cos, sin = R.rope_tables(S, rope, 10000.0, device="cuda")
+        cos, sin = cos.contiguous(), sin.contiguous()
+    pre, post = torch.full((T, N), 7.0, device="cuda", dtype=torch.bfloat16), torch.full((T, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    n.gemm_qkv_norm_rope(h, W, pre, post, cos, sin, gain, H, Hkv, rope, S, eps)
+    pre2, post2 = torch.empty_like(pre), torch.full_like(post, 7.0)
+    n.gemm(h, W, pre2)
+    C.qk_norm_rope_fwd(pre2, post2, cos, sin, gain, H, Hkv, hd, rope, S, eps)
+    torch.cuda.synchronize()
+    n.check_status()
+    assert torch.equal(pre, pre2)
+    qk = (H + Hkv) * hd
+    assert torch.equal(post[:, qk:], torch.full_like(post[:, qk:], 7.0))            # the value columns of post are not touched
+    assert (post[:, :qk].float() - post2[:, :qk].float()).abs().max() < 0.02
+    if T % S == 0:
+        B = T // S
+        qf = pre[:, :H * hd].float().reshape(B, S, H, hd)
+        kf = pre[:, H * hd:qk].float().reshape(B, S, Hkv, hd)
+        q_ref, k_ref = R.qk_norm_rope_gain(qf, kf, cos, sin, rope, gain, eps)
+        _close(post[:, :H * hd], q_ref.reshape(T, H * hd))
+        _close(post[:, H * hd:qk], k_ref.reshape(T, Hkv * hd))

@@ -97,7 +97,7 @@ std::string write_pgrs(const std::vector<PgrsTensor>& tensors, const std::string
   put_u32(out, 1);
   put_u32(out, (uint32_t)tensors.size());
   for (const auto& t : tensors) {
-    if (t.dtype > 6) throw std::runtime_error("write_pgrs: unknown dtype code");
+    if (t.dtype > 7) throw std::runtime_error("write_pgrs: unknown dtype code");
     put_u32(out, (uint32_t)t.name.size());
     out.append(t.name);
     put_u32(out, (uint32_t)t.dims.size());
@@ -136,7 +136,7 @@ std::vector<PgrsTensor> read_pgrs(const std::string& buf, std::string* metadata)
     if (nd > 8) throw std::runtime_error("tensor " + t.name + ": too many dimensions");
     for (uint32_t k = 0; k < nd; ++k) t.dims.push_back(u32());
     t.dtype = (uint8_t)*take(1);
-    if (t.dtype > 6) throw std::runtime_error("tensor " + t.name + ": unknown dtype code " + std::to_string((int)t.dtype));
+    if (t.dtype > 7) throw std::runtime_error("tensor " + t.name + ": unknown dtype code " + std::to_string((int)t.dtype));
     const uint32_t dl = u32();
     t.data.assign(take(dl), dl);
     const uint32_t crc = u32();

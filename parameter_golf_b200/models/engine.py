@@ -296,7 +296,7 @@ class CudaEngine:
         self.nll = buf(T, dtype=torch.float32)
         rd = m.rope_dims
         if rd > 0:
-            cos, sin = R.rope_tables(self.S, rd, m.rope.base, train_seq_len=1024)
+            cos, sin = R.model_rope_tables(m, self.S)
             self.cos, self.sin = cos.contiguous().to(dev), sin.contiguous().to(dev)
         else:
             self.cos = self.sin = None

@@ -24,6 +24,7 @@ from ..spec import ModelSpec
 
 BANKS = ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank")
 EMBEDS = ("tok_emb", "bigram_embed", "ve_embed", "lm_head")
+TRAIN_ONLY = ("mtp_heads",)          # never exported (records/.../2026-03-23_.../train_gpt.py:1778)
 
 
 def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
@@ -61,6 +62,10 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
         sh["sparse_attn_gate_weight"] = (n, H, m.sparse_attn_gate.width)
     if not m.tie_embeddings:
         sh["lm_head"] = (m.vocab_size, d)
+    if m.value_residual:
+        sh["vr_lambda"] = (n, 2)
+    if m.mtp_num_heads > 0:
+        sh["mtp_heads"] = (m.mtp_num_heads, m.vocab_size, d)
     return sh
 
 
@@ -103,6 +108,8 @@ def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float3
         p["ve_layer_scales"].fill_(1.0)
     if "attn_gate_bias" in p:
         p["attn_gate_bias"].fill_(4.0)
+    if "vr_lambda" in p:
+        p["vr_lambda"].fill_(0.5)
     return {k: v.to(device=device, dtype=dtype) for k, v in p.items()}
 
 
@@ -118,6 +125,8 @@ def fill_deterministic(m: ModelSpec, device="cpu", dtype=torch.float32) -> Dict[
         fan_in = shape[-1] if len(shape) >= 2 else 1
         amp = {"tok_emb": 0.3, "bigram_embed": 0.3, "ve_embed": 0.3}.get(name, 1.0 / math.sqrt(fan_in) if len(shape) >= 2 else 0.2)
         v = amp * torch.sin(0.37 * i + 1.3 * t + 0.11 * (i % 97))
+        if name == "vr_lambda":
+            v = 0.5 + 0.2 * v / amp * 0.2
         if name in ("attn_scale", "mlp_scale", "skip_weights", "q_gain"):
             v = 1.0 + 0.25 * v / amp * 0.2
         if name == "resid_mix":
@@ -130,6 +139,12 @@ def fill_deterministic(m: ModelSpec, device="cpu", dtype=torch.float32) -> Dict[
             v = torch.full(shape, 0.8, dtype=torch.float64)
         p[name] = v.reshape(shape).to(device=device, dtype=dtype)
     return p
+
+
+def _small(m: ModelSpec, p, name: str, qat: bool):
+    """A small 2-D float tensor as the forward sees it: through the FP8 round trip while QAT is on and the spec stores it so."""
+    w = p[name]
+    return R.fake_quant_fp8_ste(w) if (qat and m.fp8_qat) else w
 
 
 def layer_ln_scale(m: ModelSpec, layer: int) -> float:
@@ -146,7 +161,11 @@ def layer_schedule(m: ModelSpec):
     return order
 
 
-def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = False, lora=None, return_kv: bool = False, taps=None):
+def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = False, lora=None, return_kv: bool = False, taps=None, v0=None,
+                  return_raw_v: bool = False):
+    """One block. ``v0`` / ``return_raw_v`` serve the value residual (records/.../2026-03-23_.../train_gpt.py:655-658): the
+    block's own value projection is handed back, and when an earlier layer's is given the attention runs on
+    ``lambda_0 * v0 + lambda_1 * v``."""
     n, H, Hkv, D = m.num_layers, m.num_heads, m.num_kv_heads, m.head_dim
     B, T, d = x.shape
     dt = x.dtype
@@ -170,11 +189,15 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
     v = F.linear(h, wv.to(dt))
     if m.value_embedding.enabled and i in m.value_embedding.layers:
         li = m.value_embedding.layers.index(i)
-        ve = F.linear(p["ve_embed"][ids].to(dt), p["ve_proj"].to(dt))
+        ve = F.linear(_small(m, p, "ve_embed", qat)[ids].to(dt), _small(m, p, "ve_proj", qat).to(dt))
         v = v + (p["ve_layer_scales"][li] * p["ve_scale"][0]).to(dt) * ve
     q = q.reshape(B, T, H, D)
     k = k.reshape(B, T, Hkv, D)
     v = v.reshape(B, T, Hkv, D)
+    raw_v = v
+    if m.value_residual and v0 is not None:
+        lam = p["vr_lambda"][i].to(dt)
+        v = lam[0] * v0 + lam[1] * v
     q, k = R.qk_norm_rope_gain(q, k, cos, sin, m.rope_dims, p["q_gain"][i])
     y = R.causal_gqa_attention(q, k, v)
     if i in m.xsa_layers():
@@ -196,6 +219,8 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
     out = x_mid + p["mlp_scale"][i].to(dt)[None, None, :] * F.linear(hid, wd.to(dt))
     if return_kv:
         return out, (k, v)
+    if return_raw_v:
+        return out, raw_v
     return out
 
 
@@ -205,25 +230,31 @@ def gpt_hidden(m: ModelSpec, p, ids: torch.Tensor, qat: bool = False, lora=None,
     B, T = ids.shape
     x = p["tok_emb"][ids].to(dt)
     if m.bigram.enabled:
-        bg = p["bigram_embed"][R.bigram_hash(ids, m.bigram.vocab_size)].to(dt)
+        bg = _small(m, p, "bigram_embed", qat)[R.bigram_hash(ids, m.bigram.vocab_size)].to(dt)
         if "bigram_proj" in p:
-            bg = F.linear(bg, p["bigram_proj"].to(dt))
+            bg = F.linear(bg, _small(m, p, "bigram_proj", qat).to(dt))
         x = x + p["bigram_scale"][0].to(dt) * bg
     x = R.rms_norm(x)
     if m.smear_gate:
         x = R.smear_gate(x, p["smear_gate"], ids, m.smear_gate_boundary_token_id)
     x0 = x
     rd = m.rope_dims
-    cos, sin = R.rope_tables(T, rd, m.rope.base, train_seq_len=1024, device=ids.device) if rd > 0 else (None, None)
+    cos, sin = R.model_rope_tables(m, T, device=ids.device)
     enc = m.num_layers // 2
     unet = m.skip_topology == "unet" and "skip_weights" in p
     skips = []
     sched = layer_schedule(m)
+    v0 = None
     for j, (i, rep) in enumerate(sched):
         last_pass = j + 1 == len(sched) or sched[j + 1][0] != i
         if unet and i >= enc and rep == 0 and skips:
             x = x + p["skip_weights"][i - enc].to(dt)[None, None, :] * skips.pop()
-        x = block_forward(m, p, i, x, x0, ids, cos, sin, qat=qat, lora=lora, taps=taps)
+        if m.value_residual:
+            x, raw_v = block_forward(m, p, i, x, x0, ids, cos, sin, qat=qat, lora=lora, taps=taps, v0=v0, return_raw_v=True)
+            if v0 is None:
+                v0 = raw_v                  # the first block's values, mixed into every later block's
+        else:
+            x = block_forward(m, p, i, x, x0, ids, cos, sin, qat=qat, lora=lora, taps=taps)
         if unet and i < enc and last_pass:
             skips.append(x)
     return R.rms_norm(x)
@@ -237,18 +268,42 @@ def gpt_logits(m: ModelSpec, p, ids, qat: bool = False, lora=None, dtype=None):
     return m.logit_softcap * torch.tanh(z.float() / m.logit_softcap)
 
 
-def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dtype=None, reduction: str = "mean", token_weights=None):
+def mtp_loss(m: ModelSpec, p, h, targets):
+    """Mean over the extra heads of the soft-capped cross-entropy of head k (on the final hidden state of position t) against
+    the token k + 2 positions ahead, i.e. ``targets[:, t + k + 1]`` (records/.../2026-03-23_.../train_gpt.py:947-962)."""
+    T = h.shape[1]
+    total, count = None, 0
+    for k in range(m.mtp_num_heads):
+        valid = T - (k + 1)
+        if valid <= 0:
+            continue
+        z = F.linear(h[:, :valid], p["mtp_heads"][k].to(h.dtype))
+        l = R.softcap_cross_entropy(z, targets[:, k + 1:], m.logit_softcap, reduction="mean")
+        total = l if total is None else total + l
+        count += 1
+    return None if count == 0 else total / count
+
+
+def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dtype=None, reduction: str = "mean", token_weights=None,
+                mtp: bool = False):
     """Training loss: mean soft-capped cross-entropy over all tokens (``reduction='none'`` gives the
     per-token losses [B,T]). With ``token_weights`` (same shape as ``targets``) the mean is weighted and normalised
-    by the sum of the weights (complementary training, ``pg-kernels/src/complementary.rs:226-240``)."""
+    by the sum of the weights (complementary training, ``pg-kernels/src/complementary.rs:226-240``). ``mtp`` (training steps
+    only) adds ``mtp_loss_weight`` times the multi-token-prediction loss of the extra heads."""
     h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
-    w = p["tok_emb"] if m.tie_embeddings else p["lm_head"]
+    w = p["tok_emb"] if m.tie_embeddings else _small(m, p, "lm_head", qat)
     z = F.linear(h, w.to(h.dtype))
+    extra = None
+    if mtp and reduction == "mean" and m.mtp_num_heads > 0 and m.mtp_loss_weight > 0.0 and "mtp_heads" in p:
+        extra = mtp_loss(m, p, h, targets)
     if token_weights is not None and reduction == "mean":
         per = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction="none").reshape(-1).float()
         tw = token_weights.reshape(-1).to(per.dtype)
-        return (per * tw).sum() / tw.sum().clamp_min(1e-12)
+        loss = (per * tw).sum() / tw.sum().clamp_min(1e-12)
+        return loss if extra is None else loss + m.mtp_loss_weight * extra
     loss = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction=reduction)
+    if extra is not None:
+        loss = loss + m.mtp_loss_weight * extra
     return loss.reshape(ids.shape) if reduction == "none" else loss
 
 

@@ -28,16 +28,39 @@ def rms_norm(x: torch.Tensor, scale: float = 1.0, eps: float = RMS_EPS) -> torch
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * scale).to(x.dtype)
 
 
-def rope_tables(seq_len: int, rope_dims: int, base: float = 10000.0, train_seq_len: int = 0, device=None):
+def rope_tables(seq_len: int, rope_dims: int, base: float = 10000.0, train_seq_len: int = 0, device=None, yarn_max_len: int = 0):
     """cos/sin tables of shape [seq_len, rope_dims/2], ``theta = pos / base^(2i/rope_dims)``
     (``pg-kernels/src/rope.rs:13-28``). When ``seq_len > train_seq_len > 0`` the base is rescaled
-    NTK-style (``records/.../2026-03-23_.../train_gpt.py:578-584``)."""
+    NTK-style (``records/.../2026-03-23_.../train_gpt.py:578-584``).
+
+    ``yarn_max_len`` > 0 selects the YaRN-style frequency ramp of the ternary record instead
+    (``records/track_10min_16mb/2026-03-24_74M_Ternary_.../train_gpt_cuda_ternary.py:570-575``): with
+    ``scale = train_seq_len / yarn_max_len`` the low-frequency pairs (the last three quarters of the index range,
+    linearly ramped) are slowed down by up to ``1 / scale``; the base is left alone."""
     rd = rope_dims
-    if train_seq_len and seq_len > train_seq_len and rd > 2:
-        base = base * ((seq_len / train_seq_len) ** (rd / (rd - 2)))
-    inv = 1.0 / (base ** (torch.arange(0, rd, 2, dtype=torch.float32, device=device) / rd))
+    idx = torch.arange(0, rd, 2, dtype=torch.float32, device=device)
+    if yarn_max_len > 0:
+        inv = 1.0 / (base ** (idx / rd))
+        scale = (train_seq_len or seq_len) / yarn_max_len
+        ramp = torch.clamp((idx / rd - 0.25) / 0.75, 0.0, 1.0)
+        inv = inv / (ramp * (1.0 / scale - 1.0) + 1.0)
+    else:
+        if train_seq_len and seq_len > train_seq_len and rd > 2:
+            base = base * ((seq_len / train_seq_len) ** (rd / (rd - 2)))
+        inv = 1.0 / (base ** (idx / rd))
     fr = torch.outer(torch.arange(seq_len, dtype=torch.float32, device=device), inv)
     return fr.cos(), fr.sin()
+
+
+def model_rope_tables(m, seq_len: int, device=None):
+    """The tables a model spec asks for (``m`` is a `ModelSpec`): partial or full rotary with the NTK rescale beyond 1024
+    positions, or the YaRN ramp when ``rope.mode == "yarn"``. ``(None, None)`` without rotary dims."""
+    rd = m.rope_dims
+    if rd <= 0:
+        return None, None
+    if m.rope.mode == "yarn":
+        return rope_tables(seq_len, rd, m.rope.base, train_seq_len=m.rope.yarn_train_len, device=device, yarn_max_len=m.rope.yarn_max_len)
+    return rope_tables(seq_len, rd, m.rope.base, train_seq_len=1024, device=device)
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rope_dims: int) -> torch.Tensor:
@@ -133,6 +156,15 @@ def softcap_cross_entropy(logits, targets, cap: float, reduction: str = "mean"):
     """``CE(cap * tanh(z / cap))`` in fp32 (``pg-kernels/src/cross_entropy.rs``)."""
     c = cap * torch.tanh(_f(logits) / cap)
     return F.cross_entropy(c.reshape(-1, c.shape[-1]), targets.reshape(-1), reduction=reduction)
+
+
+def fake_quant_fp8_ste(w: torch.Tensor) -> torch.Tensor:
+    """Straight-through estimator of FP8 (e4m3) storage: forward uses the value after a round trip through
+    ``float8_e4m3fn``, the gradient passes to ``w``
+    (``records/track_10min_16mb/2026-03-24_74M_Ternary_.../train_gpt_cuda_ternary.py:418-431``)."""
+    with torch.no_grad():
+        wq = _f(w).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).to(w.dtype)
+    return w + (wq - w).detach()
 
 
 def fake_quant_int6_ste(w: torch.Tensor) -> torch.Tensor:

@@ -29,7 +29,7 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
     g = torch.Generator(device=device).manual_seed(seed)
     n, H, Hkv, D, d = m.num_layers, m.num_heads, m.num_kv_heads, m.head_dim, m.model_dim
     rd = m.rope_dims
-    cos, sin = R.rope_tables(seq_len, rd, m.rope.base, train_seq_len=1024, device=device) if rd > 0 else (None, None)
+    cos, sin = R.model_rope_tables(m, seq_len, device=device)
     toks = torch.zeros(num_seqs, seq_len, dtype=torch.int64, device=device)
     toks[:, 0] = torch.randint(0, m.vocab_size, (num_seqs,), generator=g, device=device)
     kc = [torch.zeros(num_seqs, seq_len, Hkv, D, device=device, dtype=dtype) for _ in range(n)]
@@ -64,6 +64,7 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
             x = x_new
         x0 = x
         skips = []
+        v0 = None
         for i in range(n):
             if unet and i >= enc and skips:
                 x = x + p["skip_weights"][i - enc].to(dtype)[None, :] * skips.pop()
@@ -78,6 +79,12 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
                 li = m.value_embedding.layers.index(i)
                 v = v + (p["ve_layer_scales"][li] * p["ve_scale"][0]).to(dtype) * F.linear(p["ve_embed"][ids].to(dtype), p["ve_proj"].to(dtype))
             v = v.reshape(num_seqs, 1, Hkv, D)
+            if m.value_residual:
+                if v0 is None:
+                    v0 = v
+                else:
+                    lam = p["vr_lambda"][i].to(dtype)
+                    v = lam[0] * v0 + lam[1] * v
             q = R.rms_norm(q)
             k = R.rms_norm(k)
             if rd > 0:

@@ -24,9 +24,9 @@ from typing import List, Tuple
 
 import numpy as np
 
-DTYPE_CODES = {"bf16": 0, "f16": 1, "f32": 2, "i8": 3, "i32": 4, "u16": 5, "u32": 6}
+DTYPE_CODES = {"bf16": 0, "f16": 1, "f32": 2, "i8": 3, "i32": 4, "u16": 5, "u32": 6, "f8e4m3": 7}
 CODE_NAMES = {v: k for k, v in DTYPE_CODES.items()}
-DTYPE_SIZES = {"bf16": 2, "f16": 2, "f32": 4, "i8": 1, "i32": 4, "u16": 2, "u32": 4}
+DTYPE_SIZES = {"bf16": 2, "f16": 2, "f32": 4, "i8": 1, "i32": 4, "u16": 2, "u32": 4, "f8e4m3": 1}
 DEFAULT_CHUNK_BYTES = 1 << 20
 
 

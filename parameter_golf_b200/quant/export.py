@@ -32,6 +32,15 @@ def _f16(name, t) -> C.TensorRecord:
     return C.TensorRecord(name, tuple(a.shape), "f16", a.tobytes())
 
 
+def _flt(name, t, storage: str) -> C.TensorRecord:
+    """A 2-D float tensor in the artifact's float storage: f16, or FP8 e4m3 at one byte per element (the ternary record's
+    choice for everything it does not code, train_gpt_cuda_ternary.py:218-221)."""
+    if storage != "fp8" or t.ndim != 2:
+        return _f16(name, t)
+    a = t.detach().cpu().float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    return C.TensorRecord(name, tuple(a.shape), "f8e4m3", a.tobytes())
+
+
 def _f32(name, t) -> C.TensorRecord:
     a = t.detach().cpu().float().numpy().astype("<f4")
     return C.TensorRecord(name, tuple(a.shape), "f32", a.tobytes())
@@ -97,9 +106,13 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
         recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", _store_codes(q, bits[g], spec.quant.code_storage)))
         recs.append(_f16(f"{g}.scale", s16))
     if m.bigram.enabled:
-        recs.append(_f16("bigram_embed", params["bigram_embed"].reshape(-1)))
+        fs = spec.quant.float_storage
+        if fs == "fp8":
+            recs.append(_flt("bigram_embed", params["bigram_embed"], fs))
+        else:
+            recs.append(_f16("bigram_embed", params["bigram_embed"].reshape(-1)))
         if "bigram_proj" in params:
-            recs.append(_f16("bigram_proj", params["bigram_proj"].reshape(-1)))
+            recs.append(_flt("bigram_proj", params["bigram_proj"], fs) if fs == "fp8" else _f16("bigram_proj", params["bigram_proj"].reshape(-1)))
         recs.append(_f32("bigram_scale", params["bigram_scale"].reshape(1)))
     if "smear_gate" in params:
         recs.append(_f16("smear_gate", params["smear_gate"]))
@@ -113,13 +126,16 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
             recs.append(_f16(f"blocks.{i}.attn_gate_bias", params["attn_gate_bias"][i]))
         if m.sparse_attn_gate.enabled:
             recs.append(_f16(f"blocks.{i}.sparse_attn_gate_weight", params["sparse_attn_gate_weight"][i]))
+        if m.value_residual:
+            recs.append(_f16(f"blocks.{i}.vr_lambda", params["vr_lambda"][i]))
+    # the multi-token-prediction heads are training-only and are left out (records/.../2026-03-23_.../train_gpt.py:1778)
     if m.value_embedding.enabled:
-        recs.append(_f16("ve_embed", params["ve_embed"]))
-        recs.append(_f16("ve_proj", params["ve_proj"]))
+        recs.append(_flt("ve_embed", params["ve_embed"], spec.quant.float_storage))
+        recs.append(_flt("ve_proj", params["ve_proj"], spec.quant.float_storage))
         recs.append(_f32("ve_scale", params["ve_scale"].reshape(1)))
         recs.append(_f16("ve_layer_scales", params["ve_layer_scales"]))
     if not m.tie_embeddings:
-        recs.append(_f16("lm_head", params["lm_head"]))
+        recs.append(_flt("lm_head", params["lm_head"], spec.quant.float_storage))
     return C.write_pgrs(recs, metadata_json(spec, bits))
 
 
@@ -176,6 +192,9 @@ def export_model(spec: RunSpec, params: Dict[str, torch.Tensor], path: Optional[
 
 def _np(rec: C.TensorRecord) -> np.ndarray:
     dt = {"f16": "<f2", "f32": "<f4", "i32": "<i4", "u16": "<u2", "u32": "<u4", "i8": "i1"}.get(rec.dtype)
+    if rec.dtype == "f8e4m3":
+        raw = torch.frombuffer(bytearray(rec.data), dtype=torch.uint8).view(torch.float8_e4m3fn)
+        return raw.float().numpy().reshape(rec.dims)
     if rec.dtype == "bf16":
         u = np.frombuffer(rec.data, dtype="<u2").astype(np.uint32) << 16
         return u.view(np.float32).reshape(rec.dims)
@@ -243,7 +262,7 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
             if name not in by:
                 raise C.ArtifactError(f"artifact is missing tensor {name}")
             p[name] = torch.from_numpy(_np(by[name]).astype(np.float32)).reshape(shapes[name])
-    for k in ("attn_scale", "mlp_scale", "resid_mix", "q_gain", "attn_gate_weight", "attn_gate_bias", "sparse_attn_gate_weight"):
+    for k in ("attn_scale", "mlp_scale", "resid_mix", "q_gain", "attn_gate_weight", "attn_gate_bias", "sparse_attn_gate_weight", "vr_lambda"):
         if k in shapes:
             p[k] = torch.stack([torch.from_numpy(_np(by[f"blocks.{i}.{k}"]).astype(np.float32)) for i in range(n)]).reshape(shapes[k])
     return {k: v.to(device=device, dtype=dtype) for k, v in p.items()}

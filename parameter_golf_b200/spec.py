@@ -49,9 +49,11 @@ class BigramSpec:
 
 @dataclass
 class RopeSpec:
-    mode: str = "partial"          # none | partial | yarn (yarn is declared and rejected)
+    mode: str = "partial"          # none | partial | yarn
     dims: int = 16                 # 0 or head_dim => full rotary
     base: float = 10000.0
+    yarn_max_len: int = 2048       # mode = yarn: the context the frequencies are stretched to (YARN_MAX_LEN) ...
+    yarn_train_len: int = 1024     # ... from this training length; low frequencies slow down by up to yarn_max_len / yarn_train_len
 
 
 @dataclass
@@ -117,6 +119,13 @@ class ModelSpec:
     tie_embeddings: bool = True
     tied_embed_init_std: float = 0.005
     compute_precision: str = "bf16_tensor_core"  # f32 (CPU oracle) | bf16_tensor_core
+    # Optional ideas of the Python records that their own runs leave off (train_gpt.py:70-92 of the 2026-03-23 record). They run on
+    # the autograd path (train.backend = cpu); the CUDA engine rejects them at validation.
+    value_residual: bool = False          # v <- lambda_0 * v(first layer) + lambda_1 * v in every later layer, lambda learned per layer
+    mtp_num_heads: int = 0                # extra output heads that predict the tokens 2, 3, ... ahead, training only, not exported
+    mtp_loss_weight: float = 0.2
+    fp8_qat: bool = False                 # while QAT is on, the small 2-D float tensors (bigram / value-embedding tables and
+                                          # projections, an untied head) go through an FP8 e4m3 round trip (FP_STORAGE=FP8)
 
     @property
     def head_dim(self) -> int:
@@ -226,6 +235,8 @@ class QuantSpec:
                                         # bytes: one int8 per code (the Python records' container: the entropy coder then sees the code distribution)
     prune_to_target: bool = True        # zero the cheapest +-1 codes until artifact + code fit target_artifact_bytes
     prune_max_magnitude: int = 1        # widen the candidates to |code| <= this when the +-1 codes are not enough
+    float_storage: str = "f16"          # f16 | fp8: how the 2-D float tensors that are not quantised to integer codes are stored
+                                        # (fp8 = e4m3, one byte per element; 1-D control tensors stay f16)
     matrix_bits: int = 6
     embed_bits: int = 8
     attn_gate_bits: int = 8
@@ -357,6 +368,8 @@ class RunSpec:
         if has("TIE_EMBEDDINGS"): m.tie_embeddings = B("TIE_EMBEDDINGS")
         if has("ROPE_BASE"): m.rope.base = F("ROPE_BASE")
         if has("ROPE_DIMS"): m.rope.dims = I("ROPE_DIMS")
+        if has("ROPE_TYPE"): m.rope.mode = "yarn" if env["ROPE_TYPE"].lower() == "yarn" else m.rope.mode
+        if has("YARN_MAX_LEN"): m.rope.yarn_max_len = I("YARN_MAX_LEN")
         if has("LOGIT_SOFTCAP"): m.logit_softcap = F("LOGIT_SOFTCAP")
         if has("EMBED_LR"): t.embed_lr = F("EMBED_LR")
         if has("HEAD_LR"): t.head_lr = F("HEAD_LR")
@@ -377,12 +390,19 @@ class RunSpec:
         if has("SWA_ENABLED"): t.swa_enabled = B("SWA_ENABLED")
         if has("SWA_EVERY"): t.swa_every = I("SWA_EVERY")
         if has("QAT_ENABLED"): t.qat_enabled = B("QAT_ENABLED")
+        if has("FP_STORAGE"):
+            fp8 = env["FP_STORAGE"].strip().upper() == "FP8"
+            q.float_storage = "fp8" if fp8 else "f16"
+            m.fp8_qat = fp8
         if has("LATE_QAT_THRESHOLD"): t.late_qat_threshold = F("LATE_QAT_THRESHOLD")
         if has("BIGRAM_VOCAB_SIZE"):
             m.bigram.vocab_size = I("BIGRAM_VOCAB_SIZE")
             m.bigram.enabled = m.bigram.vocab_size > 0
         if has("BIGRAM_DIM"): m.bigram.dim = I("BIGRAM_DIM")
         if has("XSA_LAST_N"): m.xsa_last_n = I("XSA_LAST_N")
+        if has("VALUE_RESIDUAL"): m.value_residual = B("VALUE_RESIDUAL")
+        if has("MTP_NUM_HEADS"): m.mtp_num_heads = I("MTP_NUM_HEADS")
+        if has("MTP_LOSS_WEIGHT"): m.mtp_loss_weight = F("MTP_LOSS_WEIGHT")
         if has("LN_SCALE"): m.ln_scale = B("LN_SCALE")
         if has("VE_ENABLED"): m.value_embedding.enabled = B("VE_ENABLED")
         if has("VE_DIM"): m.value_embedding.dim = I("VE_DIM")
@@ -426,7 +446,7 @@ class RunSpec:
         chk(t.muon_ns_profile in NS_PROFILES, f"train.muon_ns_profile must be one of {NS_PROFILES}")
         chk(m.activation in ("relu_sq", "leaky_relu_sq"), "model.activation must be relu_sq or leaky_relu_sq")
         chk(m.rope.mode in ("none", "partial", "yarn"), "unknown rope.mode")
-        chk(m.rope.mode != "yarn", "rope.mode=yarn is declared but not implemented")
+        chk(m.rope.mode != "yarn" or (m.rope.yarn_max_len > 0 and m.rope.yarn_train_len > 0), "rope.mode=yarn needs yarn_max_len and yarn_train_len > 0")
         chk(m.skip_topology in ("none", "unet"), "unknown skip_topology")
         chk(m.num_layers >= 1, "num_layers must be >= 1")
         chk(m.model_dim % m.num_heads == 0, "model_dim must be divisible by num_heads")
@@ -435,6 +455,10 @@ class RunSpec:
         chk(m.rope_dims % 2 == 0 and m.rope_dims <= m.head_dim, "rope.dims must be even and <= head_dim")
         chk(m.logit_softcap > 0, "logit_softcap must be positive")
         chk(m.xsa_last_n <= m.num_layers, "xsa_last_n exceeds num_layers")
+        chk(m.mtp_num_heads >= 0 and m.mtp_loss_weight >= 0.0, "mtp_num_heads and mtp_loss_weight must be >= 0")
+        chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat) or t.backend == "cpu",
+            "model.value_residual, model.mtp_num_heads and model.fp8_qat run on train.backend=cpu only (the CUDA engine has no path for them)")
+        chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
         chk(m.vocab_size <= 65536, "token ids are uint16: vocab_size must be <= 65536")
         chk(not (m.attn_out_gate.enabled and m.sparse_attn_gate.enabled),
             "attn_out_gate and sparse_attn_gate are mutually exclusive")

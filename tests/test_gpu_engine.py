@@ -31,7 +31,8 @@ def rel_err(a, b):
     return float((a.double().cpu() - b.double().cpu()).norm() / (b.double().cpu().norm() + 1e-12))
 
 
-@pytest.mark.parametrize("variant", ["record", "baseline", "ve", "recurrence", "parallel", "attn_gate", "sparse_gate", "parallel_gate", "untied"])
+@pytest.mark.parametrize("variant", ["record", "baseline", "ve", "recurrence", "parallel", "attn_gate", "sparse_gate", "parallel_gate", "untied", "yarn",
+                                     "full_rope"])
 def test_one_step_loss_and_gradients_match_oracle(variant):
     from parameter_golf_b200.models import gpt
     from parameter_golf_b200.models.engine import CudaEngine
@@ -52,6 +53,10 @@ def test_one_step_loss_and_gradients_match_oracle(variant):
         ov.update({"model.sparse_attn_gate.enabled": "true", "model.sparse_attn_gate.width": 12, "model.sparse_attn_gate.scale": 1.5})
     if variant == "untied":
         ov = {"model.tie_embeddings": "false"}
+    if variant == "yarn":                        # the frequency ramp only changes the tables the kernels are given
+        ov = {"model.rope.mode": "yarn", "model.rope.yarn_max_len": 4096, "model.rope.base": 5000.0}
+    if variant == "full_rope":                   # all 64 dims rotate: the widest rotary case of the QKV output stage
+        ov = {"model.rope.dims": 64}
     spec = small_spec(**ov)
     params = gpt.fill_deterministic(spec.model)
     torch.manual_seed(0)

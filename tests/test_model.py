@@ -124,3 +124,71 @@ def test_lora_with_zero_b_is_identity():
     ids = torch.randint(0, 32, (1, 8))
     lora = init_q_lora(m, 4, 4.0)
     assert torch.allclose(gpt.gpt_logits(m, p, ids, lora=lora), gpt.gpt_logits(m, p, ids), atol=1e-6)
+
+
+def test_value_residual_mixes_the_first_layers_values_into_later_layers():
+    """records/.../2026-03-23_.../train_gpt.py:655-658: layer 0 is unchanged; with lambda = (0, 1) the model is the plain one;
+    the lambdas get gradients and match a finite difference."""
+    m0, m1 = full_model(), full_model()
+    m1.value_residual = True
+    p1 = {k: v.double() for k, v in gpt.fill_deterministic(m1).items()}
+    assert p1["vr_lambda"].shape == (3, 2)
+    ids = torch.randint(0, 32, (2, 7))
+    tgt = torch.randint(0, 32, (2, 7))
+    p0 = {k: v for k, v in p1.items() if k != "vr_lambda"}
+    ident = dict(p1, vr_lambda=torch.tensor([[0.0, 1.0]] * 3, dtype=torch.float64))
+    assert torch.allclose(gpt.gpt_forward(m1, ident, ids, tgt), gpt.gpt_forward(m0, p0, ids, tgt), atol=1e-12)
+    assert abs(float(gpt.gpt_forward(m1, p1, ids, tgt)) - float(gpt.gpt_forward(m0, p0, ids, tgt))) > 1e-6
+    leaf = p1["vr_lambda"].clone().requires_grad_(True)
+    (g,) = torch.autograd.grad(gpt.gpt_forward(m1, dict(p1, vr_lambda=leaf), ids, tgt), leaf)
+    assert float(g[0].abs().max()) == 0.0                      # the first layer has nothing to mix with
+    for idx in ((1, 0), (2, 1)):
+        eps = 1e-6
+        pp, pm = p1["vr_lambda"].clone(), p1["vr_lambda"].clone()
+        pp[idx] += eps
+        pm[idx] -= eps
+        fd = (gpt.gpt_forward(m1, dict(p1, vr_lambda=pp), ids, tgt) - gpt.gpt_forward(m1, dict(p1, vr_lambda=pm), ids, tgt)) / (2 * eps)
+        assert abs(float(fd) - float(g[idx])) < 1e-4 * max(1.0, abs(float(fd)))
+
+
+def test_multi_token_prediction_heads_add_a_training_only_loss():
+    """records/.../2026-03-23_.../train_gpt.py:947-962: head k scores the token k + 2 ahead from the final hidden state; the
+    term is weighted, averaged over the heads and left out of evaluation."""
+    import torch.nn.functional as F
+    from parameter_golf_b200.ops import reference as R
+    m = full_model()
+    m.mtp_num_heads, m.mtp_loss_weight = 2, 0.3
+    p = {k: v.double() for k, v in gpt.fill_deterministic(m).items()}
+    assert p["mtp_heads"].shape == (2, 32, 16)
+    ids = torch.randint(0, 32, (2, 9))
+    tgt = torch.randint(0, 32, (2, 9))
+    base = gpt.gpt_forward(m, p, ids, tgt)
+    with_mtp = gpt.gpt_forward(m, p, ids, tgt, mtp=True)
+    h = gpt.gpt_hidden(m, p, ids)
+    want = 0.0
+    for k in range(2):
+        z = F.linear(h[:, :9 - (k + 1)], p["mtp_heads"][k])
+        want = want + R.softcap_cross_entropy(z, tgt[:, k + 1:], m.logit_softcap)
+    assert torch.allclose(with_mtp, base + 0.3 * want / 2, atol=1e-12)
+    assert gpt.gpt_forward(m, p, ids, tgt, reduction="none").shape == (2, 9)             # evaluation path: no extra term
+    leaf = p["mtp_heads"].clone().requires_grad_(True)
+    (g,) = torch.autograd.grad(gpt.gpt_forward(m, dict(p, mtp_heads=leaf), ids, tgt, mtp=True), leaf)
+    assert float(g[0].abs().max()) > 0 and float(g[1].abs().max()) > 0
+    assert gpt.init_params(m)["mtp_heads"].abs().max() == 0                                # zero-initialised heads
+
+
+@pytest.mark.parametrize("value_residual", [False, True])
+def test_cached_generation_follows_the_full_forward(value_residual):
+    """At a vanishing temperature the K/V-cached sampler must pick the arg-max of the full model's logits at every step."""
+    from parameter_golf_b200.quant.calibrate import generate_autoregressive
+    m = full_model()
+    m.value_residual = value_residual
+    p = gpt.fill_deterministic(m)
+    p["tok_emb"] = p["tok_emb"] * 4.0                           # wider logit margins than the fill pattern gives
+    toks = generate_autoregressive(m, p, num_seqs=3, seq_len=10, temperature=1e-4, seed=5)
+    logits = gpt.gpt_logits(m, p, toks)
+    top2 = logits.topk(2, dim=-1).values
+    decided = (top2[..., 0] - top2[..., 1]) > 1e-3              # skip near-ties, where fp32 summation order decides
+    pred = logits.argmax(-1)[:, :-1]
+    same = (pred == toks[:, 1:]) | ~decided[:, :-1]
+    assert bool(same.all()) and int(decided[:, :-1].sum()) >= 20

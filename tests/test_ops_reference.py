@@ -31,6 +31,27 @@ def test_rope_is_a_rotation_and_partial():
     _gc(lambda t: R.apply_rope(t, cos.double(), sin.double(), 4), x)
 
 
+def test_yarn_tables_slow_down_the_low_frequencies_only():
+    """The ramp of the ternary record (train_gpt_cuda_ternary.py:570-575): the first quarter of the frequency pairs is left
+    alone, the last one is slowed down by exactly yarn_max_len / train_seq_len, and the ones between are ramped linearly."""
+    rd, S = 16, 64
+    plain = R.rope_tables(S, rd, 5000.0)
+    yarn = R.rope_tables(S, rd, 5000.0, train_seq_len=1024, yarn_max_len=2048)
+    idx = torch.arange(0, rd, 2, dtype=torch.float32)
+    inv = 1.0 / (5000.0 ** (idx / rd))
+    ramp = torch.clamp((idx / rd - 0.25) / 0.75, 0.0, 1.0)
+    want = torch.outer(torch.arange(S, dtype=torch.float32), inv / (ramp * (2.0 - 1.0) + 1.0))
+    assert torch.allclose(yarn[0], want.cos(), atol=1e-6) and torch.allclose(yarn[1], want.sin(), atol=1e-6)
+    assert torch.equal(yarn[0][:, :2], plain[0][:, :2])             # index / rd <= 0.25: untouched
+    assert not torch.allclose(yarn[0][:, -1], plain[0][:, -1])
+    # through the model spec
+    from parameter_golf_b200.spec import family_preset
+    m = family_preset("tiny_cpu").apply_overrides(["model.rope.mode=yarn", "model.rope.yarn_max_len=4096"]).validate().model
+    c, s_ = R.model_rope_tables(m, 32)
+    c2, s2 = R.rope_tables(32, m.rope_dims, m.rope.base, train_seq_len=1024, yarn_max_len=4096)
+    assert torch.equal(c, c2) and torch.equal(s_, s2)
+
+
 def test_rope_ntk_rescale_only_beyond_train_len():
     a = R.rope_tables(16, 8, 10000.0, train_seq_len=16)[0]
     b = R.rope_tables(16, 8, 10000.0, train_seq_len=0)[0]

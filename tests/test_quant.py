@@ -334,3 +334,51 @@ def test_byte_per_code_storage_round_trips_and_prune_to_target_meets_the_budget(
     pruned = E.load_artifact(small, spec)
     changed = sum(int((pruned[k] != loaded[k]).sum()) for k in ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank"))
     assert 0 < changed and torch.equal(pruned["tok_emb"], loaded["tok_emb"])          # only matrix codes of magnitude one were dropped
+
+
+def test_fp8_float_storage_round_trips_and_halves_the_float_tables():
+    """quant.float_storage = fp8: the 2-D float tensors that are not coded (bigram and value-embedding tables, projections)
+    are stored as e4m3 bytes and come back as the e4m3-rounded values; 1-D control tensors stay f16."""
+    from parameter_golf_b200.quant import container as Cn
+    from parameter_golf_b200.quant.export import build_artifact
+    s = family_preset("tiny_cpu")
+    s.model.bigram.enabled, s.model.bigram.vocab_size, s.model.bigram.dim = True, 64, 32
+    s.model.value_embedding.enabled, s.model.value_embedding.dim, s.model.value_embedding.layers = True, 32, [1]
+    s.validate()
+    p = gpt.fill_deterministic(s.model)
+    a16 = build_artifact(s, p)
+    s.quant.float_storage = "fp8"
+    s.validate()
+    a8 = build_artifact(s, p)
+    recs = {r.name: r for r in Cn.read_pgrs(a8)[0]}
+    assert recs["bigram_embed"].dtype == "f8e4m3" and len(recs["bigram_embed"].data) == 64 * 32
+    assert recs["ve_proj"].dtype == "f8e4m3" and recs["smear_gate"].dtype == "f16" if "smear_gate" in recs else True
+    assert len(a8) < len(a16)
+    back = load_artifact(a8, s)
+    for k in ("bigram_embed", "bigram_proj", "ve_embed", "ve_proj"):
+        want = p[k].clamp(-448, 448).to(torch.float8_e4m3fn).float()
+        assert torch.equal(back[k], want), k
+    # the python reader agrees with the native one on the new dtype code
+    assert [(r.name, r.dtype, r.data) for r in Cn.read_pgrs(a8, native=False)[0]] == [(r.name, r.dtype, r.data) for r in Cn.read_pgrs(a8)[0]]
+
+
+def test_fp8_qat_forward_uses_the_rounded_tables_and_passes_gradients_straight_through():
+    from parameter_golf_b200.ops import reference as R
+    s = family_preset("tiny_cpu")
+    s.model.bigram.enabled, s.model.bigram.vocab_size, s.model.bigram.dim = True, 64, 32
+    s.model.fp8_qat = True
+    s.quant.float_storage = "fp8"
+    s.validate()
+    m = s.model
+    p = gpt.fill_deterministic(m)
+    ids = torch.randint(0, m.vocab_size, (2, 16))
+    plain = gpt.gpt_forward(m, p, ids, ids)
+    qat = gpt.gpt_forward(m, p, ids, ids, qat=True)
+    rounded = dict(p, bigram_embed=p["bigram_embed"].to(torch.float8_e4m3fn).float(), bigram_proj=p["bigram_proj"].to(torch.float8_e4m3fn).float())
+    m2 = family_preset("tiny_cpu").model
+    m2.bigram.enabled, m2.bigram.vocab_size, m2.bigram.dim = True, 64, 32
+    assert float(plain) != float(qat)
+    assert torch.allclose(qat, gpt.gpt_forward(m2, rounded, ids, ids, qat=True), atol=1e-6)
+    w = p["bigram_proj"].clone().requires_grad_(True)
+    (g,) = torch.autograd.grad(R.fake_quant_fp8_ste(w).sum(), w)
+    assert torch.equal(g, torch.ones_like(w))

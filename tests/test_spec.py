@@ -41,11 +41,11 @@ def test_overrides():
         s.apply_overrides(["train.nope=1"])
 
 
-@pytest.mark.parametrize("ov", ["model.num_heads=7", "model.rope.mode=yarn", "quant.compression=brotli", "train.rank=3",
+@pytest.mark.parametrize("ov", ["model.num_heads=7", "model.rope.mode=spiral", "model.rope.yarn_max_len=0 model.rope.mode=yarn", "quant.compression=brotli", "train.rank=3",
                                 "model.vocab_size=70000", "quant.matrix_bits=3", "train.batch_tokens=1000"])
 def test_validation_rejects(ov):
     with pytest.raises(ValueError):
-        family_preset("tiny_cpu").apply_overrides([ov]).validate()
+        family_preset("tiny_cpu").apply_overrides(ov.split()).validate()
 
 
 def test_single_gpu_backends_reject_more_than_one_rank_but_cpu_runs_data_parallel():
@@ -86,3 +86,18 @@ def test_presets_match_benchmark_configs():
     r = family_preset("record_11l").validate()
     assert (r.model.mlp_dim, r.model.rope_dims, r.model.xsa_layers(), r.model.bigram.vocab_size) == (1536, 16, [7, 8, 9, 10], 3072)
     assert r.train.distributed_optimizer_backend == "sharded_parallel_muon" and r.train.batch_tokens == 786432
+
+
+def test_optional_record_ideas_are_cpu_only_and_read_from_the_environment():
+    from parameter_golf_b200.spec import RunSpec
+    s = family_preset("tiny_cpu").apply_overrides(["model.value_residual=true", "model.mtp_num_heads=2"]).validate()
+    assert s.model.value_residual and s.model.mtp_num_heads == 2
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["model.value_residual=true"]).validate()
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["model.mtp_num_heads=1"]).validate()
+    e = family_preset("tiny_cpu")
+    e.apply_env({"VALUE_RESIDUAL": "1", "MTP_NUM_HEADS": "3", "MTP_LOSS_WEIGHT": "0.1", "ROPE_TYPE": "yarn", "YARN_MAX_LEN": "4096"})
+    assert e.model.value_residual and e.model.mtp_num_heads == 3 and e.model.mtp_loss_weight == 0.1
+    assert e.model.rope.mode == "yarn" and e.model.rope.yarn_max_len == 4096
+    e.validate()

@@ -166,3 +166,28 @@ print('OK', dist.get_rank(), res.steps, res.val_bpb, flush=True)
     import re
     oks = re.findall(r"OK (\d) (\d+) ([0-9.eE+-]+)", out.stdout)
     assert len(oks) == 2 and oks[0][2] == oks[1][2], out.stdout[-500:]          # identical reduced val_bpb on both ranks
+
+
+def test_optional_record_ideas_train_export_and_reload_on_the_cpu_backend(tmp_path, monkeypatch):
+    """YaRN tables, the value residual and two multi-token-prediction heads through the trainer: the heads are trained but not
+    exported, the learned lambdas are, and the artifact reloads into an evaluable model."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.apply_overrides(["model.value_residual=true", "model.mtp_num_heads=2", "model.mtp_loss_weight=0.2", "model.rope.mode=yarn",
+                       "model.rope.yarn_max_len=1024", "model.rope.yarn_train_len=256"])
+    s.train.total_iterations = 6
+    s.train.artifact_path = str(tmp_path / "ideas.pgrs")
+    s.eval.max_tokens = 512
+    r = quiet(s)
+    import parameter_golf_b200.train as tr
+    monkeypatch.setattr(tr, "mode_max_steps", lambda spec, mode: 6)
+    res = r.run()
+    assert res.steps == 6 and np.isfinite(res.val_loss) and np.isfinite(res.train_loss_last)
+    # zero-initialised heads: the first training loss is the uniform one plus 0.2 times the heads' uniform loss
+    assert abs(res.train_loss_first - 1.2 * np.log(s.model.vocab_size)) < 0.05
+    back = load_artifact(open(s.train.artifact_path, "rb").read(), s)
+    assert "mtp_heads" not in back and back["vr_lambda"].shape == (s.model.num_layers, 2)
+    assert float((back["vr_lambda"] - 0.5).abs().max()) > 0          # the lambdas moved
+    ids = torch.randint(0, s.model.vocab_size, (1, 32))
+    assert torch.isfinite(gpt.gpt_forward(s.model, back, ids, ids))

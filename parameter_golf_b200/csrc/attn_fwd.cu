@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "pgb.h"
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 #include "tma_host.h"
@@ -482,7 +483,7 @@ void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, 
   p.xsa_eps = xsa_eps;
   static bool configured[64] = {};          // the attribute is a per-device property of the kernel
   static unsigned* sched_base[64] = {};
-  static unsigned sched_next = 0;
+  static std::atomic<unsigned> sched_next{0};     // host threads launching on different streams must not share a slot
   static int sm_count[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -505,7 +506,7 @@ void attn_fwd(const void* q, const void* k, const void* v, void* y, float* lse, 
       configured[dev] = true;
     }
   }
-  p.sched = base + 2 * (sched_next++ % A1_SCHED_SLOTS);
+  p.sched = base + 2 * (sched_next.fetch_add(1, std::memory_order_relaxed) % A1_SCHED_SLOTS);
   const int grid = std::min(p.n_qt * B * H, 2 * sms);
   attn_fwd_kernel<<<grid, A1_THREADS, A1_SMEM, st>>>(mq, mk, mv, p);
 }

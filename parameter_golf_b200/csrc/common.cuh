@@ -24,6 +24,7 @@ enum StatusCode : int {
   ST_WAIT_FLAG = 5,       // a peer/readiness flag never reached the expected epoch
   ST_BAD_ARG = 6,
   ST_WAIT_MISC = 7,
+  ST_BAD_INDEX = 8,       // an index read from data (a token id) was outside its table; the access was skipped
 };
 
 #ifndef PGB_WAIT_LIMIT_NS

@@ -88,7 +88,9 @@ void softcap_ce(const void* logits, const int* targets, float* nll, void* dlogit
                 cudaStream_t st, const float* tok_w = nullptr, const float* w_total = nullptr, int norm_rows = 0);
 // w[i] = table[prev[i] * V + curr[i]], *w_total = sum_i w[i] (zeroed here first)
 void pair_weights(const int* prev, const int* curr, const float* table, float* w, float* w_total, int rows, int V, cudaStream_t st);
-void embed_gather(const int* ids, const void* table, void* out, int rows, int d, int bigram_buckets, int seq_len, cudaStream_t st);
+// ids outside [0, table_rows) give a zero row and ST_BAD_INDEX in the status word instead of an address
+void embed_gather(const int* ids, const void* table, void* out, int rows, int d, int table_rows, int bigram_buckets, int seq_len, cudaStream_t st,
+                  int* status = nullptr);
 void embed_scatter_add(const int* ids, const void* g, float* dtable, int rows, int d, int table_rows, int bigram_buckets, int seq_len,
                        cudaStream_t st);
 

@@ -750,8 +750,10 @@ __global__ void __launch_bounds__(256) pair_weights_kernel(const int* __restrict
 // -------------------------------------------------------------------------------------------------------------
 // Embedding gathers: e[t] = table[ids[t]] (bf16 rows of width d); bigram bucket = ((36313*cur) ^ (27191*prev)) % (B-1),
 // sentinel bucket B-1 at sequence starts.
+// A token id outside the table (a shard written with another tokenizer, a corrupted span) must not become an address: the
+// row is written as zeros and the status word records the row, so the host can stop the run with a message.
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out, int rows,
-                                    int d, int bigram_buckets, int seq_len) {
+                                    int d, int table_rows, int bigram_buckets, int seq_len, int* __restrict__ status) {
   const int vec = d / 8;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)rows * vec) return;
@@ -763,7 +765,10 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const __nv_bflo
   } else {
     id = ids[row];
   }
-  *reinterpret_cast<uint4*>(out + (size_t)row * d + c) = *reinterpret_cast<const uint4*>(table + (size_t)id * d + c);
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if ((unsigned)id < (unsigned)table_rows) v = *reinterpret_cast<const uint4*>(table + (size_t)id * d + c);
+  else if (c == 0) report(status, ST_BAD_INDEX, row);
+  *reinterpret_cast<uint4*>(out + (size_t)row * d + c) = v;
 }
 
 // Scatter-add of row gradients into an embedding-table gradient: each CTA owns a slice of `SLICE` columns and
@@ -786,6 +791,7 @@ __global__ void __launch_bounds__(256) embed_scatter_kernel(const int* __restric
     } else {
       id = ids[row];
     }
+    if ((unsigned)id >= (unsigned)table_rows) continue;       // no table row to add to (the forward gather has flagged it)
     if (c0 + sub < d) {
       F8 a = ld8(g + (size_t)row * d + c0 + sub);
 #pragma unroll
@@ -803,7 +809,8 @@ __global__ void __launch_bounds__(256) embed_scatter_kernel(const int* __restric
 // Tables too tall for the shared-memory tile (8192-row vocabularies): one warp per gradient row, fp32 atomics straight into
 // the table gradient. With thousands of table rows the atomics rarely collide.
 __global__ void __launch_bounds__(256) embed_scatter_atomic_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ g,
-                                                                   float* __restrict__ dtable, int rows, int d, int bigram_buckets, int seq_len) {
+                                                                   float* __restrict__ dtable, int rows, int d, int table_rows, int bigram_buckets,
+                                                                   int seq_len) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
     int id;
@@ -813,6 +820,7 @@ __global__ void __launch_bounds__(256) embed_scatter_atomic_kernel(const int* __
     } else {
       id = ids[row];
     }
+    if ((unsigned)id >= (unsigned)table_rows) continue;       // warp-uniform: no table row to add to
     float* dst = dtable + (size_t)id * d;
     for (int col = lane * 8; col < d; col += 256) {
       F8 a = ld8(g + (size_t)row * d + col);
@@ -953,10 +961,11 @@ void pair_weights(const int* prev, const int* curr, const float* table, float* w
   pair_weights_kernel<<<grid, 256, 0, st>>>(prev, curr, table, w, w_total, rows, V);
 }
 
-void embed_gather(const int* ids, const void* table, void* out, int rows, int d, int bigram_buckets, int seq_len, cudaStream_t st) {
+void embed_gather(const int* ids, const void* table, void* out, int rows, int d, int table_rows, int bigram_buckets, int seq_len, cudaStream_t st,
+                  int* status) {
   const long long n = (long long)rows * (d / 8);
-  embed_gather_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, rows, d, bigram_buckets,
-                                                                   seq_len);
+  embed_gather_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, rows, d, table_rows,
+                                                                   bigram_buckets, seq_len, status);
 }
 
 void embed_scatter_add(const int* ids, const void* g, float* dtable, int rows, int d, int table_rows, int bigram_buckets, int seq_len,
@@ -966,7 +975,7 @@ void embed_scatter_add(const int* ids, const void* g, float* dtable, int rows, i
   while (slice > 8 && (size_t)table_rows * slice * 4 > 200 * 1024) slice /= 2;
   if ((size_t)table_rows * slice * 4 > 200 * 1024) {
     embed_scatter_atomic_kernel<<<std::max(1, std::min((rows + 7) / 8, 148 * 8)), 256, 0, st>>>(ids, (const __nv_bfloat16*)g, dtable, rows, d,
-                                                                                               bigram_buckets, seq_len);
+                                                                                               table_rows, bigram_buckets, seq_len);
     return;
   }
   const int cslices = (d + slice - 1) / slice;

@@ -528,12 +528,12 @@ class CudaEngine:
             self.ids.copy_(ids.reshape(-1))
             if targets is not None and targets is not True:
                 self.tgt.copy_(targets.reshape(-1))
-        C.embed_gather(self.ids, self.E, self.e, 0, S)
+        C.embed_gather(self.ids, self.E, self.e, 0, S, N.status_word(self.dev))
         if m.bigram.enabled:
-            C.embed_gather(self.ids, self.BE, self.bg, m.bigram.vocab_size, S)
+            C.embed_gather(self.ids, self.BE, self.bg, m.bigram.vocab_size, S, N.status_word(self.dev))
             N.gemm(self.bg, self.BP, self.xe, epi=N.EPI_AXPBY_BF16, alpha=1.0, beta=1.0, aux=self.e)
         if m.value_embedding.enabled:
-            C.embed_gather(self.ids, self.VE, self.ve_e, 0, S)
+            C.embed_gather(self.ids, self.VE, self.ve_e, 0, S, N.status_word(self.dev))
         bid = m.smear_gate_boundary_token_id
         C.norm_smear_fwd(self.xe, p["smear_gate"] if m.smear_gate else None, self.ids if (m.smear_gate and bid is not None) else None, self.x0,
                          S, -1 if bid is None else bid, self.eps)
@@ -1012,8 +1012,8 @@ class EngineBackend:
         code, block, detail, count = rb[4:8].view(torch.int32).tolist()
         if code:
             st.zero_()
-            raise RuntimeError(f"kernel wait timed out during the training step: {N.STATUS_NAMES.get(code, code)} "
-                               f"(block {block}, detail {detail}, {count} reports); gradients or weights of this step are not trustworthy")
+            raise RuntimeError(N.status_message(code, block, detail, count).replace("kernel wait timed out", "kernel wait timed out during the training step")
+                               + "; gradients or weights of this step are not trustworthy")
         return float(rb[0]) / (e.T * micro_batches)
 
     def _graphed_micro_step(self, span: torch.Tensor, accum: int):

@@ -17,7 +17,16 @@ _C = None
 
 EPI_BF16, EPI_F32, EPI_F32_ATOMIC, EPI_AXPBY_BF16, EPI_RESID_BF16, EPI_ACT_SQ, EPI_MUL_ACTGRAD = range(7)
 
-STATUS_NAMES = {0: "ok", 1: "wait_full", 2: "wait_empty", 3: "wait_tmem_full", 4: "wait_tmem_empty", 5: "wait_flag", 6: "bad_arg", 7: "wait_misc"}
+STATUS_NAMES = {0: "ok", 1: "wait_full", 2: "wait_empty", 3: "wait_tmem_full", 4: "wait_tmem_empty", 5: "wait_flag", 6: "bad_arg", 7: "wait_misc",
+                8: "bad_index"}
+
+
+def status_message(code: int, block: int, detail: int, count: int) -> str:
+    """What a non-zero status word means, for the exception the host raises."""
+    if code == 8:
+        return (f"a token id outside its embedding table reached a kernel (row {detail} of the micro-batch, {count} reports); "
+                f"the row was read as zeros. Check the shards against model.vocab_size")
+    return f"kernel wait timed out: {STATUS_NAMES.get(code, code)} (block {block}, detail {detail}, {count} reports)"
 
 
 def load():
@@ -115,19 +124,21 @@ _status = {}
 def status_word(device=None) -> torch.Tensor:
     """Per-device int32[4] status word that bounded waits write to: [code, block, detail, count]."""
     dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    if dev.type == "cuda" and dev.index is None:          # "cuda" and "cuda:N" must name the same word
+        dev = torch.device("cuda", torch.cuda.current_device())
     if dev not in _status:
         _status[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
     return _status[dev]
 
 
 def check_status(device=None, reset: bool = True):
-    """Raise if any kernel recorded a timed-out wait since the last check (synchronises the device)."""
+    """Raise if any kernel recorded a timed-out wait or a rejected index since the last check (synchronises the device)."""
     st = status_word(device)
     code, block, detail, count = st.tolist()
     if reset and code:
         st.zero_()
     if code:
-        raise RuntimeError(f"kernel wait timed out: {STATUS_NAMES.get(code, code)} (block {block}, detail {detail}, {count} reports)")
+        raise RuntimeError(status_message(code, block, detail, count))
 
 
 def gemm(A, B, D, a_kmajor=True, b_kmajor=True, epi=EPI_BF16, alpha=1.0, beta=0.0, slope=0.0, aux=None, colscale=None, D2=None, splits=0,

@@ -476,6 +476,44 @@ def test_training_step_raises_when_a_device_wait_ran_out():
     assert math.isfinite(be.train_step([(ids, ids)], 1.0, 0.95, False))     # status cleared, context alive
 
 
+def test_token_ids_outside_the_vocabulary_are_rejected_not_dereferenced():
+    """A span from a shard written with a larger vocabulary: the embedding kernels must not turn the id into an address. The
+    gather writes a zero row and flags the status word, the scatter skips the row, the training step raises with a message
+    that names the cause, and the next step on clean data runs."""
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.engine import EngineBackend
+    from parameter_golf_b200.ops import native
+    C = native.load()
+    table = torch.randn(256, 64, device="cuda").bfloat16()
+    ids = torch.tensor([3, 255, 256, 70000, -1, 7], dtype=torch.int32, device="cuda")
+    out = torch.full((6, 64), 9.0, device="cuda", dtype=torch.bfloat16)
+    C.embed_gather(ids, table, out, 0, 6, native.status_word())
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], table[3]) and torch.equal(out[1], table[255]) and torch.equal(out[5], table[7])
+    assert float(out[2:5].abs().max()) == 0.0
+    with pytest.raises(RuntimeError, match="outside its embedding table"):
+        native.check_status()
+    dtable = torch.zeros(256, 64, device="cuda")
+    g = torch.ones(6, 64, device="cuda", dtype=torch.bfloat16)
+    C.embed_scatter_add(ids, g, dtable, 0, 6)
+    torch.cuda.synchronize()
+    assert float(dtable.sum()) == 3 * 64 and float(dtable[3].sum()) == 64 and float(dtable[255].sum()) == 64
+    big = torch.zeros(8192, 64, device="cuda")                  # the table too tall for the shared-memory form: the atomic kernel
+    C.embed_scatter_add(ids, g, big, 0, 6)
+    torch.cuda.synchronize()
+    assert float(big.sum()) == 4 * 64                            # id 256 is a row of this taller table; 70000 and -1 are not
+    spec = small_spec(**{"train.ema_decay": 0.0})
+    spec.mode = "record"
+    spec.allow_unsupported_variants = True
+    be = EngineBackend(spec, gpt.init_params(spec.model, 3))
+    good = torch.randint(0, 256, (4, 128))
+    bad = good.clone()
+    bad[1, 17] = 300
+    with pytest.raises(RuntimeError, match="outside its embedding table"):
+        be.train_step([(bad, good)], 1.0, 0.95, False)
+    assert math.isfinite(be.train_step([(good, good)], 1.0, 0.95, False))
+
+
 @pytest.mark.parametrize("rank", [16, 80])
 def test_q_lora_forward_and_adapter_gradients_match_the_oracle(rank):
     """Q-LoRA on the CUDA engine (two skinny products in the forward, four in the backward) against the autograd model with the

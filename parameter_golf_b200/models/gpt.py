@@ -64,6 +64,9 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
         sh["lm_head"] = (m.vocab_size, d)
     if m.value_residual:
         sh["vr_lambda"] = (n, 2)
+    if m.dtg:
+        sh["dtg_gate_weight"] = (n, d)
+        sh["dtg_gate_bias"] = (n,)
     if m.mtp_num_heads > 0:
         sh["mtp_heads"] = (m.mtp_num_heads, m.vocab_size, d)
     return sh
@@ -110,6 +113,8 @@ def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float3
         p["attn_gate_bias"].fill_(4.0)
     if "vr_lambda" in p:
         p["vr_lambda"].fill_(0.5)
+    if "dtg_gate_bias" in p:
+        p["dtg_gate_bias"].fill_(2.0)             # sigmoid(2) = 0.88 of the block's update at the start, the weight at zero
     return {k: v.to(device=device, dtype=dtype) for k, v in p.items()}
 
 
@@ -217,6 +222,10 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
     if taps is not None:
         taps.add(i, "down", hid)
     out = x_mid + p["mlp_scale"][i].to(dt)[None, None, :] * F.linear(hid, wd.to(dt))
+    if m.dtg:
+        # records/.../2026-03-23_.../train_gpt.py:769-771: the gate reads the block input without sending it a gradient
+        gate = torch.sigmoid(F.linear(x_in.detach(), p["dtg_gate_weight"][i].to(dt)[None, :], p["dtg_gate_bias"][i].to(dt)[None]))
+        out = x_in + gate * (out - x_in)
     if return_kv:
         return out, (k, v)
     if return_raw_v:

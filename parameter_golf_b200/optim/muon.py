@@ -194,6 +194,37 @@ class Swa:
         return {k: v / self.count for k, v in self.sum.items()}
 
 
+class Lawa:
+    """Latest-weight averaging: a window of the last ``k`` snapshots, one every ``freq`` steps, averaged uniformly at the end of
+    training (``records/track_10min_16mb/2026-03-23_LeakyReLU_LegalTTT_ParallelMuon/train_gpt.py:1635,1727-1758``). When it is
+    on and holds at least two snapshots its average replaces the EMA weights."""
+
+    def __init__(self, k: int = 10, freq: int = 100):
+        from collections import deque
+        self.k, self.freq = k, freq
+        self.queue = deque(maxlen=max(k, 1))
+
+    def should_collect(self, step: int) -> bool:
+        return self.freq > 0 and step % self.freq == 0
+
+    @torch.no_grad()
+    def collect(self, params: Dict[str, torch.Tensor]):
+        self.queue.append({k: v.detach().float().cpu().clone() for k, v in params.items()})
+
+    @property
+    def count(self) -> int:
+        return len(self.queue)
+
+    def average(self) -> Optional[Dict[str, torch.Tensor]]:
+        if not self.queue:
+            return None
+        out = {k: torch.zeros_like(v) for k, v in self.queue[0].items()}
+        for snap in self.queue:
+            for k, v in snap.items():
+                out[k].add_(v)
+        return {k: v / len(self.queue) for k, v in out.items()}
+
+
 # ---- schedules --------------------------------------------------------------------------------------
 
 def lr_scale(step: int, warmup: int, total: int, warmdown: int) -> float:

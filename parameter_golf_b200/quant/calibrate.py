@@ -108,6 +108,9 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
             mlp_in = R.rms_norm(x_in if m.parallel_residual.enabled else x_mid, s_l)
             hid = R.act_sq(F.linear(mlp_in, p["mlp_up_bank"][i].to(dtype)), slope)
             x = x_mid + p["mlp_scale"][i].to(dtype)[None, :] * F.linear(hid, p["mlp_down_bank"][i].to(dtype))
+            if m.dtg:
+                gate = torch.sigmoid(F.linear(x_in, p["dtg_gate_weight"][i].to(dtype)[None, :], p["dtg_gate_bias"][i].to(dtype)[None]))
+                x = x_in + gate * (x - x_in)
             if unet and i < enc:
                 skips.append(x)
         hfin = R.rms_norm(x)

@@ -128,6 +128,9 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
             recs.append(_f16(f"blocks.{i}.sparse_attn_gate_weight", params["sparse_attn_gate_weight"][i]))
         if m.value_residual:
             recs.append(_f16(f"blocks.{i}.vr_lambda", params["vr_lambda"][i]))
+        if m.dtg:
+            recs.append(_f16(f"blocks.{i}.dtg_gate_weight", params["dtg_gate_weight"][i]))
+            recs.append(_f16(f"blocks.{i}.dtg_gate_bias", params["dtg_gate_bias"][i].reshape(1)))
     # the multi-token-prediction heads are training-only and are left out (records/.../2026-03-23_.../train_gpt.py:1778)
     if m.value_embedding.enabled:
         recs.append(_flt("ve_embed", params["ve_embed"], spec.quant.float_storage))
@@ -262,7 +265,8 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
             if name not in by:
                 raise C.ArtifactError(f"artifact is missing tensor {name}")
             p[name] = torch.from_numpy(_np(by[name]).astype(np.float32)).reshape(shapes[name])
-    for k in ("attn_scale", "mlp_scale", "resid_mix", "q_gain", "attn_gate_weight", "attn_gate_bias", "sparse_attn_gate_weight", "vr_lambda"):
+    for k in ("attn_scale", "mlp_scale", "resid_mix", "q_gain", "attn_gate_weight", "attn_gate_bias", "sparse_attn_gate_weight", "vr_lambda", "dtg_gate_weight",
+              "dtg_gate_bias"):
         if k in shapes:
             p[k] = torch.stack([torch.from_numpy(_np(by[f"blocks.{i}.{k}"]).astype(np.float32)) for i in range(n)]).reshape(shapes[k])
     return {k: v.to(device=device, dtype=dtype) for k, v in p.items()}

@@ -124,6 +124,7 @@ class ModelSpec:
     value_residual: bool = False          # v <- lambda_0 * v(first layer) + lambda_1 * v in every later layer, lambda learned per layer
     mtp_num_heads: int = 0                # extra output heads that predict the tokens 2, 3, ... ahead, training only, not exported
     mtp_loss_weight: float = 0.2
+    dtg: bool = False                     # per-block scalar gate on the block's update, sigmoid(w . x_in + b) read from the detached input (DTG_ENABLED)
     fp8_qat: bool = False                 # while QAT is on, the small 2-D float tensors (bigram / value-embedding tables and
                                           # projections, an untied head) go through an FP8 e4m3 round trip (FP_STORAGE=FP8)
 
@@ -189,6 +190,9 @@ class TrainSpec:
     swa_enabled: bool = True
     swa_every: int = 50
     swa_threshold: float = 0.2
+    lawa_enabled: bool = False     # latest-weight averaging: the last lawa_k snapshots, one every lawa_freq steps, replace the EMA weights
+    lawa_k: int = 10
+    lawa_freq: int = 100
     late_qat_threshold: float = 0.15
     qat_enabled: bool = False
     seed: int = 1337
@@ -389,6 +393,9 @@ class RunSpec:
         if has("ADAM_WD"): t.adam_wd = F("ADAM_WD")
         if has("SWA_ENABLED"): t.swa_enabled = B("SWA_ENABLED")
         if has("SWA_EVERY"): t.swa_every = I("SWA_EVERY")
+        if has("LAWA_ENABLED"): t.lawa_enabled = B("LAWA_ENABLED")
+        if has("LAWA_K"): t.lawa_k = I("LAWA_K")
+        if has("LAWA_FREQ"): t.lawa_freq = I("LAWA_FREQ")
         if has("QAT_ENABLED"): t.qat_enabled = B("QAT_ENABLED")
         if has("FP_STORAGE"):
             fp8 = env["FP_STORAGE"].strip().upper() == "FP8"
@@ -401,6 +408,7 @@ class RunSpec:
         if has("BIGRAM_DIM"): m.bigram.dim = I("BIGRAM_DIM")
         if has("XSA_LAST_N"): m.xsa_last_n = I("XSA_LAST_N")
         if has("VALUE_RESIDUAL"): m.value_residual = B("VALUE_RESIDUAL")
+        if has("DTG_ENABLED"): m.dtg = B("DTG_ENABLED")
         if has("MTP_NUM_HEADS"): m.mtp_num_heads = I("MTP_NUM_HEADS")
         if has("MTP_LOSS_WEIGHT"): m.mtp_loss_weight = F("MTP_LOSS_WEIGHT")
         if has("LN_SCALE"): m.ln_scale = B("LN_SCALE")
@@ -456,9 +464,10 @@ class RunSpec:
         chk(m.logit_softcap > 0, "logit_softcap must be positive")
         chk(m.xsa_last_n <= m.num_layers, "xsa_last_n exceeds num_layers")
         chk(m.mtp_num_heads >= 0 and m.mtp_loss_weight >= 0.0, "mtp_num_heads and mtp_loss_weight must be >= 0")
-        chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat) or t.backend == "cpu",
-            "model.value_residual, model.mtp_num_heads and model.fp8_qat run on train.backend=cpu only (the CUDA engine has no path for them)")
+        chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat or m.dtg) or t.backend == "cpu",
+            "model.value_residual, model.mtp_num_heads, model.dtg and model.fp8_qat run on train.backend=cpu only (the CUDA engine has no path for them)")
         chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
+        chk(not t.lawa_enabled or (t.lawa_k >= 1 and t.lawa_freq >= 1), "train.lawa_k and train.lawa_freq must be >= 1")
         chk(m.vocab_size <= 65536, "token ids are uint16: vocab_size must be <= 65536")
         chk(not (m.attn_out_gate.enabled and m.sparse_attn_gate.enabled),
             "attn_out_gate and sparse_attn_gate are mutually exclusive")

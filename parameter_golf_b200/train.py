@@ -34,7 +34,7 @@ from .eval.ttt import eval_lora_phased_ttt, eval_score_first_ttt
 from .models import gpt
 from .models.runner import OracleRunner
 from .parallel.agree import agree
-from .optim.muon import AdamW, Ema, Muon, Swa, clip_grads_, lr_scale_with_floor, muon_momentum_at, wallclock_lr_scale
+from .optim.muon import AdamW, Ema, Lawa, Muon, Swa, clip_grads_, lr_scale_with_floor, muon_momentum_at, wallclock_lr_scale
 from .quant.export import check_budget, code_bytes, export_model, load_artifact
 from .spec import RunSpec, family_preset
 from .utils.checkpoint import load_checkpoint, save_checkpoint
@@ -280,6 +280,7 @@ class VariantRunner:
         fused_ema = getattr(backend, "fused_ema", False)       # CUDA engine: EMA is updated inside the optimizer kernels
         ema = Ema(t.ema_decay) if (t.ema_decay > 0 and not fused_ema) else None
         swa = Swa(t.swa_every, t.swa_threshold) if t.swa_enabled else None
+        lawa = Lawa(t.lawa_k, t.lawa_freq) if t.lawa_enabled else None
         step0 = 0
         if t.resume_from:
             ck = load_checkpoint(t.resume_from)
@@ -359,6 +360,8 @@ class VariantRunner:
                     ema.update(backend.sync_params())
             if swa is not None and swa.should_collect(step, scale):
                 swa.collect(backend.final_params(ema=False) if fused_ema else backend.sync_params())
+            if lawa is not None and lawa.should_collect(step):
+                lawa.collect(backend.final_params(ema=False) if fused_ema else backend.sync_params())
             now_ms = train_ms + 1000.0 * (self.clock() - t_start)
             if t.train_log_every > 0 and (step <= 10 or step % t.train_log_every == 0 or step == max_steps):
                 log.info(f"step:{step}/{max_steps} train_loss:{loss:.4f} train_time:{now_ms:.0f}ms step_avg:{now_ms / (step - step0):.2f}ms")
@@ -392,7 +395,10 @@ class VariantRunner:
                 log.info("ema:applying EMA weights")
         else:
             final = {k: v.detach().cpu().float().clone() for k, v in backend.sync_params().items()}
-        if swa is not None and swa.count > 1:
+        if lawa is not None and lawa.count > 1:
+            log.info(f"lawa:applying LAWA averaging k={lawa.count}")
+            final = lawa.average()
+        elif swa is not None and swa.count > 1:
             log.info(f"swa:applying {swa.count} snapshots")
             final = {k: v.cpu() for k, v in swa.average().items()}
         elif ema is not None and ema.shadow is not None:

@@ -177,12 +177,37 @@ def test_multi_token_prediction_heads_add_a_training_only_loss():
     assert gpt.init_params(m)["mtp_heads"].abs().max() == 0                                # zero-initialised heads
 
 
+def test_dtg_gate_scales_the_block_update_and_reads_a_detached_input():
+    """records/.../2026-03-23_.../train_gpt.py:757-771: out = x_in + sigmoid(w . x_in + b) * (block(x_in) - x_in); a large bias
+    makes it the plain block, and the gate's input carries no gradient."""
+    m0, m1 = full_model(), full_model()
+    m1.dtg = True
+    p1 = {k: v.double() for k, v in gpt.fill_deterministic(m1).items()}
+    assert p1["dtg_gate_weight"].shape == (3, 16) and gpt.init_params(m1)["dtg_gate_bias"].tolist() == [2.0] * 3
+    ids = torch.randint(0, 32, (2, 7))
+    tgt = torch.randint(0, 32, (2, 7))
+    p0 = {k: v for k, v in p1.items() if not k.startswith("dtg_")}
+    open_gate = dict(p1, dtg_gate_weight=torch.zeros(3, 16, dtype=torch.float64), dtg_gate_bias=torch.full((3,), 40.0, dtype=torch.float64))
+    assert torch.allclose(gpt.gpt_forward(m1, open_gate, ids, tgt), gpt.gpt_forward(m0, p0, ids, tgt), atol=1e-10)
+    assert abs(float(gpt.gpt_forward(m1, p1, ids, tgt)) - float(gpt.gpt_forward(m0, p0, ids, tgt))) > 1e-6
+    for name, idx in (("dtg_gate_weight", (1, 3)), ("dtg_gate_bias", (2,))):
+        leaf = p1[name].clone().requires_grad_(True)
+        (g,) = torch.autograd.grad(gpt.gpt_forward(m1, dict(p1, **{name: leaf}), ids, tgt), leaf)
+        eps = 1e-6
+        pp, pm = p1[name].clone(), p1[name].clone()
+        pp[idx] += eps
+        pm[idx] -= eps
+        fd = (gpt.gpt_forward(m1, dict(p1, **{name: pp}), ids, tgt) - gpt.gpt_forward(m1, dict(p1, **{name: pm}), ids, tgt)) / (2 * eps)
+        assert abs(float(fd) - float(g[idx])) < 1e-4 * max(1.0, abs(float(fd))), name
+
+
 @pytest.mark.parametrize("value_residual", [False, True])
 def test_cached_generation_follows_the_full_forward(value_residual):
     """At a vanishing temperature the K/V-cached sampler must pick the arg-max of the full model's logits at every step."""
     from parameter_golf_b200.quant.calibrate import generate_autoregressive
     m = full_model()
     m.value_residual = value_residual
+    m.dtg = value_residual                                     # the gated block update rides along in the same variant
     p = gpt.fill_deterministic(m)
     p["tok_emb"] = p["tok_emb"] * 4.0                           # wider logit margins than the fill pattern gives
     toks = generate_autoregressive(m, p, num_seqs=3, seq_len=10, temperature=1e-4, seed=5)

@@ -89,6 +89,14 @@ def test_swa_window_and_average():
     assert s.average()["w"].item() == 2.0
 
 
+def test_lawa_keeps_the_last_k_snapshots():
+    l = M.Lawa(k=3, freq=10)
+    assert l.should_collect(20) and not l.should_collect(25)
+    for v in (1.0, 2.0, 6.0, 7.0):
+        l.collect({"w": torch.tensor([v])})
+    assert l.count == 3 and l.average()["w"].item() == 5.0          # the first snapshot fell out of the window
+
+
 def test_wsd_schedule():
     assert M.lr_scale(0, 20, 9000, 3500) == 0.0 and M.lr_scale(10, 20, 9000, 3500) == 0.5
     assert M.lr_scale(20, 20, 9000, 3500) == 1.0 and M.lr_scale(5499, 20, 9000, 3500) == 1.0

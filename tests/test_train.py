@@ -191,3 +191,37 @@ def test_optional_record_ideas_train_export_and_reload_on_the_cpu_backend(tmp_pa
     assert float((back["vr_lambda"] - 0.5).abs().max()) > 0          # the lambdas moved
     ids = torch.randint(0, s.model.vocab_size, (1, 32))
     assert torch.isfinite(gpt.gpt_forward(s.model, back, ids, ids))
+
+
+def test_lawa_average_replaces_the_final_weights(tmp_path, monkeypatch):
+    """train.lawa_enabled: the exported weights are the mean of the windowed snapshots, not the last iterate or the EMA."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.apply_overrides(["train.lawa_enabled=true", "train.lawa_k=2", "train.lawa_freq=2"])
+    s.train.total_iterations = 6
+    s.train.artifact_path = str(tmp_path / "lawa.pgrs")
+    s.eval.max_tokens = 512
+    r = quiet(s)
+    import parameter_golf_b200.train as tr
+    monkeypatch.setattr(tr, "mode_max_steps", lambda spec, mode: 6)
+    snaps = []
+    real = tr.Lawa.collect
+
+    def spy(self, params):
+        real(self, params)
+        snaps.append({k: v.detach().float().cpu().clone() for k, v in params.items()})
+    monkeypatch.setattr(tr.Lawa, "collect", spy)
+    exported = {}
+    real_export = tr.export_model
+
+    def grab(spec, params, *a, **k):
+        exported.update({n: v.detach().float().cpu().clone() for n, v in params.items()})
+        return real_export(spec, params, *a, **k)
+    monkeypatch.setattr(tr, "export_model", grab)
+    res = r.run()
+    assert res.steps == 6 and len(snaps) == 3 and any("lawa:applying LAWA averaging k=2" in l for l in r.log.lines)
+    for name in ("qo_bank", "tok_emb", "attn_scale"):
+        want = (snaps[1][name] + snaps[2][name]) / 2
+        assert torch.allclose(exported[name], want, atol=1e-6), name
+    assert not torch.allclose(exported["qo_bank"], snaps[2]["qo_bank"], atol=1e-6)      # not simply the last iterate

@@ -6,6 +6,15 @@ import pytest
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def free_port() -> int:
+    """A TCP port nobody listens on right now, for a rendezvous on 127.0.0.1 (a fixed number can still be in TIME_WAIT from the
+    previous run, or taken by another job on the machine)."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 box)")
     config.addinivalue_line("markers", "multigpu: needs two or more CUDA devices")

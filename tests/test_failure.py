@@ -14,7 +14,9 @@ from parameter_golf_b200.spec import family_preset
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(tmp_path, body, nproc=2, port=29690, timeout=120):
+def _run(tmp_path, body, nproc=2, port=None, timeout=120):
+    from conftest import free_port
+    port = free_port()
     script = tmp_path / "w.py"
     script.write_text("import os, sys, time, datetime\nsys.path.insert(0, %r)\nimport torch, torch.distributed as dist\n" % ROOT + textwrap.dedent(body))
     env = dict(os.environ, PYTHONPATH=ROOT)

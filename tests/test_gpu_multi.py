@@ -12,6 +12,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def run_workers(mode, nproc=2, port=29731):
+    try:                                       # a port that is free now; the fixed numbers are the fallback
+        from conftest import free_port
+        port = free_port()
+    except Exception:
+        pass
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "tests", "multi_worker.py"), mode]

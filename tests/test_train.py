@@ -14,6 +14,7 @@ from parameter_golf_b200.utils.checkpoint import load_checkpoint, save_checkpoin
 from parameter_golf_b200.utils.logging import RunLog
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+from conftest import free_port  # noqa: E402
 
 
 def quiet(spec):
@@ -161,7 +162,7 @@ print('OK', dist.get_rank(), res.steps, res.val_bpb, flush=True)
 """)
     env = dict(os.environ, PGB_DATA_ROOT=str(tmp_path / "d"), PYTHONPATH=ROOT)
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-                          "--master-port", "29611", str(script)], capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+                          "--master-port", str(free_port()), str(script)], capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
     assert out.returncode == 0, out.stderr[-3000:]
     import re
     oks = re.findall(r"OK (\d) (\d+) ([0-9.eE+-]+)", out.stdout)

@@ -236,3 +236,63 @@ def test_synthetic_validation_shard_follows_the_training_chain(tmp_path):
     v = top_successor(os.path.join(root, "fineweb_val_000000.bin"))
     assert (a == v).mean() > 0.9 and (a == b).mean() > 0.9
     assert not np.array_equal(S.open_shard(os.path.join(root, "fineweb_train_000000.bin"))[:1000], S.open_shard(os.path.join(root, "fineweb_val_000000.bin"))[:1000])
+
+
+# ---- local text -> tokenizer -> shards (data/text_shards.py) -----------------------------------------------------------------
+
+def _corpus(n=400, seed=3):
+    rng = np.random.default_rng(seed)
+    words = ["alpha", "beta", "gamma", "delta", "tensor", "memory", "kernel", "golf", "parameter", "stream", "42", "2048", "the", "of", "and"]
+    return [" ".join(rng.choice(words, size=int(rng.integers(5, 40)))) + "." for _ in range(n)]
+
+
+def test_sentencepiece_training_and_shard_export_round_trip(tmp_path):
+    """A BPE tokenizer trained on local documents with the reference's settings, exported to shards: documents start with
+    BOS, the first documents form the validation split, the text comes back from the ids, and the byte sidecar adds up to
+    the UTF-8 size of the validation text."""
+    import json
+    from parameter_golf_b200.data import text_shards as T
+    from parameter_golf_b200.data.bpb import BpbLuts
+    docs = _corpus()
+    jl = tmp_path / "docs.jsonl"
+    jl.write_text("\n".join(json.dumps({"text": d}) for d in docs) + "\n")
+    assert list(T.iter_documents(str(jl))) == docs
+    model = T.train_sentencepiece(T.iter_documents(str(jl)), 320, str(tmp_path / "tok" / "sp320"))
+    tok = T.load_sentencepiece(model)
+    assert tok.vocab_size <= 320 and tok.bos_id == 1 and tok.eos_id == 2
+    stats = T.export_shards(T.iter_documents(str(jl)), tok, str(tmp_path / "out"), num_val_docs=50, shard_tokens=4000)
+    assert stats["docs_val"] == 50 and stats["docs_train"] == 350 and stats["files_train"] >= 2
+    val = S.load_validation_tokens(str(tmp_path / "out" / "fineweb_val_*.bin"), 16)           # sidecars matched by the pattern are left out
+    side = S.load_validation_byte_sidecar(str(tmp_path / "out" / "fineweb_val_bytes_*.bin"))
+    allval = np.concatenate([np.asarray(S.open_shard(f)) for f in sorted((tmp_path / "out").glob("fineweb_val_0*.bin"))])
+    assert len(side) == len(allval) == stats["tokens_val"] and np.array_equal(val, allval[:len(val)])
+    starts = np.flatnonzero(allval == tok.bos_id)
+    assert len(starts) == 50 and starts[0] == 0
+    first = allval[starts[0] + 1:starts[1]]
+    assert tok.decode(first) == docs[0]
+    assert int(side.sum()) == stats["bytes_val"] == sum(len(d.encode()) for d in docs[:50])
+    # the table rule gives the same byte counts as the sidecar
+    luts = BpbLuts.from_sentencepiece(model, tok.vocab_size)
+    assert np.array_equal(luts.token_bytes(allval[:-1], allval[1:]), side[1:])
+    train = np.concatenate([np.asarray(S.open_shard(f)) for f in sorted((tmp_path / "out").glob("fineweb_train_*.bin"))])
+    assert len(train) == stats["tokens_train"] and int((train == tok.bos_id).sum()) == 350 and int(train.max()) < tok.vocab_size
+    assert json.load(open(tmp_path / "out" / "manifest.json"))["vocab_size"] == tok.vocab_size
+
+
+def test_byte_tokenizer_export_and_the_vocabulary_guard(tmp_path):
+    from parameter_golf_b200.data import text_shards as T
+    txt = tmp_path / "notes.txt"
+    txt.write_text("first block\nstill first\n\nsecond block with an accent: café\n\n\nthird\n")
+    docs = list(T.iter_documents(str(tmp_path)))
+    assert docs == ["first block\nstill first", "second block with an accent: café", "third"]
+    tok = T.ByteTokenizer().as_tokenizer()
+    stats = T.export_shards(docs, tok, str(tmp_path / "b"), num_val_docs=2, shard_tokens=1000, append_eos=True)
+    val = np.asarray(S.open_shard(str(tmp_path / "b" / "fineweb_val_000000.bin")))
+    side = np.asarray(S.open_shard(str(tmp_path / "b" / "fineweb_val_bytes_000000.bin")))
+    assert val[0] == 1 and int((val == 2).sum()) == 2 and stats["bytes_val"] == int(side.sum()) == sum(len(d.encode()) for d in docs[:2])
+    assert T.ByteTokenizer().decode(val[1:1 + len(docs[0].encode())]) == docs[0]
+    bad = T.Tokenizer("bad", 10, 1, 2, lambda texts: [np.array([3, 11]) for _ in texts], lambda ids: "", tok.luts)
+    with pytest.raises(ValueError, match="outside declared vocab_size"):
+        T.export_shards(["x"], bad, str(tmp_path / "c"))
+    assert T._main(["--docs", str(txt), "--out", str(tmp_path / "cli"), "--tokenizer", "bytes", "--val-docs", "1", "--shard-tokens", "64"]) == 0
+    assert (tmp_path / "cli" / "fineweb_train_000000.bin").exists()

@@ -16,6 +16,11 @@ tokenizer ``:36-70``). This module is the part of that which works on files that
 
     python -m parameter_golf_b200.data.text_shards --docs corpus.jsonl --out data/sp1024 --vocab 1024 --val-docs 500
     python -m parameter_golf_b200.data.text_shards --docs texts/ --out data/bytes --tokenizer bytes
+
+A run then points at the result with ``train.train_data_pattern=data/sp1024/fineweb_train_*.bin``,
+``train.validation_data_pattern=data/sp1024/fineweb_val_*.bin`` (byte sidecars matched by the pattern are skipped),
+``model.vocab_size=1024`` and either ``eval.tokenizer_vocab_path=data/sp1024/tokenizers/fineweb_1024_bpe.model`` or
+``eval.caseops_byte_sidecar_pattern=data/sp1024/fineweb_val_bytes_*.bin`` for the bits-per-byte denominator.
 """
 from __future__ import annotations
 

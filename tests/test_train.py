@@ -226,3 +226,36 @@ def test_lawa_average_replaces_the_final_weights(tmp_path, monkeypatch):
         want = (snaps[1][name] + snaps[2][name]) / 2
         assert torch.allclose(exported[name], want, atol=1e-6), name
     assert not torch.allclose(exported["qo_bank"], snaps[2]["qo_bank"], atol=1e-6)      # not simply the last iterate
+
+
+def test_training_on_exported_text_shards_and_bpb_from_the_byte_sidecar(tmp_path, monkeypatch):
+    """Local text -> tokenizer -> shards -> trainer -> evaluation: the bits-per-byte denominator read from the per-position
+    byte sidecar equals the one derived from the tokenizer's piece table."""
+    import json
+    from parameter_golf_b200.data import text_shards as T
+    rng = np.random.default_rng(0)
+    words = ["alpha", "beta", "gamma", "delta", "tensor", "memory", "kernel", "golf", "parameter", "stream", "42", "the", "of", "and"]
+    docs = [" ".join(rng.choice(words, size=int(rng.integers(20, 60)))) + "." for _ in range(500)]
+    model = T.train_sentencepiece(iter(docs), 300, str(tmp_path / "tok" / "sp"))
+    tok = T.load_sentencepiece(model)
+    out = tmp_path / "shards"
+    T.export_shards(iter(docs), tok, str(out), num_val_docs=60, shard_tokens=1 << 20)
+
+    def run(extra):
+        s = family_preset("tiny_cpu")
+        s.mode = "smoke"
+        s.apply_overrides([f"model.vocab_size={tok.vocab_size}", "train.seq_len=64", "model.train_seq_len=64", "model.eval_seq_len=64",
+                           "train.batch_tokens=512", f"train.train_data_pattern={out}/fineweb_train_*.bin",
+                           f"train.validation_data_pattern={out}/fineweb_val_*.bin", "eval.stride=64"] + extra)
+        s.train.total_iterations = 3
+        s.train.artifact_path = str(tmp_path / "a.pgrs")
+        s.eval.max_tokens = 1024
+        import parameter_golf_b200.train as tr
+        monkeypatch.setattr(tr, "mode_max_steps", lambda spec, mode: 3)
+        return quiet(s).run()
+
+    a = run([f"eval.tokenizer_vocab_path={model}"])
+    b = run([f"eval.caseops_byte_sidecar_pattern={out}/fineweb_val_bytes_*.bin"])
+    assert np.isfinite(a.val_bpb) and a.val_loss == b.val_loss
+    assert a.val_bpb == pytest.approx(b.val_bpb, rel=1e-9)
+    assert abs(a.train_loss_first - np.log(tok.vocab_size)) < 0.2

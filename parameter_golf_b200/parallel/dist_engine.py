@@ -62,6 +62,15 @@ def shard_range(slots: int, rank: int, world: int) -> Tuple[int, int]:
     return s0, min(s0 + chunk, slots)
 
 
+def slot_layer(bank: str, s: int, n: int) -> int:
+    """The layer whose ready counter slot ``s`` of ``bank`` bumps when its new weights have been pushed. ``qo_bank`` holds the
+    ``n`` query matrices and then the ``n`` output projections, ``kv_bank`` the keys and then the values, the MLP banks one
+    matrix per layer; every layer therefore collects six bumps per step, from whichever ranks own those slots."""
+    if bank in ("qo_bank", "kv_bank"):
+        return s % n
+    return s
+
+
 class DistributedStep:
     def __init__(self, engine, spec: RunSpec, group=None, overlap: bool = True):
         """``overlap=False`` queues the whole sharded step on the caller's stream after the backward pass (the serial
@@ -177,17 +186,17 @@ class DistributedStep:
         e = self.e
         n, d, kv, mlp = e.n, e.d, e.kv, e.mlp
         per = e.p[bank][0].numel()
+        layer = slot_layer(bank, s, n)
+        flag = SIG_LAYER + layer
         if bank == "qo_bank" and s < n:
-            return [self.w_off["Wqkv"] + s * e.qkvw * d, -1, 0, SIG_LAYER + s]
+            return [self.w_off["Wqkv"] + s * e.qkvw * d, -1, 0, flag]
         if bank == "qo_bank":
-            layer = s - n
-            return [self.w_off["Wo"] + layer * d * d, self.w_off["Wo_u"] + layer * per, e.p["attn_scale"][layer].data_ptr(), SIG_LAYER + layer]
+            return [self.w_off["Wo"] + layer * d * d, self.w_off["Wo_u"] + layer * per, e.p["attn_scale"][layer].data_ptr(), flag]
         if bank == "kv_bank":
-            layer = s % n
-            return [self.w_off["Wqkv"] + layer * e.qkvw * d + (d if s < n else d + kv) * d, -1, 0, SIG_LAYER + layer]
+            return [self.w_off["Wqkv"] + layer * e.qkvw * d + (d if s < n else d + kv) * d, -1, 0, flag]
         if bank == "mlp_up_bank":
-            return [self.w_off["Wup"] + s * mlp * d, -1, 0, SIG_LAYER + s]
-        return [self.w_off["Wd"] + s * d * mlp, self.w_off["Wd_u"] + s * per, e.p["mlp_scale"][s].data_ptr(), SIG_LAYER + s]
+            return [self.w_off["Wup"] + s * mlp * d, -1, 0, flag]
+        return [self.w_off["Wd"] + s * d * mlp, self.w_off["Wd_u"] + s * per, e.p["mlp_scale"][s].data_ptr(), flag]
 
     def _push_bank(self, bank: str):
         """Write the bf16 compute rows of every owned slot of ``bank`` into every rank (one launch) and bump the ready

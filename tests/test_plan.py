@@ -66,3 +66,25 @@ def test_preliminary_sweep_script_runs_on_cpu():
     out = json.loads(r.stdout.strip().splitlines()[-1])
     fams = {row["family"]: row for row in out["arch"]}
     assert fams["record_11l"]["fits"] and fams["record_11l"]["params"] > 26_000_000 and fams["tiny_cpu"]["engine_gib"] < 5
+
+
+def test_bank_shards_cover_every_slot_once_and_every_layer_gets_six_weight_pushes():
+    """Host-side bookkeeping of the sharded optimizer: the slot ranges of the ranks tile each bank, trailing ranks may own
+    nothing, and per step every layer's ready counter is bumped by exactly six slots (Q, O, K, V, up, down) whatever the
+    world size: the value the QKV product of the next forward waits for."""
+    from parameter_golf_b200.parallel.dist_engine import shard_range, slot_layer
+    for n in (1, 3, 11, 12):
+        banks = {"qo_bank": 2 * n, "kv_bank": 2 * n, "mlp_up_bank": n, "mlp_down_bank": n}
+        for world in range(1, 9):
+            bumps = [0] * n
+            for bank, slots in banks.items():
+                seen = []
+                for rank in range(world):
+                    s0, s1 = shard_range(slots, rank, world)
+                    assert 0 <= s0 <= s1 <= slots
+                    seen.extend(range(s0, s1))
+                    for s in range(s0, s1):
+                        bumps[slot_layer(bank, s, n)] += 1
+                assert seen == list(range(slots)), (bank, world)
+            assert bumps == [6] * n, (n, world, bumps)
+    assert shard_range(22, 7, 8) == (21, 22) and shard_range(11, 6, 8) == (11, 11)       # the last ranks of 8 own little or nothing

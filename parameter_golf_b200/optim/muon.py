@@ -106,6 +106,102 @@ class Muon:
             b.copy_(s)
 
 
+def shard_range(slots: int, rank: int, world: int):
+    """[start, end) of the leading-axis slots of a bank that ``rank`` owns: equal chunks of ceil(slots / world), the last
+    ranks may own fewer or none (the reference's ``chunk_batch``, ``pg-train/src/lib.rs:577-591``)."""
+    chunk = -(-slots // world)
+    s0 = min(rank * chunk, slots)
+    return s0, min(s0 + chunk, slots)
+
+
+class ShardedMuon:
+    """Parallel Muon over a process group, on any backend `torch.distributed` offers (gloo for CPU ranks): the reference form of
+    the sharded optimizer the CUDA path runs with peer-memory kernels (``records/.../2026-03-23_.../train_gpt.py:127-266``,
+    ``pg-train/src/lib.rs:3259-3772``).
+
+    Every bank ``[slots, M, N]`` is split along its first axis. A rank receives the sum of all ranks' gradients for the slots it
+    owns (one reduce per owner), keeps momentum for those slots only, orthogonalises and applies the update to them, and the
+    updated slots are all-gathered so that every rank ends the step with identical full banks."""
+
+    def __init__(self, params: List[torch.Tensor], lr: float, momentum: float, ns_steps: int = 5, ns_profile: str = "quintic",
+                 weight_decay: float = 0.0, nesterov: bool = True, group=None):
+        import torch.distributed as dist
+        self.params, self.group = params, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.lr, self.momentum, self.ns_steps, self.ns_profile = lr, momentum, ns_steps, ns_profile
+        self.weight_decay, self.nesterov = weight_decay, nesterov
+        self.own = [shard_range(p.shape[0], self.rank, self.world) for p in params]
+        self.bufs = [torch.zeros_like(p[s0:s1], dtype=torch.float32) for p, (s0, s1) in zip(params, self.own)]
+
+    @torch.no_grad()
+    def reduce_to_owners(self, grads: List[torch.Tensor]) -> List[torch.Tensor]:
+        """Mean over ranks of the gradient slots each rank owns (the other slots of ``grads`` are left as they are)."""
+        import torch.distributed as dist
+        out = []
+        for g, p in zip(grads, self.params):
+            mine = None
+            for r in range(self.world):
+                s0, s1 = shard_range(p.shape[0], r, self.world)
+                if s1 <= s0:
+                    continue
+                part = g[s0:s1].float().contiguous()
+                dist.reduce(part, dst=dist.get_global_rank(self.group, r) if self.group is not None else r, group=self.group)
+                if r == self.rank:
+                    mine = part / self.world
+            s0, s1 = self.own[len(out)]
+            out.append(mine if mine is not None else g[s0:s1].float())
+        return out
+
+    @torch.no_grad()
+    def step(self, own_grads: List[torch.Tensor], lr: Optional[float] = None, momentum: Optional[float] = None):
+        """``own_grads[i]`` is the reduced gradient of the owned slots of bank i (what `reduce_to_owners` returns, possibly
+        rescaled by the clip factor). Updates the owned slots, then exchanges them."""
+        import torch.distributed as dist
+        lr = self.lr if lr is None else lr
+        mu = self.momentum if momentum is None else momentum
+        for p, g, buf, (s0, s1) in zip(self.params, own_grads, self.bufs, self.own):
+            if s1 > s0:
+                buf.mul_(mu).add_(g)
+                u = g.add(buf, alpha=mu) if self.nesterov else buf
+                u = newton_schulz(u, self.ns_steps, self.ns_profile).float()
+                if self.weight_decay > 0:
+                    p[s0:s1].mul_(1.0 - lr * self.weight_decay)
+                p[s0:s1].add_(u.to(p.dtype), alpha=-lr * muon_scale(p.shape))
+            chunk = -(-p.shape[0] // self.world)
+            send = torch.zeros((chunk,) + tuple(p.shape[1:]), dtype=p.dtype)
+            send[: s1 - s0].copy_(p[s0:s1])
+            recv = [torch.empty_like(send) for _ in range(self.world)]
+            dist.all_gather(recv, send, group=self.group)
+            for r, t in enumerate(recv):
+                r0, r1 = shard_range(p.shape[0], r, self.world)
+                if r1 > r0 and r != self.rank:
+                    p[r0:r1].copy_(t[: r1 - r0])
+
+    def own_sumsq(self, own_grads: List[torch.Tensor]) -> torch.Tensor:
+        return sum((g.float().pow(2).sum() for g in own_grads), torch.zeros(()))
+
+    def state_dict(self):
+        """Full momentum buffers, gathered from the owners (a collective: every rank calls it)."""
+        import torch.distributed as dist
+        full = []
+        for p, buf, (s0, s1) in zip(self.params, self.bufs, self.own):
+            chunk = -(-p.shape[0] // self.world)
+            send = torch.zeros((chunk,) + tuple(p.shape[1:]), dtype=torch.float32)
+            send[: s1 - s0].copy_(buf)
+            recv = [torch.empty_like(send) for _ in range(self.world)]
+            dist.all_gather(recv, send, group=self.group)
+            f = torch.zeros_like(p, dtype=torch.float32)
+            for r, t in enumerate(recv):
+                r0, r1 = shard_range(p.shape[0], r, self.world)
+                f[r0:r1].copy_(t[: r1 - r0])
+            full.append(f)
+        return {"bufs": full}
+
+    def load_state_dict(self, st):
+        for buf, s, (s0, s1) in zip(self.bufs, st["bufs"], self.own):
+            buf.copy_(s[s0:s1])
+
+
 class AdamW:
     """Decoupled-weight-decay Adam with bias correction (``pg-optim/src/adamw.rs:46-70``); one lr per group."""
 

@@ -55,11 +55,7 @@ BF = torch.bfloat16
 SIG_BARRIER, SIG_SCALAR, SIG_BARRIER2, SIG_LAYER, SIG_GRAD = 0, 32, 64, 128, 512      # slots in the int32 signal pad
 
 
-def shard_range(slots: int, rank: int, world: int) -> Tuple[int, int]:
-    """[start, end) slots of a bank owned by ``rank`` (may be empty for trailing ranks)."""
-    chunk = -(-slots // world)
-    s0 = min(rank * chunk, slots)
-    return s0, min(s0 + chunk, slots)
+from ..optim.muon import shard_range  # noqa: E402,F401  ([start, end) slots of a bank owned by a rank; shared with the CPU-rank form)
 
 
 def slot_layer(bank: str, s: int, n: int) -> int:

@@ -34,7 +34,7 @@ from .eval.ttt import eval_lora_phased_ttt, eval_score_first_ttt
 from .models import gpt
 from .models.runner import OracleRunner
 from .parallel.agree import agree
-from .optim.muon import AdamW, Ema, Lawa, Muon, Swa, clip_grads_, lr_scale_with_floor, muon_momentum_at, wallclock_lr_scale
+from .optim.muon import AdamW, Ema, Lawa, Muon, ShardedMuon, Swa, clip_grads_, lr_scale_with_floor, muon_momentum_at, wallclock_lr_scale
 from .quant.export import check_budget, code_bytes, export_model, load_artifact
 from .spec import RunSpec, family_preset
 from .utils.checkpoint import load_checkpoint, save_checkpoint
@@ -91,8 +91,16 @@ class OracleBackend:
         self.token_weight_table = None      # [V, V] fp32 loss weights per (input token, target), see `set_token_weight_table`
         t = spec.train
         self.bank_names, self.adam_groups = split_param_groups(spec, params)
-        self.muon = Muon([params[k] for k in self.bank_names], t.matrix_lr, t.muon_momentum, t.muon_ns_steps,
-                         t.muon_ns_profile, t.muon_wd)
+        import torch.distributed as dist
+        self.sharded = (t.distributed_optimizer_backend == "sharded_parallel_muon" and dist.is_available() and dist.is_initialized()
+                        and dist.get_world_size() > 1)
+        if self.sharded:
+            # CPU ranks: the same split of the banks as the CUDA path, with gloo reduces and all-gathers in place of the peer kernels
+            self.muon = ShardedMuon([params[k] for k in self.bank_names], t.matrix_lr, t.muon_momentum, t.muon_ns_steps, t.muon_ns_profile,
+                                    t.muon_wd)
+        else:
+            self.muon = Muon([params[k] for k in self.bank_names], t.matrix_lr, t.muon_momentum, t.muon_ns_steps,
+                             t.muon_ns_profile, t.muon_wd)
         self.adam = AdamW([{"params": [params[k] for k in g["names"]], "lr": g["lr"]} for g in self.adam_groups],
                           (t.adam_beta1, t.adam_beta2), t.adam_eps, t.adam_wd)
 
@@ -109,6 +117,8 @@ class OracleBackend:
             total = g if total is None else {k: total[k] + g[k] for k in g}
         inv = 1.0 / len(batches)
         grads = {k: v * inv for k, v in total.items()}
+        if self.sharded:
+            return self._sharded_update(grads, lr_scale, momentum, loss_sum * inv)
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             flat = torch.cat([grads[k].reshape(-1) for k in sorted(grads)])
             dist.all_reduce(flat)
@@ -123,6 +133,36 @@ class OracleBackend:
         self.adam.step([[grads[k] for k in g["names"]] for g in self.adam_groups], lr_scale)
         self.muon.step([grads[k] for k in self.bank_names], lr=self.spec.train.matrix_lr * lr_scale, momentum=momentum)
         return loss_sum * inv
+
+    def _sharded_update(self, grads, lr_scale: float, momentum: float, loss: float) -> float:
+        """Sharded Parallel Muon on CPU ranks: the replicated (non-bank) gradients are averaged with one all-reduce, every bank
+        slot's gradient goes to its owner, the clip factor comes from one scalar all-reduce in which each rank contributes
+        ||replicated||^2 / world + ||own slots||^2 (``pg-train/src/lib.rs:3495-3559``), AdamW runs replicated and Muon on the
+        owned slots, whose new values are then all-gathered."""
+        import torch.distributed as dist
+        world = dist.get_world_size()
+        small = sorted(k for k in grads if k not in self.bank_names)
+        flat = torch.cat([grads[k].reshape(-1) for k in small])
+        dist.all_reduce(flat)
+        flat /= world
+        off = 0
+        for k in small:
+            n = grads[k].numel()
+            grads[k] = flat[off:off + n].reshape(grads[k].shape)
+            off += n
+        own = self.muon.reduce_to_owners([grads[k] for k in self.bank_names])
+        clip = self.spec.train.grad_clip_norm
+        if clip > 0:
+            sq = (flat.float().pow(2).sum() / world + self.muon.own_sumsq(own)).reshape(1)
+            dist.all_reduce(sq)
+            norm = float(sq.sqrt())
+            if norm > clip:
+                f = clip / (norm + 1e-6)
+                flat.mul_(f)
+                own = [g * f for g in own]
+        self.adam.step([[grads[k] for k in g["names"]] for g in self.adam_groups], lr_scale)
+        self.muon.step(own, lr=self.spec.train.matrix_lr * lr_scale, momentum=momentum)
+        return loss
 
     def set_token_weight_table(self, table) -> None:
         self.token_weight_table = None if table is None else np.ascontiguousarray(table, dtype=np.float32)

@@ -259,3 +259,58 @@ def test_training_on_exported_text_shards_and_bpb_from_the_byte_sidecar(tmp_path
     assert np.isfinite(a.val_bpb) and a.val_loss == b.val_loss
     assert a.val_bpb == pytest.approx(b.val_bpb, rel=1e-9)
     assert abs(a.train_loss_first - np.log(tok.vocab_size)) < 0.2
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_parallel_muon_on_cpu_ranks_matches_the_replicated_optimizer(tmp_path, world):
+    """gloo ranks with different data: three steps of the sharded optimizer (gradient slots reduced to their owners, momentum
+    and Newton-Schulz on the owned slots only, all-gather of the new slots, clip factor from one scalar all-reduce) leave every
+    rank with the parameters the replicated all-reduce path produces. With three ranks the two-slot MLP banks leave the last
+    rank without a slot."""
+    script = tmp_path / "w.py"
+    script.write_text(f"""
+import sys
+sys.path.insert(0, {ROOT!r})
+import torch, torch.distributed as dist
+dist.init_process_group('gloo')
+rank, world = dist.get_rank(), dist.get_world_size()
+from parameter_golf_b200.models import gpt
+from parameter_golf_b200.spec import family_preset
+from parameter_golf_b200.train import OracleBackend
+def backend(mode):
+    s = family_preset('tiny_cpu')
+    s.train.world_size, s.train.rank = world, rank
+    s.train.distributed_optimizer_backend = mode
+    s.train.grad_clip_norm = 0.05                      # small enough to bite, so the agreed norm matters
+    s.validate()
+    return OracleBackend(s, gpt.init_params(s.model, 11)), s
+A, s = backend('all_reduce_replicated_muon')
+B, _ = backend('sharded_parallel_muon')
+assert B.sharded and not A.sharded
+g = torch.Generator().manual_seed(100 + rank)
+for step in range(3):
+    ids = torch.randint(0, s.model.vocab_size, (2, 64), generator=g)
+    tgt = torch.randint(0, s.model.vocab_size, (2, 64), generator=g)
+    A.train_step([(ids, tgt)], 1.0, 0.95, False)
+    B.train_step([(ids, tgt)], 1.0, 0.95, False)
+worst = max(float((A.params[k] - B.params[k]).abs().max()) for k in A.params)
+moved = float((A.params['qo_bank'] - gpt.init_params(s.model, 11)['qo_bank']).abs().max())
+own = [tuple(b.shape) for b in B.muon.bufs]
+full = B.muon.state_dict()['bufs']
+mom = max(float((f - a).abs().max()) for f, a in zip(full, A.muon.bufs))
+# every rank holds the same parameters
+flat = torch.cat([B.params[k].reshape(-1) for k in sorted(B.params)])
+ref = flat.clone()
+dist.broadcast(ref, 0)
+open({str(tmp_path)!r} + f'/res{{rank}}.txt', 'w').write(' '.join(str(x) for x in ('RES', rank, worst, moved, mom, float((flat - ref).abs().max()), own[2][0])))
+""")
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                          "--master-port", str(free_port()), str(script)], capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    rows = [open(tmp_path / f"res{r}.txt").read().split() for r in range(world)]      # one file per rank: prints of several ranks interleave
+    for _, rank, worst, moved, mom, spread, up_slots in rows:
+        assert float(moved) > 1e-3                                   # the optimizer did something
+        assert float(worst) < 2e-5 and float(mom) < 2e-5, (worst, mom)
+        assert float(spread) == 0.0
+        assert int(up_slots) == (1 if int(rank) < 2 else 0)         # tiny_cpu has two layers: two MLP slots

@@ -38,8 +38,12 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="parameter_golf_b200.evalcli")
     ap.add_argument("--artifact", required=True)
     ap.add_argument("--spec")
-    ap.add_argument("--family", default="record_11l")
-    ap.add_argument("--val-pattern")
+    ap.add_argument("--family", "--builtin", dest="family", default="record_11l")
+    ap.add_argument("--val-pattern", "--val-data", dest="val_pattern", help="validation shards (default: the spec's train.validation_data_pattern)")
+    # the reference binary's flag names (pg-eval/src/bin/run.rs:19-27); each one overrides the spec key it names
+    ap.add_argument("--stride", type=int)
+    ap.add_argument("--tokenizer-vocab")
+    ap.add_argument("--caseops-byte-sidecar")
     ap.add_argument("--bytes", choices=["tokenizer", "seeded", "placeholder"], default="seeded")
     ap.add_argument("--leaderboard", action="store_true")
     ap.add_argument("--device", default="cpu")
@@ -50,6 +54,16 @@ def main(argv=None) -> int:
     spec.apply_overrides(a.overrides)
     if a.max_tokens is not None:
         spec.eval.max_tokens = a.max_tokens
+    if a.stride is not None:
+        spec.eval.stride = a.stride
+    if a.tokenizer_vocab:
+        spec.eval.tokenizer_vocab_path = a.tokenizer_vocab
+        if a.bytes == "seeded":
+            a.bytes = "tokenizer"              # a tokenizer given on the command line is meant to be used
+    if a.caseops_byte_sidecar:
+        spec.eval.caseops_byte_sidecar_pattern = a.caseops_byte_sidecar
+    if not a.val_pattern:
+        a.val_pattern = spec.train.validation_data_pattern
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if a.device == "cuda":                        # one process per GPU: each rank evaluates on its own device
         import torch
@@ -76,7 +90,7 @@ def main(argv=None) -> int:
     m = spec.model
     params = load_artifact(blob, spec)
     if not a.val_pattern:
-        raise SystemExit("--val-pattern is required")
+        raise SystemExit("--val-pattern (or train.validation_data_pattern in the spec) is required")
     val = load_validation_tokens(a.val_pattern, m.eval_seq_len, spec.eval.max_tokens)
     luts = {"tokenizer": lambda: BpbLuts.from_sentencepiece(spec.eval.tokenizer_vocab_path, m.vocab_size),
             "seeded": lambda: BpbLuts.seeded(m.vocab_size, spec.eval.byte_table_seed),

@@ -75,3 +75,27 @@ def test_eval_cli_and_leaderboard_gate(tmp_path):
     assert kv["eval_kind"] == "sliding" and float(kv["val_bpb"]) > 0 and "eval_audit_json=" in out.stdout
     out = subprocess.run(base + ["--leaderboard", "--bytes", "placeholder", "--max-tokens", "300"], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
     assert out.returncode == 2 and "placeholder" in out.stderr and "full validation set" in out.stderr
+
+
+def test_eval_cli_accepts_the_reference_binary_flag_names(tmp_path):
+    """``--builtin``, ``--val-data``, ``--stride``, ``--tokenizer-vocab``, ``--caseops-byte-sidecar`` (pg-eval/src/bin/run.rs:19-27)
+    set the spec keys they name; with a byte sidecar the bits-per-byte denominator is the sidecar's sum."""
+    import json
+    from parameter_golf_b200.data.shards import write_shard, generate_markov_tokens
+    from parameter_golf_b200.quant.export import export_model
+    s = family_preset("tiny_cpu")
+    art = str(tmp_path / "a.pgrs")
+    export_model(s, gpt.init_params(s.model, 1), art)
+    n = 256 * 2 + 1
+    write_shard(str(tmp_path / "v_val_000000.bin"), generate_markov_tokens(n, 1024, 5))
+    write_shard(str(tmp_path / "v_val_bytes_000000.bin"), np.full(n, 3, dtype=np.uint16))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "parameter_golf_b200.evalcli", "--artifact", art, "--builtin", "tiny_cpu", "--val-data", str(tmp_path / "v_val_*.bin"),
+           "--stride", "128", "--caseops-byte-sidecar", str(tmp_path / "v_val_bytes_*.bin")]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr[-1500:]
+    kv = dict(l.split("=", 1) for l in out.stdout.splitlines() if "=" in l and not l.startswith("eval_audit_json"))
+    audit = json.loads([l for l in out.stdout.splitlines() if l.startswith("eval_audit_json=")][0].split("=", 1)[1])
+    assert audit["stride"] == 128
+    # 3 bytes per token everywhere: bits per byte = loss / ln 2 / 3
+    assert float(kv["val_bpb"]) == pytest.approx(float(kv["val_loss"]) / np.log(2) / 3, rel=1e-6)

@@ -523,13 +523,33 @@ class VariantRunner:
         return res
 
 
+# The reference trainer's command-line flags (pg-train/src/main.rs:58-122) and the spec keys they set. Every one of them can
+# also be given as a ``section.key=value`` override; the flags are for scripts written against that binary.
+REFERENCE_FLAGS = {
+    "--train-data": "train.train_data_pattern", "--val-data": "train.validation_data_pattern", "--rank": "train.rank",
+    "--world-size": "train.world_size", "--batch-tokens": "train.batch_tokens", "--seq-len": "train.seq_len",
+    "--total-iterations": "train.total_iterations", "--max-steps": "train.total_iterations",
+    "--max-wallclock-seconds": "train.max_wallclock_seconds", "--min-lr-scale": "train.min_lr_scale",
+    "--tokenizer-vocab": "eval.tokenizer_vocab_path", "--caseops-byte-sidecar": "eval.caseops_byte_sidecar_pattern",
+    "--eval-max-tokens": "eval.max_tokens", "--eval-stride": "eval.stride", "--distributed-optimizer": "train.distributed_optimizer_backend",
+    "--eval-adaptation": "eval.adaptation_backend", "--attn-out-gate-width": "model.attn_out_gate.width", "--quant-scheme": "quant.scheme",
+    "--prune-keep-ratio": "quant.prune_keep_ratio",
+}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="parameter_golf_b200.train")
     sub = ap.add_subparsers(dest="cmd", required=True)
     for name in ("run", "sweep", "plan"):
         sp = sub.add_parser(name)
         sp.add_argument("--spec")
-        sp.add_argument("--family", default=None)
+        sp.add_argument("--family", "--builtin", dest="family", default=None)
+        for flag, key in REFERENCE_FLAGS.items():
+            sp.add_argument(flag, dest="ref_" + key.replace(".", "__"), default=None, help=f"sets {key}")
+        sp.add_argument("--attn-out-gate", action="store_true", help="sets model.attn_out_gate.enabled=true")
+        sp.add_argument("--allow-unsupported-variants", action="store_true")
+        sp.add_argument("--attention-backend", default=None, help="accepted for compatibility: there is one attention path")
+        sp.add_argument("--fast-bank-updates", action="store_true", help="accepted for compatibility: bank updates are always fused")
         sp.add_argument("--families", default="tiny_cpu")
         sp.add_argument("--mode", default=None)
         sp.add_argument("--env", action="store_true", help="overlay train_gpt.py environment variable names")
@@ -549,6 +569,14 @@ def main(argv=None) -> int:
             spec.train.backend = a.backend
         if a.artifact:
             spec.train.artifact_path = a.artifact
+        ref = [f"{k[4:].replace('__', '.')}={v}" for k, v in vars(a).items() if k.startswith("ref_") and v is not None]
+        if a.attn_out_gate:
+            ref.append("model.attn_out_gate.enabled=true")
+        spec.apply_overrides(ref)
+        if any(o.startswith("train.seq_len=") for o in ref):          # the binary's --seq-len sets the model's lengths too
+            spec.model.train_seq_len = spec.model.eval_seq_len = spec.train.seq_len
+        if a.allow_unsupported_variants:
+            spec.allow_unsupported_variants = True
         spec.apply_overrides(a.overrides)
         if a.mode:
             spec.mode = a.mode

@@ -314,3 +314,23 @@ open({str(tmp_path)!r} + f'/res{{rank}}.txt', 'w').write(' '.join(str(x) for x i
         assert float(worst) < 2e-5 and float(mom) < 2e-5, (worst, mom)
         assert float(spread) == 0.0
         assert int(up_slots) == (1 if int(rank) < 2 else 0)         # tiny_cpu has two layers: two MLP slots
+
+
+def test_cli_accepts_the_reference_trainer_flag_names(tmp_path):
+    """pg-train/src/main.rs:58-122: --builtin, --seq-len, --batch-tokens, --max-steps, --eval-stride, --quant-scheme, ... map to
+    spec keys; `plan` shows the result without running anything."""
+    env = dict(os.environ, PGB_DATA_ROOT=str(tmp_path / "d"), PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-m", "parameter_golf_b200.train", "run", "--builtin", "tiny_cpu", "--mode", "smoke", "--seq-len", "128",
+                          "--batch-tokens", "1024", "--max-steps", "2", "--eval-stride", "32", "--eval-max-tokens", "512", "--quant-scheme",
+                          "gptq_lite_int6", "--min-lr-scale", "0.1", "--attention-backend", "cudnn", "--fast-bank-updates",
+                          "--artifact", str(tmp_path / "x.pgrs")], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    kv = dict(l.split("=", 1) for l in out.stdout.splitlines() if "=" in l and not l.startswith("record_audit_json"))
+    assert kv["steps"] == "2" and float(kv["val_bpb"]) > 0
+    from parameter_golf_b200.train import REFERENCE_FLAGS
+    s = family_preset("tiny_cpu")
+    for key in REFERENCE_FLAGS.values():                   # every mapped key exists in the spec
+        obj = s
+        for part in key.split("."):
+            assert hasattr(obj, part), key
+            obj = getattr(obj, part)

@@ -99,3 +99,27 @@ def test_eval_cli_accepts_the_reference_binary_flag_names(tmp_path):
     assert audit["stride"] == 128
     # 3 bytes per token everywhere: bits per byte = loss / ln 2 / 3
     assert float(kv["val_bpb"]) == pytest.approx(float(kv["val_loss"]) / np.log(2) / 3, rel=1e-6)
+
+
+def test_submission_manifest_counts_source_and_fails_closed(tmp_path):
+    from parameter_golf_b200 import submission as Sub
+    from parameter_golf_b200.quant.export import export_model
+    s = family_preset("tiny_cpu")
+    art = str(tmp_path / "a.pgrs")
+    export_model(s, gpt.init_params(s.model, 1), art)
+    code = tmp_path / "code"
+    (code / "pkg" / "__pycache__").mkdir(parents=True)
+    (code / "pkg" / "a.py").write_text("x = 1\n" * 100)
+    (code / "pkg" / "k.cu").write_text("// kernel\n" * 50)
+    (code / "pkg" / "lib.so").write_bytes(b"\0" * 5000)                 # build products are not source
+    (code / "pkg" / "__pycache__" / "a.pyc").write_bytes(b"\0" * 999)
+    man = Sub.build_manifest(art, [str(code)])
+    assert man["code_file_count"] == 2 and man["code_bytes"] == 600 + 500 and man["code_bytes_by_type"] == {".cu": 500, ".py": 600}
+    assert man["artifact"]["bytes"] == os.path.getsize(art) and man["artifact"]["tensors"] > 10
+    assert man["artifact"]["variant_fingerprint"] == f"{s.fingerprint():016x}"
+    assert man["under_budget"] and man["total_bytes"] == man["artifact"]["bytes"] + 1100
+    out = tmp_path / "m" / "submission.json"
+    assert Sub.main(["--artifact", art, "--code", str(code), "--out", str(out)]) == 0 and json.load(open(out))["code_bytes"] == 1100
+    assert Sub.main(["--artifact", art, "--code", str(code), "--limit", str(man["total_bytes"])]) == 1      # the limit itself is over budget
+    assert Sub.main(["--artifact", art, "--code", str(tmp_path / "missing")]) == 2
+    assert Sub.main(["--artifact", str(tmp_path / "none.pgrs"), "--code", str(code)]) == 2

@@ -88,3 +88,16 @@ def test_bank_shards_cover_every_slot_once_and_every_layer_gets_six_weight_pushe
                 assert seen == list(range(slots)), (bank, world)
             assert bumps == [6] * n, (n, world, bumps)
     assert shard_range(22, 7, 8) == (21, 22) and shard_range(11, 6, 8) == (11, 11)       # the last ranks of 8 own little or nothing
+
+
+def test_logit_chunk_rows_keeps_small_heads_whole_and_bounds_large_ones():
+    """The output head is chunked by rows only when [T, V] passes 2^27 elements; chunks are multiples of 128 rows, at least 128,
+    never more than T, and an explicit override wins."""
+    from parameter_golf_b200.plan import logit_chunk_rows
+    T = 98304
+    assert logit_chunk_rows(T, 1024) == T                       # 100 M logits: kept whole
+    r = logit_chunk_rows(T, 8192)
+    assert r < T and r % 128 == 0 and r * 8192 <= 1 << 26       # 805 M logits: chunks of at most 2^26
+    assert logit_chunk_rows(256, 65536) == 256                  # small batch: still whole
+    assert logit_chunk_rows(T, 1024, override=1000) == 896 and logit_chunk_rows(T, 1024, override=64) == 128
+    assert logit_chunk_rows(512, 1024, override=4096) == 512

@@ -91,6 +91,14 @@ def from_python_state_dict(m: ModelSpec, sd: Dict[str, torch.Tensor]) -> Dict[st
             p[k] = torch.stack([sd[f"blocks.{i}.{k}"].float() for i in range(n)])
     if "blocks.0.attn.q_gain" in sd:
         p["q_gain"] = torch.stack([sd[f"blocks.{i}.attn.q_gain"].float() for i in range(n)])
+    if "blocks.0.attn.vr_lambda" in sd:
+        p["vr_lambda"] = torch.stack([sd[f"blocks.{i}.attn.vr_lambda"].float() for i in range(n)])
+    if "blocks.0.dtg_gate.weight" in sd:
+        p["dtg_gate_weight"] = torch.stack([sd[f"blocks.{i}.dtg_gate.weight"].float().reshape(-1) for i in range(n)])
+        p["dtg_gate_bias"] = torch.stack([sd[f"blocks.{i}.dtg_gate.bias"].float().reshape(()) for i in range(n)])
+    heads = [sd[k].float() for k in sorted((k for k in sd if k.startswith("mtp_heads.") and k.endswith(".weight")), key=lambda k: int(k.split(".")[1]))]
+    if heads:
+        p["mtp_heads"] = torch.stack(heads)
     ls = [sd[k].float().reshape(()) for k in sorted(sd) if k.startswith("ve_layer_scales.")]
     if ls:
         p["ve_layer_scales"] = torch.stack(ls)
@@ -126,6 +134,16 @@ def to_python_state_dict(m: ModelSpec, p: Dict[str, torch.Tensor]) -> Dict[str, 
         for k in ("attn_scale", "mlp_scale", "resid_mix"):
             sd[f"blocks.{i}.{k}"] = p[k][i]
         sd[f"blocks.{i}.attn.q_gain"] = p["q_gain"][i]
+        if "vr_lambda" in p:
+            sd[f"blocks.{i}.attn.vr_lambda"] = p["vr_lambda"][i]
+        if "dtg_gate_weight" in p:
+            sd[f"blocks.{i}.dtg_gate.weight"] = p["dtg_gate_weight"][i].reshape(1, -1)
+            sd[f"blocks.{i}.dtg_gate.bias"] = p["dtg_gate_bias"][i].reshape(1)
+    if "mtp_heads" in p:
+        for k in range(p["mtp_heads"].shape[0]):
+            sd[f"mtp_heads.{k}.weight"] = p["mtp_heads"][k]
+    if "lm_head" in p:
+        sd["lm_head.weight"] = p["lm_head"]
     return sd
 
 

@@ -38,6 +38,15 @@ def test_name_map_roundtrip():
     assert "blocks.1.attn.q_gain" in sd and "bigram.proj.weight" in sd and "ve_layer_scales.1" in sd
     back = I.from_python_state_dict(s.model, sd)
     assert set(back) == set(p) and all(torch.equal(back[k], p[k]) for k in p)
+    # the optional parameters of the record script keep its names: value-residual lambdas, the update gate, the extra heads
+    m = s.model
+    m.value_residual, m.dtg, m.mtp_num_heads, m.tie_embeddings = True, True, 2, False
+    p = gpt.fill_deterministic(m)
+    sd = I.to_python_state_dict(m, p)
+    assert sd["blocks.1.attn.vr_lambda"].shape == (2,) and sd["blocks.0.dtg_gate.weight"].shape == (1, 64) and sd["blocks.0.dtg_gate.bias"].shape == (1,)
+    assert sd["mtp_heads.1.weight"].shape == (m.vocab_size, 64) and "lm_head.weight" in sd
+    back = I.from_python_state_dict(m, sd)
+    assert set(back) == set(p) and all(torch.equal(back[k], p[k]) for k in p)
     del sd["qo_bank"]
     with pytest.raises(KeyError):
         I.from_python_state_dict(s.model, sd)

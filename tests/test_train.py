@@ -334,3 +334,52 @@ def test_cli_accepts_the_reference_trainer_flag_names(tmp_path):
         for part in key.split("."):
             assert hasattr(obj, part), key
             obj = getattr(obj, part)
+
+
+def test_sharded_optimizer_state_survives_a_change_of_world_size(tmp_path):
+    """Elastic restart: the checkpointed optimizer state is the full momentum (gathered from the owners), so a job resumed on a
+    different number of ranks re-slices it; gathering it again gives back exactly what was saved."""
+    def launch(world, body):
+        script = tmp_path / f"w{world}.py"
+        script.write_text(f"""
+import sys
+sys.path.insert(0, {ROOT!r})
+import torch, torch.distributed as dist
+dist.init_process_group('gloo')
+rank, world = dist.get_rank(), dist.get_world_size()
+from parameter_golf_b200.models import gpt
+from parameter_golf_b200.spec import family_preset
+from parameter_golf_b200.train import OracleBackend
+s = family_preset('tiny_cpu')
+s.train.world_size, s.train.rank = world, rank
+s.train.distributed_optimizer_backend = 'sharded_parallel_muon'
+s.validate()
+path = {str(tmp_path / 'opt.pt')!r}
+""" + body)
+        env = dict(os.environ, PYTHONPATH=ROOT)
+        out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                              "--master-port", str(free_port()), str(script)], capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+        assert out.returncode == 0, out.stderr[-3000:]
+
+    launch(2, """
+B = OracleBackend(s, gpt.init_params(s.model, 11))
+g = torch.Generator().manual_seed(7 + rank)
+for _ in range(2):
+    ids = torch.randint(0, s.model.vocab_size, (2, 64), generator=g)
+    B.train_step([(ids, ids)], 1.0, 0.95, False)
+st = B.state_dict()                      # a collective
+if rank == 0:
+    torch.save({'opt': st, 'params': B.params}, path)
+""")
+    launch(3, """
+ck = torch.load(path, weights_only=False)
+B = OracleBackend(s, {k: v.clone() for k, v in ck['params'].items()})
+B.load_state_dict(ck['opt'])
+assert [tuple(b.shape)[0] for b in B.muon.bufs][:2] == ([2, 2] if rank < 2 else [0, 0])      # four attention slots over three ranks
+again = B.state_dict()
+for a, b in zip(again['muon']['bufs'], ck['opt']['muon']['bufs']):
+    assert torch.equal(a, b)
+assert float(ck['opt']['muon']['bufs'][0].abs().max()) > 0
+ids = torch.randint(0, s.model.vocab_size, (2, 64), generator=torch.Generator().manual_seed(rank))
+assert B.train_step([(ids, ids)], 1.0, 0.95, False) > 0
+""")

@@ -307,6 +307,47 @@ class RunSpec:
     def to_dict(self) -> dict:
         return dataclasses.asdict(self)
 
+    def describe_keys(self) -> list:
+        """Every ``section.key`` this spec accepts, with its type name and current value, in declaration order: the list a
+        ``section.key=value`` override or a TOML file may use."""
+        out = []
+
+        def walk(obj, prefix):
+            for f in dataclasses.fields(obj):
+                v = getattr(obj, f.name)
+                if dataclasses.is_dataclass(v):
+                    walk(v, prefix + f.name + ".")
+                else:
+                    tname = f.type if isinstance(f.type, str) else getattr(f.type, "__name__", str(f.type))
+                    out.append((prefix + f.name, tname, v))
+        walk(self, "")
+        return out
+
+    @staticmethod
+    def env_names() -> dict:
+        """``train_gpt.py`` environment variable name -> the spec key(s) `apply_env` sets from it, read off `apply_env` itself
+        so that the list cannot drift from the code."""
+        import inspect
+        import re
+        alias = {"m": "model", "t": "train", "q": "quant", "e": "eval"}
+        names: dict = {}
+        current = None
+        for line in inspect.getsource(RunSpec.apply_env).splitlines():
+            hit = re.search(r'has\("([A-Z0-9_]+)"\)', line)
+            if hit:
+                current = hit.group(1)
+                names.setdefault(current, [])
+            if current:
+                for var, key in re.findall(r"\b([mtqe])\.([a-z_][a-z0-9_.]*)\s*=(?!=)", line):
+                    k = f"{alias[var]}.{key}"
+                    if k not in names[current]:
+                        names[current].append(k)
+                if re.search(r"\bself\.name\s*=", line) and "name" not in names[current]:
+                    names[current].append("name")
+            if hit and ":" in line.split("has(")[1] and not line.rstrip().endswith(":"):
+                current = None              # one-line form: the assignment was on the same line
+        return names
+
     def to_toml(self) -> str:
         return _to_toml(self.to_dict())
 

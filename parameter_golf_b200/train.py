@@ -540,6 +540,7 @@ REFERENCE_FLAGS = {
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="parameter_golf_b200.train")
     sub = ap.add_subparsers(dest="cmd", required=True)
+    sub.add_parser("keys", help="list every spec key (type, default) and the train_gpt.py environment names that map onto them")
     for name in ("run", "sweep", "plan"):
         sp = sub.add_parser(name)
         sp.add_argument("--spec")
@@ -557,6 +558,17 @@ def main(argv=None) -> int:
         sp.add_argument("--artifact", default=None)
         sp.add_argument("overrides", nargs="*")
     a = ap.parse_args(argv)
+    if a.cmd == "keys":
+        spec = RunSpec()
+        by_key: dict = {}
+        for env_name, keys in RunSpec.env_names().items():
+            for k in keys:
+                by_key.setdefault(k, []).append(env_name)
+        flags = {v: k for k, v in REFERENCE_FLAGS.items()}
+        for key, tname, default in spec.describe_keys():
+            extra = "".join(f"  env {n}" for n in by_key.get(key, [])) + (f"  flag {flags[key]}" if key in flags else "")
+            print(f"{key} ({tname}) = {default!r}{extra}")
+        return 0
     fams = [a.family] if (a.cmd != "sweep" and a.family) else ([None] if a.cmd != "sweep" else a.families.split(","))
     rc = 0
     for fam in fams:

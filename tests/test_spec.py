@@ -101,3 +101,30 @@ def test_optional_record_ideas_are_cpu_only_and_read_from_the_environment():
     assert e.model.value_residual and e.model.mtp_num_heads == 3 and e.model.mtp_loss_weight == 0.1
     assert e.model.rope.mode == "yarn" and e.model.rope.yarn_max_len == 4096
     e.validate()
+
+
+def test_key_listing_and_environment_names_follow_the_code():
+    """`describe_keys` walks the dataclasses; `env_names` is read off `apply_env` itself: every environment name maps to keys
+    that exist, and setting the variable really changes one of them."""
+    from parameter_golf_b200.spec import RunSpec
+    keys = {k for k, _, _ in RunSpec().describe_keys()}
+    assert {"model.num_layers", "model.rope.yarn_max_len", "train.lawa_k", "quant.float_storage", "eval.stride", "mode"} <= keys
+    env = RunSpec.env_names()
+    assert env["NUM_LAYERS"] == ["model.num_layers"] and env["TRAIN_SEQ_LEN"] == ["train.seq_len", "model.train_seq_len"]
+    assert env["RUN_ID"] == ["name"] and "model.fp8_qat" in env["FP_STORAGE"]
+    for name, mapped in env.items():
+        assert mapped, name
+        for k in mapped:
+            assert k in keys, (name, k)
+    sample = {"NUM_LAYERS": "7", "MUON_WD": "0.01", "EVAL_STRIDE": "32", "LAWA_K": "4"}
+    before = dict((k, v) for k, _, v in RunSpec().describe_keys())
+    after = dict((k, v) for k, _, v in RunSpec().apply_env(sample).describe_keys())
+    for name in sample:
+        assert any(before[k] != after[k] for k in env[name]), name
+
+
+def test_keys_subcommand_prints_every_key(capsys):
+    from parameter_golf_b200.train import main
+    assert main(["keys"]) == 0
+    out = capsys.readouterr().out
+    assert "model.num_layers (int) = 11  env NUM_LAYERS" in out and "train.seq_len (int) = 2048  env TRAIN_SEQ_LEN  flag --seq-len" in out

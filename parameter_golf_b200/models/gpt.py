@@ -179,7 +179,10 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
     wk, wv = p["kv_bank"][i], p["kv_bank"][n + i]
     wu, wd = p["mlp_up_bank"][i], p["mlp_down_bank"][i]
     if qat:
-        wq, wo, wk, wv, wu, wd = (R.fake_quant_int6_ste(w) for w in (wq, wo, wk, wv, wu, wd))
+        if m.qat_kind == "ternary":
+            wq, wo, wk, wv, wu, wd = (R.fake_quant_ternary_ste(w, m.qat_ternary_group) for w in (wq, wo, wk, wv, wu, wd))
+        else:
+            wq, wo, wk, wv, wu, wd = (R.fake_quant_int6_ste(w) for w in (wq, wo, wk, wv, wu, wd))
     s_l = layer_ln_scale(m, i)
     mix = p["resid_mix"][i].to(dt)
     x_in = mix[0][None, None, :] * x + mix[1][None, None, :] * x0

@@ -167,6 +167,19 @@ def fake_quant_fp8_ste(w: torch.Tensor) -> torch.Tensor:
     return w + (wq - w).detach()
 
 
+def fake_quant_ternary_ste(w: torch.Tensor, group: int = 128) -> torch.Tensor:
+    """Straight-through estimator of BitNet b1.58 weights: the forward uses ``s * q`` with ``q`` in {-1, 0, 1} and one scale per
+    group of ``group`` input columns, computed by the same rule as the ternary export (`quant.ternary.quantize_ternary`, scale
+    fitted to the non-zero codes), so what is trained is what is stored; the gradient passes to ``w``. Matrices or stacks of
+    matrices (the last axis is the input dimension)."""
+    from ..quant.ternary import dequantize_ternary, quantize_ternary
+    with torch.no_grad():
+        w2 = _f(w).reshape(-1, w.shape[-1])
+        q, s = quantize_ternary(w2, group)
+        wq = dequantize_ternary(q, s.half().float(), group).reshape(w.shape).to(w.dtype)       # scales are stored as fp16
+    return w + (wq - w).detach()
+
+
 def fake_quant_int6_ste(w: torch.Tensor) -> torch.Tensor:
     """Late-QAT straight-through estimator: per-row ``s = max(|w|)/31`` (floored at 1/31),
     ``w_q = clamp(round(w/s), -32, 31) * s``; forward uses ``w_q`` and the gradient passes to ``w``

@@ -60,7 +60,7 @@ def metadata_json(spec: RunSpec, bits: Dict[str, int]) -> str:
         "num_kv_heads": m.num_kv_heads, "head_dim": m.head_dim, "mlp_dim": m.mlp_dim,
         "attn_out_gate_enabled": int(m.attn_out_gate.enabled), "attn_out_gate_width": m.attn_out_gate.width,
         "sparse_attn_gate_enabled": int(m.sparse_attn_gate.enabled), "sparse_attn_gate_width": m.sparse_attn_gate.width,
-        "groups": {g: bits[g] for g in GROUPS}, "code_storage": q.code_storage,
+        "groups": {g: bits[g] for g in GROUPS}, "code_storage": q.code_storage, "scheme": q.scheme, "ternary_group": q.ternary_group,
     }
     return json.dumps(md, separators=(",", ":"))
 
@@ -77,7 +77,11 @@ def quantize_groups(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed:
         w = views[g].detach().cpu().float()
         if spec.quant.prune_keep_ratio is not None and g != "tok_emb":
             w = prune_rows(w, spec.quant.prune_keep_ratio)
-        out[g] = quantize_rows(w, bits[g])
+        if spec.quant.scheme == "ternary_b158" and g != "tok_emb":
+            from .ternary import quantize_ternary
+            out[g] = quantize_ternary(w, spec.quant.ternary_group)          # codes in {-1, 0, 1}, scales [rows, groups]
+        else:
+            out[g] = quantize_rows(w, bits[g])
     return out, bits
 
 
@@ -103,7 +107,12 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
             recs.append(_f16(f"{g}.lqer.a.scale", f.a_s))
             recs.append(C.TensorRecord(f"{g}.lqer.b.weight", tuple(f.b_q.shape), "i8", C.pack_bits(f.b_q.numpy(), spec.quant.lqer.b_bits)))
             recs.append(_f16(f"{g}.lqer.b.scale", f.b_s))
-        recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", _store_codes(q, bits[g], spec.quant.code_storage)))
+        if spec.quant.scheme == "ternary_b158" and g != "tok_emb":
+            from .ternary import pack_trits
+            data = q.cpu().numpy().astype(np.int8).tobytes() if spec.quant.code_storage == "bytes" else pack_trits(q.cpu().numpy())
+            recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", data))        # five codes per byte, base 3
+        else:
+            recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", _store_codes(q, bits[g], spec.quant.code_storage)))
         recs.append(_f16(f"{g}.scale", s16))
     if m.bigram.enabled:
         fs = spec.quant.float_storage
@@ -150,7 +159,7 @@ def export_model(spec: RunSpec, params: Dict[str, torch.Tensor], path: Optional[
         qs, bits = quantize_groups(spec, params, precomputed)
         blob = C.compress_payload(build_artifact(spec, params, quantized=(qs, bits)), spec.quant.compression)
         limit = spec.quant.target_artifact_bytes - code_bytes()
-        if spec.quant.prune_to_target and spec.quant.scheme != "none" and len(blob) > limit > 0:
+        if spec.quant.prune_to_target and spec.quant.scheme not in ("none", "ternary_b158") and len(blob) > limit > 0:
             # +-1 pruning to the byte budget (the 2026-03-25 record's selective prune, train_gpt.py:1997-2040): the codes whose
             # removal costs least squared error go to zero until the compressed artifact fits beside the code
             from .quantize import selective_prune_to_target
@@ -233,6 +242,13 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
         bits = 6 if legacy else int(md["groups"][g])
         wrec, srec = by[f"{g}.weight"], by[f"{g}.scale"]
         rows, cols = wrec.dims
+        if md.get("scheme") == "ternary_b158" and g != "tok_emb":
+            from .ternary import dequantize_ternary, unpack_trits
+            if len(wrec.data) == rows * cols:
+                q = torch.from_numpy(np.frombuffer(wrec.data, dtype=np.int8).copy().reshape(rows, cols))
+            else:
+                q = torch.from_numpy(unpack_trits(wrec.data, rows * cols).copy().reshape(rows, cols))
+            return dequantize_ternary(q, torch.from_numpy(_np(srec).astype(np.float32)), int(md.get("ternary_group", 128)))
         if (legacy or md.get("code_storage") == "bytes") and len(wrec.data) == rows * cols:
             q = torch.from_numpy(np.frombuffer(wrec.data, dtype=np.int8).astype(np.int32).reshape(rows, cols))
         else:

@@ -27,7 +27,7 @@ RUN_MODES = ("smoke", "proxy", "record_shaped_proxy", "record")
 TRAIN_BACKENDS = ("cpu", "cuda_single", "cuda_single_parity", "cuda_distributed")
 DIST_OPT_BACKENDS = ("all_reduce_replicated_muon", "sharded_parallel_muon")
 QUANT_SCHEMES = ("none", "gptq_lite_int6", "mixed_int5_int6", "aggressive", "tight_int7_int4", "full_gptq_int6",
-                 "int8_zlib")       # int8_zlib: the baseline trainer's per-row int8 + zlib-9 export (train_gpt.py:342-422)
+                 "int8_zlib", "ternary_b158")       # int8_zlib: the baseline trainer's per-row int8 + zlib-9 export (train_gpt.py:342-422)
 COMPRESSION_MODES = ("none", "zstd22", "lzma9", "pergroup")
 CALIBRATION_MODES = ("disabled", "self_generated")
 ADAPTATION_BACKENDS = ("none", "cpu_q_only", "gpu_lora_phased", "full_sgd", "lact", "slot")
@@ -37,6 +37,7 @@ FAMILIES = (
     "hybrid_competitive_sp8192", "frontier_1855_like",
     # families of this framework, named after the benchmark configurations
     "tiny_cpu", "baseline_9l", "record_11l",
+    "ternary_10l",       # the 2026-03-24 ternary record's shape: autograd path only (head_dim 96, ternary QAT)
 )
 
 
@@ -125,6 +126,8 @@ class ModelSpec:
     mtp_num_heads: int = 0                # extra output heads that predict the tokens 2, 3, ... ahead, training only, not exported
     mtp_loss_weight: float = 0.2
     dtg: bool = False                     # per-block scalar gate on the block's update, sigmoid(w . x_in + b) read from the detached input (DTG_ENABLED)
+    qat_kind: str = "int6"                # what QAT simulates in the bank matrices: int6 rows, or ternary codes with one scale per group
+    qat_ternary_group: int = 128          # qat_kind = ternary: input columns per scale (keep equal to quant.ternary_group)
     fp8_qat: bool = False                 # while QAT is on, the small 2-D float tensors (bigram / value-embedding tables and
                                           # projections, an untied head) go through an FP8 e4m3 round trip (FP_STORAGE=FP8)
 
@@ -239,6 +242,7 @@ class QuantSpec:
                                         # bytes: one int8 per code (the Python records' container: the entropy coder then sees the code distribution)
     prune_to_target: bool = True        # zero the cheapest +-1 codes until artifact + code fit target_artifact_bytes
     prune_max_magnitude: int = 1        # widen the candidates to |code| <= this when the +-1 codes are not enough
+    ternary_group: int = 128            # scheme ternary_b158 (and model.qat_kind = ternary): input columns per scale
     float_storage: str = "f16"          # f16 | fp8: how the 2-D float tensors that are not quantised to integer codes are stored
                                         # (fp8 = e4m3, one byte per element; 1-D control tensors stay f16)
     matrix_bits: int = 6
@@ -508,6 +512,12 @@ class RunSpec:
         chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat or m.dtg) or t.backend == "cpu",
             "model.value_residual, model.mtp_num_heads, model.dtg and model.fp8_qat run on train.backend=cpu only (the CUDA engine has no path for them)")
         chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
+        chk(m.qat_kind in ("int6", "ternary"), "model.qat_kind must be int6 or ternary")
+        chk(m.qat_kind != "ternary" or t.backend == "cpu", "model.qat_kind=ternary runs on train.backend=cpu only")
+        chk(q.ternary_group >= 8, "quant.ternary_group must be >= 8")
+        chk(m.qat_kind != "ternary" or q.scheme != "ternary_b158" or m.qat_ternary_group == q.ternary_group,
+            "model.qat_ternary_group and quant.ternary_group must agree: what is trained is what is stored")
+        chk(q.scheme != "ternary_b158" or not q.lqer.enabled, "the ternary scheme has no low-rank residual")
         chk(not t.lawa_enabled or (t.lawa_k >= 1 and t.lawa_freq >= 1), "train.lawa_k and train.lawa_freq must be >= 1")
         chk(m.vocab_size <= 65536, "token ids are uint16: vocab_size must be <= 65536")
         chk(not (m.attn_out_gate.enabled and m.sparse_attn_gate.enabled),
@@ -602,6 +612,24 @@ def family_preset(family: str) -> RunSpec:
         s.quant.code_storage, s.quant.prune_max_magnitude = "bytes", 3      # the Python records' container and prune-to-budget step
         s.eval.legal_score_first = True
         s.eval.adaptation_backend = "full_sgd"
+    elif family == "ternary_10l":
+        # records/track_10min_16mb/2026-03-24_74M_Ternary_UNet_FP8_10L_8192BPE_YaRN_NeoMuon (README "Architecture", run_cuda_ternary.sh):
+        # ternary weights trained with a straight-through estimator from the first step, FP8 for the rest, YaRN, three
+        # Newton-Schulz steps, sliding evaluation at stride 16. Its factored embedding and polynomial soft-cap are not modelled.
+        m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads = 8192, 10, 768, 8, 4
+        m.mlp_mult, m.activation = 4.0, "relu_sq"
+        m.train_seq_len = m.eval_seq_len = 1024
+        m.rope = RopeSpec("yarn", 0, 5000.0, 2048, 1024)
+        m.logit_softcap, m.qk_gain_init = 10.0, 2.25
+        m.qat_kind, m.fp8_qat = "ternary", True
+        t.backend, t.batch_tokens, t.seq_len = "cpu", 524_288, 1024
+        t.qat_enabled, t.late_qat_threshold = True, 0.0
+        t.matrix_lr, t.scalar_lr, t.tied_embed_lr, t.head_lr = 0.04, 0.02, 0.02, 0.02
+        t.muon_wd, t.muon_ns_steps, t.muon_momentum_warmup_steps = 0.0, 3, 500
+        t.total_iterations, t.warmup_steps, t.max_wallclock_seconds = 10000, 5, 599.0
+        s.quant.scheme, s.quant.compression, s.quant.float_storage = "ternary_b158", "lzma9", "fp8"
+        s.quant.prune_to_target = False
+        s.eval.stride = 16
     else:
         m.vocab_size = 8192
         m.num_layers, m.mlp_mult, m.activation = 11, 3.0, "leaky_relu_sq"

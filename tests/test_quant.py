@@ -382,3 +382,38 @@ def test_fp8_qat_forward_uses_the_rounded_tables_and_passes_gradients_straight_t
     w = p["bigram_proj"].clone().requires_grad_(True)
     (g,) = torch.autograd.grad(R.fake_quant_fp8_ste(w).sum(), w)
     assert torch.equal(g, torch.ones_like(w))
+
+
+def test_ternary_scheme_exports_what_ternary_qat_trains(tmp_path):
+    """quant.scheme = ternary_b158 with model.qat_kind = ternary: the artifact holds base-3 packed codes and per-group fp16
+    scales, reloads to exactly the weights the QAT forward used, so the loss after the round trip equals the QAT loss (the
+    record's "no round-trip gap"), and costs about 1.6 bits per bank weight before compression."""
+    from parameter_golf_b200.ops import reference as R
+    from parameter_golf_b200.quant.export import build_artifact
+    s = family_preset("tiny_cpu")
+    s.apply_overrides(["quant.scheme=ternary_b158", "quant.compression=lzma9", "quant.ternary_group=64", "model.qat_kind=ternary",
+                       "model.qat_ternary_group=64", "quant.prune_to_target=false"])
+    s.validate()
+    m = s.model
+    p = gpt.fill_deterministic(m)
+    blob = export_model(s, p, str(tmp_path / "t.pgrs"))
+    back = load_artifact(blob, s)
+    for bank in ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank"):
+        want = R.fake_quant_ternary_ste(p[bank], 64)
+        assert torch.allclose(back[bank], want, atol=1e-7), bank
+        vals = (back[bank].reshape(-1, 64) / back[bank].reshape(-1, 64).abs().amax(-1, keepdim=True).clamp_min(1e-12)).round().unique()
+        assert set(vals.tolist()) <= {-1.0, 0.0, 1.0}
+    ids = torch.randint(0, m.vocab_size, (2, 32))
+    trained = dict(back, **{b: p[b] for b in ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank")})      # the fp32 banks QAT trains
+    qat_loss = gpt.gpt_forward(m, trained, ids, ids, qat=True)
+    assert torch.allclose(gpt.gpt_forward(m, back, ids, ids), qat_loss, atol=1e-5)
+    raw = build_artifact(s, p)
+    bank_params = sum(p[b].numel() for b in ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank"))
+    emb_bytes = p["tok_emb"].numel() + 2 * p["tok_emb"].shape[0]
+    assert (len(raw) - emb_bytes) * 8 / bank_params < 2.0            # 1.6 bits of codes + scales and small tensors
+    s.quant.code_storage = "bytes"
+    assert torch.equal(load_artifact(export_model(s, p), s)["qo_bank"], back["qo_bank"])
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["model.qat_kind=ternary"]).validate()
+    t = family_preset("ternary_10l").validate()
+    assert t.model.head_dim == 96 and t.quant.scheme == "ternary_b158" and t.train.qat_enabled and t.model.rope.mode == "yarn"

@@ -431,3 +431,30 @@ if dist.get_rank() == 0:
     # training losses differ; the model does not: same global gradient and optimizer state, so the same validation loss up to
     # what the int6 export makes of last-bit differences in the weights (the single-process resume test allows the same)
     assert abs(resumed["val_loss"] - full["val_loss"]) < 1e-2, (resumed["val_loss"], full["val_loss"])
+
+
+def test_ternary_family_trains_with_its_estimator_and_round_trips(tmp_path, monkeypatch):
+    """Ternary QAT from the first step, ternary export with xz, FP8 storage of the small tensors, YaRN tables, three
+    Newton-Schulz steps: the pieces of the ternary record's recipe through the trainer at a toy size."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.apply_overrides(["model.qat_kind=ternary", "model.qat_ternary_group=64", "quant.ternary_group=64", "quant.scheme=ternary_b158",
+                       "quant.compression=lzma9", "quant.float_storage=fp8", "quant.prune_to_target=false", "train.qat_enabled=true",
+                       "train.muon_ns_steps=3", "model.rope.mode=yarn", "model.rope.dims=16", "model.rope.yarn_max_len=1024",
+                       "model.rope.yarn_train_len=256", "model.bigram.enabled=true", "model.bigram.vocab_size=128", "model.bigram.dim=32",
+                       "model.fp8_qat=true"])
+    s.train.total_iterations = 4
+    s.train.artifact_path = str(tmp_path / "t.pgrs")
+    s.eval.max_tokens = 512
+    import parameter_golf_b200.train as tr
+    monkeypatch.setattr(tr, "mode_max_steps", lambda spec, mode: 4)
+    r = quiet(s)
+    res = r.run()
+    assert res.steps == 4 and np.isfinite(res.val_loss) and res.budget_ok
+    blob = open(s.train.artifact_path, "rb").read()
+    assert blob[:6] == bytes([0xFD]) + b"7zXZ" + bytes([0])           # an xz stream
+    back = load_artifact(blob, s)
+    codes = (back["mlp_up_bank"].reshape(-1, 64) / back["mlp_up_bank"].reshape(-1, 64).abs().amax(-1, keepdim=True).clamp_min(1e-12)).round()
+    assert set(codes.unique().tolist()) <= {-1.0, 0.0, 1.0}
+    assert torch.equal(back["bigram_embed"], back["bigram_embed"].to(torch.float8_e4m3fn).float())      # stored as e4m3

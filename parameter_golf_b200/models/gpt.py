@@ -31,7 +31,7 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
     n, d, kv, mlp, H = m.num_layers, m.model_dim, m.kv_dim, m.mlp_dim, m.num_heads
     enc = n // 2
     sh = {
-        "tok_emb": (m.vocab_size, d),
+        "tok_emb": (m.vocab_size, m.embed_dim if m.embed_dim > 0 else d),
         "qo_bank": (2 * n, d, d),
         "kv_bank": (2 * n, kv, d),
         "mlp_up_bank": (n, mlp, d),
@@ -62,6 +62,9 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
         sh["sparse_attn_gate_weight"] = (n, H, m.sparse_attn_gate.width)
     if not m.tie_embeddings:
         sh["lm_head"] = (m.vocab_size, d)
+    if m.embed_dim > 0:
+        sh["embed_proj_in"] = (d, m.embed_dim)           # embedding -> model width at the input
+        sh["embed_proj_out"] = (m.embed_dim, d)          # model width -> embedding before the tied output product
     if m.value_residual:
         sh["vr_lambda"] = (n, 2)
     if m.dtg:
@@ -111,6 +114,9 @@ def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float3
         p["ve_layer_scales"].fill_(1.0)
     if "attn_gate_bias" in p:
         p["attn_gate_bias"].fill_(4.0)
+    if "embed_proj_in" in p:
+        p["embed_proj_in"] = _orthogonal(d, m.embed_dim, g)
+        p["embed_proj_out"] = p["embed_proj_in"].t().contiguous().clone()     # starts as the transpose: the tied pair is consistent
     if "vr_lambda" in p:
         p["vr_lambda"].fill_(0.5)
     if "dtg_gate_bias" in p:
@@ -150,6 +156,24 @@ def _small(m: ModelSpec, p, name: str, qat: bool):
     """A small 2-D float tensor as the forward sees it: through the FP8 round trip while QAT is on and the spec stores it so."""
     w = p[name]
     return R.fake_quant_fp8_ste(w) if (qat and m.fp8_qat) else w
+
+
+def embed_tokens(m: ModelSpec, p, ids, dt, qat: bool = False):
+    """Token embedding at model width: a table row, through the input projection when the embedding is factored."""
+    x = p["tok_emb"][ids].to(dt)
+    if m.embed_dim > 0:
+        x = F.linear(x, _small(m, p, "embed_proj_in", qat).to(dt))
+    return x
+
+
+def output_logits(m: ModelSpec, p, h, qat: bool = False):
+    """Un-capped logits of final hidden states: the tied table (after the output projection when the embedding is factored) or
+    the untied head."""
+    if not m.tie_embeddings:
+        return F.linear(h, _small(m, p, "lm_head", qat).to(h.dtype))
+    if m.embed_dim > 0:
+        h = F.linear(h, _small(m, p, "embed_proj_out", qat).to(h.dtype))
+    return F.linear(h, p["tok_emb"].to(h.dtype))
 
 
 def layer_ln_scale(m: ModelSpec, layer: int) -> float:
@@ -240,7 +264,7 @@ def gpt_hidden(m: ModelSpec, p, ids: torch.Tensor, qat: bool = False, lora=None,
     """Final-norm hidden states [B,T,d]."""
     dt = dtype or p["tok_emb"].dtype
     B, T = ids.shape
-    x = p["tok_emb"][ids].to(dt)
+    x = embed_tokens(m, p, ids, dt, qat)
     if m.bigram.enabled:
         bg = _small(m, p, "bigram_embed", qat)[R.bigram_hash(ids, m.bigram.vocab_size)].to(dt)
         if "bigram_proj" in p:
@@ -275,8 +299,7 @@ def gpt_hidden(m: ModelSpec, p, ids: torch.Tensor, qat: bool = False, lora=None,
 def gpt_logits(m: ModelSpec, p, ids, qat: bool = False, lora=None, dtype=None):
     """Soft-capped logits [B,T,V]."""
     h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
-    w = p["tok_emb"] if m.tie_embeddings else p["lm_head"]
-    z = F.linear(h, w.to(h.dtype))
+    z = output_logits(m, p, h, qat)
     return m.logit_softcap * torch.tanh(z.float() / m.logit_softcap)
 
 
@@ -303,8 +326,7 @@ def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dty
     by the sum of the weights (complementary training, ``pg-kernels/src/complementary.rs:226-240``). ``mtp`` (training steps
     only) adds ``mtp_loss_weight`` times the multi-token-prediction loss of the extra heads."""
     h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
-    w = p["tok_emb"] if m.tie_embeddings else _small(m, p, "lm_head", qat)
-    z = F.linear(h, w.to(h.dtype))
+    z = output_logits(m, p, h, qat)
     extra = None
     if mtp and reduction == "mean" and m.mtp_num_heads > 0 and m.mtp_loss_weight > 0.0 and "mtp_heads" in p:
         extra = mtp_loss(m, p, h, targets)

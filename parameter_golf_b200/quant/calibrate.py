@@ -43,7 +43,7 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
     slope = m.leaky_slope if m.activation == "leaky_relu_sq" else 0.0
     for t in range(seq_len - 1):
         ids = toks[:, t]
-        x = p["tok_emb"][ids].to(dtype)
+        x = gpt.embed_tokens(m, p, ids, dtype)
         if m.bigram.enabled:
             if t == 0:
                 b = torch.full_like(ids, m.bigram.vocab_size - 1)
@@ -114,8 +114,7 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
             if unet and i < enc:
                 skips.append(x)
         hfin = R.rms_norm(x)
-        w = p["tok_emb"] if m.tie_embeddings else p["lm_head"]
-        z = m.logit_softcap * torch.tanh(F.linear(hfin, w.to(dtype)).float() / m.logit_softcap)
+        z = m.logit_softcap * torch.tanh(gpt.output_logits(m, p, hfin).float() / m.logit_softcap)
         probs = torch.softmax(z / temperature, dim=-1)
         toks[:, t + 1] = torch.multinomial(probs, 1, generator=g)[:, 0]
     return toks

@@ -148,6 +148,9 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
         recs.append(_f16("ve_layer_scales", params["ve_layer_scales"]))
     if not m.tie_embeddings:
         recs.append(_flt("lm_head", params["lm_head"], spec.quant.float_storage))
+    if m.embed_dim > 0:
+        recs.append(_flt("embed_proj_in", params["embed_proj_in"], spec.quant.float_storage))
+        recs.append(_flt("embed_proj_out", params["embed_proj_out"], spec.quant.float_storage))
     return C.write_pgrs(recs, metadata_json(spec, bits))
 
 
@@ -276,7 +279,7 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
     p["tok_emb"] = group("tok_emb")
     shapes = param_shapes(m)
     for name in ("bigram_embed", "bigram_proj", "bigram_scale", "smear_gate", "skip_weights", "ve_embed", "ve_proj",
-                 "ve_scale", "ve_layer_scales", "lm_head"):
+                 "ve_scale", "ve_layer_scales", "lm_head", "embed_proj_in", "embed_proj_out"):
         if name in shapes:
             if name not in by:
                 raise C.ArtifactError(f"artifact is missing tensor {name}")

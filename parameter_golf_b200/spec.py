@@ -126,6 +126,8 @@ class ModelSpec:
     mtp_num_heads: int = 0                # extra output heads that predict the tokens 2, 3, ... ahead, training only, not exported
     mtp_loss_weight: float = 0.2
     dtg: bool = False                     # per-block scalar gate on the block's update, sigmoid(w . x_in + b) read from the detached input (DTG_ENABLED)
+    embed_dim: int = 0                    # > 0: factored tied embedding, tok_emb [V, embed_dim] with learned projections to and from
+                                          # model_dim (the ternary record's 254-wide bottleneck); 0 = tok_emb [V, model_dim]
     qat_kind: str = "int6"                # what QAT simulates in the bank matrices: int6 rows, or ternary codes with one scale per group
     qat_ternary_group: int = 128          # qat_kind = ternary: input columns per scale (keep equal to quant.ternary_group)
     fp8_qat: bool = False                 # while QAT is on, the small 2-D float tensors (bigram / value-embedding tables and
@@ -452,6 +454,7 @@ class RunSpec:
             m.bigram.enabled = m.bigram.vocab_size > 0
         if has("BIGRAM_DIM"): m.bigram.dim = I("BIGRAM_DIM")
         if has("XSA_LAST_N"): m.xsa_last_n = I("XSA_LAST_N")
+        if has("EMBED_DIM"): m.embed_dim = I("EMBED_DIM")
         if has("VALUE_RESIDUAL"): m.value_residual = B("VALUE_RESIDUAL")
         if has("DTG_ENABLED"): m.dtg = B("DTG_ENABLED")
         if has("MTP_NUM_HEADS"): m.mtp_num_heads = I("MTP_NUM_HEADS")
@@ -509,8 +512,10 @@ class RunSpec:
         chk(m.logit_softcap > 0, "logit_softcap must be positive")
         chk(m.xsa_last_n <= m.num_layers, "xsa_last_n exceeds num_layers")
         chk(m.mtp_num_heads >= 0 and m.mtp_loss_weight >= 0.0, "mtp_num_heads and mtp_loss_weight must be >= 0")
-        chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat or m.dtg) or t.backend == "cpu",
-            "model.value_residual, model.mtp_num_heads, model.dtg and model.fp8_qat run on train.backend=cpu only (the CUDA engine has no path for them)")
+        chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat or m.dtg or m.embed_dim > 0) or t.backend == "cpu",
+            "model.value_residual, model.mtp_num_heads, model.dtg, model.embed_dim and model.fp8_qat run on train.backend=cpu only "
+            "(the CUDA engine has no path for them)")
+        chk(m.embed_dim == 0 or (m.tie_embeddings and 0 < m.embed_dim <= m.model_dim), "model.embed_dim needs tied embeddings and 0 < embed_dim <= model_dim")
         chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
         chk(m.qat_kind in ("int6", "ternary"), "model.qat_kind must be int6 or ternary")
         chk(m.qat_kind != "ternary" or t.backend == "cpu", "model.qat_kind=ternary runs on train.backend=cpu only")
@@ -615,12 +620,13 @@ def family_preset(family: str) -> RunSpec:
     elif family == "ternary_10l":
         # records/track_10min_16mb/2026-03-24_74M_Ternary_UNet_FP8_10L_8192BPE_YaRN_NeoMuon (README "Architecture", run_cuda_ternary.sh):
         # ternary weights trained with a straight-through estimator from the first step, FP8 for the rest, YaRN, three
-        # Newton-Schulz steps, sliding evaluation at stride 16. Its factored embedding and polynomial soft-cap are not modelled.
+        # Newton-Schulz steps, the 254-wide factored tied embedding, sliding evaluation at stride 16. Its polynomial soft-cap is not modelled (tanh instead).
         m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads = 8192, 10, 768, 8, 4
         m.mlp_mult, m.activation = 4.0, "relu_sq"
         m.train_seq_len = m.eval_seq_len = 1024
         m.rope = RopeSpec("yarn", 0, 5000.0, 2048, 1024)
         m.logit_softcap, m.qk_gain_init = 10.0, 2.25
+        m.embed_dim = 254
         m.qat_kind, m.fp8_qat = "ternary", True
         t.backend, t.batch_tokens, t.seq_len = "cpu", 524_288, 1024
         t.qat_enabled, t.late_qat_threshold = True, 0.0

@@ -219,3 +219,40 @@ def test_cached_generation_follows_the_full_forward(value_residual):
     pred = logits.argmax(-1)[:, :-1]
     same = (pred == toks[:, 1:]) | ~decided[:, :-1]
     assert bool(same.all()) and int(decided[:, :-1].sum()) >= 20
+
+
+def test_factored_tied_embedding_projects_in_and_out():
+    """model.embed_dim: the table is [V, e]; the input goes through embed_proj_in, the tied output through embed_proj_out
+    first. With e = d and identity projections the model is the unfactored one; the projections get gradients; the cached
+    sampler follows the full forward."""
+    import torch.nn.functional as F
+    from parameter_golf_b200.quant.calibrate import generate_autoregressive
+    m0, m1 = full_model(), full_model()
+    m1.embed_dim = 16
+    p0 = {k: v.double() for k, v in gpt.fill_deterministic(m0).items()}
+    eye = torch.eye(16, dtype=torch.float64)
+    p1 = dict(p0, embed_proj_in=eye, embed_proj_out=eye)
+    ids = torch.randint(0, 32, (2, 7))
+    tgt = torch.randint(0, 32, (2, 7))
+    assert torch.allclose(gpt.gpt_forward(m1, p1, ids, tgt), gpt.gpt_forward(m0, p0, ids, tgt), atol=1e-12)
+    m2 = full_model()
+    m2.embed_dim = 6
+    sh = gpt.param_shapes(m2)
+    assert sh["tok_emb"] == (32, 6) and sh["embed_proj_in"] == (16, 6) and sh["embed_proj_out"] == (6, 16)
+    init = gpt.init_params(m2)
+    assert torch.allclose(init["embed_proj_in"].t() @ init["embed_proj_in"], torch.eye(6), atol=1e-5)
+    assert torch.equal(init["embed_proj_out"], init["embed_proj_in"].t())
+    p2 = {k: v.double() for k, v in gpt.fill_deterministic(m2).items()}
+    h = gpt.gpt_hidden(m2, p2, ids)
+    want = m2.logit_softcap * torch.tanh(F.linear(F.linear(h, p2["embed_proj_out"]), p2["tok_emb"]) / m2.logit_softcap)
+    assert torch.allclose(gpt.gpt_logits(m2, p2, ids).double(), want, atol=1e-6)
+    leaves = {k: p2[k].clone().requires_grad_(True) for k in ("embed_proj_in", "embed_proj_out", "tok_emb")}
+    gs = torch.autograd.grad(gpt.gpt_forward(m2, dict(p2, **leaves), ids, tgt), list(leaves.values()))
+    assert all(float(g.abs().max()) > 0 for g in gs)
+    pf = gpt.fill_deterministic(m2)
+    pf["tok_emb"] = pf["tok_emb"] * 6.0
+    toks = generate_autoregressive(m2, pf, num_seqs=2, seq_len=8, temperature=1e-4, seed=1)
+    logits = gpt.gpt_logits(m2, pf, toks)
+    top2 = logits.topk(2, dim=-1).values
+    decided = (top2[..., 0] - top2[..., 1]) > 1e-3
+    assert bool(((logits.argmax(-1)[:, :-1] == toks[:, 1:]) | ~decided[:, :-1]).all())

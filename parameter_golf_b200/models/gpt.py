@@ -300,7 +300,7 @@ def gpt_logits(m: ModelSpec, p, ids, qat: bool = False, lora=None, dtype=None):
     """Soft-capped logits [B,T,V]."""
     h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
     z = output_logits(m, p, h, qat)
-    return m.logit_softcap * torch.tanh(z.float() / m.logit_softcap)
+    return R.softcap(z, m.logit_softcap, m.softcap_kind)
 
 
 def mtp_loss(m: ModelSpec, p, h, targets):
@@ -313,29 +313,30 @@ def mtp_loss(m: ModelSpec, p, h, targets):
         if valid <= 0:
             continue
         z = F.linear(h[:, :valid], p["mtp_heads"][k].to(h.dtype))
-        l = R.softcap_cross_entropy(z, targets[:, k + 1:], m.logit_softcap, reduction="mean")
+        l = R.softcap_cross_entropy(z, targets[:, k + 1:], m.logit_softcap, reduction="mean", kind=m.softcap_kind)
         total = l if total is None else total + l
         count += 1
     return None if count == 0 else total / count
 
 
 def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dtype=None, reduction: str = "mean", token_weights=None,
-                mtp: bool = False):
+                mtp: bool = False, train: bool = False):
     """Training loss: mean soft-capped cross-entropy over all tokens (``reduction='none'`` gives the
     per-token losses [B,T]). With ``token_weights`` (same shape as ``targets``) the mean is weighted and normalised
     by the sum of the weights (complementary training, ``pg-kernels/src/complementary.rs:226-240``). ``mtp`` (training steps
-    only) adds ``mtp_loss_weight`` times the multi-token-prediction loss of the extra heads."""
+    only) adds ``mtp_loss_weight`` times the multi-token-prediction loss of the extra heads; ``train`` adds the z-loss term
+    (``model.z_loss_weight`` times the mean squared log-partition), which evaluation never includes."""
     h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
     z = output_logits(m, p, h, qat)
     extra = None
     if mtp and reduction == "mean" and m.mtp_num_heads > 0 and m.mtp_loss_weight > 0.0 and "mtp_heads" in p:
         extra = mtp_loss(m, p, h, targets)
     if token_weights is not None and reduction == "mean":
-        per = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction="none").reshape(-1).float()
+        per = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction="none", kind=m.softcap_kind).reshape(-1).float()
         tw = token_weights.reshape(-1).to(per.dtype)
         loss = (per * tw).sum() / tw.sum().clamp_min(1e-12)
         return loss if extra is None else loss + m.mtp_loss_weight * extra
-    loss = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction=reduction)
+    loss = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction=reduction, kind=m.softcap_kind, z_loss=m.z_loss_weight if (train or mtp) else 0.0)
     if extra is not None:
         loss = loss + m.mtp_loss_weight * extra
     return loss.reshape(ids.shape) if reduction == "none" else loss

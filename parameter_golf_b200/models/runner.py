@@ -44,7 +44,8 @@ class OracleRunner:
     def logits(self, ids: torch.Tensor) -> torch.Tensor:
         return gpt.gpt_logits(self.model, self._p(), ids, lora=self.lora, dtype=self.compute_dtype)
 
-    def loss_and_grads(self, ids, targets, qat: bool = False, names=None, token_weights=None, mtp: bool = False) -> Tuple[torch.Tensor, Dict[str, torch.Tensor]]:
+    def loss_and_grads(self, ids, targets, qat: bool = False, names=None, token_weights=None, mtp: bool = False,
+                       train: bool = False) -> Tuple[torch.Tensor, Dict[str, torch.Tensor]]:
         names = list(self.params) if names is None else list(names)
         leaves = {k: self.params[k].detach().requires_grad_(True) for k in names}
         p = dict(self.params)
@@ -56,7 +57,8 @@ class OracleRunner:
         if lora is not None and lora.get("trainable", False):
             lora_leaves = {"a": lora["a"].detach().requires_grad_(True), "b": lora["b"].detach().requires_grad_(True)}
             lora = dict(lora, **lora_leaves)
-        loss = gpt.gpt_forward(self.model, p, ids, targets, qat=qat, lora=lora, dtype=self.compute_dtype, token_weights=token_weights, mtp=mtp)
+        loss = gpt.gpt_forward(self.model, p, ids, targets, qat=qat, lora=lora, dtype=self.compute_dtype, token_weights=token_weights, mtp=mtp,
+                               train=train)
         wanted = list(leaves.values()) + (list(lora_leaves.values()) if lora_leaves else [])
         gs = torch.autograd.grad(loss, wanted, allow_unused=True)
         grads = {k: (g if g is not None else torch.zeros_like(leaves[k])) for k, g in zip(names, gs[: len(names)])}

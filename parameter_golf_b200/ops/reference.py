@@ -152,10 +152,29 @@ def act_sq(x, slope: float):
     return F.leaky_relu(x, negative_slope=slope).square()
 
 
-def softcap_cross_entropy(logits, targets, cap: float, reduction: str = "mean"):
-    """``CE(cap * tanh(z / cap))`` in fp32 (``pg-kernels/src/cross_entropy.rs``)."""
-    c = cap * torch.tanh(_f(logits) / cap)
-    return F.cross_entropy(c.reshape(-1, c.shape[-1]), targets.reshape(-1), reduction=reduction)
+def softcap(z, cap: float, kind: str = "tanh"):
+    """Soft cap of logits to (-cap, cap) in fp32. ``tanh``: ``cap * tanh(z / cap)``. ``poly5``: the degree-5 odd polynomial of the
+    ternary record, ``x (1 - x^2/3 + x^4/15)`` of ``x = clamp(z / cap, -2, 2)``, clamped to [-1, 1] and scaled by ``cap``
+    (``records/track_10min_16mb/2026-03-24_74M_Ternary_.../train_gpt_cuda_ternary.py:859-865``)."""
+    zf = _f(z)
+    if kind == "tanh":
+        return cap * torch.tanh(zf / cap)
+    if kind == "poly5":
+        x = torch.clamp(zf / cap, -2.0, 2.0)
+        x2 = x * x
+        return cap * torch.clamp(x * (1.0 - x2 / 3.0 + x2 * x2 / 15.0), -1.0, 1.0)
+    raise ValueError(f"unknown softcap kind {kind!r}")
+
+
+def softcap_cross_entropy(logits, targets, cap: float, reduction: str = "mean", kind: str = "tanh", z_loss: float = 0.0):
+    """``CE(softcap(z))`` in fp32 (``pg-kernels/src/cross_entropy.rs``); ``z_loss`` > 0 adds that weight times the mean squared
+    log-partition (only to the mean reduction: a training-time regulariser)."""
+    c = softcap(logits, cap, kind)
+    c2, t = c.reshape(-1, c.shape[-1]), targets.reshape(-1)
+    loss = F.cross_entropy(c2, t, reduction=reduction)
+    if z_loss > 0.0 and reduction == "mean":
+        loss = loss + z_loss * torch.logsumexp(c2, dim=-1).pow(2).mean()
+    return loss
 
 
 def fake_quant_fp8_ste(w: torch.Tensor) -> torch.Tensor:

@@ -114,7 +114,7 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
             if unet and i < enc:
                 skips.append(x)
         hfin = R.rms_norm(x)
-        z = m.logit_softcap * torch.tanh(gpt.output_logits(m, p, hfin).float() / m.logit_softcap)
+        z = R.softcap(gpt.output_logits(m, p, hfin), m.logit_softcap, m.softcap_kind)
         probs = torch.softmax(z / temperature, dim=-1)
         toks[:, t + 1] = torch.multinomial(probs, 1, generator=g)[:, 0]
     return toks

@@ -126,6 +126,8 @@ class ModelSpec:
     mtp_num_heads: int = 0                # extra output heads that predict the tokens 2, 3, ... ahead, training only, not exported
     mtp_loss_weight: float = 0.2
     dtg: bool = False                     # per-block scalar gate on the block's update, sigmoid(w . x_in + b) read from the detached input (DTG_ENABLED)
+    softcap_kind: str = "tanh"            # tanh | poly5 (the ternary record's degree-5 polynomial cap)
+    z_loss_weight: float = 0.0            # training only: this weight times the mean squared log-partition is added to the loss
     embed_dim: int = 0                    # > 0: factored tied embedding, tok_emb [V, embed_dim] with learned projections to and from
                                           # model_dim (the ternary record's 254-wide bottleneck); 0 = tok_emb [V, model_dim]
     qat_kind: str = "int6"                # what QAT simulates in the bank matrices: int6 rows, or ternary codes with one scale per group
@@ -455,6 +457,7 @@ class RunSpec:
         if has("BIGRAM_DIM"): m.bigram.dim = I("BIGRAM_DIM")
         if has("XSA_LAST_N"): m.xsa_last_n = I("XSA_LAST_N")
         if has("EMBED_DIM"): m.embed_dim = I("EMBED_DIM")
+        if has("SOFTCAP_TYPE"): m.softcap_kind = "poly5" if env["SOFTCAP_TYPE"].lower().startswith("poly") else "tanh"
         if has("VALUE_RESIDUAL"): m.value_residual = B("VALUE_RESIDUAL")
         if has("DTG_ENABLED"): m.dtg = B("DTG_ENABLED")
         if has("MTP_NUM_HEADS"): m.mtp_num_heads = I("MTP_NUM_HEADS")
@@ -515,6 +518,9 @@ class RunSpec:
         chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat or m.dtg or m.embed_dim > 0) or t.backend == "cpu",
             "model.value_residual, model.mtp_num_heads, model.dtg, model.embed_dim and model.fp8_qat run on train.backend=cpu only "
             "(the CUDA engine has no path for them)")
+        chk(m.softcap_kind in ("tanh", "poly5") and m.z_loss_weight >= 0.0, "model.softcap_kind must be tanh or poly5 and z_loss_weight >= 0")
+        chk((m.softcap_kind == "tanh" and m.z_loss_weight == 0.0) or t.backend == "cpu",
+            "model.softcap_kind=poly5 and model.z_loss_weight run on train.backend=cpu only (the fused cross-entropy kernel caps with tanh)")
         chk(m.embed_dim == 0 or (m.tie_embeddings and 0 < m.embed_dim <= m.model_dim), "model.embed_dim needs tied embeddings and 0 < embed_dim <= model_dim")
         chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
         chk(m.qat_kind in ("int6", "ternary"), "model.qat_kind must be int6 or ternary")
@@ -620,12 +626,13 @@ def family_preset(family: str) -> RunSpec:
     elif family == "ternary_10l":
         # records/track_10min_16mb/2026-03-24_74M_Ternary_UNet_FP8_10L_8192BPE_YaRN_NeoMuon (README "Architecture", run_cuda_ternary.sh):
         # ternary weights trained with a straight-through estimator from the first step, FP8 for the rest, YaRN, three
-        # Newton-Schulz steps, the 254-wide factored tied embedding, sliding evaluation at stride 16. Its polynomial soft-cap is not modelled (tanh instead).
+        # Newton-Schulz steps, the 254-wide factored tied embedding, the degree-5 polynomial soft-cap with a z-loss of 1e-4, sliding evaluation at stride 16.
         m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads = 8192, 10, 768, 8, 4
         m.mlp_mult, m.activation = 4.0, "relu_sq"
         m.train_seq_len = m.eval_seq_len = 1024
         m.rope = RopeSpec("yarn", 0, 5000.0, 2048, 1024)
         m.logit_softcap, m.qk_gain_init = 10.0, 2.25
+        m.softcap_kind, m.z_loss_weight = "poly5", 1e-4
         m.embed_dim = 254
         m.qat_kind, m.fp8_qat = "ternary", True
         t.backend, t.batch_tokens, t.seq_len = "cpu", 524_288, 1024

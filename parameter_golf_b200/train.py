@@ -112,7 +112,7 @@ class OracleBackend:
             tw = None
             if self.token_weight_table is not None:
                 tw = torch.from_numpy(self.token_weight_table[ids.numpy().astype(np.int64), tgt.numpy().astype(np.int64)])
-            loss, g = self.runner.loss_and_grads(ids, tgt, qat=qat, token_weights=tw, mtp=self.spec.model.mtp_num_heads > 0)
+            loss, g = self.runner.loss_and_grads(ids, tgt, qat=qat, token_weights=tw, mtp=self.spec.model.mtp_num_heads > 0, train=True)
             loss_sum += float(loss)
             total = g if total is None else {k: total[k] + g[k] for k in g}
         inv = 1.0 / len(batches)

@@ -144,3 +144,24 @@ def test_fake_quant_ste_forward_and_gradient():
     assert torch.allclose(codes, codes.round(), atol=1e-5) and codes.min() >= -32 - 1e-4 and codes.max() <= 31 + 1e-4
     wq.sum().backward()
     assert torch.allclose(w.grad, torch.ones_like(w))
+
+
+def test_polynomial_softcap_and_z_loss():
+    """poly5: x (1 - x^2/3 + x^4/15) of the clamped ratio, within [-cap, cap], odd, close to tanh for small arguments; the
+    z-loss adds weight * mean(logsumexp^2) to the mean loss only (train_gpt_cuda_ternary.py:859-865, :903-906)."""
+    import torch.nn.functional as F
+    z = torch.linspace(-40, 40, 801)
+    c = R.softcap(z, 10.0, "poly5")
+    assert float(c.abs().max()) <= 10.0 + 1e-6 and torch.allclose(c, -R.softcap(-z, 10.0, "poly5"))
+    small = torch.linspace(-3, 3, 61)
+    assert torch.allclose(R.softcap(small, 10.0, "poly5"), R.softcap(small, 10.0, "tanh"), atol=2e-3)
+    x = torch.tensor([0.5])
+    assert torch.allclose(R.softcap(10.0 * x, 10.0, "poly5"), 10.0 * x * (1 - x ** 2 / 3 + x ** 4 / 15))
+    logits, tgt = torch.randn(4, 7, 13) * 5, torch.randint(0, 13, (4, 7))
+    base = R.softcap_cross_entropy(logits, tgt, 10.0, kind="poly5")
+    capped = R.softcap(logits, 10.0, "poly5").reshape(-1, 13)
+    assert torch.allclose(base, F.cross_entropy(capped, tgt.reshape(-1)))
+    with_z = R.softcap_cross_entropy(logits, tgt, 10.0, kind="poly5", z_loss=1e-2)
+    assert torch.allclose(with_z, base + 1e-2 * torch.logsumexp(capped, -1).pow(2).mean())
+    assert R.softcap_cross_entropy(logits, tgt, 10.0, reduction="none", z_loss=1.0).shape == (28,)
+    _gc(lambda t: R.softcap(t, 10.0, "poly5"), torch.randn(3, 5) * 8)

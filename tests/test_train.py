@@ -443,7 +443,8 @@ def test_ternary_family_trains_with_its_estimator_and_round_trips(tmp_path, monk
                        "quant.compression=lzma9", "quant.float_storage=fp8", "quant.prune_to_target=false", "train.qat_enabled=true",
                        "train.muon_ns_steps=3", "model.rope.mode=yarn", "model.rope.dims=16", "model.rope.yarn_max_len=1024",
                        "model.rope.yarn_train_len=256", "model.bigram.enabled=true", "model.bigram.vocab_size=128", "model.bigram.dim=32",
-                       "model.fp8_qat=true"])
+                       "model.fp8_qat=true", "model.softcap_kind=poly5", "model.z_loss_weight=0.0001", "model.logit_softcap=10",
+                       "model.embed_dim=48"])
     s.train.total_iterations = 4
     s.train.artifact_path = str(tmp_path / "t.pgrs")
     s.eval.max_tokens = 512

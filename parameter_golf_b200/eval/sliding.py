@@ -107,6 +107,29 @@ def eval_sliding(nll_fn: Callable, tokens: np.ndarray, window: int, stride: int,
     return sums.all_reduce(device).result()
 
 
+def find_temperature(runner, tokens: np.ndarray, seq_len: int, grid, batch_seqs: int = 16, device="cpu") -> Tuple[float, dict]:
+    """Score ``tokens`` (training data, never the validation split) once per temperature of ``grid`` through ``runner.nll`` and
+    return the temperature with the lowest mean loss and the whole table (the five-point search of the ternary record,
+    ``records/track_10min_16mb/2026-03-24_74M_Ternary_.../train_gpt_cuda_ternary.py:1044-1054``). The runner's temperature is
+    left at the winner."""
+    n = (tokens.shape[0] - 1) // seq_len
+    if n <= 0:
+        raise ValueError("not enough calibration tokens for one sequence")
+    tok64 = tokens.astype(np.int64)
+    x = torch.from_numpy(tok64[: n * seq_len].reshape(n, seq_len)).to(device)
+    y = torch.from_numpy(tok64[1: n * seq_len + 1].reshape(n, seq_len)).to(device)
+    table = {}
+    for t in grid:
+        runner.temperature = float(t)
+        total = 0.0
+        for i in range(0, n, batch_seqs):
+            total += float(runner.nll(x[i:i + batch_seqs], y[i:i + batch_seqs]).double().sum())
+        table[float(t)] = total / (n * seq_len)
+    best = min(table, key=table.get)
+    runner.temperature = best
+    return best, table
+
+
 def eval_contiguous(nll_fn: Callable, tokens: np.ndarray, seq_len: int, luts: BpbLuts, rank: int = 0, world: int = 1,
                     batch_seqs: int = 32, device="cpu") -> Tuple[float, float]:
     """Non-overlapping evaluation of ``train_gpt.py:221-278``: every sequence scored once, rank-contiguous split."""

@@ -44,6 +44,8 @@ def main(argv=None) -> int:
     ap.add_argument("--stride", type=int)
     ap.add_argument("--tokenizer-vocab")
     ap.add_argument("--caseops-byte-sidecar")
+    ap.add_argument("--find-temperature", action="store_true",
+                    help="pick eval.temperature from eval.temperature_grid on the first training tokens before scoring (autograd runner)")
     ap.add_argument("--bytes", choices=["tokenizer", "seeded", "placeholder"], default="seeded")
     ap.add_argument("--leaderboard", action="store_true")
     ap.add_argument("--device", default="cpu")
@@ -104,7 +106,18 @@ def main(argv=None) -> int:
     if a.device == "cpu":
         from .models.runner import OracleRunner
         runner = OracleRunner(m, params)
+        runner.temperature = spec.eval.temperature
+        if a.find_temperature:
+            from .eval.sliding import find_temperature
+            if not spec.train.train_data_pattern:
+                raise SystemExit("--find-temperature needs train.train_data_pattern (the grid is scored on training tokens)")
+            calib = load_validation_tokens(spec.train.train_data_pattern, m.eval_seq_len, spec.eval.temperature_calibration_tokens)
+            best, table = find_temperature(runner, calib, m.eval_seq_len, spec.eval.temperature_grid)
+            if rank == 0:
+                print("temperature_search=" + json.dumps({str(k): round(v, 6) for k, v in table.items()}) + f"\ntemperature={best}")
     else:
+        if spec.eval.temperature != 1.0 or a.find_temperature:
+            raise SystemExit("temperature scaling is scored by the autograd runner: use --device cpu")
         from .models.engine import EngineRunner
         runner = EngineRunner(spec, params, a.device)
     t0 = time.perf_counter()

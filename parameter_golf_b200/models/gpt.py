@@ -320,7 +320,7 @@ def mtp_loss(m: ModelSpec, p, h, targets):
 
 
 def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dtype=None, reduction: str = "mean", token_weights=None,
-                mtp: bool = False, train: bool = False):
+                mtp: bool = False, train: bool = False, temperature: float = 1.0):
     """Training loss: mean soft-capped cross-entropy over all tokens (``reduction='none'`` gives the
     per-token losses [B,T]). With ``token_weights`` (same shape as ``targets``) the mean is weighted and normalised
     by the sum of the weights (complementary training, ``pg-kernels/src/complementary.rs:226-240``). ``mtp`` (training steps
@@ -332,11 +332,12 @@ def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dty
     if mtp and reduction == "mean" and m.mtp_num_heads > 0 and m.mtp_loss_weight > 0.0 and "mtp_heads" in p:
         extra = mtp_loss(m, p, h, targets)
     if token_weights is not None and reduction == "mean":
-        per = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction="none", kind=m.softcap_kind).reshape(-1).float()
+        per = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction="none", kind=m.softcap_kind, temperature=temperature).reshape(-1).float()
         tw = token_weights.reshape(-1).to(per.dtype)
         loss = (per * tw).sum() / tw.sum().clamp_min(1e-12)
         return loss if extra is None else loss + m.mtp_loss_weight * extra
-    loss = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction=reduction, kind=m.softcap_kind, z_loss=m.z_loss_weight if (train or mtp) else 0.0)
+    loss = R.softcap_cross_entropy(z, targets, m.logit_softcap, reduction=reduction, kind=m.softcap_kind, z_loss=m.z_loss_weight if (train or mtp) else 0.0,
+                                   temperature=temperature)
     if extra is not None:
         loss = loss + m.mtp_loss_weight * extra
     return loss.reshape(ids.shape) if reduction == "none" else loss

@@ -26,6 +26,7 @@ class OracleRunner:
         self.params = params
         self.compute_dtype = compute_dtype
         self.lora = None
+        self.temperature = 1.0           # evaluation-time scaling of the capped logits (`eval.temperature`); training never uses it
 
     @property
     def device(self):
@@ -38,7 +39,8 @@ class OracleRunner:
 
     @torch.no_grad()
     def nll(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-        return gpt.gpt_forward(self.model, self._p(), ids, targets, lora=self.lora, dtype=self.compute_dtype, reduction="none").float()
+        return gpt.gpt_forward(self.model, self._p(), ids, targets, lora=self.lora, dtype=self.compute_dtype, reduction="none",
+                               temperature=self.temperature).float()
 
     @torch.no_grad()
     def logits(self, ids: torch.Tensor) -> torch.Tensor:

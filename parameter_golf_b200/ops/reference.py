@@ -166,10 +166,13 @@ def softcap(z, cap: float, kind: str = "tanh"):
     raise ValueError(f"unknown softcap kind {kind!r}")
 
 
-def softcap_cross_entropy(logits, targets, cap: float, reduction: str = "mean", kind: str = "tanh", z_loss: float = 0.0):
-    """``CE(softcap(z))`` in fp32 (``pg-kernels/src/cross_entropy.rs``); ``z_loss`` > 0 adds that weight times the mean squared
-    log-partition (only to the mean reduction: a training-time regulariser)."""
+def softcap_cross_entropy(logits, targets, cap: float, reduction: str = "mean", kind: str = "tanh", z_loss: float = 0.0, temperature: float = 1.0):
+    """``CE(softcap(z) / temperature)`` in fp32 (``pg-kernels/src/cross_entropy.rs``); ``z_loss`` > 0 adds that weight times the
+    mean squared log-partition (only to the mean reduction: a training-time regulariser). ``temperature`` != 1 is the evaluation-time
+    scaling of the ternary record (its capped logits are slightly under-confident)."""
     c = softcap(logits, cap, kind)
+    if temperature != 1.0:
+        c = c / temperature
     c2, t = c.reshape(-1, c.shape[-1]), targets.reshape(-1)
     loss = F.cross_entropy(c2, t, reduction=reduction)
     if z_loss > 0.0 and reduction == "mean":

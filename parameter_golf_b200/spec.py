@@ -285,6 +285,9 @@ class EvalSpec:
     ttt_grad_clip: float = 1.0
     ttt_freeze_blocks: int = 0
     max_eval_seconds: float = 600.0
+    temperature: float = 1.0           # capped logits are divided by this when scoring (autograd runner); `find_temperature` picks it
+    temperature_grid: list = field(default_factory=lambda: [0.90, 0.95, 1.00, 1.05, 1.10])
+    temperature_calibration_tokens: int = 65536       # training tokens the grid is scored on
     byte_table_seed: int = 20240520
 
 
@@ -523,6 +526,7 @@ class RunSpec:
             "model.softcap_kind=poly5 and model.z_loss_weight run on train.backend=cpu only (the fused cross-entropy kernel caps with tanh)")
         chk(m.embed_dim == 0 or (m.tie_embeddings and 0 < m.embed_dim <= m.model_dim), "model.embed_dim needs tied embeddings and 0 < embed_dim <= model_dim")
         chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
+        chk(e.temperature > 0 and all(x > 0 for x in e.temperature_grid), "eval.temperature and its grid must be positive")
         chk(m.qat_kind in ("int6", "ternary"), "model.qat_kind must be int6 or ternary")
         chk(m.qat_kind != "ternary" or t.backend == "cpu", "model.qat_kind=ternary runs on train.backend=cpu only")
         chk(q.ternary_group >= 8, "quant.ternary_group must be >= 8")
@@ -564,7 +568,8 @@ class RunSpec:
             "model": dataclasses.asdict(self.model),
             "quant": dataclasses.asdict(self.quant),
             "eval": {k: v for k, v in dataclasses.asdict(self.eval).items()
-                     if k not in ("tokenizer_vocab_path", "caseops_byte_sidecar_pattern", "max_eval_seconds")},
+                     if k not in ("tokenizer_vocab_path", "caseops_byte_sidecar_pattern", "max_eval_seconds", "temperature_grid",
+                                  "temperature_calibration_tokens")},
             "train": {k: getattr(t, k) for k in (
                 "batch_tokens", "seq_len", "matrix_lr", "scalar_lr", "embed_lr", "tied_embed_lr", "muon_momentum",
                 "muon_wd", "adam_wd", "muon_ns_profile", "muon_ns_steps", "ema_decay", "late_qat_threshold",
@@ -687,7 +692,10 @@ def _coerce(text: str, current, ftype=None):
     if isinstance(current, float):
         return float(text)
     if isinstance(current, list):
-        return [int(x) for x in text.strip("[]").split(",") if x.strip()]
+        items = [x.strip() for x in text.strip("[]").split(",") if x.strip()]
+        if any(isinstance(c, float) for c in current) or any(("." in x or "e" in x.lower()) for x in items):
+            return [float(x) for x in items]          # a list of floats (e.g. eval.temperature_grid)
+        return [int(x) for x in items]
     if current is None:
         if text.lower() in ("none", "null", ""):
             return None

@@ -492,8 +492,11 @@ class VariantRunner:
                 luts = luts.with_sidecar(load_validation_byte_sidecar(spec.eval.caseops_byte_sidecar_pattern)[: val.shape[0]])
             if t.backend == "cpu":
                 runner = OracleRunner(m, eval_params)
+                runner.temperature = spec.eval.temperature
                 edev = "cpu"
             else:
+                if spec.eval.temperature != 1.0:
+                    raise RuntimeError("eval.temperature != 1 is scored by the autograd runner (train.backend=cpu or evalcli --device cpu)")
                 from .models.engine import EngineRunner
                 runner = EngineRunner(spec, eval_params, device)
                 edev = device

@@ -160,3 +160,40 @@ def test_slot_limits():
     assert abs(tab.row_probs(np.array([1]))[0, 3] - 3 / 11) < 1e-12                     # add-one smoothing
     mid = T.slot_nll(logits, prev, cur, tab, alpha=0.5, adaptive=True)
     assert np.isfinite(mid).all()
+
+
+def test_temperature_scaling_and_its_grid_search():
+    """eval.temperature divides the capped logits when scoring; the grid search scores training tokens once per temperature and
+    keeps the best. A model whose logits are too flat by a known factor gets that factor back."""
+    import torch.nn.functional as F
+    from parameter_golf_b200.eval.sliding import find_temperature
+    from parameter_golf_b200.models import gpt
+    from parameter_golf_b200.models.runner import OracleRunner
+    from parameter_golf_b200.spec import family_preset
+    s = family_preset("tiny_cpu")
+    s.model.vocab_size, s.model.num_layers, s.model.model_dim, s.model.num_heads, s.model.num_kv_heads = 32, 1, 16, 2, 1
+    m = s.validate().model
+    p = gpt.fill_deterministic(m)
+    r = OracleRunner(m, p)
+    ids = torch.randint(0, 32, (3, 12))
+    tgt = torch.randint(0, 32, (3, 12))
+    base = r.nll(ids, tgt)
+    r.temperature = 0.5
+    want = F.cross_entropy((gpt.gpt_logits(m, p, ids) / 0.5).reshape(-1, 32), tgt.reshape(-1), reduction="none").reshape(3, 12)
+    assert torch.allclose(r.nll(ids, tgt), want, atol=1e-5) and not torch.allclose(base, want)
+    # targets drawn from softmax(logits / 0.7): the log-likelihood is maximised near T = 0.7
+    g = torch.Generator().manual_seed(0)
+    stream = torch.randint(0, 32, (4097,), generator=g)
+    x = stream[:-1].reshape(-1, 64)
+    probs = torch.softmax(gpt.gpt_logits(m, p, x) / 0.7, -1)
+    y = torch.multinomial(probs.reshape(-1, 32), 1, generator=g).reshape(x.shape)
+    toks = np.concatenate([x.reshape(-1).numpy()[:1], y.reshape(-1).numpy()])          # a stream whose shift-by-one targets are y
+
+    class Fixed:                                      # a runner that scores x against y at the current temperature
+        temperature = 1.0
+        def nll(self, a, b):
+            rr = OracleRunner(m, p)
+            rr.temperature = self.temperature
+            return rr.nll(x[: a.shape[0]], y[: a.shape[0]])
+    best, table = find_temperature(Fixed(), toks, 64, [0.5, 0.7, 1.0, 1.4], batch_seqs=64)
+    assert best == 0.7 and table[0.7] < table[1.0] < table[1.4]

@@ -132,3 +132,23 @@ def test_submission_manifest_counts_source_and_fails_closed(tmp_path):
     assert Sub.main(["--artifact", art, "--code", str(code), "--limit", str(man["total_bytes"])]) == 1      # the limit itself is over budget
     assert Sub.main(["--artifact", art, "--code", str(tmp_path / "missing")]) == 2
     assert Sub.main(["--artifact", str(tmp_path / "none.pgrs"), "--code", str(code)]) == 2
+
+
+def test_eval_cli_temperature_search(tmp_path):
+    from parameter_golf_b200.data.shards import write_shard, generate_markov_tokens
+    from parameter_golf_b200.quant.export import export_model
+    s = family_preset("tiny_cpu")
+    art = str(tmp_path / "a.pgrs")
+    export_model(s, gpt.init_params(s.model, 1), art)
+    write_shard(str(tmp_path / "v_val_000000.bin"), generate_markov_tokens(256 * 2 + 1, 1024, 5))
+    write_shard(str(tmp_path / "t_train_000000.bin"), generate_markov_tokens(256 * 4 + 1, 1024, 6))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "parameter_golf_b200.evalcli", "--artifact", art, "--family", "tiny_cpu", "--val-pattern", str(tmp_path / "v_val_*.bin"),
+           "--find-temperature", f"train.train_data_pattern={tmp_path}/t_train_*.bin", "eval.temperature_calibration_tokens=1024",
+           "eval.temperature_grid=[0.9,1.0,1.1]"]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr[-1500:]
+    kv = dict(l.split("=", 1) for l in out.stdout.splitlines() if "=" in l and not l.startswith("eval_audit_json"))
+    assert float(kv["temperature"]) in (0.9, 1.0, 1.1) and len(json.loads(kv["temperature_search"])) == 3 and float(kv["val_bpb"]) > 0
+    out = subprocess.run(cmd[:-3] + ["--device", "cuda"], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode != 0

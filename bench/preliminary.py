@@ -92,7 +92,7 @@ def prune_sweep():
 
 def arch_sweep():
     print("== 3. architecture families: parameters, estimated artifact bytes, engine memory for one record micro-batch")
-    print(f"{'family':>28} {'params':>12} {'int6 MB':>9} {'int5/6 MB':>10} {'fits':>5} {'engine GiB @98,304 tok':>23}   (ternary families: their own scheme in both columns)")
+    print(f"{'family':>28} {'params':>12} {'int6 MB':>9} {'int5/6 MB':>10} {'fits':>5} {'engine GiB @98,304 tok':>23}   (ternary / binary families: their own scheme before xz in both columns; xz takes a few percent off the scales and codes)")
     rows = []
     for fam in FAMILIES:
         s = family_preset(fam)
@@ -110,6 +110,8 @@ def arch_sweep():
         if s.quant.scheme == "ternary_b158":                # five codes per byte plus one fp16 scale per group; xz gains little on top
             tern = sum(bank.values()) * (1 / 5 + 2 / s.quant.ternary_group) + emb + other * (1 if s.quant.float_storage == "fp8" else 2)
             int6 = mixed = tern
+        if s.quant.scheme == "binary_b1":                   # eight codes per byte plus one fp16 scale per group
+            int6 = mixed = sum(bank.values()) * (1 / 8 + 2 / s.quant.ternary_group) + emb + other * (1 if s.quant.float_storage == "fp8" else 2)
         try:
             mem = estimate_engine_memory(s, 98304).total / 2 ** 30
         except Exception:

@@ -72,7 +72,8 @@ def mask_grads(model: ModelSpec, grads: Dict[str, torch.Tensor], mode: str, free
                 g[:fb] = 0
                 g[n:n + fb] = 0
             elif k in ("mlp_up_bank", "mlp_down_bank", "attn_scale", "mlp_scale", "resid_mix", "q_gain",
-                       "attn_gate_weight", "attn_gate_bias", "sparse_attn_gate_weight"):
+                       "attn_gate_weight", "attn_gate_bias", "sparse_attn_gate_weight", "vr_lambda", "dtg_gate_weight", "dtg_gate_bias",
+                       "block_smear_gate"):
                 g[:fb] = 0
 
 

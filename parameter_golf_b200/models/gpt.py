@@ -5,7 +5,7 @@ Parameter layout (``parameter-golf-rs/crates/pg-model/src/model.rs:18-67``; Pyth
 ``tok_emb[V,d]`` (tied output), banks ``qo_bank[2n,d,d]`` (Q then O), ``kv_bank[2n,kv,d]`` (K then V),
 ``mlp_up_bank[n,mlp,d]``, ``mlp_down_bank[n,d,mlp]``; per-block controls are stored stacked over layers:
 ``attn_scale[n,d]``, ``mlp_scale[n,d]``, ``resid_mix[n,2,d]``, ``q_gain[n,H]``; ``skip_weights[min(n/2,n-n/2),d]``,
-``smear_gate[d]``, BigramHash ``bigram_embed[B,bd]``/``bigram_proj[d,bd]``/``bigram_scale``, value embedding
+``smear_gate[d]``, ``block_smear_gate[n,d]`` (per-block running-mean smear), BigramHash ``bigram_embed[B,bd]``/``bigram_proj[d,bd]``/``bigram_scale``, value embedding
 ``ve_embed[V,ve]``/``ve_proj[kv,ve]``/``ve_scale``/``ve_layer_scales``, optional attention gates.
 
 `gpt_forward` is the single definition of the model function (forward math of
@@ -27,6 +27,11 @@ EMBEDS = ("tok_emb", "bigram_embed", "ve_embed", "lm_head")
 TRAIN_ONLY = ("mtp_heads",)          # never exported (records/.../2026-03-23_.../train_gpt.py:1778)
 
 
+def up_rows(m: ModelSpec) -> int:
+    """Rows of one block's slice of ``mlp_up_bank``: the hidden width, twice that for SwiGLU (gate rows, then up rows)."""
+    return 2 * m.mlp_dim if m.activation == "swiglu" else m.mlp_dim
+
+
 def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
     n, d, kv, mlp, H = m.num_layers, m.model_dim, m.kv_dim, m.mlp_dim, m.num_heads
     enc = n // 2
@@ -34,7 +39,7 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
         "tok_emb": (m.vocab_size, m.embed_dim if m.embed_dim > 0 else d),
         "qo_bank": (2 * n, d, d),
         "kv_bank": (2 * n, kv, d),
-        "mlp_up_bank": (n, mlp, d),
+        "mlp_up_bank": (n, up_rows(m), d),
         "mlp_down_bank": (n, d, mlp),
         "attn_scale": (n, d),
         "mlp_scale": (n, d),
@@ -72,6 +77,10 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
         sh["dtg_gate_bias"] = (n,)
     if m.mtp_num_heads > 0:
         sh["mtp_heads"] = (m.mtp_num_heads, m.vocab_size, d)
+    if m.block_smear:
+        sh["block_smear_gate"] = (n, d)
+    if m.vocab_bias:
+        sh["vocab_bias"] = (m.vocab_size,)
     return sh
 
 
@@ -99,7 +108,7 @@ def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float3
         p["qo_bank"][i] = _orthogonal(d, d, g)
         p["kv_bank"][i] = _orthogonal(m.kv_dim, d, g)
         p["kv_bank"][n + i] = _orthogonal(m.kv_dim, d, g)
-        p["mlp_up_bank"][i] = _orthogonal(m.mlp_dim, d, g)
+        p["mlp_up_bank"][i] = _orthogonal(up_rows(m), d, g)
     p["attn_scale"].fill_(1.0)
     p["mlp_scale"].fill_(1.0)
     p["resid_mix"][:, 0].fill_(1.0)
@@ -169,11 +178,25 @@ def embed_tokens(m: ModelSpec, p, ids, dt, qat: bool = False):
 def output_logits(m: ModelSpec, p, h, qat: bool = False):
     """Un-capped logits of final hidden states: the tied table (after the output projection when the embedding is factored) or
     the untied head."""
+    bias = p["vocab_bias"].to(h.dtype) if m.vocab_bias else None      # train_gpt_cuda_ternary.py:851
     if not m.tie_embeddings:
-        return F.linear(h, _small(m, p, "lm_head", qat).to(h.dtype))
+        return F.linear(h, _small(m, p, "lm_head", qat).to(h.dtype), bias)
     if m.embed_dim > 0:
         h = F.linear(h, _small(m, p, "embed_proj_out", qat).to(h.dtype))
-    return F.linear(h, p["tok_emb"].to(h.dtype))
+    return F.linear(h, p["tok_emb"].to(h.dtype), bias)
+
+
+def mlp_hidden(m: ModelSpec, u):
+    """The MLP's hidden activation from the up-projection's output: the squared (leaky) ReLU, or for SwiGLU
+    ``silu(gate) * up`` with the gate in the first half of the columns
+    (records/track_non_record_16mb/2026-03-24_106M_Binary_.../train_gpt_cuda_binary.py:635-639), followed by the RMSNorm that the
+    ternary and binary submissions put in front of their down projection when ``normed_out_proj`` is set."""
+    if m.activation == "swiglu":
+        gate, up = u.chunk(2, dim=-1)
+        hid = F.silu(gate) * up
+    else:
+        hid = R.act_sq(u, m.leaky_slope if m.activation == "leaky_relu_sq" else 0.0)
+    return R.rms_norm(hid) if m.normed_out_proj else hid
 
 
 def layer_ln_scale(m: ModelSpec, layer: int) -> float:
@@ -205,6 +228,8 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
     if qat:
         if m.qat_kind == "ternary":
             wq, wo, wk, wv, wu, wd = (R.fake_quant_ternary_ste(w, m.qat_ternary_group) for w in (wq, wo, wk, wv, wu, wd))
+        elif m.qat_kind == "binary":
+            wq, wo, wk, wv, wu, wd = (R.fake_quant_binary_ste(w, m.qat_ternary_group) for w in (wq, wo, wk, wv, wu, wd))
         else:
             wq, wo, wk, wv, wu, wd = (R.fake_quant_int6_ste(w) for w in (wq, wo, wk, wv, wu, wd))
     s_l = layer_ln_scale(m, i)
@@ -238,14 +263,17 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
         y = R.attn_out_gate(y, h, p["attn_gate_weight"][i], p["attn_gate_bias"][i])
     if m.sparse_attn_gate.enabled:
         y = R.sparse_attn_gate(y, h, p["sparse_attn_gate_weight"][i], m.sparse_attn_gate.scale)
+    y = y.reshape(B, T, d)
+    if m.normed_out_proj:
+        y = R.rms_norm(y)                 # train_gpt_cuda_ternary.py:468-470: the output projection norms its own input
     if taps is not None:
-        taps.add(i, "o", y.reshape(B, T, d))
-    attn = F.linear(y.reshape(B, T, d), wo.to(dt))
+        taps.add(i, "o", y)
+    attn = F.linear(y, wo.to(dt))
     x_mid = x_in + p["attn_scale"][i].to(dt)[None, None, :] * attn
     mlp_in = R.rms_norm(x_in if m.parallel_residual.enabled else x_mid, s_l)
     if taps is not None:
         taps.add(i, "up", mlp_in)
-    hid = R.act_sq(F.linear(mlp_in, wu.to(dt)), m.leaky_slope if m.activation == "leaky_relu_sq" else 0.0)
+    hid = mlp_hidden(m, F.linear(mlp_in, wu.to(dt)))
     if taps is not None:
         taps.add(i, "down", hid)
     out = x_mid + p["mlp_scale"][i].to(dt)[None, None, :] * F.linear(hid, wd.to(dt))
@@ -253,6 +281,8 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
         # records/.../2026-03-23_.../train_gpt.py:769-771: the gate reads the block input without sending it a gradient
         gate = torch.sigmoid(F.linear(x_in.detach(), p["dtg_gate_weight"][i].to(dt)[None, :], p["dtg_gate_bias"][i].to(dt)[None]))
         out = x_in + gate * (out - x_in)
+    if m.block_smear:
+        out = R.running_mean_smear(out, p["block_smear_gate"][i])
     if return_kv:
         return out, (k, v)
     if return_raw_v:
@@ -352,7 +382,7 @@ def bank_views(m: ModelSpec, p) -> Dict[str, torch.Tensor]:
         "qo_bank.o": p["qo_bank"][n:].reshape(n * d, d),
         "kv_bank.k": p["kv_bank"][:n].reshape(n * kv, d),
         "kv_bank.v": p["kv_bank"][n:].reshape(n * kv, d),
-        "mlp_up_bank": p["mlp_up_bank"].reshape(n * mlp, d),
+        "mlp_up_bank": p["mlp_up_bank"].reshape(n * up_rows(m), d),
         "mlp_down_bank": p["mlp_down_bank"].reshape(n * d, mlp),
         "tok_emb": p["tok_emb"],
     }

@@ -133,6 +133,15 @@ def smear_gate(x, gate, ids=None, boundary_id=None):
     return (1 - s) * x + s * x_prev
 
 
+def running_mean_smear(x, gate):
+    """``x + tanh(gate) * (m - x)`` where ``m[t]`` is the mean of ``x[0..t]`` of the same sequence: every position is blended with
+    the causal running mean of its sequence, per feature, by a gate that starts at zero
+    (records/track_non_record_16mb/2026-03-24_106M_Binary_.../train_gpt_cuda_binary.py:647-656). x: [B,T,d], gate: [d]."""
+    counts = torch.arange(1, x.shape[1] + 1, device=x.device, dtype=x.dtype)[None, :, None]
+    mean = x.cumsum(dim=1) / counts
+    return x + torch.tanh(_f(gate)).to(x.dtype)[None, None, :] * (mean - x)
+
+
 def bigram_hash(ids: torch.Tensor, buckets: int) -> torch.Tensor:
     """``((36313*cur) xor (27191*prev)) mod (buckets-1)`` in wrapping 32-bit arithmetic; the first
     position of each sequence maps to the sentinel bucket ``buckets-1``
@@ -199,6 +208,19 @@ def fake_quant_ternary_ste(w: torch.Tensor, group: int = 128) -> torch.Tensor:
         w2 = _f(w).reshape(-1, w.shape[-1])
         q, s = quantize_ternary(w2, group)
         wq = dequantize_ternary(q, s.half().float(), group).reshape(w.shape).to(w.dtype)       # scales are stored as fp16
+    return w + (wq - w).detach()
+
+
+def fake_quant_binary_ste(w: torch.Tensor, group: int = 128) -> torch.Tensor:
+    """Straight-through estimator of 1-bit weights: the forward uses ``s * sign(w)`` (zero counts as +1) with ``s`` the mean
+    magnitude of each group of ``group`` input columns, the rule of the binary export (`quant.binary.quantize_binary`) with the
+    scale rounded to fp16 as it is stored; the gradient passes to ``w``
+    (records/track_non_record_16mb/2026-03-24_106M_Binary_.../train_gpt_cuda_binary.py:417-428). Matrices or stacks of matrices."""
+    from ..quant.binary import dequantize_binary, quantize_binary
+    with torch.no_grad():
+        w2 = _f(w).reshape(-1, w.shape[-1])
+        q, s = quantize_binary(w2, group)
+        wq = dequantize_binary(q, s.half().float(), group).reshape(w.shape).to(w.dtype)
     return w + (wq - w).detach()
 
 

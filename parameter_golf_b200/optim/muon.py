@@ -358,6 +358,22 @@ def wallclock_lr_scale(step: int, elapsed_ms: float, iterations: int, warmdown_i
     return remaining / max(warmdown_ms, 1e-9) if remaining <= warmdown_ms else 1.0
 
 
+def fraction_lr_scale(step: int, elapsed_ms: float, iterations: int, fraction: float, max_wallclock_ms: Optional[float]) -> float:
+    """Warm-down over the last ``fraction`` of the run: of the wall-clock budget when there is one (the scale is the time left
+    over the length of that window), else of the step count. It fixes the schedule whose step-counted window was longer than the
+    whole capped run, so that the rate decayed from the first step
+    (records/track_non_record_16mb/2026-03-19_SwiGLU_WarmdownFix_QuarterBatch_1x5090/README.md "Warmdown Schedule Bug";
+    records/track_10min_16mb/2026-03-24_74M_Ternary_.../train_gpt_cuda_ternary.py ``lr_mul``)."""
+    if fraction <= 0:
+        return 1.0
+    if not max_wallclock_ms:
+        window = iterations * fraction
+        return max((iterations - step) / max(window, 1.0), 0.0) if step >= int(iterations * (1.0 - fraction)) else 1.0
+    window_ms = max_wallclock_ms * fraction
+    remaining = max(max_wallclock_ms - elapsed_ms, 0.0)
+    return remaining / max(window_ms, 1e-9) if remaining <= window_ms else 1.0
+
+
 def muon_momentum_at(step: int, start: float, end: float, warmup_steps: int) -> float:
     frac = min(step / warmup_steps, 1.0) if warmup_steps > 0 else 1.0
     return (1 - frac) * start + frac * end

@@ -100,7 +100,7 @@ class ExecutionPlan:
         q, e = spec.quant, spec.eval
         return ExecutionPlan(
             name=spec.name, fingerprint=f"{spec.fingerprint():016x}", micro_batch_tokens=micro_batch_tokens, grad_accum_steps=accum,
-            bank_layout=BankLayout((2 * n, d, d), (2 * n, kv, d), (n, mlp, d), (n, d, mlp)),
+            bank_layout=BankLayout((2 * n, d, d), (2 * n, kv, d), (n, gpt.up_rows(m), d), (n, d, mlp)),
             layer_schedule=masks, saved_mode=t.save_layer_acts, memory=estimate_engine_memory(spec, micro_batch_tokens),
             quant_layout={"scheme": q.scheme, "compression": q.compression, "matrix_bits": q.matrix_bits, "embed_bits": q.embed_bits,
                           "gptq_calibration_batches": q.gptq_calibration_batches, "target_artifact_bytes": q.target_artifact_bytes},

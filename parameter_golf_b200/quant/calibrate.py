@@ -40,7 +40,7 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
     if any(r for _, r in sched):
         raise NotImplementedError("cached generation does not cover recurrent layers; use re-prefill")
     x_prev_embed = torch.zeros(num_seqs, d, device=device, dtype=dtype)
-    slope = m.leaky_slope if m.activation == "leaky_relu_sq" else 0.0
+    run_sum = [torch.zeros(num_seqs, d, device=device, dtype=dtype) for _ in range(n)] if m.block_smear else None
     for t in range(seq_len - 1):
         ids = toks[:, t]
         x = gpt.embed_tokens(m, p, ids, dtype)
@@ -104,13 +104,19 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
                 y = R.attn_out_gate(y, h[:, None], p["attn_gate_weight"][i], p["attn_gate_bias"][i])
             if m.sparse_attn_gate.enabled:
                 y = R.sparse_attn_gate(y, h[:, None], p["sparse_attn_gate_weight"][i], m.sparse_attn_gate.scale)
-            x_mid = x_in + p["attn_scale"][i].to(dtype)[None, :] * F.linear(y.reshape(num_seqs, d), p["qo_bank"][n + i].to(dtype))
+            y = y.reshape(num_seqs, d)
+            if m.normed_out_proj:
+                y = R.rms_norm(y)
+            x_mid = x_in + p["attn_scale"][i].to(dtype)[None, :] * F.linear(y, p["qo_bank"][n + i].to(dtype))
             mlp_in = R.rms_norm(x_in if m.parallel_residual.enabled else x_mid, s_l)
-            hid = R.act_sq(F.linear(mlp_in, p["mlp_up_bank"][i].to(dtype)), slope)
+            hid = gpt.mlp_hidden(m, F.linear(mlp_in, p["mlp_up_bank"][i].to(dtype)))
             x = x_mid + p["mlp_scale"][i].to(dtype)[None, :] * F.linear(hid, p["mlp_down_bank"][i].to(dtype))
             if m.dtg:
                 gate = torch.sigmoid(F.linear(x_in, p["dtg_gate_weight"][i].to(dtype)[None, :], p["dtg_gate_bias"][i].to(dtype)[None]))
                 x = x_in + gate * (x - x_in)
+            if m.block_smear:
+                run_sum[i] = run_sum[i] + x           # the running mean over positions 0..t of this block's output
+                x = x + torch.tanh(p["block_smear_gate"][i].float()).to(dtype)[None, :] * (run_sum[i] / (t + 1) - x)
             if unet and i < enc:
                 skips.append(x)
         hfin = R.rms_norm(x)

@@ -19,7 +19,7 @@ from typing import Dict, Optional, Tuple
 import numpy as np
 import torch
 
-from ..models.gpt import bank_views, param_shapes
+from ..models.gpt import bank_views, param_shapes, up_rows
 from ..spec import RunSpec
 from . import container as C
 from .quantize import GROUPS, LqerFactors, dequantize_rows, lqer_factors, lqer_reconstruct, prune_rows, quantize_rows, scheme_bits
@@ -80,6 +80,9 @@ def quantize_groups(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed:
         if spec.quant.scheme == "ternary_b158" and g != "tok_emb":
             from .ternary import quantize_ternary
             out[g] = quantize_ternary(w, spec.quant.ternary_group)          # codes in {-1, 0, 1}, scales [rows, groups]
+        elif spec.quant.scheme == "binary_b1" and g != "tok_emb":
+            from .binary import quantize_binary
+            out[g] = quantize_binary(w, spec.quant.ternary_group)           # codes in {-1, 1}, scales [rows, groups]
         else:
             out[g] = quantize_rows(w, bits[g])
     return out, bits
@@ -111,6 +114,10 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
             from .ternary import pack_trits
             data = q.cpu().numpy().astype(np.int8).tobytes() if spec.quant.code_storage == "bytes" else pack_trits(q.cpu().numpy())
             recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", data))        # five codes per byte, base 3
+        elif spec.quant.scheme == "binary_b1" and g != "tok_emb":
+            from .binary import pack_signs
+            data = q.cpu().numpy().astype(np.int8).tobytes() if spec.quant.code_storage == "bytes" else pack_signs(q.cpu().numpy())
+            recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", data))        # eight codes per byte
         else:
             recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", _store_codes(q, bits[g], spec.quant.code_storage)))
         recs.append(_f16(f"{g}.scale", s16))
@@ -140,6 +147,8 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
         if m.dtg:
             recs.append(_f16(f"blocks.{i}.dtg_gate_weight", params["dtg_gate_weight"][i]))
             recs.append(_f16(f"blocks.{i}.dtg_gate_bias", params["dtg_gate_bias"][i].reshape(1)))
+        if m.block_smear:
+            recs.append(_f16(f"blocks.{i}.block_smear_gate", params["block_smear_gate"][i]))
     # the multi-token-prediction heads are training-only and are left out (records/.../2026-03-23_.../train_gpt.py:1778)
     if m.value_embedding.enabled:
         recs.append(_flt("ve_embed", params["ve_embed"], spec.quant.float_storage))
@@ -148,6 +157,8 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
         recs.append(_f16("ve_layer_scales", params["ve_layer_scales"]))
     if not m.tie_embeddings:
         recs.append(_flt("lm_head", params["lm_head"], spec.quant.float_storage))
+    if m.vocab_bias:
+        recs.append(_f16("vocab_bias", params["vocab_bias"]))
     if m.embed_dim > 0:
         recs.append(_flt("embed_proj_in", params["embed_proj_in"], spec.quant.float_storage))
         recs.append(_flt("embed_proj_out", params["embed_proj_out"], spec.quant.float_storage))
@@ -162,7 +173,7 @@ def export_model(spec: RunSpec, params: Dict[str, torch.Tensor], path: Optional[
         qs, bits = quantize_groups(spec, params, precomputed)
         blob = C.compress_payload(build_artifact(spec, params, quantized=(qs, bits)), spec.quant.compression)
         limit = spec.quant.target_artifact_bytes - code_bytes()
-        if spec.quant.prune_to_target and spec.quant.scheme not in ("none", "ternary_b158") and len(blob) > limit > 0:
+        if spec.quant.prune_to_target and spec.quant.scheme not in ("none", "ternary_b158", "binary_b1") and len(blob) > limit > 0:
             # +-1 pruning to the byte budget (the 2026-03-25 record's selective prune, train_gpt.py:1997-2040): the codes whose
             # removal costs least squared error go to zero until the compressed artifact fits beside the code
             from .quantize import selective_prune_to_target
@@ -252,6 +263,13 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
             else:
                 q = torch.from_numpy(unpack_trits(wrec.data, rows * cols).copy().reshape(rows, cols))
             return dequantize_ternary(q, torch.from_numpy(_np(srec).astype(np.float32)), int(md.get("ternary_group", 128)))
+        if md.get("scheme") == "binary_b1" and g != "tok_emb":
+            from .binary import dequantize_binary, unpack_signs
+            if len(wrec.data) == rows * cols:
+                q = torch.from_numpy(np.frombuffer(wrec.data, dtype=np.int8).copy().reshape(rows, cols))
+            else:
+                q = torch.from_numpy(unpack_signs(wrec.data, rows * cols).copy().reshape(rows, cols))
+            return dequantize_binary(q, torch.from_numpy(_np(srec).astype(np.float32)), int(md.get("ternary_group", 128)))
         if (legacy or md.get("code_storage") == "bytes") and len(wrec.data) == rows * cols:
             q = torch.from_numpy(np.frombuffer(wrec.data, dtype=np.int8).astype(np.int32).reshape(rows, cols))
         else:
@@ -274,18 +292,18 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
     else:
         p["qo_bank"] = torch.cat([group("qo_bank.q"), group("qo_bank.o")]).reshape(2 * n, d, d)
         p["kv_bank"] = torch.cat([group("kv_bank.k"), group("kv_bank.v")]).reshape(2 * n, kv, d)
-    p["mlp_up_bank"] = group("mlp_up_bank").reshape(n, mlp, d)
+    p["mlp_up_bank"] = group("mlp_up_bank").reshape(n, up_rows(m), d)
     p["mlp_down_bank"] = group("mlp_down_bank").reshape(n, d, mlp)
     p["tok_emb"] = group("tok_emb")
     shapes = param_shapes(m)
     for name in ("bigram_embed", "bigram_proj", "bigram_scale", "smear_gate", "skip_weights", "ve_embed", "ve_proj",
-                 "ve_scale", "ve_layer_scales", "lm_head", "embed_proj_in", "embed_proj_out"):
+                 "ve_scale", "ve_layer_scales", "lm_head", "embed_proj_in", "embed_proj_out", "vocab_bias"):
         if name in shapes:
             if name not in by:
                 raise C.ArtifactError(f"artifact is missing tensor {name}")
             p[name] = torch.from_numpy(_np(by[name]).astype(np.float32)).reshape(shapes[name])
     for k in ("attn_scale", "mlp_scale", "resid_mix", "q_gain", "attn_gate_weight", "attn_gate_bias", "sparse_attn_gate_weight", "vr_lambda", "dtg_gate_weight",
-              "dtg_gate_bias"):
+              "dtg_gate_bias", "block_smear_gate"):
         if k in shapes:
             p[k] = torch.stack([torch.from_numpy(_np(by[f"blocks.{i}.{k}"]).astype(np.float32)) for i in range(n)]).reshape(shapes[k])
     return {k: v.to(device=device, dtype=dtype) for k, v in p.items()}

@@ -84,6 +84,8 @@ def scheme_bits(scheme: str, matrix_bits: int = 6, embed_bits: int = 8) -> Dict[
         a, m, e = 7, 4, 8
     elif scheme == "ternary_b158":       # matrix groups are ternary codes (stored base-3, 1.6 bits each); the value is a marker
         a, m, e = 2, 2, embed_bits
+    elif scheme == "binary_b1":          # matrix groups are sign codes, one bit each; the value is a marker
+        a, m, e = 1, 1, embed_bits
     else:
         raise ValueError(f"unknown quant scheme {scheme!r}")
     out = {g: a for g in attn}

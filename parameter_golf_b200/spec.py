@@ -27,7 +27,7 @@ RUN_MODES = ("smoke", "proxy", "record_shaped_proxy", "record")
 TRAIN_BACKENDS = ("cpu", "cuda_single", "cuda_single_parity", "cuda_distributed")
 DIST_OPT_BACKENDS = ("all_reduce_replicated_muon", "sharded_parallel_muon")
 QUANT_SCHEMES = ("none", "gptq_lite_int6", "mixed_int5_int6", "aggressive", "tight_int7_int4", "full_gptq_int6",
-                 "int8_zlib", "ternary_b158")       # int8_zlib: the baseline trainer's per-row int8 + zlib-9 export (train_gpt.py:342-422)
+                 "int8_zlib", "ternary_b158", "binary_b1")       # int8_zlib: the baseline trainer's per-row int8 + zlib-9 export (train_gpt.py:342-422)
 COMPRESSION_MODES = ("none", "zstd22", "lzma9", "pergroup")
 CALIBRATION_MODES = ("disabled", "self_generated")
 ADAPTATION_BACKENDS = ("none", "cpu_q_only", "gpu_lora_phased", "full_sgd", "lact", "slot")
@@ -38,6 +38,7 @@ FAMILIES = (
     # families of this framework, named after the benchmark configurations
     "tiny_cpu", "baseline_9l", "record_11l",
     "ternary_10l",       # the 2026-03-24 ternary record's shape: autograd path only (head_dim 96, ternary QAT)
+    "binary_15l",        # the 2026-03-24 binary non-record submission's shape: 15 x 768, 1-bit weights, per-block smear; autograd path only
 )
 
 
@@ -99,7 +100,7 @@ class ModelSpec:
     num_heads: int = 8
     num_kv_heads: int = 4
     mlp_mult: float = 3.0
-    activation: str = "leaky_relu_sq"     # relu_sq | leaky_relu_sq
+    activation: str = "leaky_relu_sq"     # relu_sq | leaky_relu_sq | swiglu (autograd path only: mlp_up_bank holds gate rows then up rows)
     leaky_slope: float = 0.5
     train_seq_len: int = 2048
     eval_seq_len: int = 2048
@@ -130,8 +131,12 @@ class ModelSpec:
     z_loss_weight: float = 0.0            # training only: this weight times the mean squared log-partition is added to the loss
     embed_dim: int = 0                    # > 0: factored tied embedding, tok_emb [V, embed_dim] with learned projections to and from
                                           # model_dim (the ternary record's 254-wide bottleneck); 0 = tok_emb [V, model_dim]
-    qat_kind: str = "int6"                # what QAT simulates in the bank matrices: int6 rows, or ternary codes with one scale per group
-    qat_ternary_group: int = 128          # qat_kind = ternary: input columns per scale (keep equal to quant.ternary_group)
+    qat_kind: str = "int6"                # what QAT simulates in the bank matrices: int6 rows, or ternary / binary codes with one scale per group
+    qat_ternary_group: int = 128          # qat_kind = ternary | binary: input columns per scale (keep equal to quant.ternary_group)
+    normed_out_proj: bool = False         # RMSNorm on the inputs of the attention output and MLP down projections (the ternary and
+                                          # binary submissions' "normed" linear layers, which see un-normalised activations)
+    vocab_bias: bool = False              # a learned bias per vocabulary entry added to the logits before the soft-cap (zero at the start)
+    block_smear: bool = False             # every block ends with x + tanh(g) * (causal running mean of x - x), g[d] learned per block from zero
     fp8_qat: bool = False                 # while QAT is on, the small 2-D float tensors (bigram / value-embedding tables and
                                           # projections, an untied head) go through an FP8 e4m3 round trip (FP_STORAGE=FP8)
 
@@ -145,7 +150,7 @@ class ModelSpec:
 
     @property
     def mlp_dim(self) -> int:
-        return int(self.mlp_mult * self.model_dim)
+        return int(self.mlp_mult * self.model_dim + 1e-6)        # MLP_HIDDEN / model_dim * model_dim must give MLP_HIDDEN back
 
     @property
     def rope_dims(self) -> int:
@@ -408,6 +413,9 @@ class RunSpec:
         if has("TRAIN_LOG_EVERY"): t.train_log_every = I("TRAIN_LOG_EVERY")
         if has("ITERATIONS"): t.total_iterations = I("ITERATIONS")
         if has("WARMDOWN_ITERS"): t.warmdown_iters = I("WARMDOWN_ITERS")
+        if has("WARMDOWN_FRACTION"): t.warmdown_frac = F("WARMDOWN_FRACTION")
+        if has("WARMDOWN_FRAC"): t.warmdown_frac = F("WARMDOWN_FRAC")
+        if has("GRAD_ACCUM_STEPS"): t.grad_accum_steps = I("GRAD_ACCUM_STEPS")
         if has("WARMUP_STEPS"): t.warmup_steps = I("WARMUP_STEPS")
         if has("TRAIN_BATCH_TOKENS"): t.batch_tokens = I("TRAIN_BATCH_TOKENS")
         if has("TRAIN_SEQ_LEN"): t.seq_len = m.train_seq_len = I("TRAIN_SEQ_LEN")
@@ -421,6 +429,11 @@ class RunSpec:
         if has("MODEL_DIM"): m.model_dim = I("MODEL_DIM")
         if has("NUM_HEADS"): m.num_heads = I("NUM_HEADS")
         if has("MLP_MULT"): m.mlp_mult = F("MLP_MULT")
+        if has("MLP_HIDDEN") and I("MLP_HIDDEN") > 0: m.mlp_mult = I("MLP_HIDDEN") / m.model_dim
+        if has("ACTIVATION"):
+            m.activation = {"relu2": "relu_sq", "relu_sq": "relu_sq", "leaky_relu_sq": "leaky_relu_sq", "swiglu": "swiglu"}.get(env["ACTIVATION"].lower(), env["ACTIVATION"].lower())
+        if has("SMEAR"): m.block_smear = B("SMEAR")
+        if has("BITNET_GROUP_SIZE"): m.qat_ternary_group = q.ternary_group = I("BITNET_GROUP_SIZE")
         if has("TIE_EMBEDDINGS"): m.tie_embeddings = B("TIE_EMBEDDINGS")
         if has("ROPE_BASE"): m.rope.base = F("ROPE_BASE")
         if has("ROPE_DIMS"): m.rope.dims = I("ROPE_DIMS")
@@ -506,7 +519,9 @@ class RunSpec:
         chk(0.0 <= t.complementary_alpha <= 1.0, "train.complementary_alpha must be in [0, 1]")
         chk(t.complementary_shape in ("linear", "power", "floored"), "unknown train.complementary_shape")
         chk(t.muon_ns_profile in NS_PROFILES, f"train.muon_ns_profile must be one of {NS_PROFILES}")
-        chk(m.activation in ("relu_sq", "leaky_relu_sq"), "model.activation must be relu_sq or leaky_relu_sq")
+        chk(m.activation in ("relu_sq", "leaky_relu_sq", "swiglu"), "model.activation must be relu_sq, leaky_relu_sq or swiglu")
+        chk(not (m.activation == "swiglu" or m.normed_out_proj or m.block_smear or m.vocab_bias) or t.backend == "cpu",
+            "model.activation=swiglu, model.normed_out_proj, model.block_smear and model.vocab_bias run on train.backend=cpu only")
         chk(m.rope.mode in ("none", "partial", "yarn"), "unknown rope.mode")
         chk(m.rope.mode != "yarn" or (m.rope.yarn_max_len > 0 and m.rope.yarn_train_len > 0), "rope.mode=yarn needs yarn_max_len and yarn_train_len > 0")
         chk(m.skip_topology in ("none", "unet"), "unknown skip_topology")
@@ -527,12 +542,13 @@ class RunSpec:
         chk(m.embed_dim == 0 or (m.tie_embeddings and 0 < m.embed_dim <= m.model_dim), "model.embed_dim needs tied embeddings and 0 < embed_dim <= model_dim")
         chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
         chk(e.temperature > 0 and all(x > 0 for x in e.temperature_grid), "eval.temperature and its grid must be positive")
-        chk(m.qat_kind in ("int6", "ternary"), "model.qat_kind must be int6 or ternary")
-        chk(m.qat_kind != "ternary" or t.backend == "cpu", "model.qat_kind=ternary runs on train.backend=cpu only")
+        chk(m.qat_kind in ("int6", "ternary", "binary"), "model.qat_kind must be int6, ternary or binary")
+        chk(m.qat_kind == "int6" or t.backend == "cpu", "model.qat_kind=ternary|binary runs on train.backend=cpu only")
         chk(q.ternary_group >= 8, "quant.ternary_group must be >= 8")
-        chk(m.qat_kind != "ternary" or q.scheme != "ternary_b158" or m.qat_ternary_group == q.ternary_group,
+        chk(not ((m.qat_kind == "ternary" and q.scheme == "ternary_b158") or (m.qat_kind == "binary" and q.scheme == "binary_b1"))
+            or m.qat_ternary_group == q.ternary_group,
             "model.qat_ternary_group and quant.ternary_group must agree: what is trained is what is stored")
-        chk(q.scheme != "ternary_b158" or not q.lqer.enabled, "the ternary scheme has no low-rank residual")
+        chk(q.scheme not in ("ternary_b158", "binary_b1") or not q.lqer.enabled, "the ternary and binary schemes have no low-rank residual")
         chk(not t.lawa_enabled or (t.lawa_k >= 1 and t.lawa_freq >= 1), "train.lawa_k and train.lawa_freq must be >= 1")
         chk(m.vocab_size <= 65536, "token ids are uint16: vocab_size must be <= 65536")
         chk(not (m.attn_out_gate.enabled and m.sparse_attn_gate.enabled),
@@ -643,9 +659,37 @@ def family_preset(family: str) -> RunSpec:
         t.backend, t.batch_tokens, t.seq_len = "cpu", 524_288, 1024
         t.qat_enabled, t.late_qat_threshold = True, 0.0
         t.matrix_lr, t.scalar_lr, t.tied_embed_lr, t.head_lr = 0.04, 0.02, 0.02, 0.02
-        t.muon_wd, t.muon_ns_steps, t.muon_momentum_warmup_steps = 0.0, 3, 500
+        t.muon_momentum, t.muon_momentum_warmup_start, t.muon_momentum_warmup_steps = 0.95, 0.85, 500
+        t.muon_wd, t.adam_wd, t.muon_ns_steps = 0.0, 0.05, 3
         t.total_iterations, t.warmup_steps, t.max_wallclock_seconds = 10000, 5, 599.0
+        t.warmdown_frac = 0.2
+        t.grad_clip_norm, t.ema_decay, t.swa_enabled = 0.0, 0.0, False      # the script's defaults: no clipping, no weight averaging
+        m.normed_out_proj = m.vocab_bias = True
         s.quant.scheme, s.quant.compression, s.quant.float_storage = "ternary_b158", "lzma9", "fp8"
+        s.quant.prune_to_target = False
+        s.eval.stride = 16
+    elif family == "binary_15l":
+        # records/track_non_record_16mb/2026-03-24_106M_Binary_Asymmetric_UNet_FP8_15L_8192BPE_YaRN_NeoMuon_Smear (README "Architecture",
+        # run_cuda_binary.sh): the ternary recipe with 1-bit weights, 15 blocks (7 before the U-Net's turn, 8 after) and the
+        # per-block running-mean smear; 50,000 steps with no wall-clock cap, the last fifth of them warm-down.
+        m.vocab_size, m.num_layers, m.model_dim, m.num_heads, m.num_kv_heads = 8192, 15, 768, 8, 4
+        m.mlp_mult, m.activation = 4.0, "relu_sq"
+        m.train_seq_len = m.eval_seq_len = 1024
+        m.rope = RopeSpec("yarn", 0, 5000.0, 2048, 1024)
+        m.logit_softcap, m.qk_gain_init = 10.0, 2.25
+        m.softcap_kind, m.z_loss_weight = "poly5", 1e-4
+        m.embed_dim = 254
+        m.qat_kind, m.fp8_qat = "binary", True
+        m.normed_out_proj, m.block_smear, m.vocab_bias = True, True, True
+        t.backend, t.batch_tokens, t.seq_len = "cpu", 524_288, 1024
+        t.qat_enabled, t.late_qat_threshold = True, 0.0
+        t.matrix_lr, t.scalar_lr, t.tied_embed_lr, t.head_lr = 0.04, 0.02, 0.02, 0.02
+        t.muon_momentum, t.muon_momentum_warmup_start, t.muon_momentum_warmup_steps = 0.95, 0.85, 500
+        t.muon_wd, t.adam_wd, t.muon_ns_steps = 0.0, 0.05, 3
+        t.total_iterations, t.warmup_steps, t.max_wallclock_seconds = 50000, 5, 0.0
+        t.warmdown_frac, t.swa_enabled = 0.2, False
+        t.grad_clip_norm, t.ema_decay = 0.0, 0.0
+        s.quant.scheme, s.quant.compression, s.quant.float_storage = "binary_b1", "lzma9", "fp8"
         s.quant.prune_to_target = False
         s.eval.stride = 16
     else:

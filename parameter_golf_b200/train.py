@@ -34,7 +34,7 @@ from .eval.ttt import eval_lora_phased_ttt, eval_score_first_ttt
 from .models import gpt
 from .models.runner import OracleRunner
 from .parallel.agree import agree
-from .optim.muon import AdamW, Ema, Lawa, Muon, ShardedMuon, Swa, clip_grads_, lr_scale_with_floor, muon_momentum_at, wallclock_lr_scale
+from .optim.muon import AdamW, Ema, Lawa, Muon, ShardedMuon, Swa, clip_grads_, fraction_lr_scale, lr_scale_with_floor, muon_momentum_at, wallclock_lr_scale
 from .quant.export import check_budget, code_bytes, export_model, load_artifact
 from .spec import RunSpec, family_preset
 from .utils.checkpoint import load_checkpoint, save_checkpoint
@@ -370,7 +370,9 @@ class VariantRunner:
                 res.stopped_early = True
                 log.info(f"stopping_early: wallclock_cap train_time:{elapsed:.0f}ms step:{step}/{max_steps}")
                 break
-            if t.wallclock_warmdown and max_ms is not None:
+            if t.wallclock_warmdown and max_ms is not None and t.warmdown_frac > 0:
+                scale = fraction_lr_scale(step, elapsed, max_steps, t.warmdown_frac, max_ms)    # the last fraction of the time budget
+            elif t.wallclock_warmdown and max_ms is not None:
                 scale = wallclock_lr_scale(step, elapsed, max_steps, t.warmdown_iters, max_ms)
             else:
                 wd = int(round(max_steps * t.warmdown_frac)) if t.warmdown_frac > 0 else min(t.warmdown_iters, max_steps)

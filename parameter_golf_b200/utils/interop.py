@@ -79,7 +79,7 @@ def from_python_state_dict(m: ModelSpec, sd: Dict[str, torch.Tensor]) -> Dict[st
     p: Dict[str, torch.Tensor] = {}
     direct = {"tok_emb.weight": "tok_emb", "qo_bank": "qo_bank", "kv_bank": "kv_bank", "mlp_up_bank": "mlp_up_bank", "mlp_down_bank": "mlp_down_bank",
               "skip_weights": "skip_weights", "smear.gate": "smear_gate", "bigram.embed.weight": "bigram_embed", "bigram.proj.weight": "bigram_proj",
-              "ve_shared.embed.weight": "ve_embed", "ve_shared.proj.weight": "ve_proj", "lm_head.weight": "lm_head"}
+              "ve_shared.embed.weight": "ve_embed", "ve_shared.proj.weight": "ve_proj", "lm_head.weight": "lm_head", "vocab_bias": "vocab_bias"}
     for src, dst in direct.items():
         if src in sd:
             p[dst] = sd[src].float()
@@ -96,6 +96,8 @@ def from_python_state_dict(m: ModelSpec, sd: Dict[str, torch.Tensor]) -> Dict[st
     if "blocks.0.dtg_gate.weight" in sd:
         p["dtg_gate_weight"] = torch.stack([sd[f"blocks.{i}.dtg_gate.weight"].float().reshape(-1) for i in range(n)])
         p["dtg_gate_bias"] = torch.stack([sd[f"blocks.{i}.dtg_gate.bias"].float().reshape(()) for i in range(n)])
+    if "blocks.0.smear.gate" in sd:
+        p["block_smear_gate"] = torch.stack([sd[f"blocks.{i}.smear.gate"].float() for i in range(n)])
     heads = [sd[k].float() for k in sorted((k for k in sd if k.startswith("mtp_heads.") and k.endswith(".weight")), key=lambda k: int(k.split(".")[1]))]
     if heads:
         p["mtp_heads"] = torch.stack(heads)
@@ -139,11 +141,15 @@ def to_python_state_dict(m: ModelSpec, p: Dict[str, torch.Tensor]) -> Dict[str, 
         if "dtg_gate_weight" in p:
             sd[f"blocks.{i}.dtg_gate.weight"] = p["dtg_gate_weight"][i].reshape(1, -1)
             sd[f"blocks.{i}.dtg_gate.bias"] = p["dtg_gate_bias"][i].reshape(1)
+        if "block_smear_gate" in p:
+            sd[f"blocks.{i}.smear.gate"] = p["block_smear_gate"][i]
     if "mtp_heads" in p:
         for k in range(p["mtp_heads"].shape[0]):
             sd[f"mtp_heads.{k}.weight"] = p["mtp_heads"][k]
     if "lm_head" in p:
         sd["lm_head.weight"] = p["lm_head"]
+    if "vocab_bias" in p:
+        sd["vocab_bias"] = p["vocab_bias"]
     return sd
 
 

@@ -256,3 +256,80 @@ def test_factored_tied_embedding_projects_in_and_out():
     top2 = logits.topk(2, dim=-1).values
     decided = (top2[..., 0] - top2[..., 1]) > 1e-3
     assert bool(((logits.argmax(-1)[:, :-1] == toks[:, 1:]) | ~decided[:, :-1]).all())
+
+
+def _variant(*ov):
+    s = family_preset("tiny_cpu")
+    s.apply_overrides(list(ov))
+    s.validate()
+    return s
+
+
+def test_swiglu_normed_projections_block_smear_and_vocab_bias_match_plain_statements():
+    """The options of the ternary / binary submissions' blocks (train_gpt_cuda_binary.py:617-656, :692-700) against statements
+    written out here: SwiGLU with the gate in the first half of the up projection, RMSNorm in front of the two output
+    projections, the running-mean smear at the end of every block, a bias per vocabulary entry on the logits."""
+    import torch.nn.functional as F
+    from parameter_golf_b200.ops import reference as R
+    s = _variant("model.activation=swiglu", "model.normed_out_proj=true", "model.block_smear=true", "model.vocab_bias=true", "model.skip_topology=none")
+    m = s.model
+    shapes = gpt.param_shapes(m)
+    assert shapes["mlp_up_bank"] == (m.num_layers, 2 * m.mlp_dim, m.model_dim) and shapes["block_smear_gate"] == (m.num_layers, m.model_dim)
+    assert shapes["vocab_bias"] == (m.vocab_size,)
+    p = gpt.fill_deterministic(m)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, m.vocab_size, (2, 24), generator=g)
+    n, H, Hkv, D, d = m.num_layers, m.num_heads, m.num_kv_heads, m.head_dim, m.model_dim
+    x = R.rms_norm(p["tok_emb"][ids])
+    x0 = x
+    cos, sin = R.model_rope_tables(m, 24)
+    for i in range(n):
+        x_in = p["resid_mix"][i][0] * x + p["resid_mix"][i][1] * x0
+        h = R.rms_norm(x_in)
+        q = F.linear(h, p["qo_bank"][i]).reshape(2, 24, H, D)
+        k = F.linear(h, p["kv_bank"][i]).reshape(2, 24, Hkv, D)
+        v = F.linear(h, p["kv_bank"][n + i]).reshape(2, 24, Hkv, D)
+        q, k = R.qk_norm_rope_gain(q, k, cos, sin, m.rope_dims, p["q_gain"][i])
+        y = R.causal_gqa_attention(q, k, v).reshape(2, 24, d)
+        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + 1e-6)
+        x_mid = x_in + p["attn_scale"][i] * F.linear(y, p["qo_bank"][n + i])
+        u = F.linear(R.rms_norm(x_mid), p["mlp_up_bank"][i])
+        hid = F.silu(u[..., : m.mlp_dim]) * u[..., m.mlp_dim:]
+        hid = hid * torch.rsqrt(hid.pow(2).mean(-1, keepdim=True) + 1e-6)
+        out = x_mid + p["mlp_scale"][i] * F.linear(hid, p["mlp_down_bank"][i])
+        mean = torch.stack([out[:, : t + 1].mean(1) for t in range(24)], dim=1)
+        x = out + torch.tanh(p["block_smear_gate"][i]) * (mean - out)
+    z = F.linear(R.rms_norm(x), p["tok_emb"]) + p["vocab_bias"]
+    want = R.softcap(z, m.logit_softcap, m.softcap_kind)
+    got = gpt.gpt_logits(m, p, ids)
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+    # the smear is causal: changing the last token leaves every earlier position as it was
+    ids2 = ids.clone()
+    ids2[:, -1] = (ids2[:, -1] + 1) % m.vocab_size
+    assert torch.allclose(gpt.gpt_logits(m, p, ids2)[:, :-1], got[:, :-1], atol=1e-6)
+    # a zero gate and a zero bias are the identity
+    p0 = dict(p, block_smear_gate=torch.zeros_like(p["block_smear_gate"]), vocab_bias=torch.zeros_like(p["vocab_bias"]))
+    plain = _variant("model.activation=swiglu", "model.normed_out_proj=true", "model.skip_topology=none").model
+    assert torch.allclose(gpt.gpt_logits(m, p0, ids), gpt.gpt_logits(plain, {k: v for k, v in p0.items() if k in gpt.param_shapes(plain)}, ids), atol=1e-6)
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["model.activation=swiglu"]).validate()
+
+
+def test_cached_generation_follows_the_block_options():
+    """Self-generated calibration decodes with a K/V cache; with the block smear it also keeps a running sum per block. Greedy-free
+    check: the logits of the cached decoder at every step equal the full forward's at that position (same seed, same tokens)."""
+    from parameter_golf_b200.quant.calibrate import generate_autoregressive
+    s = _variant("model.activation=swiglu", "model.normed_out_proj=true", "model.block_smear=true", "model.vocab_bias=true")
+    m = s.model
+    p = gpt.fill_deterministic(m)
+    toks = generate_autoregressive(m, p, 2, 12, temperature=0.8, seed=7)
+    again = generate_autoregressive(m, p, 2, 12, temperature=0.8, seed=7)
+    assert torch.equal(toks, again) and toks.shape == (2, 12)
+    # replay: sampling position t + 1 from the full forward's distribution at t with the same generator state gives the same tokens
+    g = torch.Generator().manual_seed(7)
+    first = torch.randint(0, m.vocab_size, (2,), generator=g)
+    assert torch.equal(first, toks[:, 0])
+    for t in range(11):
+        z = gpt.gpt_logits(m, p, toks[:, : t + 1])[:, -1]
+        nxt = torch.multinomial(torch.softmax(z / 0.8, -1), 1, generator=g)[:, 0]
+        assert torch.equal(nxt, toks[:, t + 1]), t

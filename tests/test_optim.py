@@ -120,3 +120,17 @@ def test_momentum_warmup_and_clip():
     n = M.clip_grads_(g, 1.0)
     assert abs(n - math.sqrt(36 + 144)) < 1e-5
     assert abs(math.sqrt(sum(float(x.pow(2).sum()) for x in g)) - 1.0) < 1e-4
+
+
+def test_fraction_warmdown_by_time_and_by_steps():
+    """The last fifth of the budget: of the wall clock when there is a cap (whatever the step count), else of the steps
+    (train_gpt_cuda_ternary.py lr_mul)."""
+    f = M.fraction_lr_scale
+    assert f(10, 100_000.0, 20000, 0.2, 600_000.0) == 1.0
+    assert f(10, 480_000.0, 20000, 0.2, 600_000.0) == 1.0
+    assert abs(f(10, 540_000.0, 20000, 0.2, 600_000.0) - 0.5) < 1e-12
+    assert f(10, 700_000.0, 20000, 0.2, 600_000.0) == 0.0
+    assert f(79, 0.0, 100, 0.2, None) == 1.0 and abs(f(90, 0.0, 100, 0.2, None) - 0.5) < 1e-12 and f(100, 0.0, 100, 0.2, None) == 0.0
+    assert f(5, 0.0, 100, 0.0, 600_000.0) == 1.0
+    # the bug it fixes: a 1200-step window on a run the cap ends after 900 steps decays from the very first step
+    assert M.wallclock_lr_scale(1, 650.0, 20000, 1200, 600_000.0) < 1.0 and f(1, 650.0, 20000, 0.2, 600_000.0) == 1.0

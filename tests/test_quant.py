@@ -417,3 +417,65 @@ def test_ternary_scheme_exports_what_ternary_qat_trains(tmp_path):
         family_preset("record_11l").apply_overrides(["model.qat_kind=ternary"]).validate()
     t = family_preset("ternary_10l").validate()
     assert t.model.head_dim == 96 and t.quant.scheme == "ternary_b158" and t.train.qat_enabled and t.model.rope.mode == "yarn"
+
+
+def test_binary_quantiser_bit_packing_and_scale_rule():
+    """1-bit codes, absmean scale per group (the least-squares scale for sign codes), eight codes per byte with element i in bit
+    i mod 8 (train_gpt_cuda_binary.py:117-127), a ragged last group scaled over the columns that exist."""
+    from parameter_golf_b200.quant import binary as B1
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(6, 200, generator=g)
+    w[0, 0] = 0.0                                        # zero codes as +1
+    q, s = B1.quantize_binary(w, 64)
+    assert q.shape == w.shape and s.shape == (6, 4) and set(q.unique().tolist()) == {-1, 1} and q[0, 0] == 1
+    assert torch.allclose(s[:, 0], w[:, :64].abs().mean(-1)) and torch.allclose(s[:, 3], w[:, 192:].abs().mean(-1))
+    base = (w - B1.dequantize_binary(q, s, 64)).pow(2).sum()
+    for f in (0.9, 1.1):
+        assert (w - B1.dequantize_binary(q, s * f, 64)).pow(2).sum() > base
+    raw = B1.pack_signs(q.numpy())
+    assert len(raw) == (q.numel() + 7) // 8
+    first = q.reshape(-1)[:8].numpy()
+    assert raw[0] == sum(int(first[i] > 0) << i for i in range(8))
+    assert np.array_equal(B1.unpack_signs(raw, q.numel()), q.reshape(-1).numpy())
+    with pytest.raises(ValueError):
+        B1.pack_signs(np.array([0, 1], dtype=np.int8))
+    with pytest.raises(ValueError):
+        B1.unpack_signs(raw[:3], q.numel())
+
+
+def test_binary_scheme_exports_what_binary_qat_trains(tmp_path):
+    """quant.scheme = binary_b1 with model.qat_kind = binary: one bit per bank weight plus fp16 group scales, reloading to exactly
+    the weights the QAT forward used."""
+    from parameter_golf_b200.ops import reference as R
+    from parameter_golf_b200.quant.export import build_artifact
+    s = family_preset("tiny_cpu")
+    s.apply_overrides(["quant.scheme=binary_b1", "quant.compression=lzma9", "quant.ternary_group=64", "model.qat_kind=binary",
+                       "model.qat_ternary_group=64", "quant.prune_to_target=false"])
+    s.validate()
+    m = s.model
+    p = gpt.fill_deterministic(m)
+    blob = export_model(s, p, str(tmp_path / "b.pgrs"))
+    back = load_artifact(blob, s)
+    banks = ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank")
+    for bank in banks:
+        assert torch.allclose(back[bank], R.fake_quant_binary_ste(p[bank], 64), atol=1e-7), bank
+        grp = back[bank].reshape(-1, 64).abs()
+        assert torch.allclose(grp, grp[:, :1].expand_as(grp))                    # one magnitude per group: sign codes
+    ids = torch.randint(0, m.vocab_size, (2, 32))
+    trained = dict(back, **{b: p[b] for b in banks})
+    assert torch.allclose(gpt.gpt_forward(m, back, ids, ids), gpt.gpt_forward(m, trained, ids, ids, qat=True), atol=1e-5)
+    w = p["qo_bank"].clone().requires_grad_(True)
+    (gw,) = torch.autograd.grad(R.fake_quant_binary_ste(w, 64).sum(), w)
+    assert torch.equal(gw, torch.ones_like(w))                                    # straight through
+    raw = build_artifact(s, p)
+    bank_params = sum(p[b].numel() for b in banks)
+    emb_bytes = p["tok_emb"].numel() + 2 * p["tok_emb"].shape[0]
+    assert (len(raw) - emb_bytes) * 8 / bank_params < 1.45                        # 1 bit of code + 0.25 of scales + the small tensors
+    s.quant.code_storage = "bytes"
+    assert torch.equal(load_artifact(export_model(s, p), s)["kv_bank"], back["kv_bank"])
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["model.qat_kind=binary"]).validate()
+    b = family_preset("binary_15l").validate()
+    assert (b.model.num_layers, b.model.head_dim, b.quant.scheme, b.model.block_smear, b.train.max_wallclock_seconds) == (15, 96, "binary_b1", True, 0.0)
+    shapes = gpt.param_shapes(b.model)
+    assert shapes["skip_weights"] == (7, 768)                                     # 7 blocks before the turn, 8 after

@@ -103,6 +103,19 @@ def test_optional_record_ideas_are_cpu_only_and_read_from_the_environment():
     e.validate()
 
 
+def test_binary_submission_environment_names():
+    """run_cuda_binary.sh's names: ACTIVATION=relu2 / swiglu, SMEAR (the per-block running-mean smear), BITNET_GROUP_SIZE (both the
+    trained and the stored group), WARMDOWN_FRACTION; the SwiGLU non-record run's MLP_HIDDEN, WARMDOWN_FRAC, GRAD_ACCUM_STEPS."""
+    e = family_preset("tiny_cpu")
+    e.apply_env({"ACTIVATION": "relu2", "SMEAR": "1", "BITNET_GROUP_SIZE": "64", "WARMDOWN_FRACTION": "0.2", "MODEL_DIM": "96", "MLP_HIDDEN": "200",
+                 "GRAD_ACCUM_STEPS": "2"})
+    assert e.model.activation == "relu_sq" and e.model.block_smear and e.model.qat_ternary_group == e.quant.ternary_group == 64
+    assert e.train.warmdown_frac == 0.2 and e.model.mlp_dim == 200 and e.train.grad_accum_steps == 2
+    e.apply_env({"ACTIVATION": "swiglu", "WARMDOWN_FRAC": "0.3"})
+    assert e.model.activation == "swiglu" and e.train.warmdown_frac == 0.3
+    e.validate()
+
+
 def test_key_listing_and_environment_names_follow_the_code():
     """`describe_keys` walks the dataclasses; `env_names` is read off `apply_env` itself: every environment name maps to keys
     that exist, and setting the variable really changes one of them."""

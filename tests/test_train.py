@@ -459,3 +459,37 @@ def test_ternary_family_trains_with_its_estimator_and_round_trips(tmp_path, monk
     codes = (back["mlp_up_bank"].reshape(-1, 64) / back["mlp_up_bank"].reshape(-1, 64).abs().amax(-1, keepdim=True).clamp_min(1e-12)).round()
     assert set(codes.unique().tolist()) <= {-1.0, 0.0, 1.0}
     assert torch.equal(back["bigram_embed"], back["bigram_embed"].to(torch.float8_e4m3fn).float())      # stored as e4m3
+
+
+def test_binary_family_recipe_trains_and_round_trips(tmp_path, monkeypatch):
+    """The binary submission's recipe at a toy size through the trainer: 1-bit QAT from the first step with the matching export,
+    xz, FP8 small tensors, normed output projections, the per-block smear, the vocabulary bias, the time-fraction warm-down."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.apply_overrides(["model.qat_kind=binary", "model.qat_ternary_group=64", "quant.ternary_group=64", "quant.scheme=binary_b1",
+                       "quant.compression=lzma9", "quant.float_storage=fp8", "quant.prune_to_target=false", "train.qat_enabled=true",
+                       "train.muon_ns_steps=3", "model.normed_out_proj=true", "model.block_smear=true", "model.vocab_bias=true",
+                       "model.softcap_kind=poly5", "model.logit_softcap=10", "model.embed_dim=48", "model.fp8_qat=true",
+                       "train.warmdown_frac=0.5", "train.ema_decay=0", "train.swa_enabled=false"])
+    s.train.total_iterations = 4
+    s.train.artifact_path = str(tmp_path / "b.pgrs")
+    s.eval.max_tokens = 512
+    import parameter_golf_b200.train as tr
+    monkeypatch.setattr(tr, "mode_max_steps", lambda spec, mode: 4)
+    seen = []
+    real = tr.OracleBackend.train_step
+
+    def spy(self, batches, scale, mom, qat):
+        seen.append((scale, qat))
+        return real(self, batches, scale, mom, qat)
+    monkeypatch.setattr(tr.OracleBackend, "train_step", spy)
+    res = quiet(s).run()
+    assert res.steps == 4 and np.isfinite(res.val_loss) and res.budget_ok
+    assert [q for _, q in seen] == [True] * 4
+    assert seen[0][0] == 1.0 and seen[-1][0] < 1.0                    # the second half of the run (by time or by steps) decays
+    back = load_artifact(open(s.train.artifact_path, "rb").read(), s)
+    grp = back["mlp_down_bank"].reshape(-1, 64).abs()
+    assert torch.allclose(grp, grp[:, :1].expand_as(grp))             # sign codes: one magnitude per group
+    assert back["block_smear_gate"].shape == (s.model.num_layers, s.model.model_dim) and back["vocab_bias"].shape == (s.model.vocab_size,)
+    assert float(back["block_smear_gate"].abs().max()) > 0.0          # the gates moved off their zero start

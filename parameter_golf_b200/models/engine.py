@@ -49,7 +49,8 @@ def _unsupported(m: ModelSpec) -> Optional[str]:
     only_autograd = [k for k, on in (("value_residual", m.value_residual), ("mtp_num_heads", m.mtp_num_heads > 0), ("dtg", m.dtg),
                                      ("embed_dim", m.embed_dim > 0), ("softcap_kind", m.softcap_kind != "tanh"),
                                      ("activation=swiglu", m.activation == "swiglu"), ("normed_out_proj", m.normed_out_proj),
-                                     ("block_smear", m.block_smear), ("vocab_bias", m.vocab_bias)) if on]
+                                     ("block_smear", m.block_smear), ("vocab_bias", m.vocab_bias),
+                                     ("recurrence.effective_depth", m.cycled)) if on]
     if only_autograd:
         return "model options of the autograd path (" + ", ".join(only_autograd) + ")"
     if m.model_dim % 64 or m.kv_dim % 64 or m.mlp_dim % 64 or m.head_dim % 8 or m.vocab_size % 64:

@@ -34,7 +34,7 @@ def up_rows(m: ModelSpec) -> int:
 
 def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
     n, d, kv, mlp, H = m.num_layers, m.model_dim, m.kv_dim, m.mlp_dim, m.num_heads
-    enc = n // 2
+    enc = m.depth // 2                 # the U-Net split counts virtual layers (= blocks unless they are cycled)
     sh = {
         "tok_emb": (m.vocab_size, m.embed_dim if m.embed_dim > 0 else d),
         "qo_bank": (2 * n, d, d),
@@ -46,8 +46,8 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
         "resid_mix": (n, 2, d),
         "q_gain": (n, H),
     }
-    if m.skip_topology == "unet" and min(enc, n - enc) > 0:
-        sh["skip_weights"] = (min(enc, n - enc), d)
+    if m.skip_topology == "unet" and min(enc, m.depth - enc) > 0:
+        sh["skip_weights"] = (min(enc, m.depth - enc), d)
     if m.smear_gate:
         sh["smear_gate"] = (d,)
     if m.bigram.enabled:
@@ -81,6 +81,12 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
         sh["block_smear_gate"] = (n, d)
     if m.vocab_bias:
         sh["vocab_bias"] = (m.vocab_size,)
+    r = m.recurrence.depth_lora_rank if m.cycled else 0
+    if r > 0:
+        sh["depth_lora_q_down"] = (m.depth, r, d)
+        sh["depth_lora_q_up"] = (m.depth, d, r)
+        sh["depth_lora_v_down"] = (m.depth, r, d)
+        sh["depth_lora_v_up"] = (m.depth, kv, r)
     return sh
 
 
@@ -128,6 +134,9 @@ def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float3
         p["embed_proj_out"] = p["embed_proj_in"].t().contiguous().clone()     # starts as the transpose: the tied pair is consistent
     if "vr_lambda" in p:
         p["vr_lambda"].fill_(0.5)
+    for k in ("depth_lora_q_down", "depth_lora_v_down"):          # the up halves stay zero: the adapters start as no-ops
+        if k in p:
+            p[k].uniform_(-1.0 / math.sqrt(d), 1.0 / math.sqrt(d), generator=g)
     if "dtg_gate_bias" in p:
         p["dtg_gate_bias"].fill_(2.0)             # sigmoid(2) = 0.88 of the block's update at the start, the weight at zero
     return {k: v.to(device=device, dtype=dtype) for k, v in p.items()}
@@ -205,7 +214,10 @@ def layer_ln_scale(m: ModelSpec, layer: int) -> float:
 
 def layer_schedule(m: ModelSpec):
     """Execution order as (layer index, pass index): recurrent layers run the block twice in a row
-    (``pg-model/src/model.rs:666-671``)."""
+    (``pg-model/src/model.rs:666-671``); in the cycled form the blocks run round robin for ``effective_depth`` executions
+    (records/track_non_record_16mb/2026-03-21_DepthRecurrence_MixedPrecisionQuant/train_gpt.py:863)."""
+    if m.cycled:
+        return [(v % m.num_layers, v // m.num_layers) for v in range(m.depth)]
     order = []
     for i in range(m.num_layers):
         reps = 2 if (m.recurrence.enabled and m.recurrence.start_layer <= i < m.recurrence.start_layer + m.recurrence.repeat_layers) else 1
@@ -213,8 +225,16 @@ def layer_schedule(m: ModelSpec):
     return order
 
 
+def shared_layers(m: ModelSpec) -> set:
+    """Blocks that run more than once in a forward pass."""
+    seen, twice = set(), set()
+    for i, _ in layer_schedule(m):
+        (twice if i in seen else seen).add(i)
+    return twice
+
+
 def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = False, lora=None, return_kv: bool = False, taps=None, v0=None,
-                  return_raw_v: bool = False):
+                  return_raw_v: bool = False, depth_index: Optional[int] = None):
     """One block. ``v0`` / ``return_raw_v`` serve the value residual (records/.../2026-03-23_.../train_gpt.py:655-658): the
     block's own value projection is handed back, and when an earlier layer's is given the attention runs on
     ``lambda_0 * v0 + lambda_1 * v``."""
@@ -230,6 +250,10 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
             wq, wo, wk, wv, wu, wd = (R.fake_quant_ternary_ste(w, m.qat_ternary_group) for w in (wq, wo, wk, wv, wu, wd))
         elif m.qat_kind == "binary":
             wq, wo, wk, wv, wu, wd = (R.fake_quant_binary_ste(w, m.qat_ternary_group) for w in (wq, wo, wk, wv, wu, wd))
+        elif m.qat_kind == "noise":
+            shared = shared_layers(m)
+            if not shared or i in shared:
+                wq, wo, wk, wv, wu, wd = (R.quant_noise(w, m.qat_noise_qmax) for w in (wq, wo, wk, wv, wu, wd))
         else:
             wq, wo, wk, wv, wu, wd = (R.fake_quant_int6_ste(w) for w in (wq, wo, wk, wv, wu, wd))
     s_l = layer_ln_scale(m, i)
@@ -244,6 +268,10 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
         q = q + (alpha / a.shape[0]) * F.linear(F.linear(h, a.to(dt)), b.to(dt))
     k = F.linear(h, wk.to(dt))
     v = F.linear(h, wv.to(dt))
+    if depth_index is not None and "depth_lora_q_up" in p:
+        # per-virtual-layer corrections of a shared block's query and value projections (…DepthRecurrence…/train_gpt.py:771-793, :755-760)
+        q = q + F.linear(F.linear(h, p["depth_lora_q_down"][depth_index].to(dt)), p["depth_lora_q_up"][depth_index].to(dt))
+        v = v + F.linear(F.linear(h, p["depth_lora_v_down"][depth_index].to(dt)), p["depth_lora_v_up"][depth_index].to(dt))
     if m.value_embedding.enabled and i in m.value_embedding.layers:
         li = m.value_embedding.layers.index(i)
         ve = F.linear(_small(m, p, "ve_embed", qat)[ids].to(dt), _small(m, p, "ve_proj", qat).to(dt))
@@ -306,22 +334,25 @@ def gpt_hidden(m: ModelSpec, p, ids: torch.Tensor, qat: bool = False, lora=None,
     x0 = x
     rd = m.rope_dims
     cos, sin = R.model_rope_tables(m, T, device=ids.device)
-    enc = m.num_layers // 2
+    enc = m.depth // 2
     unet = m.skip_topology == "unet" and "skip_weights" in p
     skips = []
     sched = layer_schedule(m)
     v0 = None
     for j, (i, rep) in enumerate(sched):
         last_pass = j + 1 == len(sched) or sched[j + 1][0] != i
-        if unet and i >= enc and rep == 0 and skips:
-            x = x + p["skip_weights"][i - enc].to(dt)[None, None, :] * skips.pop()
+        # position in the U-Net: the block index, or the execution index when the blocks are cycled (every execution is then a layer of its own)
+        pos, first, last = (j, True, True) if m.cycled else (i, rep == 0, last_pass)
+        if unet and pos >= enc and first and skips:
+            x = x + p["skip_weights"][pos - enc].to(dt)[None, None, :] * skips.pop()
         if m.value_residual:
-            x, raw_v = block_forward(m, p, i, x, x0, ids, cos, sin, qat=qat, lora=lora, taps=taps, v0=v0, return_raw_v=True)
+            x, raw_v = block_forward(m, p, i, x, x0, ids, cos, sin, qat=qat, lora=lora, taps=taps, v0=v0, return_raw_v=True,
+                                     depth_index=j if m.cycled else None)
             if v0 is None:
                 v0 = raw_v                  # the first block's values, mixed into every later block's
         else:
-            x = block_forward(m, p, i, x, x0, ids, cos, sin, qat=qat, lora=lora, taps=taps)
-        if unet and i < enc and last_pass:
+            x = block_forward(m, p, i, x, x0, ids, cos, sin, qat=qat, lora=lora, taps=taps, depth_index=j if m.cycled else None)
+        if unet and pos < enc and last:
             skips.append(x)
     return R.rms_norm(x)
 

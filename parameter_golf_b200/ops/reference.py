@@ -224,6 +224,17 @@ def fake_quant_binary_ste(w: torch.Tensor, group: int = 128) -> torch.Tensor:
     return w + (wq - w).detach()
 
 
+def quant_noise(w: torch.Tensor, qmax: int = 127) -> torch.Tensor:
+    """``w + u * step`` with ``u`` uniform in [-0.5, 0.5) and ``step = max|row| / qmax``: noise of the size of a per-row
+    quantisation step instead of the rounding itself. Unlike the straight-through forms the perturbation is part of the
+    graph, so a block that runs several times per pass learns weights that tolerate the error it will carry after export
+    (records/track_non_record_16mb/2026-03-21_DepthRecurrence_MixedPrecisionQuant/README.md "Noisy QAT"). The noise comes from
+    torch's global generator (seed it for a repeatable run)."""
+    with torch.no_grad():
+        step = _f(w).abs().amax(dim=-1, keepdim=True).clamp_min(1e-12) / float(qmax)
+    return w + (torch.rand_like(w) - 0.5) * step.to(w.dtype)
+
+
 def fake_quant_int6_ste(w: torch.Tensor) -> torch.Tensor:
     """Late-QAT straight-through estimator: per-row ``s = max(|w|)/31`` (floored at 1/31),
     ``w_q = clamp(round(w/s), -32, 31) * s``; forward uses ``w_q`` and the gradient passes to ``w``

@@ -86,7 +86,7 @@ class ExecutionPlan:
             micro_batch_tokens = max(t.batch_tokens // (world * accum), t.seq_len)
         sched = gpt.layer_schedule(m)
         saved = saved_slots(sched, t.save_layer_acts)
-        enc = n // 2
+        enc = m.depth // 2
         unet = m.skip_topology == "unet"
         passes: Dict[int, int] = {}
         for l, _ in sched:
@@ -95,7 +95,7 @@ class ExecutionPlan:
                                   value_embedding=m.value_embedding.enabled and l in m.value_embedding.layers,
                                   recurrent=passes[l] > 1, parallel_residual=m.parallel_residual.enabled,
                                   attn_out_gate=m.attn_out_gate.enabled, sparse_attn_gate=m.sparse_attn_gate.enabled,
-                                  saved=saved[j], unet_role=("encoder" if l < enc else "decoder") if unet else "none")
+                                  saved=saved[j], unet_role=("encoder" if (j if m.cycled else l) < enc else "decoder") if unet else "none")
                  for j, (l, rep) in enumerate(sched)]
         q, e = spec.quant, spec.eval
         return ExecutionPlan(

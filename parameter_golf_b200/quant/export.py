@@ -25,6 +25,7 @@ from . import container as C
 from .quantize import GROUPS, LqerFactors, dequantize_rows, lqer_factors, lqer_reconstruct, prune_rows, quantize_rows, scheme_bits
 
 CODE_BUDGET_ENV = "PG_SUBMISSION_CODE_BYTES"
+DEPTH_LORA = ("q_down", "q_up", "v_down", "v_up")
 
 
 def _f16(name, t) -> C.TensorRecord:
@@ -159,6 +160,10 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
         recs.append(_flt("lm_head", params["lm_head"], spec.quant.float_storage))
     if m.vocab_bias:
         recs.append(_f16("vocab_bias", params["vocab_bias"]))
+    if "depth_lora_q_up" in params:
+        for v in range(m.depth):
+            for k in DEPTH_LORA:
+                recs.append(_f16(f"depth.{v}.{k}", params[f"depth_lora_{k}"][v]))
     if m.embed_dim > 0:
         recs.append(_flt("embed_proj_in", params["embed_proj_in"], spec.quant.float_storage))
         recs.append(_flt("embed_proj_out", params["embed_proj_out"], spec.quant.float_storage))
@@ -306,6 +311,9 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
               "dtg_gate_bias", "block_smear_gate"):
         if k in shapes:
             p[k] = torch.stack([torch.from_numpy(_np(by[f"blocks.{i}.{k}"]).astype(np.float32)) for i in range(n)]).reshape(shapes[k])
+    for k in DEPTH_LORA:
+        if f"depth_lora_{k}" in shapes:
+            p[f"depth_lora_{k}"] = torch.stack([torch.from_numpy(_np(by[f"depth.{v}.{k}"]).astype(np.float32)) for v in range(m.depth)])
     return {k: v.to(device=device, dtype=dtype) for k, v in p.items()}
 
 

@@ -1,7 +1,7 @@
 """Ternary (BitNet b1.58) weight quantisation with base-3 packing, the export idea of the record
 ``records/track_10min_16mb/2026-03-24_74M_Ternary_UNet_FP8_10L_8192BPE_YaRN_NeoMuon`` (its README: weights in
 {-1, 0, +1}, per-group (128) absmean scaling, 5 trits per byte, LZMA preset 9, and a scale correction for the fraction of
-zeros). The record ships no training script in this tree, so the statements below are this framework's own:
+zeros; ``train_gpt_cuda_ternary.py:186-260`` is its export). The statements below are this framework's own form of it:
 
 * a row is cut into groups of ``group`` columns; ``s = mean(|w|)`` per group; ``q = clamp(round(w / s), -1, 1)``;
 * *shrinkage fix*: after rounding, the scale that minimises ``||w - s q||^2`` for the chosen ``q`` is

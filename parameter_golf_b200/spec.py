@@ -70,6 +70,11 @@ class RecurrenceSpec:
     enabled: bool = False
     start_layer: int = 0
     repeat_layers: int = 0
+    # Cycled form (autograd path only; records/track_non_record_16mb/2026-03-21_DepthRecurrence_MixedPrecisionQuant/train_gpt.py:831-863):
+    # with effective_depth > num_layers the num_layers unique blocks run in the order 0, 1, ..., n-1, 0, 1, ... for
+    # effective_depth virtual layers; the U-Net split, its skip weights and xsa_last_n then count virtual layers.
+    effective_depth: int = 0
+    depth_lora_rank: int = 0          # > 0: a low-rank correction of the query and value projections per virtual layer (its DepthLoRA)
 
 
 @dataclass
@@ -132,6 +137,8 @@ class ModelSpec:
     embed_dim: int = 0                    # > 0: factored tied embedding, tok_emb [V, embed_dim] with learned projections to and from
                                           # model_dim (the ternary record's 254-wide bottleneck); 0 = tok_emb [V, model_dim]
     qat_kind: str = "int6"                # what QAT simulates in the bank matrices: int6 rows, or ternary / binary codes with one scale per group
+    qat_noise_qmax: int = 127             # qat_kind = noise: uniform noise of one quantisation step (row max / qmax) on the blocks that run more
+                                          # than once (all blocks when none does), with gradients flowing through it
     qat_ternary_group: int = 128          # qat_kind = ternary | binary: input columns per scale (keep equal to quant.ternary_group)
     normed_out_proj: bool = False         # RMSNorm on the inputs of the attention output and MLP down projections (the ternary and
                                           # binary submissions' "normed" linear layers, which see un-normalised activations)
@@ -159,7 +166,20 @@ class ModelSpec:
         d = self.rope.dims
         return self.head_dim if d <= 0 or d >= self.head_dim else d
 
+    @property
+    def cycled(self) -> bool:
+        return self.recurrence.enabled and self.recurrence.effective_depth > 0
+
+    @property
+    def depth(self) -> int:
+        """Virtual layers: block executions whose position counts for the U-Net split and the per-depth adapters."""
+        return self.recurrence.effective_depth if self.cycled else self.num_layers
+
     def xsa_layers(self) -> list:
+        """Blocks with the exclusive-self-attention step: the last xsa_last_n layers; in the cycled form every block that runs as
+        one of the last xsa_last_n virtual layers (the flag sits on the block, so it holds in all of that block's passes)."""
+        if self.cycled:
+            return sorted({v % self.num_layers for v in range(max(0, self.depth - self.xsa_last_n), self.depth)})
         return list(range(max(0, self.num_layers - self.xsa_last_n), self.num_layers))
 
 
@@ -472,6 +492,14 @@ class RunSpec:
             m.bigram.enabled = m.bigram.vocab_size > 0
         if has("BIGRAM_DIM"): m.bigram.dim = I("BIGRAM_DIM")
         if has("XSA_LAST_N"): m.xsa_last_n = I("XSA_LAST_N")
+        if has("NUM_UNIQUE_BLOCKS"): m.num_layers = I("NUM_UNIQUE_BLOCKS")
+        if has("EFFECTIVE_DEPTH"):
+            m.recurrence.effective_depth = I("EFFECTIVE_DEPTH")
+            m.recurrence.enabled = m.recurrence.effective_depth > 0
+        if has("DEPTH_LORA_RANK"): m.recurrence.depth_lora_rank = I("DEPTH_LORA_RANK")
+        if has("BIGRAM_BUCKETS"):
+            m.bigram.vocab_size = I("BIGRAM_BUCKETS")
+            m.bigram.enabled = m.bigram.vocab_size > 0
         if has("EMBED_DIM"): m.embed_dim = I("EMBED_DIM")
         if has("SOFTCAP_TYPE"): m.softcap_kind = "poly5" if env["SOFTCAP_TYPE"].lower().startswith("poly") else "tanh"
         if has("VALUE_RESIDUAL"): m.value_residual = B("VALUE_RESIDUAL")
@@ -531,7 +559,13 @@ class RunSpec:
         chk(m.head_dim % 2 == 0, "head_dim must be even for RoPE")
         chk(m.rope_dims % 2 == 0 and m.rope_dims <= m.head_dim, "rope.dims must be even and <= head_dim")
         chk(m.logit_softcap > 0, "logit_softcap must be positive")
-        chk(m.xsa_last_n <= m.num_layers, "xsa_last_n exceeds num_layers")
+        chk(m.xsa_last_n <= m.depth, "xsa_last_n exceeds the number of layers")
+        rc = m.recurrence
+        chk(rc.effective_depth == 0 or (rc.enabled and rc.effective_depth >= m.num_layers and rc.repeat_layers == 0),
+            "recurrence.effective_depth needs recurrence.enabled, effective_depth >= num_layers and repeat_layers = 0")
+        chk(rc.depth_lora_rank == 0 or m.cycled, "recurrence.depth_lora_rank needs the cycled form (recurrence.effective_depth)")
+        chk(not m.cycled or t.backend == "cpu", "recurrence.effective_depth (cycled blocks) runs on train.backend=cpu only")
+        chk(m.qat_noise_qmax >= 1, "model.qat_noise_qmax must be >= 1")
         chk(m.mtp_num_heads >= 0 and m.mtp_loss_weight >= 0.0, "mtp_num_heads and mtp_loss_weight must be >= 0")
         chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat or m.dtg or m.embed_dim > 0) or t.backend == "cpu",
             "model.value_residual, model.mtp_num_heads, model.dtg, model.embed_dim and model.fp8_qat run on train.backend=cpu only "
@@ -542,8 +576,8 @@ class RunSpec:
         chk(m.embed_dim == 0 or (m.tie_embeddings and 0 < m.embed_dim <= m.model_dim), "model.embed_dim needs tied embeddings and 0 < embed_dim <= model_dim")
         chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
         chk(e.temperature > 0 and all(x > 0 for x in e.temperature_grid), "eval.temperature and its grid must be positive")
-        chk(m.qat_kind in ("int6", "ternary", "binary"), "model.qat_kind must be int6, ternary or binary")
-        chk(m.qat_kind == "int6" or t.backend == "cpu", "model.qat_kind=ternary|binary runs on train.backend=cpu only")
+        chk(m.qat_kind in ("int6", "ternary", "binary", "noise"), "model.qat_kind must be int6, ternary, binary or noise")
+        chk(m.qat_kind == "int6" or t.backend == "cpu", "model.qat_kind=ternary|binary|noise runs on train.backend=cpu only")
         chk(q.ternary_group >= 8, "quant.ternary_group must be >= 8")
         chk(not ((m.qat_kind == "ternary" and q.scheme == "ternary_b158") or (m.qat_kind == "binary" and q.scheme == "binary_b1"))
             or m.qat_ternary_group == q.ternary_group,

@@ -333,3 +333,81 @@ def test_cached_generation_follows_the_block_options():
         z = gpt.gpt_logits(m, p, toks[:, : t + 1])[:, -1]
         nxt = torch.multinomial(torch.softmax(z / 0.8, -1), 1, generator=g)[:, 0]
         assert torch.equal(nxt, toks[:, t + 1]), t
+
+
+def test_cycled_blocks_with_per_depth_adapters_match_an_unrolled_model():
+    """Three unique blocks cycled to seven virtual layers (…DepthRecurrence…/train_gpt.py:863, :897-919): the same function as a
+    seven-block model whose blocks are copies in round-robin order, with the U-Net split, skip weights and XSA flags counted on
+    virtual layers; the per-depth adapters start as no-ops and, once their up halves are non-zero, add h A^T B^T to q and v."""
+    s = _variant("model.num_layers=3", "model.recurrence.enabled=true", "model.recurrence.effective_depth=7", "model.xsa_last_n=2",
+                 "model.recurrence.depth_lora_rank=2")
+    m = s.model
+    assert gpt.layer_schedule(m) == [(0, 0), (1, 0), (2, 0), (0, 1), (1, 1), (2, 1), (0, 2)] and m.depth == 7
+    assert m.xsa_layers() == [0, 2]                      # virtual layers 5 and 6 are blocks 2 and 0
+    assert gpt.shared_layers(m) == {0, 1, 2}
+    shapes = gpt.param_shapes(m)
+    assert shapes["skip_weights"] == (3, m.model_dim) and shapes["depth_lora_v_up"] == (7, m.kv_dim, 2)
+    p = gpt.fill_deterministic(m)
+    p0 = dict(p, depth_lora_q_up=torch.zeros_like(p["depth_lora_q_up"]), depth_lora_v_up=torch.zeros_like(p["depth_lora_v_up"]))
+    ids = torch.randint(0, m.vocab_size, (2, 16), generator=torch.Generator().manual_seed(1))
+    flat = _variant("model.num_layers=7", "model.xsa_last_n=0").model
+    order = [v % 3 for v in range(7)]
+    pf = {k: v for k, v in p0.items() if not k.startswith("depth_lora")}
+    n = 3
+    pf["qo_bank"] = torch.cat([p["qo_bank"][order], p["qo_bank"][[n + i for i in order]]])
+    pf["kv_bank"] = torch.cat([p["kv_bank"][order], p["kv_bank"][[n + i for i in order]]])
+    for k in ("mlp_up_bank", "mlp_down_bank", "attn_scale", "mlp_scale", "resid_mix", "q_gain"):
+        pf[k] = p[k][order]
+    assert {k: tuple(v.shape) for k, v in pf.items()} == gpt.param_shapes(flat)
+    flat.xsa_last_n = 0
+    real_xsa = type(flat).xsa_layers
+    try:
+        type(flat).xsa_layers = lambda self: [0, 2, 3, 5, 6] if self is flat else real_xsa(self)     # where blocks 0 and 2 sit when unrolled
+        want = gpt.gpt_logits(flat, pf, ids)
+    finally:
+        type(flat).xsa_layers = real_xsa
+    got = gpt.gpt_logits(m, p0, ids)
+    assert torch.allclose(got, want, atol=1e-5), float((got - want).abs().max())
+    moved = gpt.gpt_logits(m, p, ids)
+    assert float((moved - got).abs().max()) > 1e-4
+    # the adapters of one virtual layer do not touch the other executions of the same block: gradient lands on that slice only
+    pg = {k: v.clone().requires_grad_(True) for k, v in p.items()}
+    gpt.gpt_forward(m, pg, ids, ids).backward()
+    assert all(float(pg["depth_lora_q_up"].grad[v].abs().max()) > 0 for v in range(7))
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["model.recurrence.enabled=true", "model.recurrence.effective_depth=22"]).validate()
+    with pytest.raises(ValueError):
+        _variant("model.recurrence.depth_lora_rank=2")
+
+
+def test_noisy_qat_perturbs_shared_blocks_by_one_quantisation_step_with_gradients():
+    from parameter_golf_b200.ops import reference as R
+    torch.manual_seed(0)
+    w = torch.randn(8, 64, requires_grad=True)
+    out = R.quant_noise(w, 127)
+    step = w.detach().abs().amax(-1, keepdim=True) / 127
+    delta = (out - w).detach()
+    assert float((delta.abs() / step).max()) <= 0.5 + 1e-6 and float(delta.abs().mean()) > 0
+    assert abs(float((delta / step).std()) - (1 / 12) ** 0.5) < 0.03            # uniform over one step
+    (g,) = torch.autograd.grad(out.sum(), w)
+    assert torch.equal(g, torch.ones_like(w))
+    s = _variant("model.recurrence.enabled=true", "model.recurrence.start_layer=1", "model.recurrence.repeat_layers=1", "model.qat_kind=noise")
+    m = s.model
+    assert gpt.shared_layers(m) == {1}
+    p = gpt.fill_deterministic(m)
+    ids = torch.randint(0, m.vocab_size, (2, 16), generator=torch.Generator().manual_seed(2))
+    clean = gpt.gpt_forward(m, p, ids, ids)
+    torch.manual_seed(3)
+    a = gpt.gpt_forward(m, p, ids, ids, qat=True)
+    torch.manual_seed(3)
+    b = gpt.gpt_forward(m, p, ids, ids, qat=True)
+    assert torch.equal(a, b) and float((a - clean).abs()) > 0
+    # only the block that runs twice is perturbed: with its weights zeroed out of the picture the loss is the clean one
+    calls = []
+    real = R.quant_noise
+    try:
+        R.quant_noise = lambda w_, q_: calls.append(tuple(w_.shape)) or real(w_, q_)
+        gpt.gpt_forward(m, p, ids, ids, qat=True)
+    finally:
+        R.quant_noise = real
+    assert len(calls) == 2 * 6                                                  # six matrices, two passes of block 1, nothing else

@@ -110,6 +110,12 @@ def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float3
     for name, shape in param_shapes(m).items():
         p[name] = torch.zeros(shape, dtype=torch.float32)
     p["tok_emb"].normal_(0.0, m.tied_embed_init_std if m.tie_embeddings else 1.0, generator=g)
+    if m.embed_init == "overtone" and m.tie_embeddings:
+        # records/track_10min_16mb/2026-03-19_SlidingWindow_FP16Emb_10L_MuonWD_OvertoneInit/train_gpt.py:723-728: keep the singular
+        # vectors of the random table and give it the spectrum s_1 k^(-1/2)
+        U, S, Vh = torch.linalg.svd(p["tok_emb"], full_matrices=False)
+        target = S[0] * torch.arange(1, S.shape[0] + 1, dtype=S.dtype).rsqrt()
+        p["tok_emb"] = ((U * target[None, :]) @ Vh).contiguous()
     for i in range(n):
         p["qo_bank"][i] = _orthogonal(d, d, g)
         p["kv_bank"][i] = _orthogonal(m.kv_dim, d, g)
@@ -118,6 +124,12 @@ def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float3
     p["attn_scale"].fill_(1.0)
     p["mlp_scale"].fill_(1.0)
     p["resid_mix"][:, 0].fill_(1.0)
+    if m.resid_mix_init == "phase":
+        # …OvertoneInit/train_gpt.py:731-737: early blocks lean on the embedding stream x0, late ones on the residual stream
+        for i in range(n):
+            phase = float(torch.sigmoid(torch.tensor(3.0 * (i / max(n - 1, 1) - 0.5))))
+            p["resid_mix"][i, 0].fill_(phase)
+            p["resid_mix"][i, 1].fill_(1.0 - phase)
     p["q_gain"].fill_(m.qk_gain_init)
     if "skip_weights" in p:
         p["skip_weights"].fill_(1.0)

@@ -84,9 +84,26 @@ def quantize_groups(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed:
         elif spec.quant.scheme == "binary_b1" and g != "tok_emb":
             from .binary import quantize_binary
             out[g] = quantize_binary(w, spec.quant.ternary_group)           # codes in {-1, 1}, scales [rows, groups]
+        elif g == "tok_emb" and bits[g] == 16:
+            out[g] = (w.half(), torch.ones(w.shape[0]))                     # kept as fp16: no codes, the scale is a placeholder
         else:
             out[g] = quantize_rows(w, bits[g])
+            if spec.quant.coarse_layers and spec.quant.coarse_step > 1 and g != "tok_emb":
+                out[g] = (_coarsen_rows(out[g][0], spec, bits[g]), out[g][1])
     return out, bits
+
+
+def _coarsen_rows(q: torch.Tensor, spec: RunSpec, bits: int) -> torch.Tensor:
+    """Codes of the blocks in ``quant.coarse_layers`` rounded to multiples of ``quant.coarse_step`` (a group's rows are the
+    blocks' matrices stacked in order), kept inside the code range; see `int8_baseline.coarsen_bank_codes`."""
+    n, step = spec.model.num_layers, spec.quant.coarse_step
+    per = q.shape[0] // n
+    lo, hi = -(1 << (bits - 1)), (1 << (bits - 1)) - 1
+    q = q.clone()
+    for l in set(int(x) for x in spec.quant.coarse_layers):
+        blk = q[l * per:(l + 1) * per]
+        q[l * per:(l + 1) * per] = (torch.round(blk.float() / step) * step).clamp(lo, hi).to(q.dtype)
+    return q
 
 
 def _store_codes(q: torch.Tensor, bits: int, storage: str) -> bytes:
@@ -119,6 +136,8 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
             from .binary import pack_signs
             data = q.cpu().numpy().astype(np.int8).tobytes() if spec.quant.code_storage == "bytes" else pack_signs(q.cpu().numpy())
             recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", data))        # eight codes per byte
+        elif g == "tok_emb" and bits[g] == 16:
+            recs.append(_f16(f"{g}.weight", q))
         else:
             recs.append(C.TensorRecord(f"{g}.weight", tuple(q.shape), "i8", _store_codes(q, bits[g], spec.quant.code_storage)))
         recs.append(_f16(f"{g}.scale", s16))
@@ -173,7 +192,9 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
 def export_model(spec: RunSpec, params: Dict[str, torch.Tensor], path: Optional[str] = None, precomputed=None) -> bytes:
     if spec.quant.scheme == "int8_zlib":         # the baseline trainer's own artifact, outside the PGRS family
         from .int8_baseline import export_int8_zlib
-        blob, _ = export_int8_zlib({k: v.detach().float().cpu() for k, v in params.items()})
+        q = spec.quant
+        blob, _ = export_int8_zlib({k: v.detach().float().cpu() for k, v in params.items()}, keep_fp16=("tok_emb",) if q.embed_bits == 16 else (),
+                                   coarse_layers=q.coarse_layers, coarse_step=q.coarse_step, num_layers=spec.model.num_layers)
     else:
         qs, bits = quantize_groups(spec, params, precomputed)
         blob = C.compress_payload(build_artifact(spec, params, quantized=(qs, bits)), spec.quant.compression)
@@ -261,6 +282,8 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
         bits = 6 if legacy else int(md["groups"][g])
         wrec, srec = by[f"{g}.weight"], by[f"{g}.scale"]
         rows, cols = wrec.dims
+        if wrec.dtype == "f16":                  # an embedding table kept as fp16 (quant.embed_bits = 16)
+            return torch.from_numpy(_np(wrec).astype(np.float32))
         if md.get("scheme") == "ternary_b158" and g != "tok_emb":
             from .ternary import dequantize_ternary, unpack_trits
             if len(wrec.data) == rows * cols:

@@ -135,7 +135,7 @@ def gptq_quantize_model(spec: RunSpec, params: Dict[str, torch.Tensor], hessians
         if device is not None:
             W = W.to(device)
         if g == "tok_emb":
-            qq, ss = quantize_rows(W, bits[g])
+            qq, ss = (W.half(), torch.ones(W.shape[0])) if bits[g] == 16 else quantize_rows(W, bits[g])     # 16: the table stays fp16
             out[g] = (qq.cpu(), ss.cpu())
             continue
         per = W.shape[0] // m.num_layers

@@ -61,9 +61,23 @@ def quantize_float_tensor(t: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return q, scale
 
 
-def quantize_state_dict_int8(state: Dict[str, torch.Tensor]):
+def coarsen_bank_codes(name: str, q: torch.Tensor, layers, step: int, num_layers: int) -> torch.Tensor:
+    """Round the int8 codes of the listed blocks to multiples of ``step`` (4 leaves 64 levels, 16 leaves 16): the entropy coder
+    then spends fewer bits on those blocks (records/track_10min_16mb/2026-03-19_10L_MixedPrecision/train_gpt.py:1089-1101, which
+    picks the middle blocks). Works on the stacked banks: slot ``s`` of ``qo_bank`` / ``kv_bank`` belongs to block ``s mod n``."""
+    if step <= 1 or not layers or name not in ("qo_bank", "kv_bank", "mlp_up_bank", "mlp_down_bank"):
+        return q
+    q = q.clone()
+    for slot in range(q.shape[0]):
+        if slot % num_layers in layers:
+            q[slot] = (torch.round(q[slot].float() / step) * step).clamp(-127, 127).to(torch.int8)
+    return q
+
+
+def quantize_state_dict_int8(state: Dict[str, torch.Tensor], keep_fp16=(), coarse_layers=(), coarse_step: int = 1, num_layers: int = 0):
     """Returns ``(obj, stats)``; ``obj`` has the reference's keys (`quantized`, `scales`, `dtypes`, `passthrough`,
-    `passthrough_orig_dtypes`, `qmeta`, `__quant_format__`)."""
+    `passthrough_orig_dtypes`, `qmeta`, `__quant_format__`). ``keep_fp16``: names stored as fp16 whatever their size (the tied
+    embedding of records/track_10min_16mb/2026-03-18_FP16Embed_WD3600, whose int8 error enters at both ends of the model)."""
     obj = {"__quant_format__": FORMAT, "quantized": {}, "scales": {}, "dtypes": {}, "passthrough": {}, "passthrough_orig_dtypes": {},
            "qmeta": {}}
     stats = {"param_count": 0, "num_tensors": 0, "baseline_tensor_bytes": 0, "int8_payload_bytes": 0}
@@ -76,7 +90,7 @@ def quantize_state_dict_int8(state: Dict[str, torch.Tensor]):
             obj["passthrough"][name] = t
             stats["int8_payload_bytes"] += t.numel() * t.element_size()
             continue
-        if t.numel() <= KEEP_FLOAT_MAX_NUMEL:
+        if t.numel() <= KEEP_FLOAT_MAX_NUMEL or name in keep_fp16:
             if any(p in name for p in CONTROL_PATTERNS):
                 kept = t.float().contiguous()
             elif t.dtype in (torch.float32, torch.bfloat16):
@@ -88,6 +102,7 @@ def quantize_state_dict_int8(state: Dict[str, torch.Tensor]):
             stats["int8_payload_bytes"] += kept.numel() * kept.element_size()
             continue
         q, s = quantize_float_tensor(t)
+        q = coarsen_bank_codes(name, q, set(int(l) for l in coarse_layers), coarse_step, num_layers)
         if s.ndim > 0:
             obj["qmeta"][name] = {"scheme": "per_row", "axis": 0}
         obj["quantized"][name], obj["scales"][name] = q, s
@@ -161,9 +176,9 @@ def deserialize(raw: bytes):
     return obj
 
 
-def export_int8_zlib(state: Dict[str, torch.Tensor], path: str = None):
+def export_int8_zlib(state: Dict[str, torch.Tensor], path: str = None, keep_fp16=(), coarse_layers=(), coarse_step: int = 1, num_layers: int = 0):
     """Quantise, serialise and compress; returns ``(blob, stats)`` with the byte counts the baseline logs."""
-    obj, stats = quantize_state_dict_int8(state)
+    obj, stats = quantize_state_dict_int8(state, keep_fp16, coarse_layers, coarse_step, num_layers)
     raw = serialize(obj)
     blob = zlib.compress(raw, level=9)
     stats.update(raw_bytes=len(raw), compressed_bytes=len(blob),

@@ -125,6 +125,8 @@ class ModelSpec:
     ln_scale: bool = False
     tie_embeddings: bool = True
     tied_embed_init_std: float = 0.005
+    embed_init: str = "normal"            # normal | overtone: the tied table's singular values reshaped to s_1 / sqrt(k)
+    resid_mix_init: str = "identity"      # identity (x, no x0) | phase: sigmoid(3 (l / (n-1) - 1/2)) on x and the rest on x0, per layer
     compute_precision: str = "bf16_tensor_core"  # f32 (CPU oracle) | bf16_tensor_core
     # Optional ideas of the Python records that their own runs leave off (train_gpt.py:70-92 of the 2026-03-23 record). They run on
     # the autograd path (train.backend = cpu); the CUDA engine rejects them at validation.
@@ -275,7 +277,9 @@ class QuantSpec:
     float_storage: str = "f16"          # f16 | fp8: how the 2-D float tensors that are not quantised to integer codes are stored
                                         # (fp8 = e4m3, one byte per element; 1-D control tensors stay f16)
     matrix_bits: int = 6
-    embed_bits: int = 8
+    embed_bits: int = 8                 # 16 = keep the (tied) embedding table as fp16 instead of integer codes
+    coarse_layers: list = field(default_factory=list)   # blocks whose integer codes are rounded to multiples of coarse_step
+    coarse_step: int = 1                # (INT4_LAYERS / INT4_STEP of the 10-layer mixed-precision record: 4 turns int8 codes into 64 levels)
     attn_gate_bits: int = 8
     mlp_clip_sigmas: float = 0.0
     attn_clip_sigmas: float = 0.0
@@ -523,6 +527,8 @@ class RunSpec:
         if has("TTT_GRAD_CLIP"): e.ttt_grad_clip = F("TTT_GRAD_CLIP")
         if has("GPTQ_CALIB_BATCHES"): q.gptq_calibration_batches = I("GPTQ_CALIB_BATCHES")
         if has("GPTQ_BLOCK_SIZE"): q.gptq_block_size = I("GPTQ_BLOCK_SIZE")
+        if has("INT4_LAYERS"): q.coarse_layers = [int(x) for x in env["INT4_LAYERS"].split(",") if x.strip()]
+        if has("INT4_STEP"): q.coarse_step = I("INT4_STEP")
         if has("TARGET_MB"): q.target_artifact_bytes = int(F("TARGET_MB") * 1024 * 1024)
         return self
 
@@ -575,6 +581,9 @@ class RunSpec:
             "model.softcap_kind=poly5 and model.z_loss_weight run on train.backend=cpu only (the fused cross-entropy kernel caps with tanh)")
         chk(m.embed_dim == 0 or (m.tie_embeddings and 0 < m.embed_dim <= m.model_dim), "model.embed_dim needs tied embeddings and 0 < embed_dim <= model_dim")
         chk(q.float_storage in ("f16", "fp8"), "quant.float_storage must be f16 or fp8")
+        chk(m.embed_init in ("normal", "overtone") and m.resid_mix_init in ("identity", "phase"), "unknown model.embed_init or model.resid_mix_init")
+        chk(q.coarse_step >= 1 and all(0 <= int(l) < m.num_layers for l in q.coarse_layers), "quant.coarse_step must be >= 1 and coarse_layers inside the model")
+        chk(not q.coarse_layers or q.scheme not in ("ternary_b158", "binary_b1"), "quant.coarse_layers does not apply to the ternary and binary schemes")
         chk(e.temperature > 0 and all(x > 0 for x in e.temperature_grid), "eval.temperature and its grid must be positive")
         chk(m.qat_kind in ("int6", "ternary", "binary", "noise"), "model.qat_kind must be int6, ternary, binary or noise")
         chk(m.qat_kind == "int6" or t.backend == "cpu", "model.qat_kind=ternary|binary|noise runs on train.backend=cpu only")
@@ -598,7 +607,7 @@ class RunSpec:
         if t.backend in ("cuda_single", "cuda_single_parity"):
             chk(t.world_size == 1, f"backend {t.backend} requires world_size == 1")
         # the cpu backend with world_size > 1 is data parallel over a gloo process group (host-side logic and its tests)
-        chk(4 <= q.matrix_bits <= 8 and 4 <= q.embed_bits <= 8, "quant bits must be in [4, 8]")
+        chk(4 <= q.matrix_bits <= 8 and (4 <= q.embed_bits <= 8 or q.embed_bits == 16), "quant bits must be in [4, 8] (embed_bits may also be 16 = fp16)")
         chk(e.stride >= 1, "eval.stride must be >= 1")
         chk(t.grad_wire_dtype in ("bf16", "f32"), "grad_wire_dtype must be bf16 or f32")
         if self.mode == "record" and not self.allow_unsupported_variants:

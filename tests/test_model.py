@@ -411,3 +411,20 @@ def test_noisy_qat_perturbs_shared_blocks_by_one_quantisation_step_with_gradient
     finally:
         R.quant_noise = real
     assert len(calls) == 2 * 6                                                  # six matrices, two passes of block 1, nothing else
+
+
+def test_overtone_embedding_spectrum_and_phase_residual_mix_initialisation():
+    """…OvertoneInit/train_gpt.py:723-737: the tied table keeps its random singular vectors and gets singular values
+    s_1 / sqrt(k); resid_mix starts at sigmoid(3 (l / (n - 1) - 1/2)) on the residual stream and the rest on the embedding stream."""
+    s = _variant("model.num_layers=5", "model.embed_init=overtone", "model.resid_mix_init=phase")
+    m = s.model
+    p = gpt.init_params(m, seed=11)
+    S = torch.linalg.svdvals(p["tok_emb"])
+    k = torch.arange(1, S.numel() + 1, dtype=S.dtype)
+    assert torch.allclose(S, S[0] * k.rsqrt(), rtol=1e-4)
+    ref = gpt.init_params(_variant("model.num_layers=5").model, seed=11)
+    assert torch.allclose(torch.linalg.svdvals(ref["tok_emb"])[0], S[0], rtol=1e-5)         # the largest one is the random table's
+    want = torch.sigmoid(3.0 * (torch.arange(5) / 4 - 0.5))
+    assert torch.allclose(p["resid_mix"][:, 0, 0], want) and torch.allclose(p["resid_mix"][:, 1, 3], 1 - want)
+    assert torch.equal(ref["resid_mix"][:, 0], torch.ones(5, m.model_dim)) and float(ref["resid_mix"][:, 1].abs().max()) == 0.0
+    assert torch.equal(p["kv_bank"], ref["kv_bank"])                                          # nothing else moves

@@ -479,3 +479,47 @@ def test_binary_scheme_exports_what_binary_qat_trains(tmp_path):
     assert (b.model.num_layers, b.model.head_dim, b.quant.scheme, b.model.block_smear, b.train.max_wallclock_seconds) == (15, 96, "binary_b1", True, 0.0)
     shapes = gpt.param_shapes(b.model)
     assert shapes["skip_weights"] == (7, 768)                                     # 7 blocks before the turn, 8 after
+
+
+def test_fp16_embedding_and_coarse_middle_layers_in_both_exporters(tmp_path):
+    """quant.embed_bits = 16 keeps the tied table as fp16 (records/.../2026-03-18_FP16Embed_WD3600); quant.coarse_layers /
+    coarse_step round the codes of the listed blocks to multiples of the step (records/.../2026-03-19_10L_MixedPrecision,
+    INT4_LAYERS / INT4_STEP), which shrinks the compressed artifact and costs accuracy only in those blocks."""
+    from parameter_golf_b200.quant.int8_baseline import load_int8_zlib
+    s = family_preset("tiny_cpu")
+    s.apply_overrides(["model.num_layers=4", "quant.prune_to_target=false"])
+    m = s.model
+    p = gpt.init_params(m, seed=3)
+    for k in ("qo_bank", "mlp_down_bank"):                       # the zero-initialised halves would hide the effect
+        p[k] = torch.randn(p[k].shape, generator=torch.Generator().manual_seed(4)) * 0.05
+    plain = export_model(s, p)
+    s.apply_env({"INT4_LAYERS": "1,2", "INT4_STEP": "4"})
+    s.quant.embed_bits = 16
+    s.validate()
+    blob = export_model(s, p)
+    back = load_artifact(blob, s)
+    assert torch.equal(back["tok_emb"], p["tok_emb"].half().float())
+    base = load_artifact(plain, s)
+    n = m.num_layers
+    for l in range(n):
+        changed = not torch.equal(back["mlp_up_bank"][l], base["mlp_up_bank"][l])
+        assert changed == (l in (1, 2)), l
+        assert (not torch.equal(back["kv_bank"][n + l], base["kv_bank"][n + l])) == (l in (1, 2))
+    err = lambda a, l: float((a["mlp_up_bank"][l] - p["mlp_up_bank"][l]).pow(2).mean())
+    assert err(back, 1) > err(base, 1) and err(back, 0) == err(base, 0)
+    # the baseline trainer's int8 + zlib artifact takes the same two options
+    s.quant.scheme = "int8_zlib"
+    z = export_model(s, p)
+    zs = load_int8_zlib(z)
+    assert zs["tok_emb"].dtype == torch.float32 and torch.equal(zs["tok_emb"], p["tok_emb"].half().float())
+    s.quant.embed_bits = 8
+    zc = export_model(s, p)
+    s.quant.coarse_layers = []
+    z0 = export_model(s, p)
+    assert len(zc) < 0.97 * len(z0) and len(z) > len(zc)        # coarser codes in two of four blocks compress better; the fp16 table costs bytes
+    z0s = load_int8_zlib(z0)
+    for l in range(n):
+        assert (not torch.equal(zs["qo_bank"][l], z0s["qo_bank"][l])) == (l in (1, 2))
+        assert (not torch.equal(zs["qo_bank"][n + l], z0s["qo_bank"][n + l])) == (l in (1, 2))
+    with pytest.raises(ValueError):
+        family_preset("tiny_cpu").apply_overrides(["quant.coarse_layers=[7]"]).validate()

@@ -138,6 +138,19 @@ def main(argv=None) -> int:
             hook = PeerAllReduce(2 * m.num_layers * m.model_dim * spec.eval.lora_rank + 64).mean_
         loss, bpb = eval_lora_phased_ttt(runner, val, m, spec.eval, luts, rank, world, a.device, print, all_reduce=hook)
         kind = "lora_phased"
+    elif spec.eval.legal_score_first and ab == "doc_lora":
+        from .eval.doc_lora import eval_doc_lora_ttt
+        hook = None
+        if world > 1:
+            import torch.distributed as dist
+
+            def hook(t):           # three float64 sums: the process group's own all-reduce (gloo on cpu)
+                dev_t = t.to(a.device) if a.device != "cpu" else t
+                dist.all_reduce(dev_t)
+                t.copy_(dev_t.cpu())
+        loss, bpb = eval_doc_lora_ttt(runner.params, m, val, spec.eval, luts, rank, world, a.device, print, all_reduce=hook,
+                                      betas=(spec.train.adam_beta1, spec.train.adam_beta2))
+        kind = "doc_lora"
     else:
         loss, bpb = eval_sliding(runner.nll, val, m.eval_seq_len, spec.eval.stride, luts, rank, world, spec.eval.batch_windows, a.device)
         kind = "sliding"

@@ -196,15 +196,18 @@ def embed_tokens(m: ModelSpec, p, ids, dt, qat: bool = False):
     return x
 
 
-def output_logits(m: ModelSpec, p, h, qat: bool = False):
+def output_logits(m: ModelSpec, p, h, qat: bool = False, lora=None):
     """Un-capped logits of final hidden states: the tied table (after the output projection when the embedding is factored) or
-    the untied head."""
+    the untied head; plus the per-batch-element head adapter of per-document test-time training when ``lora`` carries one."""
     bias = p["vocab_bias"].to(h.dtype) if m.vocab_bias else None      # train_gpt_cuda_ternary.py:851
+    extra = 0
+    if lora is not None and "head_a" in lora:
+        extra = torch.bmm(torch.bmm(h, lora["head_a"].to(h.dtype).mT), lora["head_b"].to(h.dtype).mT)
     if not m.tie_embeddings:
-        return F.linear(h, _small(m, p, "lm_head", qat).to(h.dtype), bias)
+        return F.linear(h, _small(m, p, "lm_head", qat).to(h.dtype), bias) + extra
     if m.embed_dim > 0:
         h = F.linear(h, _small(m, p, "embed_proj_out", qat).to(h.dtype))
-    return F.linear(h, p["tok_emb"].to(h.dtype), bias)
+    return F.linear(h, p["tok_emb"].to(h.dtype), bias) + extra
 
 
 def mlp_hidden(m: ModelSpec, u):
@@ -275,11 +278,16 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
     if taps is not None:
         taps.add(i, "qkv", h)
     q = F.linear(h, wq.to(dt))
-    if lora is not None:
-        a, b, alpha = lora["a"][i], lora["b"][i], lora["alpha"]
-        q = q + (alpha / a.shape[0]) * F.linear(F.linear(h, a.to(dt)), b.to(dt))
     k = F.linear(h, wk.to(dt))
     v = F.linear(h, wv.to(dt))
+    if lora is not None and "q_a" in lora:
+        # one adapter per batch element on the query and value projections (per-document test-time training,
+        # records/track_10min_16mb/2026-03-17_LoRA_TTT/train_gpt.py:755-766): A [B, r, d], B [B, out, r]
+        q = q + torch.bmm(torch.bmm(h, lora["q_a"][i].to(dt).mT), lora["q_b"][i].to(dt).mT)
+        v = v + torch.bmm(torch.bmm(h, lora["v_a"][i].to(dt).mT), lora["v_b"][i].to(dt).mT)
+    elif lora is not None:
+        a, b, alpha = lora["a"][i], lora["b"][i], lora["alpha"]
+        q = q + (alpha / a.shape[0]) * F.linear(F.linear(h, a.to(dt)), b.to(dt))
     if depth_index is not None and "depth_lora_q_up" in p:
         # per-virtual-layer corrections of a shared block's query and value projections (…DepthRecurrence…/train_gpt.py:771-793, :755-760)
         q = q + F.linear(F.linear(h, p["depth_lora_q_down"][depth_index].to(dt)), p["depth_lora_q_up"][depth_index].to(dt))
@@ -372,7 +380,7 @@ def gpt_hidden(m: ModelSpec, p, ids: torch.Tensor, qat: bool = False, lora=None,
 def gpt_logits(m: ModelSpec, p, ids, qat: bool = False, lora=None, dtype=None):
     """Soft-capped logits [B,T,V]."""
     h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
-    z = output_logits(m, p, h, qat)
+    z = output_logits(m, p, h, qat, lora)
     return R.softcap(z, m.logit_softcap, m.softcap_kind)
 
 
@@ -400,7 +408,7 @@ def gpt_forward(m: ModelSpec, p, ids, targets, qat: bool = False, lora=None, dty
     only) adds ``mtp_loss_weight`` times the multi-token-prediction loss of the extra heads; ``train`` adds the z-loss term
     (``model.z_loss_weight`` times the mean squared log-partition), which evaluation never includes."""
     h = gpt_hidden(m, p, ids, qat=qat, lora=lora, dtype=dtype)
-    z = output_logits(m, p, h, qat)
+    z = output_logits(m, p, h, qat, lora)
     extra = None
     if mtp and reduction == "mean" and m.mtp_num_heads > 0 and m.mtp_loss_weight > 0.0 and "mtp_heads" in p:
         extra = mtp_loss(m, p, h, targets)

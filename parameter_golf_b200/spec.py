@@ -30,7 +30,7 @@ QUANT_SCHEMES = ("none", "gptq_lite_int6", "mixed_int5_int6", "aggressive", "tig
                  "int8_zlib", "ternary_b158", "binary_b1")       # int8_zlib: the baseline trainer's per-row int8 + zlib-9 export (train_gpt.py:342-422)
 COMPRESSION_MODES = ("none", "zstd22", "lzma9", "pergroup")
 CALIBRATION_MODES = ("disabled", "self_generated")
-ADAPTATION_BACKENDS = ("none", "cpu_q_only", "gpu_lora_phased", "full_sgd", "lact", "slot")
+ADAPTATION_BACKENDS = ("none", "cpu_q_only", "gpu_lora_phased", "full_sgd", "lact", "slot", "doc_lora")
 NS_PROFILES = ("simple", "quintic", "polar_express")
 FAMILIES = (
     "baseline_sp8192", "xsa_all_sp8192", "recurrence_mid_sp8192", "parallel_resid_sp8192",
@@ -318,6 +318,13 @@ class EvalSpec:
     temperature_grid: list = field(default_factory=lambda: [0.90, 0.95, 1.00, 1.05, 1.10])
     temperature_calibration_tokens: int = 65536       # training tokens the grid is scored on
     byte_table_seed: int = 20240520
+    # adaptation_backend = doc_lora: documents (cut at doc_boundary_token_id) scored in isolation, chunk by chunk, with adapters
+    # per document trained by one Adam step after each scored chunk (TTT_LORA_RANK / TTT_LORA_LR / TTT_CHUNK_SIZE / TTT_BATCH_SIZE)
+    doc_lora_rank: int = 8             # 0 = no adapters: plain document-isolated, strided scoring
+    doc_lora_lr: float = 0.01
+    doc_chunk_size: int = 256
+    doc_batch_size: int = 64
+    doc_boundary_token_id: int = 1
 
 
 @dataclass
@@ -525,6 +532,11 @@ class RunSpec:
         if has("TTT_MOMENTUM"): e.ttt_momentum = F("TTT_MOMENTUM")
         if has("TTT_BATCH_SEQS"): e.ttt_batch_seqs = I("TTT_BATCH_SEQS")
         if has("TTT_GRAD_CLIP"): e.ttt_grad_clip = F("TTT_GRAD_CLIP")
+        if has("TTT_LORA_RANK"): e.doc_lora_rank = I("TTT_LORA_RANK")
+        if has("TTT_LORA_LR"): e.doc_lora_lr = F("TTT_LORA_LR")
+        if has("TTT_CHUNK_SIZE"): e.doc_chunk_size = I("TTT_CHUNK_SIZE")
+        if has("TTT_BATCH_SIZE"): e.doc_batch_size = I("TTT_BATCH_SIZE")
+        if has("TTT_EVAL_SEQ_LEN"): m.eval_seq_len = I("TTT_EVAL_SEQ_LEN")
         if has("GPTQ_CALIB_BATCHES"): q.gptq_calibration_batches = I("GPTQ_CALIB_BATCHES")
         if has("GPTQ_BLOCK_SIZE"): q.gptq_block_size = I("GPTQ_BLOCK_SIZE")
         if has("INT4_LAYERS"): q.coarse_layers = [int(x) for x in env["INT4_LAYERS"].split(",") if x.strip()]
@@ -584,6 +596,7 @@ class RunSpec:
         chk(m.embed_init in ("normal", "overtone") and m.resid_mix_init in ("identity", "phase"), "unknown model.embed_init or model.resid_mix_init")
         chk(q.coarse_step >= 1 and all(0 <= int(l) < m.num_layers for l in q.coarse_layers), "quant.coarse_step must be >= 1 and coarse_layers inside the model")
         chk(not q.coarse_layers or q.scheme not in ("ternary_b158", "binary_b1"), "quant.coarse_layers does not apply to the ternary and binary schemes")
+        chk(e.doc_lora_rank >= 0 and e.doc_chunk_size >= 1 and e.doc_batch_size >= 1 and e.doc_lora_lr > 0, "eval.doc_* out of range")
         chk(e.temperature > 0 and all(x > 0 for x in e.temperature_grid), "eval.temperature and its grid must be positive")
         chk(m.qat_kind in ("int6", "ternary", "binary", "noise"), "model.qat_kind must be int6, ternary, binary or noise")
         chk(m.qat_kind == "int6" or t.backend == "cpu", "model.qat_kind=ternary|binary|noise runs on train.backend=cpu only")

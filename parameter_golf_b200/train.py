@@ -510,6 +510,19 @@ class VariantRunner:
             elif spec.eval.legal_score_first and ab == "gpu_lora_phased":
                 res.val_loss, res.val_bpb = eval_lora_phased_ttt(runner, val, m, spec.eval, luts, t.rank, t.world_size, edev, log.info)
                 res.eval_kind = "lora_phased"
+            elif spec.eval.legal_score_first and ab == "doc_lora":
+                from .eval.doc_lora import eval_doc_lora_ttt
+                hook = None
+                if t.world_size > 1:
+                    import torch.distributed as dist
+
+                    def hook(x):
+                        dev_x = x.to(edev) if edev != "cpu" else x
+                        dist.all_reduce(dev_x)
+                        x.copy_(dev_x.cpu())
+                res.val_loss, res.val_bpb = eval_doc_lora_ttt(runner.params, m, val, spec.eval, luts, t.rank, t.world_size, edev, log.info,
+                                                              all_reduce=hook, betas=(t.adam_beta1, t.adam_beta2))
+                res.eval_kind = "doc_lora"
             else:
                 res.val_loss, res.val_bpb = eval_sliding(runner.nll, val, m.eval_seq_len, spec.eval.stride, luts, t.rank, t.world_size,
                                                          spec.eval.batch_windows, edev)

@@ -197,3 +197,94 @@ def test_temperature_scaling_and_its_grid_search():
             return rr.nll(x[: a.shape[0]], y[: a.shape[0]])
     best, table = find_temperature(Fixed(), toks, 64, [0.5, 0.7, 1.0, 1.4], batch_seqs=64)
     assert best == 0.7 and table[0.7] < table[1.0] < table[1.4]
+
+
+def _doc_stream(vocab, n_docs, rng, lo=20, hi=90):
+    """Documents that each repeat a short private pattern (so an adapter trained on the start of a document helps on its end),
+    every one opened by the boundary token 1."""
+    out = []
+    for _ in range(n_docs):
+        pat = rng.integers(2, vocab, size=5)
+        ln = int(rng.integers(lo, hi))
+        out.append(np.concatenate([[1], np.tile(pat, ln // 5 + 1)[:ln]]))
+    return np.concatenate(out).astype(np.uint16)
+
+
+def test_documents_and_chunk_windows():
+    from parameter_golf_b200.eval import doc_lora as D
+    toks = np.array([9, 9, 1, 5, 6, 7, 1, 8, 1, 1, 4, 4, 4], dtype=np.uint16)
+    # a document takes the next boundary token as its last target; the last one runs to the end of the stream
+    assert D.find_documents(toks, 1) == [(2, 5), (6, 3), (8, 2), (9, 4)]
+    assert D.find_documents(toks, 1, include_next_boundary=False) == [(2, 4), (6, 2), (9, 4)]
+    assert sum(ln - 1 for _, ln in D.find_documents(toks, 1)) == len(toks) - 1 - 2            # every target after the first boundary, once
+    # chunk 2 of 3 with chunks of 4 in a window of 6: ends at 10 predictions, reaches back 6, the chunk sits at offset 4
+    assert D.chunk_window(2, 10, 3, 4, 6) == (4, 6, 4, 2)
+    assert D.chunk_window(0, 10, 3, 4, 6) == (0, 4, 0, 4) and D.chunk_window(1, 10, 3, 4, 6) == (2, 6, 2, 4)
+
+
+def test_doc_isolated_scoring_without_adapters_equals_per_document_forward():
+    """rank 0 adapters: every document scored alone, each token with all of its document's earlier tokens (up to the window)."""
+    from parameter_golf_b200.eval.doc_lora import eval_doc_lora_ttt, find_documents
+    s = spec()
+    m = s.model
+    m.eval_seq_len = 64
+    p = gpt.fill_deterministic(m)
+    rng = np.random.default_rng(0)
+    toks = _doc_stream(m.vocab_size, 7, rng, 20, 60)
+    luts = BpbLuts.seeded(m.vocab_size)
+    s.eval.doc_lora_rank, s.eval.doc_chunk_size, s.eval.doc_batch_size = 0, 16, 3
+    loss, bpb = eval_doc_lora_ttt(p, m, toks, s.eval, luts)
+    tot, nb, cnt = 0.0, 0.0, 0
+    for d0, ln in find_documents(toks, 1):
+        ids = torch.from_numpy(toks[d0: d0 + ln].astype(np.int64))[None]
+        nll = gpt.gpt_forward(m, p, ids[:, :-1], ids[:, 1:], reduction="none")[0]
+        tot += float(nll.double().sum())
+        nb += float(luts.token_bytes(ids[0, :-1].numpy(), ids[0, 1:].numpy()).sum())
+        cnt += ln - 1
+    assert abs(loss - tot / cnt) < 1e-5 and abs(bpb - tot / math.log(2) / nb) < 1e-5
+    # ranks take contiguous slices of the documents and their sums add up to the same result
+    parts = []
+    for r in range(2):
+        got = {}
+        eval_doc_lora_ttt(p, m, toks, s.eval, luts, rank=r, world=2, all_reduce=lambda t, got=got: got.setdefault("s", t.clone()))
+        parts.append(got["s"])
+    both = parts[0] + parts[1]
+    assert abs(float(both[0] / both[2]) - loss) < 1e-6 and int(both[2]) == cnt
+
+
+def test_doc_lora_ttt_scores_before_it_trains_and_never_crosses_documents():
+    from parameter_golf_b200.eval import doc_lora as D
+    s = spec()
+    m = s.model
+    m.eval_seq_len = 64
+    p = gpt.init_params(m, seed=5)
+    rng = np.random.default_rng(1)
+    toks = _doc_stream(m.vocab_size, 6, rng, 60, 100)
+    luts = BpbLuts.seeded(m.vocab_size)
+    s.eval.doc_chunk_size, s.eval.doc_batch_size, s.eval.doc_lora_lr = 16, 4, 0.02
+    s.eval.doc_lora_rank = 0
+    base_loss, _ = D.eval_doc_lora_ttt(p, m, toks, s.eval, luts)
+    s.eval.doc_lora_rank = 4
+    before = {k: v.clone() for k, v in p.items()}
+    loss, bpb = D.eval_doc_lora_ttt(p, m, toks, s.eval, luts)
+    assert all(torch.equal(before[k], p[k]) for k in p)                      # the model itself never changes
+    assert loss < base_loss - 0.02 and bpb > 0                               # repeated patterns: adapting inside a document helps
+    # the first chunk of every document is scored by fresh adapters (B = 0): same numbers as without adapters
+    docs = D.find_documents(toks, 1)
+    short = np.concatenate([toks[d0: d0 + 16] for d0, _ in docs] + [[1]]).astype(np.uint16)      # 16 predictions = one chunk per document
+    s.eval.doc_lora_rank = 0
+    a, _ = D.eval_doc_lora_ttt(p, m, short, s.eval, luts)
+    s.eval.doc_lora_rank = 4
+    b, _ = D.eval_doc_lora_ttt(p, m, short, s.eval, luts)
+    assert abs(a - b) < 1e-7
+    # a document's score does not depend on which documents share its batch or come before it
+    s.eval.doc_batch_size = 1
+    one, _ = D.eval_doc_lora_ttt(p, m, toks, s.eval, luts, seed=0)
+    s.eval.doc_batch_size = 4
+    rev = np.concatenate([toks[d0: d0 + ln - (1 if i + 1 < len(docs) else 0)] for i, (d0, ln) in reversed(list(enumerate(docs)))]).astype(np.uint16)
+    # (adapter A matrices are drawn per batch, so equality across batchings is statistical, not bitwise: compare the gain instead)
+    two, _ = D.eval_doc_lora_ttt(p, m, rev, s.eval, luts, seed=3)
+    assert abs(one - loss) < 0.05 and abs(two - loss) < 0.05 and one < base_loss and two < base_loss
+    e = family_preset("tiny_cpu")
+    e.apply_env({"TTT_LORA_RANK": "8", "TTT_LORA_LR": "0.01", "TTT_CHUNK_SIZE": "256", "TTT_BATCH_SIZE": "64", "TTT_EVAL_SEQ_LEN": "1024"})
+    assert (e.eval.doc_lora_rank, e.eval.doc_chunk_size, e.eval.doc_batch_size, e.model.eval_seq_len) == (8, 256, 64, 1024)

@@ -152,3 +152,22 @@ def test_eval_cli_temperature_search(tmp_path):
     assert float(kv["temperature"]) in (0.9, 1.0, 1.1) and len(json.loads(kv["temperature_search"])) == 3 and float(kv["val_bpb"]) > 0
     out = subprocess.run(cmd[:-3] + ["--device", "cuda"], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
     assert out.returncode != 0
+
+
+def test_eval_cli_runs_document_isolated_lora_ttt(tmp_path):
+    """eval.adaptation_backend = doc_lora through the evaluation CLI on a stream of boundary-opened documents."""
+    from parameter_golf_b200.data.shards import write_shard
+    from parameter_golf_b200.quant.export import export_model
+    s = family_preset("tiny_cpu")
+    art = str(tmp_path / "a.pgrs")
+    export_model(s, gpt.init_params(s.model, 1), art)
+    rng = np.random.default_rng(0)
+    docs = [np.concatenate([[1], rng.integers(2, 1024, size=int(rng.integers(40, 120)))]) for _ in range(5)]
+    write_shard(str(tmp_path / "v_val_000000.bin"), np.concatenate(docs).astype(np.uint16))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "parameter_golf_b200.evalcli", "--artifact", art, "--family", "tiny_cpu", "--val-pattern", str(tmp_path / "v_val_*.bin"),
+           "eval.adaptation_backend=doc_lora", "eval.legal_score_first=true", "eval.doc_chunk_size=32", "eval.doc_lora_rank=4", "eval.doc_batch_size=4"]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr[-1500:]
+    kv = dict(l.split("=", 1) for l in out.stdout.splitlines() if "=" in l and not l.startswith("eval_audit_json"))
+    assert kv["eval_kind"] == "doc_lora" and float(kv["val_bpb"]) > 0 and np.isfinite(float(kv["val_loss"]))

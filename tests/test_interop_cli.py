@@ -64,7 +64,7 @@ def test_parity_report_tolerances():
 
 
 def test_shipped_specs_load_and_validate():
-    for name in ("record_profile", "baseline_9l", "tiny_cpu"):
+    for name in ("record_profile", "baseline_9l", "tiny_cpu", "ternary_10l", "binary_15l"):
         s = RunSpec.load(os.path.join(ROOT, "specs", f"{name}.toml")).validate()
         assert s.fingerprint() == family_preset(s.model.family).fingerprint()
 

@@ -192,6 +192,13 @@ class TrainSpec:
     batch_tokens: int = 524_288
     seq_len: int = 2048
     grad_accum_steps: int = 0           # 0 = automatic: 8 // world_size on CUDA backends, 1 on cpu
+    # Curriculum of the ternary record (train_gpt_cuda_ternary.py:1210-1289; cpu backend only, the CUDA engine's buffers have one
+    # shape): start with shorter sequences and / or a smaller global batch and switch to seq_len / batch_tokens once the given
+    # fraction of the wall-clock budget (of the step count without a cap) has passed. 0 = off.
+    seq_len_start: int = 0
+    seq_schedule_fraction: float = 0.33
+    batch_tokens_start: int = 0
+    batch_schedule_fraction: float = 0.33
     train_data_pattern: Optional[str] = None
     validation_data_pattern: Optional[str] = None
     rank: int = 0
@@ -221,6 +228,8 @@ class TrainSpec:
     adam_eps: float = 1e-8
     grad_clip_norm: float = 0.3
     ema_decay: float = 0.997
+    ema_start_fraction: float = 0.0     # cpu backend: the average starts (from the weights of that moment) once this fraction of the
+                                        # wall-clock budget, or of the steps without a cap, has passed (EMA_START_FRACTION of the ternary record)
     swa_enabled: bool = True
     swa_every: int = 50
     swa_threshold: float = 0.2
@@ -447,6 +456,10 @@ class RunSpec:
         if has("WARMDOWN_FRACTION"): t.warmdown_frac = F("WARMDOWN_FRACTION")
         if has("WARMDOWN_FRAC"): t.warmdown_frac = F("WARMDOWN_FRAC")
         if has("GRAD_ACCUM_STEPS"): t.grad_accum_steps = I("GRAD_ACCUM_STEPS")
+        if has("SEQ_LEN_START"): t.seq_len_start = I("SEQ_LEN_START")
+        if has("SEQ_SCHEDULE_FRACTION"): t.seq_schedule_fraction = F("SEQ_SCHEDULE_FRACTION")
+        if has("BATCH_TOKENS_START"): t.batch_tokens_start = I("BATCH_TOKENS_START")
+        if has("BATCH_SCHEDULE_FRACTION"): t.batch_schedule_fraction = F("BATCH_SCHEDULE_FRACTION")
         if has("WARMUP_STEPS"): t.warmup_steps = I("WARMUP_STEPS")
         if has("TRAIN_BATCH_TOKENS"): t.batch_tokens = I("TRAIN_BATCH_TOKENS")
         if has("TRAIN_SEQ_LEN"): t.seq_len = m.train_seq_len = I("TRAIN_SEQ_LEN")
@@ -487,6 +500,9 @@ class RunSpec:
         if has("GRAD_CLIP_NORM"): t.grad_clip_norm = F("GRAD_CLIP_NORM")
         if has("MUON_WD"): t.muon_wd = F("MUON_WD")
         if has("ADAM_WD"): t.adam_wd = F("ADAM_WD")
+        if has("EMA_DECAY"): t.ema_decay = F("EMA_DECAY")
+        if has("EMA") and not B("EMA"): t.ema_decay = 0.0
+        if has("EMA_START_FRACTION"): t.ema_start_fraction = F("EMA_START_FRACTION")
         if has("SWA_ENABLED"): t.swa_enabled = B("SWA_ENABLED")
         if has("SWA_EVERY"): t.swa_every = I("SWA_EVERY")
         if has("LAWA_ENABLED"): t.lawa_enabled = B("LAWA_ENABLED")
@@ -616,6 +632,13 @@ class RunSpec:
         if m.recurrence.enabled:
             chk(m.recurrence.start_layer + m.recurrence.repeat_layers <= m.num_layers, "recurrence range out of bounds")
         chk(t.seq_len > 0 and t.batch_tokens % t.seq_len == 0, "batch_tokens must be a multiple of seq_len")
+        chk((t.seq_len_start == 0 and t.batch_tokens_start == 0) or t.backend == "cpu",
+            "train.seq_len_start and train.batch_tokens_start run on train.backend=cpu only")
+        chk(0.0 <= t.ema_start_fraction < 1.0 and (t.ema_start_fraction == 0.0 or t.backend == "cpu"),
+            "train.ema_start_fraction must be in [0, 1) and runs on train.backend=cpu only (the CUDA optimizer kernels average from the first step)")
+        chk(t.seq_len_start == 0 or (0 < t.seq_len_start <= t.seq_len and t.seq_len % t.seq_len_start == 0), "train.seq_len_start must divide train.seq_len")
+        chk(t.seq_len_start >= 0 and t.batch_tokens_start >= 0 and 0.0 <= t.seq_schedule_fraction <= 1.0 and 0.0 <= t.batch_schedule_fraction <= 1.0,
+            "train.*_start must be >= 0 and the schedule fractions in [0, 1]")
         chk(t.world_size >= 1 and 0 <= t.rank < t.world_size, "rank must be in [0, world_size)")
         if t.backend in ("cuda_single", "cuda_single_parity"):
             chk(t.world_size == 1, f"backend {t.backend} requires world_size == 1")

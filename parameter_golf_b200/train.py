@@ -353,6 +353,12 @@ class VariantRunner:
         train_ms = 0.0
         step = step0
         t_start = self.clock()
+        # curriculum: shorter sequences / a smaller global batch until a fraction of the budget has passed
+        unit = t.world_size * accum
+        cur_seq = t.seq_len_start if 0 < t.seq_len_start < t.seq_len else t.seq_len
+        cur_tokens = tokens_per_step
+        if 0 < t.batch_tokens_start < tokens_per_step:
+            cur_tokens = max(t.batch_tokens_start // (unit * t.seq_len), 1) * unit * t.seq_len     # whole sequences of either length per micro-batch
         health = None
         if t.world_size > 1:
             from .parallel.health import RankHealth
@@ -381,13 +387,20 @@ class VariantRunner:
                 qat = True
                 log.info(f"late_qat:enabled step:{step} scale:{scale:.4f}")
             mom = muon_momentum_at(step, t.muon_momentum_warmup_start, t.muon_momentum, t.muon_momentum_warmup_steps)
+            progress = elapsed / max_ms if max_ms is not None else step / max(max_steps, 1)
+            if cur_seq != t.seq_len and progress >= t.seq_schedule_fraction:
+                log.info(f"step:{step} seq_len_switch:{cur_seq}->{t.seq_len}")
+                cur_seq = t.seq_len
+            if cur_tokens != tokens_per_step and progress >= t.batch_schedule_fraction:
+                log.info(f"step:{step} batch_switch:{cur_tokens}->{tokens_per_step}")
+                cur_tokens = tokens_per_step
             with timers.time("data"):
                 batches, spans = [], None
                 if hasattr(backend, "train_step_spans"):
                     spans = [loader.next_prefetched() for _ in range(accum)]     # page-locked uint16 spans (2 bytes per token over PCIe)
                 else:
                     for _ in range(accum):
-                        x, y = loader.next_batch(tokens_per_step, t.seq_len, accum)
+                        x, y = loader.next_batch(cur_tokens, cur_seq, accum)
                         batches.append((torch.from_numpy(x), torch.from_numpy(y)))
             with timers.time("train_step"), (health.guard() if health is not None else contextlib.nullcontext()):
                 loss = backend.train_step_spans(spans, scale, mom, qat) if spans is not None else backend.train_step(batches, scale, mom, qat)
@@ -397,7 +410,7 @@ class VariantRunner:
             if step == step0 + 1:
                 res.train_loss_first = loss
             res.train_loss_last = loss
-            if ema is not None:
+            if ema is not None and progress >= t.ema_start_fraction:
                 with timers.time("ema"):
                     ema.update(backend.sync_params())
             if swa is not None and swa.should_collect(step, scale):

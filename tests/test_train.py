@@ -521,3 +521,50 @@ def test_cycled_recurrent_model_trains_exports_and_reloads(tmp_path, monkeypatch
     for k in ("depth_lora_q_down", "depth_lora_q_up", "depth_lora_v_down", "depth_lora_v_up", "skip_weights"):
         assert back[k].shape == p[k].shape and torch.allclose(back[k], p[k].half().float(), atol=0), k
     assert float((back["qo_bank"] - p["qo_bank"]).abs().max()) <= float(p["qo_bank"].abs().amax()) / 127
+
+
+def test_sequence_and_batch_curriculum_switches_at_its_fractions(tmp_path, monkeypatch):
+    """SEQ_LEN_START / BATCH_TOKENS_START of the ternary record: short sequences and a small batch first, the full shapes once the
+    given fraction of the steps (no wall-clock cap here) has passed."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "record_shaped_proxy"
+    s.apply_env({"SEQ_LEN_START": "64", "SEQ_SCHEDULE_FRACTION": "0.5", "BATCH_TOKENS_START": "512", "BATCH_SCHEDULE_FRACTION": "0.25"})
+    s.train.batch_tokens, s.train.total_iterations = 1024, 8
+    s.train.artifact_path = str(tmp_path / "c.pgrs")
+    s.eval.max_tokens = 512
+    s.validate()
+    import parameter_golf_b200.train as tr
+    shapes = []
+    real = tr.OracleBackend.train_step
+
+    def spy(self, batches, scale, mom, qat):
+        shapes.append(tuple(batches[0][0].shape))
+        return real(self, batches, scale, mom, qat)
+    monkeypatch.setattr(tr.OracleBackend, "train_step", spy)
+    res = quiet(s).run()
+    assert res.steps == 8
+    # steps 0-1: 512 tokens as rows of 64; steps 2-3: the full 1024 tokens, still rows of 64; from step 4: rows of 256
+    assert shapes == [(8, 64)] * 2 + [(16, 64)] * 2 + [(4, 256)] * 4
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["train.seq_len_start=1024"]).validate()
+    with pytest.raises(ValueError):
+        family_preset("tiny_cpu").apply_overrides(["train.seq_len_start=100"]).validate()
+
+
+def test_ema_starts_at_its_fraction_of_the_run(tmp_path, monkeypatch):
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.apply_env({"EMA_DECAY": "0.9", "EMA_START_FRACTION": "0.5"})
+    s.train.swa_enabled = False
+    s.train.artifact_path = str(tmp_path / "e.pgrs")
+    s.eval.max_tokens = 512
+    import parameter_golf_b200.train as tr
+    calls = []
+    real = tr.Ema.update
+    monkeypatch.setattr(tr.Ema, "update", lambda self, p: (calls.append(1), real(self, p))[1])
+    res = quiet(s).run()
+    assert res.steps == 4 and len(calls) == 2           # the steps that begin at progress 2/4 and 3/4
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["train.ema_start_fraction=0.5"]).validate()

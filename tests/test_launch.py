@@ -98,3 +98,14 @@ def test_byte_sidecars_follow_the_tokenizer_table(tmp_path):
     L.ensure_byte_sidecars(str(tmp_path / "fineweb_val_*.bin"), str(tmp_path / "tok.model"), 320)
     assert os.path.getmtime(names[0]) == stamp
     assert np.array_equal(load_validation_tokens(str(tmp_path / "fineweb_val_*.bin"), 4)[: len(ids)], ids[: len(load_validation_tokens(str(tmp_path / "fineweb_val_*.bin"), 4))])
+
+
+def test_doctor_reports_the_environment_without_a_gpu(capsys):
+    from parameter_golf_b200 import doctor
+    info = doctor.collect()
+    assert info["torch"] and "gloo" in info["dist_backends"] and isinstance(info["gpus"], list) and info["sm100_gpus"] == len(
+        [g for g in info["gpus"] if g["capability"].startswith("10.")])
+    assert doctor.main(["--json"]) == 0
+    assert json.loads(capsys.readouterr().out)["python"] == info["python"]
+    if not info["cuda_available"]:
+        assert doctor.main(["--require-gpu"]) == 1

@@ -171,3 +171,27 @@ def test_eval_cli_runs_document_isolated_lora_ttt(tmp_path):
     assert out.returncode == 0, out.stderr[-1500:]
     kv = dict(l.split("=", 1) for l in out.stdout.splitlines() if "=" in l and not l.startswith("eval_audit_json"))
     assert kv["eval_kind"] == "doc_lora" and float(kv["val_bpb"]) > 0 and np.isfinite(float(kv["val_loss"]))
+
+
+def test_eval_cli_document_lora_on_two_cpu_ranks_matches_one(tmp_path):
+    """Documents are split over ranks in contiguous slices and the three sums reduced: without adapters (which are drawn from a
+    per-rank generator) two ranks must print exactly the one-rank result."""
+    from conftest import free_port
+    from parameter_golf_b200.data.shards import write_shard
+    from parameter_golf_b200.quant.export import export_model
+    s = family_preset("tiny_cpu")
+    art = str(tmp_path / "a.pgrs")
+    export_model(s, gpt.init_params(s.model, 1), art)
+    rng = np.random.default_rng(2)
+    docs = [np.concatenate([[1], rng.integers(2, 1024, size=int(rng.integers(30, 90)))]) for _ in range(6)]
+    write_shard(str(tmp_path / "v_val_000000.bin"), np.concatenate(docs).astype(np.uint16))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    tail = ["--artifact", art, "--family", "tiny_cpu", "--val-pattern", str(tmp_path / "v_val_*.bin"), "eval.adaptation_backend=doc_lora",
+            "eval.legal_score_first=true", "eval.doc_chunk_size=32", "eval.doc_lora_rank=0", "eval.doc_batch_size=2"]
+    one = subprocess.run([sys.executable, "-m", "parameter_golf_b200.evalcli"] + tail, capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    two = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                          "--master-port", str(free_port()), "-m", "parameter_golf_b200.evalcli"] + tail,
+                         capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert one.returncode == 0 and two.returncode == 0, (one.stderr[-800:], two.stderr[-1500:])
+    get = lambda out: float([l for l in out.stdout.splitlines() if l.startswith("val_loss=")][0].split("=")[1])
+    assert abs(get(one) - get(two)) < 1e-9

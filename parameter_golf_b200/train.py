@@ -231,11 +231,14 @@ class VariantResult:
     eval_kind: str = "none"
     peak_mem_mib: int = 0
     complementary_mean_weight: float = 1.0
+    val_history: list = field(default_factory=list)      # (step, val_loss, val_bpb) of the periodic validations (train.val_loss_every)
     timers: dict = field(default_factory=dict)
 
     def key_value_lines(self) -> List[str]:
         out = []
         for k, v in self.__dict__.items():
+            if isinstance(v, list):
+                continue
             if isinstance(v, dict):
                 out.extend(f"{k}.{kk}={vv}" for kk, vv in v.items())
             else:
@@ -363,6 +366,34 @@ class VariantRunner:
         if t.world_size > 1:
             from .parallel.health import RankHealth
             health = RankHealth.from_process_group(timeout_s=float(os.environ.get("PGB_HEALTH_TIMEOUT_S", "120")))
+        val_cache = {}
+
+        def validate_now():
+            """Periodic validation of the baseline trainer (train_gpt.py:964-994): the current weights on non-overlapping
+            validation sequences, every rank on its slice; its time does not count as training time."""
+            nonlocal train_ms, t_start
+            train_ms += 1000.0 * (self.clock() - t_start)
+            t_val = time.perf_counter()
+            if not val_cache:
+                limit = spec.eval.max_tokens if mode == "record" else min(spec.eval.max_tokens or (1 << 62), 8 * m.eval_seq_len)
+                val_cache["tokens"] = load_validation_tokens(t.validation_data_pattern, m.eval_seq_len, limit)
+                val_cache["luts"] = (BpbLuts.from_sentencepiece(spec.eval.tokenizer_vocab_path, m.vocab_size) if spec.eval.tokenizer_vocab_path
+                                     else BpbLuts.seeded(m.vocab_size, spec.eval.byte_table_seed))
+            # CUDA backends: a host copy with the sharded banks gathered from their owners (a collective: every rank is at this step)
+            cur = backend.final_params(ema=False) if fused_ema else backend.sync_params()
+            if t.backend == "cpu":
+                runner_v, vdev = OracleRunner(m, cur), "cpu"
+            else:
+                from .models.engine import EngineRunner
+                runner_v, vdev = EngineRunner(spec, cur, device, train=False), device
+            vl, vb = eval_contiguous(runner_v.nll, val_cache["tokens"], m.eval_seq_len, val_cache["luts"], t.rank, t.world_size,
+                                     spec.eval.batch_windows, vdev)
+            del runner_v
+            res.val_history.append((step, vl, vb))
+            log.info(f"step:{step}/{max_steps} val_loss:{vl:.4f} val_bpb:{vb:.4f} train_time:{train_ms:.0f}ms "
+                     f"step_avg:{train_ms / max(step - step0, 1):.2f}ms eval_time:{1000.0 * (time.perf_counter() - t_val):.0f}ms")
+            t_start = self.clock()
+
         while step < max_steps:
             if health is not None:
                 health.check()        # a peer that failed or went silent ends this rank on the host, before its next launch
@@ -420,6 +451,8 @@ class VariantRunner:
             now_ms = train_ms + 1000.0 * (self.clock() - t_start)
             if t.train_log_every > 0 and (step <= 10 or step % t.train_log_every == 0 or step == max_steps):
                 log.info(f"step:{step}/{max_steps} train_loss:{loss:.4f} train_time:{now_ms:.0f}ms step_avg:{now_ms / (step - step0):.2f}ms")
+            if t.val_loss_every > 0 and t.validation_data_pattern and (step % t.val_loss_every == 0 or step == max_steps):
+                validate_now()
             if t.checkpoint_every > 0 and t.checkpoint_path and step % t.checkpoint_every == 0:
                 # Every rank takes part: the sharded optimizer gathers its state from the slot owners (a collective), rank 0
                 # writes, and the others wait for the write at a host barrier instead of starting a step whose device-side

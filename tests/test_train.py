@@ -568,3 +568,35 @@ def test_ema_starts_at_its_fraction_of_the_run(tmp_path, monkeypatch):
     assert res.steps == 4 and len(calls) == 2           # the steps that begin at progress 2/4 and 3/4
     with pytest.raises(ValueError):
         family_preset("record_11l").apply_overrides(["train.ema_start_fraction=0.5"]).validate()
+
+
+def test_periodic_validation_logs_and_does_not_count_as_training_time(tmp_path, monkeypatch):
+    """VAL_LOSS_EVERY of the baseline trainer (train_gpt.py:964-994): the current weights on the validation split every N steps
+    and at the last step; the clock that drives the wall-clock cap and the step average is stopped meanwhile."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "record_shaped_proxy"
+    s.apply_env({"VAL_LOSS_EVERY": "3"})
+    s.train.total_iterations = 7
+    s.train.artifact_path = str(tmp_path / "v.pgrs")
+    s.eval.max_tokens = 1024
+    r = quiet(s)
+    lines = []
+    real_info = r.log.info
+    r.log.info = lambda msg: (lines.append(msg), real_info(msg))[1]
+    now = [0.0]
+
+    def clock():                     # one second per reading: validation would add readings if it ran on this clock
+        now[0] += 1.0
+        return now[0]
+    r.clock = clock
+    res = r.run()
+    assert [h[0] for h in res.val_history] == [3, 6, 7]
+    assert all(np.isfinite(h[1]) and h[2] > 0 for h in res.val_history)
+    assert res.val_history[-1][1] < res.val_history[0][1]                          # it learns between the validations
+    vals = [l for l in lines if " val_loss:" in l and l.startswith("step:")]
+    assert len(vals) == 3 and "val_bpb:" in vals[0] and "train_time:" in vals[0]
+    assert not any(k.startswith("val_history") for k in (l.split("=")[0] for l in res.key_value_lines()))
+    # without the option nothing is evaluated during training
+    s.train.val_loss_every = 0
+    assert quiet(s).run().val_history == []

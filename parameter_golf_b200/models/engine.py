@@ -99,7 +99,7 @@ class CudaEngine:
         self.nact = nsaved + (0 if all(self.saved) else 1)     # number of activation buffer sets
         self.act_slot = [a if a >= 0 else self.nact - 1 for a in self.act_slot]
         self.block_in = [None] * self.nslots                   # (x, skip, skip weight) each slot's block consumed
-        self.parallel = m.parallel_residual.enabled
+        self.parallel = m.parallel
         self.gates = []                                        # (weight name, bias name or None, scale, multiplier)
         if m.attn_out_gate.enabled:
             self.gates.append(("attn_gate_weight", "attn_gate_bias", 1.0, 2.0))

@@ -318,7 +318,7 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
         taps.add(i, "o", y)
     attn = F.linear(y, wo.to(dt))
     x_mid = x_in + p["attn_scale"][i].to(dt)[None, None, :] * attn
-    mlp_in = R.rms_norm(x_in if m.parallel_residual.enabled else x_mid, s_l)
+    mlp_in = R.rms_norm(x_in if m.parallel else x_mid, s_l)
     if taps is not None:
         taps.add(i, "up", mlp_in)
     hid = mlp_hidden(m, F.linear(mlp_in, wu.to(dt)))

@@ -93,7 +93,7 @@ class ExecutionPlan:
             passes[l] = passes.get(l, 0) + 1
         masks = [LayerFeatureMask(layer=l, pass_index=rep, xsa=l in m.xsa_layers(),
                                   value_embedding=m.value_embedding.enabled and l in m.value_embedding.layers,
-                                  recurrent=passes[l] > 1, parallel_residual=m.parallel_residual.enabled,
+                                  recurrent=passes[l] > 1, parallel_residual=m.parallel,
                                   attn_out_gate=m.attn_out_gate.enabled, sparse_attn_gate=m.sparse_attn_gate.enabled,
                                   saved=saved[j], unet_role=("encoder" if (j if m.cycled else l) < enc else "decoder") if unet else "none")
                  for j, (l, rep) in enumerate(sched)]
@@ -188,7 +188,7 @@ def estimate_engine_memory(spec: RunSpec, micro_batch_tokens: int, train: bool =
         nact = sum(saved) + (0 if all(saved) else 1)
     gates = int(m.attn_out_gate.enabled) + int(m.sparse_attn_gate.enabled)
     # per activation set: x_in, h, y, x_mid (+ mm unless parallel residual), qkv_pre, qk_post, hu, a, lse, gate outputs
-    per_set = 2 * T * d * (4 + (0 if m.parallel_residual.enabled else 1)) + 2 * 2 * T * qkvw + 2 * 2 * T * mlp + 4 * T * H
+    per_set = 2 * T * d * (4 + (0 if m.parallel else 1)) + 2 * 2 * T * qkvw + 2 * 2 * T * mlp + 4 * T * H
     per_set += gates * (2 * T * d + 4 * T * H)
     act = nact * per_set
     if train:
@@ -219,7 +219,7 @@ def estimate_engine_memory(spec: RunSpec, micro_batch_tokens: int, train: bool =
             scratch += 4 * T * d                                                        # fp32 dQ accumulator of the single-pass attention backward
         if m.bigram.enabled:
             scratch += 2 * T * m.bigram.dim
-        if gates and not m.parallel_residual.enabled:
+        if gates and not m.parallel:
             scratch += 2 * T * d
         est.backward_scratch = scratch
     return est

@@ -108,7 +108,7 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
             if m.normed_out_proj:
                 y = R.rms_norm(y)
             x_mid = x_in + p["attn_scale"][i].to(dtype)[None, :] * F.linear(y, p["qo_bank"][n + i].to(dtype))
-            mlp_in = R.rms_norm(x_in if m.parallel_residual.enabled else x_mid, s_l)
+            mlp_in = R.rms_norm(x_in if m.parallel else x_mid, s_l)
             hid = gpt.mlp_hidden(m, F.linear(mlp_in, p["mlp_up_bank"][i].to(dtype)))
             x = x_mid + p["mlp_scale"][i].to(dtype)[None, :] * F.linear(hid, p["mlp_down_bank"][i].to(dtype))
             if m.dtg:

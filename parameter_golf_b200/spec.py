@@ -80,7 +80,16 @@ class RecurrenceSpec:
 @dataclass
 class ParallelResidualSpec:
     enabled: bool = False
-    split_attention_mlp: bool = False
+    split_attention_mlp: bool = True      # the MLP reads the block input beside the attention only when both are set
+                                          # (pg-model/src/spec.rs:421-422); the reference's own default is false and its presets set true
+
+
+@dataclass
+class CaseOpsSpec:
+    """Case-operator tokenisation of the late SP8192 stack: the validation bytes cannot be read off the token surfaces, so
+    bits-per-byte needs the per-position byte sidecar (``eval.caseops_byte_sidecar_pattern``)."""
+    enabled: bool = False
+    byte_sidecar: bool = False
 
 
 @dataclass
@@ -116,6 +125,7 @@ class ModelSpec:
     recurrence: RecurrenceSpec = field(default_factory=RecurrenceSpec)
     parallel_residual: ParallelResidualSpec = field(default_factory=ParallelResidualSpec)
     attn_out_gate: AttnOutGateSpec = field(default_factory=AttnOutGateSpec)
+    caseops: CaseOpsSpec = field(default_factory=CaseOpsSpec)
     sparse_attn_gate: SparseAttnGateSpec = field(default_factory=SparseAttnGateSpec)
     rope: RopeSpec = field(default_factory=RopeSpec)
     smear_gate: bool = False
@@ -127,7 +137,9 @@ class ModelSpec:
     tied_embed_init_std: float = 0.005
     embed_init: str = "normal"            # normal | overtone: the tied table's singular values reshaped to s_1 / sqrt(k)
     resid_mix_init: str = "identity"      # identity (x, no x0) | phase: sigmoid(3 (l / (n-1) - 1/2)) on x and the rest on x0, per layer
-    compute_precision: str = "bf16_tensor_core"  # f32 (CPU oracle) | bf16_tensor_core
+    compute_precision: str = "bf16_tensor_core"  # f32 / f32_tf32 (CPU oracle) | bf16_tensor_core
+    attention_backend: str = "native"     # recorded, never dispatched on: there is one attention implementation per backend. The reference's
+                                          # names (naive_f32 | flash_f32 | cudnn_sdpa_bf16) are accepted so that its spec files load
     # Optional ideas of the Python records that their own runs leave off (train_gpt.py:70-92 of the 2026-03-23 record). They run on
     # the autograd path (train.backend = cpu); the CUDA engine rejects them at validation.
     value_residual: bool = False          # v <- lambda_0 * v(first layer) + lambda_1 * v in every later layer, lambda learned per layer
@@ -177,6 +189,11 @@ class ModelSpec:
         """Virtual layers: block executions whose position counts for the U-Net split and the per-depth adapters."""
         return self.recurrence.effective_depth if self.cycled else self.num_layers
 
+    @property
+    def parallel(self) -> bool:
+        """Attention and MLP of a block both read the block input (split parallel residual)."""
+        return self.parallel_residual.enabled and self.parallel_residual.split_attention_mlp
+
     def xsa_layers(self) -> list:
         """Blocks with the exclusive-self-attention step: the last xsa_last_n layers; in the cycled form every block that runs as
         one of the last xsa_last_n virtual layers (the flag sits on the block, so it holds in all of that block's passes)."""
@@ -204,6 +221,7 @@ class TrainSpec:
     rank: int = 0
     world_size: int = 1
     artifact_path: str = "artifact.pgrs"
+    fast_bank_updates: bool = False     # accepted for the reference's spec files; bank updates are always the fused kernels here
     warmup_steps: int = 0
     total_iterations: int = 9000
     warmdown_iters: int = 3500
@@ -311,6 +329,7 @@ class EvalSpec:
     phased_ttt_prefix_docs: int = 0
     phased_ttt_phases: int = 1
     phased_ttt_weight_decay: float = 0.0
+    ttt_beta2: float = 0.99            # carried for the reference's spec files and audit line; the adapter update is SGD with weight decay
     chunk_tokens: int = 32768
     tokenizer_vocab_path: Optional[str] = None
     caseops_byte_sidecar_pattern: Optional[str] = None
@@ -349,7 +368,14 @@ class RunSpec:
     # ---- construction -------------------------------------------------------------------
     @staticmethod
     def from_dict(d: dict) -> "RunSpec":
-        return _from_dict(RunSpec, d)
+        """A spec from a (possibly partial) nested dictionary. Keys that are absent keep the values of the family the dictionary
+        names in ``model.family``, or of ``baseline_sp8192`` when it names none: the reference fills missing keys from
+        ``RunSpec::for_family(BaselineSp8192)`` (pg-model/src/spec.rs:693-697 with ``#[serde(default)]``), and its shipped spec
+        files rely on that."""
+        family = (d.get("model") or {}).get("family", "baseline_sp8192")
+        if family not in FAMILIES:
+            raise ValueError(f"unknown model.family {family!r}; known: {FAMILIES}")
+        return _overlay(family_preset(family), d)
 
     @staticmethod
     def load(path: str) -> "RunSpec":
@@ -585,6 +611,10 @@ class RunSpec:
         chk(not (m.activation == "swiglu" or m.normed_out_proj or m.block_smear or m.vocab_bias) or t.backend == "cpu",
             "model.activation=swiglu, model.normed_out_proj, model.block_smear and model.vocab_bias run on train.backend=cpu only")
         chk(m.rope.mode in ("none", "partial", "yarn"), "unknown rope.mode")
+        chk(m.attention_backend in ("native", "naive_f32", "flash_f32", "cudnn_sdpa_bf16"), "unknown model.attention_backend")
+        chk(m.compute_precision in ("f32", "f32_tf32", "bf16_tensor_core"), "unknown model.compute_precision")
+        chk(not (m.caseops.enabled and m.caseops.byte_sidecar and self.mode == "record") or bool(e.caseops_byte_sidecar_pattern),
+            "model.caseops.byte_sidecar in record mode needs eval.caseops_byte_sidecar_pattern (token surfaces do not give the byte counts)")
         chk(m.rope.mode != "yarn" or (m.rope.yarn_max_len > 0 and m.rope.yarn_train_len > 0), "rope.mode=yarn needs yarn_max_len and yarn_train_len > 0")
         chk(m.skip_topology in ("none", "unet"), "unknown skip_topology")
         chk(m.num_layers >= 1, "num_layers must be >= 1")
@@ -627,6 +657,9 @@ class RunSpec:
             "attn_out_gate and sparse_attn_gate are mutually exclusive")
         if m.bigram.enabled:
             chk(m.bigram.vocab_size >= 2, "bigram.vocab_size must be >= 2")
+            chk(t.backend == "cpu" or (m.bigram.dim % 64 == 0 and m.bigram.dim != m.model_dim),
+                "the CUDA engine needs model.bigram.dim to be a multiple of 64 below model_dim (its products tile the output in 64 columns); "
+                "the reference families' 112 runs on train.backend=cpu, or set model.bigram.dim=128")
         if m.value_embedding.enabled:
             chk(all(0 <= l < m.num_layers for l in m.value_embedding.layers), "value_embedding.layers out of range")
         if m.recurrence.enabled:
@@ -772,29 +805,47 @@ def family_preset(family: str) -> RunSpec:
         s.quant.prune_to_target = False
         s.eval.stride = 16
     else:
+        # The six families of the reference engine, field for field (pg-model/src/spec.rs:313-399 ModelSpec::for_family, with
+        # TrainSpec / QuantSpec / EvalSpec defaults of :489-524, :603-664): SP8192 vocabulary, 11 x 512, BigramHash 3072 x 112, value
+        # embeddings on the last two blocks, boundary-masked SmearGate, query gain 5.
         m.vocab_size = 8192
         m.num_layers, m.mlp_mult, m.activation = 11, 3.0, "leaky_relu_sq"
-        m.ln_scale, m.smear_gate = True, True
-        m.bigram = BigramSpec(True, 2048, 128)
-        t.batch_tokens, t.seq_len = 524_288, 2048
+        m.train_seq_len = m.eval_seq_len = 2048
+        m.bigram = BigramSpec(True, 3072, 112)
+        m.xsa_last_n = 4
+        m.value_embedding = ValueEmbeddingSpec(True, 128, [9, 10])
+        m.rope = RopeSpec("partial", 16, 10000.0)
+        m.smear_gate, m.smear_gate_boundary_token_id = True, 1
+        m.logit_softcap, m.qk_gain_init, m.ln_scale, m.tie_embeddings = 30.0, 5.0, True, True
+        m.attention_backend, m.compute_precision = "flash_f32", "f32_tf32"
+        t.batch_tokens, t.seq_len, t.warmup_steps = 524_288, 2048, 20
+        q, e = s.quant, s.eval
+        q.lqer = LqerSpec(False, 4, 3, 2, 4, 64, True)
+        q.mlp_clip_sigmas, q.attn_clip_sigmas, q.embed_clip_sigmas, q.gptq_calibration_batches = 12.0, 13.0, 14.0, 0
+        e.legal_score_first, e.lora_rank, e.lora_alpha = True, 128, 144.0
+        e.phased_ttt_prefix_docs, e.phased_ttt_phases, e.phased_ttt_weight_decay, e.ttt_beta2 = 2000, 3, 1.0, 0.99
         if family == "xsa_all_sp8192":
             m.xsa_last_n = m.num_layers
         elif family == "recurrence_mid_sp8192":
-            m.xsa_last_n = 4
             m.recurrence = RecurrenceSpec(True, 4, 2)
         elif family == "parallel_resid_sp8192":
-            m.xsa_last_n = 4
-            m.parallel_residual = ParallelResidualSpec(True, False)
+            m.parallel_residual = ParallelResidualSpec(True, True)
         elif family == "hybrid_competitive_sp8192":
-            m.xsa_last_n = m.num_layers
+            m.xsa_last_n, m.qk_gain_init = m.num_layers, 5.25
+            m.value_embedding = ValueEmbeddingSpec(False, 128, [])
             m.recurrence = RecurrenceSpec(True, 4, 2)
-            m.value_embedding = ValueEmbeddingSpec(True, 128, [9, 10])
-        elif family == "frontier_1855_like":
-            m.xsa_last_n = m.num_layers
+            m.parallel_residual = ParallelResidualSpec(True, True)
+            m.caseops = CaseOpsSpec(True, True)
             m.sparse_attn_gate = SparseAttnGateSpec(True, 12, 1.0)
-            m.value_embedding = ValueEmbeddingSpec(True, 128, [9, 10])
-        else:  # baseline_sp8192
-            m.xsa_last_n = 4
+        elif family == "frontier_1855_like":
+            m.attention_backend, m.compute_precision = "cudnn_sdpa_bf16", "bf16_tensor_core"
+            m.mlp_mult, m.xsa_last_n, m.qk_gain_init = 4.0, m.num_layers, 5.0
+            m.value_embedding = ValueEmbeddingSpec(False, 128, [])
+            m.recurrence = RecurrenceSpec(True, 4, 2)
+            m.parallel_residual = ParallelResidualSpec(True, True)
+            m.caseops = CaseOpsSpec(True, True)
+            m.sparse_attn_gate = SparseAttnGateSpec(True, 12, 0.5)
+            m.bigram.enabled = False
     return s
 
 
@@ -831,17 +882,17 @@ def _coerce(text: str, current, ftype=None):
     return text
 
 
-def _from_dict(cls, d: dict):
-    obj = cls()
-    known = {f.name: f for f in fields(cls)}
+def _overlay(obj, d: dict):
+    """Set the keys of ``d`` on the dataclass ``obj`` (tables recurse into the nested dataclass that is already there)."""
+    known = {f.name: f for f in fields(obj)}
     for k, v in d.items():
         if k not in known:
-            raise KeyError(f"unknown key {k!r} in [{cls.__name__}]")
+            raise KeyError(f"unknown key {k!r} in [{type(obj).__name__}]")
         cur = getattr(obj, k)
         if is_dataclass(cur):
             if not isinstance(v, dict):
                 raise TypeError(f"{k} must be a table")
-            setattr(obj, k, _from_dict(type(cur), v))
+            _overlay(cur, v)
         else:
             if isinstance(cur, float) and isinstance(v, int) and not isinstance(v, bool):
                 v = float(v)

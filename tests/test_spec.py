@@ -7,9 +7,107 @@ from parameter_golf_b200.spec import RunSpec, family_preset
 
 def test_partial_toml_loads(tmp_path):
     f = tmp_path / "s.toml"
-    f.write_text('name = "x"\nmode = "smoke"\n[model]\nnum_layers = 3\n[model.bigram]\nenabled = true\nvocab_size = 64\n[eval]\nstride = 32\n')
+    f.write_text('name = "x"\nmode = "smoke"\n[model]\nnum_layers = 12\n[model.bigram]\nenabled = true\nvocab_size = 64\n[eval]\nstride = 32\n')
     s = RunSpec.load(str(f)).validate()
-    assert s.model.num_layers == 3 and s.model.bigram.enabled and s.eval.stride == 32 and s.train.seq_len == 2048
+    assert s.model.num_layers == 12 and s.model.bigram.enabled and s.eval.stride == 32 and s.train.seq_len == 2048
+    # what the file leaves out comes from the reference's default family (pg-model/src/spec.rs:693-697), nested tables included
+    assert (s.model.family, s.model.vocab_size, s.model.bigram.vocab_size, s.model.bigram.dim) == ("baseline_sp8192", 8192, 64, 112)
+    g = tmp_path / "t.toml"
+    g.write_text('[model]\nfamily = "tiny_cpu"\nnum_layers = 3\n')
+    t = RunSpec.load(str(g)).validate()
+    assert t.model.num_layers == 3 and t.model.model_dim == family_preset("tiny_cpu").model.model_dim
+    g.write_text('[model]\nfamily = "nope"\n')
+    with pytest.raises(ValueError):
+        RunSpec.load(str(g))
+
+
+def test_the_reference_engines_shipped_spec_files_load(tmp_path):
+    """The five spec files of the reference tree, restated here key for key where they matter (the files themselves are not
+    part of this repository): every key they use is accepted, omitted keys fall back to baseline_sp8192."""
+    frontier = tmp_path / "frontier.toml"
+    frontier.write_text("""
+name = "frontier_1855_merged_target"
+mode = "smoke"
+[model]
+family = "frontier_1855_like"
+attention_backend = "cudnn_sdpa_bf16"
+compute_precision = "bf16_tensor_core"
+mlp_mult = 4.0
+xsa_last_n = 11
+smear_gate_boundary_token_id = 1
+[model.bigram]
+enabled = false
+vocab_size = 3072
+dim = 112
+[model.value_embedding]
+enabled = false
+dim = 128
+layers = []
+[model.recurrence]
+enabled = true
+start_layer = 4
+repeat_layers = 2
+[model.parallel_residual]
+enabled = true
+split_attention_mlp = true
+[model.attn_out_gate]
+enabled = false
+width = 24
+[model.caseops]
+enabled = true
+byte_sidecar = true
+[model.sparse_attn_gate]
+enabled = true
+width = 12
+scale = 0.5
+[train]
+backend = "cuda_distributed"
+distributed_optimizer_backend = "sharded_parallel_muon"
+batch_tokens = 786432
+world_size = 8
+fast_bank_updates = false
+warmdown_frac = 0.85
+min_lr_scale = 0.10
+adam_beta2 = 0.99
+[quant]
+scheme = "mixed_int5_int6"
+calibration = "self_generated"
+compression = "pergroup"
+embed_bits = 7
+mlp_clip_sigmas = 11.5
+gptq_calibration_batches = 16
+[quant.lqer]
+enabled = true
+rank = 4
+top_k = 3
+a_bits = 2
+b_bits = 4
+group_size = 64
+asymmetric = true
+[eval]
+qttt = true
+adaptation_backend = "gpu_lora_phased"
+lora_rank = 80
+phased_ttt_prefix_docs = 2500
+phased_ttt_weight_decay = 0.5
+ttt_beta2 = 0.99
+caseops_byte_sidecar_pattern = "data/fineweb_val_bytes_*.bin"
+""")
+    s = RunSpec.load(str(frontier)).validate()
+    m = s.model
+    assert m.parallel and m.caseops.byte_sidecar and not m.bigram.enabled and m.mlp_dim == 2048 and m.xsa_layers() == list(range(11))
+    assert s.eval.lora_alpha == 144.0 and s.eval.phased_ttt_phases == 3 and s.quant.attn_clip_sigmas == 13.0        # left out: reference defaults
+    smoke = tmp_path / "lora.toml"
+    smoke.write_text('name = "baseline_gpu_lora_eval_smoke"\nmode = "smoke"\n[eval]\nstride = 512\nqttt = true\nadaptation_backend = "gpu_lora_phased"\n'
+                     'lora_rank = 16\nlora_alpha = 16.0\nphased_ttt_phases = 2\nchunk_tokens = 4096\nmax_tokens = 4096\n')
+    b = RunSpec.load(str(smoke)).validate()
+    assert b.model.family == "baseline_sp8192" and b.model.value_embedding.enabled and b.model.qk_gain_init == 5.0 and b.eval.legal_score_first
+    # enabled without the split flag is the sequential block, as in the reference (pg-model/src/spec.rs:421-422)
+    seq = family_preset("parallel_resid_sp8192")
+    seq.model.parallel_residual.split_attention_mlp = False
+    assert not seq.model.parallel and family_preset("parallel_resid_sp8192").model.parallel
+    with pytest.raises(ValueError):
+        RunSpec.load(str(frontier)).apply_overrides(["mode=record", "eval.caseops_byte_sidecar_pattern=", "train.train_data_pattern=a", "train.validation_data_pattern=b"]).validate()
 
 
 def test_unknown_key_rejected(tmp_path):

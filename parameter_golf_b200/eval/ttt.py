@@ -182,6 +182,19 @@ def schedule_prefix_docs(tokens: np.ndarray, boundary_id: Optional[int], prefix_
     return min(-(-end // chunk_tokens) * chunk_tokens, tokens.shape[0] - 1)
 
 
+def chunk_phases(num_chunks: int, phases: int, prefix_chunks: int = 0) -> List[int]:
+    """Phase of every chunk (``pg-eval/src/gpu_lora_ttt.rs:688-750``): without a prefix, chunk ``i`` is in phase
+    ``i * phases / num_chunks``; with one, the chunks of the leading documents form phase 0 (the warm-up) and the rest is spread
+    evenly over phases 1 .. phases-1."""
+    phases = max(phases, 1)
+    if prefix_chunks <= 0:
+        return [min(i * phases // max(num_chunks, 1), phases - 1) for i in range(num_chunks)]
+    prefix_chunks = min(prefix_chunks, num_chunks)
+    rest = max(num_chunks - prefix_chunks, 1)
+    tail = [0 if phases <= 1 else 1 + min(i * (phases - 1) // rest, phases - 2) for i in range(num_chunks - prefix_chunks)]
+    return [0] * prefix_chunks + tail
+
+
 def eval_lora_phased_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalSpec, luts: BpbLuts, rank: int = 0, world: int = 1,
                          device="cpu", log: Callable = lambda s: None, all_reduce: Optional[Callable] = None) -> Tuple[float, float]:
     """Phased Q-LoRA test-time training: score a chunk with the adapter as it stands (guarded against mutation), then one
@@ -192,8 +205,13 @@ def eval_lora_phased_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalS
     total = tokens.shape[0] - 1
     chunks = build_ttt_chunks(total, window, stride, ev.chunk_tokens)
     runner.lora = init_q_lora(model, ev.lora_rank, ev.lora_alpha, device)
-    phases = max(ev.phased_ttt_phases, 1)
-    per_phase = -(-len(chunks) // phases)
+    prefix_end = schedule_prefix_docs(tokens[: total + 1], ev.doc_boundary_token_id, ev.phased_ttt_prefix_docs, ev.chunk_tokens)
+    phase_of = chunk_phases(len(chunks), ev.phased_ttt_phases, -(-prefix_end // ev.chunk_tokens))
+    if rank == 0:
+        log("ttt_audit_json=" + json.dumps({"event": "lora_phased_ttt_start", "chunks": len(chunks), "phases": max(ev.phased_ttt_phases, 1),
+                                            "prefix_docs": ev.phased_ttt_prefix_docs, "prefix_token_end": prefix_end,
+                                            "boundary_token_id": ev.doc_boundary_token_id, "lora_rank": ev.lora_rank, "lora_alpha": ev.lora_alpha,
+                                            "weight_decay": ev.phased_ttt_weight_decay, "ttt_beta2": ev.ttt_beta2, "score_first": True}))
     sums = ScoreSums()
     t0 = time.perf_counter()
     tok64 = tokens.astype(np.int64)
@@ -201,7 +219,7 @@ def eval_lora_phased_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalS
         if ev.max_eval_seconds > 0 and agree([time.perf_counter() - t0], "max", world, device)[0] > ev.max_eval_seconds:
             log(f"ttt_deadline_reached chunk={ci}")
             break
-        if ci % per_phase == 0 and ci > 0:
+        if ci > 0 and phase_of[ci] != phase_of[ci - 1]:
             runner.lora["b"].zero_()                         # phase change resets B
         if not windows:
             continue
@@ -232,7 +250,7 @@ def eval_lora_phased_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalS
                         runner.lora[key].mul_(1.0 - lr * ev.phased_ttt_weight_decay)
                     runner.lora[key].add_(g[gk], alpha=-lr)
         if rank == 0:
-            log("ttt_audit_json=" + json.dumps({"chunk": ci, "windows": len(windows), "lr": lr,
+            log("ttt_audit_json=" + json.dumps({"chunk": ci, "phase": phase_of[ci], "prefix_warmup": ci * ev.chunk_tokens < prefix_end, "windows": len(windows), "lr": lr,
                                                 "elapsed_s": round(time.perf_counter() - t0, 3)}))
     runner.lora = None
     return sums.all_reduce(device).result()

@@ -288,3 +288,28 @@ def test_doc_lora_ttt_scores_before_it_trains_and_never_crosses_documents():
     e = family_preset("tiny_cpu")
     e.apply_env({"TTT_LORA_RANK": "8", "TTT_LORA_LR": "0.01", "TTT_CHUNK_SIZE": "256", "TTT_BATCH_SIZE": "64", "TTT_EVAL_SEQ_LEN": "1024"})
     assert (e.eval.doc_lora_rank, e.eval.doc_chunk_size, e.eval.doc_batch_size, e.model.eval_seq_len) == (8, 256, 64, 1024)
+
+
+def test_phases_and_the_prefix_document_warm_up_schedule():
+    """pg-eval/src/gpu_lora_ttt.rs:688-750: without a prefix chunk i is in phase i * P / n; with one, the leading documents'
+    chunks are phase 0 and the rest spreads over phases 1 .. P-1; the adapter's B restarts at every phase change."""
+    import json
+    assert T.chunk_phases(6, 3) == [0, 0, 1, 1, 2, 2] and T.chunk_phases(5, 1) == [0] * 5 and T.chunk_phases(4, 8) == [0, 2, 4, 6]
+    assert T.chunk_phases(7, 3, prefix_chunks=2) == [0, 0, 1, 1, 1, 2, 2] and T.chunk_phases(4, 1, prefix_chunks=2) == [0] * 4
+    assert T.chunk_phases(3, 2, prefix_chunks=9) == [0, 0, 0]
+    s = spec()
+    s.eval.lora_rank, s.eval.phased_ttt_phases, s.eval.ttt_lr, s.eval.chunk_tokens = 4, 3, 0.05, 32
+    s.eval.phased_ttt_prefix_docs, s.eval.doc_boundary_token_id = 2, 1
+    p = gpt.fill_deterministic(s.model)
+    rng = np.random.default_rng(6)
+    body = rng.integers(2, 32, 32 * 6 + 1).astype(np.uint16)
+    body[[0, 20, 50, 90, 140]] = 1                                   # document starts: the first two documents end before token 51
+    logs = []
+    loss, _ = T.eval_lora_phased_ttt(OracleRunner(s.model, p), body, s.model, s.eval, BpbLuts.seeded(32), log=logs.append)
+    audits = [json.loads(l.split("=", 1)[1]) for l in logs if l.startswith("ttt_audit_json=")]
+    start = audits[0]
+    assert start["event"] == "lora_phased_ttt_start" and start["prefix_docs"] == 2 and start["prefix_token_end"] == 32 and start["ttt_beta2"] == 0.99
+    per_chunk = [a for a in audits[1:] if "chunk" in a]
+    assert T.chunk_phases(6, 3, prefix_chunks=1) == [0, 1, 1, 1, 2, 2]
+    assert [a["phase"] for a in per_chunk] == [0, 1, 1, 1, 2]            # the last chunk is scored and never trained on: no line
+    assert [a["prefix_warmup"] for a in per_chunk] == [True] + [False] * 4 and math.isfinite(loss)

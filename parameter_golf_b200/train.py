@@ -386,8 +386,10 @@ class VariantRunner:
             else:
                 from .models.engine import EngineRunner
                 runner_v, vdev = EngineRunner(spec, cur, device, train=False), device
-            vl, vb = eval_contiguous(runner_v.nll, val_cache["tokens"], m.eval_seq_len, val_cache["luts"], t.rank, t.world_size,
-                                     spec.eval.batch_windows, vdev)
+            # sequences per forward: the baseline's VAL_BATCH_SIZE split over ranks and micro-batches (train_gpt.py:238-247), never
+            # more than the evaluation batch the spec allows
+            seqs = max(min(t.val_batch_size // max(t.world_size * accum * m.eval_seq_len, 1), spec.eval.batch_windows), 1)
+            vl, vb = eval_contiguous(runner_v.nll, val_cache["tokens"], m.eval_seq_len, val_cache["luts"], t.rank, t.world_size, seqs, vdev)
             del runner_v
             res.val_history.append((step, vl, vb))
             log.info(f"step:{step}/{max_steps} val_loss:{vl:.4f} val_bpb:{vb:.4f} train_time:{train_ms:.0f}ms "

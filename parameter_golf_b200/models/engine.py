@@ -50,7 +50,9 @@ def _unsupported(m: ModelSpec) -> Optional[str]:
                                      ("embed_dim", m.embed_dim > 0), ("softcap_kind", m.softcap_kind != "tanh"),
                                      ("activation=swiglu", m.activation == "swiglu"), ("normed_out_proj", m.normed_out_proj),
                                      ("block_smear", m.block_smear), ("vocab_bias", m.vocab_bias),
-                                     ("recurrence.effective_depth", m.cycled)) if on]
+                                     ("recurrence.effective_depth", m.cycled), ("gated_attention", m.gated_attention),
+                                     ("bigram.trigram", m.bigram.enabled and m.bigram.trigram),
+                                     ("recurrence.repeats", m.recurrence.enabled and m.recurrence.repeats != 2)) if on]
     if only_autograd:
         return "model options of the autograd path (" + ", ".join(only_autograd) + ")"
     if m.model_dim % 64 or m.kv_dim % 64 or m.mlp_dim % 64 or m.head_dim % 8 or m.vocab_size % 64:

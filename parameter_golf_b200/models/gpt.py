@@ -81,6 +81,9 @@ def param_shapes(m: ModelSpec) -> Dict[str, tuple]:
         sh["block_smear_gate"] = (n, d)
     if m.vocab_bias:
         sh["vocab_bias"] = (m.vocab_size,)
+    if m.gated_attention:
+        sh["gated_attn_weight"] = (n, H, d)
+        sh["gated_attn_bias"] = (n, H)
     r = m.recurrence.depth_lora_rank if m.cycled else 0
     if r > 0:
         sh["depth_lora_q_down"] = (m.depth, r, d)
@@ -141,6 +144,8 @@ def init_params(m: ModelSpec, seed: int = 1337, device="cpu", dtype=torch.float3
         p["ve_layer_scales"].fill_(1.0)
     if "attn_gate_bias" in p:
         p["attn_gate_bias"].fill_(4.0)
+    if "gated_attn_bias" in p:
+        p["gated_attn_bias"].fill_(4.0)           # sigmoid(4) = 0.98: the gate starts almost open, its weight at zero
     if "embed_proj_in" in p:
         p["embed_proj_in"] = _orthogonal(d, m.embed_dim, g)
         p["embed_proj_out"] = p["embed_proj_in"].t().contiguous().clone()     # starts as the transpose: the tied pair is consistent
@@ -235,7 +240,7 @@ def layer_schedule(m: ModelSpec):
         return [(v % m.num_layers, v // m.num_layers) for v in range(m.depth)]
     order = []
     for i in range(m.num_layers):
-        reps = 2 if (m.recurrence.enabled and m.recurrence.start_layer <= i < m.recurrence.start_layer + m.recurrence.repeat_layers) else 1
+        reps = m.recurrence.repeats if (m.recurrence.enabled and m.recurrence.start_layer <= i < m.recurrence.start_layer + m.recurrence.repeat_layers) else 1
         order.extend((i, r) for r in range(reps))
     return order
 
@@ -311,6 +316,10 @@ def block_forward(m: ModelSpec, p, i: int, x, x0, ids, cos, sin, qat: bool = Fal
         y = R.attn_out_gate(y, h, p["attn_gate_weight"][i], p["attn_gate_bias"][i])
     if m.sparse_attn_gate.enabled:
         y = R.sparse_attn_gate(y, h, p["sparse_attn_gate_weight"][i], m.sparse_attn_gate.scale)
+    if m.gated_attention:
+        # records/.../2026-03-23_.../train_gpt.py:668-671: the gate reads the whole normed block input
+        gate = torch.sigmoid(F.linear(h, p["gated_attn_weight"][i].to(dt), p["gated_attn_bias"][i].to(dt)))
+        y = y * gate[..., None]
     y = y.reshape(B, T, d)
     if m.normed_out_proj:
         y = R.rms_norm(y)                 # train_gpt_cuda_ternary.py:468-470: the output projection norms its own input
@@ -344,7 +353,10 @@ def gpt_hidden(m: ModelSpec, p, ids: torch.Tensor, qat: bool = False, lora=None,
     B, T = ids.shape
     x = embed_tokens(m, p, ids, dt, qat)
     if m.bigram.enabled:
-        bg = _small(m, p, "bigram_embed", qat)[R.bigram_hash(ids, m.bigram.vocab_size)].to(dt)
+        table = _small(m, p, "bigram_embed", qat)
+        bg = table[R.bigram_hash(ids, m.bigram.vocab_size)].to(dt)
+        if m.bigram.trigram:
+            bg = bg + table[R.trigram_hash(ids, m.bigram.vocab_size)].to(dt)
         if "bigram_proj" in p:
             bg = F.linear(bg, _small(m, p, "bigram_proj", qat).to(dt))
         x = x + p["bigram_scale"][0].to(dt) * bg

@@ -133,6 +133,23 @@ def smear_gate(x, gate, ids=None, boundary_id=None):
     return (1 - s) * x + s * x_prev
 
 
+def trigram_hash(ids: torch.Tensor, buckets: int) -> torch.Tensor:
+    """``((36313*cur) xor (27191*prev) xor (51497*prev2)) mod (buckets-1)`` in wrapping 32-bit arithmetic into the bigram table;
+    the first two positions of each sequence map to the sentinel bucket
+    (records/track_10min_16mb/2026-03-25_ValCalib_GPTQ_XSA_BigramHash3072/train_gpt.py:698-705). ids: [B,T]."""
+    t = ids.to(torch.int64)
+    mod = buckets - 1
+    out = torch.full_like(t, mod)
+    if t.shape[-1] > 2:
+        # int32 products wrap; xor and the remainder then act on the signed value, as torch does on int32 tensors
+        def wrap(v):
+            v = v & 0xFFFFFFFF
+            return torch.where(v >= 2 ** 31, v - 2 ** 32, v)
+        h = wrap(36313 * t[..., 2:]) ^ wrap(27191 * t[..., 1:-1]) ^ wrap(51497 * t[..., :-2])
+        out[..., 2:] = torch.remainder(h, mod)
+    return out
+
+
 def running_mean_smear(x, gate):
     """``x + tanh(gate) * (m - x)`` where ``m[t]`` is the mean of ``x[0..t]`` of the same sequence: every position is blended with
     the causal running mean of its sequence, per feature, by a gate that starts at zero

@@ -50,6 +50,9 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
             else:
                 b = torch.bitwise_xor((36313 * ids) & 0xFFFFFFFF, (27191 * toks[:, t - 1]) & 0xFFFFFFFF) % (m.bigram.vocab_size - 1)
             bg = p["bigram_embed"][b].to(dtype)
+            if m.bigram.trigram:
+                tri = R.trigram_hash(toks[:, max(t - 2, 0): t + 1], m.bigram.vocab_size)[:, -1] if t >= 2 else torch.full_like(ids, m.bigram.vocab_size - 1)
+                bg = bg + p["bigram_embed"][tri].to(dtype)
             if "bigram_proj" in p:
                 bg = F.linear(bg, p["bigram_proj"].to(dtype))
             x = x + p["bigram_scale"][0].to(dtype) * bg
@@ -104,6 +107,8 @@ def generate_autoregressive(m: ModelSpec, p: Dict[str, torch.Tensor], num_seqs: 
                 y = R.attn_out_gate(y, h[:, None], p["attn_gate_weight"][i], p["attn_gate_bias"][i])
             if m.sparse_attn_gate.enabled:
                 y = R.sparse_attn_gate(y, h[:, None], p["sparse_attn_gate_weight"][i], m.sparse_attn_gate.scale)
+            if m.gated_attention:
+                y = y * torch.sigmoid(F.linear(h, p["gated_attn_weight"][i].to(dtype), p["gated_attn_bias"][i].to(dtype)))[:, None, :, None]
             y = y.reshape(num_seqs, d)
             if m.normed_out_proj:
                 y = R.rms_norm(y)

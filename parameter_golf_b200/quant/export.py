@@ -169,6 +169,9 @@ def build_artifact(spec: RunSpec, params: Dict[str, torch.Tensor], precomputed=N
             recs.append(_f16(f"blocks.{i}.dtg_gate_bias", params["dtg_gate_bias"][i].reshape(1)))
         if m.block_smear:
             recs.append(_f16(f"blocks.{i}.block_smear_gate", params["block_smear_gate"][i]))
+        if m.gated_attention:
+            recs.append(_f16(f"blocks.{i}.gated_attn_weight", params["gated_attn_weight"][i]))
+            recs.append(_f16(f"blocks.{i}.gated_attn_bias", params["gated_attn_bias"][i]))
     # the multi-token-prediction heads are training-only and are left out (records/.../2026-03-23_.../train_gpt.py:1778)
     if m.value_embedding.enabled:
         recs.append(_flt("ve_embed", params["ve_embed"], spec.quant.float_storage))
@@ -331,7 +334,7 @@ def load_artifact(blob: bytes, spec: RunSpec, device="cpu", dtype=torch.float32)
                 raise C.ArtifactError(f"artifact is missing tensor {name}")
             p[name] = torch.from_numpy(_np(by[name]).astype(np.float32)).reshape(shapes[name])
     for k in ("attn_scale", "mlp_scale", "resid_mix", "q_gain", "attn_gate_weight", "attn_gate_bias", "sparse_attn_gate_weight", "vr_lambda", "dtg_gate_weight",
-              "dtg_gate_bias", "block_smear_gate"):
+              "dtg_gate_bias", "block_smear_gate", "gated_attn_weight", "gated_attn_bias"):
         if k in shapes:
             p[k] = torch.stack([torch.from_numpy(_np(by[f"blocks.{i}.{k}"]).astype(np.float32)) for i in range(n)]).reshape(shapes[k])
     for k in DEPTH_LORA:

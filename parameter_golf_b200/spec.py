@@ -47,6 +47,7 @@ class BigramSpec:
     enabled: bool = False
     vocab_size: int = 2048
     dim: int = 128
+    trigram: bool = False        # also add the row hashed from (t-2, t-1, t) of the same table (TRIGRAM of the 2026-03-25 record; autograd path)
 
 
 @dataclass
@@ -74,6 +75,8 @@ class RecurrenceSpec:
     # with effective_depth > num_layers the num_layers unique blocks run in the order 0, 1, ..., n-1, 0, 1, ... for
     # effective_depth virtual layers; the U-Net split, its skip weights and xsa_last_n then count virtual layers.
     effective_depth: int = 0
+    repeats: int = 2                  # passes of each recurrent block in a row; other values than 2 run on the autograd path only
+                                      # (TRAINING_DEPTH_RECURRENCE of the ternary record repeats every block)
     depth_lora_rank: int = 0          # > 0: a low-rank correction of the query and value projections per virtual layer (its DepthLoRA)
 
 
@@ -156,6 +159,8 @@ class ModelSpec:
     qat_ternary_group: int = 128          # qat_kind = ternary | binary: input columns per scale (keep equal to quant.ternary_group)
     normed_out_proj: bool = False         # RMSNorm on the inputs of the attention output and MLP down projections (the ternary and
                                           # binary submissions' "normed" linear layers, which see un-normalised activations)
+    gated_attention: bool = False         # per-head sigmoid(W_h . x + b_h) on the attention output, full-width input, W from zero and b = 4
+                                          # (GATED_ATTENTION of the 2026-03-23 record; autograd path)
     vocab_bias: bool = False              # a learned bias per vocabulary entry added to the logits before the soft-cap (zero at the start)
     block_smear: bool = False             # every block ends with x + tanh(g) * (causal running mean of x - x), g[d] learned per block from zero
     fp8_qat: bool = False                 # while QAT is on, the small 2-D float tensors (bigram / value-embedding tables and
@@ -255,6 +260,8 @@ class TrainSpec:
     lawa_k: int = 10
     lawa_freq: int = 100
     late_qat_threshold: float = 0.15
+    qat_fraction: float = 0.0           # > 0: QAT switches on for the last fraction of the wall-clock budget (of the steps without a cap),
+                                        # whatever the learning-rate scale (QAT_FRACTION of the depth-recurrence submission)
     qat_enabled: bool = False
     seed: int = 1337
     val_loss_every: int = 0
@@ -545,6 +552,17 @@ class RunSpec:
             m.bigram.enabled = m.bigram.vocab_size > 0
         if has("BIGRAM_DIM"): m.bigram.dim = I("BIGRAM_DIM")
         if has("XSA_LAST_N"): m.xsa_last_n = I("XSA_LAST_N")
+        if has("GATED_ATTENTION"): m.gated_attention = B("GATED_ATTENTION")
+        if has("TRIGRAM"): m.bigram.trigram = B("TRIGRAM")
+        if has("QAT_FRACTION"): t.qat_fraction = F("QAT_FRACTION")
+        if has("MUON_WEIGHT_DECAY"): t.muon_wd = F("MUON_WEIGHT_DECAY")
+        if has("MTP_HEADS"): m.mtp_num_heads = I("MTP_HEADS")
+        if has("SLIDING_EVAL_STRIDE"): e.stride = I("SLIDING_EVAL_STRIDE")
+        if has("SLIDING_BATCH_SIZE"): e.batch_windows = I("SLIDING_BATCH_SIZE")
+        if has("VAL_MAX_TOKENS") and I("VAL_MAX_TOKENS") > 0: e.max_tokens = I("VAL_MAX_TOKENS")
+        if has("TRAINING_DEPTH_RECURRENCE") and I("TRAINING_DEPTH_RECURRENCE") > 1:
+            m.recurrence.enabled, m.recurrence.start_layer, m.recurrence.repeat_layers = True, 0, m.num_layers
+            m.recurrence.repeats = I("TRAINING_DEPTH_RECURRENCE")
         if has("NUM_UNIQUE_BLOCKS"): m.num_layers = I("NUM_UNIQUE_BLOCKS")
         if has("EFFECTIVE_DEPTH"):
             m.recurrence.effective_depth = I("EFFECTIVE_DEPTH")
@@ -630,6 +648,10 @@ class RunSpec:
         chk(rc.depth_lora_rank == 0 or m.cycled, "recurrence.depth_lora_rank needs the cycled form (recurrence.effective_depth)")
         chk(not m.cycled or t.backend == "cpu", "recurrence.effective_depth (cycled blocks) runs on train.backend=cpu only")
         chk(m.qat_noise_qmax >= 1, "model.qat_noise_qmax must be >= 1")
+        chk(rc.repeats >= 1 and (rc.repeats == 2 or not rc.enabled or t.backend == "cpu"), "recurrence.repeats other than 2 runs on train.backend=cpu only")
+        chk(not (m.gated_attention or (m.bigram.enabled and m.bigram.trigram)) or t.backend == "cpu",
+            "model.gated_attention and model.bigram.trigram run on train.backend=cpu only")
+        chk(0.0 <= t.qat_fraction <= 1.0, "train.qat_fraction must be in [0, 1]")
         chk(m.mtp_num_heads >= 0 and m.mtp_loss_weight >= 0.0, "mtp_num_heads and mtp_loss_weight must be >= 0")
         chk(not (m.value_residual or m.mtp_num_heads > 0 or m.fp8_qat or m.dtg or m.embed_dim > 0) or t.backend == "cpu",
             "model.value_residual, model.mtp_num_heads, model.dtg, model.embed_dim and model.fp8_qat run on train.backend=cpu only "

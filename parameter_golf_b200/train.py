@@ -416,6 +416,9 @@ class VariantRunner:
             else:
                 wd = int(round(max_steps * t.warmdown_frac)) if t.warmdown_frac > 0 else min(t.warmdown_iters, max_steps)
                 scale = lr_scale_with_floor(step, t.warmup_steps, max_steps, wd, t.min_lr_scale) if (wd or t.warmup_steps) else 1.0
+            if t.qat_fraction > 0 and not qat and (elapsed / max_ms if max_ms is not None else step / max(max_steps, 1)) >= 1.0 - t.qat_fraction:
+                qat = True
+                log.info(f"late_qat:enabled step:{step} by qat_fraction:{t.qat_fraction}")
             if t.late_qat_threshold > 0 and scale < t.late_qat_threshold and not qat:
                 qat = True
                 log.info(f"late_qat:enabled step:{step} scale:{scale:.4f}")

@@ -96,6 +96,9 @@ def from_python_state_dict(m: ModelSpec, sd: Dict[str, torch.Tensor]) -> Dict[st
     if "blocks.0.dtg_gate.weight" in sd:
         p["dtg_gate_weight"] = torch.stack([sd[f"blocks.{i}.dtg_gate.weight"].float().reshape(-1) for i in range(n)])
         p["dtg_gate_bias"] = torch.stack([sd[f"blocks.{i}.dtg_gate.bias"].float().reshape(()) for i in range(n)])
+    if "blocks.0.attn.attn_gate.weight" in sd:
+        p["gated_attn_weight"] = torch.stack([sd[f"blocks.{i}.attn.attn_gate.weight"].float() for i in range(n)])
+        p["gated_attn_bias"] = torch.stack([sd[f"blocks.{i}.attn.attn_gate.bias"].float() for i in range(n)])
     if "blocks.0.smear.gate" in sd:
         p["block_smear_gate"] = torch.stack([sd[f"blocks.{i}.smear.gate"].float() for i in range(n)])
     heads = [sd[k].float() for k in sorted((k for k in sd if k.startswith("mtp_heads.") and k.endswith(".weight")), key=lambda k: int(k.split(".")[1]))]
@@ -143,6 +146,8 @@ def to_python_state_dict(m: ModelSpec, p: Dict[str, torch.Tensor]) -> Dict[str, 
             sd[f"blocks.{i}.dtg_gate.bias"] = p["dtg_gate_bias"][i].reshape(1)
         if "block_smear_gate" in p:
             sd[f"blocks.{i}.smear.gate"] = p["block_smear_gate"][i]
+        if "gated_attn_weight" in p:
+            sd[f"blocks.{i}.attn.attn_gate.weight"], sd[f"blocks.{i}.attn.attn_gate.bias"] = p["gated_attn_weight"][i], p["gated_attn_bias"][i]
     if "mtp_heads" in p:
         for k in range(p["mtp_heads"].shape[0]):
             sd[f"mtp_heads.{k}.weight"] = p["mtp_heads"][k]

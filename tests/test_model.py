@@ -428,3 +428,52 @@ def test_overtone_embedding_spectrum_and_phase_residual_mix_initialisation():
     assert torch.allclose(p["resid_mix"][:, 0, 0], want) and torch.allclose(p["resid_mix"][:, 1, 3], 1 - want)
     assert torch.equal(ref["resid_mix"][:, 0], torch.ones(5, m.model_dim)) and float(ref["resid_mix"][:, 1].abs().max()) == 0.0
     assert torch.equal(p["kv_bank"], ref["kv_bank"])                                          # nothing else moves
+
+
+def test_gated_attention_trigram_hash_and_repeat_count():
+    """GATED_ATTENTION (records/.../2026-03-23_.../train_gpt.py:629-633, :668-671), TRIGRAM (…2026-03-25_…:698-710) and blocks that
+    run r times in a row (TRAINING_DEPTH_RECURRENCE of the ternary record), on the autograd model."""
+    import torch.nn.functional as F
+    from parameter_golf_b200.ops import reference as R
+    from parameter_golf_b200.quant.calibrate import generate_autoregressive
+    s = _variant("model.gated_attention=true", "model.bigram.enabled=true", "model.bigram.vocab_size=64", "model.bigram.dim=16", "model.bigram.trigram=true")
+    m = s.model
+    p = gpt.init_params(m, seed=2)
+    assert p["gated_attn_weight"].shape == (m.num_layers, m.num_heads, m.model_dim) and float(p["gated_attn_weight"].abs().max()) == 0.0
+    assert torch.equal(p["gated_attn_bias"], torch.full((m.num_layers, m.num_heads), 4.0))
+    ids = torch.randint(0, m.vocab_size, (2, 20), generator=torch.Generator().manual_seed(0))
+    # at initialisation every gate is sigmoid(4): the ungated model's attention output times that constant
+    pd = gpt.fill_deterministic(m)
+    pd["gated_attn_weight"].zero_()
+    pd["gated_attn_bias"].fill_(4.0)
+    plain = _variant("model.bigram.enabled=true", "model.bigram.vocab_size=64", "model.bigram.dim=16", "model.bigram.trigram=true").model
+    pp = {k: v.clone() for k, v in pd.items() if not k.startswith("gated_attn")}
+    pp["qo_bank"][plain.num_layers:] *= float(torch.sigmoid(torch.tensor(4.0)))                  # fold the constant gate into W_o
+    assert torch.allclose(gpt.gpt_logits(m, pd, ids), gpt.gpt_logits(plain, pp, ids), atol=2e-5)
+    # the trigram row: positions 0 and 1 take the sentinel row, later ones the hash of three tokens
+    h3 = R.trigram_hash(ids, 64)
+    assert torch.equal(h3[:, :2], torch.full((2, 2), 63)) and int(h3.max()) <= 63 and int(h3[:, 2:].min()) >= 0
+    no_tri = _variant("model.gated_attention=true", "model.bigram.enabled=true", "model.bigram.vocab_size=64", "model.bigram.dim=16").model
+    pd = gpt.fill_deterministic(m)
+    a, b = gpt.gpt_logits(m, pd, ids), gpt.gpt_logits(no_tri, pd, ids)
+    assert float((a - b).abs().max()) > 1e-4
+    pz = dict(pd, bigram_embed=pd["bigram_embed"].clone())
+    pz["bigram_embed"][R.trigram_hash(ids, 64).reshape(-1).unique()] = 0                           # rows the trigram path reads
+    # cached decoding follows both options
+    toks = generate_autoregressive(m, pd, 2, 10, seed=3)
+    g = torch.Generator().manual_seed(3)
+    assert torch.equal(torch.randint(0, m.vocab_size, (2,), generator=g), toks[:, 0])
+    for t in range(9):
+        z = gpt.gpt_logits(m, pd, toks[:, : t + 1])[:, -1]
+        assert torch.equal(torch.multinomial(torch.softmax(z / 0.8, -1), 1, generator=g)[:, 0], toks[:, t + 1]), t
+    # every block three times in a row
+    e = family_preset("tiny_cpu")
+    e.apply_env({"TRAINING_DEPTH_RECURRENCE": "3", "GATED_ATTENTION": "1", "TRIGRAM": "1", "QAT_FRACTION": "0.25", "MUON_WEIGHT_DECAY": "0.02",
+                 "MTP_HEADS": "1", "SLIDING_EVAL_STRIDE": "16", "SLIDING_BATCH_SIZE": "8", "VAL_MAX_TOKENS": "0"})
+    e.validate()
+    assert gpt.layer_schedule(e.model) == [(0, 0), (0, 1), (0, 2), (1, 0), (1, 1), (1, 2)] and e.train.qat_fraction == 0.25
+    assert e.train.muon_wd == 0.02 and e.model.mtp_num_heads == 1 and e.eval.stride == 16 and e.eval.batch_windows == 8 and e.eval.max_tokens is None
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["model.gated_attention=true"]).validate()
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["model.recurrence.enabled=true", "model.recurrence.repeat_layers=2", "model.recurrence.repeats=3"]).validate()

@@ -600,3 +600,18 @@ def test_periodic_validation_logs_and_does_not_count_as_training_time(tmp_path, 
     # without the option nothing is evaluated during training
     s.train.val_loss_every = 0
     assert quiet(s).run().val_history == []
+
+
+def test_qat_switches_on_for_the_last_fraction_of_the_run(tmp_path, monkeypatch):
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "record_shaped_proxy"
+    s.apply_overrides(["train.qat_fraction=0.25", "train.late_qat_threshold=0", "train.total_iterations=8"])
+    s.train.artifact_path = str(tmp_path / "q.pgrs")
+    s.eval.max_tokens = 512
+    import parameter_golf_b200.train as tr
+    seen = []
+    real = tr.OracleBackend.train_step
+    monkeypatch.setattr(tr.OracleBackend, "train_step", lambda self, b, scale, mom, qat: (seen.append(qat), real(self, b, scale, mom, qat))[1])
+    quiet(s).run()
+    assert seen == [False] * 6 + [True] * 2

@@ -27,6 +27,20 @@ def leaderboard_violations(spec: RunSpec, args) -> list:
         bad.append("leaderboard evaluation must cover the full validation set (eval.max_tokens is set)")
     if spec.eval.adaptation_backend != "none" and not spec.eval.legal_score_first:
         bad.append("test-time adaptation must be score-first")
+    if not spec.eval.legal_score_first:
+        bad.append("leaderboard evaluation requires eval.legal_score_first=true")
+    if (spec.eval.adaptation_backend == "gpu_lora_phased" and spec.eval.phased_ttt_prefix_docs > 0
+            and spec.model.smear_gate_boundary_token_id is None):
+        bad.append("prefix-document TTT needs the document boundary token (model.smear_gate_boundary_token_id)")
+    if spec.eval.adaptation_backend == "gpu_lora_phased" and int(os.environ.get("WORLD_SIZE", 1)) < max(spec.train.world_size, 1):
+        bad.append("leaderboard LoRA-phased evaluation runs on the configured world size, not on fewer ranks")
+    if spec.model.caseops.enabled and spec.model.caseops.byte_sidecar:
+        if not spec.eval.caseops_byte_sidecar_pattern:
+            bad.append("leaderboard evaluation with CaseOps needs --caseops-byte-sidecar")
+    elif args.bytes == "tokenizer" and not spec.eval.tokenizer_vocab_path:
+        bad.append("leaderboard evaluation with --bytes tokenizer needs --tokenizer-vocab")
+    # (--bytes seeded, the fixed 1-6 byte table that stands in for a tokenizer on synthetic data, is accepted; the reference
+    # insists on a tokenizer here, pg-eval/src/bin/run.rs:296-301)
     if args.bytes == "placeholder":
         bad.append("leaderboard evaluation needs real byte counts, not the 4-bytes-per-token placeholder")
     if not args.val_pattern:

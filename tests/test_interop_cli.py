@@ -195,3 +195,26 @@ def test_eval_cli_document_lora_on_two_cpu_ranks_matches_one(tmp_path):
     assert one.returncode == 0 and two.returncode == 0, (one.stderr[-800:], two.stderr[-1500:])
     get = lambda out: float([l for l in out.stdout.splitlines() if l.startswith("val_loss=")][0].split("=")[1])
     assert abs(get(one) - get(two)) < 1e-9
+
+
+def test_leaderboard_rules_follow_the_reference_binary():
+    """pg-eval/src/bin/run.rs:251-303: score-first, a boundary token for prefix-document TTT, the configured world size for the
+    LoRA-phased evaluator, the byte sidecar when CaseOps is on."""
+    import argparse
+    from parameter_golf_b200.evalcli import leaderboard_violations
+    args = argparse.Namespace(bytes="seeded", val_pattern="v_*.bin")
+    s = family_preset("baseline_sp8192")
+    assert leaderboard_violations(s, args) == []
+    s.eval.legal_score_first = False
+    assert any("legal_score_first" in b for b in leaderboard_violations(s, args))
+    s = family_preset("baseline_sp8192")
+    s.eval.adaptation_backend, s.model.smear_gate_boundary_token_id = "gpu_lora_phased", None
+    assert any("boundary token" in b for b in leaderboard_violations(s, args))
+    s.model.smear_gate_boundary_token_id, s.train.world_size = 1, 8
+    assert any("world size" in b for b in leaderboard_violations(s, args))
+    h = family_preset("hybrid_competitive_sp8192")
+    assert any("caseops-byte-sidecar" in b for b in leaderboard_violations(h, args))
+    h.eval.caseops_byte_sidecar_pattern = "x_bytes_*.bin"
+    assert leaderboard_violations(h, args) == []
+    args.bytes = "tokenizer"
+    assert any("tokenizer-vocab" in b for b in leaderboard_violations(family_preset("baseline_sp8192"), args))

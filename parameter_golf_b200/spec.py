@@ -234,6 +234,8 @@ class TrainSpec:
     min_lr_scale: float = 0.0
     wallclock_warmdown: bool = True
     max_wallclock_seconds: float = 600.0
+    record_max_ms_per_step: float = 130.0   # record mode fails closed when the measured step time is above this; 0 disables (PG_RECORD_MAX_MS_PER_STEP)
+    timing_skip_steps: int = 0              # steps left out of the measured step time (start-up, PG_RECORD_TIMING_SKIP_STEPS)
     matrix_lr: float = 0.025
     scalar_lr: float = 0.025
     embed_lr: float = 0.6
@@ -601,6 +603,8 @@ class RunSpec:
         if has("GPTQ_BLOCK_SIZE"): q.gptq_block_size = I("GPTQ_BLOCK_SIZE")
         if has("INT4_LAYERS"): q.coarse_layers = [int(x) for x in env["INT4_LAYERS"].split(",") if x.strip()]
         if has("INT4_STEP"): q.coarse_step = I("INT4_STEP")
+        if has("PG_RECORD_MAX_MS_PER_STEP"): t.record_max_ms_per_step = F("PG_RECORD_MAX_MS_PER_STEP")
+        if has("PG_RECORD_TIMING_SKIP_STEPS"): t.timing_skip_steps = I("PG_RECORD_TIMING_SKIP_STEPS")
         if has("TARGET_MB"): q.target_artifact_bytes = int(F("TARGET_MB") * 1024 * 1024)
         return self
 

@@ -217,6 +217,7 @@ class VariantResult:
     train_loss_last: float = float("nan")
     train_ms: float = 0.0
     step_avg_ms: float = 0.0
+    measured_ms_per_step: float = 0.0       # step time without the first train.timing_skip_steps steps
     tokens_per_step: int = 0
     tokens_per_s: float = 0.0
     stopped_early: bool = False
@@ -262,6 +263,13 @@ def record_gaps(spec: RunSpec, mode: str) -> List[str]:
         if t.world_size != 8:
             gaps.append("record is defined on 8 GPUs")
     return gaps
+
+
+def check_record_step_time(mode: str, steps: int, measured_ms_per_step: float, limit_ms: float) -> None:
+    """A record run whose measured step time is above the limit is refused before export (``pg-train/src/lib.rs:1514-1521``)."""
+    if mode == "record" and limit_ms > 0 and steps > 0 and measured_ms_per_step > limit_ms:
+        raise RuntimeError(f"record run is too slow for a submission: measured_ms_per_step={measured_ms_per_step:.3f} "
+                           f"max_ms_per_step={limit_ms:.3f} (train.record_max_ms_per_step=0 only for debugging)")
 
 
 class VariantRunner:
@@ -367,6 +375,7 @@ class VariantRunner:
             from .parallel.health import RankHealth
             health = RankHealth.from_process_group(timeout_s=float(os.environ.get("PGB_HEALTH_TIMEOUT_S", "120")))
         val_cache = {}
+        skipped_ms = 0.0
 
         def validate_now():
             """Periodic validation of the baseline trainer (train_gpt.py:964-994): the current weights on non-overlapping
@@ -441,6 +450,8 @@ class VariantRunner:
             with timers.time("train_step"), (health.guard() if health is not None else contextlib.nullcontext()):
                 loss = backend.train_step_spans(spans, scale, mom, qat) if spans is not None else backend.train_step(batches, scale, mom, qat)
             step += 1
+            if step - step0 == t.timing_skip_steps and step < max_steps:
+                skipped_ms = train_ms + 1000.0 * (self.clock() - t_start)
             if health is not None:
                 health.beat(step)
             if step == step0 + 1:
@@ -476,6 +487,11 @@ class VariantRunner:
         res.steps = step - step0
         res.train_ms = train_ms
         res.step_avg_ms = train_ms / max(res.steps, 1)
+        # the measured step time leaves out the first timing_skip_steps steps (pg-train/src/lib.rs:4129-4134, :1509-1521)
+        timed_steps = res.steps - min(t.timing_skip_steps, max(res.steps - 1, 0))
+        res.measured_ms_per_step = (train_ms - skipped_ms) / max(timed_steps, 1)
+        if not spec.allow_unsupported_variants:          # the development switch that waives the other record gates waives this one too
+            check_record_step_time(mode, res.steps, res.measured_ms_per_step, t.record_max_ms_per_step)
         res.tokens_per_s = tokens_per_step * res.steps / max(train_ms / 1000.0, 1e-9)
         if torch.cuda.is_available() and t.backend != "cpu":
             res.peak_mem_mib = torch.cuda.max_memory_allocated() // (1 << 20)

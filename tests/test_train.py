@@ -615,3 +615,33 @@ def test_qat_switches_on_for_the_last_fraction_of_the_run(tmp_path, monkeypatch)
     monkeypatch.setattr(tr.OracleBackend, "train_step", lambda self, b, scale, mom, qat: (seen.append(qat), real(self, b, scale, mom, qat))[1])
     quiet(s).run()
     assert seen == [False] * 6 + [True] * 2
+
+
+def test_record_gate_on_the_measured_step_time(tmp_path, monkeypatch):
+    """Record mode fails closed when steps are slower than train.record_max_ms_per_step; the measurement leaves out the first
+    train.timing_skip_steps steps (pg-train/src/lib.rs:1509-1521, :4129-4134)."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.train.timing_skip_steps = 1
+    s.train.artifact_path = str(tmp_path / "g.pgrs")
+    s.eval.max_tokens = 512
+    r = quiet(s)
+    now, calls = [0.0], []
+
+    def clock():
+        now[0] += 10.0 if len(calls) == 2 else 0.05           # the reading that ends the first step comes 10 s late
+        calls.append(1)
+        return now[0]
+    r.clock = clock
+    res = r.run()
+    assert res.steps == 4 and res.step_avg_ms > 2000 and res.measured_ms_per_step < 500       # the slow first step is left out
+    # the gate itself applies to record runs only
+    import parameter_golf_b200.train as tr
+    with pytest.raises(RuntimeError, match="too slow"):
+        tr.check_record_step_time("record", 100, 131.0, 130.0)
+    tr.check_record_step_time("record", 100, 129.0, 130.0)
+    tr.check_record_step_time("record", 100, 500.0, 0.0)
+    tr.check_record_step_time("record_shaped_proxy", 100, 500.0, 130.0)
+    e = family_preset("record_11l").apply_env({"PG_RECORD_MAX_MS_PER_STEP": "90", "PG_RECORD_TIMING_SKIP_STEPS": "5"})
+    assert e.train.record_max_ms_per_step == 90.0 and e.train.timing_skip_steps == 5

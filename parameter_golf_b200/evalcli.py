@@ -171,6 +171,13 @@ def main(argv=None) -> int:
     ms = 1000.0 * (time.perf_counter() - t0)
     if rank == 0:
         print(f"val_loss={loss}\nval_bpb={bpb}\neval_ms={ms:.1f}\neval_kind={kind}")
+        # the same facts under the names the reference evaluator prints (pg-eval/src/bin/run.rs:96-214)
+        print(f"eval_loss={loss}\neval_bpb={bpb}\neval_wallclock_seconds={ms / 1000.0:.3f}\neval_max_wallclock_seconds={spec.eval.max_eval_seconds}\n"
+              f"eval_status={'ok' if ms / 1000.0 <= spec.eval.max_eval_seconds or spec.eval.max_eval_seconds <= 0 else 'over_budget'}\n"
+              f"eval_stride={spec.eval.stride}\neval_tokens={int(val.shape[0] - 1)}\neval_gpu_world_size={world if a.device != 'cpu' else 0}\n"
+              f"legal_score_first={str(spec.eval.legal_score_first).lower()}\nqttt={str(spec.eval.qttt).lower()}\nlora_rank={spec.eval.lora_rank}\n"
+              f"lora_alpha={spec.eval.lora_alpha}\nphased_ttt_phases={spec.eval.phased_ttt_phases}\nvariant_fingerprint={spec.fingerprint():016x}\n"
+              f"submission_code_bytes={cb}\nsubmission_total_bytes={cb + len(blob)}")
         print("eval_audit_json=" + json.dumps({"artifact": a.artifact, "artifact_bytes": len(blob), "eval_kind": kind, "stride": spec.eval.stride,
                                                "window": m.eval_seq_len, "tokens": int(val.shape[0] - 1), "world_size": world, "bytes": a.bytes,
                                                "fingerprint": f"{spec.fingerprint():016x}", "eval_ms": round(ms, 1),

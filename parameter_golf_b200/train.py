@@ -234,11 +234,15 @@ class VariantResult:
     complementary_mean_weight: float = 1.0
     val_history: list = field(default_factory=list)      # (step, val_loss, val_bpb) of the periodic validations (train.val_loss_every)
     timers: dict = field(default_factory=dict)
+    reference_keys: dict = field(default_factory=dict)   # the same facts under the names the reference trainer prints (pg-train/src/main.rs:218-431)
 
     def key_value_lines(self) -> List[str]:
         out = []
         for k, v in self.__dict__.items():
             if isinstance(v, list):
+                continue
+            if k == "reference_keys":
+                out.extend(f"{kk}={vv}" for kk, vv in v.items())
                 continue
             if isinstance(v, dict):
                 out.extend(f"{k}.{kk}={vv}" for kk, vv in v.items())
@@ -302,6 +306,7 @@ class VariantRunner:
         device = "cpu" if t.backend == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}"
 
         # ---- data ----------------------------------------------------------------------------------
+        synthetic_data = not t.train_data_pattern
         if not t.train_data_pattern:
             root = os.path.join(os.environ.get("PGB_DATA_ROOT", "/tmp/pgb200_synth"), f"v{m.vocab_size}_s{t.seed}")
             # One writer: rank 0 generates (each shard is written to a temporary name and renamed), the others wait at a
@@ -597,6 +602,23 @@ class VariantRunner:
             res.eval_ms = 1000.0 * (time.perf_counter() - t_eval)
         log.info(f"final_{res.eval_kind}_roundtrip val_loss:{res.val_loss:.4f} val_bpb:{res.val_bpb:.4f} eval_time:{res.eval_ms:.0f}ms")
         res.timers = timers.summary()
+        tm = res.timers
+        res.reference_keys = {
+            "run_name": spec.name, "train_backend": t.backend, "variant_fingerprint": res.fingerprint, "steps_completed": res.steps,
+            "train_loss": f"{res.train_loss_last:.6f}", "train_loss_source": "last_step_mean_over_local_microbatches",
+            "ms_per_step": f"{res.measured_ms_per_step:.3f}", "wallclock_seconds": f"{res.train_ms / 1000.0:.3f}",
+            "timing_steps": max(res.steps - min(t.timing_skip_steps, max(res.steps - 1, 0)), 0), "rank": t.rank, "world_size": t.world_size,
+            "seq_len": t.seq_len, "global_batch_tokens": tokens_per_step, "tokens_seen_global": tokens_per_step * res.steps,
+            "distributed_sync": "none" if t.world_size == 1 else t.distributed_optimizer_backend,
+            "attention_backend": "autograd_reference" if t.backend == "cpu" else "native_tcgen05_flash",
+            "eval_adaptation_backend": spec.eval.adaptation_backend, "frontier_record_ready": str(not gaps).lower(),
+            "bank_update_backend": "torch" if t.backend == "cpu" else "fused_kernels",
+            "train_data_source": "shards" if not synthetic_data else "synthetic_zipf_markov",
+            "bpb_byte_source": ("caseops_sidecar" if spec.eval.caseops_byte_sidecar_pattern else "tokenizer" if spec.eval.tokenizer_vocab_path
+                                else "seeded_table"),
+            "timing_backend": "host_perf_counter" if t.backend == "cpu" else "cuda_events_max_over_ranks",
+            "timing_train_step_ms": tm.get("train_step_ms", 0.0), "timing_data_sampling_ms": tm.get("data_ms", 0.0),
+            "timing_artifact_export_ms": tm.get("export_ms", 0.0), "timing_eval_ms": tm.get("eval_ms", 0.0)}
         if t.rank == 0:
             log.raw("record_audit_json=" + json.dumps({
                 "name": spec.name, "mode": mode, "fingerprint": res.fingerprint, "backend": t.backend,

@@ -82,6 +82,9 @@ def test_eval_cli_and_leaderboard_gate(tmp_path):
     assert out.returncode == 0, out.stderr[-1500:]
     kv = dict(l.split("=", 1) for l in out.stdout.splitlines() if "=" in l and not l.startswith("eval_audit_json"))
     assert kv["eval_kind"] == "sliding" and float(kv["val_bpb"]) > 0 and "eval_audit_json=" in out.stdout
+    # and under the reference evaluator's names (pg-eval/src/bin/run.rs)
+    assert kv["eval_bpb"] == kv["val_bpb"] and kv["eval_status"] == "ok" and kv["eval_tokens"] == str(256 * 3) and kv["eval_stride"] == "64"
+    assert int(kv["submission_total_bytes"]) == int(kv["artifact_bytes"]) + int(kv["code_bytes"])
     out = subprocess.run(base + ["--leaderboard", "--bytes", "placeholder", "--max-tokens", "300"], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
     assert out.returncode == 2 and "placeholder" in out.stderr and "full validation set" in out.stderr
 

@@ -645,3 +645,19 @@ def test_record_gate_on_the_measured_step_time(tmp_path, monkeypatch):
     tr.check_record_step_time("record_shaped_proxy", 100, 500.0, 130.0)
     e = family_preset("record_11l").apply_env({"PG_RECORD_MAX_MS_PER_STEP": "90", "PG_RECORD_TIMING_SKIP_STEPS": "5"})
     assert e.train.record_max_ms_per_step == 90.0 and e.train.timing_skip_steps == 5
+
+
+def test_result_lines_also_carry_the_reference_trainers_key_names(tmp_path, monkeypatch):
+    """Scripts that parse the reference binary's ``key=value`` output (pg-train/src/main.rs:218-431) find the same names here."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.train.artifact_path = str(tmp_path / "k.pgrs")
+    s.eval.max_tokens = 512
+    res = quiet(s).run()
+    kv = dict(l.split("=", 1) for l in res.key_value_lines())
+    assert kv["run_name"] == "tiny_cpu" and kv["steps_completed"] == "4" and kv["train_backend"] == "cpu" and kv["world_size"] == "1"
+    assert kv["variant_fingerprint"] == res.fingerprint and float(kv["ms_per_step"]) > 0 and kv["timing_steps"] == "4"
+    assert int(kv["tokens_seen_global"]) == 4 * int(kv["global_batch_tokens"]) and kv["train_data_source"] == "synthetic_zipf_markov"
+    assert kv["bpb_byte_source"] == "seeded_table" and kv["timing_backend"] == "host_perf_counter" and float(kv["timing_eval_ms"]) > 0
+    assert kv["steps"] == "4" and "val_bpb" in kv                       # this framework's own names stay

@@ -269,6 +269,28 @@ def record_gaps(spec: RunSpec, mode: str) -> List[str]:
     return gaps
 
 
+def frontier_algorithm_notes(spec: RunSpec) -> List[str]:
+    """Where a spec departs from the reference's late-frontier algorithm target (``pg-train/src/lib.rs:5637-5665``): CaseOps with a
+    byte sidecar, SparseAttnGate of width 12, boundary-masked SmearGate, LQER. Informational: the audit line carries the list,
+    nothing is refused because of it (the benchmark configurations are the Python records, which predate that target)."""
+    m, notes = spec.model, []
+    if not (m.caseops.enabled and m.caseops.byte_sidecar):
+        notes.append("no CaseOps byte sidecar")
+    elif not spec.eval.caseops_byte_sidecar_pattern:
+        notes.append("CaseOps byte sidecar enabled but eval.caseops_byte_sidecar_pattern is not set")
+    if not m.sparse_attn_gate.enabled:
+        notes.append("no SparseAttnGate")
+    elif m.sparse_attn_gate.width != 12:
+        notes.append("SparseAttnGate width is not 12")
+    if not m.smear_gate:
+        notes.append("no SmearGate")
+    elif m.smear_gate_boundary_token_id is None:
+        notes.append("SmearGate is not masked at document boundaries: the previous-token mix can cross packed documents")
+    if not spec.quant.lqer.enabled:
+        notes.append("no LQER correction")
+    return notes
+
+
 def check_record_step_time(mode: str, steps: int, measured_ms_per_step: float, limit_ms: float) -> None:
     """A record run whose measured step time is above the limit is refused before export (``pg-train/src/lib.rs:1514-1521``)."""
     if mode == "record" and limit_ms > 0 and steps > 0 and measured_ms_per_step > limit_ms:
@@ -626,7 +648,7 @@ class VariantRunner:
                 "tokens_per_step": tokens_per_step, "grad_accum": accum, "seq_len": t.seq_len, "steps": res.steps,
                 "step_avg_ms": round(res.step_avg_ms, 3), "ns_profile": t.muon_ns_profile, "grad_wire_dtype": t.grad_wire_dtype,
                 "quant_scheme": spec.quant.scheme, "compression": spec.quant.compression, "artifact_bytes": res.artifact_bytes,
-                "eval_kind": res.eval_kind, "gaps": gaps, "timing_backend": "host_perf_counter" if t.backend == "cpu" else "cuda_events_max_over_ranks"}))
+                "eval_kind": res.eval_kind, "gaps": gaps, "frontier_algorithm_notes": frontier_algorithm_notes(spec), "timing_backend": "host_perf_counter" if t.backend == "cpu" else "cuda_events_max_over_ranks"}))
         return res
 
 

@@ -661,3 +661,12 @@ def test_result_lines_also_carry_the_reference_trainers_key_names(tmp_path, monk
     assert int(kv["tokens_seen_global"]) == 4 * int(kv["global_batch_tokens"]) and kv["train_data_source"] == "synthetic_zipf_markov"
     assert kv["bpb_byte_source"] == "seeded_table" and kv["timing_backend"] == "host_perf_counter" and float(kv["timing_eval_ms"]) > 0
     assert kv["steps"] == "4" and "val_bpb" in kv                       # this framework's own names stay
+
+
+def test_frontier_algorithm_notes_are_informational():
+    from parameter_golf_b200.train import frontier_algorithm_notes
+    f = family_preset("frontier_1855_like")
+    f.quant.lqer.enabled, f.eval.caseops_byte_sidecar_pattern = True, "v_bytes_*.bin"
+    assert frontier_algorithm_notes(f) == []
+    r = frontier_algorithm_notes(family_preset("record_11l"))
+    assert any("document boundaries" in n for n in r) and any("LQER" in n for n in r) and any("SparseAttnGate" in n for n in r)

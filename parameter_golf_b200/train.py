@@ -682,6 +682,7 @@ def main(argv=None) -> int:
         sp.add_argument("--fast-bank-updates", action="store_true", help="accepted for compatibility: bank updates are always fused")
         sp.add_argument("--families", default="tiny_cpu")
         sp.add_argument("--mode", default=None)
+        sp.add_argument("--log-dir", default=None, help="also write the run log to <dir>/<run name>.txt (or set PGB_LOG_DIR)")
         sp.add_argument("--env", action="store_true", help="overlay train_gpt.py environment variable names")
         sp.add_argument("--backend", default=None)
         sp.add_argument("--artifact", default=None)
@@ -729,9 +730,23 @@ def main(argv=None) -> int:
             from .plan import ExecutionPlan
             print("\n".join(ExecutionPlan.from_run_spec(spec).summary_lines()))
             continue
-        res = VariantRunner(spec).run()
+        log_dir = a.log_dir or os.environ.get("PGB_LOG_DIR")
+        run_log = RunLog(spec.name, directory=log_dir, rank=spec.train.rank)
+        if run_log.path:
+            # the file starts with what produced the run, as the Python trainer's log starts with its source and the GPU list
+            # (train_gpt.py:777-794): here the resolved spec and the environment summary
+            from .doctor import collect
+            env = collect()
+            head = ["=" * 100, spec.to_toml().rstrip(), "=" * 100] + [f"{k}={v}" for k, v in env.items() if k != "gpus"]
+            head += [f"gpu{g['index']}={g['name']} sm_{g['capability'].replace('.', '')} {g['memory_gib']}GiB" for g in env["gpus"]] + ["=" * 100]
+            with open(run_log.path, "a", encoding="utf-8") as f:
+                f.write("\n".join(head) + "\n")
+        res = VariantRunner(spec, run_log).run()
         if spec.train.rank == 0:
             print("\n".join(res.key_value_lines()))
+            if run_log.path:
+                with open(run_log.path, "a", encoding="utf-8") as f:
+                    f.write("\n".join(res.key_value_lines()) + "\n")
         rc |= 0 if (res.budget_ok or spec.mode != "record") else 1
     return rc
 

@@ -670,3 +670,13 @@ def test_frontier_algorithm_notes_are_informational():
     assert frontier_algorithm_notes(f) == []
     r = frontier_algorithm_notes(family_preset("record_11l"))
     assert any("document boundaries" in n for n in r) and any("LQER" in n for n in r) and any("SparseAttnGate" in n for n in r)
+
+
+def test_cli_log_file_starts_with_the_spec_and_the_environment(tmp_path):
+    env = dict(os.environ, PGB_DATA_ROOT=str(tmp_path / "d"), PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, "-m", "parameter_golf_b200.train", "run", "--family", "tiny_cpu", "--mode", "smoke", "--log-dir", str(tmp_path / "logs"),
+                          "--artifact", str(tmp_path / "x.pgrs")], capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    text = open(tmp_path / "logs" / "tiny_cpu.txt").read()
+    assert text.startswith("=" * 100) and 'family = "tiny_cpu"' in text and "torch=" in text and "step:4/4 train_loss:" in text
+    assert "record_audit_json=" in text and "\nval_bpb=" in text and "steps_completed=4" in text

@@ -623,6 +623,7 @@ class VariantRunner:
                 res.eval_kind = "sliding"
             res.eval_ms = 1000.0 * (time.perf_counter() - t_eval)
         log.info(f"final_{res.eval_kind}_roundtrip val_loss:{res.val_loss:.4f} val_bpb:{res.val_bpb:.4f} eval_time:{res.eval_ms:.0f}ms")
+        log.info(f"final_{res.eval_kind}_roundtrip_exact val_loss:{res.val_loss:.8f} val_bpb:{res.val_bpb:.8f}")     # train_gpt.py:1119
         res.timers = timers.summary()
         tm = res.timers
         res.reference_keys = {

@@ -250,6 +250,8 @@ class VariantResult:
                 out.append(f"{k}={v}")
         if self.steps:
             out.append(f"train_ms_per_step={self.train_ms / self.steps:.3f}")
+            # per-step derivatives of the stage totals, under the reference's naming (pg-train/src/main.rs:432-690)
+            out.extend(f"timing_{k}_per_step={v / self.steps:.3f}" for k, v in self.timers.items() if k in ("data_ms", "train_step_ms", "ema_ms"))
         return out
 
 

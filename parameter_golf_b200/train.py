@@ -717,6 +717,10 @@ def main(argv=None) -> int:
         ref = [f"{k[4:].replace('__', '.')}={v}" for k, v in vars(a).items() if k.startswith("ref_") and v is not None]
         if a.attn_out_gate:
             ref.append("model.attn_out_gate.enabled=true")
+        if a.attention_backend:                    # recorded in the spec (and so in its fingerprint), never dispatched on
+            ref.append(f"model.attention_backend={a.attention_backend.replace('-', '_')}")
+        if a.fast_bank_updates:
+            ref.append("train.fast_bank_updates=true")
         spec.apply_overrides(ref)
         if any(o.startswith("train.seq_len=") for o in ref):          # the binary's --seq-len sets the model's lengths too
             spec.model.train_seq_len = spec.model.eval_seq_len = spec.train.seq_len

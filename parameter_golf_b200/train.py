@@ -717,7 +717,9 @@ def main(argv=None) -> int:
         ref = [f"{k[4:].replace('__', '.')}={v}" for k, v in vars(a).items() if k.startswith("ref_") and v is not None]
         if a.attn_out_gate:
             ref.append("model.attn_out_gate.enabled=true")
-        if a.attention_backend:                    # recorded in the spec (and so in its fingerprint), never dispatched on
+        if a.attention_backend and a.attention_backend.replace("-", "_") in ("native", "naive_f32", "flash_f32", "cudnn_sdpa_bf16"):
+            # recorded in the spec (and so in its fingerprint), never dispatched on; other spellings are ignored, as the reference's
+            # parser does (pg-train/src/main.rs:981-988)
             ref.append(f"model.attention_backend={a.attention_backend.replace('-', '_')}")
         if a.fast_bank_updates:
             ref.append("train.fast_bank_updates=true")

@@ -236,6 +236,62 @@ def export_shards(docs: Iterable[str], tok: Tokenizer, out_dir: str, num_val_doc
     return stats
 
 
+def tokenizer_kind(spec: dict) -> str:
+    """``byte`` or ``sentencepiece_bpe`` for an entry of a tokenizer config (the rules of data/download_hf_docs_and_tokenize.py:192-214:
+    an explicit ``kind``, the ``byte260`` dataset suffix, else a ``vocab_size`` means SentencePiece BPE)."""
+    kind = spec.get("kind")
+    if kind in ("byte", "pure_byte") or str(spec.get("builder", "")).endswith("build_pure_byte_tokenizer") or spec.get("dataset_suffix") == "byte260":
+        return "byte"
+    if kind in ("sentencepiece_bpe", "sentencepiece") or str(spec.get("builder", "")).endswith("build_sentencepiece_tokenizer") or "vocab_size" in spec:
+        return "sentencepiece_bpe"
+    raise ValueError(f"unsupported tokenizer spec {spec.get('name', '<unnamed>')!r}: expected a pure-byte or SentencePiece BPE entry")
+
+
+def export_from_config(docs_path: str, output_root: str, config_path: str, val_docs: int = 1000, shard_tokens: int = 10 ** 8,
+                       tokenizer_train_docs: Optional[int] = None, append_eos: bool = False) -> dict:
+    """One dataset per entry of a tokenizer config file (``{"tokenizers": [{"name", "dataset_suffix", "vocab_size"}, ...]}``, the
+    format of the reference's data/tokenizer_specs.json), in its directory layout: ``<root>/tokenizers/`` for the models,
+    ``<root>/datasets/fineweb10B_<suffix>/`` for the shards, ``<root>/manifest.json`` listing both
+    (data/download_hf_docs_and_tokenize.py:578-622)."""
+    with open(config_path, encoding="utf-8") as fh:
+        payload = json.load(fh)
+    specs = payload.get("tokenizer_specs", payload.get("tokenizers")) if isinstance(payload, dict) else payload
+    if not isinstance(specs, list) or not specs or not all(isinstance(x, dict) for x in specs):
+        raise ValueError("the tokenizer config must hold a non-empty list of objects")
+    manifest = {"version": 1, "num_val_docs": val_docs, "shard_size": shard_tokens, "append_eos": append_eos, "docs": os.path.basename(docs_path),
+                "tokenizer_specs": specs, "tokenizers": [], "datasets": []}
+    for spec in specs:
+        kind = tokenizer_kind(spec)
+        suffix = spec.get("dataset_suffix") or ("byte260" if kind == "byte" else f"sp{int(spec['vocab_size'])}")
+        name = spec.get("name") or ("pure_byte_260" if kind == "byte" else f"sp_bpe_{int(spec['vocab_size'])}")
+        if kind == "byte":
+            tok = ByteTokenizer().as_tokenizer()
+            tok_manifest = {"name": name, "kind": kind, "vocab_size": tok.vocab_size}
+        else:
+            vocab = int(spec["vocab_size"])
+            model = train_sentencepiece(iter_documents(docs_path), vocab, os.path.join(output_root, "tokenizers", f"fineweb_{vocab}_bpe"),
+                                        max_docs=spec.get("tokenizer_train_docs", tokenizer_train_docs))
+            tok = load_sentencepiece(model)
+            tok_manifest = {"name": name, "kind": kind, "vocab_size": vocab, "model_path": os.path.relpath(model, output_root),
+                            "vocab_path": os.path.relpath(os.path.splitext(model)[0] + ".vocab", output_root)}
+        out_dir = os.path.join(output_root, "datasets", f"fineweb10B_{suffix}")
+        stats = export_shards(iter_documents(docs_path), tok, out_dir, val_docs, shard_tokens, append_eos)
+        rel = os.path.relpath(out_dir, output_root)
+        manifest["tokenizers"].append(tok_manifest)
+        manifest["datasets"].append({"name": f"fineweb10B_{suffix}", "tokenizer_name": name, "tokenizer_kind": kind, "path": rel,
+                                     "train_glob": os.path.join(rel, "fineweb_train_*.bin"), "val_glob": os.path.join(rel, "fineweb_val_[0-9]*.bin"),
+                                     "val_bytes_glob": os.path.join(rel, "fineweb_val_bytes_*.bin"), "vocab_size": tok.vocab_size, "bos_id": tok.bos_id,
+                                     "eos_id": tok.eos_id, "stats": stats})
+    os.makedirs(output_root, exist_ok=True)
+    with open(os.path.join(output_root, "manifest.json"), "w", encoding="utf-8") as fh:
+        json.dump(manifest, fh, indent=2)
+        fh.write("\n")
+    with open(os.path.join(output_root, "tokenizer_config.export.json"), "w", encoding="utf-8") as fh:
+        json.dump({"tokenizers": specs}, fh, indent=2)
+        fh.write("\n")
+    return manifest
+
+
 def _main(argv=None) -> int:
     import argparse
     ap = argparse.ArgumentParser(prog="parameter_golf_b200.data.text_shards")
@@ -247,7 +303,14 @@ def _main(argv=None) -> int:
     ap.add_argument("--val-docs", type=int, default=1000)
     ap.add_argument("--shard-tokens", type=int, default=10 ** 8)
     ap.add_argument("--append-eos", action="store_true")
+    ap.add_argument("--tokenizer-config", default=None,
+                    help="JSON list of tokenizers ({'tokenizers': [{'name', 'dataset_suffix', 'vocab_size'}]}): one dataset per entry under "
+                         "<out>/datasets/fineweb10B_<suffix>/, models under <out>/tokenizers/, <out>/manifest.json")
     a = ap.parse_args(argv)
+    if a.tokenizer_config:
+        man = export_from_config(a.docs, a.out, a.tokenizer_config, a.val_docs, a.shard_tokens, a.tokenizer_train_docs, a.append_eos)
+        print(json.dumps({"datasets": [d["name"] for d in man["datasets"]], "manifest": os.path.join(a.out, "manifest.json")}))
+        return 0
     if a.tokenizer == "bytes":
         tok = ByteTokenizer().as_tokenizer()
     else:

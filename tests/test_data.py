@@ -296,3 +296,29 @@ def test_byte_tokenizer_export_and_the_vocabulary_guard(tmp_path):
         T.export_shards(["x"], bad, str(tmp_path / "c"))
     assert T._main(["--docs", str(txt), "--out", str(tmp_path / "cli"), "--tokenizer", "bytes", "--val-docs", "1", "--shard-tokens", "64"]) == 0
     assert (tmp_path / "cli" / "fineweb_train_000000.bin").exists()
+
+
+def test_export_from_a_tokenizer_config_uses_the_reference_layout(tmp_path):
+    """A tokenizer config in the format of the reference's data/tokenizer_specs.json: one dataset per entry under
+    datasets/fineweb10B_<suffix>/, tokenizer models under tokenizers/, a manifest listing both."""
+    import json
+    from parameter_golf_b200.data import text_shards as T
+    jl = tmp_path / "docs.jsonl"
+    jl.write_text("\n".join(json.dumps({"text": d}) for d in _corpus(200)) + "\n")
+    cfg = tmp_path / "specs.json"
+    cfg.write_text(json.dumps({"tokenizers": [{"name": "sp_bpe_320", "dataset_suffix": "sp320", "vocab_size": 320},
+                                              {"name": "pure_byte_260", "dataset_suffix": "byte260", "kind": "byte"}]}))
+    assert T._main(["--docs", str(jl), "--out", str(tmp_path / "root"), "--tokenizer-config", str(cfg), "--val-docs", "20", "--shard-tokens", "5000"]) == 0
+    root = tmp_path / "root"
+    man = json.load(open(root / "manifest.json"))
+    assert [d["name"] for d in man["datasets"]] == ["fineweb10B_sp320", "fineweb10B_byte260"]
+    assert [t["kind"] for t in man["tokenizers"]] == ["sentencepiece_bpe", "byte"] and man["tokenizers"][0]["model_path"] == "tokenizers/fineweb_320_bpe.model"
+    assert (root / "tokenizers" / "fineweb_320_bpe.model").exists() and (root / "tokenizer_config.export.json").exists()
+    for d in man["datasets"]:
+        assert d["stats"]["docs_val"] == 20 and d["stats"]["docs_train"] == 180
+        toks = S.load_validation_tokens(str(root / d["val_glob"]), 8)
+        assert int(toks.max()) < d["vocab_size"] and toks[0] == d["bos_id"]
+        assert len(list((root / d["path"]).glob("fineweb_train_*.bin"))) >= 1
+    assert T.tokenizer_kind({"vocab_size": 1024}) == "sentencepiece_bpe" and T.tokenizer_kind({"dataset_suffix": "byte260"}) == "byte"
+    with pytest.raises(ValueError):
+        T.tokenizer_kind({"name": "x"})

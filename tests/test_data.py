@@ -322,3 +322,36 @@ def test_export_from_a_tokenizer_config_uses_the_reference_layout(tmp_path):
     assert T.tokenizer_kind({"vocab_size": 1024}) == "sentencepiece_bpe" and T.tokenizer_kind({"dataset_suffix": "byte260"}) == "byte"
     with pytest.raises(ValueError):
         T.tokenizer_kind({"name": "x"})
+
+
+def test_fetch_from_a_local_mirror_follows_the_manifest(tmp_path):
+    """export (tokenizer config) -> mirror -> fetch: the validation split with its sidecars, the first N training shards and the
+    tokenizer files land under the destination; a second call writes nothing; asking for more shards than exist is refused."""
+    import json
+    from parameter_golf_b200.data import fetch_cached as F
+    from parameter_golf_b200.data import text_shards as T
+    jl = tmp_path / "docs.jsonl"
+    jl.write_text("\n".join(json.dumps({"text": d}) for d in _corpus(300)) + "\n")
+    cfg = tmp_path / "specs.json"
+    cfg.write_text(json.dumps({"tokenizers": [{"name": "sp_bpe_320", "dataset_suffix": "sp320", "vocab_size": 320}]}))
+    mirror = tmp_path / "mirror"
+    T.export_from_config(str(jl), str(mirror), str(cfg), val_docs=20, shard_tokens=1500)
+    have = json.load(open(mirror / "manifest.json"))["datasets"][0]["stats"]["files_train"]
+    assert have >= 3
+    dest = tmp_path / "data"
+    assert F.main(["--source", str(mirror), "--dest", str(dest), "--variant", "sp320", "--train-shards", "2"]) == 0
+    got = sorted(p.name for p in (dest / "datasets" / "fineweb10B_sp320").iterdir())
+    assert [g for g in got if "train" in g] == ["fineweb_train_000000.bin", "fineweb_train_000001.bin"]
+    assert any(g.startswith("fineweb_val_bytes_") for g in got) and any(g.startswith("fineweb_val_0") for g in got)
+    assert (dest / "tokenizers" / "fineweb_320_bpe.model").exists() and (dest / "manifest.json").exists()
+    out = F.fetch_variant(F.local_getter(str(mirror)), str(dest), "sp320", 3)
+    assert out["written"] == ["datasets/fineweb10B_sp320/fineweb_train_000002.bin"]           # only what was missing
+    assert F.fetch_variant(F.local_getter(str(mirror)), str(dest), "sp320", 3)["written"] == []
+    toks = S.load_validation_tokens(str(dest / "datasets" / "fineweb10B_sp320" / "fineweb_val_*.bin"), 8)
+    assert toks[0] == 1 and int(toks.max()) < 320
+    with pytest.raises(ValueError, match="training shards"):
+        F.fetch_variant(F.local_getter(str(mirror)), str(dest), "sp320", have + 1)
+    with pytest.raises(ValueError):
+        F.dataset_dir_for_variant("gpt2")
+    with pytest.raises(ValueError, match="not in the manifest"):
+        F.fetch_variant(F.local_getter(str(mirror)), str(dest), "sp1024", 1)

@@ -186,3 +186,90 @@ def compare_step_dumps(a: Dict[str, torch.Tensor], b: Dict[str, torch.Tensor]) -
         if rel > rep.worst_grad_rel:
             rep.worst_grad_rel, rep.worst_grad_name = rel, k
     return rep
+
+
+# ---- command line: the parity workflow between a PyTorch script and this framework ------------------------------------------------
+def dump_step(spec, params: Dict[str, torch.Tensor], ids: torch.Tensor, targets: torch.Tensor, python_names: bool = False) -> Dict[str, torch.Tensor]:
+    """``{"loss", "grad.<name>"...}`` of one forward+backward of the autograd model in fp32 (the step dump the parity report
+    compares, pg-compat/src/loader.rs:230-360). With ``python_names`` the gradients are keyed as the Python records name their
+    parameters, so the dump lines up with one written from ``model.named_parameters()``."""
+    from ..models.runner import OracleRunner
+    loss, grads = OracleRunner(spec.model, {k: v.float() for k, v in params.items()}).loss_and_grads(ids, targets)
+    if python_names:
+        grads = to_python_state_dict(spec.model, grads)
+    out = {"loss": loss.reshape(1).float()}
+    out.update({f"grad.{k}": v.float().contiguous() for k, v in grads.items()})
+    return out
+
+
+def main(argv=None) -> int:
+    """``python -m parameter_golf_b200.utils.interop <command>``:
+
+    * ``import --family F --state model.safetensors --artifact out.pgrs``: a Python-record ``state_dict`` to a quantised artifact;
+    * ``export --family F --artifact a.pgrs --state out.safetensors``: an artifact's (de-quantised) weights under the Python names;
+    * ``dump-step --family F --state model.safetensors --tokens t.bin --out step.safetensors [--python-names]``: loss and gradients
+      of one step on the first ``batch x (seq + 1)`` tokens of a shard;
+    * ``compare a.safetensors b.safetensors``: the parity report (loss |a - b| <= 1e-3, worst gradient relative error <= 0.02);
+      exit code 1 when it fails."""
+    import argparse
+    import sys
+    ap = argparse.ArgumentParser(prog="parameter_golf_b200.utils.interop")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    for name in ("import", "export", "dump-step"):
+        p = sub.add_parser(name)
+        p.add_argument("--family", default="record_11l")
+        p.add_argument("--spec")
+        p.add_argument("--state", required=True)
+        p.add_argument("overrides", nargs="*")
+        if name != "dump-step":
+            p.add_argument("--artifact", required=True)
+        else:
+            p.add_argument("--tokens", required=True)
+            p.add_argument("--out", required=True)
+            p.add_argument("--batch", type=int, default=2)
+            p.add_argument("--seq-len", type=int, default=0)
+            p.add_argument("--python-names", action="store_true")
+    p = sub.add_parser("compare")
+    p.add_argument("a")
+    p.add_argument("b")
+    a = ap.parse_args(argv)
+    if a.cmd == "compare":
+        rep = compare_step_dumps(read_safetensors(a.a), read_safetensors(a.b))
+        print(f"loss_diff={rep.loss_diff:.3e}\nworst_grad_rel={rep.worst_grad_rel:.3e}\nworst_grad_name={rep.worst_grad_name}\n"
+              f"missing={','.join(rep.missing)}\nloss_atol={LOSS_ATOL}\ngrad_max_rel={GRAD_MAX_REL}\nparity_ok={str(rep.ok).lower()}")
+        for k, v in sorted(rep.per_tensor.items(), key=lambda kv: -kv[1])[:10]:
+            print(f"rel.{k}={v:.3e}")
+        return 0 if rep.ok else 1
+    from ..spec import RunSpec, family_preset
+    spec = RunSpec.load(a.spec) if a.spec else family_preset(a.family)
+    spec.apply_overrides(a.overrides)
+    spec.validate()
+    if a.cmd == "import":
+        from ..quant.export import export_model
+        params = from_python_state_dict(spec.model, read_safetensors(a.state))
+        blob = export_model(spec, params, a.artifact)
+        print(f"artifact_bytes={len(blob)}\nvariant_fingerprint={spec.fingerprint():016x}")
+    elif a.cmd == "export":
+        from ..quant.export import load_artifact
+        with open(a.artifact, "rb") as fh:
+            params = load_artifact(fh.read(), spec)
+        sd = to_python_state_dict(spec.model, params)
+        write_safetensors(a.state, {k: v.float().contiguous() for k, v in sd.items()}, {"variant_fingerprint": f"{spec.fingerprint():016x}"})
+        print(f"tensors={len(sd)}")
+    else:
+        from ..data.shards import open_shard
+        params = from_python_state_dict(spec.model, read_safetensors(a.state))
+        S = a.seq_len or spec.model.train_seq_len
+        toks = torch.from_numpy(np.asarray(open_shard(a.tokens)[: a.batch * S + 1]).astype(np.int64))
+        if toks.numel() < a.batch * S + 1:
+            print(f"the shard holds {toks.numel()} tokens, {a.batch * S + 1} are needed", file=sys.stderr)
+            return 2
+        ids, tgt = toks[:-1].reshape(a.batch, S), toks[1:].reshape(a.batch, S)
+        dump = dump_step(spec, params, ids, tgt, a.python_names)
+        write_safetensors(a.out, dump, {"tokens": str(a.batch * S)})
+        print(f"loss={float(dump['loss']):.6f}\ntensors={len(dump)}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

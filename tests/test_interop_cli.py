@@ -221,3 +221,33 @@ def test_leaderboard_rules_follow_the_reference_binary():
     assert leaderboard_violations(h, args) == []
     args.bytes = "tokenizer"
     assert any("tokenizer-vocab" in b for b in leaderboard_violations(family_preset("baseline_sp8192"), args))
+
+
+def test_interop_command_line_round_trip_and_parity_report(tmp_path, capsys):
+    """state_dict (Python names) -> artifact -> state_dict; a step dump compared with itself passes, with a perturbed copy fails."""
+    from parameter_golf_b200.data.shards import write_shard
+    from parameter_golf_b200.utils import interop as I
+    s = family_preset("tiny_cpu")
+    p = gpt.init_params(s.model, 4)
+    p["qo_bank"][s.model.num_layers:] = torch.randn_like(p["qo_bank"][s.model.num_layers:]) * 0.05
+    p["mlp_down_bank"] = torch.randn_like(p["mlp_down_bank"]) * 0.05
+    state = str(tmp_path / "model.safetensors")
+    I.write_safetensors(state, {k: v.contiguous() for k, v in I.to_python_state_dict(s.model, p).items()})
+    art, back = str(tmp_path / "m.pgrs"), str(tmp_path / "back.safetensors")
+    assert I.main(["import", "--family", "tiny_cpu", "--state", state, "--artifact", art, "quant.prune_to_target=false"]) == 0
+    assert I.main(["export", "--family", "tiny_cpu", "--artifact", art, "--state", back]) == 0
+    rt = I.from_python_state_dict(s.model, I.read_safetensors(back))
+    assert float((rt["kv_bank"] - p["kv_bank"]).abs().max()) < float(p["kv_bank"].abs().max()) / 20          # int6 round trip
+    write_shard(str(tmp_path / "t.bin"), np.random.default_rng(0).integers(0, 1024, 2 * 64 + 1).astype(np.uint16))
+    d1, d2 = str(tmp_path / "a.safetensors"), str(tmp_path / "b.safetensors")
+    args = ["dump-step", "--family", "tiny_cpu", "--state", state, "--tokens", str(tmp_path / "t.bin"), "--batch", "2", "--seq-len", "64", "--python-names"]
+    assert I.main(args + ["--out", d1]) == 0 and I.main(args + ["--out", d2]) == 0
+    dump = I.read_safetensors(d1)
+    assert "grad.blocks.0.attn.q_gain" in dump and "grad.tok_emb.weight" in dump and float(dump["loss"]) > 0
+    capsys.readouterr()
+    assert I.main(["compare", d1, d2]) == 0 and "parity_ok=true" in capsys.readouterr().out
+    dump["grad.qo_bank"] = dump["grad.qo_bank"] * 1.05
+    I.write_safetensors(d2, dump)
+    assert I.main(["compare", d1, d2]) == 1
+    out = capsys.readouterr().out
+    assert "parity_ok=false" in out and "worst_grad_name=grad.qo_bank" in out

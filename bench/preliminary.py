@@ -94,8 +94,12 @@ def arch_sweep():
     print("== 3. architecture families: parameters, estimated artifact bytes, engine memory for one record micro-batch")
     print(f"{'family':>28} {'params':>12} {'int6 MB':>9} {'int5/6 MB':>10} {'fits':>5} {'engine GiB @98,304 tok':>23}   (ternary / binary families: their own scheme before xz in both columns; xz takes a few percent off the scales and codes)")
     rows = []
-    for fam in FAMILIES:
-        s = family_preset(fam)
+    from parameter_golf_b200.spec import ARCH_VARIANTS, arch_label, arch_variant
+    # the families, then the reference's ten sweep architectures (pg-bench/src/bin/preliminary.rs:247-290, pg-model/src/arch.rs:137-168)
+    for fam in list(FAMILIES) + [f"arch:{k}" for k in ARCH_VARIANTS]:
+        s = arch_variant(fam[5:]) if fam.startswith("arch:") else family_preset(fam)
+        if fam.startswith("arch:"):
+            fam = arch_label(fam[5:])
         m = s.model
         shapes = gpt.param_shapes(m)
         n_params = gpt.count_params(m)

@@ -875,6 +875,49 @@ def family_preset(family: str) -> RunSpec:
     return s
 
 
+# The ten architectures of the reference's sweep (pg-model/src/arch.rs:137-168), as
+# (model_dim, heads, kv_heads, layers, mlp_mult, rope_dims, first XSA layer, seq_len) over its "sota" base configuration
+# (pg-model/src/config.rs:60-110: vocabulary 1024, BigramHash 1536 x 128, value embeddings on blocks 9 and 10, boundary-masked SmearGate).
+ARCH_VARIANTS = {
+    "baseline": (512, 8, 4, 11, 3, 16, 7, 2048),
+    "wide": (576, 8, 4, 11, 3, 16, 7, 2048),                  # head_dim 72
+    "wide_narrow_mlp": (576, 8, 4, 11, 2, 16, 7, 2048),
+    "deep": (512, 8, 4, 13, 3, 16, 9, 2048),
+    "deep_narrow": (384, 6, 3, 16, 3, 12, 12, 2048),
+    "full_xsa": (512, 8, 4, 11, 3, 16, 0, 2048),
+    "more_rope": (512, 8, 4, 11, 3, 32, 7, 2048),
+    "high_gqa": (480, 12, 3, 11, 3, 16, 7, 2048),             # head_dim 40
+    "long_ctx": (512, 8, 4, 11, 3, 16, 7, 4096),
+    "aggressive_quant": (640, 8, 4, 11, 3, 16, 7, 2048),      # fits 16 MB only at int4
+}
+
+
+def arch_label(name: str) -> str:
+    d, h, kv, n, mm, rd, xf, sl = ARCH_VARIANTS[name]
+    return f"d{d}_h{h}_kv{kv}_L{n}_m{mm}_r{rd}_x{xf}_s{sl}"
+
+
+def arch_variant(name: str) -> RunSpec:
+    """The run spec of one sweep architecture: the record stack with the eight numbers of `ARCH_VARIANTS` put in. Widths whose
+    head_dim is not 64 (wide, high_gqa) run on the autograd path; the CUDA engine's attention kernels are written for 64."""
+    if name not in ARCH_VARIANTS:
+        raise ValueError(f"unknown architecture {name!r}; known: {tuple(ARCH_VARIANTS)}")
+    d, h, kv, n, mm, rd, xf, sl = ARCH_VARIANTS[name]
+    s = family_preset("record_11l")
+    s.name = f"arch_{name}"
+    m = s.model
+    m.vocab_size, m.model_dim, m.num_heads, m.num_kv_heads, m.num_layers, m.mlp_mult = 1024, d, h, kv, n, float(mm)
+    m.rope = RopeSpec("partial", rd, 10000.0)
+    m.xsa_last_n = 0 if xf >= n else n - xf
+    m.train_seq_len = m.eval_seq_len = s.train.seq_len = sl
+    m.bigram = BigramSpec(True, 1536, 128)
+    m.value_embedding = ValueEmbeddingSpec(True, 128, [9, 10])
+    m.smear_gate, m.smear_gate_boundary_token_id, m.ln_scale, m.qk_gain_init = True, 1, True, 1.5
+    if m.head_dim != 64 or rd % 16:          # shapes the CUDA kernels are not written (or not tested) for
+        s.train.backend, s.train.distributed_optimizer_backend = "cpu", "all_reduce_replicated_muon"
+    return s
+
+
 # ---- helpers --------------------------------------------------------------------------------------
 
 def _field_type(obj, name):

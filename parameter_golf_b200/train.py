@@ -685,6 +685,7 @@ def main(argv=None) -> int:
         sp.add_argument("--fast-bank-updates", action="store_true", help="accepted for compatibility: bank updates are always fused")
         sp.add_argument("--families", default="tiny_cpu")
         sp.add_argument("--mode", default=None)
+        sp.add_argument("--arch", default=None, help="one of the sweep architectures (spec.ARCH_VARIANTS) instead of a family")
         sp.add_argument("--log-dir", default=None, help="also write the run log to <dir>/<run name>.txt (or set PGB_LOG_DIR)")
         sp.add_argument("--env", action="store_true", help="overlay train_gpt.py environment variable names")
         sp.add_argument("--backend", default=None)
@@ -705,7 +706,11 @@ def main(argv=None) -> int:
     fams = [a.family] if (a.cmd != "sweep" and a.family) else ([None] if a.cmd != "sweep" else a.families.split(","))
     rc = 0
     for fam in fams:
-        spec = RunSpec.load(a.spec) if a.spec else family_preset(fam or "tiny_cpu")
+        if a.arch:
+            from .spec import arch_variant
+            spec = arch_variant(a.arch)
+        else:
+            spec = RunSpec.load(a.spec) if a.spec else family_preset(fam or "tiny_cpu")
         if a.env:
             spec.apply_env()
         if "RANK" in os.environ:

@@ -239,3 +239,23 @@ def test_keys_subcommand_prints_every_key(capsys):
     assert main(["keys"]) == 0
     out = capsys.readouterr().out
     assert "model.num_layers (int) = 11  env NUM_LAYERS" in out and "train.seq_len (int) = 2048  env TRAIN_SEQ_LEN  flag --seq-len" in out
+
+
+def test_sweep_architectures_match_the_reference_table():
+    """pg-model/src/arch.rs:137-168 and its tests (:46-85): baseline = 512 x 11 x 3 with XSA on the last four; wide has head_dim 72
+    and kv_dim 288; full XSA covers all 11; deep-narrow is 16 x 384 with head_dim 64 and four XSA layers."""
+    from parameter_golf_b200.spec import ARCH_VARIANTS, arch_label, arch_variant
+    assert len(ARCH_VARIANTS) == 10
+    b = arch_variant("baseline").validate().model
+    assert (b.model_dim, b.num_layers, b.mlp_dim, b.rope_dims, b.xsa_last_n, b.train_seq_len, b.vocab_size) == (512, 11, 1536, 16, 4, 2048, 1024)
+    w = arch_variant("wide").validate()
+    assert w.model.head_dim == 72 and w.model.kv_dim == 288 and w.train.backend == "cpu"
+    assert arch_variant("full_xsa").model.xsa_last_n == 11
+    dn = arch_variant("deep_narrow").validate().model
+    assert (dn.num_layers, dn.model_dim, dn.head_dim, dn.xsa_last_n, dn.rope_dims) == (16, 384, 64, 4, 12)
+    assert arch_variant("long_ctx").train.seq_len == 4096 and arch_variant("high_gqa").model.head_dim == 40
+    assert arch_label("baseline") == "d512_h8_kv4_L11_m3_r16_x7_s2048"
+    with pytest.raises(ValueError):
+        arch_variant("nope")
+    for k in ARCH_VARIANTS:
+        arch_variant(k).validate()

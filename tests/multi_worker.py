@@ -127,7 +127,11 @@ def main():
         dist.barrier()
         if be.dist is not None:
             be.dist.close()
-    print("RESULT", rank, json.dumps(out), flush=True)
+    line = f"RESULT {rank} {json.dumps(out)}"
+    if os.environ.get("PGB_RESULT_DIR"):                      # a file per rank: lines of several ranks can interleave on a shared stdout
+        with open(os.path.join(os.environ["PGB_RESULT_DIR"], f"result_{rank}.txt"), "w") as fh:
+            fh.write(line + "\n")
+    print(line, flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -17,16 +17,25 @@ def run_workers(mode, nproc=2, port=29731):
         port = free_port()
     except Exception:
         pass
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    import tempfile
+    result_dir = tempfile.mkdtemp(prefix="pgb_multi_")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, PGB_RESULT_DIR=result_dir)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "tests", "multi_worker.py"), mode]
     out = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
     assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-3000:])
     res = {}
-    for line in out.stdout.splitlines():
+    lines = out.stdout.splitlines()
+    for name in sorted(os.listdir(result_dir)):               # the per-rank files first, stdout lines as the fallback
+        with open(os.path.join(result_dir, name)) as fh:
+            lines = fh.read().splitlines() + lines
+    for line in lines:
         if line.startswith("RESULT"):
-            _, rank, payload = line.split(" ", 2)
-            res[int(rank)] = json.loads(payload)
+            try:
+                _, rank, payload = line.split(" ", 2)
+                res.setdefault(int(rank), json.loads(payload))
+            except ValueError:                                # an interleaved stdout line; the rank's file has the clean copy
+                pass
     assert len(res) == nproc
     return res
 

@@ -68,6 +68,24 @@ def quant_sweep():
         rows.append({"attn_bits": a, "mlp_bits": m_, "embed_bits": e, "packed_bytes": tot_p, "zstd_bytes": tot_z, "attn_mse": mse["attn"],
                      "mlp_mse": mse["mlp"], "fits": tot_z <= BUDGET})
         print(f"{a:>5} {m_:>4} {e:>4} {tot_p / 1e6:>10.2f} {tot_z / 1e6:>11.2f} {mse['attn']:>10.3e} {mse['mlp']:>10.3e} {str(tot_z <= BUDGET):>10}")
+    # the group-scaled low-bit schemes of the 2026-03-24 submissions on the same matrices: codes + one fp16 scale per 128 columns, xz
+    import lzma
+    from parameter_golf_b200.quant import binary as B1
+    from parameter_golf_b200.quant import ternary as T3
+    for label, quant, deq, pack in (("ternary", T3.quantize_ternary, T3.dequantize_ternary, T3.pack_trits),
+                                    ("binary", B1.quantize_binary, B1.dequantize_binary, B1.pack_signs)):
+        tot_p = tot_z = 0
+        mse = {}
+        for name in ("attn", "mlp"):
+            q, sc = quant(mats[name], 128)
+            raw = pack(q.numpy()) + sc.half().numpy().tobytes()
+            tot_p += len(raw) * counts[name]
+            tot_z += len(lzma.compress(raw, preset=9)) * counts[name]
+            mse[name] = float((mats[name] - deq(q, sc.half().float(), 128)).pow(2).mean())
+        emb = cache[("embed", 8)]
+        tot_p, tot_z = tot_p + emb[0], tot_z + emb[1]
+        rows.append({"scheme": label, "packed_bytes": tot_p, "xz_bytes": tot_z, "attn_mse": mse["attn"], "mlp_mse": mse["mlp"], "fits": tot_z <= BUDGET})
+        print(f"{label:>14} {tot_p / 1e6:>10.2f} {tot_z / 1e6:>11.2f} {mse['attn']:>10.3e} {mse['mlp']:>10.3e} {str(tot_z <= BUDGET):>10}   (xz instead of zstd)")
     return rows
 
 

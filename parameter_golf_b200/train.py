@@ -22,7 +22,7 @@ import os
 import sys
 import time
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional
+from typing import Callable, Dict, List, Optional, Tuple
 
 import numpy as np
 import torch
@@ -291,6 +291,81 @@ def frontier_algorithm_notes(spec: RunSpec) -> List[str]:
     if not spec.quant.lqer.enabled:
         notes.append("no LQER correction")
     return notes
+
+
+def preflight(spec: RunSpec) -> Tuple[List[str], bool]:
+    """``(key=value lines, ok)``: what can be verified about a run before any process group or device exists, for every rank at once
+    (the reference keeps a metadata-only communicator so that its CPU build can do this per-rank data check,
+    pg-core/src/nccl.rs:125-134, pg-train/src/lib.rs:879-886): spec validation and record gates, the training and validation
+    shards (headers, token counts, how often the run would wrap around its data, per-rank span arithmetic), tokenizer and byte
+    sidecar, the engine's memory estimate against one GPU, the artifact directory and the counted code size."""
+    import glob as _glob
+    from .data.shards import is_byte_sidecar_path, read_shard_header
+    out, problems = [], []
+    t, m, e = spec.train, spec.model, spec.eval
+    try:
+        spec.validate()
+    except ValueError as exc:
+        problems.append(str(exc))
+    gaps = record_gaps(spec, spec.mode)
+    out.append(f"preflight.mode={spec.mode}")
+    out.append(f"preflight.record_gaps={json.dumps(gaps)}")
+    if gaps and not spec.allow_unsupported_variants:
+        problems.append("record gates: " + "; ".join(gaps))
+    tokens_per_step, accum = step_batch_plan(spec, spec.mode)
+    steps = mode_max_steps(spec, spec.mode)
+    world = max(t.world_size, 1)
+    if tokens_per_step % (world * accum * t.seq_len):
+        problems.append(f"{tokens_per_step} tokens per step do not split into whole sequences of {t.seq_len} over {world} ranks x {accum} micro-batches")
+    out += [f"preflight.tokens_per_step={tokens_per_step}", f"preflight.grad_accum={accum}", f"preflight.steps={steps}",
+            f"preflight.local_sequences_per_micro_batch={tokens_per_step // max(world * accum * t.seq_len, 1)}"]
+    for kind, pattern in (("train", t.train_data_pattern), ("val", t.validation_data_pattern)):
+        if not pattern:
+            out.append(f"preflight.{kind}_data=synthetic (generated by rank 0 at start-up)")
+            continue
+        files = sorted(f for f in _glob.glob(pattern) if not is_byte_sidecar_path(f))
+        total = 0
+        for f in files:
+            try:
+                total += read_shard_header(f)
+            except Exception as exc:            # noqa: BLE001 - every bad shard is reported
+                problems.append(f"{f}: {exc}")
+        out += [f"preflight.{kind}_shards={len(files)}", f"preflight.{kind}_tokens={total}"]
+        if not files:
+            problems.append(f"no {kind} shard matches {pattern!r}")
+        elif kind == "train":
+            need = steps * (tokens_per_step + world * accum)          # every rank and micro-batch reads one token more than it trains on
+            out += [f"preflight.train_tokens_needed={need}", f"preflight.train_data_passes={need / max(total, 1):.3f}"]
+            if total < tokens_per_step + world * accum:
+                problems.append(f"the training shards hold {total} tokens, one step needs {tokens_per_step + world * accum}")
+        elif total < m.eval_seq_len + 1:
+            problems.append(f"the validation shards hold {total} tokens, one window needs {m.eval_seq_len + 1}")
+    if e.tokenizer_vocab_path and not os.path.isfile(e.tokenizer_vocab_path):
+        problems.append(f"eval.tokenizer_vocab_path {e.tokenizer_vocab_path!r} does not exist")
+    if e.caseops_byte_sidecar_pattern:
+        side = sorted(_glob.glob(e.caseops_byte_sidecar_pattern))
+        out.append(f"preflight.byte_sidecar_shards={len(side)}")
+        if not side:
+            problems.append(f"no byte sidecar matches {e.caseops_byte_sidecar_pattern!r}")
+    if t.backend != "cpu" and not problems:
+        from .plan import HBM_BYTES_B200, estimate_engine_memory
+        mem = estimate_engine_memory(spec, tokens_per_step // (world * accum)).total
+        out.append(f"preflight.engine_memory_gib={mem / 2 ** 30:.2f}")
+        if mem > 0.95 * HBM_BYTES_B200:
+            problems.append(f"the engine's buffers are estimated at {mem / 2 ** 30:.1f} GiB, more than one GPU holds")
+    art_dir = os.path.dirname(os.path.abspath(t.artifact_path))
+    probe = art_dir
+    while not os.path.isdir(probe):
+        probe = os.path.dirname(probe)
+    if not os.access(probe, os.W_OK):
+        problems.append(f"the artifact directory {art_dir!r} cannot be written")
+    cb = code_bytes()
+    out += [f"preflight.code_bytes={cb}", f"preflight.artifact_budget_bytes={spec.quant.target_artifact_bytes - cb}"]
+    if spec.quant.target_artifact_bytes - cb <= 0:
+        problems.append("the counted source alone exceeds quant.target_artifact_bytes (set PG_SUBMISSION_CODE_BYTES to the submission's real code size)")
+    out += [f"preflight.problem={p}" for p in problems]
+    out.append(f"preflight.ok={str(not problems).lower()}")
+    return out, not problems
 
 
 def check_record_step_time(mode: str, steps: int, measured_ms_per_step: float, limit_ms: float) -> None:
@@ -673,7 +748,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="parameter_golf_b200.train")
     sub = ap.add_subparsers(dest="cmd", required=True)
     sub.add_parser("keys", help="list every spec key (type, default) and the train_gpt.py environment names that map onto them")
-    for name in ("run", "sweep", "plan"):
+    for name in ("run", "sweep", "plan", "preflight"):
         sp = sub.add_parser(name)
         sp.add_argument("--spec")
         sp.add_argument("--family", "--builtin", dest="family", default=None)
@@ -736,10 +811,15 @@ def main(argv=None) -> int:
         spec.apply_overrides(a.overrides)
         if a.mode:
             spec.mode = a.mode
-        if spec.train.world_size > 1 and a.cmd != "plan":
+        if spec.train.world_size > 1 and a.cmd not in ("plan", "preflight"):
             import torch.distributed as dist
             if not dist.is_initialized():
                 dist.init_process_group("gloo" if spec.train.backend == "cpu" else "nccl")
+        if a.cmd == "preflight":         # everything that can be checked about a planned run without a device
+            lines, ok = preflight(spec)
+            print("\n".join(lines))
+            rc |= 0 if ok else 1
+            continue
         if a.cmd == "plan":              # print the execution plan (layout, block schedule, memory estimate) and stop
             from .plan import ExecutionPlan
             print("\n".join(ExecutionPlan.from_run_spec(spec).summary_lines()))

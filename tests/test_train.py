@@ -680,3 +680,32 @@ def test_cli_log_file_starts_with_the_spec_and_the_environment(tmp_path):
     text = open(tmp_path / "logs" / "tiny_cpu.txt").read()
     assert text.startswith("=" * 100) and 'family = "tiny_cpu"' in text and "torch=" in text and "step:4/4 train_loss:" in text
     assert "record_audit_json=" in text and "\nval_bpb=" in text and "steps_completed=4" in text
+
+
+def test_preflight_checks_a_planned_run_without_a_device(tmp_path, capsys):
+    from parameter_golf_b200.data.shards import write_shard, write_synthetic_dataset
+    from parameter_golf_b200.train import main, preflight
+    root = str(tmp_path / "shards")
+    write_synthetic_dataset(root, 1024, train_tokens=1 << 16, val_tokens=1 << 12, seed=1)
+    s = family_preset("record_11l")
+    s.mode = "record_shaped_proxy"
+    s.train.world_size, s.train.artifact_path = 8, str(tmp_path / "out" / "a.pgrs")
+    s.train.train_data_pattern, s.train.validation_data_pattern = root + "/fineweb_train_*.bin", root + "/fineweb_val_*.bin"
+    lines, ok = preflight(s)
+    kv = dict(l.split("=", 1) for l in lines)
+    assert not ok and "one step needs 786440" in kv["preflight.problem"]            # 65,536 tokens cannot feed one record step
+    assert kv["preflight.tokens_per_step"] == "786432" and kv["preflight.local_sequences_per_micro_batch"] == "48"
+    s.train.batch_tokens = 8 * 2048
+    lines, ok = preflight(s)
+    kv = dict(l.split("=", 1) for l in lines)
+    assert ok and kv["preflight.train_tokens"] == str(1 << 16) and float(kv["preflight.train_data_passes"]) == pytest.approx(8 * (8 * 2048 + 8) / 65536, abs=1e-3)
+    assert float(kv["preflight.engine_memory_gib"]) > 0 and int(kv["preflight.artifact_budget_bytes"]) < 16_000_000
+    # a damaged shard and a missing sidecar are both reported
+    bad = tmp_path / "shards" / "fineweb_train_000009.bin"
+    bad.write_bytes(b"\\0" * 100)
+    s.eval.caseops_byte_sidecar_pattern = str(tmp_path / "nothing_*.bin")
+    lines, ok = preflight(s)
+    probs = [l for l in lines if l.startswith("preflight.problem=")]
+    assert not ok and any("fineweb_train_000009.bin" in p for p in probs) and any("byte sidecar" in p for p in probs)
+    assert main(["preflight", "--family", "tiny_cpu", "--mode", "smoke", "--artifact", str(tmp_path / "x.pgrs")]) == 0
+    assert "preflight.ok=true" in capsys.readouterr().out

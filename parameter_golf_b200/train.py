@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import contextlib
+import copy
 import json
 import math
 import os
@@ -463,6 +464,19 @@ class VariantRunner:
         max_steps = mode_max_steps(spec, mode)
         max_ms = 1000.0 * t.max_wallclock_seconds if t.max_wallclock_seconds > 0 else None
         qat = t.qat_enabled
+        if t.prime_steps > 0 and step0 == 0:
+            # priming: real steps whose every effect is undone afterwards (train_gpt.py:937-961)
+            keep_p = {k: v.detach().clone() for k, v in backend.sync_params().items()}
+            keep_o, keep_l, keep_r = copy.deepcopy(backend.state_dict()), loader.state(), torch.get_rng_state()
+            for ws in range(t.prime_steps):
+                prime = [tuple(torch.from_numpy(a) for a in loader.next_batch(tokens_per_step, t.seq_len, accum)) for _ in range(accum)]
+                backend.train_step(prime, 1.0, t.muon_momentum_warmup_start, qat)
+                log.info(f"warmup_step:{ws + 1}/{t.prime_steps}")
+            for k, v in keep_p.items():
+                backend.sync_params()[k].copy_(v)
+            backend.load_state_dict(keep_o)
+            loader.restore(keep_l)
+            torch.set_rng_state(keep_r)
         log.info(f"model_params:{gpt.count_params(m)} world_size:{t.world_size} grad_accum_steps:{accum} "
                  f"train_batch_tokens:{tokens_per_step} train_seq_len:{t.seq_len} iterations:{max_steps}")
         train_ms = 0.0

@@ -709,3 +709,29 @@ def test_preflight_checks_a_planned_run_without_a_device(tmp_path, capsys):
     assert not ok and any("fineweb_train_000009.bin" in p for p in probs) and any("byte sidecar" in p for p in probs)
     assert main(["preflight", "--family", "tiny_cpu", "--mode", "smoke", "--artifact", str(tmp_path / "x.pgrs")]) == 0
     assert "preflight.ok=true" in capsys.readouterr().out
+
+
+def test_priming_steps_leave_no_trace(tmp_path, monkeypatch):
+    """WARMUP_STEPS of the Python trainers: steps that run and are then undone (weights, optimizer state, data position, random
+    state), so a primed run equals an unprimed one (train_gpt.py:937-961)."""
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+
+    def run(prime):
+        s = family_preset("tiny_cpu")
+        s.mode = "smoke"
+        s.apply_env({"WARMUP_STEPS": str(prime)})
+        assert s.train.prime_steps == prime and s.train.warmup_steps == 0
+        s.train.artifact_path = str(tmp_path / f"p{prime}.pgrs")
+        s.eval.max_tokens = 512
+        r = quiet(s)
+        lines = []
+        real = r.log.info
+        r.log.info = lambda msg: (lines.append(msg), real(msg))[1]
+        res = r.run()
+        return res, lines
+    plain, _ = run(0)
+    primed, lines = run(3)
+    assert [l for l in lines if l.startswith("warmup_step:")] == ["warmup_step:1/3", "warmup_step:2/3", "warmup_step:3/3"]
+    assert primed.train_loss_first == plain.train_loss_first and primed.train_loss_last == plain.train_loss_last and primed.val_loss == plain.val_loss
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["train.prime_steps=2"]).validate()

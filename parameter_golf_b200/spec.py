@@ -226,7 +226,7 @@ class TrainSpec:
     rank: int = 0
     world_size: int = 1
     artifact_path: str = "artifact.pgrs"
-    prime_steps: int = 0                # cpu backend: run this many steps first, then put weights, optimizer state, data position and
+    prime_steps: int = 0                # cpu backend (ignored with a log line on the CUDA backends): run this many steps first, then put weights, optimizer state, data position and
                                         # random state back (the Python trainers' WARMUP_STEPS, which primes compiled kernels without
                                         # training, train_gpt.py:937-961; the CUDA engine compiles nothing at run time)
     fast_bank_updates: bool = False     # accepted for the reference's spec files; bank updates are always the fused kernels here
@@ -501,7 +501,7 @@ class RunSpec:
         if has("WARMUP_STEPS"):
             # in the Python trainers these are priming steps whose effect is undone, not a learning-rate warm-up
             # (train.warmup_steps is the reference engine's linear warm-up and is set from TOML / CLI only)
-            t.prime_steps = I("WARMUP_STEPS") if t.backend == "cpu" else 0
+            t.prime_steps = I("WARMUP_STEPS")
         if has("TRAIN_BATCH_TOKENS"): t.batch_tokens = I("TRAIN_BATCH_TOKENS")
         if has("TRAIN_SEQ_LEN"): t.seq_len = m.train_seq_len = I("TRAIN_SEQ_LEN")
         if has("EVAL_SEQ_LEN"): m.eval_seq_len = I("EVAL_SEQ_LEN")
@@ -699,7 +699,7 @@ class RunSpec:
         chk(t.seq_len > 0 and t.batch_tokens % t.seq_len == 0, "batch_tokens must be a multiple of seq_len")
         chk((t.seq_len_start == 0 and t.batch_tokens_start == 0) or t.backend == "cpu",
             "train.seq_len_start and train.batch_tokens_start run on train.backend=cpu only")
-        chk(t.prime_steps >= 0 and (t.prime_steps == 0 or t.backend == "cpu"), "train.prime_steps runs on train.backend=cpu only")
+        chk(t.prime_steps >= 0, "train.prime_steps must be >= 0")
         chk(0.0 <= t.ema_start_fraction < 1.0 and (t.ema_start_fraction == 0.0 or t.backend == "cpu"),
             "train.ema_start_fraction must be in [0, 1) and runs on train.backend=cpu only (the CUDA optimizer kernels average from the first step)")
         chk(t.seq_len_start == 0 or (0 < t.seq_len_start <= t.seq_len and t.seq_len % t.seq_len_start == 0), "train.seq_len_start must divide train.seq_len")

@@ -464,7 +464,9 @@ class VariantRunner:
         max_steps = mode_max_steps(spec, mode)
         max_ms = 1000.0 * t.max_wallclock_seconds if t.max_wallclock_seconds > 0 else None
         qat = t.qat_enabled
-        if t.prime_steps > 0 and step0 == 0:
+        if t.prime_steps > 0 and t.backend != "cpu":
+            log.info(f"warmup_steps:{t.prime_steps} skipped: the CUDA engine compiles nothing at run time")
+        if t.prime_steps > 0 and step0 == 0 and t.backend == "cpu":
             # priming: real steps whose every effect is undone afterwards (train_gpt.py:937-961)
             keep_p = {k: v.detach().clone() for k, v in backend.sync_params().items()}
             keep_o, keep_l, keep_r = copy.deepcopy(backend.state_dict()), loader.state(), torch.get_rng_state()

@@ -733,5 +733,4 @@ def test_priming_steps_leave_no_trace(tmp_path, monkeypatch):
     primed, lines = run(3)
     assert [l for l in lines if l.startswith("warmup_step:")] == ["warmup_step:1/3", "warmup_step:2/3", "warmup_step:3/3"]
     assert primed.train_loss_first == plain.train_loss_first and primed.train_loss_last == plain.train_loss_last and primed.val_loss == plain.val_loss
-    with pytest.raises(ValueError):
-        family_preset("record_11l").apply_overrides(["train.prime_steps=2"]).validate()
+    family_preset("record_11l").apply_overrides(["train.prime_steps=2"]).validate()          # accepted; the CUDA backends skip it with a log line

@@ -742,7 +742,15 @@ class VariantRunner:
                 "tokens_per_step": tokens_per_step, "grad_accum": accum, "seq_len": t.seq_len, "steps": res.steps,
                 "step_avg_ms": round(res.step_avg_ms, 3), "ns_profile": t.muon_ns_profile, "grad_wire_dtype": t.grad_wire_dtype,
                 "quant_scheme": spec.quant.scheme, "compression": spec.quant.compression, "artifact_bytes": res.artifact_bytes,
-                "eval_kind": res.eval_kind, "gaps": gaps, "frontier_algorithm_notes": frontier_algorithm_notes(spec), "timing_backend": "host_perf_counter" if t.backend == "cpu" else "cuda_events_max_over_ranks"}))
+                "eval_kind": res.eval_kind, "gaps": gaps, "frontier_algorithm_notes": frontier_algorithm_notes(spec), "timing_backend": "host_perf_counter" if t.backend == "cpu" else "cuda_events_max_over_ranks",
+                # everything that shaped the run, so that a result can be traced to its configuration from the log alone
+                # (the reference's audit line carries every switch, pg-train/src/lib.rs:4227-4824)
+                "measured_ms_per_step": round(res.measured_ms_per_step, 3), "tokens_per_s": round(res.tokens_per_s, 1), "stopped_early": res.stopped_early,
+                "train_loss_first": res.train_loss_first, "train_loss_last": res.train_loss_last, "val_loss": res.val_loss, "val_bpb": res.val_bpb,
+                "prequant_val_bpb": res.prequant_val_bpb, "code_bytes": res.code_bytes, "budget_ok": res.budget_ok, "peak_mem_mib": res.peak_mem_mib,
+                "model_params": gpt.count_params(m), "bank_shapes": {k: list(gpt.param_shapes(m)[k]) for k in gpt.BANKS},
+                "layer_schedule": gpt.layer_schedule(m), "xsa_layers": m.xsa_layers(), "parallel_residual": m.parallel,
+                "torch": torch.__version__, "cuda": torch.version.cuda, "spec": spec.to_dict()}, default=str))
         return res
 
 

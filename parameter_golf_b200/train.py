@@ -736,7 +736,15 @@ class VariantRunner:
             "timing_train_step_ms": tm.get("train_step_ms", 0.0), "timing_data_sampling_ms": tm.get("data_ms", 0.0),
             "timing_artifact_export_ms": tm.get("export_ms", 0.0), "timing_eval_ms": tm.get("eval_ms", 0.0)}
         if t.rank == 0:
-            log.raw("record_audit_json=" + json.dumps({
+            def finite(x):          # strict JSON has no NaN: a value that was not measured is null
+                if isinstance(x, float) and not math.isfinite(x):
+                    return None
+                if isinstance(x, dict):
+                    return {k: finite(v) for k, v in x.items()}
+                if isinstance(x, (list, tuple)):
+                    return [finite(v) for v in x]
+                return x
+            log.raw("record_audit_json=" + json.dumps(finite({
                 "name": spec.name, "mode": mode, "fingerprint": res.fingerprint, "backend": t.backend,
                 "distributed_optimizer_backend": t.distributed_optimizer_backend, "world_size": t.world_size,
                 "tokens_per_step": tokens_per_step, "grad_accum": accum, "seq_len": t.seq_len, "steps": res.steps,
@@ -750,7 +758,7 @@ class VariantRunner:
                 "prequant_val_bpb": res.prequant_val_bpb, "code_bytes": res.code_bytes, "budget_ok": res.budget_ok, "peak_mem_mib": res.peak_mem_mib,
                 "model_params": gpt.count_params(m), "bank_shapes": {k: list(gpt.param_shapes(m)[k]) for k in gpt.BANKS},
                 "layer_schedule": gpt.layer_schedule(m), "xsa_layers": m.xsa_layers(), "parallel_residual": m.parallel,
-                "torch": torch.__version__, "cuda": torch.version.cuda, "spec": spec.to_dict()}, default=str))
+                "torch": torch.__version__, "cuda": torch.version.cuda, "spec": spec.to_dict()}), default=str, allow_nan=False))
         return res
 
 

@@ -852,6 +852,7 @@ def family_preset(family: str) -> RunSpec:
         m.logit_softcap, m.qk_gain_init, m.ln_scale, m.tie_embeddings = 30.0, 5.0, True, True
         m.attention_backend, m.compute_precision = "flash_f32", "f32_tf32"
         t.batch_tokens, t.seq_len, t.warmup_steps = 524_288, 2048, 20
+        t.wallclock_warmdown = False      # the engine's schedule is counted in steps (warm-up from zero, stable, warm-down; pg-optim/src/scheduler.rs:12-66); its wall-clock cap only stops the run
         q, e = s.quant, s.eval
         q.lqer = LqerSpec(False, 4, 3, 2, 4, 64, True)
         q.mlp_clip_sigmas, q.attn_clip_sigmas, q.embed_clip_sigmas, q.gptq_calibration_batches = 12.0, 13.0, 14.0, 0

@@ -543,8 +543,11 @@ class VariantRunner:
             elif t.wallclock_warmdown and max_ms is not None:
                 scale = wallclock_lr_scale(step, elapsed, max_steps, t.warmdown_iters, max_ms)
             else:
-                wd = int(round(max_steps * t.warmdown_frac)) if t.warmdown_frac > 0 else min(t.warmdown_iters, max_steps)
-                scale = lr_scale_with_floor(step, t.warmup_steps, max_steps, wd, t.min_lr_scale) if (wd or t.warmup_steps) else 1.0
+                # counted against the configured run length, not the (shorter) length of a smoke or proxy run, as the reference
+                # does (pg-train/src/lib.rs:1105-1111; warm-down length from the fraction as in pg-model/src/spec.rs:527-531)
+                total = max(t.total_iterations, max_steps)
+                wd = int(round(total * t.warmdown_frac)) if t.warmdown_frac > 0 else min(t.warmdown_iters, total)
+                scale = lr_scale_with_floor(step, t.warmup_steps, total, wd, t.min_lr_scale) if (wd or t.warmup_steps) else 1.0
             if t.qat_fraction > 0 and not qat and (elapsed / max_ms if max_ms is not None else step / max(max_steps, 1)) >= 1.0 - t.qat_fraction:
                 qat = True
                 log.info(f"late_qat:enabled step:{step} by qat_fraction:{t.qat_fraction}")

@@ -732,5 +732,8 @@ def test_priming_steps_leave_no_trace(tmp_path, monkeypatch):
     plain, _ = run(0)
     primed, lines = run(3)
     assert [l for l in lines if l.startswith("warmup_step:")] == ["warmup_step:1/3", "warmup_step:2/3", "warmup_step:3/3"]
-    assert primed.train_loss_first == plain.train_loss_first and primed.train_loss_last == plain.train_loss_last and primed.val_loss == plain.val_loss
+    assert primed.train_loss_first == plain.train_loss_first and primed.train_loss_last == plain.train_loss_last
+    # (two identical runs differ in the last digits of the round-tripped validation loss: threaded CPU reductions move a few
+    # weights across an int6 rounding boundary)
+    assert abs(primed.val_loss - plain.val_loss) < 1e-4
     family_preset("record_11l").apply_overrides(["train.prime_steps=2"]).validate()          # accepted; the CUDA backends skip it with a log line

@@ -851,6 +851,7 @@ def family_preset(family: str) -> RunSpec:
         m.smear_gate, m.smear_gate_boundary_token_id = True, 1
         m.logit_softcap, m.qk_gain_init, m.ln_scale, m.tie_embeddings = 30.0, 5.0, True, True
         m.attention_backend, m.compute_precision = "flash_f32", "f32_tf32"
+        m.attn_out_gate = AttnOutGateSpec(False, 24)                  # its default width (spec.rs:233-240)
         m.parallel_residual = ParallelResidualSpec(False, False)      # the reference's default: `enabled` alone does not split (spec.rs:216-222)
         t.batch_tokens, t.seq_len, t.warmup_steps = 524_288, 2048, 20
         t.wallclock_warmdown = False      # the engine's schedule is counted in steps (warm-up from zero, stable, warm-down; pg-optim/src/scheduler.rs:12-66); its wall-clock cap only stops the run

@@ -533,6 +533,10 @@ class RunSpec:
         if has("SCALAR_LR"): t.scalar_lr = F("SCALAR_LR")
         if has("MUON_MOMENTUM"): t.muon_momentum = F("MUON_MOMENTUM")
         if has("MUON_BACKEND_STEPS"): t.muon_ns_steps = I("MUON_BACKEND_STEPS")
+        for name in ("PG_MUON_NS_PROFILE", "PG_GPU_MUON_NS_PROFILE"):          # the reference's spellings (pg-optim/src/muon.rs:20-30)
+            if has(name):
+                raw = env[name].lower()
+                t.muon_ns_profile = ("simple" if raw in ("simple", "legacy", "ns5") else "quintic" if raw in ("quintic", "modded_nanogpt") else "polar_express")
         if has("MUON_MOMENTUM_WARMUP_START"): t.muon_momentum_warmup_start = F("MUON_MOMENTUM_WARMUP_START")
         if has("MUON_MOMENTUM_WARMUP_STEPS"): t.muon_momentum_warmup_steps = I("MUON_MOMENTUM_WARMUP_STEPS")
         if has("BETA1"): t.adam_beta1 = F("BETA1")
@@ -854,6 +858,7 @@ def family_preset(family: str) -> RunSpec:
         m.attn_out_gate = AttnOutGateSpec(False, 24)                  # its default width (spec.rs:233-240)
         m.parallel_residual = ParallelResidualSpec(False, False)      # the reference's default: `enabled` alone does not split (spec.rs:216-222)
         t.batch_tokens, t.seq_len, t.warmup_steps = 524_288, 2048, 20
+        t.muon_ns_profile, t.muon_ns_steps = "polar_express", 5      # its default coefficients (pg-optim/src/muon.rs:19-30), five steps (spec.rs:544)
         t.wallclock_warmdown = False      # the engine's schedule is counted in steps (warm-up from zero, stable, warm-down; pg-optim/src/scheduler.rs:12-66); its wall-clock cap only stops the run
         q, e = s.quant, s.eval
         q.lqer = LqerSpec(False, 4, 3, 2, 4, 64, True)

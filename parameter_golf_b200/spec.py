@@ -533,10 +533,8 @@ class RunSpec:
         if has("SCALAR_LR"): t.scalar_lr = F("SCALAR_LR")
         if has("MUON_MOMENTUM"): t.muon_momentum = F("MUON_MOMENTUM")
         if has("MUON_BACKEND_STEPS"): t.muon_ns_steps = I("MUON_BACKEND_STEPS")
-        for name in ("PG_MUON_NS_PROFILE", "PG_GPU_MUON_NS_PROFILE"):          # the reference's spellings (pg-optim/src/muon.rs:20-30)
-            if has(name):
-                raw = env[name].lower()
-                t.muon_ns_profile = ("simple" if raw in ("simple", "legacy", "ns5") else "quintic" if raw in ("quintic", "modded_nanogpt") else "polar_express")
+        if has("PG_MUON_NS_PROFILE"): t.muon_ns_profile = _ns_profile_name(env["PG_MUON_NS_PROFILE"])
+        if has("PG_GPU_MUON_NS_PROFILE"): t.muon_ns_profile = _ns_profile_name(env["PG_GPU_MUON_NS_PROFILE"])
         if has("MUON_MOMENTUM_WARMUP_START"): t.muon_momentum_warmup_start = F("MUON_MOMENTUM_WARMUP_START")
         if has("MUON_MOMENTUM_WARMUP_STEPS"): t.muon_momentum_warmup_steps = I("MUON_MOMENTUM_WARMUP_STEPS")
         if has("BETA1"): t.adam_beta1 = F("BETA1")
@@ -931,6 +929,12 @@ def arch_variant(name: str) -> RunSpec:
     if m.head_dim != 64 or rd % 16:          # shapes the CUDA kernels are not written (or not tested) for
         s.train.backend, s.train.distributed_optimizer_backend = "cpu", "all_reduce_replicated_muon"
     return s
+
+
+def _ns_profile_name(raw: str) -> str:
+    """The reference's spellings of its three coefficient profiles (pg-optim/src/muon.rs:20-30); anything else is polar_express."""
+    raw = raw.lower()
+    return "simple" if raw in ("simple", "legacy", "ns5") else "quintic" if raw in ("quintic", "modded_nanogpt") else "polar_express"
 
 
 # ---- helpers --------------------------------------------------------------------------------------

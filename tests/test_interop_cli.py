@@ -198,7 +198,7 @@ def test_eval_cli_document_lora_on_two_cpu_ranks_matches_one(tmp_path):
                          capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
     assert one.returncode == 0 and two.returncode == 0, (one.stderr[-800:], two.stderr[-1500:])
     get = lambda out: float([l for l in out.stdout.splitlines() if l.startswith("val_loss=")][0].split("=")[1])
-    assert abs(get(one) - get(two)) < 1e-9
+    assert abs(get(one) - get(two)) < 1e-5            # the same tokens in differently shaped batches: equal up to float32 rounding
 
 
 def test_leaderboard_rules_follow_the_reference_binary():

@@ -254,8 +254,10 @@ def test_training_on_exported_text_shards_and_bpb_from_the_byte_sidecar(tmp_path
 
     a = run([f"eval.tokenizer_vocab_path={model}"])
     b = run([f"eval.caseops_byte_sidecar_pattern={out}/fineweb_val_bytes_*.bin"])
-    assert np.isfinite(a.val_bpb) and a.val_loss == b.val_loss
-    assert a.val_bpb == pytest.approx(b.val_bpb, rel=1e-9)
+    # two runs of the same configuration agree only to the rounding of threaded CPU reductions (a few int6 codes flip), so the
+    # losses are compared loosely and the byte counts, which are what this test is about, through the bpb / loss ratio
+    assert np.isfinite(a.val_bpb) and a.val_loss == pytest.approx(b.val_loss, rel=1e-4)
+    assert a.val_bpb / a.val_loss == pytest.approx(b.val_bpb / b.val_loss, rel=1e-9)
     assert abs(a.train_loss_first - np.log(tok.vocab_size)) < 0.2
 
 
@@ -732,7 +734,7 @@ def test_priming_steps_leave_no_trace(tmp_path, monkeypatch):
     plain, _ = run(0)
     primed, lines = run(3)
     assert [l for l in lines if l.startswith("warmup_step:")] == ["warmup_step:1/3", "warmup_step:2/3", "warmup_step:3/3"]
-    assert primed.train_loss_first == plain.train_loss_first and primed.train_loss_last == plain.train_loss_last
+    assert primed.train_loss_first == pytest.approx(plain.train_loss_first, rel=1e-6) and primed.train_loss_last == pytest.approx(plain.train_loss_last, rel=1e-5)
     # (two identical runs differ in the last digits of the round-tripped validation loss: threaded CPU reductions move a few
     # weights across an int6 rounding boundary)
     assert abs(primed.val_loss - plain.val_loss) < 1e-4

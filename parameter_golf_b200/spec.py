@@ -271,6 +271,8 @@ class TrainSpec:
     seed: int = 1337
     val_loss_every: int = 0
     train_log_every: int = 200
+    churn_log_every: int = 0            # cpu backend, ternary / binary QAT: every N steps log the fraction of bank codes that changed since
+                                        # the last such line (CHURN_LOG_EVERY of the 2026-03-24 scripts: how settled the discrete weights are)
     val_batch_size: int = 524_288
     grad_wire_dtype: str = "bf16"       # wire dtype of bank-gradient reduce-scatter
     cuda_graph: bool = False            # replay the micro-batch forward+backward from a captured CUDA graph
@@ -489,6 +491,7 @@ class RunSpec:
         if has("VAL_BATCH_SIZE"): t.val_batch_size = I("VAL_BATCH_SIZE")
         if has("VAL_LOSS_EVERY"): t.val_loss_every = I("VAL_LOSS_EVERY")
         if has("TRAIN_LOG_EVERY"): t.train_log_every = I("TRAIN_LOG_EVERY")
+        if has("CHURN_LOG_EVERY"): t.churn_log_every = I("CHURN_LOG_EVERY")
         if has("ITERATIONS"): t.total_iterations = I("ITERATIONS")
         if has("WARMDOWN_ITERS"): t.warmdown_iters = I("WARMDOWN_ITERS")
         if has("WARMDOWN_FRACTION"): t.warmdown_frac = F("WARMDOWN_FRACTION")

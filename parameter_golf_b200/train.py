@@ -233,6 +233,7 @@ class VariantResult:
     eval_kind: str = "none"
     peak_mem_mib: int = 0
     complementary_mean_weight: float = 1.0
+    churn_history: list = field(default_factory=list)    # (step, fraction of discrete codes that changed) at every train.churn_log_every steps
     val_history: list = field(default_factory=list)      # (step, val_loss, val_bpb) of the periodic validations (train.val_loss_every)
     timers: dict = field(default_factory=dict)
     reference_keys: dict = field(default_factory=dict)   # the same facts under the names the reference trainer prints (pg-train/src/main.rs:218-431)
@@ -270,6 +271,23 @@ def record_gaps(spec: RunSpec, mode: str) -> List[str]:
         if t.world_size != 8:
             gaps.append("record is defined on 8 GPUs")
     return gaps
+
+
+def code_churn(m, params: Dict[str, torch.Tensor], prev: Optional[dict]):
+    """``(fraction of bank codes that differ from the previous call, the codes of this call)``: the discrete weights a ternary or
+    binary QAT run would export now, compared with those of the last look
+    (records/track_non_record_16mb/2026-03-24_106M_Binary_.../train_gpt_cuda_binary.py:246-261). 0 on the first call."""
+    from .quant.binary import quantize_binary
+    from .quant.ternary import quantize_ternary
+    quant = quantize_binary if m.qat_kind == "binary" else quantize_ternary
+    cur, changed, total = {}, 0, 0
+    for name in gpt.BANKS:
+        w = params[name].detach().float().cpu()
+        cur[name] = quant(w.reshape(-1, w.shape[-1]), m.qat_ternary_group)[0]
+        if prev is not None:
+            changed += int((cur[name] != prev[name]).sum())
+            total += cur[name].numel()
+    return changed / max(total, 1), cur
 
 
 def frontier_algorithm_notes(spec: RunSpec) -> List[str]:
@@ -495,6 +513,7 @@ class VariantRunner:
             from .parallel.health import RankHealth
             health = RankHealth.from_process_group(timeout_s=float(os.environ.get("PGB_HEALTH_TIMEOUT_S", "120")))
         val_cache = {}
+        churn_prev = None
         skipped_ms = 0.0
 
         def validate_now():
@@ -590,6 +609,10 @@ class VariantRunner:
             now_ms = train_ms + 1000.0 * (self.clock() - t_start)
             if t.train_log_every > 0 and (step <= 10 or step % t.train_log_every == 0 or step == max_steps):
                 log.info(f"step:{step}/{max_steps} train_loss:{loss:.4f} train_time:{now_ms:.0f}ms step_avg:{now_ms / (step - step0):.2f}ms")
+            if t.churn_log_every > 0 and step % t.churn_log_every == 0 and t.backend == "cpu" and m.qat_kind in ("ternary", "binary"):
+                frac, churn_prev = code_churn(m, backend.sync_params(), churn_prev)
+                log.info(f"step:{step} churn:{frac:.4f}")
+                res.churn_history.append((step, frac))
             if t.val_loss_every > 0 and t.validation_data_pattern and (step % t.val_loss_every == 0 or step == max_steps):
                 validate_now()
             if t.checkpoint_every > 0 and t.checkpoint_path and step % t.checkpoint_every == 0:

@@ -739,3 +739,24 @@ def test_priming_steps_leave_no_trace(tmp_path, monkeypatch):
     # weights across an int6 rounding boundary)
     assert abs(primed.val_loss - plain.val_loss) < 1e-4
     family_preset("record_11l").apply_overrides(["train.prime_steps=2"]).validate()          # accepted; the CUDA backends skip it with a log line
+
+
+def test_code_churn_is_logged_for_discrete_weight_training(tmp_path, monkeypatch):
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    from parameter_golf_b200.train import code_churn
+    s = family_preset("tiny_cpu")
+    p = gpt.init_params(s.model, 1)
+    s.model.qat_kind, s.model.qat_ternary_group = "binary", 64
+    frac, prev = code_churn(s.model, p, None)
+    assert frac == 0.0
+    p2 = {k: v.clone() for k, v in p.items()}
+    p2["kv_bank"][0, 0, :8] *= -1                                    # eight signs flip
+    frac, _ = code_churn(s.model, p2, prev)
+    assert frac == pytest.approx(8 / sum(p[b].numel() for b in gpt.BANKS))
+    s.mode = "smoke"
+    s.apply_env({"CHURN_LOG_EVERY": "2"})
+    s.apply_overrides(["quant.scheme=binary_b1", "quant.ternary_group=64", "quant.prune_to_target=false", "train.qat_enabled=true"])
+    s.train.artifact_path = str(tmp_path / "c.pgrs")
+    s.eval.max_tokens = 512
+    res = quiet(s).run()
+    assert [h[0] for h in res.churn_history] == [2, 4] and res.churn_history[0][1] == 0.0 and 0.0 < res.churn_history[1][1] < 1.0

@@ -358,6 +358,7 @@ class EvalSpec:
     max_eval_seconds: float = 600.0
     temperature: float = 1.0           # capped logits are divided by this when scoring (autograd runner); `find_temperature` picks it
     temperature_grid: list = field(default_factory=lambda: [0.90, 0.95, 1.00, 1.05, 1.10])
+    auto_temperature: bool = False     # trainer, cpu backend: pick the temperature from the grid on training tokens before the final evaluation (TEMP_SCALING)
     temperature_calibration_tokens: int = 65536       # training tokens the grid is scored on
     byte_table_seed: int = 20240520
     # adaptation_backend = doc_lora: documents (cut at doc_boundary_token_id) scored in isolation, chunk by chunk, with adapters
@@ -570,6 +571,7 @@ class RunSpec:
         if has("QAT_FRACTION"): t.qat_fraction = F("QAT_FRACTION")
         if has("MUON_WEIGHT_DECAY"): t.muon_wd = F("MUON_WEIGHT_DECAY")
         if has("MTP_HEADS"): m.mtp_num_heads = I("MTP_HEADS")
+        if has("TEMP_SCALING"): e.auto_temperature = B("TEMP_SCALING")
         if has("SLIDING_EVAL_STRIDE"): e.stride = I("SLIDING_EVAL_STRIDE")
         if has("SLIDING_BATCH_SIZE"): e.batch_windows = I("SLIDING_BATCH_SIZE")
         if has("VAL_MAX_TOKENS") and I("VAL_MAX_TOKENS") > 0: e.max_tokens = I("VAL_MAX_TOKENS")
@@ -680,6 +682,7 @@ class RunSpec:
         chk(q.coarse_step >= 1 and all(0 <= int(l) < m.num_layers for l in q.coarse_layers), "quant.coarse_step must be >= 1 and coarse_layers inside the model")
         chk(not q.coarse_layers or q.scheme not in ("ternary_b158", "binary_b1"), "quant.coarse_layers does not apply to the ternary and binary schemes")
         chk(e.doc_lora_rank >= 0 and e.doc_chunk_size >= 1 and e.doc_batch_size >= 1 and e.doc_lora_lr > 0, "eval.doc_* out of range")
+        chk(not e.auto_temperature or t.backend == "cpu", "eval.auto_temperature is scored by the autograd runner (train.backend=cpu)")
         chk(e.temperature > 0 and all(x > 0 for x in e.temperature_grid), "eval.temperature and its grid must be positive")
         chk(m.qat_kind in ("int6", "ternary", "binary", "noise"), "model.qat_kind must be int6, ternary, binary or noise")
         chk(m.qat_kind == "int6" or t.backend == "cpu", "model.qat_kind=ternary|binary|noise runs on train.backend=cpu only")
@@ -817,7 +820,7 @@ def family_preset(family: str) -> RunSpec:
         m.normed_out_proj = m.vocab_bias = True
         s.quant.scheme, s.quant.compression, s.quant.float_storage = "ternary_b158", "lzma9", "fp8"
         s.quant.prune_to_target = False
-        s.eval.stride = 16
+        s.eval.stride, s.eval.auto_temperature = 16, True       # SLIDING_EVAL_STRIDE=16, TEMP_SCALING=1 in the run script
     elif family == "binary_15l":
         # records/track_non_record_16mb/2026-03-24_106M_Binary_Asymmetric_UNet_FP8_15L_8192BPE_YaRN_NeoMuon_Smear (README "Architecture",
         # run_cuda_binary.sh): the ternary recipe with 1-bit weights, 15 blocks (7 before the U-Net's turn, 8 after) and the
@@ -841,7 +844,7 @@ def family_preset(family: str) -> RunSpec:
         t.grad_clip_norm, t.ema_decay = 0.0, 0.0
         s.quant.scheme, s.quant.compression, s.quant.float_storage = "binary_b1", "lzma9", "fp8"
         s.quant.prune_to_target = False
-        s.eval.stride = 16
+        s.eval.stride, s.eval.auto_temperature = 16, True       # SLIDING_EVAL_STRIDE=16, TEMP_SCALING=1 in the run script
     else:
         # The six families of the reference engine, field for field (pg-model/src/spec.rs:313-399 ModelSpec::for_family, with
         # TrainSpec / QuantSpec / EvalSpec defaults of :489-524, :603-664): SP8192 vocabulary, 11 x 512, BigramHash 3072 x 112, value

@@ -233,6 +233,7 @@ class VariantResult:
     eval_kind: str = "none"
     peak_mem_mib: int = 0
     complementary_mean_weight: float = 1.0
+    eval_temperature: float = 1.0           # the logit temperature the final evaluation used (eval.temperature, or the grid's best)
     churn_history: list = field(default_factory=list)    # (step, fraction of discrete codes that changed) at every train.churn_log_every steps
     val_history: list = field(default_factory=list)      # (step, val_loss, val_bpb) of the periodic validations (train.val_loss_every)
     timers: dict = field(default_factory=dict)
@@ -709,6 +710,15 @@ class VariantRunner:
                 runner = OracleRunner(m, eval_params)
                 runner.temperature = spec.eval.temperature
                 edev = "cpu"
+                if spec.eval.auto_temperature:
+                    # the ternary / binary scripts' TEMP_SCALING: the grid is scored on training tokens with the round-tripped
+                    # model, the best value scales the logits of the final evaluation (train_gpt_cuda_ternary.py find_temp)
+                    from .eval.sliding import find_temperature
+                    calib = load_validation_tokens(t.train_data_pattern, m.eval_seq_len, min(spec.eval.temperature_calibration_tokens,
+                                                                                             8 * m.eval_seq_len if mode != "record" else 1 << 62))
+                    best, table = find_temperature(runner, calib, m.eval_seq_len, spec.eval.temperature_grid)
+                    runner.temperature = res.eval_temperature = best
+                    log.info("temperature_search:" + json.dumps({str(k): round(v, 6) for k, v in table.items()}) + f" optimal_T:{best}")
             else:
                 if spec.eval.temperature != 1.0:
                     raise RuntimeError("eval.temperature != 1 is scored by the autograd runner (train.backend=cpu or evalcli --device cpu)")

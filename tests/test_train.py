@@ -760,3 +760,25 @@ def test_code_churn_is_logged_for_discrete_weight_training(tmp_path, monkeypatch
     s.eval.max_tokens = 512
     res = quiet(s).run()
     assert [h[0] for h in res.churn_history] == [2, 4] and res.churn_history[0][1] == 0.0 and 0.0 < res.churn_history[1][1] < 1.0
+
+
+def test_trainer_picks_the_evaluation_temperature_from_its_grid(tmp_path, monkeypatch):
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.apply_env({"TEMP_SCALING": "1"})
+    s.eval.temperature_grid = [0.5, 1.0, 2.0]
+    s.train.artifact_path = str(tmp_path / "t.pgrs")
+    s.eval.max_tokens = 512
+    r = quiet(s)
+    lines = []
+    real = r.log.info
+    r.log.info = lambda msg: (lines.append(msg), real(msg))[1]
+    res = r.run()
+    search = [l for l in lines if l.startswith("temperature_search:")]
+    assert len(search) == 1 and f"optimal_T:{res.eval_temperature}" in search[0] and res.eval_temperature in (0.5, 1.0, 2.0)
+    import json
+    table = json.loads(search[0].split("temperature_search:")[1].split(" optimal_T")[0])
+    assert min(table, key=table.get) == str(res.eval_temperature) and np.isfinite(res.val_loss)
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["eval.auto_temperature=true"]).validate()

@@ -19,6 +19,7 @@ seen those tokens, then adapts on the chunk; the last chunk is never trained on.
 from __future__ import annotations
 
 import json
+import os
 import math
 import time
 from typing import Callable, Dict, List, Optional, Tuple
@@ -182,6 +183,16 @@ def schedule_prefix_docs(tokens: np.ndarray, boundary_id: Optional[int], prefix_
     return min(-(-end // chunk_tokens) * chunk_tokens, tokens.shape[0] - 1)
 
 
+def replicas_agree(lora: dict, world: int, device, agree_fn=agree) -> None:
+    """Debugging aid (``PGB_DEBUG_TTT_SYNC=1``; the reference's PG_DEBUG_DISTRIBUTED_TTT_SYNC, pg-eval/src/gpu_lora_ttt.rs:570-592):
+    after an adapter update every rank must hold the same factors, since all of them applied the same averaged gradient. Compares a
+    checksum of A and B across ranks (max against min) and raises on the rank(s) that see a difference."""
+    cs = float(lora["a"].double().sum()) + 3.0 * float(lora["b"].double().sum()) + float(lora["b"].double().abs().sum())
+    hi, lo = agree_fn([cs], "max", world, device)[0], agree_fn([cs], "min", world, device)[0]
+    if abs(hi - lo) > 1e-9 * max(1.0, abs(hi)):
+        raise RuntimeError(f"test-time-training replicas diverged: adapter checksum {cs!r} here, range over ranks [{lo!r}, {hi!r}]")
+
+
 def chunk_phases(num_chunks: int, phases: int, prefix_chunks: int = 0) -> List[int]:
     """Phase of every chunk (``pg-eval/src/gpu_lora_ttt.rs:688-750``): without a prefix, chunk ``i`` is in phase
     ``i * phases / num_chunks``; with one, the chunks of the leading documents form phase 0 (the warm-up) and the rest is spread
@@ -249,6 +260,8 @@ def eval_lora_phased_ttt(runner, tokens: np.ndarray, model: ModelSpec, ev: EvalS
                     if ev.phased_ttt_weight_decay > 0:
                         runner.lora[key].mul_(1.0 - lr * ev.phased_ttt_weight_decay)
                     runner.lora[key].add_(g[gk], alpha=-lr)
+            if world > 1 and os.environ.get("PGB_DEBUG_TTT_SYNC") == "1":
+                replicas_agree(runner.lora, world, device)
         if rank == 0:
             log("ttt_audit_json=" + json.dumps({"chunk": ci, "phase": phase_of[ci], "prefix_warmup": ci * ev.chunk_tokens < prefix_end, "windows": len(windows), "lr": lr,
                                                 "elapsed_s": round(time.perf_counter() - t0, 3)}))

@@ -313,3 +313,12 @@ def test_phases_and_the_prefix_document_warm_up_schedule():
     assert T.chunk_phases(6, 3, prefix_chunks=1) == [0, 1, 1, 1, 2, 2]
     assert [a["phase"] for a in per_chunk] == [0, 1, 1, 1, 2]            # the last chunk is scored and never trained on: no line
     assert [a["prefix_warmup"] for a in per_chunk] == [True] + [False] * 4 and math.isfinite(loss)
+
+
+def test_replica_agreement_check_catches_a_diverged_adapter():
+    lora = {"a": torch.ones(2, 3, 4), "b": torch.full((2, 4, 3), 0.5)}
+    same = lambda vals, op, world, device: list(vals)
+    T.replicas_agree(lora, 2, "cpu", agree_fn=same)
+    other = lambda vals, op, world, device: [vals[0] + (1e-3 if op == "max" else 0.0)]          # some rank holds different factors
+    with pytest.raises(RuntimeError, match="diverged"):
+        T.replicas_agree(lora, 2, "cpu", agree_fn=other)

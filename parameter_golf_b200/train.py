@@ -816,7 +816,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="parameter_golf_b200.train")
     sub = ap.add_subparsers(dest="cmd", required=True)
     sub.add_parser("keys", help="list every spec key (type, default) and the train_gpt.py environment names that map onto them")
-    for name in ("run", "sweep", "plan", "preflight"):
+    for name in ("run", "sweep", "plan", "preflight", "spec"):
         sp = sub.add_parser(name)
         sp.add_argument("--spec")
         sp.add_argument("--family", "--builtin", dest="family", default=None)
@@ -879,10 +879,14 @@ def main(argv=None) -> int:
         spec.apply_overrides(a.overrides)
         if a.mode:
             spec.mode = a.mode
-        if spec.train.world_size > 1 and a.cmd not in ("plan", "preflight"):
+        if spec.train.world_size > 1 and a.cmd not in ("plan", "preflight", "spec"):
             import torch.distributed as dist
             if not dist.is_initialized():
                 dist.init_process_group("gloo" if spec.train.backend == "cpu" else "nccl")
+        if a.cmd == "spec":              # the resolved spec as a TOML file: every key, after the family, file, environment and overrides
+            spec.validate()
+            print(spec.to_toml(), end="")
+            continue
         if a.cmd == "preflight":         # everything that can be checked about a planned run without a device
             lines, ok = preflight(spec)
             print("\n".join(lines))

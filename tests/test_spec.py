@@ -259,3 +259,15 @@ def test_sweep_architectures_match_the_reference_table():
         arch_variant("nope")
     for k in ARCH_VARIANTS:
         arch_variant(k).validate()
+
+
+def test_spec_subcommand_writes_a_loadable_file_for_every_family(tmp_path, capsys):
+    from parameter_golf_b200.spec import FAMILIES
+    from parameter_golf_b200.train import main
+    for fam in FAMILIES:
+        assert main(["spec", "--family", fam]) == 0
+        f = tmp_path / f"{fam}.toml"
+        f.write_text(capsys.readouterr().out)
+        assert RunSpec.load(str(f)).validate().fingerprint() == family_preset(fam).fingerprint(), fam
+    assert main(["spec", "--family", "tiny_cpu", "model.num_layers=3"]) == 0
+    assert "num_layers = 3" in capsys.readouterr().out

@@ -240,6 +240,8 @@ class TrainSpec:
     record_max_ms_per_step: float = 130.0   # record mode fails closed when the measured step time is above this; 0 disables (PG_RECORD_MAX_MS_PER_STEP)
     timing_skip_steps: int = 0              # steps left out of the measured step time (start-up, PG_RECORD_TIMING_SKIP_STEPS)
     matrix_lr: float = 0.025
+    matrix_optimizer: str = "muon"      # muon | adamw (cpu backend: the banks go to AdamW at adam_matrix_lr; MATRIX_OPTIMIZER / ADAM_LR of the ternary script)
+    adam_matrix_lr: float = 0.05
     scalar_lr: float = 0.025
     embed_lr: float = 0.6
     tied_embed_lr: float = 0.035
@@ -534,6 +536,8 @@ class RunSpec:
         if has("TIED_EMBED_LR"): t.tied_embed_lr = F("TIED_EMBED_LR")
         if has("TIED_EMBED_INIT_STD"): m.tied_embed_init_std = F("TIED_EMBED_INIT_STD")
         if has("MATRIX_LR"): t.matrix_lr = F("MATRIX_LR")
+        if has("MATRIX_OPTIMIZER"): t.matrix_optimizer = "adamw" if env["MATRIX_OPTIMIZER"].lower().startswith("adam") else "muon"
+        if has("ADAM_LR"): t.adam_matrix_lr = F("ADAM_LR")
         if has("SCALAR_LR"): t.scalar_lr = F("SCALAR_LR")
         if has("MUON_MOMENTUM"): t.muon_momentum = F("MUON_MOMENTUM")
         if has("MUON_BACKEND_STEPS"): t.muon_ns_steps = I("MUON_BACKEND_STEPS")
@@ -708,6 +712,8 @@ class RunSpec:
         chk((t.seq_len_start == 0 and t.batch_tokens_start == 0) or t.backend == "cpu",
             "train.seq_len_start and train.batch_tokens_start run on train.backend=cpu only")
         chk(t.prime_steps >= 0, "train.prime_steps must be >= 0")
+        chk(t.matrix_optimizer in ("muon", "adamw") and (t.matrix_optimizer == "muon" or t.backend == "cpu"),
+            "train.matrix_optimizer must be muon or adamw; adamw on the banks runs on train.backend=cpu only")
         chk(0.0 <= t.ema_start_fraction < 1.0 and (t.ema_start_fraction == 0.0 or t.backend == "cpu"),
             "train.ema_start_fraction must be in [0, 1) and runs on train.backend=cpu only (the CUDA optimizer kernels average from the first step)")
         chk(t.seq_len_start == 0 or (0 < t.seq_len_start <= t.seq_len and t.seq_len % t.seq_len_start == 0), "train.seq_len_start must divide train.seq_len")

@@ -54,6 +54,9 @@ def split_param_groups(spec: RunSpec, params: Dict[str, torch.Tensor]):
     groups = [{"names": emb, "lr": emb_lr}, {"names": scalars, "lr": t.scalar_lr}]
     if head:
         groups.append({"names": head, "lr": t.head_lr})
+    if t.matrix_optimizer == "adamw":           # the ternary script's MATRIX_OPTIMIZER=adam: no Muon, the matrices are one more AdamW group
+        groups.append({"names": banks, "lr": t.adam_matrix_lr})
+        banks = []
     return banks, groups
 
 

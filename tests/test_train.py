@@ -782,3 +782,20 @@ def test_trainer_picks_the_evaluation_temperature_from_its_grid(tmp_path, monkey
     assert min(table, key=table.get) == str(res.eval_temperature) and np.isfinite(res.val_loss)
     with pytest.raises(ValueError):
         family_preset("record_11l").apply_overrides(["eval.auto_temperature=true"]).validate()
+
+
+def test_matrices_can_be_trained_with_adamw_instead_of_muon(tmp_path, monkeypatch):
+    monkeypatch.setenv("PGB_DATA_ROOT", str(tmp_path / "data"))
+    s = family_preset("tiny_cpu")
+    s.mode = "smoke"
+    s.apply_env({"MATRIX_OPTIMIZER": "adam", "ADAM_LR": "0.003"})
+    from parameter_golf_b200.train import split_param_groups
+    p = gpt.init_params(s.model, 1)
+    banks, groups = split_param_groups(s, p)
+    assert banks == [] and groups[-1] == {"names": list(gpt.BANKS), "lr": 0.003}
+    s.train.artifact_path = str(tmp_path / "m.pgrs")
+    s.eval.max_tokens = 512
+    res = quiet(s).run()
+    assert res.steps == 4 and np.isfinite(res.val_loss)
+    with pytest.raises(ValueError):
+        family_preset("record_11l").apply_overrides(["train.matrix_optimizer=adamw"]).validate()

@@ -119,7 +119,7 @@ def main(argv=None) -> int:
         luts = luts.with_sidecar(side[: val.shape[0]])
     if a.device == "cpu":
         from .models.runner import OracleRunner
-        runner = OracleRunner(m, params)
+        runner = OracleRunner(m.for_evaluation(spec.eval.depth_recurrence), params)
         runner.temperature = spec.eval.temperature
         if a.find_temperature:
             from .eval.sliding import find_temperature

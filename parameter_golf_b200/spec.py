@@ -199,6 +199,15 @@ class ModelSpec:
         """Attention and MLP of a block both read the block input (split parallel residual)."""
         return self.parallel_residual.enabled and self.parallel_residual.split_attention_mlp
 
+    def for_evaluation(self, depth_recurrence: int = 0) -> "ModelSpec":
+        """The model as the evaluator runs it: a copy whose blocks all repeat ``depth_recurrence`` times when that is > 1."""
+        if depth_recurrence <= 1 or self.cycled:
+            return self
+        import copy
+        m = copy.deepcopy(self)
+        m.recurrence.enabled, m.recurrence.start_layer, m.recurrence.repeat_layers, m.recurrence.repeats = True, 0, self.num_layers, depth_recurrence
+        return m
+
     def xsa_layers(self) -> list:
         """Blocks with the exclusive-self-attention step: the last xsa_last_n layers; in the cycled form every block that runs as
         one of the last xsa_last_n virtual layers (the flag sits on the block, so it holds in all of that block's passes)."""
@@ -360,6 +369,8 @@ class EvalSpec:
     max_eval_seconds: float = 600.0
     temperature: float = 1.0           # capped logits are divided by this when scoring (autograd runner); `find_temperature` picks it
     temperature_grid: list = field(default_factory=lambda: [0.90, 0.95, 1.00, 1.05, 1.10])
+    depth_recurrence: int = 0          # > 1: the autograd evaluator runs every block this many times in a row, whatever the training
+                                       # schedule was (EVAL_DEPTH_RECURRENCE of the ternary script)
     auto_temperature: bool = False     # trainer, cpu backend: pick the temperature from the grid on training tokens before the final evaluation (TEMP_SCALING)
     temperature_calibration_tokens: int = 65536       # training tokens the grid is scored on
     byte_table_seed: int = 20240520
@@ -576,6 +587,7 @@ class RunSpec:
         if has("MUON_WEIGHT_DECAY"): t.muon_wd = F("MUON_WEIGHT_DECAY")
         if has("MTP_HEADS"): m.mtp_num_heads = I("MTP_HEADS")
         if has("TEMP_SCALING"): e.auto_temperature = B("TEMP_SCALING")
+        if has("EVAL_DEPTH_RECURRENCE"): e.depth_recurrence = I("EVAL_DEPTH_RECURRENCE")
         if has("SLIDING_EVAL_STRIDE"): e.stride = I("SLIDING_EVAL_STRIDE")
         if has("SLIDING_BATCH_SIZE"): e.batch_windows = I("SLIDING_BATCH_SIZE")
         if has("VAL_MAX_TOKENS") and I("VAL_MAX_TOKENS") > 0: e.max_tokens = I("VAL_MAX_TOKENS")

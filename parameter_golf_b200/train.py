@@ -710,7 +710,7 @@ class VariantRunner:
                 from .data.shards import load_validation_byte_sidecar
                 luts = luts.with_sidecar(load_validation_byte_sidecar(spec.eval.caseops_byte_sidecar_pattern)[: val.shape[0]])
             if t.backend == "cpu":
-                runner = OracleRunner(m, eval_params)
+                runner = OracleRunner(m.for_evaluation(spec.eval.depth_recurrence), eval_params)
                 runner.temperature = spec.eval.temperature
                 edev = "cpu"
                 if spec.eval.auto_temperature:

@@ -322,3 +322,17 @@ def test_replica_agreement_check_catches_a_diverged_adapter():
     other = lambda vals, op, world, device: [vals[0] + (1e-3 if op == "max" else 0.0)]          # some rank holds different factors
     with pytest.raises(RuntimeError, match="diverged"):
         T.replicas_agree(lora, 2, "cpu", agree_fn=other)
+
+
+def test_evaluation_depth_recurrence_repeats_every_block():
+    s = spec()
+    m = s.model
+    assert m.for_evaluation(0) is m and m.for_evaluation(1) is m
+    e = m.for_evaluation(3)
+    assert gpt.layer_schedule(e) == [(0, 0), (0, 1), (0, 2), (1, 0), (1, 1), (1, 2)] and gpt.layer_schedule(m) == [(0, 0), (1, 0)]
+    assert gpt.param_shapes(e) == gpt.param_shapes(m)                      # the same weights, run more often
+    p = gpt.fill_deterministic(m)
+    ids = torch.randint(0, 32, (2, 16), generator=torch.Generator().manual_seed(0))
+    assert float((gpt.gpt_logits(e, p, ids) - gpt.gpt_logits(m, p, ids)).abs().max()) > 1e-4
+    f = family_preset("tiny_cpu").apply_env({"EVAL_DEPTH_RECURRENCE": "2"})
+    assert f.eval.depth_recurrence == 2

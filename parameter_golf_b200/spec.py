@@ -580,6 +580,26 @@ class RunSpec:
             m.bigram.vocab_size = I("BIGRAM_VOCAB_SIZE")
             m.bigram.enabled = m.bigram.vocab_size > 0
         if has("BIGRAM_DIM"): m.bigram.dim = I("BIGRAM_DIM")
+        # spellings other record scripts use for the same settings
+        if has("ADAM_WEIGHT_DECAY"): t.adam_wd = F("ADAM_WEIGHT_DECAY")
+        if has("BIGRAM_HASH_BUCKETS"):
+            m.bigram.vocab_size = I("BIGRAM_HASH_BUCKETS")
+            m.bigram.enabled = m.bigram.vocab_size > 0
+        if has("BIGRAM_HASH_DIM"): m.bigram.dim = I("BIGRAM_HASH_DIM")
+        if has("EMA_ENABLED") and not B("EMA_ENABLED"): t.ema_decay = 0.0
+        if has("EVAL_BATCH_SEQS"): e.batch_windows = I("EVAL_BATCH_SEQS")
+        if has("SW_EVAL_BATCH"): e.batch_windows = I("SW_EVAL_BATCH")
+        if has("FP16_EMBED_EXPORT") and B("FP16_EMBED_EXPORT"): q.embed_bits = 16
+        if has("INT6_LAYER_START") and has("INT6_LAYER_END") and I("INT6_LAYER_START") >= 0:
+            q.coarse_layers = list(range(I("INT6_LAYER_START"), I("INT6_LAYER_END")))      # int8 codes of these blocks rounded to 64 levels
+            q.coarse_step = 4
+        if has("QAT_THRESHOLD"): t.late_qat_threshold = F("QAT_THRESHOLD")
+        if has("LATE_QAT") and not B("LATE_QAT"): t.late_qat_threshold = 0.0
+        if has("SWA_START_FRAC"): t.swa_threshold = F("SWA_START_FRAC")
+        if has("USE_SMEARGATE"): m.smear_gate = B("USE_SMEARGATE")
+        if has("USE_ZSTD"): q.compression = "zstd22" if B("USE_ZSTD") else q.compression
+        if has("LORA_RANK"): e.doc_lora_rank = I("LORA_RANK")
+        if has("LORA_LR"): e.doc_lora_lr = F("LORA_LR")
         if has("XSA_LAST_N"): m.xsa_last_n = I("XSA_LAST_N")
         if has("GATED_ATTENTION"): m.gated_attention = B("GATED_ATTENTION")
         if has("TRIGRAM"): m.bigram.trigram = B("TRIGRAM")
